@@ -1,0 +1,216 @@
+/* quickdraw_b200 — C ABI of the sm_100a batch-one decode kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as
+ * void*), launches asynchronously on that stream, allocates nothing, owns no device
+ * memory and returns one of the QD_* codes below.  No C++ exception crosses this
+ * boundary.  The functions mirror the host functions of the reference's kernel
+ * backends; each declaration names the reference interface it replaces.
+ *
+ * Formats: bf16 activations; NVFP4 weights as uint8 codes [out, in/2] (low nibble =
+ * even input), float8_e4m3fn block scales [out, in/group], fp32 global scale.
+ */
+#ifndef QUICKDRAW_B200_H
+#define QUICKDRAW_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    QD_OK = 0,
+    QD_ERR_ARG = 1,          /* contract violation detected before launch */
+    QD_ERR_LAUNCH = 2,       /* the CUDA runtime refused the launch */
+    QD_ERR_TIMEOUT = 3,      /* a bounded device-side wait ran out (status word) */
+    QD_ERR_UNSUPPORTED = 4   /* shape outside what the entry point covers */
+};
+
+int qd_version(void);
+const char* qd_error_string(int code);
+
+/* rms_norm(x, gamma, eps) — quickdraw/kernel/triton/norm.py:18-23, qwen.py:19-22.
+ * x, out: [rows, width] bf16 (is_fp32 = 0) or fp32 (1); gamma fp32 [width]. */
+int qd_rms_norm(const void* x, const float* gamma, void* out, int rows, int width, float eps,
+                int is_fp32, void* stream);
+
+/* The step's fused residual update — quickdraw/models/qwen.py:214-217.
+ * normed = bf16(rms_norm(x + residual) * gamma), residual_out = bf16(x + residual);
+ * residual may be NULL (zero); residual_out must not alias an input. */
+int qd_add_rms_norm(const void* x, const void* residual, const float* gamma, void* normed,
+                    void* residual_out, int width, float eps, void* stream);
+
+/* nvfp4_gemv(x, proj, routing_weight=None) — quickdraw/kernel/cute/matvec.py:146-149,
+ * quickdraw/kernel/triton/matvec.py:65-81, arithmetic qwen.py:36-54.
+ * routing_weight: device fp32 scalar or NULL.  force_generic != 0 selects the
+ * shape-generic kernel even where the streaming kernel applies. */
+int qd_nvfp4_gemv(const void* x, const void* codes, const void* scales, const float* global,
+                  const float* routing_weight, void* y, int rows, int in_features,
+                  int group_size, int force_generic, void* stream);
+
+/* expert_gemv(x, proj, ids, weights=None) — quickdraw/kernel/cute/matvec.py:152-154,
+ * quickdraw/kernel/triton/matvec.py:84-99.  Bank [E, rows, in/2]; y [slots, rows];
+ * x [in] or, with per_slot_input, [slots, in]; global fp32 scalar or [E]. */
+int qd_nvfp4_expert_gemv(const void* x, const void* codes, const void* scales, const float* global,
+                         const int32_t* ids, const float* routing, void* y, int rows,
+                         int in_features, int group_size, int slots, int per_slot_input,
+                         int global_per_expert, int force_generic, void* stream);
+
+/* gate_up(x, gate, up, ids=None) — quickdraw/kernel/cute/matvec.py:157-159:
+ * y = bf16(silu(bf16 gate.x)) * bf16(up.x); ids NULL for a plain projection pair. */
+int qd_nvfp4_gate_up(const void* x, const void* gate_codes, const void* gate_scales,
+                     const float* gate_global, const void* up_codes, const void* up_scales,
+                     const float* up_global, const int32_t* ids, void* y, int rows,
+                     int in_features, int group_size, int slots, int global_per_expert,
+                     int force_generic, void* stream);
+
+/* NVFP4Linear.dequantize without the bf16 cast — quickdraw/models/weights.py:21-26,46-55.
+ * hardware_convert != 0 decodes the codes with the sm_100a e2m1x2 convert the streaming
+ * kernels use, 0 with integer bit arithmetic. */
+int qd_nvfp4_dequantize(const void* codes, const void* scales, float global, float* out,
+                        long long rows, int in_features, int group_size, int hardware_convert,
+                        void* stream);
+
+/* F.linear on bf16 with a bf16 result (router, shared-expert gate, DeltaNet a/b, bf16 LM
+ * head) — quickdraw/models/qwen.py:129-130,173,192. */
+int qd_bf16_gemv(const void* x, const void* w, void* y, int rows, int width, void* stream);
+
+/* fp8_gemv(x, proj) — quickdraw/kernel/triton/matvec.py:102-115, qwen.py:25-33. */
+int qd_fp8_gemv(const void* x, const void* w, const float* w_scale, const float* in_scale, void* y,
+                int rows, int width, int is_fp32, void* stream);
+
+/* route(logits, topk) -> (int32 ids, fp32 weights) — quickdraw/kernel/cute/moe.py:87-98,
+ * quickdraw/kernel/triton/moe.py:11-30, qwen.py:174-177.  experts <= 1024, topk <= 32. */
+int qd_route_topk(const void* logits, int logits_fp32, int experts, int topk, int32_t* ids,
+                  float* weights, void* stream);
+
+/* _reduce — quickdraw/kernel/cute/moe.py:61-73, quickdraw/kernel/triton/moe.py:42-57:
+ * out = bf16(sum over slots, ascending expert id) + bf16(shared * bf16(sigmoid(strength))). */
+int qd_moe_combine(const void* contributions, const int32_t* ids, const void* shared,
+                   const void* strength, void* out, int hidden, int topk, void* stream);
+
+/* _silu_kernel — quickdraw/kernel/triton/moe.py:33-39. */
+int qd_swiglu(const void* gate, const void* up, void* out, int n, void* stream);
+
+/* ---- Gated-DeltaNet mixer core — quickdraw/kernel/triton/delta.py:37-121, qwen.py:134-164 */
+
+/* _conv_kernel: depthwise causal conv of one token over [channels, width] taps; shifts the
+ * [channels, width-1] history in place. */
+int qd_gdn_conv(const void* mixed, const void* taps, void* conv_state, void* out, int channels,
+                int width, void* stream);
+
+/* _delta_kernel: l2norm(q,k), decay/beta gates, delta-rule update of the fp32 state
+ * [value_heads, key_dim, value_dim] in place, out = bf16(S^T q).  key_dim <= 128. */
+int qd_gdn_recurrence(const void* conv_qkv, const void* a, const void* b, const void* a_log,
+                      const void* dt_bias, float* rec_state, void* out, int key_heads,
+                      int value_heads, int key_dim, int value_dim, int pdl, void* stream);
+
+/* _gate_kernel: per-head RMSNorm(o) * gamma * silu(z). */
+int qd_gdn_gated_norm(const void* o, const void* z, const void* gamma, void* out, int heads,
+                      int value_dim, float eps, void* stream);
+
+/* ---- GQA decode attention — quickdraw/kernel/triton/attention.py:10-100, qwen.py:66-116.
+ * _prepare and _attend in one launch: q/k RMSNorm (gamma = 1 + w), partial RoPE, cache write
+ * at the position, split-context online softmax, sigmoid output gate.
+ * qg [q_heads, 2*head_dim] (query | gate), k_new/v_new [kv_heads, head_dim], caches
+ * [capacity, kv_heads, head_dim]; out [q_heads*head_dim].  position_dev (int32 device scalar)
+ * overrides position_host when not NULL.  scratch: qd_attn_scratch_floats() floats;
+ * counters: kv_heads zeroed uint32 (the kernel leaves them zero).  head_dim <= 256,
+ * q_heads / kv_heads <= 8. */
+int qd_attn_scratch_floats(int q_heads, int kv_heads, int head_dim, int splits);
+int qd_attn_decode(const void* qg, const void* k_new, const void* v_new, const void* q_norm,
+                   const void* k_norm, void* k_cache, void* v_cache, void* out, float* scratch,
+                   unsigned int* counters, const int* position_dev, int position_host, int capacity,
+                   int q_heads, int kv_heads, int head_dim, int rotary_dim, float theta, float eps,
+                   int splits, int pdl, void* stream);
+
+/* ---- MoE tail — quickdraw/kernel/cute/moe.py:101-116 (expert_gemv(down, routed) +
+ * shared down + _reduce in one launch).  hidden [topk+1, 512] (last row: shared expert).
+ * Either `out` (combined bf16 [hidden_size]) or, for expert parallelism, `routed_out`
+ * (fp32 partial sum over the experts in [expert_lo, expert_hi), bank pointers local to that
+ * range) with `shared_out` (gated shared row); qd_moe_finish adds them after the all-reduce. */
+int qd_moe_down_combine(const void* hidden, const int32_t* ids, const float* weights,
+                        const void* down_codes, const void* down_scales, const float* down_global,
+                        const void* shared_codes, const void* shared_scales, const float* shared_global,
+                        const void* strength, void* out, float* routed_out, void* shared_out,
+                        int hidden_size, int intermediate, int topk, int global_per_expert,
+                        int expert_lo, int expert_hi, int pdl, void* stream);
+int qd_moe_finish(const float* routed, const void* shared, void* out, int n, int pdl, void* stream);
+
+/* ---- Whole decode step — quickdraw/models/qwen.py:196-241 behind Engine.decode_step
+ * (quickdraw/engine/engine.py:114-127).  The caller owns every buffer; the model object is
+ * a host-side table of pointers. */
+typedef struct {
+    const void* codes; const void* scales; const float* global;   /* NVFP4 projection */
+} qd_fp4;
+
+typedef struct {
+    int is_attention;
+    const float* gamma_in; const float* gamma_post;      /* fp32 [hidden]: 1 + layernorm weight */
+    /* DeltaNet: qkv, z, out.  Attention: q(+gate), k, v, o. */
+    qd_fp4 proj_a, proj_b, proj_c, proj_out;
+    const void* in_proj_a; const void* in_proj_b;        /* bf16 [value_heads, hidden] */
+    const void* conv1d; const void* a_log; const void* dt_bias; const void* head_norm;
+    const void* q_norm; const void* k_norm;
+    const void* router; const void* shared_expert_gate;  /* bf16 [experts, hidden], [1, hidden] */
+    qd_fp4 experts_gate, experts_up, experts_down;       /* banks, local to [expert_lo, expert_hi) */
+    qd_fp4 shared_gate, shared_up, shared_down;
+    int experts_global_per_expert;
+    int state_index;                                     /* index into rec/conv or kv arrays */
+} qd_layer;
+
+typedef struct {
+    int hidden, layers, vocab;
+    int q_heads, kv_heads, head_dim, rotary_dim;
+    int key_heads, value_heads, key_dim, value_dim, conv_width;
+    int experts, topk, intermediate;
+    float eps, rope_theta;
+    int expert_lo, expert_hi;                            /* owned expert range (expert parallel) */
+    const void* embed;                                   /* bf16 [vocab, hidden] */
+    const float* final_gamma;                            /* fp32 [hidden] */
+    const void* lm_head;                                 /* bf16 [vocab, hidden] */
+} qd_model_config;
+
+typedef struct {
+    void* kv_k; void* kv_v;      /* bf16 [attention_layers, capacity, kv_heads, head_dim] */
+    float* rec_state;            /* fp32 [linear_layers, value_heads, key_dim, value_dim] */
+    void* conv_state;            /* bf16 [linear_layers, channels, conv_width - 1] */
+    int capacity;
+} qd_state;
+
+typedef struct qd_model qd_model;
+
+int qd_model_create(const qd_model_config* config, qd_model** out);
+int qd_model_set_layer(qd_model* model, int index, const qd_layer* layer);
+int qd_model_destroy(qd_model* model);
+/* Bytes of zero-initialised device workspace one decode stream needs. */
+long long qd_decode_workspace_bytes(const qd_model* model);
+
+/* One token through every layer.  token: int64 device scalar; position: int32 device
+ * scalar (preferred, graph-replayable) or host value.  Writes bf16 logits [vocab] and the
+ * greedy next token (int64 device scalar, lowest index on ties).  phase selects a slice of
+ * the step for expert parallelism: QD_PHASE_ALL runs everything; with QD_PHASE_UNTIL_MOE /
+ * QD_PHASE_AFTER_MOE the caller all-reduces the workspace's routed partial sum between the
+ * two calls for layer `layer`. */
+enum { QD_FLAG_PDL = 1, QD_FLAG_NO_LOGITS = 2 };
+int qd_decode_step(qd_model* model, const qd_state* state, const long long* token,
+                   const int* position_dev, int position_host, void* workspace, void* logits_out,
+                   long long* next_token, int flags, void* stream);
+/* Expert-parallel variant: runs layers [layer_begin, layer_end) and stops after the MoE tail
+ * of the last one with the fp32 routed partial sum in `routed_partial` (hidden floats);
+ * the caller all-reduces it and continues with the next call.  layer_end == layers also
+ * needs the final call with layer_begin == layers for the LM head. */
+int qd_decode_layers(qd_model* model, const qd_state* state, const long long* token,
+                     const int* position_dev, int position_host, void* workspace,
+                     float* routed_partial, int layer_begin, int layer_end, void* logits_out,
+                     long long* next_token, int flags, void* stream);
+
+/* Measurement helper: the streaming NVFP4 matvec over a bank of `matrices` equally shaped
+ * [rows, in_features] matrices, one launch per matrix, so the working set can exceed L2. */
+int qd_nvfp4_gemv_bank(const void* x, const void* codes, const void* scales, const float* global,
+                       void* y, int rows, int in_features, int matrices, int pdl, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

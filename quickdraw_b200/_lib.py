@@ -1,0 +1,95 @@
+"""ctypes binding of ``libquickdraw_b200.so`` (declarations: ``include/quickdraw_b200.h``).
+
+The library is the only execution path of this package: if it cannot be loaded the
+import of any operator raises, there is no PyTorch or CPU fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_void_p
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "libquickdraw_b200.so"
+
+P, I, F, L = c_void_p, c_int, c_float, c_longlong
+
+SIGNATURES = {
+    "qd_version": [],
+    "qd_rms_norm": [P, P, P, I, I, F, I, P],
+    "qd_add_rms_norm": [P, P, P, P, P, I, F, P],
+    "qd_nvfp4_gemv": [P, P, P, P, P, P, I, I, I, I, P],
+    "qd_nvfp4_expert_gemv": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+    "qd_nvfp4_gate_up": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "qd_nvfp4_dequantize": [P, P, F, P, L, I, I, I, P],
+    "qd_bf16_gemv": [P, P, P, I, I, P],
+    "qd_fp8_gemv": [P, P, P, P, P, I, I, I, P],
+    "qd_route_topk": [P, I, I, I, P, P, P],
+    "qd_moe_combine": [P, P, P, P, P, I, I, P],
+    "qd_swiglu": [P, P, P, I, P],
+    "qd_gdn_conv": [P, P, P, P, I, I, P],
+    "qd_gdn_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "qd_gdn_gated_norm": [P, P, P, P, I, I, F, P],
+    "qd_attn_scratch_floats": [I, I, I, I],
+    "qd_attn_decode": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, I, P],
+    "qd_moe_down_combine": [P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+    "qd_moe_finish": [P, P, P, I, I, P],
+    "qd_model_create": [P, P],
+    "qd_model_destroy": [P],
+    "qd_model_set_layer": [P, I, P],
+    "qd_decode_workspace_bytes": [P],
+    "qd_decode_step": [P, P, P, P, I, P, P, P, I, P],
+    "qd_decode_layers": [P, P, P, P, I, P, P, I, I, P, P, I, P],
+    "qd_nvfp4_gemv_bank": [P, P, P, P, P, I, I, I, I, P],
+}
+
+_lib = None
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """Load the CUDA library once; raise loudly if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise LibraryMissing(
+                f"{LIB_PATH} not found: build it with `python -m quickdraw_b200.build` "
+                "(this package has no fallback path)")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(handle, name, None)
+            if fn is None:
+                continue
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        handle.qd_error_string.argtypes = [c_int]
+        handle.qd_error_string.restype = c_char_p
+        _lib = handle
+    return _lib
+
+
+def exported_symbols() -> list[str]:
+    return sorted(SIGNATURES) + ["qd_error_string"]
+
+
+def ptr(t: torch.Tensor | None):
+    """Device address of a tensor (or NULL)."""
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def stream_of(t: torch.Tensor):
+    return c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def check(code: int, name: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{name} failed: {lib().qd_error_string(code).decode()} (code {code})")
+
+
+def call(name: str, *args) -> None:
+    check(getattr(lib(), name)(*args), name)

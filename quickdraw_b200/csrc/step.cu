@@ -1,0 +1,273 @@
+// One decode step of the hybrid MoE model as a fixed sequence of fused launches
+// (reference: quickdraw/models/qwen.py:196-241).  Per layer:
+//   A  residual add + RMSNorm  ->  mixer input projections (+ short conv for DeltaNet)
+//   M  DeltaNet recurrence, or split-context GQA attention
+//   B  (DeltaNet: gated per-head norm ->) output projection
+//   C  residual add + RMSNorm  ->  router logits, shared-expert gate logit, shared gate/up
+//   D  top-k routing            ->  routed gate/up with SwiGLU
+//   E  routed + shared down projections and the combine
+// then   residual add + final RMSNorm -> bf16 LM head with greedy argmax.
+// Every launch can be a programmatic dependent of the one before it, so its weight
+// fetches overlap the predecessor's tail.  The model object is a host-side pointer table.
+#include <new>
+#include <vector>
+
+#include "stream.cuh"
+
+using namespace qd;
+
+struct qd_model {
+    qd_model_config cfg;
+    std::vector<qd_layer> layers;
+    std::vector<char> layer_set;
+};
+
+namespace {
+
+struct Workspace {
+    bf16 *resid[2], *xnorm, *big, *mid, *ab, *o, *mixed, *router_logits, *strength, *hidden, *moe_out, *shared_row;
+    int32_t* ids; float* weights; float* routed_partial; float* attn_scratch;
+    unsigned int* attn_counters; float* best_val; int* best_idx; unsigned int* argmax_counter;
+    unsigned int* status; int* cursor;
+    size_t bytes;
+};
+
+constexpr int kAttnSplits = 32;
+constexpr int kMaxGrid = 256;
+
+size_t align_up(size_t v) { return (v + 255) & ~size_t(255); }
+
+Workspace carve(const qd_model_config& c, uint8_t* base) {
+    Workspace w;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { uint8_t* p = base ? base + off : nullptr; off += align_up(bytes); return p; };
+    const int channels = 2 * c.key_heads * c.key_dim + c.value_heads * c.value_dim;
+    const int q_width = c.q_heads * c.head_dim, kv_width = c.kv_heads * c.head_dim;
+    const int value_width = c.value_heads * c.value_dim;
+    const int big = channels > 2 * q_width ? channels : 2 * q_width;
+    const int mid = value_width > 2 * kv_width ? value_width : 2 * kv_width;
+    const int owide = value_width > q_width ? value_width : q_width;
+    w.cursor = (int*)take(4);                       // which residual buffer is current
+    w.status = (unsigned int*)take(4);
+    w.argmax_counter = (unsigned int*)take(4);
+    w.attn_counters = (unsigned int*)take(4 * c.kv_heads);
+    w.resid[0] = (bf16*)take(2 * c.hidden); w.resid[1] = (bf16*)take(2 * c.hidden);
+    w.xnorm = (bf16*)take(2 * c.hidden);
+    w.big = (bf16*)take(2 * big);
+    w.mid = (bf16*)take(2 * mid);
+    w.ab = (bf16*)take(2 * 2 * c.value_heads);
+    w.o = (bf16*)take(2 * owide);
+    w.mixed = (bf16*)take(2 * c.hidden);
+    w.router_logits = (bf16*)take(2 * c.experts);
+    w.strength = (bf16*)take(2);
+    w.hidden = (bf16*)take(2 * (size_t)(c.topk + 1) * c.intermediate);
+    w.ids = (int32_t*)take(4 * c.topk);
+    w.weights = (float*)take(4 * c.topk);
+    w.moe_out = (bf16*)take(2 * c.hidden);
+    w.shared_row = (bf16*)take(2 * c.hidden);
+    w.routed_partial = (float*)take(4 * c.hidden);
+    w.attn_scratch = (float*)take(4 * (size_t)qd_attn_scratch_floats(c.q_heads, c.kv_heads, c.head_dim, kAttnSplits));
+    w.best_val = (float*)take(4 * kMaxGrid);
+    w.best_idx = (int*)take(4 * kMaxGrid);
+    w.bytes = off;
+    return w;
+}
+
+bool fused_shape_ok(const qd_model_config& c) {
+    return c.hidden == 2048 && c.value_heads * c.value_dim == 4096 && c.q_heads * c.head_dim == 4096 &&
+           c.intermediate == 512 && c.key_dim <= 128 && c.value_dim == 128 && c.topk >= 1 && c.topk <= 8 &&
+           c.experts <= 256 && c.head_dim <= 256 && c.q_heads / c.kv_heads <= 8 && c.conv_width >= 1 &&
+           c.conv_width <= 32;
+}
+
+StreamSeg fp4_seg(const qd_fp4& w, int rows, bf16* y, int epilogue = EP_PLAIN) {
+    StreamSeg s = {};
+    s.w = (const uint8_t*)w.codes; s.s = (const uint8_t*)w.scales; s.g = w.global;
+    s.y = y; s.rows = rows; s.kind = SEG_FP4; s.epilogue = epilogue; s.slot = -1;
+    return s;
+}
+StreamSeg bf16_seg(const void* w, int rows, bf16* y, int epilogue = EP_PLAIN) {
+    StreamSeg s = {};
+    s.w = (const uint8_t*)w; s.y = y; s.rows = rows; s.kind = SEG_BF16; s.epilogue = epilogue; s.slot = -1;
+    return s;
+}
+StreamSeg pair_seg(const qd_fp4& gate, const qd_fp4& up, int rows, bf16* y) {
+    StreamSeg s = fp4_seg(gate, rows, y);
+    s.kind = SEG_FP4_PAIR;
+    s.w2 = (const uint8_t*)up.codes; s.s2 = (const uint8_t*)up.scales; s.g2 = up.global;
+    return s;
+}
+
+#define QD_TRY(expr) do { const int rc_ = (expr); if (rc_ != QD_OK) return rc_; } while (0)
+
+int run_layers(qd_model* m, const qd_state* st, const long long* token, const int* pos_dev, int pos_host,
+               void* workspace, float* routed_partial, int begin, int end, bool head, void* logits,
+               long long* next_token, int flags, cudaStream_t stream) {
+    const qd_model_config& c = m->cfg;
+    if (!fused_shape_ok(c)) return QD_ERR_UNSUPPORTED;
+    const bool pdl = flags & QD_FLAG_PDL;
+    const bool ep = routed_partial != nullptr;
+    Workspace w = carve(c, (uint8_t*)workspace);
+    const int H = c.hidden;
+    const int channels = 2 * c.key_heads * c.key_dim + c.value_heads * c.value_dim;
+    const int value_width = c.value_heads * c.value_dim;
+    const int q_width = c.q_heads * c.head_dim, kv_width = c.kv_heads * c.head_dim;
+    // Residual ping-pong: every add+norm flips it; two flips per layer, so the buffer index at
+    // the start of layer L is always 0.
+    for (int L = begin; L < end; ++L) {
+        const qd_layer& ly = m->layers[L];
+        if (!m->layer_set[L]) return QD_ERR_ARG;
+        if (ep && L > 0 && L == begin) QD_TRY(qd_moe_finish(routed_partial, w.shared_row, w.moe_out, H, pdl, stream));
+        // ---- A
+        StreamParams a = {};
+        a.width = H; a.prologue = PRO_ADD_NORM; a.gamma = ly.gamma_in; a.eps = c.eps;
+        a.residual_out = w.resid[1]; a.status = w.status; a.expert_hi = 0x7fffffff;
+        if (L == 0) { a.token = token; a.embed = (const bf16*)c.embed; a.residual = nullptr; }
+        else { a.x = w.moe_out; a.residual = w.resid[0]; }
+        if (ly.is_attention) {
+            a.nseg = 3;
+            a.seg[0] = fp4_seg(ly.proj_a, 2 * q_width, w.big);
+            a.seg[1] = fp4_seg(ly.proj_b, kv_width, w.mid);
+            a.seg[2] = fp4_seg(ly.proj_c, kv_width, w.mid + kv_width);
+        } else {
+            a.nseg = 4;
+            a.seg[0] = fp4_seg(ly.proj_a, channels, w.big, EP_CONV);
+            a.seg[1] = fp4_seg(ly.proj_b, value_width, w.mid);
+            a.seg[2] = bf16_seg(ly.in_proj_a, c.value_heads, w.ab);
+            a.seg[3] = bf16_seg(ly.in_proj_b, c.value_heads, w.ab + c.value_heads);
+            a.conv_state = (bf16*)st->conv_state + (size_t)ly.state_index * channels * (c.conv_width - 1);
+            a.conv_taps = (const bf16*)ly.conv1d; a.conv_width = c.conv_width;
+        }
+        QD_TRY(stream_launch(a, 0, stream, pdl));
+        // ---- M and B
+        StreamParams b = {};
+        b.width = 4096; b.status = w.status; b.expert_hi = 0x7fffffff; b.eps = c.eps;
+        b.x = w.o; b.nseg = 1; b.seg[0] = fp4_seg(ly.proj_out, H, w.mixed);
+        if (ly.is_attention) {
+            const size_t layer_elems = (size_t)st->capacity * kv_width;
+            QD_TRY(qd_attn_decode(w.big, w.mid, w.mid + kv_width, ly.q_norm, ly.k_norm,
+                                  (bf16*)st->kv_k + ly.state_index * layer_elems,
+                                  (bf16*)st->kv_v + ly.state_index * layer_elems, w.o, w.attn_scratch,
+                                  w.attn_counters, pos_dev, pos_host, st->capacity, c.q_heads, c.kv_heads,
+                                  c.head_dim, c.rotary_dim, c.rope_theta, c.eps, kAttnSplits, pdl, stream));
+            b.prologue = PRO_NONE;
+        } else {
+            QD_TRY(qd_gdn_recurrence(w.big, w.ab, w.ab + c.value_heads, ly.a_log, ly.dt_bias,
+                                     st->rec_state + (size_t)ly.state_index * c.value_heads * c.key_dim * c.value_dim,
+                                     w.o, c.key_heads, c.value_heads, c.key_dim, c.value_dim, pdl, stream));
+            b.prologue = PRO_GATED_NORM; b.z = w.mid; b.head_gamma = (const bf16*)ly.head_norm; b.head_dim = c.value_dim;
+        }
+        QD_TRY(stream_launch(b, 0, stream, pdl));
+        // ---- C
+        StreamParams cc = {};
+        cc.width = H; cc.prologue = PRO_ADD_NORM; cc.gamma = ly.gamma_post; cc.eps = c.eps;
+        cc.x = w.mixed; cc.residual = w.resid[1]; cc.residual_out = w.resid[0]; cc.x_out = w.xnorm;
+        cc.status = w.status; cc.expert_hi = 0x7fffffff;
+        cc.nseg = 3;
+        cc.seg[0] = bf16_seg(ly.router, c.experts, w.router_logits);
+        cc.seg[1] = bf16_seg(ly.shared_expert_gate, 1, w.strength);
+        cc.seg[2] = pair_seg(ly.shared_gate, ly.shared_up, c.intermediate, w.hidden + (size_t)c.topk * c.intermediate);
+        QD_TRY(stream_launch(cc, 0, stream, pdl));
+        // ---- D
+        StreamParams d = {};
+        d.width = H; d.prologue = PRO_NONE; d.x = w.xnorm; d.status = w.status;
+        d.router_logits = w.router_logits; d.experts = c.experts; d.topk = c.topk;
+        d.ids_out = w.ids; d.weights_out = w.weights;
+        d.expert_lo = c.expert_lo; d.expert_hi = c.expert_hi;
+        d.nseg = c.topk;
+        for (int s = 0; s < c.topk; ++s) {
+            StreamSeg sg = pair_seg(ly.experts_gate, ly.experts_up, c.intermediate, w.hidden + (size_t)s * c.intermediate);
+            sg.slot = s; sg.g_per_expert = ly.experts_global_per_expert;
+            sg.w_stride = (long long)c.intermediate * (H / 2);
+            sg.s_stride = (long long)c.intermediate * (H / 16);
+            d.seg[s] = sg;
+        }
+        QD_TRY(stream_launch(d, 0, stream, pdl));
+        // ---- E
+        QD_TRY(qd_moe_down_combine(w.hidden, w.ids, w.weights, ly.experts_down.codes, ly.experts_down.scales,
+                                   ly.experts_down.global, ly.shared_down.codes, ly.shared_down.scales,
+                                   ly.shared_down.global, w.strength, ep ? nullptr : w.moe_out,
+                                   ep ? routed_partial : nullptr, ep ? w.shared_row : nullptr, H, c.intermediate,
+                                   c.topk, ly.experts_global_per_expert, c.expert_lo, c.expert_hi, pdl, stream));
+    }
+    if (head) {
+        if (ep) QD_TRY(qd_moe_finish(routed_partial, w.shared_row, w.moe_out, H, pdl, stream));
+        StreamParams h = {};
+        h.width = H; h.prologue = PRO_ADD_NORM; h.gamma = c.final_gamma; h.eps = c.eps;
+        h.x = w.moe_out; h.residual = w.resid[0]; h.residual_out = w.resid[1];
+        h.status = w.status; h.expert_hi = 0x7fffffff;
+        h.nseg = 1;
+        h.seg[0] = bf16_seg(c.lm_head, c.vocab, (bf16*)logits, EP_ARGMAX);
+        h.best_val = w.best_val; h.best_idx = w.best_idx; h.counter = w.argmax_counter; h.token_out = next_token;
+        int grid = stream_sm_count();
+        if (grid > kMaxGrid) grid = kMaxGrid;
+        QD_TRY(stream_launch(h, grid, stream, pdl));
+    }
+    return QD_OK;
+}
+
+}  // namespace
+
+extern "C" int qd_model_create(const qd_model_config* config, qd_model** out) {
+    QD_CHECK_ARG(config && out && config->layers > 0 && config->hidden > 0);
+    qd_model* m = new (std::nothrow) qd_model();
+    if (!m) return QD_ERR_ARG;
+    m->cfg = *config;
+    m->layers.resize(config->layers);
+    m->layer_set.assign(config->layers, 0);
+    *out = m;
+    return QD_OK;
+}
+
+extern "C" int qd_model_set_layer(qd_model* model, int index, const qd_layer* layer) {
+    QD_CHECK_ARG(model && layer && index >= 0 && index < model->cfg.layers);
+    model->layers[index] = *layer;
+    model->layer_set[index] = 1;
+    return QD_OK;
+}
+
+extern "C" int qd_model_destroy(qd_model* model) {
+    delete model;
+    return QD_OK;
+}
+
+extern "C" long long qd_decode_workspace_bytes(const qd_model* model) {
+    if (!model) return -1;
+    return (long long)carve(model->cfg, nullptr).bytes;
+}
+
+extern "C" int qd_decode_step(qd_model* model, const qd_state* state, const long long* token,
+                              const int* position_dev, int position_host, void* workspace, void* logits_out,
+                              long long* next_token, int flags, void* stream) {
+    QD_CHECK_ARG(model && state && token && workspace && logits_out && next_token);
+    return run_layers(model, state, token, position_dev, position_host, workspace, nullptr, 0, model->cfg.layers,
+                      !(flags & QD_FLAG_NO_LOGITS), logits_out, next_token, flags, (cudaStream_t)stream);
+}
+
+extern "C" int qd_decode_layers(qd_model* model, const qd_state* state, const long long* token,
+                                const int* position_dev, int position_host, void* workspace,
+                                float* routed_partial, int layer_begin, int layer_end, void* logits_out,
+                                long long* next_token, int flags, void* stream) {
+    QD_CHECK_ARG(model && state && token && workspace && routed_partial);
+    QD_CHECK_ARG(layer_begin >= 0 && layer_begin <= layer_end && layer_end <= model->cfg.layers);
+    const bool head = layer_begin == model->cfg.layers;
+    QD_CHECK_ARG(!head || (logits_out && next_token));
+    return run_layers(model, state, token, position_dev, position_host, workspace, routed_partial, layer_begin,
+                      layer_end, head, logits_out, next_token, flags, (cudaStream_t)stream);
+}
+
+extern "C" int qd_nvfp4_gemv_bank(const void* x, const void* codes, const void* scales, const float* global,
+                                  void* y, int rows, int in_features, int matrices, int pdl, void* stream) {
+    QD_CHECK_ARG(x && codes && scales && global && y && rows > 0 && matrices > 0);
+    if (in_features != 2048 && in_features != 4096) return QD_ERR_UNSUPPORTED;
+    for (int i = 0; i < matrices; ++i) {
+        StreamParams p = {};
+        p.width = in_features; p.prologue = PRO_NONE; p.x = (const bf16*)x; p.expert_hi = 0x7fffffff;
+        p.nseg = 1;
+        qd_fp4 w = {(const uint8_t*)codes + (size_t)i * rows * (in_features / 2),
+                    (const uint8_t*)scales + (size_t)i * rows * (in_features / 16), global};
+        p.seg[0] = fp4_seg(w, rows, (bf16*)y + (size_t)i * rows);
+        QD_TRY(stream_launch(p, 0, (cudaStream_t)stream, pdl != 0));
+    }
+    return QD_OK;
+}

@@ -1,0 +1,145 @@
+"""Single-request greedy generation on the B200 decode kernels.
+
+Same surface and behaviour as the reference engine (quickdraw/engine/engine.py:10-148):
+``Engine(ckpt, max_context, device, backend, *, kernels, step, cuda_graph, ...)``, the
+attributes ``state, pending_token, eos_token_ids, graph, step, ckpt, max_context, backend``
+and the methods ``capture_decode, prefill, decode_step, generate, reset``.  The engine
+owns ``state.position``; a step never touches it.  ``reset`` zeroes the recurrent and
+convolution history, keeps every buffer address (a captured graph stays valid) and leaves
+the KV cache alone (slots at or beyond the position are never read).
+
+Backends: ``"b200"`` (default) runs the fused CUDA step where the checkpoint has the
+36B-A3B widths and the composed operator table otherwise; passing ``kernels=`` or
+``step=`` gives the ``"custom"`` backend used by tests (no graph).  There is no CPU
+backend: on a CPU device only a caller-supplied ``step`` can run.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .state import DecodeState
+from .weights import Checkpoint
+
+
+class Engine:
+    def __init__(self, ckpt: Checkpoint, max_context: int = 32768, device: str = "cuda",
+                 backend: str | None = None, *, kernels: dict | None = None, step=None,
+                 cuda_graph: bool = True, prefill_chunk_size: int = 128,
+                 sequence_prefill: bool = True):
+        custom = kernels is not None or step is not None
+        if backend is None:
+            backend = "custom" if custom else "b200"
+        assert backend in ("b200", "custom")
+        assert kernels is None or step is None
+        assert backend == "custom" or not custom
+        assert max_context > 0 and prefill_chunk_size > 0
+        self.ckpt, self.max_context, self.device, self.backend = ckpt, max_context, device, backend
+        self.prefill_chunk_size = prefill_chunk_size
+        self.sequence_prefill = False      # token-loop prefill; kept for interface parity
+        self.graph = None
+        self.fused = None
+        on_cuda = torch.device(device).type == "cuda"
+        if step is not None:
+            self.step = step
+        else:
+            assert on_cuda, "the b200 backend needs a CUDA device; there is no CPU path"
+            from . import fused
+            from .kernels import bind_kernels
+            if kernels is None and fused.supports(ckpt):
+                self.fused = fused.FusedStep(ckpt)
+                self.step = self.fused
+            else:
+                prepared = ([(1 + l.input_layernorm.float(), 1 + l.post_attention_layernorm.float())
+                             for l in ckpt.layers], 1 + ckpt.final_norm.float())
+                self.step = bind_kernels(prepared=prepared, **(kernels or {}))["forward_step"]
+        self.state = DecodeState.allocate(ckpt.config, max_context, device)
+        self.pending_token: torch.Tensor | None = None
+        self.eos_token_ids: set[int] = set()
+        if backend == "b200" and cuda_graph:
+            self.capture_decode()
+
+    # ----------------------------------------------------------------- graph capture
+    @torch.inference_mode()
+    def capture_decode(self):
+        """Capture one decode step (position read from a device scalar) plus the greedy
+        selection; three warm-up steps run on a scratch state first
+        (quickdraw/engine/engine.py:65-83)."""
+        assert self.backend == "b200" and self.state.position == 0
+        dev = self.device
+        self._decode_input = torch.zeros((), dtype=torch.long, device=dev)
+        self._device_position = torch.zeros((), dtype=torch.int32, device=dev)
+        self._decode_output = torch.empty((), dtype=torch.long, device=dev)
+        scratch = DecodeState(torch.empty_like(self.state.kv_k), torch.empty_like(self.state.kv_v),
+                              torch.zeros_like(self.state.rec_state),
+                              torch.zeros_like(self.state.conv_state), 0)
+        stream = torch.cuda.Stream(device=dev)
+        stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                self.step(self.ckpt, self._decode_input, self._device_position, scratch)
+        torch.cuda.current_stream(dev).wait_stream(stream)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=stream):
+            logits = self.step(self.ckpt, self._decode_input, self._device_position, self.state)
+            if self.fused is not None:
+                self._decode_output.copy_(self.fused.next_token)
+            else:
+                torch.argmax(logits, out=self._decode_output)
+            self._decode_logits = logits
+        del scratch
+        self.reset()
+
+    # ----------------------------------------------------------------------- requests
+    @torch.inference_mode()
+    def prefill(self, token_ids: list[int]) -> torch.Tensor:
+        """Start a fresh request: run the prompt token by token, return the logits after
+        its last token (quickdraw/engine/engine.py:93-111)."""
+        assert 0 < len(token_ids) <= self.max_context, "prompt must fit within max_context"
+        self.reset()
+        tokens = torch.tensor(token_ids, dtype=torch.long, device=self.device)
+        logits = None
+        for index, token in enumerate(tokens):
+            if self.backend == "b200":
+                logits = self.step(self.ckpt, token, self.state.position, self.state,
+                                   logits=index == len(tokens) - 1)
+            else:
+                logits = self.step(self.ckpt, token, self.state.position, self.state)
+            self.state.position += 1
+        return logits
+
+    @torch.inference_mode()
+    def decode_step(self) -> torch.Tensor:
+        """Process the pending token, select and return its successor (0-d int64)."""
+        assert self.pending_token is not None, "select a pending token before decode"
+        assert self.state.position < self.max_context, "context capacity reached"
+        if self.graph is None:
+            logits = self.step(self.ckpt, self.pending_token, self.state.position, self.state)
+            self.pending_token = torch.argmax(logits)
+        else:
+            self._decode_input.copy_(self.pending_token)
+            self._device_position.fill_(self.state.position)
+            self.graph.replay()
+            self.pending_token = self._decode_output.clone()
+        self.state.position += 1
+        return self.pending_token
+
+    @torch.inference_mode()
+    def generate(self, token_ids: list[int], max_tokens: int) -> list[int]:
+        """New token ids, EOS included; stops before a step would exceed the capacity."""
+        assert max_tokens >= 0, "max_tokens must be nonnegative"
+        if max_tokens == 0:
+            return []
+        logits = self.prefill(token_ids)
+        self.pending_token = torch.argmax(logits)
+        output = [int(self.pending_token.item())]
+        while (len(output) < max_tokens and output[-1] not in self.eos_token_ids
+               and self.state.position < self.max_context):
+            output.append(int(self.decode_step().item()))
+        return output
+
+    def reset(self) -> None:
+        self.state.rec_state.zero_()
+        self.state.conv_state.zero_()
+        self.state.position = 0
+        self.pending_token = None

@@ -1,0 +1,124 @@
+"""GPU parity of the token step and the engine: composed operator-table step and fused
+C-ABI step against the CPU oracle (greedy tokens, logits, state), CUDA-graph replay
+against eager execution, and engine control flow on the device."""
+
+import pytest
+import torch
+
+from oracle import decode_oracle as O
+from quickdraw_b200 import synthetic
+from quickdraw_b200.state import DecodeState
+from quickdraw_b200.synthetic import to_device
+from tests.golden.fixture_io import from_tree
+
+pytestmark = pytest.mark.gpu
+
+
+def small_real_width(layers=4, experts=16, vocab=2048, seed=11, device="cuda"):
+    """Real widths (hidden 2048, 128/256-wide heads, intermediate 512), reduced depth,
+    expert count and vocabulary so the CPU oracle finishes in seconds."""
+    cfg = synthetic.model_config(num_layers=layers, vocab_size=vocab, experts=experts, topk=8)
+    return synthetic.make_checkpoint(cfg, seed=seed, device=device)
+
+
+def test_composed_step_reproduces_reference_generation(cuda_device, reference_outputs):
+    from quickdraw_b200.engine import Engine
+    ckpt = to_device(from_tree(reference_outputs["mini_ckpt"]), cuda_device)
+    gen = from_tree(reference_outputs["generation"])
+    engine = Engine(ckpt, max_context=32, device="cuda", cuda_graph=False)
+    assert engine.fused is None          # hidden 256: composed operator table
+    engine.state.kv_k.fill_(9.0)
+    engine.state.kv_v.fill_(-11.0)
+    tokens = engine.generate(gen["prompt"], len(gen["tokens"]))
+    assert tokens == gen["tokens"]
+    torch.testing.assert_close(engine.state.rec_state.cpu(), gen["rec_after"], rtol=1e-2, atol=1e-4)
+    used = engine.state.position
+    assert O.rel_l2(engine.state.kv_k[:, :used].cpu(), gen["k_after"][:, :used]) < 1e-2
+    assert torch.equal(engine.state.kv_k[:, used:].cpu(), gen["k_after"][:, used:])   # untouched slots
+
+
+def _oracle_tokens(ckpt_cpu, prompt, steps, capacity):
+    state = DecodeState.allocate(ckpt_cpu.config, capacity, "cpu")
+    state.kv_k.zero_()
+    state.kv_v.zero_()
+    return O.greedy_decode(ckpt_cpu, state, prompt, steps), state
+
+
+@pytest.fixture(scope="module")
+def real_width_case(cuda_device):
+    ckpt = small_real_width()
+    ckpt_cpu = to_device(ckpt, "cpu")
+    prompt = [5, 1900, 77, 1033, 640, 12]
+    tokens, state = _oracle_tokens(ckpt_cpu, prompt, 64, 96)
+    return ckpt, ckpt_cpu, prompt, tokens, state
+
+
+def test_fused_step_single_token_matches_oracle(cuda_device, real_width_case):
+    from quickdraw_b200.fused import FusedStep
+    ckpt, ckpt_cpu, *_ = real_width_case
+    step = FusedStep(ckpt)
+    state = DecodeState.allocate(ckpt.config, 96, "cuda")
+    ref = DecodeState.allocate(ckpt.config, 96, "cpu")
+    for position, token in enumerate([7, 1500, 3]):
+        got = step(ckpt, torch.tensor(token, device="cuda"), position, state)
+        want = O.forward_step(ckpt_cpu, torch.tensor(token), position, ref)
+        assert O.rel_l2(got.cpu(), want) < 1e-2
+        assert int(step.next_token) == int(got.float().argmax())
+    assert step.status() == 0
+    assert O.rel_l2(state.rec_state.cpu(), ref.rec_state) < 1e-2
+    assert O.rel_l2(state.conv_state.cpu(), ref.conv_state) < 1e-2
+    assert O.rel_l2(state.kv_k[:, :3].cpu(), ref.kv_k[:, :3]) < 1e-2
+
+
+def test_fused_matches_composed(cuda_device, real_width_case):
+    from quickdraw_b200.fused import FusedStep
+    from quickdraw_b200.kernels import bind_kernels
+    ckpt = real_width_case[0]
+    fused, composed = FusedStep(ckpt), bind_kernels()["forward_step"]
+    s1, s2 = (DecodeState.allocate(ckpt.config, 16, "cuda") for _ in range(2))
+    for position, token in enumerate([9, 100, 2000, 31]):
+        t = torch.tensor(token, device="cuda")
+        a, b = fused(ckpt, t, position, s1), composed(ckpt, t, position, s2)
+        assert O.rel_l2(a.cpu(), b.cpu()) < 1e-2
+    assert O.rel_l2(s1.rec_state.cpu(), s2.rec_state.cpu()) < 1e-2
+
+
+def test_greedy_64_tokens_identical_to_oracle(cuda_device, real_width_case):
+    from quickdraw_b200.engine import Engine
+    ckpt, _, prompt, want, _ = real_width_case
+    engine = Engine(ckpt, max_context=96, device="cuda")
+    assert engine.fused is not None and engine.graph is not None
+    engine.state.kv_k.zero_()
+    engine.state.kv_v.zero_()
+    got = engine.generate(prompt, 64)
+    first_diff = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), None)
+    assert got == want, f"first mismatch at generated token {first_diff}"
+    assert engine.fused.status() == 0
+
+
+def test_graph_replay_equals_eager(cuda_device, real_width_case):
+    from quickdraw_b200.engine import Engine
+    ckpt, _, prompt, *_ = real_width_case
+    eager = Engine(ckpt, max_context=40, device="cuda", cuda_graph=False)
+    graph = Engine(ckpt, max_context=40, device="cuda", cuda_graph=True)
+    for _ in range(2):        # second round exercises reset + replay
+        a, b = eager.generate(prompt, 20), graph.generate(prompt, 20)
+        assert a == b
+        assert torch.equal(eager.state.rec_state, graph.state.rec_state)
+        assert torch.equal(eager.state.conv_state, graph.state.conv_state)
+        used = eager.state.position
+        assert torch.equal(eager.state.kv_k[:, :used], graph.state.kv_k[:, :used])
+
+
+def test_engine_capacity_and_eos(cuda_device, real_width_case):
+    from quickdraw_b200.engine import Engine
+    ckpt, _, prompt, want, _ = real_width_case
+    engine = Engine(ckpt, max_context=len(prompt) + 3, device="cuda")
+    out = engine.generate(prompt, 50)
+    assert out == want[:4] and engine.state.position == len(prompt) + 3
+    with pytest.raises(AssertionError):
+        engine.decode_step()
+    engine.eos_token_ids = {want[2]}
+    assert engine.generate(prompt, 50) == want[:3]
+    with pytest.raises(AssertionError):
+        engine.generate(list(range(engine.max_context + 1)), 1)
