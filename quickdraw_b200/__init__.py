@@ -15,9 +15,9 @@ def __getattr__(name):
     if name == "Engine":
         from .engine import Engine
         return Engine
-    if name in ("bind_kernels", "kernels"):
-        from . import kernels as _k
-        return getattr(_k, name)
+    if name == "bind_kernels":
+        import importlib
+        return importlib.import_module(".kernels", __name__).bind_kernels
     raise AttributeError(name)
 
 

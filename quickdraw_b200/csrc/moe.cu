@@ -105,7 +105,11 @@ moe_down_kernel(const __grid_constant__ DownParams p) {
         else scale = round_bf16(p.dg[p.g_per_expert ? e - p.expert_lo : 0] * s_w[s]);
         const bool ok = !owned || mbar_wait(bar, 0, p.status);
         const uint8_t* base = smem + (size_t)s * kDownMaxRows * kDownRowBytes;
-        for (int r = half; r < n; r += 2) {
+        // both half-warps run the same number of iterations (the shuffles below name all
+        // 32 lanes); a half-warp past the last row recomputes it and does not store.
+        for (int rr = 0; rr < n; rr += 2) {
+            const bool live = rr + half < n;
+            const int r = live ? rr + half : n - 1;
             float value = 0.f;
             if (owned && ok) {
                 const uint4 w = lds128(base + r * (kDownWidth / 2) + hl * 16);
@@ -128,7 +132,7 @@ moe_down_kernel(const __grid_constant__ DownParams p) {
                 acc = group_sum<16>(acc) * mult;
                 value = shared ? round_bf16(acc * scale) : round_bf16(round_bf16(acc) * scale);
             }
-            if (hl == 0) contrib[s * kDownMaxRows + r] = value;
+            if (hl == 0 && live) contrib[s * kDownMaxRows + r] = value;
         }
     }
     __syncthreads();

@@ -41,7 +41,12 @@ def _oracle_tokens(ckpt_cpu, prompt, steps, capacity):
     state = DecodeState.allocate(ckpt_cpu.config, capacity, "cpu")
     state.kv_k.zero_()
     state.kv_v.zero_()
-    return O.greedy_decode(ckpt_cpu, state, prompt, steps), state
+    O.cache_dequantised(True)       # the same few matrices every step
+    try:
+        with torch.inference_mode():
+            return O.greedy_decode(ckpt_cpu, state, prompt, steps), state
+    finally:
+        O.cache_dequantised(False)
 
 
 @pytest.fixture(scope="module")
