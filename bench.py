@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Batch-one greedy decode benchmark of the synthetic 36B-A3B NVFP4 hybrid MoE model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one decode token through all 48 layers and the LM head.  The model is
+generated on the device from a fixed seed (no checkpoint ships with the package), the
+prompt is 512 uniform random token ids.  Rank 0 prints one JSON line:
+
+  value      decode tokens/s, device-timed (CUDA events around K graph replays, inputs
+             resident in HBM), max over ranks;
+  e2e        the same through ``Engine.decode_step`` with the token and position coming
+             from pinned host memory and the selected token read back every step;
+  roofline   the NVFP4 streaming matvec on the single-matvec configuration
+             ([1024, 2048] fused gate+up of one expert) over a bank of 256 distinct
+             matrices (302 MB, larger than L2), algorithmic bytes / CUDA-event time per
+             launch against the measured HBM copy bandwidth;
+  cpu_baseline  the CPU oracle (a port of the reference's PyTorch path) timed on this
+             host on a bounded sample: one 4-layer group and the LM head, scaled to 48 layers.
+
+``--impl reference`` times only that CPU path and prints the same line shape.
+With N > 1 (torchrun) the routed experts are sharded across ranks (expert parallel);
+every rank runs the replicated parts, one fp32 all-reduce of the routed partial sum per
+layer goes over NCCL.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PROMPT_LEN = 512
+BF16 = torch.bfloat16
+CONFIG1_BYTES = 1024 * 1024 + 1024 * 128 + 4 + 4096 + 2048     # weights + x + y of one matvec
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def bytes_per_token(cfg, position: int) -> int:
+    """Algorithmic HBM bytes of one decode token: every weight the token touches once
+    (selected experts only), recurrent/conv state read and written, KV history read."""
+    h, inter = cfg.hidden_size, cfg.moe_intermediate_size
+    fp4 = lambda out, inp: out * inp // 2 + out * inp // 16 + 4
+    moe = (cfg.num_experts * h * 2 + h * 2
+           + (cfg.num_experts_per_tok + 1) * (2 * fp4(inter, h) + fp4(h, inter)))
+    kw = cfg.linear_num_key_heads * cfg.linear_key_head_dim
+    vw = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+    gdn_w = fp4(2 * kw + vw, h) + fp4(vw, h) + fp4(h, vw) + 2 * cfg.linear_num_value_heads * h * 2 \
+        + (2 * kw + vw) * cfg.linear_conv_kernel_dim * 2
+    rec = cfg.linear_num_value_heads * cfg.linear_key_head_dim * cfg.linear_value_head_dim * 4
+    conv = (2 * kw + vw) * (cfg.linear_conv_kernel_dim - 1) * 2
+    gdn = gdn_w + 2 * rec + 2 * conv
+    qw, kvw = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    attn = fp4(2 * qw, h) + 2 * fp4(kvw, h) + fp4(h, qw) + 2 * kvw * 2 * (position + 1)
+    n_full = cfg.layer_types.count("full_attention")
+    n_lin = cfg.num_hidden_layers - n_full
+    norms = (2 * cfg.num_hidden_layers + 1) * h * 4
+    return (cfg.num_hidden_layers * moe + n_lin * gdn + n_full * attn
+            + cfg.vocab_size * h * 2 + norms + h * 2)
+
+
+class ClockSampler:
+    """nvidia-smi SM clock / throttle-reason samples while a timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = sorted({n for r in self.rows if len(r) >= 6
+                          for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        mx = max((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), default=None)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# ------------------------------------------------------------------ CPU oracle timing
+def cpu_sample(cfg, threads: int):
+    """Seconds per token of the CPU oracle, from one 4-layer group and the LM head."""
+    from oracle import decode_oracle as O
+    from quickdraw_b200 import synthetic
+    from quickdraw_b200.state import DecodeState
+    torch.set_num_threads(threads)
+    group = cfg.full_attention_interval
+    sub = synthetic.model_config(num_layers=group, vocab_size=cfg.vocab_size, interval=group)
+    ckpt = synthetic.make_checkpoint(sub, seed=0, device="cpu")
+    state = DecodeState.allocate(sub, 1024, "cpu")
+    state.kv_k.normal_()
+    state.kv_v.normal_()
+    with torch.inference_mode():
+        x = torch.nn.functional.embedding(torch.tensor(7), ckpt.embed_tokens)
+
+        def layers_once():
+            step = O.forward_step(ckpt, torch.tensor(7), PROMPT_LEN + 128, state, logits=False)
+            return step
+
+        def head_once():
+            normed, _ = O.add_norm(x, torch.zeros_like(x), 1 + ckpt.final_norm.float(), sub.rms_norm_eps)
+            return O.project(normed, ckpt.lm_head)
+        layers_once()
+        times = []
+        for _ in range(2):
+            t = time.perf_counter()
+            layers_once()
+            times.append(time.perf_counter() - t)
+        t = time.perf_counter()
+        head_once()
+        head = time.perf_counter() - t
+    per_group = sorted(times)[0]
+    return per_group * (cfg.num_hidden_layers / group) + head, per_group, head
+
+
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    from quickdraw_b200 import synthetic
+    cfg = synthetic.model_config()
+    threads = len(os.sched_getaffinity(0))
+    t0 = time.perf_counter()
+    samples = []
+    for _ in range(max(1, min(args.steps, 3))):
+        per_token, per_group, head = cpu_sample(cfg, threads)
+        samples.append(per_token)
+        if time.perf_counter() - t0 > 150:
+            break
+    per_token = sorted(samples)[len(samples) // 2]
+    value = 1.0 / per_token
+    sample = ("one 4-layer group (3 DeltaNet + 1 attention + 4 MoE blocks) and the bf16 LM head at "
+              "position 640, group time x12 + head time")
+    line = {
+        "impl": "reference", "metric": "batch-1 decode tok/s (36B-A3B NVFP4 MoE)", "value": value,
+        "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": per_token * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 activations, NVFP4 (E2M1 + E4M3 block scale) weights, fp32 accumulate",
+        "data": "synthetic", "config": workload_config(cfg, world),
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, world):
+    return {"workload": "config 4: synthetic 36B-A3B hybrid (36 gated-DeltaNet + 12 GQA layers, "
+                        "256-expert top-8 NVFP4 MoE, vocab 151936), 512-token prompt then greedy decode, batch 1",
+            "layers": cfg.num_hidden_layers, "prompt": PROMPT_LEN,
+            "parallelism": "single GPU" if world == 1 else f"expert parallel x{world} (experts sharded, rest replicated)",
+            "l2": "every token streams ~2.5 GB of weights, far beyond the 126 MB L2; no flush needed"}
+
+
+# ----------------------------------------------------------------------- GPU benchmark
+def matvec_roofline(device):
+    """NVFP4 streaming matvec over a bank of 256 distinct [1024, 2048] matrices."""
+    from quickdraw_b200 import synthetic
+    from quickdraw_b200._lib import call, ptr, stream_of
+    rows, width, mats = 1024, 2048, 256
+    src = synthetic.Source(1, device)
+    bank = src.nvfp4("roofline.bank", rows, width, mats)
+    x = src.normal("roofline.x", width)
+    y = torch.empty(mats, rows, dtype=BF16, device=device)
+
+    def launch():
+        call("qd_nvfp4_gemv_bank", ptr(x), ptr(bank.weight), ptr(bank.weight_scale),
+             ptr(bank.weight_scale_2), ptr(y), rows, width, mats, 1, stream_of(x))
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        launch()
+    torch.cuda.current_stream(device).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        launch()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize(device)
+    reps = 20
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(device)
+    per_launch_s = e0.elapsed_time(e1) * 1e-3 / (reps * mats)
+    return CONFIG1_BYTES / per_launch_s / 1e9, per_launch_s
+
+
+def run_gpu(args):
+    rank, local, world = dist_env()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    from quickdraw_b200 import synthetic
+    cfg = synthetic.model_config()
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+        from quickdraw_b200.expert_parallel import ExpertParallelEngine
+        engine = ExpertParallelEngine(cfg, seed=0, max_context=2048, device=device)
+    else:
+        from quickdraw_b200.engine import Engine
+        ckpt = synthetic.make_checkpoint(cfg, seed=0, device=device)
+        engine = Engine(ckpt, max_context=2048, device=str(device))
+    gen = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=gen).tolist()
+    logits = engine.prefill(prompt)
+    engine.pending_token = torch.argmax(logits)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            torch.distributed.barrier()
+            torch.cuda.synchronize(device)
+
+    # ---- device-timed decode: graph replays with the token fed back on the device
+    for _ in range(args.warmup):
+        engine.decode_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            engine.decode_step()
+        e1.record()
+        barrier()
+    device_ms = e0.elapsed_time(e1)
+    # ---- end to end: host token and position in, selected token out, every step
+    token_host = torch.zeros((), dtype=torch.long).pin_memory()
+    pos_host = torch.zeros((), dtype=torch.int32).pin_memory()
+    token_host.fill_(int(engine.pending_token.item()))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        pos_host.fill_(engine.state.position)
+        engine._decode_input.copy_(token_host, non_blocking=True)
+        engine._device_position.copy_(pos_host, non_blocking=True)
+        engine.graph.replay()
+        engine.state.position += 1
+        token_host.fill_(int(engine._decode_output.item()))
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    times = torch.tensor([device_ms, e2e_ms], device=device)
+    if world > 1:
+        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
+    device_ms, e2e_ms = times.tolist()
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peaks()
+    achieved, per_launch_s = matvec_roofline(device)
+    position = args.prompt + args.warmup + args.steps // 2
+    token_bytes = bytes_per_token(cfg, position)
+    tok_s = args.steps / (device_ms * 1e-3)
+    threads = len(os.sched_getaffinity(0))
+    per_token_cpu = float('nan') if args.no_cpu_baseline else cpu_sample(cfg, threads)[0]
+    launches = getattr(engine, "launches_per_step", None) or engine.fused.launches_per_step
+    line = {
+        "metric": "batch-1 decode tok/s (36B-A3B NVFP4 MoE)", "value": tok_s, "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 activations, NVFP4 (E2M1 + E4M3 block scale) weights, fp32 accumulate",
+        "data": "synthetic", "config": workload_config(cfg, world),
+        "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 12,
+                "d2h_bytes_per_step": 8},
+        "gpu_launches": launches * args.steps,
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "kernel": "stream_kernel (NVFP4 matvec, [1024,2048] x 256-matrix bank)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+                     "launch_us": per_launch_s * 1e6, "bytes_per_launch": CONFIG1_BYTES},
+        "decode_roofline": {"bytes_per_token": token_bytes,
+                            "achieved_gbs": token_bytes * tok_s / 1e9 / world,
+                            "frac_of_measured_peak": token_bytes * tok_s / 1e9 / world / peak,
+                            "frac_of_8tbs": token_bytes * tok_s / 8e12 / world},
+        "cpu_baseline": {"value": 1.0 / per_token_cpu, "unit": "tok/s", "cores": threads, "kind": "port",
+                         "sample": "one 4-layer group and the LM head at position 640, group time x12 + head time"},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    ap.add_argument("--prompt", type=int, default=PROMPT_LEN, help="prompt length (512 in the headline workload)")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU sample (profiling runs)")
+    args = ap.parse_args()
+    assert args.warmup >= 0 and args.steps > 0
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        with torch.inference_mode():
+            run_gpu(args)
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
