@@ -205,6 +205,12 @@ int qd_decode_layers(qd_model* model, const qd_state* state, const long long* to
                      float* routed_partial, int layer_begin, int layer_end, void* logits_out,
                      long long* next_token, int flags, void* stream);
 
+/* Profiling aid: per-block timestamps of the next `launches` streaming launches (see stream.cu). */
+int qd_stream_trace(unsigned long long* buffer, int launches);
+
+/* Tuning: blocks per SM (1 or 2) of the streaming matvec kernel when 2048 inputs wide. */
+int qd_stream_blocks_per_sm(int n);
+
 /* Measurement helper: the streaming NVFP4 matvec over a bank of `matrices` equally shaped
  * [rows, in_features] matrices, one launch per matrix, so the working set can exceed L2. */
 int qd_nvfp4_gemv_bank(const void* x, const void* codes, const void* scales, const float* global,

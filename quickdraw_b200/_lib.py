@@ -42,6 +42,8 @@ SIGNATURES = {
     "qd_decode_workspace_bytes": [P],
     "qd_decode_step": [P, P, P, P, I, P, P, P, I, P],
     "qd_decode_layers": [P, P, P, P, I, P, P, I, I, P, P, I, P],
+    "qd_stream_blocks_per_sm": [I],
+    "qd_stream_trace": [P, I],
     "qd_nvfp4_gemv_bank": [P, P, P, P, P, I, I, I, I, P],
 }
 

@@ -54,14 +54,14 @@ QD_DEVINL uint32_t e2m1x2_to_f16x2(uint32_t byte) {
     asm("{\n\t.reg .b8 lo, hi;\n\tmov.b16 {lo, hi}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, lo;\n\t}" : "=r"(out) : "h"(b));
     return out;
 }
-// four NVFP4 bytes (eight codes) of a 32-bit word -> four f16x2, byte 0 first.  Each byte
-// is isolated with a byte permute and converted on its own: splitting one register into
-// several .b8 operands inside a single asm block produced wrong bytes in large kernels.
+// four NVFP4 bytes (eight codes) of a 32-bit word -> four f16x2, byte 0 first.  The word is
+// unpacked into its four bytes in ONE vector move (a two-level b32 -> b16 -> b8 unpack gave
+// wrong bytes when inlined into a large kernel).
 QD_DEVINL void e2m1x8_to_f16x2(uint32_t word, uint32_t (&out)[4]) {
-    out[0] = e2m1x2_to_f16x2(__byte_perm(word, 0u, 0x4440u));
-    out[1] = e2m1x2_to_f16x2(__byte_perm(word, 0u, 0x4441u));
-    out[2] = e2m1x2_to_f16x2(__byte_perm(word, 0u, 0x4442u));
-    out[3] = e2m1x2_to_f16x2(__byte_perm(word, 0u, 0x4443u));
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3]) : "r"(word));
 }
 
 // d = a(f16) * b(f16) + c(f32), one rounding, on the low / high halves of packed pairs.
@@ -141,7 +141,7 @@ QD_DEVINL unsigned long long global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-QD_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status) {
+static __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status) {
     for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long start = global_timer_ns();

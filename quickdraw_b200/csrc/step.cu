@@ -28,12 +28,12 @@ struct Workspace {
     bf16 *resid[2], *xnorm, *big, *mid, *ab, *o, *mixed, *router_logits, *strength, *hidden, *moe_out, *shared_row;
     int32_t* ids; float* weights; float* routed_partial; float* attn_scratch;
     unsigned int* attn_counters; float* best_val; int* best_idx; unsigned int* argmax_counter;
-    unsigned int* status; int* cursor;
+    unsigned int* status; int* cursor; unsigned int* route_counter;
     size_t bytes;
 };
 
 constexpr int kAttnSplits = 32;
-constexpr int kMaxGrid = 256;
+constexpr int kMaxGrid = 1024;
 
 size_t align_up(size_t v) { return (v + 255) & ~size_t(255); }
 
@@ -50,6 +50,7 @@ Workspace carve(const qd_model_config& c, uint8_t* base) {
     w.cursor = (int*)take(4);                       // which residual buffer is current
     w.status = (unsigned int*)take(4);
     w.argmax_counter = (unsigned int*)take(4);
+    w.route_counter = (unsigned int*)take(4);
     w.attn_counters = (unsigned int*)take(4 * c.kv_heads);
     w.resid[0] = (bf16*)take(2 * c.hidden); w.resid[1] = (bf16*)take(2 * c.hidden);
     w.xnorm = (bf16*)take(2 * c.hidden);
@@ -155,7 +156,7 @@ int run_layers(qd_model* m, const qd_state* st, const long long* token, const in
             QD_TRY(qd_gdn_recurrence(w.big, w.ab, w.ab + c.value_heads, ly.a_log, ly.dt_bias,
                                      st->rec_state + (size_t)ly.state_index * c.value_heads * c.key_dim * c.value_dim,
                                      w.o, c.key_heads, c.value_heads, c.key_dim, c.value_dim, pdl, stream));
-            b.prologue = PRO_GATED_NORM; b.z = w.mid; b.head_gamma = (const bf16*)ly.head_norm; b.head_dim = c.value_dim;
+            b.prologue = PRO_GATED_NORM; b.z = w.mid; b.head_gamma = (const bf16*)ly.head_norm;
         }
         QD_TRY(stream_launch(b, 0, stream, pdl));
         // ---- C
@@ -164,15 +165,15 @@ int run_layers(qd_model* m, const qd_state* st, const long long* token, const in
         cc.x = w.mixed; cc.residual = w.resid[1]; cc.residual_out = w.resid[0]; cc.x_out = w.xnorm;
         cc.status = w.status; cc.expert_hi = 0x7fffffff;
         cc.nseg = 3;
-        cc.seg[0] = bf16_seg(ly.router, c.experts, w.router_logits);
+        cc.seg[0] = bf16_seg(ly.router, c.experts, w.router_logits, EP_ROUTE);
+        cc.ids_out = w.ids; cc.weights_out = w.weights; cc.route_counter = w.route_counter; cc.route_topk = c.topk;
         cc.seg[1] = bf16_seg(ly.shared_expert_gate, 1, w.strength);
         cc.seg[2] = pair_seg(ly.shared_gate, ly.shared_up, c.intermediate, w.hidden + (size_t)c.topk * c.intermediate);
         QD_TRY(stream_launch(cc, 0, stream, pdl));
         // ---- D
         StreamParams d = {};
         d.width = H; d.prologue = PRO_NONE; d.x = w.xnorm; d.status = w.status;
-        d.router_logits = w.router_logits; d.experts = c.experts; d.topk = c.topk;
-        d.ids_out = w.ids; d.weights_out = w.weights;
+        d.ids_in = w.ids; d.topk = c.topk;
         d.expert_lo = c.expert_lo; d.expert_hi = c.expert_hi;
         d.nseg = c.topk;
         for (int s = 0; s < c.topk; ++s) {
@@ -199,7 +200,7 @@ int run_layers(qd_model* m, const qd_state* st, const long long* token, const in
         h.nseg = 1;
         h.seg[0] = bf16_seg(c.lm_head, c.vocab, (bf16*)logits, EP_ARGMAX);
         h.best_val = w.best_val; h.best_idx = w.best_idx; h.counter = w.argmax_counter; h.token_out = next_token;
-        int grid = stream_sm_count();
+        int grid = stream_sm_count() * 2;
         if (grid > kMaxGrid) grid = kMaxGrid;
         QD_TRY(stream_launch(h, grid, stream, pdl));
     }

@@ -1,11 +1,12 @@
 // Parameter block of the streaming matvec kernel (stream.cu).
 //
 // One launch multiplies ONE activation vector with a list of weight segments that share
-// its width: NVFP4 row blocks, NVFP4 gate/up pairs (SwiGLU fused) and bf16 row blocks.
-// Weights travel global -> shared memory as 1-D bulk copies (TMA) through a ring of
-// stages; the activation vector lives in registers.  A prologue can build the vector
-// (residual add + RMSNorm, or the DeltaNet per-head gated norm), an epilogue can post-
-// process each output row (short convolution, greedy argmax).
+// its width: NVFP4 row blocks, NVFP4 gate/up pairs (SwiGLU fused) and bf16 row blocks, all
+// in the reference's checkpoint layout.  Weights travel global -> shared memory as 1-D
+// bulk copies (TMA) through a ring of stages; the activation vector lives in registers.
+// A prologue can build the vector (residual add + RMSNorm, or the DeltaNet per-head gated
+// norm), an epilogue can post-process each output row (short convolution, greedy argmax),
+// and the block that completes the router rows can do the top-k routing for the next launch.
 #pragma once
 #include "common.cuh"
 
@@ -26,9 +27,11 @@ constexpr int kStreamConsumerWarps = 8;
 constexpr int kStreamThreads = (kStreamConsumerWarps + 1) * 32;   // + one producer warp
 constexpr int kStreamStages = 3;
 constexpr int kStreamStageBytes = 27648;   // 24 NVFP4 rows of 2048 inputs (codes + scales)
+constexpr int kStreamConvRows = 256;       // conv rows one block can stage
+constexpr int kStreamConvWidth = 4;        // widest short convolution the fused epilogue takes
 
 enum SegKind { SEG_FP4 = 0, SEG_FP4_PAIR = 1, SEG_BF16 = 2 };
-enum SegEpilogue { EP_PLAIN = 0, EP_CONV = 1, EP_ARGMAX = 2 };
+enum SegEpilogue { EP_PLAIN = 0, EP_CONV = 1, EP_ARGMAX = 2, EP_ROUTE = 3 };
 enum Prologue { PRO_NONE = 0, PRO_ADD_NORM = 1, PRO_GATED_NORM = 2 };
 
 struct StreamSeg {
@@ -58,21 +61,23 @@ struct StreamParams {
     bf16* residual_out;       // PRO_ADD_NORM: written by block 0
     bf16* x_out;              // prologue result, written by block 0 (may be null)
     const bf16* z;            // PRO_GATED_NORM: gate input [K]
-    const bf16* head_gamma;   // PRO_GATED_NORM: bf16 [head_dim]
-    int head_dim;
-    // routing done inside the kernel (segments with slot >= 0)
-    const bf16* router_logits; int experts; int topk;
-    const int32_t* ids_in;    // alternative: ids given by the caller
-    int32_t* ids_out; float* weights_out;   // written by block 0 (may be null)
+    const bf16* head_gamma;   // PRO_GATED_NORM: bf16 [128]
+    // expert ids of segments with slot >= 0 (device, written by an earlier launch or the caller)
+    const int32_t* ids_in; int topk;
     int expert_lo, expert_hi; // owned expert range; routed segments outside it are skipped
+    // EP_ROUTE: the segment's rows are router logits; the block that completes them selects
+    // the top-k experts (quickdraw/models/qwen.py:174-177)
+    int32_t* ids_out; float* weights_out; unsigned int* route_counter; int route_topk;
     // EP_CONV
     bf16* conv_state; const bf16* conv_taps; int conv_width;
     // EP_ARGMAX
     float* best_val; int* best_idx; unsigned int* counter; long long* token_out;
     unsigned int* status;
+    unsigned int quota, remainder;   // filled by stream_launch: total cost = quota * grid + remainder
+    unsigned long long* trace;   // optional: 16 timestamps (ns) per block, for profiling
 };
 
-// grid <= 0 picks one block per SM.  Returns a QD_* code.
+// grid <= 0 picks the default number of blocks per SM.  Returns a QD_* code.
 int stream_launch(const StreamParams& p, int grid, cudaStream_t stream, bool pdl);
 int stream_sm_count();
 
