@@ -26,7 +26,7 @@ class Engine:
     def __init__(self, ckpt: Checkpoint, max_context: int = 32768, device: str = "cuda",
                  backend: str | None = None, *, kernels: dict | None = None, step=None,
                  cuda_graph: bool = True, prefill_chunk_size: int = 128,
-                 sequence_prefill: bool = True):
+                 sequence_prefill: bool = True, _step_object=None):
         custom = kernels is not None or step is not None
         if backend is None:
             backend = "custom" if custom else "b200"
@@ -40,7 +40,11 @@ class Engine:
         self.graph = None
         self.fused = None
         on_cuda = torch.device(device).type == "cuda"
-        if step is not None:
+        if _step_object is not None:      # a prebuilt fused-style step (expert parallel)
+            assert on_cuda and not custom
+            self.fused = _step_object
+            self.step = _step_object
+        elif step is not None:
             self.step = step
         else:
             assert on_cuda, "the b200 backend needs a CUDA device; there is no CPU path"

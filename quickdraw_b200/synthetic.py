@@ -71,15 +71,29 @@ class Source:
         return NVFP4Linear(codes, scales.to(torch.float8_e4m3fn), gs)
 
 
-def make_moe(cfg: ModelConfig, src: Source, tag: str = "moe") -> MoEWeights:
+def expert_slice(bank: NVFP4Linear, lo: int, hi: int) -> NVFP4Linear:
+    """Experts [lo, hi) of a bank as an independent (contiguous) bank."""
+    g = bank.weight_scale_2
+    return NVFP4Linear(bank.weight[lo:hi].clone(), bank.weight_scale[lo:hi].clone(),
+                       g if g.numel() == 1 else g[lo:hi].clone(), group_size=bank.group_size)
+
+
+def make_moe(cfg: ModelConfig, src: Source, tag: str = "moe",
+             expert_range: tuple[int, int] | None = None) -> MoEWeights:
+    """``expert_range`` keeps only the experts [lo, hi) of each bank (expert parallelism);
+    the values are those of the full bank, so ranks hold slices of one model."""
     h, m, s, e = (cfg.hidden_size, cfg.moe_intermediate_size,
                   cfg.shared_expert_intermediate_size, cfg.num_experts)
+
+    def bank(name, out, inp):
+        full = src.nvfp4(name, out, inp, e)
+        return full if expert_range is None else expert_slice(full, *expert_range)
     return MoEWeights(
         router=src.normal(f"{tag}.router", e, h, std=0.02),
         shared_expert_gate=src.normal(f"{tag}.shared_expert_gate", 1, h, std=0.02),
-        experts_gate=src.nvfp4(f"{tag}.experts_gate", m, h, e),
-        experts_up=src.nvfp4(f"{tag}.experts_up", m, h, e),
-        experts_down=src.nvfp4(f"{tag}.experts_down", h, m, e),
+        experts_gate=bank(f"{tag}.experts_gate", m, h),
+        experts_up=bank(f"{tag}.experts_up", m, h),
+        experts_down=bank(f"{tag}.experts_down", h, m),
         shared_gate=src.nvfp4(f"{tag}.shared_gate", s, h),
         shared_up=src.nvfp4(f"{tag}.shared_up", s, h),
         shared_down=src.nvfp4(f"{tag}.shared_down", h, s))
@@ -115,7 +129,7 @@ def make_attention(cfg: ModelConfig, src: Source, tag: str = "attn") -> FullAttn
         k_norm=src.normal(f"{tag}.k_norm", cfg.head_dim, std=0.02))
 
 
-def make_layer(cfg: ModelConfig, src: Source, idx: int) -> LayerWeights:
+def make_layer(cfg: ModelConfig, src: Source, idx: int, expert_range=None) -> LayerWeights:
     kind = cfg.layer_types[idx]
     tag = f"layer{idx}"
     mixer = (make_attention(cfg, src, f"{tag}.attn") if kind == "full_attention"
@@ -125,18 +139,19 @@ def make_layer(cfg: ModelConfig, src: Source, idx: int) -> LayerWeights:
         input_layernorm=src.normal(f"{tag}.input_layernorm", cfg.hidden_size, std=0.02),
         post_attention_layernorm=src.normal(f"{tag}.post_attention_layernorm",
                                             cfg.hidden_size, std=0.02),
-        attn=mixer, moe=make_moe(cfg, src, f"{tag}.moe"))
+        attn=mixer, moe=make_moe(cfg, src, f"{tag}.moe", expert_range))
 
 
-def make_checkpoint(cfg: ModelConfig, seed: int = 0, device="cuda") -> Checkpoint:
-    """Whole model with a bf16 embedding and a bf16 LM head (about 23 GB at 48 layers)."""
+def make_checkpoint(cfg: ModelConfig, seed: int = 0, device="cuda", expert_range=None) -> Checkpoint:
+    """Whole model with a bf16 embedding and a bf16 LM head (about 23 GB at 48 layers);
+    with ``expert_range`` only that slice of every expert bank is kept."""
     src = Source(seed, device)
     return Checkpoint(
         config=cfg,
         embed_tokens=src.normal("embed_tokens", cfg.vocab_size, cfg.hidden_size, std=0.02),
         final_norm=src.normal("final_norm", cfg.hidden_size, std=0.02),
         lm_head=src.normal("lm_head", cfg.vocab_size, cfg.hidden_size, std=0.02),
-        layers=[make_layer(cfg, src, i) for i in range(cfg.num_hidden_layers)])
+        layers=[make_layer(cfg, src, i, expert_range) for i in range(cfg.num_hidden_layers)])
 
 
 def to_device(obj, device):
