@@ -96,7 +96,8 @@ def test_greedy_64_tokens_against_oracle(cuda_device, real_width_case):
     """64 decode steps fed with the oracle's own tokens: the greedy choice must be the
     oracle's at every step whose top-2 logit margin in the oracle exceeds the step noise
     (0.125, four bf16 roundings at the logit magnitude seen here), and at 56 steps or more
-    overall.  A free-running comparison would only test where the first near-tie falls:
+    overall.  (The oracle itself does not reproduce its own free-running tokens across runs
+    at near-ties: its multi-threaded fp32 sums are not order-stable.)  A free-running comparison would only test where the first near-tie falls:
     after one different token the two sequences are unrelated."""
     from quickdraw_b200.fused import FusedStep
     ckpt, ckpt_cpu, prompt, want, _ = real_width_case
@@ -121,7 +122,6 @@ def test_greedy_64_tokens_against_oracle(cuda_device, real_width_case):
                 top = ref_logits.float().topk(2)
                 margin = float(top.values[0] - top.values[1])
                 mine, theirs = int(step.next_token), int(top.indices[0])
-                assert theirs == want[position - len(prompt) + 1]
                 if mine == theirs:
                     agree += 1
                 elif margin > 0.125:
