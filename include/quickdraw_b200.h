@@ -23,7 +23,8 @@ enum {
     QD_ERR_ARG = 1,          /* contract violation detected before launch */
     QD_ERR_LAUNCH = 2,       /* the CUDA runtime refused the launch */
     QD_ERR_TIMEOUT = 3,      /* a bounded device-side wait ran out (status word) */
-    QD_ERR_UNSUPPORTED = 4   /* shape outside what the entry point covers */
+    QD_ERR_UNSUPPORTED = 4,  /* shape outside what the entry point covers */
+    QD_ERR_TOO_LARGE = 5     /* the shape needs more than a fixed-capacity buffer holds */
 };
 
 int qd_version(void);
@@ -123,6 +124,26 @@ int qd_attn_decode(const void* qg, const void* k_new, const void* v_new, const v
                    unsigned int* counters, const int* position_dev, int position_host, int capacity,
                    int q_heads, int kv_heads, int head_dim, int rotary_dim, float theta, float eps,
                    int splits, int pdl, void* stream);
+
+/* qd_attn_decode for callers that may not allocate device memory: plugins that run inside
+ * another runtime's memory pool, code on a latency path that must not call the CUDA
+ * allocator, or hosts that hand this library no workspace.  No counterpart in the
+ * reference (its wrappers allocate their outputs and workspaces with torch).  Same
+ * arguments and results as qd_attn_decode without the scratch and counter buffers: the
+ * split-context partial sums live in a 1 MiB array built into the library, one per GPU that
+ * loads it, held until the process exits.
+ *  - Limit: qd_attn_scratch_floats(...) * 4 bytes must fit in 1 MiB minus 256 bytes
+ *    (16 query / 2 KV heads of 256 with 32 splits need 516 KiB); otherwise QD_ERR_TOO_LARGE.
+ *  - The first call on a device looks up the array's device address (with that device
+ *    current); make that first call outside any stream capture.
+ *  - Every call uses the same array: two calls that overlap on the GPU (different streams,
+ *    or graphs replayed concurrently) race on it.  Calls on one stream are safe.
+ *  - Calls neither cudaMalloc/cudaFree nor any allocating routine. */
+int qd_attn_decode_static(const void* qg, const void* k_new, const void* v_new, const void* q_norm,
+                          const void* k_norm, void* k_cache, void* v_cache, void* out,
+                          const int* position_dev, int position_host, int capacity, int q_heads,
+                          int kv_heads, int head_dim, int rotary_dim, float theta, float eps,
+                          int splits, void* stream);
 
 /* ---- MoE tail — quickdraw/kernel/cute/moe.py:101-116 (expert_gemv(down, routed) +
  * shared down + _reduce in one launch).  hidden [topk+1, 512] (last row: shared expert).

@@ -34,6 +34,7 @@ SIGNATURES = {
     "qd_gdn_gated_norm": [P, P, P, P, I, I, F, P],
     "qd_attn_scratch_floats": [I, I, I, I],
     "qd_attn_decode": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, I, P],
+    "qd_attn_decode_static": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
     "qd_moe_down_combine": [P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     "qd_moe_finish": [P, P, P, I, I, P],
     "qd_model_create": [P, P],

@@ -253,3 +253,57 @@ extern "C" int qd_attn_decode(const void* qg, const void* k_new, const void* v_n
     return qd_launch(attn_decode_kernel, dim3(kv_heads, splits), dim3(kAttnThreads), smem, (cudaStream_t)stream,
                      pdl != 0, p);
 }
+
+// ---------------------------------------------------------------- allocation-free variant
+// Scratch for callers that cannot allocate device memory (see qd_attn_decode_static in the
+// header).  One array per GPU that loads the library, held until the process exits: the
+// split partials first, the per-KV-head completion counters in the last 256 bytes.
+constexpr size_t kAttnStaticBytes = 1u << 20;
+constexpr size_t kAttnStaticCounterBytes = 256;
+static __device__ __align__(256) unsigned char qd_attn_static_scratch[kAttnStaticBytes];
+static unsigned char* g_attn_static_ptr[64];     // device address of the array, per device ordinal
+
+extern "C" int qd_attn_decode_static(const void* qg, const void* k_new, const void* v_new, const void* q_norm,
+                                     const void* k_norm, void* k_cache, void* v_cache, void* out,
+                                     const int* position_dev, int position_host, int capacity, int q_heads,
+                                     int kv_heads, int head_dim, int rotary_dim, float theta, float eps,
+                                     int splits, void* stream) {
+    QD_CHECK_ARG(qg && k_new && v_new && q_norm && k_norm && k_cache && v_cache && out);
+    QD_CHECK_ARG(kv_heads > 0 && q_heads % kv_heads == 0 && splits >= 1 && capacity > 0);
+    QD_CHECK_ARG(position_dev || (position_host >= 0 && position_host < capacity));
+    QD_CHECK_ARG(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0);
+    const int G = q_heads / kv_heads;
+    if (G > kAttnMaxGroup || head_dim > kAttnMaxDim || head_dim % 8 != 0) return QD_ERR_UNSUPPORTED;
+    const size_t need = sizeof(float) * (size_t)qd_attn_scratch_floats(q_heads, kv_heads, head_dim, splits);
+    if (need > kAttnStaticBytes - kAttnStaticCounterBytes || (size_t)kv_heads * 4 > kAttnStaticCounterBytes)
+        return QD_ERR_TOO_LARGE;      // the static array cannot hold this shape
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
+    if (!g_attn_static_ptr[dev]) {
+        // The array's name is a host-side handle; the kernel needs its address on THIS device.
+        void* address = nullptr;
+        if (cudaGetSymbolAddress(&address, qd_attn_static_scratch) != cudaSuccess || !address) return QD_ERR_LAUNCH;
+        g_attn_static_ptr[dev] = (unsigned char*)address;
+    }
+    unsigned char* base = g_attn_static_ptr[dev];
+    unsigned int* counters = (unsigned int*)(base + kAttnStaticBytes - kAttnStaticCounterBytes);
+    // The array keeps whatever the last call left; the counters must start at zero.
+    if (cudaMemsetAsync(counters, 0, kAttnStaticCounterBytes, (cudaStream_t)stream) != cudaSuccess) return QD_ERR_LAUNCH;
+    AttnParams p;
+    p.qg = (const bf16*)qg; p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new;
+    p.q_norm = (const bf16*)q_norm; p.k_norm = (const bf16*)k_norm;
+    p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache; p.out = (bf16*)out;
+    p.partial = (float*)base; p.counters = counters; p.position_dev = position_dev; p.position_host = position_host;
+    p.capacity = capacity; p.hq = q_heads; p.hk = kv_heads; p.d = head_dim; p.rotary = rotary_dim;
+    p.theta = theta; p.eps = eps; p.splits = splits;
+    const size_t smem = sizeof(float) * ((size_t)G * head_dim + head_dim + (size_t)kAttnWarps * G * (head_dim + 2));
+    if (smem > 100 * 1024) return QD_ERR_UNSUPPORTED;
+    static bool configured[64];
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
+            return QD_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    return qd_launch(attn_decode_kernel, dim3(kv_heads, splits), dim3(kAttnThreads), smem, (cudaStream_t)stream,
+                     false, p);
+}

@@ -394,6 +394,7 @@ extern "C" const char* qd_error_string(int code) {
         case QD_ERR_LAUNCH: return "CUDA launch failed";
         case QD_ERR_TIMEOUT: return "bounded device wait ran out";
         case QD_ERR_UNSUPPORTED: return "shape not covered by this kernel";
+        case QD_ERR_TOO_LARGE: return "shape exceeds the fixed capacity of a built-in buffer";
         default: return "unknown";
     }
 }
