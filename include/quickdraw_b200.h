@@ -209,10 +209,9 @@ long long qd_decode_workspace_bytes(const qd_model* model);
 
 /* One token through every layer.  token: int64 device scalar; position: int32 device
  * scalar (preferred, graph-replayable) or host value.  Writes bf16 logits [vocab] and the
- * greedy next token (int64 device scalar, lowest index on ties).  phase selects a slice of
- * the step for expert parallelism: QD_PHASE_ALL runs everything; with QD_PHASE_UNTIL_MOE /
- * QD_PHASE_AFTER_MOE the caller all-reduces the workspace's routed partial sum between the
- * two calls for layer `layer`. */
+ * greedy next token (int64 device scalar, lowest index on ties).  flags: QD_FLAG_PDL makes
+ * every launch a programmatic dependent of its predecessor, QD_FLAG_NO_LOGITS skips the LM
+ * head (prompt tokens). */
 enum { QD_FLAG_PDL = 1, QD_FLAG_NO_LOGITS = 2 };
 int qd_decode_step(qd_model* model, const qd_state* state, const long long* token,
                    const int* position_dev, int position_host, void* workspace, void* logits_out,
@@ -225,6 +224,21 @@ int qd_decode_layers(qd_model* model, const qd_state* state, const long long* to
                      const int* position_dev, int position_host, void* workspace,
                      float* routed_partial, int layer_begin, int layer_end, void* logits_out,
                      long long* next_token, int flags, void* stream);
+
+/* The same step as ONE cooperative launch (a persistent kernel with grid-wide barriers
+ * between the phases of qwen.py:196-241 and a weight ring that runs ahead across them).
+ * The phase list ("program") holds device addresses of the model and of `workspace`, so it
+ * is built once per (model, workspace) pair: qd_program_build fills a HOST buffer of
+ * qd_program_bytes bytes, the caller copies it to the device and passes that copy here.
+ * Needs a whole idle GPU (one block per SM, all resident) and a single-GPU model
+ * (expert_lo == 0, expert_hi == experts).  `trace` (optional, device) receives
+ * [phase][8][blocks] nanosecond timestamps. */
+long long qd_program_bytes(const qd_model* model);
+int qd_program_build(const qd_model* model, void* workspace, void* host_out, long long bytes);
+int qd_decode_step_persistent(const qd_model* model, const qd_state* state, const long long* token,
+                              const int* position_dev, int position_host, void* workspace,
+                              const void* program, void* logits_out, long long* next_token, int flags,
+                              unsigned long long* trace, void* stream);
 
 /* Profiling aid: per-block timestamps of the next `launches` streaming launches (see stream.cu). */
 int qd_stream_trace(unsigned long long* buffer, int launches);

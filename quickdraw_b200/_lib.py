@@ -43,10 +43,15 @@ SIGNATURES = {
     "qd_decode_workspace_bytes": [P],
     "qd_decode_step": [P, P, P, P, I, P, P, P, I, P],
     "qd_decode_layers": [P, P, P, P, I, P, P, I, I, P, P, I, P],
+    "qd_program_bytes": [P],
+    "qd_program_build": [P, P, P, L],
+    "qd_decode_step_persistent": [P, P, P, P, I, P, P, P, P, I, P, P],
     "qd_stream_blocks_per_sm": [I],
     "qd_stream_trace": [P, I],
     "qd_nvfp4_gemv_bank": [P, P, P, P, P, I, I, I, I, P],
 }
+
+LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes"}
 
 _lib = None
 
@@ -69,7 +74,7 @@ def lib() -> ctypes.CDLL:
             if fn is None:
                 continue
             fn.argtypes = argtypes
-            fn.restype = c_int
+            fn.restype = c_longlong if name in LONG_RESULTS else c_int
         handle.qd_error_string.argtypes = [c_int]
         handle.qd_error_string.restype = c_char_p
         _lib = handle

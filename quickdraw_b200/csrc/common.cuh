@@ -133,25 +133,33 @@ QD_DEVINL bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                  "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after QD_WAIT_LIMIT polls, records the failure in *status and
-// returns false so the caller can leave the kernel instead of spinning for ever.
+// Bounded wait: gives up after QD_WAIT_LIMIT_NS of wall time, records the failure in
+// *status and returns false so the caller can leave the kernel instead of spinning for ever.
+// The polling loops stay rolled: unrolled, every poll would run through fresh code.
 #define QD_WAIT_LIMIT_NS 200000000ull   /* 0.2 s of wall time */
 QD_DEVINL unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-static __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status) {
-    for (int i = 0; i < 64; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, unsigned int* status) {
     const unsigned long long start = global_timer_ns();
     for (;;) {
+#pragma unroll 1
         for (int i = 0; i < 32; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (global_timer_ns() - start > QD_WAIT_LIMIT_NS) break;
     }
     if (status) atomicOr(status, QD_STATUS_WAIT_TIMEOUT);
     return false;
+}
+// The usual case (the barrier completes within a few polls) stays inline, so that no
+// registers are saved around a call in the row loops.
+QD_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, status);
 }
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
 // dst, src 16-byte aligned; bytes a multiple of 16.

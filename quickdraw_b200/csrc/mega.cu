@@ -1,0 +1,1056 @@
+// Persistent decode kernel: one cooperative launch per token.
+//
+// The grid is one block per SM.  A block has sixteen consumer warps and one producer warp.
+// The producer walks the program phase by phase and streams this block's share of every
+// phase's weights into a ring of shared-memory stages (1-D bulk copies, full/empty
+// mbarriers); it never waits for other blocks except where the weights to fetch depend on
+// the routing, so at a grid barrier the ring already holds the start of the next phase.
+// The consumers run the phases in order:
+//     static prefetch (what no other block writes)  ->  grid barrier  ->  build the
+//     activation vector  ->  rows of the ring  ->  arrive at the next barrier.
+// Activations written by one block and read by another travel through L2: every such read
+// is a cache-global load, every phase ends with a fence and a release on the barrier word.
+//
+// The arithmetic of every phase is that of the separate kernels (stream.cu, gdn.cu,
+// moe.cu): same rounding points, same summation order; attention uses its own split of the
+// context (reference: quickdraw/models/qwen.py:66-241).
+//
+// Every wait is bounded.  A wait that runs out sets the status word and an abort bit in
+// the barrier word, which lets every other block fall through its barriers and leave.
+#include "mega.cuh"
+#include "rowdot.cuh"
+
+namespace qd {
+namespace {
+
+constexpr int CW = kMegaConsumerWarps, CT = kMegaConsumers, NS = kMegaStages;
+constexpr unsigned kAbortBit = 0x80000000u;
+constexpr int kDownWidth = 512;
+constexpr int kDownRowBytes = kDownWidth / 2 + kDownWidth / 16;   // 288
+constexpr int kAttnStride = 256 + 2;
+constexpr int kScratchFloats = 8 * 4 * kAttnStride + 3 * 8 * kMegaAttnSplits + 64;   // attention merge buffers
+
+struct Smem {
+    uint8_t* stages;
+    bf16* xs;              // [4096] activation vector, bf16           (attention: q rows, fp32)
+    uint32_t* xf;          // [2048] the same as f16 pairs             (attention: new key, trig table)
+    float* scratch;        // attention merge / DeltaNet vectors / down contributions
+    bf16* conv_taps; bf16* conv_state;
+    MegaPhase* cph;        // [2] consumer copies of the current and the next phase
+    MegaPhase* pph;        // producer copy
+    uint64_t* full; uint64_t* empty;
+    float* red;            // [64]
+    int32_t* ids; float* weights;      // [8] routing of the current layer
+    volatile int* ids_seq;             // layers routed so far
+    volatile int* abort;
+    int* flag;
+};
+
+QD_DEVINL Smem carve_smem(uint8_t* base) {
+    Smem s;
+    s.stages = base;                                  base += (size_t)NS * kStreamStageBytes;
+    s.xs = reinterpret_cast<bf16*>(base);             base += 4096 * 2;
+    s.xf = reinterpret_cast<uint32_t*>(base);         base += 2048 * 4;
+    s.scratch = reinterpret_cast<float*>(base);       base += (size_t)kScratchFloats * 4;
+    s.conv_taps = reinterpret_cast<bf16*>(base);      base += kMegaConvRows * kStreamConvWidth * 2;
+    s.conv_state = reinterpret_cast<bf16*>(base);     base += kMegaConvRows * kStreamConvWidth * 2;
+    s.cph = reinterpret_cast<MegaPhase*>(base);       base += 2 * sizeof(MegaPhase);
+    s.pph = reinterpret_cast<MegaPhase*>(base);       base += sizeof(MegaPhase);
+    s.full = reinterpret_cast<uint64_t*>(base);       base += NS * 8;
+    s.empty = reinterpret_cast<uint64_t*>(base);      base += NS * 8;
+    s.red = reinterpret_cast<float*>(base);           base += 64 * 4;
+    s.ids = reinterpret_cast<int32_t*>(base);         base += 8 * 4;
+    s.weights = reinterpret_cast<float*>(base);       base += 8 * 4;
+    s.ids_seq = reinterpret_cast<volatile int*>(base); base += 4;
+    s.abort = reinterpret_cast<volatile int*>(base);  base += 4;
+    s.flag = reinterpret_cast<int*>(base);            base += 8;
+    return s;
+}
+constexpr size_t kSmemBytes = (size_t)NS * kStreamStageBytes + 4096 * 2 + 2048 * 4 + (size_t)kScratchFloats * 4 +
+                              2 * kMegaConvRows * kStreamConvWidth * 2 + 3 * sizeof(MegaPhase) + 2 * NS * 8 +
+                              64 * 4 + 8 * 4 + 8 * 4 + 16;
+
+QD_DEVINL float ldcg_bf16(const bf16* p) {
+    return __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(p)) << 16);
+}
+QD_DEVINL unsigned ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+QD_DEVINL void red_release_add(unsigned* p, unsigned v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+QD_DEVINL void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+QD_DEVINL void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Bounded wait until the barrier word reaches `target` (the abort bit makes it larger than
+// any target).  On time-out: status bit, abort bit, false.
+__device__ __noinline__ bool grid_wait(unsigned* bar, unsigned target, unsigned* status) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+        if (ld_acquire(bar) >= target) return true;
+    const unsigned long long start = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (ld_acquire(bar) >= target) return true;
+        if (global_timer_ns() - start > QD_WAIT_LIMIT_NS) break;
+    }
+    atomicOr(status, QD_STATUS_WAIT_TIMEOUT);
+    atomicOr(bar, kAbortBit);
+    return false;
+}
+__device__ __noinline__ bool flag_wait(volatile int* flag, int target, volatile int* abort, unsigned* status) {
+#pragma unroll 1
+    for (int i = 0; i < 1024; ++i)
+        if (*flag >= target) return true;
+    const unsigned long long start = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (*flag >= target) return true;
+        if (*abort) return false;
+        if (global_timer_ns() - start > QD_WAIT_LIMIT_NS) break;
+    }
+    atomicOr(status, QD_STATUS_WAIT_TIMEOUT);
+    return false;
+}
+
+// The consumers' side of the grid barrier in front of phase `pi`.
+QD_DEVINL void phase_wait(const MegaParams& mp, const Smem& S, int pi, int tid) {
+    if (pi > 0 && tid == 0) {
+        if (!grid_wait(mp.bar, (unsigned)pi * gridDim.x, mp.status)) *S.abort = 1;
+        else if (ld_acquire(mp.bar) & kAbortBit) *S.abort = 1;
+        __threadfence();
+    }
+    named_barrier(1, CT);
+}
+// Profiling: eight nanosecond timestamps per phase and block.  Slots: 0 phase start (after the
+// grid barrier), 1 phase end, 2 activation vector ready, 3 first tile landed, 4 / 5 first and
+// last tile of the phase issued by the producer.
+constexpr int kTraceSlots = 8;
+QD_DEVINL void trace_mark(const MegaParams& mp, int pi, int slot) {
+    if (mp.trace) mp.trace[((size_t)pi * kTraceSlots + slot) * gridDim.x + blockIdx.x] = global_timer_ns();
+}
+QD_DEVINL void give_up(const MegaParams& mp, const Smem& S) {
+    *S.abort = 1;
+    atomicOr(mp.bar, kAbortBit);
+}
+
+// =========================================================================== producer
+template <int K>
+QD_DEVINL bool produce_stream(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it) {
+    const unsigned lo = blockIdx.x * ph.quota + min(blockIdx.x, ph.remainder);
+    const unsigned hi = (blockIdx.x + 1) * ph.quota + min(blockIdx.x + 1, ph.remainder);
+    unsigned seg_start = 0;
+#pragma unroll 1
+    for (int i = 0; i < ph.nseg; ++i) {
+        const MegaSeg& sg = ph.seg[i];
+        int ra, rb;
+        seg_range<K>(seg_start, sg.kind, sg.rows, lo, hi, ra, rb);
+        seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
+        if (ra >= rb) continue;
+        int expert = 0;
+        if (sg.slot >= 0) {
+            expert = S.ids[sg.slot];
+            if (expert < mp.expert_lo || expert >= mp.expert_hi) continue;
+            expert -= mp.expert_lo;
+        }
+        const int tile_rows = seg_tile_rows<K>(sg.kind);
+        const uint8_t* w = sg.w + (long long)expert * sg.w_stride;
+        const uint8_t* s = sg.s ? sg.s + (long long)expert * sg.s_stride : nullptr;
+        const uint8_t* w2 = sg.w2 ? sg.w2 + (long long)expert * sg.w_stride : nullptr;
+        const uint8_t* s2 = sg.s2 ? sg.s2 + (long long)expert * sg.s_stride : nullptr;
+#pragma unroll 1
+        for (int r0 = ra; r0 < rb; r0 += tile_rows, ++it) {
+            const int n = min(tile_rows, rb - r0);
+            const int st = it % NS;
+            if (*S.abort || !mbar_wait(S.empty + st, ((it / NS) & 1) ^ 1, mp.status)) return false;
+            uint8_t* dst = S.stages + (size_t)st * kStreamStageBytes;
+            uint64_t* full = S.full + st;
+            if (sg.kind == SEG_BF16) {
+                mbar_expect_tx(full, n * 2 * K);
+                bulk_load(dst, w + (long long)r0 * 2 * K, n * 2 * K, full);
+            } else if (sg.kind == SEG_FP4) {
+                mbar_expect_tx(full, n * (K / 2 + K / 16));
+                bulk_load(dst, w + (long long)r0 * (K / 2), n * (K / 2), full);
+                bulk_load(dst + tile_rows * (K / 2), s + (long long)r0 * (K / 16), n * (K / 16), full);
+            } else {
+                mbar_expect_tx(full, 2 * n * (K / 2 + K / 16));
+                uint8_t* sc = dst + 2 * tile_rows * (K / 2);
+                bulk_load(dst, w + (long long)r0 * (K / 2), n * (K / 2), full);
+                bulk_load(dst + tile_rows * (K / 2), w2 + (long long)r0 * (K / 2), n * (K / 2), full);
+                bulk_load(sc, s + (long long)r0 * (K / 16), n * (K / 16), full);
+                bulk_load(sc + tile_rows * (K / 16), s2 + (long long)r0 * (K / 16), n * (K / 16), full);
+            }
+        }
+    }
+    return true;
+}
+
+// Down projections: the block's output rows of every slot, slots grouped five to a tile.
+QD_DEVINL bool produce_down(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it) {
+    const int H = mp.hidden;
+    const int r0 = (int)((long long)H * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)H * (blockIdx.x + 1) / gridDim.x);
+    const int n = r1 - r0, nslots = mp.topk + 1;
+    const int tiles = (nslots + kMegaDownSlotsPerTile - 1) / kMegaDownSlotsPerTile;
+#pragma unroll 1
+    for (int t = 0; t < tiles; ++t, ++it) {
+        const int st = it % NS;
+        if (*S.abort || !mbar_wait(S.empty + st, ((it / NS) & 1) ^ 1, mp.status)) return false;
+        uint8_t* dst = S.stages + (size_t)st * kStreamStageBytes;
+        const int s_lo = t * kMegaDownSlotsPerTile, s_hi = min(nslots, s_lo + kMegaDownSlotsPerTile);
+        uint32_t bytes = 0;
+        for (int s = s_lo; s < s_hi; ++s) {
+            const bool shared = s == mp.topk;
+            const int e = shared ? 0 : S.ids[s];
+            if (shared || (e >= mp.expert_lo && e < mp.expert_hi)) bytes += (uint32_t)n * kDownRowBytes;
+        }
+        mbar_expect_tx(S.full + st, bytes);
+        for (int s = s_lo; s < s_hi; ++s) {
+            const bool shared = s == mp.topk;
+            const int e = shared ? 0 : S.ids[s];
+            if (!shared && (e < mp.expert_lo || e >= mp.expert_hi)) continue;
+            if (n <= 0) continue;
+            const long long row = shared ? r0 : (long long)(e - mp.expert_lo) * H + r0;
+            const uint8_t* w = (shared ? ph.sw : ph.dw) + row * (kDownWidth / 2);
+            const uint8_t* sc = (shared ? ph.ss : ph.ds) + row * (kDownWidth / 16);
+            uint8_t* d = dst + (size_t)(s - s_lo) * kMegaDownRows * kDownRowBytes;
+            bulk_load(d, w, n * (kDownWidth / 2), S.full + st);
+            bulk_load(d + kMegaDownRows * (kDownWidth / 2), sc, n * (kDownWidth / 16), S.full + st);
+        }
+    }
+    return true;
+}
+
+QD_DEVINL void producer(const MegaParams& mp, const Smem& S, int lane) {
+    int it = 0;
+    bool ok = true;
+#pragma unroll 1
+    for (int pi = 0; pi < mp.nphases && ok; ++pi) {
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(mp.program + pi);
+            uint4* dst = reinterpret_cast<uint4*>(S.pph);
+            for (int i = lane; i < (int)(sizeof(MegaPhase) / 16); i += 32) dst[i] = __ldg(src + i);
+        }
+        __syncwarp();
+        const MegaPhase& ph = *S.pph;
+        if (lane == 0 && (ph.kind == MK_STREAM || ph.kind == MK_DOWN)) {
+            if (ph.uses_ids) ok = flag_wait(S.ids_seq, ph.layer + 1, S.abort, mp.status);
+            trace_mark(mp, pi, 4);
+            if (ok) {
+                if (ph.kind == MK_DOWN) ok = produce_down(mp, ph, S, it);
+                else if (ph.width == 2048) ok = produce_stream<2048>(mp, ph, S, it);
+                else ok = produce_stream<4096>(mp, ph, S, it);
+            }
+            trace_mark(mp, pi, 5);
+            if (!ok) give_up(mp, S);
+        }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        __syncwarp();
+    }
+    // Never leave with copies in flight: the full barrier of a stage completes when its bytes
+    // have landed, whether or not the consumers have used them (bounded).
+    if (lane == 0) {
+        for (int back = 1; back <= NS && back <= it; ++back) {
+            const int j = it - back;
+            mbar_wait(S.full + (j % NS), (j / NS) & 1, nullptr);
+        }
+    }
+}
+
+// ========================================================================== consumers
+// One streaming phase: activation vector -> registers, then this block's rows of the ring.
+template <int KC, bool WITH_BF16>
+QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi, int& it) {
+    constexpr int K = KC * 1024;
+    constexpr int EPC = K / CT;                 // elements a thread converts (4 or 8)
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    bf16* xs = S.xs;
+    uint32_t* xf = S.xf;
+    float* red = S.red;
+    const unsigned lo = blockIdx.x * ph.quota + min(blockIdx.x, ph.remainder);
+    const unsigned hi = (blockIdx.x + 1) * ph.quota + min(blockIdx.x + 1, ph.remainder);
+
+    // ---- static prefetch: norm gamma, conv taps and history of this block's channels
+    float gam[8];
+    if (KC == 2 && ph.prologue == PRO_ADD_NORM && tid < 256) {
+        const float4 g0 = *reinterpret_cast<const float4*>(ph.gamma + tid * 8);
+        const float4 g1 = *reinterpret_cast<const float4*>(ph.gamma + tid * 8 + 4);
+        gam[0] = g0.x; gam[1] = g0.y; gam[2] = g0.z; gam[3] = g0.w;
+        gam[4] = g1.x; gam[5] = g1.y; gam[6] = g1.z; gam[7] = g1.w;
+    }
+    int conv_row0 = 0;
+    bf16* conv_state = nullptr;
+    if (ph.conv_taps) {
+        const int W = mp.conv_width;
+        conv_state = reinterpret_cast<bf16*>(mp.st.conv_state) + (size_t)ph.state_index * mp.channels * (W - 1);
+        unsigned seg_start = 0;
+#pragma unroll 1
+        for (int i = 0; i < ph.nseg; ++i) {
+            const MegaSeg& sg = ph.seg[i];
+            if (sg.epilogue == EP_CONV) {
+                int ra, rb;
+                seg_range<K>(seg_start, sg.kind, sg.rows, lo, hi, ra, rb);
+                conv_row0 = ra;
+                const int n = min(rb - ra, kMegaConvRows);
+                for (int e = tid; e < n * W; e += CT) S.conv_taps[e] = ph.conv_taps[(size_t)ra * W + e];
+                for (int e = tid; e < n * (W - 1); e += CT) S.conv_state[e] = conv_state[(size_t)ra * (W - 1) + e];
+            }
+            seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
+        }
+    }
+    phase_wait(mp, S, pi, tid);
+    if (tid == 0) trace_mark(mp, pi, 0);
+
+    // ---- routing for this layer (every block selects the same experts from the same logits)
+    if (ph.route && warp == 0) {
+        route_small(ph.router_logits, mp.experts, mp.topk, S.ids, S.weights, lane);
+        __syncwarp();
+        if (blockIdx.x == 0 && lane < mp.topk) { ph.ids_out[lane] = S.ids[lane]; ph.weights_out[lane] = S.weights[lane]; }
+        if (lane == 0) { __threadfence_block(); *S.ids_seq = ph.layer + 1; }
+    }
+
+    if (!ph.keep_x) {
+        const bf16* xin = ph.from_token ? mp.embed + (size_t)(*mp.token) * K : ph.x;
+        uint32_t m2 = 0u;
+        if (KC == 2 && ph.prologue == PRO_ADD_NORM) {
+            // residual add + RMSNorm by the first 256 threads, eight elements each
+            // (quickdraw/models/qwen.py:205-214)
+            if (tid < 256) {
+                float v[8];
+                float ss = 0.f;
+                const uint4 xa = __ldcg(reinterpret_cast<const uint4*>(xin + tid * 8));
+                uint4 ra4 = make_uint4(0u, 0u, 0u, 0u);
+                if (ph.residual) ra4 = __ldcg(reinterpret_cast<const uint4*>(ph.residual + tid * 8));
+                const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w}, rw0[4] = {ra4.x, ra4.y, ra4.z, ra4.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    v[2 * q] = __uint_as_float(xw[q] << 16) + __uint_as_float(rw0[q] << 16);
+                    v[2 * q + 1] = __uint_as_float(xw[q] & 0xffff0000u) + __uint_as_float(rw0[q] & 0xffff0000u);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+                ss = warp_sum(ss);
+                if (lane == 0) red[warp] = ss;
+                named_barrier(2, 256);
+                float tot = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) tot += red[w];
+                const float inv = rsqrtf(tot / (float)K + mp.eps);
+                uint32_t nw[4], rw[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const __nv_bfloat162 n2 = __floats2bfloat162_rn((v[2 * q] * inv) * gam[2 * q],
+                                                                    (v[2 * q + 1] * inv) * gam[2 * q + 1]);
+                    const __nv_bfloat162 r2 = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+                    nw[q] = *reinterpret_cast<const uint32_t*>(&n2);
+                    rw[q] = *reinterpret_cast<const uint32_t*>(&r2);
+                    m2 = max_u16x2(m2, nw[q] & 0x7fff7fffu);
+                }
+                const uint4 nv = make_uint4(nw[0], nw[1], nw[2], nw[3]);
+                *reinterpret_cast<uint4*>(xs + tid * 8) = nv;
+                if (blockIdx.x == 0) {
+                    if (ph.x_out) *reinterpret_cast<uint4*>(ph.x_out + tid * 8) = nv;
+                    *reinterpret_cast<uint4*>(ph.residual_out + tid * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                }
+            }
+        } else if (ph.prologue == PRO_GATED_NORM) {
+            // per-head RMSNorm of o, times gamma, times silu(z); one warp per 128-wide head
+            // (quickdraw/models/qwen.py:161-164)
+            for (int h = warp; h < K / 128; h += CW) {
+                float o[4], ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { o[j] = ldcg_bf16(xin + h * 128 + j * 32 + lane); ss += o[j] * o[j]; }
+                ss = warp_sum(ss);
+                const float inv = rsqrtf(ss / 128.f + mp.eps);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = h * 128 + j * 32 + lane;
+                    const float zz = ldcg_bf16(ph.z + i);
+                    const bf16 n = __float2bfloat16_rn(((o[j] * inv) * ld_bf16(ph.head_gamma + j * 32 + lane)) * silu_precise(zz));
+                    xs[i] = n;
+                    m2 = max(m2, (uint32_t)(__bfloat16_as_ushort(n) & 0x7fffu));
+                    if (blockIdx.x == 0 && ph.x_out) ph.x_out[i] = n;
+                }
+            }
+        } else {
+            for (int i = tid; i < K / 8; i += CT) {
+                const uint4 v = __ldcg(reinterpret_cast<const uint4*>(xin) + i);
+                reinterpret_cast<uint4*>(xs)[i] = v;
+                m2 = max_u16x2(m2, v.x & 0x7fff7fffu); m2 = max_u16x2(m2, v.y & 0x7fff7fffu);
+                m2 = max_u16x2(m2, v.z & 0x7fff7fffu); m2 = max_u16x2(m2, v.w & 0x7fff7fffu);
+            }
+        }
+        {
+            uint32_t m = max(m2 & 0xffffu, m2 >> 16);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0) reinterpret_cast<uint32_t*>(red)[16 + warp] = m;
+        }
+    }
+    named_barrier(1, CT);
+    // ---- the vector as f16 pairs, scaled down by a power of two only if it would overflow f16
+    uint32_t xh[KC][16];
+    float out_mult;
+    {
+        uint32_t m = 0u;
+#pragma unroll
+        for (int w = 0; w < CW; ++w) m = max(m, reinterpret_cast<const uint32_t*>(red)[16 + w]);
+        const int exponent = (int)(m >> 7) - 127;
+        const int shift = exponent > 14 ? exponent - 14 : 0;
+        const float down = __uint_as_float((uint32_t)(127 - shift) << 23);
+        out_mult = __uint_as_float((uint32_t)(127 + min(shift, 127)) << 23);
+        if (!ph.keep_x) {
+            if (EPC == 8) {
+                const uint4 v = *reinterpret_cast<const uint4*>(xs + tid * 8);
+                uint4 h;
+                h.x = pack_f16x2(__uint_as_float(v.x << 16) * down, __uint_as_float(v.x & 0xffff0000u) * down);
+                h.y = pack_f16x2(__uint_as_float(v.y << 16) * down, __uint_as_float(v.y & 0xffff0000u) * down);
+                h.z = pack_f16x2(__uint_as_float(v.z << 16) * down, __uint_as_float(v.z & 0xffff0000u) * down);
+                h.w = pack_f16x2(__uint_as_float(v.w << 16) * down, __uint_as_float(v.w & 0xffff0000u) * down);
+                *reinterpret_cast<uint4*>(xf + tid * 4) = h;
+            } else {
+                const uint2 v = *reinterpret_cast<const uint2*>(xs + tid * 4);
+                uint2 h;
+                h.x = pack_f16x2(__uint_as_float(v.x << 16) * down, __uint_as_float(v.x & 0xffff0000u) * down);
+                h.y = pack_f16x2(__uint_as_float(v.y << 16) * down, __uint_as_float(v.y & 0xffff0000u) * down);
+                *reinterpret_cast<uint2*>(xf + tid * 2) = h;
+            }
+            named_barrier(1, CT);
+        }
+#pragma unroll
+        for (int c = 0; c < KC; ++c)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 v = lds128(reinterpret_cast<const uint8_t*>(xf) + (c * 32 + lane) * 64 + q * 16);
+                xh[c][q * 4 + 0] = v.x; xh[c][q * 4 + 1] = v.y; xh[c][q * 4 + 2] = v.z; xh[c][q * 4 + 3] = v.w;
+            }
+    }
+    constexpr int NB = WITH_BF16 ? K / 256 : 1;
+    uint32_t xb[NB * 4];
+    if (WITH_BF16) {
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const uint4 v = lds128(reinterpret_cast<const uint8_t*>(xs) + (i * 32 + lane) * 16);
+            xb[i * 4 + 0] = v.x; xb[i * 4 + 1] = v.y; xb[i * 4 + 2] = v.z; xb[i * 4 + 3] = v.w;
+        }
+    }
+
+    if (tid == 0) trace_mark(mp, pi, 2);
+    // ---- rows
+    float best_val = -INFINITY;
+    bool first_tile = true;
+    int best_idx = 0x7fffffff;
+    unsigned seg_start = 0;
+    int turn = 0;                      // rows handed out so far: rotates the row -> warp map
+    bool ok = !*S.abort;
+#pragma unroll 1
+    for (int i = 0; i < ph.nseg && ok; ++i) {
+        const MegaSeg& sg = ph.seg[i];
+        int ra, rb;
+        seg_range<K>(seg_start, sg.kind, sg.rows, lo, hi, ra, rb);
+        seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
+        if (ra >= rb) continue;
+        int expert = 0;
+        if (sg.slot >= 0) {
+            expert = S.ids[sg.slot];
+            if (expert < mp.expert_lo || expert >= mp.expert_hi) continue;
+            expert -= mp.expert_lo;
+        }
+        const int tile_rows = seg_tile_rows<K>(sg.kind);
+        const float g1 = sg.g ? sg.g[sg.g_per_expert ? expert : 0] : 1.f;
+        const float g2 = sg.g2 ? sg.g2[sg.g_per_expert ? expert : 0] : 1.f;
+        bf16* y = sg.epilogue == EP_ARGMAX ? mp.logits : sg.y;
+#pragma unroll 1
+        for (int r0 = ra; r0 < rb; r0 += tile_rows, ++it) {
+            const int n = min(tile_rows, rb - r0);
+            const int st = it % NS;
+            if (!mbar_wait(S.full + st, (it / NS) & 1, mp.status)) { ok = false; break; }
+            if (first_tile && tid == 0) trace_mark(mp, pi, 3);
+            first_tile = false;
+            const uint8_t* base = S.stages + (size_t)st * kStreamStageBytes;
+#pragma unroll 1
+            for (int r = (warp - turn) & (CW - 1); r < n; r += CW) {
+                const int row = r0 + r;
+                float result;
+                if (sg.kind == SEG_BF16) {
+                    if (WITH_BF16) result = warp_sum(bf16_row_dot<NB>(base + (size_t)r * 2 * K, xb, lane));
+                    else result = 0.f;
+                } else {
+                    const int halves = sg.kind == SEG_FP4_PAIR ? 2 : 1;
+                    const uint8_t* sc = base + halves * tile_rows * (K / 2);
+                    float acc[2] = {0.f, 0.f};
+#pragma unroll 1
+                    for (int h = 0; h < halves; ++h)
+                        acc[h] = warp_sum(fp4_row_dot<KC>(base + (h * tile_rows + r) * (K / 2),
+                                                          sc + (h * tile_rows + r) * (K / 16), xh, lane));
+                    result = (acc[0] * out_mult) * g1;
+                    if (halves == 2) {
+                        const float up = round_bf16((acc[1] * out_mult) * g2);
+                        result = round_bf16(silu_precise(round_bf16(result))) * up;
+                    }
+                }
+                const bf16 rounded = __float2bfloat16_rn(result);
+                if (sg.epilogue == EP_CONV) {
+                    // depthwise causal conv of this channel (quickdraw/models/qwen.py:134-136)
+                    const int W = mp.conv_width, local = row - conv_row0;
+                    float val = 0.f, tap = 0.f;
+                    if (lane < W) {
+                        tap = __bfloat162float(S.conv_taps[local * W + lane]);
+                        val = lane < W - 1 ? __bfloat162float(S.conv_state[local * (W - 1) + lane]) : __bfloat162float(rounded);
+                    }
+                    const float conv = warp_sum(lane < W ? round_bf16(val * tap) : 0.f);
+                    if (lane >= 1 && lane < W) conv_state[(size_t)row * (W - 1) + lane - 1] = __float2bfloat16_rn(val);
+                    if (lane == 0) y[row] = __float2bfloat16_rn(silu_precise(conv));
+                } else {
+                    if (lane == 0) y[row] = rounded;
+                    if (sg.epilogue == EP_ARGMAX) {
+                        const float v = __bfloat162float(rounded);
+                        if (v > best_val || (v == best_val && row < best_idx)) { best_val = v; best_idx = row; }
+                    }
+                }
+            }
+            turn = (turn + n) & (CW - 1);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(S.empty + st);
+        }
+    }
+    if (!ok && lane == 0) give_up(mp, S);
+    // ---- greedy argmax over the logits (ties: lowest index)
+    if (ph.argmax) {
+        if (lane == 0) { red[32 + warp] = best_val; reinterpret_cast<int*>(red)[48 + warp] = best_idx; }
+        named_barrier(1, CT);
+        if (tid == 0) {
+            float bv = red[32]; int bi = reinterpret_cast<int*>(red)[48];
+            for (int w = 1; w < CW; ++w) {
+                const float v = red[32 + w]; const int ix = reinterpret_cast<int*>(red)[48 + w];
+                if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+            }
+            mp.best_val[blockIdx.x] = bv;
+            mp.best_idx[blockIdx.x] = bi;
+            __threadfence();
+            const unsigned int done = atomicAdd(mp.argmax_counter, 1u);
+            if (done == gridDim.x - 1) {
+                __threadfence();
+                float fv = -INFINITY; int fi = 0x7fffffff;
+                for (int b = 0; b < (int)gridDim.x; ++b) {
+                    const float v = __ldcg(mp.best_val + b);
+                    const int ix = __ldcg(mp.best_idx + b);
+                    if (v > fv || (v == fv && ix < fi)) { fv = v; fi = ix; }
+                }
+                *mp.next_token = fi == 0x7fffffff ? 0 : fi;
+                *mp.argmax_counter = 0;
+            }
+        }
+    }
+}
+
+// Gated delta-rule recurrence (quickdraw/models/qwen.py:139-160): block = (value head, 32
+// value columns), 256 threads = 8 key groups x 32 columns, 16 state entries per thread.
+QD_DEVINL void gdn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
+    const int tid = threadIdx.x, col = tid & 31, kg = tid >> 5;
+    const int dk = mp.dk, dv = mp.dv, hk = mp.hk, hv = mp.hv;
+    const int slices = dv / 32;
+    const int unit = blockIdx.x;
+    const bool active = unit < hv * slices && tid < 256;
+    const int head = unit / slices, c0 = (unit % slices) * 32;
+    const int kpt = (dk + 7) / 8;                 // <= 16
+    float* sq = S.scratch;            // [128]
+    float* sk = sq + 128;             // [128]
+    float* part = sk + 128;           // [8][32]
+    float* norms = part + 256;        // [2]
+    float* gates = norms + 2;         // [2]
+    float* state = mp.st.rec_state + (size_t)ph.state_index * hv * dk * dv;
+    float* tile = state + (size_t)head * dk * dv + c0 + col;
+    float s[16];
+    if (active) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int key = kg * kpt + j;
+            s[j] = (j < kpt && key < dk) ? tile[(size_t)key * dv] : 0.f;
+        }
+    }
+    phase_wait(mp, S, pi, tid);
+    if (tid == 0) trace_mark(mp, pi, 0);
+    if (!active) return;
+    const int key_head = head / (hv / hk);
+    const bf16* qh = ph.qkv + (size_t)key_head * dk;
+    const bf16* kh = ph.qkv + (size_t)hk * dk + (size_t)key_head * dk;
+    float qq = 0.f, kk = 0.f;
+    for (int i = tid; i < dk; i += 256) {
+        const float qv = ldcg_bf16(qh + i), kv = ldcg_bf16(kh + i);
+        sq[i] = qv; sk[i] = kv;
+        qq += qv * qv; kk += kv * kv;
+    }
+    qq = warp_sum(qq); kk = warp_sum(kk);
+    if (col == 0) { part[kg * 32] = qq; part[kg * 32 + 1] = kk; }
+    named_barrier(2, 256);
+    if (tid == 0) {
+        float tq = 0.f, tk = 0.f;
+        for (int w = 0; w < 8; ++w) { tq += part[w * 32]; tk += part[w * 32 + 1]; }
+        norms[0] = rsqrtf(tq + 1e-6f);
+        norms[1] = rsqrtf(tk + 1e-6f);
+        const float alpha = ldcg_bf16(ph.a + head) + ld_bf16(ph.dt_bias + head);
+        gates[0] = expf(-expf(ld_bf16(ph.a_log + head)) * softplus_precise(alpha));
+        gates[1] = sigmoid_precise(ldcg_bf16(ph.b + head));
+    }
+    named_barrier(2, 256);
+    const float kscale = norms[1];
+    const float decay = gates[0], beta = gates[1];
+    const float v = ldcg_bf16(ph.qkv + (size_t)2 * hk * dk + (size_t)head * dv + c0 + col);
+    float pred = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int key = kg * kpt + j;
+        if (j < kpt && key < dk) {
+            s[j] *= decay;
+            pred += s[j] * (sk[key] * kscale);
+        }
+    }
+    part[kg * 32 + col] = pred;
+    named_barrier(2, 256);
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += part[w * 32 + col];
+    const float corr = beta * (v - total);
+    named_barrier(2, 256);
+    float o = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int key = kg * kpt + j;
+        if (j < kpt && key < dk) {
+            s[j] += (sk[key] * kscale) * corr;
+            o += s[j] * ((sq[key] * norms[0]) / sqrtf((float)dk));
+            tile[(size_t)key * dv] = s[j];
+        }
+    }
+    part[kg * 32 + col] = o;
+    named_barrier(2, 256);
+    if (kg == 0) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) acc += part[w * 32 + col];
+        ph.mix_out[(size_t)head * dv + c0 + col] = __float2bfloat16_rn(acc);
+    }
+}
+
+// RMSNorm with gamma = 1 + weight and partial RoPE of one head by one warp; the rotation
+// angles come from a table of bf16-rounded cos / sin shared by all heads
+// (quickdraw/models/qwen.py:76-92).
+QD_DEVINL void norm_rope_row(const bf16* __restrict__ src, const bf16* __restrict__ gamma_w, int d, int rotary,
+                             float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int lane,
+                             float* __restrict__ dst) {
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) { const float v = ldcg_bf16(src + i); ss += v * v; }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)d + eps);
+    for (int i = lane; i < d; i += 32)
+        dst[i] = round_bf16((ldcg_bf16(src + i) * inv) * (1.0f + ld_bf16(gamma_w + i)));
+    __syncwarp();
+    const int half = rotary / 2;
+    float rotated[8];
+    int n = 0;
+    for (int i = lane; i < rotary; i += 32, ++n) {
+        const int f = i % half;
+        const float partner = i < half ? -dst[i + half] : dst[i - half];
+        rotated[n & 7] = round_bf16(dst[i] * cos_t[f] + partner * sin_t[f]);
+    }
+    __syncwarp();
+    n = 0;
+    for (int i = lane; i < rotary; i += 32, ++n) dst[i] = rotated[n & 7];
+    __syncwarp();
+}
+
+// Gated GQA decode attention (quickdraw/models/qwen.py:66-116): block = (KV head, context
+// split); warp = (one of eight position lanes, one half of the query heads of the KV head).
+QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = mp.hq / mp.hkv, D = mp.d;
+    const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
+    const int T = position + 1;
+    int active = (T + 31) / 32;
+    if (active > mp.attn_splits) active = mp.attn_splits;
+    const int per = ((T + active - 1) / active + 7) & ~7;
+    const int unit = blockIdx.x;
+    const int kvh = unit / active, split = unit % active;
+    const int t0 = split * per, t1 = min(T, t0 + per);
+    const bool mine = kvh < mp.hkv;
+    float* q_s = reinterpret_cast<float*>(S.xs);            // [G][D]
+    float* k_s = reinterpret_cast<float*>(S.xf);            // [D]
+    float* cos_t = k_s + 256;                               // [rotary / 2]
+    float* sin_t = cos_t + 128;
+    float* red = S.scratch;                                 // [8 position lanes][4 heads][D + 2]
+    float* wsum = red + 8 * 4 * kAttnStride;                // final merge: [G][splits] m, then weights
+    float* lsum = wsum + 8 * kMegaAttnSplits;               // [G][splits] weight * l
+    float* hmax = lsum + 8 * kMegaAttnSplits;               // [G] max, [G] denominators
+    const size_t layer_elems = (size_t)mp.st.capacity * mp.hkv * D;
+    bf16* k_cache = reinterpret_cast<bf16*>(mp.st.kv_k) + (size_t)ph.state_index * layer_elems;
+    bf16* v_cache = reinterpret_cast<bf16*>(mp.st.kv_v) + (size_t)ph.state_index * layer_elems;
+
+    phase_wait(mp, S, pi, tid);
+    if (tid == 0) trace_mark(mp, pi, 0);
+    if (!mine) return;
+    const int half = mp.rotary / 2;
+    for (int f = tid; f < half; f += CT) {
+        const float inv_freq = 1.0f / powf(mp.theta, (float)(2 * f) / (float)mp.rotary);
+        const float angle = (float)position * inv_freq;
+        cos_t[f] = round_bf16(cosf(angle));
+        sin_t[f] = round_bf16(sinf(angle));
+    }
+    named_barrier(1, CT);
+    const bool owns_new = position >= t0 && position < t1;
+    if (warp < G)
+        norm_rope_row(ph.qg + (size_t)(kvh * G + warp) * 2 * D, ph.q_norm, D, mp.rotary, mp.eps, cos_t, sin_t, lane,
+                      q_s + warp * D);
+    if (owns_new && warp == CW - 1) {
+        norm_rope_row(ph.k_new + (size_t)kvh * D, ph.k_norm, D, mp.rotary, mp.eps, cos_t, sin_t, lane, k_s);
+        bf16* krow = k_cache + ((size_t)position * mp.hkv + kvh) * D;
+        bf16* vrow = v_cache + ((size_t)position * mp.hkv + kvh) * D;
+        for (int i = lane; i < D; i += 32) {
+            krow[i] = __float2bfloat16_rn(k_s[i]);
+            vrow[i] = __float2bfloat16_rn(ldcg_bf16(ph.v_new + (size_t)kvh * D + i));
+        }
+    }
+    named_barrier(1, CT);
+
+    const int pl = warp >> 1, hh = warp & 1;
+    const int f0 = lane * 8;
+    const bool lane_on = f0 < D;
+    float m[4], l[4], acc[4][8];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
+    }
+    const float scale = rsqrtf((float)D);
+    for (int t = t0 + pl; t < t1; t += 8) {
+        float kf[8], vf[8];
+        if (lane_on) {
+            if (t == position) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    kf[j] = k_s[f0 + j];
+                    vf[j] = ldcg_bf16(ph.v_new + (size_t)kvh * D + f0 + j);
+                }
+            } else {
+                const uint4 kr = *reinterpret_cast<const uint4*>(k_cache + ((size_t)t * mp.hkv + kvh) * D + f0);
+                const uint4 vr = *reinterpret_cast<const uint4*>(v_cache + ((size_t)t * mp.hkv + kvh) * D + f0);
+                const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    kf[2 * j] = __uint_as_float(kw[j] << 16); kf[2 * j + 1] = __uint_as_float(kw[j] & 0xffff0000u);
+                    vf[2 * j] = __uint_as_float(vw[j] << 16); vf[2 * j + 1] = __uint_as_float(vw[j] & 0xffff0000u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { kf[j] = 0.f; vf[j] = 0.f; }
+        }
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            const int head = hh * 4 + h;
+            if (head < G) {
+                float dot = 0.f;
+                if (lane_on) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dot += q_s[head * D + f0 + j] * kf[j];
+                }
+                const float sc = warp_sum(dot) * scale;
+                const float nm = fmaxf(m[h], sc);
+                const float fix = expf(m[h] - nm), pr = expf(sc - nm);
+                l[h] = l[h] * fix + pr;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[h][j] = acc[h][j] * fix + pr * vf[j];
+                m[h] = nm;
+            }
+        }
+    }
+    // merge the eight position lanes, one half of the heads at a time
+    float* block_out = mp.attn_partial + (((size_t)kvh * mp.attn_splits + split) * G) * kAttnStride;
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+        if (hh == pass) {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                float* dst = red + ((size_t)pl * 4 + h) * kAttnStride;
+                if (lane_on) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dst[f0 + j] = acc[h][j];
+                }
+                if (lane == 0) { dst[256] = m[h]; dst[257] = l[h]; }
+            }
+        }
+        named_barrier(1, CT);
+        for (int idx = tid; idx < 4 * D; idx += CT) {
+            const int h = idx / D, f = idx % D;
+            const int head = pass * 4 + h;
+            if (head >= G) continue;
+            float mm = -INFINITY;
+            for (int w = 0; w < 8; ++w) mm = fmaxf(mm, red[((size_t)w * 4 + h) * kAttnStride + 256]);
+            float num = 0.f, den = 0.f;
+            for (int w = 0; w < 8; ++w) {
+                const float* src = red + ((size_t)w * 4 + h) * kAttnStride;
+                const float wgt = src[256] == -INFINITY ? 0.f : expf(src[256] - mm);
+                num += wgt * src[f];
+                den += wgt * src[257];
+            }
+            block_out[(size_t)head * kAttnStride + f] = num;
+            if (f == 0) { block_out[(size_t)head * kAttnStride + 256] = mm; block_out[(size_t)head * kAttnStride + 257] = den; }
+        }
+        named_barrier(1, CT);
+    }
+    __threadfence();
+    named_barrier(1, CT);
+    if (tid == 0) {
+        const unsigned int done = atomicAdd(mp.attn_counters + kvh, 1u);
+        *S.flag = done == (unsigned int)active - 1;
+    }
+    named_barrier(1, CT);
+    if (!*S.flag) return;
+    __threadfence();
+    // last block of this KV head: merge the splits, normalise, gate
+    const float* base = mp.attn_partial + ((size_t)kvh * mp.attn_splits) * G * kAttnStride;
+    for (int idx = tid; idx < G * active; idx += CT) {
+        const int h = idx / active, s = idx % active;
+        wsum[h * kMegaAttnSplits + s] = __ldcg(base + ((size_t)s * G + h) * kAttnStride + 256);
+        lsum[h * kMegaAttnSplits + s] = __ldcg(base + ((size_t)s * G + h) * kAttnStride + 257);
+    }
+    named_barrier(1, CT);
+    if (tid < G) {
+        float mm = -INFINITY;
+        for (int s = 0; s < active; ++s) mm = fmaxf(mm, wsum[tid * kMegaAttnSplits + s]);
+        hmax[tid] = mm;
+    }
+    named_barrier(1, CT);
+    for (int idx = tid; idx < G * active; idx += CT) {
+        const int h = idx / active, s = idx % active;
+        const float ms = wsum[h * kMegaAttnSplits + s];
+        const float wgt = ms == -INFINITY ? 0.f : expf(ms - hmax[h]);
+        wsum[h * kMegaAttnSplits + s] = wgt;
+        lsum[h * kMegaAttnSplits + s] *= wgt;
+    }
+    named_barrier(1, CT);
+    if (tid < G) {
+        float den = 0.f;
+        for (int s = 0; s < active; ++s) den += lsum[tid * kMegaAttnSplits + s];
+        hmax[8 + tid] = den;
+    }
+    named_barrier(1, CT);
+    for (int idx = tid; idx < G * D; idx += CT) {
+        const int h = idx / D, f = idx % D;
+        float num = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < active; ++s)
+            num += wsum[h * kMegaAttnSplits + s] * __ldcg(base + ((size_t)s * G + h) * kAttnStride + f);
+        const float attended = round_bf16(num / hmax[8 + h]);
+        const int qh = kvh * G + h;
+        const float gate = round_bf16(sigmoid_precise(ldcg_bf16(ph.qg + (size_t)qh * 2 * D + D + f)));
+        ph.mix_out[(size_t)qh * D + f] = __float2bfloat16_rn(attended * gate);
+    }
+    if (tid == 0) mp.attn_counters[kvh] = 0;
+}
+
+// Routed and shared down projections with the combine (quickdraw/models/qwen.py:185-193):
+// warp s works on slot s, each half-warp on alternate rows; rounding points as in moe.cu.
+QD_DEVINL void down_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi, int& it) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int H = mp.hidden;
+    const int r0 = (int)((long long)H * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)H * (blockIdx.x + 1) / gridDim.x);
+    const int n = r1 - r0, nslots = mp.topk + 1;
+    const int tiles = (nslots + kMegaDownSlotsPerTile - 1) / kMegaDownSlotsPerTile;
+    float* contrib = S.scratch;                 // [slots][kMegaDownRows]
+    phase_wait(mp, S, pi, tid);
+    if (tid == 0) trace_mark(mp, pi, 0);
+    // Both tiles are normally on chip already (the producer fetched them during the gate/up
+    // phase); wait for them first so that nothing large is live across the waits.
+    bool ok = !*S.abort;
+    const int it0 = it;
+    for (int t = 0; t < tiles && ok; ++t)
+        ok = mbar_wait(S.full + ((it0 + t) % NS), ((it0 + t) / NS) & 1, mp.status);
+    it += tiles;
+    const int s = warp;
+    const bool worker = s < nslots;
+    const bool shared = s == mp.topk;
+    const int e = (worker && !shared) ? S.ids[s] : 0;
+    const bool owned = worker && (shared || (e >= mp.expert_lo && e < mp.expert_hi));
+    const int hl = lane & 15, half = lane >> 4;
+    if (worker && ok) {
+        uint32_t xh[16];
+        float amax = 0.f;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(ph.hidden + (size_t)s * kDownWidth) + hl * 16;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            xh[j] = __ldcg(src + j);
+            amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(xh[j] << 16)), fabsf(__uint_as_float(xh[j] & 0xffff0000u))));
+        }
+        amax = warp_max(amax);
+        int ex = 0;
+        if (amax > 0.f && amax < INFINITY) frexpf(amax, &ex);
+        const int shift = ex > 15 ? ex - 15 : 0;
+        const float down = ldexpf(1.f, -shift);
+        const float mult = ldexpf(1.f, shift);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const __half2 h = __floats2half2_rn(__uint_as_float(xh[j] << 16) * down,
+                                                __uint_as_float(xh[j] & 0xffff0000u) * down);
+            xh[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        float scale;
+        if (shared) scale = ph.sg[0];
+        else scale = round_bf16(ph.dg[ph.g_per_expert ? e - mp.expert_lo : 0] * S.weights[s]);
+        const int st = (it0 + s / kMegaDownSlotsPerTile) % NS;
+        const uint8_t* base = S.stages + (size_t)st * kStreamStageBytes +
+                              (size_t)(s % kMegaDownSlotsPerTile) * kMegaDownRows * kDownRowBytes;
+#pragma unroll 1
+        for (int rr = 0; rr < n; rr += 2) {
+            const bool live = rr + half < n;
+            const int r = live ? rr + half : n - 1;
+            float value = 0.f;
+            if (owned) {
+                const uint4 w = lds128(base + r * (kDownWidth / 2) + hl * 16);
+                const float2 sc = e4m3x2_to_float2(*reinterpret_cast<const uint16_t*>(
+                    base + kMegaDownRows * (kDownWidth / 2) + r * (kDownWidth / 16) + hl * 2));
+                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+                float g[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t h2[4];
+                    e2m1x8_to_f16x2(words[q], h2);
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        g[(q >> 1) * 2] = fma_f16_lo(h2[b], xh[q * 4 + b], g[(q >> 1) * 2]);
+                        g[(q >> 1) * 2 + 1] = fma_f16_hi(h2[b], xh[q * 4 + b], g[(q >> 1) * 2 + 1]);
+                    }
+                }
+                float acc = fmaf(sc.x, g[0] + g[1], 0.f);
+                acc = fmaf(sc.y, g[2] + g[3], acc);
+                acc = group_sum<16>(acc) * mult;
+                value = shared ? round_bf16(acc * scale) : round_bf16(round_bf16(acc) * scale);
+            }
+            if (hl == 0 && live) contrib[s * kMegaDownRows + r] = value;
+        }
+    }
+    __syncwarp();
+    if (lane == 0 && ok)
+        for (int t = 0; t < tiles; ++t) mbar_arrive(S.empty + ((it0 + t) % NS));
+    if (!ok && lane == 0) give_up(mp, S);
+    named_barrier(1, CT);
+    if (tid < n && ok) {
+        float routed = 0.f;
+        int last = -1;
+        for (int k = 0; k < mp.topk; ++k) {       // ascending expert id
+            int pick = -1, pick_id = 0x7fffffff;
+            for (int q = 0; q < mp.topk; ++q) {
+                const int id = S.ids[q];
+                if (id > last && id < pick_id) { pick = q; pick_id = id; }
+            }
+            if (pick < 0) break;
+            last = pick_id;
+            routed += contrib[pick * kMegaDownRows + tid];
+        }
+        const float gate = round_bf16(sigmoid_precise(ldcg_bf16(ph.strength)));
+        const float shared_row = round_bf16(contrib[mp.topk * kMegaDownRows + tid] * gate);
+        ph.out[r0 + tid] = __float2bfloat16_rn(round_bf16(routed) + shared_row);
+    }
+}
+
+__global__ void __launch_bounds__(kMegaThreads, 1)
+mega_kernel(const __grid_constant__ MegaParams mp) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const Smem S = carve_smem(smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if ((int)gridDim.x != mp.grid) {            // the program was laid out for another grid
+        if (tid == 0) atomicOr(mp.status, QD_STATUS_BAD_SHAPE);
+        return;
+    }
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(S.full + s, 1); mbar_init(S.empty + s, CW); }
+        mbar_fence_init();
+        *S.ids_seq = 0;
+        *S.abort = 0;
+        *S.flag = 0;
+    }
+    __syncthreads();
+    if (warp == CW) {
+        producer(mp, S, lane);
+        return;
+    }
+    // first phase parameters
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(mp.program);
+        uint4* dst = reinterpret_cast<uint4*>(S.cph);
+        for (int i = tid; i < (int)(sizeof(MegaPhase) / 16); i += CT) dst[i] = __ldg(src + i);
+    }
+    named_barrier(1, CT);
+    int it = 0;
+#pragma unroll 1
+    for (int pi = 0; pi < mp.nphases; ++pi) {
+        const MegaPhase& ph = S.cph[pi & 1];
+        if (pi + 1 < mp.nphases) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(mp.program + pi + 1);
+            uint8_t* dst = reinterpret_cast<uint8_t*>(S.cph + ((pi + 1) & 1));
+            for (int i = tid; i < (int)(sizeof(MegaPhase) / 16); i += CT) cp_async16(dst + i * 16, src + i * 16);
+        }
+        if (ph.kind == MK_STREAM) {
+            if (ph.width == 2048) stream_phase<2, true>(mp, ph, S, pi, it);
+            else stream_phase<4, false>(mp, ph, S, pi, it);
+        } else if (ph.kind == MK_GDN) {
+            gdn_phase(mp, ph, S, pi);
+        } else if (ph.kind == MK_ATTN) {
+            attn_phase(mp, ph, S, pi);
+        } else {
+            down_phase(mp, ph, S, pi, it);
+        }
+        cp_async_wait_all();
+        if (tid == 0) trace_mark(mp, pi, 1);
+        named_barrier(1, CT);
+        if (tid == 0 && pi + 1 < mp.nphases) {
+            __threadfence();
+            red_release_add(mp.bar, 1u);
+        }
+    }
+    // the last block to leave resets the barrier words for the next launch
+    if (tid == 0) {
+        __threadfence();
+        const unsigned int gone = atomicAdd(mp.exit_count, 1u);
+        if (gone == gridDim.x - 1) {
+            *mp.bar = 0u;
+            *mp.exit_count = 0u;
+            __threadfence();
+        }
+    }
+}
+
+}  // namespace
+
+size_t mega_smem_bytes() { return kSmemBytes; }
+
+int mega_launch(const MegaParams& p, cudaStream_t stream) {
+    static bool configured[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
+    if (!configured[dev]) {
+        int limit = 0;
+        cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if ((size_t)limit < kSmemBytes) return QD_ERR_UNSUPPORTED;
+        if (cudaFuncSetAttribute(mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
+            return QD_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid); cfg.blockDim = dim3(kMegaThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;      // all blocks resident at once: they wait for each other
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, mega_kernel, p) == cudaSuccess ? QD_OK : QD_ERR_LAUNCH;
+}
+
+}  // namespace qd

@@ -12,7 +12,7 @@
 #include <new>
 #include <vector>
 
-#include "stream.cuh"
+#include "mega.cuh"
 
 using namespace qd;
 
@@ -29,6 +29,7 @@ struct Workspace {
     int32_t* ids; float* weights; float* routed_partial; float* attn_scratch;
     unsigned int* attn_counters; float* best_val; int* best_idx; unsigned int* argmax_counter;
     unsigned int* status; int* cursor; unsigned int* route_counter;
+    unsigned int* grid_bar; unsigned int* grid_exit; float* mega_attn_scratch;   // persistent kernel
     size_t bytes;
 };
 
@@ -70,6 +71,9 @@ Workspace carve(const qd_model_config& c, uint8_t* base) {
     w.attn_scratch = (float*)take(4 * (size_t)qd_attn_scratch_floats(c.q_heads, c.kv_heads, c.head_dim, kAttnSplits));
     w.best_val = (float*)take(4 * kMaxGrid);
     w.best_idx = (int*)take(4 * kMaxGrid);
+    w.grid_bar = (unsigned int*)take(4);
+    w.grid_exit = (unsigned int*)take(4);
+    w.mega_attn_scratch = (float*)take(4 * (size_t)qd_attn_scratch_floats(c.q_heads, c.kv_heads, c.head_dim, kMegaAttnSplits));
     w.bytes = off;
     return w;
 }
@@ -271,4 +275,185 @@ extern "C" int qd_nvfp4_gemv_bank(const void* x, const void* codes, const void* 
         QD_TRY(stream_launch(p, 0, (cudaStream_t)stream, pdl != 0));
     }
     return QD_OK;
+}
+
+// ------------------------------------------------------------- persistent kernel program
+namespace {
+
+MegaSeg mega_seg(const StreamSeg& s) {
+    MegaSeg m = {};
+    m.w = s.w; m.s = s.s; m.g = s.g; m.w2 = s.w2; m.s2 = s.s2; m.g2 = s.g2; m.y = s.y;
+    m.w_stride = s.w_stride; m.s_stride = s.s_stride; m.rows = s.rows;
+    m.kind = (short)s.kind; m.epilogue = (short)s.epilogue; m.slot = (short)s.slot; m.g_per_expert = (short)s.g_per_expert;
+    return m;
+}
+
+// Cost partition of a streaming phase over `grid` blocks; false if it does not fit.
+bool mega_finish_stream(MegaPhase& ph, int grid) {
+    unsigned long long total = 0;
+    const unsigned fp4_row = (ph.width / 2 + ph.width / 16) / 16;
+    for (int i = 0; i < ph.nseg; ++i) {
+        const unsigned cost = ph.seg[i].kind == SEG_BF16 ? 2u * ph.width / 16 : ph.seg[i].kind == SEG_FP4_PAIR ? 2 * fp4_row : fp4_row;
+        total += (unsigned long long)ph.seg[i].rows * cost;
+        if (ph.seg[i].epilogue == EP_CONV && ph.seg[i].rows / grid + 2 > kMegaConvRows) return false;
+    }
+    if (total + 1024 >= 0xffffffffull) return false;
+    ph.quota = (unsigned)(total / grid);
+    ph.remainder = (unsigned)(total % grid);
+    return true;
+}
+
+int mega_phase_count(const qd_model_config& c) { return 6 * c.layers + 1; }
+
+bool mega_shape_ok(const qd_model_config& c, int grid) {
+    return fused_shape_ok(c) && c.expert_lo == 0 && c.expert_hi >= c.experts && c.conv_width <= kStreamConvWidth &&
+           c.key_dim <= 128 && c.value_dim % 32 == 0 && c.value_heads * (c.value_dim / 32) <= grid &&
+           c.head_dim == 256 && c.rotary_dim <= 256 && c.kv_heads >= 1 && c.kv_heads <= grid &&
+           c.q_heads / c.kv_heads <= 8 && (c.hidden + grid - 1) / grid <= kMegaDownRows &&
+           c.topk + 1 <= 2 * kMegaDownSlotsPerTile && grid <= kMaxGrid;
+}
+
+int mega_attn_splits(const qd_model_config& c, int grid) {
+    int s = grid / c.kv_heads;
+    return s > kMegaAttnSplits ? kMegaAttnSplits : s;
+}
+
+}  // namespace
+
+extern "C" long long qd_program_bytes(const qd_model* model) {
+    if (!model) return -1;
+    return (long long)mega_phase_count(model->cfg) * (long long)sizeof(MegaPhase);
+}
+
+extern "C" int qd_program_build(const qd_model* model, void* workspace, void* host_out, long long bytes) {
+    QD_CHECK_ARG(model && workspace && host_out);
+    const qd_model_config& c = model->cfg;
+    const int grid = stream_sm_count();
+    if (!mega_shape_ok(c, grid)) return QD_ERR_UNSUPPORTED;
+    if (bytes < qd_program_bytes(model)) return QD_ERR_ARG;
+    Workspace w = carve(c, (uint8_t*)workspace);
+    MegaPhase* out = (MegaPhase*)host_out;
+    const int H = c.hidden;
+    const int channels = 2 * c.key_heads * c.key_dim + c.value_heads * c.value_dim;
+    const int value_width = c.value_heads * c.value_dim;
+    const int q_width = c.q_heads * c.head_dim, kv_width = c.kv_heads * c.head_dim;
+    int n = 0;
+    for (int L = 0; L < c.layers; ++L) {
+        if (!model->layer_set[L]) return QD_ERR_ARG;
+        const qd_layer& ly = model->layers[L];
+        // ---- A: residual add + norm -> mixer input projections
+        MegaPhase a = {};
+        a.kind = MK_STREAM; a.width = H; a.prologue = PRO_ADD_NORM; a.layer = L; a.state_index = ly.state_index;
+        a.gamma = ly.gamma_in; a.residual_out = w.resid[1];
+        if (L == 0) { a.from_token = 1; a.residual = nullptr; }
+        else { a.x = w.moe_out; a.residual = w.resid[0]; }
+        if (ly.is_attention) {
+            a.nseg = 3;
+            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, 2 * q_width, w.big));
+            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, kv_width, w.mid));
+            a.seg[2] = mega_seg(fp4_seg(ly.proj_c, kv_width, w.mid + kv_width));
+        } else {
+            a.nseg = 4;
+            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, channels, w.big, EP_CONV));
+            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, value_width, w.mid));
+            a.seg[2] = mega_seg(bf16_seg(ly.in_proj_a, c.value_heads, w.ab));
+            a.seg[3] = mega_seg(bf16_seg(ly.in_proj_b, c.value_heads, w.ab + c.value_heads));
+            a.conv_taps = (const bf16*)ly.conv1d;
+        }
+        if (!mega_finish_stream(a, grid)) return QD_ERR_UNSUPPORTED;
+        out[n++] = a;
+        // ---- M: mixer core
+        MegaPhase m = {};
+        m.layer = L; m.state_index = ly.state_index; m.mix_out = w.o;
+        if (ly.is_attention) {
+            m.kind = MK_ATTN;
+            m.qg = w.big; m.k_new = w.mid; m.v_new = w.mid + kv_width;
+            m.q_norm = (const bf16*)ly.q_norm; m.k_norm = (const bf16*)ly.k_norm;
+        } else {
+            m.kind = MK_GDN;
+            m.qkv = w.big; m.a = w.ab; m.b = w.ab + c.value_heads;
+            m.a_log = (const bf16*)ly.a_log; m.dt_bias = (const bf16*)ly.dt_bias;
+        }
+        out[n++] = m;
+        // ---- B: output projection
+        MegaPhase b = {};
+        b.kind = MK_STREAM; b.width = 4096; b.layer = L; b.x = w.o;
+        b.nseg = 1; b.seg[0] = mega_seg(fp4_seg(ly.proj_out, H, w.mixed));
+        if (ly.is_attention) b.prologue = PRO_NONE;
+        else { b.prologue = PRO_GATED_NORM; b.z = w.mid; b.head_gamma = (const bf16*)ly.head_norm; }
+        if (!mega_finish_stream(b, grid)) return QD_ERR_UNSUPPORTED;
+        out[n++] = b;
+        // ---- C: residual add + norm -> router logits, shared gate logit, shared gate/up
+        MegaPhase cc = {};
+        cc.kind = MK_STREAM; cc.width = H; cc.prologue = PRO_ADD_NORM; cc.layer = L;
+        cc.gamma = ly.gamma_post; cc.x = w.mixed; cc.residual = w.resid[1]; cc.residual_out = w.resid[0];
+        cc.nseg = 3;
+        cc.seg[0] = mega_seg(bf16_seg(ly.router, c.experts, w.router_logits));
+        cc.seg[1] = mega_seg(bf16_seg(ly.shared_expert_gate, 1, w.strength));
+        cc.seg[2] = mega_seg(pair_seg(ly.shared_gate, ly.shared_up, c.intermediate, w.hidden + (size_t)c.topk * c.intermediate));
+        if (!mega_finish_stream(cc, grid)) return QD_ERR_UNSUPPORTED;
+        out[n++] = cc;
+        // ---- D: routing, then the routed gate/up pairs on the vector phase C built
+        MegaPhase d = {};
+        d.kind = MK_STREAM; d.width = H; d.prologue = PRO_NONE; d.layer = L; d.keep_x = 1; d.route = 1; d.uses_ids = 1;
+        d.router_logits = w.router_logits; d.ids_out = w.ids; d.weights_out = w.weights;
+        d.nseg = c.topk;
+        for (int s = 0; s < c.topk; ++s) {
+            StreamSeg sg = pair_seg(ly.experts_gate, ly.experts_up, c.intermediate, w.hidden + (size_t)s * c.intermediate);
+            sg.slot = s; sg.g_per_expert = ly.experts_global_per_expert;
+            sg.w_stride = (long long)c.intermediate * (H / 2);
+            sg.s_stride = (long long)c.intermediate * (H / 16);
+            d.seg[s] = mega_seg(sg);
+        }
+        if (!mega_finish_stream(d, grid)) return QD_ERR_UNSUPPORTED;
+        out[n++] = d;
+        // ---- E: down projections and combine
+        MegaPhase e = {};
+        e.kind = MK_DOWN; e.layer = L; e.uses_ids = 1;
+        e.hidden = w.hidden; e.dw = (const uint8_t*)ly.experts_down.codes; e.ds = (const uint8_t*)ly.experts_down.scales;
+        e.dg = ly.experts_down.global; e.g_per_expert = ly.experts_global_per_expert;
+        e.sw = (const uint8_t*)ly.shared_down.codes; e.ss = (const uint8_t*)ly.shared_down.scales; e.sg = ly.shared_down.global;
+        e.strength = w.strength; e.out = w.moe_out;
+        out[n++] = e;
+    }
+    // ---- head: residual add + final norm -> LM head rows with greedy argmax
+    MegaPhase h = {};
+    h.kind = MK_STREAM; h.width = H; h.prologue = PRO_ADD_NORM; h.layer = c.layers; h.argmax = 1;
+    h.gamma = c.final_gamma; h.x = w.moe_out; h.residual = w.resid[0]; h.residual_out = w.resid[1];
+    h.nseg = 1;
+    h.seg[0] = mega_seg(bf16_seg(c.lm_head, c.vocab, nullptr, EP_ARGMAX));
+    if (!mega_finish_stream(h, grid)) return QD_ERR_UNSUPPORTED;
+    out[n++] = h;
+    return n == mega_phase_count(c) ? QD_OK : QD_ERR_ARG;
+}
+
+extern "C" int qd_decode_step_persistent(const qd_model* model, const qd_state* state, const long long* token,
+                                         const int* position_dev, int position_host, void* workspace,
+                                         const void* program, void* logits_out, long long* next_token,
+                                         int flags, unsigned long long* trace, void* stream) {
+    QD_CHECK_ARG(model && state && token && workspace && program && next_token);
+    QD_CHECK_ARG((flags & QD_FLAG_NO_LOGITS) || logits_out);
+    QD_CHECK_ARG(position_dev || (position_host >= 0 && position_host < state->capacity));
+    const qd_model_config& c = model->cfg;
+    const int grid = stream_sm_count();
+    if (!mega_shape_ok(c, grid)) return QD_ERR_UNSUPPORTED;
+    Workspace w = carve(c, (uint8_t*)workspace);
+    MegaParams p = {};
+    p.program = (const MegaPhase*)program;
+    p.nphases = mega_phase_count(c) - ((flags & QD_FLAG_NO_LOGITS) ? 1 : 0);
+    p.grid = grid;
+    p.st = *state;
+    p.token = token; p.pos_dev = position_dev; p.pos_host = position_host;
+    p.embed = (const bf16*)c.embed; p.logits = (bf16*)logits_out; p.next_token = next_token;
+    p.best_val = w.best_val; p.best_idx = w.best_idx; p.argmax_counter = w.argmax_counter;
+    p.bar = w.grid_bar; p.exit_count = w.grid_exit; p.status = w.status;
+    p.attn_partial = w.mega_attn_scratch; p.attn_counters = w.attn_counters; p.attn_splits = mega_attn_splits(c, grid);
+    p.hk = c.key_heads; p.hv = c.value_heads; p.dk = c.key_dim; p.dv = c.value_dim;
+    p.hq = c.q_heads; p.hkv = c.kv_heads; p.d = c.head_dim; p.rotary = c.rotary_dim;
+    p.theta = c.rope_theta; p.eps = c.eps;
+    p.conv_width = c.conv_width; p.topk = c.topk; p.experts = c.experts; p.hidden = c.hidden;
+    p.channels = 2 * c.key_heads * c.key_dim + c.value_heads * c.value_dim;
+    p.expert_lo = c.expert_lo; p.expert_hi = c.expert_hi;
+    p.trace = trace;
+    return mega_launch(p, (cudaStream_t)stream);
 }

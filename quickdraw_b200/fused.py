@@ -82,7 +82,7 @@ def supports(ckpt: Checkpoint) -> bool:
 
 class FusedStep:
     def __init__(self, ckpt: Checkpoint, *, expert_range: tuple[int, int] | None = None,
-                 pdl: bool = True):
+                 pdl: bool = True, persistent: bool | None = None):
         assert supports(ckpt), "checkpoint shapes are outside the fused step; use kernels.forward_step"
         self.ckpt, self.pdl = ckpt, pdl
         c = ckpt.config
@@ -139,12 +139,26 @@ class FusedStep:
             d.shared_gate, d.shared_up, d.shared_down = map(_fp4, (moe.shared_gate, moe.shared_up, moe.shared_down))
             d.experts_global_per_expert = int(moe.experts_gate.weight_scale_2.numel() != 1)
             check(self.lib.qd_model_set_layer(self.model, layer.idx, byref(d)), "qd_model_set_layer")
-        self.lib.qd_decode_workspace_bytes.restype = c_longlong
         nbytes = self.lib.qd_decode_workspace_bytes(self.model)
         self.workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         self.routed_partial = torch.zeros(c.hidden_size, dtype=torch.float32, device=self.device)
         self.next_token = torch.zeros((), dtype=torch.long, device=self.device)
         self.launches_per_step = 6 * c.num_hidden_layers + 1
+        # One cooperative launch per token where the model is whole on this GPU; the
+        # launch-per-phase path stays for expert-parallel slices and as a cross-check.
+        self.program = None
+        self.trace = None
+        if persistent is None:
+            persistent = False
+        if persistent:
+            assert expert_range is None, "the persistent kernel needs the whole model on one GPU"
+            size = self.lib.qd_program_bytes(self.model)
+            host = torch.zeros(size, dtype=torch.uint8)
+            check(self.lib.qd_program_build(self.model, ptr(self.workspace), c_void_p(host.data_ptr()), size),
+                  "qd_program_build")
+            self.program = host.to(self.device)
+            self.launches_per_step = 1
+        self.persistent = bool(persistent)
 
     def __del__(self):
         model = getattr(self, "model", None)
@@ -176,6 +190,12 @@ class FusedStep:
         out = torch.empty(ckpt.config.vocab_size, dtype=BF16, device=self.device) if logits else None
         flags = (FLAG_PDL if self.pdl else 0) | (0 if logits else FLAG_NO_LOGITS)
         stream = c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        if self.persistent:
+            check(self.lib.qd_decode_step_persistent(
+                self.model, byref(st), ptr(token_id), pos_dev, pos_host, ptr(self.workspace),
+                ptr(self.program), ptr(out), ptr(self.next_token), flags, ptr(self.trace), stream),
+                "qd_decode_step_persistent")
+            return out
         check(self.lib.qd_decode_step(self.model, byref(st), ptr(token_id), pos_dev, pos_host,
                                       ptr(self.workspace), ptr(out) if logits else ptr(self.workspace),
                                       ptr(self.next_token), flags, stream), "qd_decode_step")
