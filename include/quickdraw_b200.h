@@ -232,7 +232,7 @@ int qd_decode_layers(qd_model* model, const qd_state* state, const long long* to
  * qd_program_bytes bytes, the caller copies it to the device and passes that copy here.
  * Needs a whole idle GPU (one block per SM, all resident) and a single-GPU model
  * (expert_lo == 0, expert_hi == experts).  `trace` (optional, device) receives
- * [phase][8][blocks] nanosecond timestamps. */
+ * [phase][16][blocks] nanosecond timestamps. */
 long long qd_program_bytes(const qd_model* model);
 int qd_program_build(const qd_model* model, void* workspace, void* host_out, long long bytes);
 int qd_decode_step_persistent(const qd_model* model, const qd_state* state, const long long* token,

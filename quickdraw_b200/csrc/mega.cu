@@ -28,7 +28,10 @@ constexpr unsigned kAbortBit = 0x80000000u;
 constexpr int kDownWidth = 512;
 constexpr int kDownRowBytes = kDownWidth / 2 + kDownWidth / 16;   // 288
 constexpr int kAttnStride = 256 + 2;
-constexpr int kScratchFloats = 8 * 4 * kAttnStride + 3 * 8 * kMegaAttnSplits + 64;   // attention merge buffers
+constexpr int kAttnScratchFloats = 8 * 4 * kAttnStride + 3 * 8 * kMegaAttnSplits + 64;   // attention merge buffers
+constexpr int kDownSlots = 9;                                   // top-8 + shared
+constexpr int kDownBufBytes = kDownSlots * kMegaDownRows * kDownRowBytes;   // down-projection rows of one layer
+constexpr int kScratchFloats = kAttnScratchFloats > kDownBufBytes / 4 ? kAttnScratchFloats : kDownBufBytes / 4;
 
 struct Smem {
     uint8_t* stages;
@@ -41,10 +44,13 @@ struct Smem {
     uint64_t* full; uint64_t* empty;
     float* red;            // [64]
     int32_t* ids; float* weights;      // [8] routing of the current layer
-    volatile int* ids_seq;             // layers routed so far
+    uint64_t* ids_bar;                 // completes once per layer, when the routing is in ids / weights
+    uint64_t* down_bar;                // completes once per layer, when the down-projection rows have landed
     volatile int* abort;
     int* flag;
 };
+
+extern __shared__ __align__(128) uint8_t mega_smem[];
 
 QD_DEVINL Smem carve_smem(uint8_t* base) {
     Smem s;
@@ -61,14 +67,15 @@ QD_DEVINL Smem carve_smem(uint8_t* base) {
     s.red = reinterpret_cast<float*>(base);           base += 64 * 4;
     s.ids = reinterpret_cast<int32_t*>(base);         base += 8 * 4;
     s.weights = reinterpret_cast<float*>(base);       base += 8 * 4;
-    s.ids_seq = reinterpret_cast<volatile int*>(base); base += 4;
+    s.ids_bar = reinterpret_cast<uint64_t*>(base);    base += 8;
+    s.down_bar = reinterpret_cast<uint64_t*>(base);   base += 8;
     s.abort = reinterpret_cast<volatile int*>(base);  base += 4;
-    s.flag = reinterpret_cast<int*>(base);            base += 8;
+    s.flag = reinterpret_cast<int*>(base);            base += 4;
     return s;
 }
 constexpr size_t kSmemBytes = (size_t)NS * kStreamStageBytes + 4096 * 2 + 2048 * 4 + (size_t)kScratchFloats * 4 +
                               2 * kMegaConvRows * kStreamConvWidth * 2 + 3 * sizeof(MegaPhase) + 2 * NS * 8 +
-                              64 * 4 + 8 * 4 + 8 * 4 + 16;
+                              64 * 4 + 8 * 4 + 8 * 4 + 24;
 
 QD_DEVINL float ldcg_bf16(const bf16* p) {
     return __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(p)) << 16);
@@ -85,56 +92,50 @@ QD_DEVINL void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 QD_DEVINL void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// Orders this thread's earlier shared-memory accesses before later bulk copies into the same bytes.
+QD_DEVINL void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Bounded wait until the barrier word reaches `target` (the abort bit makes it larger than
 // any target).  On time-out: status bit, abort bit, false.
-__device__ __noinline__ bool grid_wait(unsigned* bar, unsigned target, unsigned* status) {
+// Returns the word it saw (abort bit included); on time-out: status bit, abort bit.
+__device__ __noinline__ unsigned grid_wait(unsigned* bar, unsigned target, unsigned* status) {
+    unsigned v;
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
-        if (ld_acquire(bar) >= target) return true;
+        if ((v = ld_acquire(bar)) >= target) return v;
     const unsigned long long start = global_timer_ns();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; ++i)
-            if (ld_acquire(bar) >= target) return true;
+            if ((v = ld_acquire(bar)) >= target) return v;
         if (global_timer_ns() - start > QD_WAIT_LIMIT_NS) break;
     }
     atomicOr(status, QD_STATUS_WAIT_TIMEOUT);
     atomicOr(bar, kAbortBit);
-    return false;
+    return kAbortBit;
 }
-__device__ __noinline__ bool flag_wait(volatile int* flag, int target, volatile int* abort, unsigned* status) {
-#pragma unroll 1
-    for (int i = 0; i < 1024; ++i)
-        if (*flag >= target) return true;
-    const unsigned long long start = global_timer_ns();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (*flag >= target) return true;
-        if (*abort) return false;
-        if (global_timer_ns() - start > QD_WAIT_LIMIT_NS) break;
-    }
-    atomicOr(status, QD_STATUS_WAIT_TIMEOUT);
-    return false;
-}
-
 // The consumers' side of the grid barrier in front of phase `pi`.
 QD_DEVINL void phase_wait(const MegaParams& mp, const Smem& S, int pi, int tid) {
+    // The acquire load orders thread 0's later reads after the other blocks' releases; the
+    // block barrier hands that order on to the rest of the block.
     if (pi > 0 && tid == 0) {
-        if (!grid_wait(mp.bar, (unsigned)pi * gridDim.x, mp.status)) *S.abort = 1;
-        else if (ld_acquire(mp.bar) & kAbortBit) *S.abort = 1;
-        __threadfence();
+        if (grid_wait(mp.bar, (unsigned)pi * gridDim.x, mp.status) & kAbortBit) *S.abort = 1;
     }
     named_barrier(1, CT);
 }
-// Profiling: eight nanosecond timestamps per phase and block.  Slots: 0 phase start (after the
-// grid barrier), 1 phase end, 2 activation vector ready, 3 first tile landed, 4 / 5 first and
-// last tile of the phase issued by the producer.
-constexpr int kTraceSlots = 8;
+// Profiling: sixteen nanosecond timestamps per phase and block.  Slots: 0 phase start (after
+// the grid barrier), 1 phase end, 2 activation vector ready, 3 first tile landed, 4 / 5 first
+// and last tile of the phase issued by the producer; 8.. are free for finer marks (QD_MARK,
+// compiled in with -DQD_FINE_TRACE).
+constexpr int kTraceSlots = 16;
 QD_DEVINL void trace_mark(const MegaParams& mp, int pi, int slot) {
     if (mp.trace) mp.trace[((size_t)pi * kTraceSlots + slot) * gridDim.x + blockIdx.x] = global_timer_ns();
 }
+#ifdef QD_FINE_TRACE
+#define QD_MARK(slot) do { if (tid == 0) trace_mark(mp, pi, slot); } while (0)
+#else
+#define QD_MARK(slot) do { } while (0)
+#endif
 QD_DEVINL void give_up(const MegaParams& mp, const Smem& S) {
     *S.abort = 1;
     atomicOr(mp.bar, kAbortBit);
@@ -143,6 +144,7 @@ QD_DEVINL void give_up(const MegaParams& mp, const Smem& S) {
 // =========================================================================== producer
 template <int K>
 QD_DEVINL bool produce_stream(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it) {
+    bool ids_ready = false;
     const unsigned lo = blockIdx.x * ph.quota + min(blockIdx.x, ph.remainder);
     const unsigned hi = (blockIdx.x + 1) * ph.quota + min(blockIdx.x + 1, ph.remainder);
     unsigned seg_start = 0;
@@ -155,6 +157,11 @@ QD_DEVINL bool produce_stream(const MegaParams& mp, const MegaPhase& ph, const S
         if (ra >= rb) continue;
         int expert = 0;
         if (sg.slot >= 0) {
+            // The routing of layer L completes phase L of the barrier; the producer is never
+            // more than one layer away from it, so the parity names the phase.  Segments in
+            // front of the first routed one have been issued by now.
+            if (!ids_ready && !mbar_wait(S.ids_bar, ph.layer & 1, mp.status)) return false;
+            ids_ready = true;
             expert = S.ids[sg.slot];
             if (expert < mp.expert_lo || expert >= mp.expert_hi) continue;
             expert -= mp.expert_lo;
@@ -191,40 +198,34 @@ QD_DEVINL bool produce_stream(const MegaParams& mp, const MegaPhase& ph, const S
     return true;
 }
 
-// Down projections: the block's output rows of every slot, slots grouped five to a tile.
-QD_DEVINL bool produce_down(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it) {
+// Down projections: this block's output rows of every selected expert and of the shared
+// expert, into their own buffer (the scratch area, idle between the mixer core and the MoE
+// tail).  Issued as soon as the routing is known, so the rows land during the gate/up phase.
+QD_DEVINL void produce_down(const MegaParams& mp, const MegaPhase& ph, const Smem& S) {
     const int H = mp.hidden;
     const int r0 = (int)((long long)H * blockIdx.x / gridDim.x);
     const int r1 = (int)((long long)H * (blockIdx.x + 1) / gridDim.x);
     const int n = r1 - r0, nslots = mp.topk + 1;
-    const int tiles = (nslots + kMegaDownSlotsPerTile - 1) / kMegaDownSlotsPerTile;
-#pragma unroll 1
-    for (int t = 0; t < tiles; ++t, ++it) {
-        const int st = it % NS;
-        if (*S.abort || !mbar_wait(S.empty + st, ((it / NS) & 1) ^ 1, mp.status)) return false;
-        uint8_t* dst = S.stages + (size_t)st * kStreamStageBytes;
-        const int s_lo = t * kMegaDownSlotsPerTile, s_hi = min(nslots, s_lo + kMegaDownSlotsPerTile);
-        uint32_t bytes = 0;
-        for (int s = s_lo; s < s_hi; ++s) {
-            const bool shared = s == mp.topk;
-            const int e = shared ? 0 : S.ids[s];
-            if (shared || (e >= mp.expert_lo && e < mp.expert_hi)) bytes += (uint32_t)n * kDownRowBytes;
-        }
-        mbar_expect_tx(S.full + st, bytes);
-        for (int s = s_lo; s < s_hi; ++s) {
-            const bool shared = s == mp.topk;
-            const int e = shared ? 0 : S.ids[s];
-            if (!shared && (e < mp.expert_lo || e >= mp.expert_hi)) continue;
-            if (n <= 0) continue;
-            const long long row = shared ? r0 : (long long)(e - mp.expert_lo) * H + r0;
-            const uint8_t* w = (shared ? ph.sw : ph.dw) + row * (kDownWidth / 2);
-            const uint8_t* sc = (shared ? ph.ss : ph.ds) + row * (kDownWidth / 16);
-            uint8_t* d = dst + (size_t)(s - s_lo) * kMegaDownRows * kDownRowBytes;
-            bulk_load(d, w, n * (kDownWidth / 2), S.full + st);
-            bulk_load(d + kMegaDownRows * (kDownWidth / 2), sc, n * (kDownWidth / 16), S.full + st);
-        }
+    uint8_t* dst = reinterpret_cast<uint8_t*>(S.scratch);
+    uint32_t bytes = 0;
+    for (int s = 0; s < nslots; ++s) {
+        const bool shared = s == mp.topk;
+        const int e = shared ? 0 : S.ids[s];
+        if (shared || (e >= mp.expert_lo && e < mp.expert_hi)) bytes += (uint32_t)n * kDownRowBytes;
     }
-    return true;
+    mbar_expect_tx(S.down_bar, bytes);
+    if (n <= 0) return;
+    for (int s = 0; s < nslots; ++s) {
+        const bool shared = s == mp.topk;
+        const int e = shared ? 0 : S.ids[s];
+        if (!shared && (e < mp.expert_lo || e >= mp.expert_hi)) continue;
+        const long long row = shared ? r0 : (long long)(e - mp.expert_lo) * H + r0;
+        const uint8_t* w = (shared ? ph.sw : ph.dw) + row * (kDownWidth / 2);
+        const uint8_t* sc = (shared ? ph.ss : ph.ds) + row * (kDownWidth / 16);
+        uint8_t* d = dst + (size_t)s * kMegaDownRows * kDownRowBytes;
+        bulk_load(d, w, n * (kDownWidth / 2), S.down_bar);
+        bulk_load(d + kMegaDownRows * (kDownWidth / 2), sc, n * (kDownWidth / 16), S.down_bar);
+    }
 }
 
 QD_DEVINL void producer(const MegaParams& mp, const Smem& S, int lane) {
@@ -239,13 +240,14 @@ QD_DEVINL void producer(const MegaParams& mp, const Smem& S, int lane) {
         }
         __syncwarp();
         const MegaPhase& ph = *S.pph;
-        if (lane == 0 && (ph.kind == MK_STREAM || ph.kind == MK_DOWN)) {
-            if (ph.uses_ids) ok = flag_wait(S.ids_seq, ph.layer + 1, S.abort, mp.status);
+        if (lane == 0 && ph.kind == MK_STREAM) {
             trace_mark(mp, pi, 4);
-            if (ok) {
-                if (ph.kind == MK_DOWN) ok = produce_down(mp, ph, S, it);
-                else if (ph.width == 2048) ok = produce_stream<2048>(mp, ph, S, it);
-                else ok = produce_stream<4096>(mp, ph, S, it);
+            if (ph.width == 2048) ok = produce_stream<2048>(mp, ph, S, it);
+            else ok = produce_stream<4096>(mp, ph, S, it);
+            // the routed gate/up phase also carries the down-projection pointers of its layer
+            if (ok && ph.route) {
+                ok = mbar_wait(S.ids_bar, ph.layer & 1, mp.status);
+                if (ok) produce_down(mp, ph, S);
             }
             trace_mark(mp, pi, 5);
             if (!ok) give_up(mp, S);
@@ -263,6 +265,51 @@ QD_DEVINL void producer(const MegaParams& mp, const Smem& S, int lane) {
     }
 }
 
+// Top-k routing by one warp over at most 256 bf16 logits written by other blocks: the same
+// fp32 softmax, tie-break (lowest index) and renormalisation as route_small, with the
+// eight selections done by integer warp reductions (probabilities are non-negative, so their
+// bit patterns order like the values).
+QD_DEVINL void route_fast(const bf16* logits, int experts, int topk, int32_t* ids, float* weights, int lane) {
+    float p[8];
+    float best = -INFINITY;
+    const unsigned short* raw = reinterpret_cast<const unsigned short*>(logits);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = i * 32 + lane;
+        p[i] = e < experts ? __uint_as_float((uint32_t)__ldcg(raw + e) << 16) : -INFINITY;
+        best = fmaxf(best, p[i]);
+    }
+    best = warp_max(best);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = i * 32 + lane;
+        p[i] = e < experts ? expf(p[i] - best) : -1.f;
+        if (e < experts) sum += p[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) if (p[i] >= 0.f) p[i] = p[i] / sum;
+    float chosen = 0.f, mine = 0.f;
+    int my_id = 0;
+#pragma unroll 1
+    for (int s = 0; s < topk; ++s) {
+        float v = -1.f; int slot = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) if (p[i] > v) { v = p[i]; slot = i; }
+        const int top = __reduce_max_sync(0xffffffffu, __float_as_int(v));
+        const int idx = __reduce_min_sync(0xffffffffu, __float_as_int(v) == top ? slot * 32 + lane : 0x7fffffff);
+        const float value = __int_as_float(top);
+        chosen += value;
+        if (lane == s) { mine = value; my_id = idx; }
+        if ((idx & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) if (i == (idx >> 5)) p[i] = -1.f;
+        }
+    }
+    if (lane < topk) { ids[lane] = my_id; weights[lane] = mine / chosen; }
+}
+
 // ========================================================================== consumers
 // One streaming phase: activation vector -> registers, then this block's rows of the ring.
 template <int KC, bool WITH_BF16>
@@ -278,15 +325,16 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
 
     // ---- static prefetch: norm gamma, conv taps and history of this block's channels
     float gam[8];
-    if (KC == 2 && ph.prologue == PRO_ADD_NORM && tid < 256) {
+    if constexpr (KC == 2) if (ph.prologue == PRO_ADD_NORM && tid < 256) {
         const float4 g0 = *reinterpret_cast<const float4*>(ph.gamma + tid * 8);
         const float4 g1 = *reinterpret_cast<const float4*>(ph.gamma + tid * 8 + 4);
         gam[0] = g0.x; gam[1] = g0.y; gam[2] = g0.z; gam[3] = g0.w;
         gam[4] = g1.x; gam[5] = g1.y; gam[6] = g1.z; gam[7] = g1.w;
     }
-    int conv_row0 = 0;
+    int conv_row0 = 0, conv_n = 0;
     bf16* conv_state = nullptr;
-    if (ph.conv_taps) {
+    unsigned short conv_tap_reg = 0, conv_state_reg = 0;     // one element of each per thread
+    if constexpr (KC == 2) if (ph.conv_taps) {
         const int W = mp.conv_width;
         conv_state = reinterpret_cast<bf16*>(mp.st.conv_state) + (size_t)ph.state_index * mp.channels * (W - 1);
         unsigned seg_start = 0;
@@ -297,26 +345,33 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                 int ra, rb;
                 seg_range<K>(seg_start, sg.kind, sg.rows, lo, hi, ra, rb);
                 conv_row0 = ra;
-                const int n = min(rb - ra, kMegaConvRows);
-                for (int e = tid; e < n * W; e += CT) S.conv_taps[e] = ph.conv_taps[(size_t)ra * W + e];
-                for (int e = tid; e < n * (W - 1); e += CT) S.conv_state[e] = conv_state[(size_t)ra * (W - 1) + e];
+                conv_n = min(rb - ra, kMegaConvRows);
+                // in flight across the grid barrier; stored to shared memory after it
+                if (tid < conv_n * W)
+                    conv_tap_reg = reinterpret_cast<const unsigned short*>(ph.conv_taps)[(size_t)ra * W + tid];
+                if (tid < conv_n * (W - 1))
+                    conv_state_reg = reinterpret_cast<const unsigned short*>(conv_state)[(size_t)ra * (W - 1) + tid];
             }
             seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
         }
     }
     phase_wait(mp, S, pi, tid);
     if (tid == 0) trace_mark(mp, pi, 0);
-
-    // ---- routing for this layer (every block selects the same experts from the same logits)
-    if (ph.route && warp == 0) {
-        route_small(ph.router_logits, mp.experts, mp.topk, S.ids, S.weights, lane);
-        __syncwarp();
-        if (blockIdx.x == 0 && lane < mp.topk) { ph.ids_out[lane] = S.ids[lane]; ph.weights_out[lane] = S.weights[lane]; }
-        if (lane == 0) { __threadfence_block(); *S.ids_seq = ph.layer + 1; }
+    if constexpr (KC == 2) if (ph.conv_taps) {
+        if (tid < conv_n * mp.conv_width) reinterpret_cast<unsigned short*>(S.conv_taps)[tid] = conv_tap_reg;
+        if (tid < conv_n * (mp.conv_width - 1)) reinterpret_cast<unsigned short*>(S.conv_state)[tid] = conv_state_reg;
     }
 
-    if (!ph.keep_x) {
-        const bf16* xin = ph.from_token ? mp.embed + (size_t)(*mp.token) * K : ph.x;
+    // ---- routing for this layer (every block selects the same experts from the same logits)
+    if constexpr (KC == 2) if (ph.route && warp == 0) {
+        route_fast(ph.router_logits, mp.experts, mp.topk, S.ids, S.weights, lane);
+        __syncwarp();
+        if (blockIdx.x == 0 && lane < mp.topk) { ph.ids_out[lane] = S.ids[lane]; ph.weights_out[lane] = S.weights[lane]; }
+        if (lane == 0) mbar_arrive(S.ids_bar);
+    }
+
+    if (KC == 4 || !ph.keep_x) {
+        const bf16* xin = (KC == 2 && ph.from_token) ? mp.embed + (size_t)(*mp.token) * K : ph.x;
         uint32_t m2 = 0u;
         if (KC == 2 && ph.prologue == PRO_ADD_NORM) {
             // residual add + RMSNorm by the first 256 threads, eight elements each
@@ -336,8 +391,10 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
 #pragma unroll
                 for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
                 ss = warp_sum(ss);
+                QD_MARK(8);
                 if (lane == 0) red[warp] = ss;
                 named_barrier(2, 256);
+                QD_MARK(9);
                 float tot = 0.f;
 #pragma unroll
                 for (int w = 0; w < 8; ++w) tot += red[w];
@@ -359,20 +416,33 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                     *reinterpret_cast<uint4*>(ph.residual_out + tid * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
                 }
             }
-        } else if (ph.prologue == PRO_GATED_NORM) {
+        } else if (KC == 4 && ph.prologue == PRO_GATED_NORM) {
             // per-head RMSNorm of o, times gamma, times silu(z); one warp per 128-wide head
             // (quickdraw/models/qwen.py:161-164)
-            for (int h = warp; h < K / 128; h += CW) {
-                float o[4], ss = 0.f;
+            constexpr int HPW = K / 128 / CW;          // heads per warp
+            float o[HPW > 0 ? HPW : 1][4], zz[HPW > 0 ? HPW : 1][4], gm[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) { o[j] = ldcg_bf16(xin + h * 128 + j * 32 + lane); ss += o[j] * o[j]; }
+            for (int a = 0; a < HPW; ++a)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = (warp + a * CW) * 128 + j * 32 + lane;
+                    o[a][j] = ldcg_bf16(xin + i);
+                    zz[a][j] = ldcg_bf16(ph.z + i);
+                }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) gm[j] = ld_bf16(ph.head_gamma + j * 32 + lane);
+            QD_MARK(8);
+#pragma unroll
+            for (int a = 0; a < HPW; ++a) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ss += o[a][j] * o[a][j];
                 ss = warp_sum(ss);
                 const float inv = rsqrtf(ss / 128.f + mp.eps);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int i = h * 128 + j * 32 + lane;
-                    const float zz = ldcg_bf16(ph.z + i);
-                    const bf16 n = __float2bfloat16_rn(((o[j] * inv) * ld_bf16(ph.head_gamma + j * 32 + lane)) * silu_precise(zz));
+                    const int i = (warp + a * CW) * 128 + j * 32 + lane;
+                    const bf16 n = __float2bfloat16_rn(((o[a][j] * inv) * gm[j]) * silu_precise(zz[a][j]));
                     xs[i] = n;
                     m2 = max(m2, (uint32_t)(__bfloat16_as_ushort(n) & 0x7fffu));
                     if (blockIdx.x == 0 && ph.x_out) ph.x_out[i] = n;
@@ -386,6 +456,7 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                 m2 = max_u16x2(m2, v.z & 0x7fff7fffu); m2 = max_u16x2(m2, v.w & 0x7fff7fffu);
             }
         }
+        QD_MARK(10);
         {
             uint32_t m = max(m2 & 0xffffu, m2 >> 16);
 #pragma unroll
@@ -394,8 +465,9 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
         }
     }
     named_barrier(1, CT);
+    QD_MARK(11);
     // ---- the vector as f16 pairs, scaled down by a power of two only if it would overflow f16
-    uint32_t xh[KC][16];
+    uint32_t xh[KC == 2 ? 2 : 1][16];      // 2048-wide phases keep the f16 slice in registers
     float out_mult;
     {
         uint32_t m = 0u;
@@ -405,7 +477,9 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
         const int shift = exponent > 14 ? exponent - 14 : 0;
         const float down = __uint_as_float((uint32_t)(127 - shift) << 23);
         out_mult = __uint_as_float((uint32_t)(127 + min(shift, 127)) << 23);
-        if (!ph.keep_x) {
+        if (KC == 4 || !ph.keep_x) {
+            // f16 layout: the 16-byte piece a lane fetches as (chunk c, quarter q) sits at
+            // ((c * 4 + q) * 32 + lane) * 16, so that a warp's fetch is one contiguous 512 bytes
             if (EPC == 8) {
                 const uint4 v = *reinterpret_cast<const uint4*>(xs + tid * 8);
                 uint4 h;
@@ -413,34 +487,24 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                 h.y = pack_f16x2(__uint_as_float(v.y << 16) * down, __uint_as_float(v.y & 0xffff0000u) * down);
                 h.z = pack_f16x2(__uint_as_float(v.z << 16) * down, __uint_as_float(v.z & 0xffff0000u) * down);
                 h.w = pack_f16x2(__uint_as_float(v.w << 16) * down, __uint_as_float(v.w & 0xffff0000u) * down);
-                *reinterpret_cast<uint4*>(xf + tid * 4) = h;
+                const int piece = tid;
+                const int pos = ((piece >> 7) * 4 + (piece & 3)) * 32 + ((piece >> 2) & 31);
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(xf) + pos * 16) = h;
             } else {
                 const uint2 v = *reinterpret_cast<const uint2*>(xs + tid * 4);
                 uint2 h;
                 h.x = pack_f16x2(__uint_as_float(v.x << 16) * down, __uint_as_float(v.x & 0xffff0000u) * down);
                 h.y = pack_f16x2(__uint_as_float(v.y << 16) * down, __uint_as_float(v.y & 0xffff0000u) * down);
-                *reinterpret_cast<uint2*>(xf + tid * 2) = h;
+                const int piece = tid >> 1;
+                const int pos = ((piece >> 7) * 4 + (piece & 3)) * 32 + ((piece >> 2) & 31);
+                *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(xf) + pos * 16 + (tid & 1) * 8) = h;
             }
             named_barrier(1, CT);
-        }
-#pragma unroll
-        for (int c = 0; c < KC; ++c)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const uint4 v = lds128(reinterpret_cast<const uint8_t*>(xf) + (c * 32 + lane) * 64 + q * 16);
-                xh[c][q * 4 + 0] = v.x; xh[c][q * 4 + 1] = v.y; xh[c][q * 4 + 2] = v.z; xh[c][q * 4 + 3] = v.w;
-            }
-    }
-    constexpr int NB = WITH_BF16 ? K / 256 : 1;
-    uint32_t xb[NB * 4];
-    if (WITH_BF16) {
-#pragma unroll
-        for (int i = 0; i < NB; ++i) {
-            const uint4 v = lds128(reinterpret_cast<const uint8_t*>(xs) + (i * 32 + lane) * 16);
-            xb[i * 4 + 0] = v.x; xb[i * 4 + 1] = v.y; xb[i * 4 + 2] = v.z; xb[i * 4 + 3] = v.w;
+            QD_MARK(12);
         }
     }
-
+    bool have_xh = false;
+    constexpr int NB = K / 256;
     if (tid == 0) trace_mark(mp, pi, 2);
     // ---- rows
     float best_val = -INFINITY;
@@ -457,15 +521,28 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
         seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
         if (ra >= rb) continue;
         int expert = 0;
-        if (sg.slot >= 0) {
+        if (KC == 2 && sg.slot >= 0) {
             expert = S.ids[sg.slot];
             if (expert < mp.expert_lo || expert >= mp.expert_hi) continue;
             expert -= mp.expert_lo;
         }
+        // 2048-wide NVFP4 rows: the lane's f16 slice goes to registers when the first such
+        // segment shows up; bf16 rows and 4096-wide rows (a block sees few of them) read the
+        // vector from shared memory as they go
+        if (KC == 2 && sg.kind != SEG_BF16 && !have_xh) {
+#pragma unroll
+            for (int c = 0; c < (KC == 2 ? 2 : 1); ++c)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint4 v = lds128(reinterpret_cast<const uint8_t*>(xf) + ((c * 4 + q) * 32 + lane) * 16);
+                    xh[c][q * 4 + 0] = v.x; xh[c][q * 4 + 1] = v.y; xh[c][q * 4 + 2] = v.z; xh[c][q * 4 + 3] = v.w;
+                }
+            have_xh = true;
+        }
         const int tile_rows = seg_tile_rows<K>(sg.kind);
         const float g1 = sg.g ? sg.g[sg.g_per_expert ? expert : 0] : 1.f;
         const float g2 = sg.g2 ? sg.g2[sg.g_per_expert ? expert : 0] : 1.f;
-        bf16* y = sg.epilogue == EP_ARGMAX ? mp.logits : sg.y;
+        bf16* y = (KC == 2 && sg.epilogue == EP_ARGMAX) ? mp.logits : sg.y;
 #pragma unroll 1
         for (int r0 = ra; r0 < rb; r0 += tile_rows, ++it) {
             const int n = min(tile_rows, rb - r0);
@@ -478,17 +555,22 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             for (int r = (warp - turn) & (CW - 1); r < n; r += CW) {
                 const int row = r0 + r;
                 float result;
-                if (sg.kind == SEG_BF16) {
-                    if (WITH_BF16) result = warp_sum(bf16_row_dot<NB>(base + (size_t)r * 2 * K, xb, lane));
-                    else result = 0.f;
+                if (WITH_BF16 && sg.kind == SEG_BF16) {
+                    result = warp_sum(bf16_row_dot_smem<NB>(base + (size_t)r * 2 * K, reinterpret_cast<const uint8_t*>(xs), lane));
                 } else {
-                    const int halves = sg.kind == SEG_FP4_PAIR ? 2 : 1;
+                    const int halves = (KC == 2 && sg.kind == SEG_FP4_PAIR) ? 2 : 1;
                     const uint8_t* sc = base + halves * tile_rows * (K / 2);
                     float acc[2] = {0.f, 0.f};
 #pragma unroll 1
-                    for (int h = 0; h < halves; ++h)
-                        acc[h] = warp_sum(fp4_row_dot<KC>(base + (h * tile_rows + r) * (K / 2),
-                                                          sc + (h * tile_rows + r) * (K / 16), xh, lane));
+                    for (int h = 0; h < halves; ++h) {
+                        if constexpr (KC == 2)
+                            acc[h] = warp_sum(fp4_row_dot<2>(base + (h * tile_rows + r) * (K / 2),
+                                                             sc + (h * tile_rows + r) * (K / 16), xh, lane));
+                        else
+                            acc[h] = warp_sum(fp4_row_dot_smem<KC>(base + (h * tile_rows + r) * (K / 2),
+                                                                   sc + (h * tile_rows + r) * (K / 16),
+                                                                   reinterpret_cast<const uint8_t*>(xf), lane));
+                    }
                     result = (acc[0] * out_mult) * g1;
                     if (halves == 2) {
                         const float up = round_bf16((acc[1] * out_mult) * g2);
@@ -496,7 +578,7 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                     }
                 }
                 const bf16 rounded = __float2bfloat16_rn(result);
-                if (sg.epilogue == EP_CONV) {
+                if (KC == 2 && sg.epilogue == EP_CONV) {
                     // depthwise causal conv of this channel (quickdraw/models/qwen.py:134-136)
                     const int W = mp.conv_width, local = row - conv_row0;
                     float val = 0.f, tap = 0.f;
@@ -504,12 +586,15 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                         tap = __bfloat162float(S.conv_taps[local * W + lane]);
                         val = lane < W - 1 ? __bfloat162float(S.conv_state[local * (W - 1) + lane]) : __bfloat162float(rounded);
                     }
-                    const float conv = warp_sum(lane < W ? round_bf16(val * tap) : 0.f);
+                    // W <= 4 and lanes >= W hold zero: the last two butterfly steps are the whole sum
+                    float conv = lane < W ? round_bf16(val * tap) : 0.f;
+                    conv += __shfl_xor_sync(0xffffffffu, conv, 2);
+                    conv += __shfl_xor_sync(0xffffffffu, conv, 1);
                     if (lane >= 1 && lane < W) conv_state[(size_t)row * (W - 1) + lane - 1] = __float2bfloat16_rn(val);
                     if (lane == 0) y[row] = __float2bfloat16_rn(silu_precise(conv));
                 } else {
                     if (lane == 0) y[row] = rounded;
-                    if (sg.epilogue == EP_ARGMAX) {
+                    if (KC == 2 && sg.epilogue == EP_ARGMAX) {
                         const float v = __bfloat162float(rounded);
                         if (v > best_val || (v == best_val && row < best_idx)) { best_val = v; best_idx = row; }
                     }
@@ -522,7 +607,7 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
     }
     if (!ok && lane == 0) give_up(mp, S);
     // ---- greedy argmax over the logits (ties: lowest index)
-    if (ph.argmax) {
+    if (KC == 2 && ph.argmax) {
         if (lane == 0) { red[32 + warp] = best_val; reinterpret_cast<int*>(red)[48 + warp] = best_idx; }
         named_barrier(1, CT);
         if (tid == 0) {
@@ -550,67 +635,60 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
     }
 }
 
-// Gated delta-rule recurrence (quickdraw/models/qwen.py:139-160): block = (value head, 32
-// value columns), 256 threads = 8 key groups x 32 columns, 16 state entries per thread.
+// Gated delta-rule recurrence (quickdraw/models/qwen.py:139-160) for 128-wide key heads:
+// block = (value head, 32 value columns), 256 threads = 8 key groups x 32 columns, 16 state
+// entries per thread, fetched before the grid barrier (only this block ever touches them).
 QD_DEVINL void gdn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
+    constexpr int DK = 128, KPT = 16;
     const int tid = threadIdx.x, col = tid & 31, kg = tid >> 5;
-    const int dk = mp.dk, dv = mp.dv, hk = mp.hk, hv = mp.hv;
+    const int dv = mp.dv, hk = mp.hk, hv = mp.hv;
     const int slices = dv / 32;
     const int unit = blockIdx.x;
     const bool active = unit < hv * slices && tid < 256;
-    const int head = unit / slices, c0 = (unit % slices) * 32;
-    const int kpt = (dk + 7) / 8;                 // <= 16
-    float* sq = S.scratch;            // [128]
-    float* sk = sq + 128;             // [128]
-    float* part = sk + 128;           // [8][32]
-    float* norms = part + 256;        // [2]
-    float* gates = norms + 2;         // [2]
-    float* state = mp.st.rec_state + (size_t)ph.state_index * hv * dk * dv;
-    float* tile = state + (size_t)head * dk * dv + c0 + col;
-    float s[16];
+    const int head = active ? unit / slices : 0, c0 = active ? (unit % slices) * 32 : 0;
+    float* qs = S.scratch;            // [128] q, normalised and scaled
+    float* ks = qs + DK;              // [128] k, normalised
+    float* part = ks + DK;            // [8][32]
+    float* gates = part + 256;        // decay, beta
+    float* tile = mp.st.rec_state + (size_t)ph.state_index * hv * DK * dv + (size_t)head * DK * dv + c0 + col;
+    float s[KPT];
     if (active) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int key = kg * kpt + j;
-            s[j] = (j < kpt && key < dk) ? tile[(size_t)key * dv] : 0.f;
-        }
+        for (int j = 0; j < KPT; ++j) s[j] = tile[(size_t)(kg * KPT + j) * dv];
     }
     phase_wait(mp, S, pi, tid);
     if (tid == 0) trace_mark(mp, pi, 0);
     if (!active) return;
     const int key_head = head / (hv / hk);
-    const bf16* qh = ph.qkv + (size_t)key_head * dk;
-    const bf16* kh = ph.qkv + (size_t)hk * dk + (size_t)key_head * dk;
-    float qq = 0.f, kk = 0.f;
-    for (int i = tid; i < dk; i += 256) {
-        const float qv = ldcg_bf16(qh + i), kv = ldcg_bf16(kh + i);
-        sq[i] = qv; sk[i] = kv;
-        qq += qv * qv; kk += kv * kv;
+    // everything this thread needs from the projections, in flight together
+    const float v = ldcg_bf16(ph.qkv + (size_t)2 * hk * DK + (size_t)head * dv + c0 + col);
+    float qv = 0.f, kv = 0.f, av = 0.f, bv = 0.f;
+    if (tid < DK) {
+        qv = ldcg_bf16(ph.qkv + (size_t)key_head * DK + tid);
+        kv = ldcg_bf16(ph.qkv + (size_t)hk * DK + (size_t)key_head * DK + tid);
     }
-    qq = warp_sum(qq); kk = warp_sum(kk);
+    if (tid == DK) { av = ldcg_bf16(ph.a + head); bv = ldcg_bf16(ph.b + head); }
+    const float qq = warp_sum(qv * qv), kk = warp_sum(kv * kv);
     if (col == 0) { part[kg * 32] = qq; part[kg * 32 + 1] = kk; }
     named_barrier(2, 256);
-    if (tid == 0) {
+    if (tid < DK) {
         float tq = 0.f, tk = 0.f;
+#pragma unroll
         for (int w = 0; w < 8; ++w) { tq += part[w * 32]; tk += part[w * 32 + 1]; }
-        norms[0] = rsqrtf(tq + 1e-6f);
-        norms[1] = rsqrtf(tk + 1e-6f);
-        const float alpha = ldcg_bf16(ph.a + head) + ld_bf16(ph.dt_bias + head);
+        qs[tid] = (qv * rsqrtf(tq + 1e-6f)) / sqrtf((float)DK);
+        ks[tid] = kv * rsqrtf(tk + 1e-6f);
+    } else if (tid == DK) {
+        const float alpha = av + ld_bf16(ph.dt_bias + head);
         gates[0] = expf(-expf(ld_bf16(ph.a_log + head)) * softplus_precise(alpha));
-        gates[1] = sigmoid_precise(ldcg_bf16(ph.b + head));
+        gates[1] = sigmoid_precise(bv);
     }
     named_barrier(2, 256);
-    const float kscale = norms[1];
     const float decay = gates[0], beta = gates[1];
-    const float v = ldcg_bf16(ph.qkv + (size_t)2 * hk * dk + (size_t)head * dv + c0 + col);
     float pred = 0.f;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const int key = kg * kpt + j;
-        if (j < kpt && key < dk) {
-            s[j] *= decay;
-            pred += s[j] * (sk[key] * kscale);
-        }
+    for (int j = 0; j < KPT; ++j) {
+        s[j] *= decay;
+        pred += s[j] * ks[kg * KPT + j];
     }
     part[kg * 32 + col] = pred;
     named_barrier(2, 256);
@@ -621,13 +699,10 @@ QD_DEVINL void gdn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& 
     named_barrier(2, 256);
     float o = 0.f;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const int key = kg * kpt + j;
-        if (j < kpt && key < dk) {
-            s[j] += (sk[key] * kscale) * corr;
-            o += s[j] * ((sq[key] * norms[0]) / sqrtf((float)dk));
-            tile[(size_t)key * dv] = s[j];
-        }
+    for (int j = 0; j < KPT; ++j) {
+        s[j] += ks[kg * KPT + j] * corr;
+        o += s[j] * qs[kg * KPT + j];
+        tile[(size_t)(kg * KPT + j) * dv] = s[j];
     }
     part[kg * 32 + col] = o;
     named_barrier(2, 256);
@@ -641,68 +716,104 @@ QD_DEVINL void gdn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& 
 
 // RMSNorm with gamma = 1 + weight and partial RoPE of one head by one warp; the rotation
 // angles come from a table of bf16-rounded cos / sin shared by all heads
-// (quickdraw/models/qwen.py:76-92).
+// (quickdraw/models/qwen.py:76-92).  Feature i = j * 32 + lane; one trip to L2 for the row.
 QD_DEVINL void norm_rope_row(const bf16* __restrict__ src, const bf16* __restrict__ gamma_w, int d, int rotary,
                              float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int lane,
                              float* __restrict__ dst) {
+    float v[8], g[8];
     float ss = 0.f;
-    for (int i = lane; i < d; i += 32) { const float v = ldcg_bf16(src + i); ss += v * v; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = j * 32 + lane;
+        v[j] = i < d ? ldcg_bf16(src + i) : 0.f;
+        g[j] = i < d ? ld_bf16(gamma_w + i) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)d + eps);
-    for (int i = lane; i < d; i += 32)
-        dst[i] = round_bf16((ldcg_bf16(src + i) * inv) * (1.0f + ld_bf16(gamma_w + i)));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = j * 32 + lane;
+        if (i < d) dst[i] = round_bf16((v[j] * inv) * (1.0f + g[j]));
+    }
     __syncwarp();
     const int half = rotary / 2;
     float rotated[8];
-    int n = 0;
-    for (int i = lane; i < rotary; i += 32, ++n) {
-        const int f = i % half;
-        const float partner = i < half ? -dst[i + half] : dst[i - half];
-        rotated[n & 7] = round_bf16(dst[i] * cos_t[f] + partner * sin_t[f]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = j * 32 + lane;
+        if (i < rotary) {
+            const int f = i % half;
+            const float partner = i < half ? -dst[i + half] : dst[i - half];
+            rotated[j] = round_bf16(dst[i] * cos_t[f] + partner * sin_t[f]);
+        }
     }
     __syncwarp();
-    n = 0;
-    for (int i = lane; i < rotary; i += 32, ++n) dst[i] = rotated[n & 7];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = j * 32 + lane;
+        if (i < rotary) dst[i] = rotated[j];
+    }
     __syncwarp();
 }
 
-// Gated GQA decode attention (quickdraw/models/qwen.py:66-116): block = (KV head, context
-// split); warp = (one of eight position lanes, one half of the query heads of the KV head).
+struct AttnSplit { int active, per; };
+// How the context [0, T) is cut into splits of `per` positions, one block per (KV head, split).
+QD_DEVINL AttnSplit attn_split(int T, int max_splits) {
+    AttnSplit a;
+    const int s = min(max_splits, T);
+    a.per = (T + s - 1) / s;
+    a.active = (T + a.per - 1) / a.per;
+    return a;
+}
+
+// Gated GQA decode attention, first half (quickdraw/models/qwen.py:66-116): block = (KV head,
+// context split); warp = (one of eight position lanes, one half of the query heads of the KV
+// head).  Writes the block's softmax partials (unnormalised sum, max, denominator per head).
 QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = mp.hq / mp.hkv, D = mp.d;
     const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
     const int T = position + 1;
-    int active = (T + 31) / 32;
-    if (active > mp.attn_splits) active = mp.attn_splits;
-    const int per = ((T + active - 1) / active + 7) & ~7;
+    const AttnSplit cut = attn_split(T, mp.attn_splits);
     const int unit = blockIdx.x;
-    const int kvh = unit / active, split = unit % active;
-    const int t0 = split * per, t1 = min(T, t0 + per);
+    const int kvh = unit / cut.active, split = unit % cut.active;
+    const int t0 = split * cut.per, t1 = min(T, t0 + cut.per);
     const bool mine = kvh < mp.hkv;
     float* q_s = reinterpret_cast<float*>(S.xs);            // [G][D]
     float* k_s = reinterpret_cast<float*>(S.xf);            // [D]
     float* cos_t = k_s + 256;                               // [rotary / 2]
     float* sin_t = cos_t + 128;
     float* red = S.scratch;                                 // [8 position lanes][4 heads][D + 2]
-    float* wsum = red + 8 * 4 * kAttnStride;                // final merge: [G][splits] m, then weights
-    float* lsum = wsum + 8 * kMegaAttnSplits;               // [G][splits] weight * l
-    float* hmax = lsum + 8 * kMegaAttnSplits;               // [G] max, [G] denominators
+    float* wgt = red + 8 * 4 * kAttnStride;                 // [4 heads][8 lanes] merge weights
     const size_t layer_elems = (size_t)mp.st.capacity * mp.hkv * D;
     bf16* k_cache = reinterpret_cast<bf16*>(mp.st.kv_k) + (size_t)ph.state_index * layer_elems;
     bf16* v_cache = reinterpret_cast<bf16*>(mp.st.kv_v) + (size_t)ph.state_index * layer_elems;
+    const int pl = warp >> 1, hh = warp & 1;
+    const int f0 = lane * 8;
+    const bool lane_on = f0 < D;
 
+    // ---- before the grid barrier: the rotation table (position only) and the first cache rows
+    // (rows of earlier positions were written by earlier steps)
+    uint4 kr = make_uint4(0u, 0u, 0u, 0u), vr = kr;
+    if (mine) {
+        const int half = mp.rotary / 2;
+        for (int f = tid; f < half; f += CT) {
+            const float inv_freq = 1.0f / powf(mp.theta, (float)(2 * f) / (float)mp.rotary);
+            const float angle = (float)position * inv_freq;
+            cos_t[f] = round_bf16(cosf(angle));
+            sin_t[f] = round_bf16(sinf(angle));
+        }
+        const int t = t0 + pl;
+        if (t < t1 && t != position && lane_on) {
+            kr = *reinterpret_cast<const uint4*>(k_cache + ((size_t)t * mp.hkv + kvh) * D + f0);
+            vr = *reinterpret_cast<const uint4*>(v_cache + ((size_t)t * mp.hkv + kvh) * D + f0);
+        }
+    }
     phase_wait(mp, S, pi, tid);
     if (tid == 0) trace_mark(mp, pi, 0);
     if (!mine) return;
-    const int half = mp.rotary / 2;
-    for (int f = tid; f < half; f += CT) {
-        const float inv_freq = 1.0f / powf(mp.theta, (float)(2 * f) / (float)mp.rotary);
-        const float angle = (float)position * inv_freq;
-        cos_t[f] = round_bf16(cosf(angle));
-        sin_t[f] = round_bf16(sinf(angle));
-    }
-    named_barrier(1, CT);
     const bool owns_new = position >= t0 && position < t1;
     if (warp < G)
         norm_rope_row(ph.qg + (size_t)(kvh * G + warp) * 2 * D, ph.q_norm, D, mp.rotary, mp.eps, cos_t, sin_t, lane,
@@ -717,10 +828,8 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
         }
     }
     named_barrier(1, CT);
+    QD_MARK(9);
 
-    const int pl = warp >> 1, hh = warp & 1;
-    const int f0 = lane * 8;
-    const bool lane_on = f0 < D;
     float m[4], l[4], acc[4][8];
 #pragma unroll
     for (int h = 0; h < 4; ++h) {
@@ -729,28 +838,28 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
         for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
     }
     const float scale = rsqrtf((float)D);
+#pragma unroll 1
     for (int t = t0 + pl; t < t1; t += 8) {
         float kf[8], vf[8];
-        if (lane_on) {
-            if (t == position) {
+        if (t == position) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    kf[j] = k_s[f0 + j];
-                    vf[j] = ldcg_bf16(ph.v_new + (size_t)kvh * D + f0 + j);
-                }
-            } else {
-                const uint4 kr = *reinterpret_cast<const uint4*>(k_cache + ((size_t)t * mp.hkv + kvh) * D + f0);
-                const uint4 vr = *reinterpret_cast<const uint4*>(v_cache + ((size_t)t * mp.hkv + kvh) * D + f0);
-                const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    kf[2 * j] = __uint_as_float(kw[j] << 16); kf[2 * j + 1] = __uint_as_float(kw[j] & 0xffff0000u);
-                    vf[2 * j] = __uint_as_float(vw[j] << 16); vf[2 * j + 1] = __uint_as_float(vw[j] & 0xffff0000u);
-                }
+            for (int j = 0; j < 8; ++j) {
+                kf[j] = lane_on ? k_s[f0 + j] : 0.f;
+                vf[j] = lane_on ? ldcg_bf16(ph.v_new + (size_t)kvh * D + f0 + j) : 0.f;
             }
         } else {
+            const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { kf[j] = 0.f; vf[j] = 0.f; }
+            for (int j = 0; j < 4; ++j) {
+                kf[2 * j] = __uint_as_float(kw[j] << 16); kf[2 * j + 1] = __uint_as_float(kw[j] & 0xffff0000u);
+                vf[2 * j] = __uint_as_float(vw[j] << 16); vf[2 * j + 1] = __uint_as_float(vw[j] & 0xffff0000u);
+            }
+        }
+        // the next row of this position lane, in flight during the arithmetic
+        const int tn = t + 8;
+        if (tn < t1 && tn != position && lane_on) {
+            kr = *reinterpret_cast<const uint4*>(k_cache + ((size_t)tn * mp.hkv + kvh) * D + f0);
+            vr = *reinterpret_cast<const uint4*>(v_cache + ((size_t)tn * mp.hkv + kvh) * D + f0);
         }
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
@@ -771,6 +880,7 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
             }
         }
     }
+    QD_MARK(10);
     // merge the eight position lanes, one half of the heads at a time
     float* block_out = mp.attn_partial + (((size_t)kvh * mp.attn_splits + split) * G) * kAttnStride;
 #pragma unroll 1
@@ -787,184 +897,197 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
             }
         }
         named_barrier(1, CT);
+        if (tid < 32) {               // weight of position lane w for head h, and the head's max / denominator
+            const int h = tid >> 3, w = tid & 7;
+            const float mw = red[((size_t)w * 4 + h) * kAttnStride + 256];
+            float mm = mw;
+            mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 1));
+            mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 2));
+            mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 4));
+            const float wv = mw == -INFINITY ? 0.f : expf(mw - mm);
+            float den = wv * red[((size_t)w * 4 + h) * kAttnStride + 257];
+            den += __shfl_xor_sync(0xffffffffu, den, 1);
+            den += __shfl_xor_sync(0xffffffffu, den, 2);
+            den += __shfl_xor_sync(0xffffffffu, den, 4);
+            wgt[tid] = wv;
+            const int head = pass * 4 + h;
+            if (w == 0 && head < G) {
+                block_out[(size_t)head * kAttnStride + 256] = mm;
+                block_out[(size_t)head * kAttnStride + 257] = den;
+            }
+        }
+        named_barrier(1, CT);
         for (int idx = tid; idx < 4 * D; idx += CT) {
             const int h = idx / D, f = idx % D;
             const int head = pass * 4 + h;
             if (head >= G) continue;
-            float mm = -INFINITY;
-            for (int w = 0; w < 8; ++w) mm = fmaxf(mm, red[((size_t)w * 4 + h) * kAttnStride + 256]);
-            float num = 0.f, den = 0.f;
-            for (int w = 0; w < 8; ++w) {
-                const float* src = red + ((size_t)w * 4 + h) * kAttnStride;
-                const float wgt = src[256] == -INFINITY ? 0.f : expf(src[256] - mm);
-                num += wgt * src[f];
-                den += wgt * src[257];
-            }
+            float num = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) num += wgt[h * 8 + w] * red[((size_t)w * 4 + h) * kAttnStride + f];
             block_out[(size_t)head * kAttnStride + f] = num;
-            if (f == 0) { block_out[(size_t)head * kAttnStride + 256] = mm; block_out[(size_t)head * kAttnStride + 257] = den; }
         }
         named_barrier(1, CT);
     }
-    __threadfence();
-    named_barrier(1, CT);
-    if (tid == 0) {
-        const unsigned int done = atomicAdd(mp.attn_counters + kvh, 1u);
-        *S.flag = done == (unsigned int)active - 1;
+    QD_MARK(11);
+}
+
+// Second half: every block merges the split partials of its share of the output features,
+// normalises and applies the sigmoid gate.  One warp per output feature, lanes over splits.
+QD_DEVINL void attn_merge_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = mp.hq / mp.hkv, D = mp.d;
+    const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
+    const AttnSplit cut = attn_split(position + 1, mp.attn_splits);
+    const int total = mp.hq * D;
+    const int share = (total + gridDim.x - 1) / gridDim.x;
+    const int o0 = blockIdx.x * share, o1 = min(total, o0 + share);
+    phase_wait(mp, S, pi, tid);
+    if (tid == 0) trace_mark(mp, pi, 0);
+#pragma unroll 1
+    for (int o = o0 + warp; o < o1; o += CW) {
+        const int qh = o / D, f = o % D;
+        const int kvh = qh / G, h = qh % G;
+        const float* base = mp.attn_partial + ((size_t)kvh * mp.attn_splits * G + h) * kAttnStride;
+        const float gate_raw = ldcg_bf16(ph.qg + (size_t)qh * 2 * D + D + f);
+        float ms[2], ls[2], as[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int s = lane + 32 * k;
+            const float* src = base + (size_t)s * G * kAttnStride;
+            const bool on = s < cut.active;
+            ms[k] = on ? __ldcg(src + 256) : -INFINITY;
+            ls[k] = on ? __ldcg(src + 257) : 0.f;
+            as[k] = on ? __ldcg(src + f) : 0.f;
+        }
+        const float mm = warp_max(fmaxf(ms[0], ms[1]));
+        const float w0 = ms[0] == -INFINITY ? 0.f : expf(ms[0] - mm);
+        const float w1 = ms[1] == -INFINITY ? 0.f : expf(ms[1] - mm);
+        const float num = warp_sum(w0 * as[0] + w1 * as[1]);
+        const float den = warp_sum(w0 * ls[0] + w1 * ls[1]);
+        if (lane == 0) {
+            const float attended = round_bf16(num / den);
+            const float gate = round_bf16(sigmoid_precise(gate_raw));
+            ph.mix_out[o] = __float2bfloat16_rn(attended * gate);
+        }
     }
-    named_barrier(1, CT);
-    if (!*S.flag) return;
-    __threadfence();
-    // last block of this KV head: merge the splits, normalise, gate
-    const float* base = mp.attn_partial + ((size_t)kvh * mp.attn_splits) * G * kAttnStride;
-    for (int idx = tid; idx < G * active; idx += CT) {
-        const int h = idx / active, s = idx % active;
-        wsum[h * kMegaAttnSplits + s] = __ldcg(base + ((size_t)s * G + h) * kAttnStride + 256);
-        lsum[h * kMegaAttnSplits + s] = __ldcg(base + ((size_t)s * G + h) * kAttnStride + 257);
+}
+
+// One down-projection row (512 inputs) by a half-warp: lane hl holds inputs [32 hl, 32 hl + 32).
+QD_DEVINL float down_row(const uint8_t* base, int r, int hl, const uint32_t (&xh)[16]) {
+    const uint4 w = lds128(base + r * (kDownWidth / 2) + hl * 16);
+    const float2 sc = e4m3x2_to_float2(*reinterpret_cast<const uint16_t*>(
+        base + kMegaDownRows * (kDownWidth / 2) + r * (kDownWidth / 16) + hl * 2));
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+    float g[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint32_t h2[4];
+        e2m1x8_to_f16x2(words[q], h2);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            g[(q >> 1) * 2] = fma_f16_lo(h2[b], xh[q * 4 + b], g[(q >> 1) * 2]);
+            g[(q >> 1) * 2 + 1] = fma_f16_hi(h2[b], xh[q * 4 + b], g[(q >> 1) * 2 + 1]);
+        }
     }
-    named_barrier(1, CT);
-    if (tid < G) {
-        float mm = -INFINITY;
-        for (int s = 0; s < active; ++s) mm = fmaxf(mm, wsum[tid * kMegaAttnSplits + s]);
-        hmax[tid] = mm;
-    }
-    named_barrier(1, CT);
-    for (int idx = tid; idx < G * active; idx += CT) {
-        const int h = idx / active, s = idx % active;
-        const float ms = wsum[h * kMegaAttnSplits + s];
-        const float wgt = ms == -INFINITY ? 0.f : expf(ms - hmax[h]);
-        wsum[h * kMegaAttnSplits + s] = wgt;
-        lsum[h * kMegaAttnSplits + s] *= wgt;
-    }
-    named_barrier(1, CT);
-    if (tid < G) {
-        float den = 0.f;
-        for (int s = 0; s < active; ++s) den += lsum[tid * kMegaAttnSplits + s];
-        hmax[8 + tid] = den;
-    }
-    named_barrier(1, CT);
-    for (int idx = tid; idx < G * D; idx += CT) {
-        const int h = idx / D, f = idx % D;
-        float num = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < active; ++s)
-            num += wsum[h * kMegaAttnSplits + s] * __ldcg(base + ((size_t)s * G + h) * kAttnStride + f);
-        const float attended = round_bf16(num / hmax[8 + h]);
-        const int qh = kvh * G + h;
-        const float gate = round_bf16(sigmoid_precise(ldcg_bf16(ph.qg + (size_t)qh * 2 * D + D + f)));
-        ph.mix_out[(size_t)qh * D + f] = __float2bfloat16_rn(attended * gate);
-    }
-    if (tid == 0) mp.attn_counters[kvh] = 0;
+    float acc = fmaf(sc.x, g[0] + g[1], 0.f);
+    acc = fmaf(sc.y, g[2] + g[3], acc);
+    return group_sum<16>(acc);
 }
 
 // Routed and shared down projections with the combine (quickdraw/models/qwen.py:185-193):
-// warp s works on slot s, each half-warp on alternate rows; rounding points as in moe.cu.
-QD_DEVINL void down_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi, int& it) {
+// warp s works on slot s, each half-warp on alternate rows, two rows in flight; rounding
+// points as in moe.cu.  The rows were fetched into the scratch area during the gate/up phase.
+QD_DEVINL void down_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int H = mp.hidden;
     const int r0 = (int)((long long)H * blockIdx.x / gridDim.x);
     const int r1 = (int)((long long)H * (blockIdx.x + 1) / gridDim.x);
     const int n = r1 - r0, nslots = mp.topk + 1;
-    const int tiles = (nslots + kMegaDownSlotsPerTile - 1) / kMegaDownSlotsPerTile;
-    float* contrib = S.scratch;                 // [slots][kMegaDownRows]
+    float* contrib = reinterpret_cast<float*>(S.xs);                         // [slots][kMegaDownRows]
+    int* order = reinterpret_cast<int*>(contrib + kDownSlots * kMegaDownRows);   // [topk]
     phase_wait(mp, S, pi, tid);
     if (tid == 0) trace_mark(mp, pi, 0);
-    // Both tiles are normally on chip already (the producer fetched them during the gate/up
-    // phase); wait for them first so that nothing large is live across the waits.
-    bool ok = !*S.abort;
-    const int it0 = it;
-    for (int t = 0; t < tiles && ok; ++t)
-        ok = mbar_wait(S.full + ((it0 + t) % NS), ((it0 + t) / NS) & 1, mp.status);
-    it += tiles;
+    const float strength = tid < kMegaDownRows ? ldcg_bf16(ph.strength) : 0.f;    // in flight during the rows
     const int s = warp;
     const bool worker = s < nslots;
     const bool shared = s == mp.topk;
     const int e = (worker && !shared) ? S.ids[s] : 0;
     const bool owned = worker && (shared || (e >= mp.expert_lo && e < mp.expert_hi));
     const int hl = lane & 15, half = lane >> 4;
+    bool ok = !*S.abort;
     if (worker && ok) {
         uint32_t xh[16];
-        float amax = 0.f;
+        uint32_t m2 = 0u;          // largest |bf16| bit pattern, per 16-bit half
         const uint32_t* src = reinterpret_cast<const uint32_t*>(ph.hidden + (size_t)s * kDownWidth) + hl * 16;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            xh[j] = __ldcg(src + j);
-            amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(xh[j] << 16)), fabsf(__uint_as_float(xh[j] & 0xffff0000u))));
+        for (int j = 0; j < 16; j += 4) {
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + j));
+            xh[j] = v.x; xh[j + 1] = v.y; xh[j + 2] = v.z; xh[j + 3] = v.w;
         }
-        amax = warp_max(amax);
-        int ex = 0;
-        if (amax > 0.f && amax < INFINITY) frexpf(amax, &ex);
-        const int shift = ex > 15 ? ex - 15 : 0;
-        const float down = ldexpf(1.f, -shift);
-        const float mult = ldexpf(1.f, shift);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const __half2 h = __floats2half2_rn(__uint_as_float(xh[j] << 16) * down,
-                                                __uint_as_float(xh[j] & 0xffff0000u) * down);
-            xh[j] = *reinterpret_cast<const uint32_t*>(&h);
-        }
+        for (int j = 0; j < 16; ++j) m2 = max_u16x2(m2, xh[j] & 0x7fff7fffu);
+        uint32_t m = max(m2 & 0xffffu, m2 >> 16);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+        // |x| < 2^(exponent + 1); scale down by a power of two only if f16 would overflow
+        // (non-finite inputs are left alone)
+        const int exponent = (int)(m >> 7) - 127;
+        const int shift = (exponent > 14 && exponent < 128) ? exponent - 14 : 0;
+        const float down = __uint_as_float((uint32_t)(127 - shift) << 23);
+        const float mult = __uint_as_float((uint32_t)(127 + shift) << 23);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) xh[j] = pack_f16x2(__uint_as_float(xh[j] << 16) * down,
+                                                       __uint_as_float(xh[j] & 0xffff0000u) * down);
         float scale;
         if (shared) scale = ph.sg[0];
         else scale = round_bf16(ph.dg[ph.g_per_expert ? e - mp.expert_lo : 0] * S.weights[s]);
-        const int st = (it0 + s / kMegaDownSlotsPerTile) % NS;
-        const uint8_t* base = S.stages + (size_t)st * kStreamStageBytes +
-                              (size_t)(s % kMegaDownSlotsPerTile) * kMegaDownRows * kDownRowBytes;
+        QD_MARK(8);
+        ok = mbar_wait(S.down_bar, ph.layer & 1, mp.status);
+        QD_MARK(9);
+        const uint8_t* base = reinterpret_cast<const uint8_t*>(S.scratch) + (size_t)s * kMegaDownRows * kDownRowBytes;
+        if (ok) {
 #pragma unroll 1
-        for (int rr = 0; rr < n; rr += 2) {
-            const bool live = rr + half < n;
-            const int r = live ? rr + half : n - 1;
-            float value = 0.f;
-            if (owned) {
-                const uint4 w = lds128(base + r * (kDownWidth / 2) + hl * 16);
-                const float2 sc = e4m3x2_to_float2(*reinterpret_cast<const uint16_t*>(
-                    base + kMegaDownRows * (kDownWidth / 2) + r * (kDownWidth / 16) + hl * 2));
-                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-                float g[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t h2[4];
-                    e2m1x8_to_f16x2(words[q], h2);
-#pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        g[(q >> 1) * 2] = fma_f16_lo(h2[b], xh[q * 4 + b], g[(q >> 1) * 2]);
-                        g[(q >> 1) * 2 + 1] = fma_f16_hi(h2[b], xh[q * 4 + b], g[(q >> 1) * 2 + 1]);
-                    }
+            for (int rr = 0; rr < n; rr += 4) {
+                // both half-warps run the same iterations (the shuffles name all 32 lanes); a
+                // half-warp past the last row recomputes it and does not store
+                const int ra = min(rr + half, n - 1), rb = min(rr + 2 + half, n - 1);
+                float va = 0.f, vb = 0.f;
+                if (owned) {
+                    const float acc_a = down_row(base, ra, hl, xh) * mult;
+                    const float acc_b = down_row(base, rb, hl, xh) * mult;
+                    va = shared ? round_bf16(acc_a * scale) : round_bf16(round_bf16(acc_a) * scale);
+                    vb = shared ? round_bf16(acc_b * scale) : round_bf16(round_bf16(acc_b) * scale);
                 }
-                float acc = fmaf(sc.x, g[0] + g[1], 0.f);
-                acc = fmaf(sc.y, g[2] + g[3], acc);
-                acc = group_sum<16>(acc) * mult;
-                value = shared ? round_bf16(acc * scale) : round_bf16(round_bf16(acc) * scale);
+                if (hl == 0 && rr + half < n) contrib[s * kMegaDownRows + ra] = va;
+                if (hl == 0 && rr + 2 + half < n) contrib[s * kMegaDownRows + rb] = vb;
             }
-            if (hl == 0 && live) contrib[s * kMegaDownRows + r] = value;
         }
+    } else if (warp == CW - 1 && lane < mp.topk) {
+        // slots in ascending expert id: the order the routed rows are summed in
+        const int id = S.ids[lane];
+        int rank = 0;
+        for (int q = 0; q < mp.topk; ++q) rank += S.ids[q] < id;
+        order[rank] = lane;
     }
-    __syncwarp();
-    if (lane == 0 && ok)
-        for (int t = 0; t < tiles; ++t) mbar_arrive(S.empty + ((it0 + t) % NS));
+    QD_MARK(10);
     if (!ok && lane == 0) give_up(mp, S);
     named_barrier(1, CT);
+    QD_MARK(11);
     if (tid < n && ok) {
         float routed = 0.f;
-        int last = -1;
-        for (int k = 0; k < mp.topk; ++k) {       // ascending expert id
-            int pick = -1, pick_id = 0x7fffffff;
-            for (int q = 0; q < mp.topk; ++q) {
-                const int id = S.ids[q];
-                if (id > last && id < pick_id) { pick = q; pick_id = id; }
-            }
-            if (pick < 0) break;
-            last = pick_id;
-            routed += contrib[pick * kMegaDownRows + tid];
-        }
-        const float gate = round_bf16(sigmoid_precise(ldcg_bf16(ph.strength)));
+        for (int k = 0; k < mp.topk; ++k) routed += contrib[order[k] * kMegaDownRows + tid];
+        const float gate = round_bf16(sigmoid_precise(strength));
         const float shared_row = round_bf16(contrib[mp.topk * kMegaDownRows + tid] * gate);
         ph.out[r0 + tid] = __float2bfloat16_rn(round_bf16(routed) + shared_row);
     }
+    // the scratch area goes back to the mixer core of the next layer and, after that, to the
+    // next bulk copies: order this thread's reads and writes of it before those
+    fence_proxy_async();
 }
 
 __global__ void __launch_bounds__(kMegaThreads, 1)
 mega_kernel(const __grid_constant__ MegaParams mp) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    const Smem S = carve_smem(smem);
+    const Smem S = carve_smem(mega_smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if ((int)gridDim.x != mp.grid) {            // the program was laid out for another grid
         if (tid == 0) atomicOr(mp.status, QD_STATUS_BAD_SHAPE);
@@ -972,8 +1095,9 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
     }
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) { mbar_init(S.full + s, 1); mbar_init(S.empty + s, CW); }
+        mbar_init(S.ids_bar, 1);
+        mbar_init(S.down_bar, 1);
         mbar_fence_init();
-        *S.ids_seq = 0;
         *S.abort = 0;
         *S.flag = 0;
     }
@@ -1005,16 +1129,18 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
             gdn_phase(mp, ph, S, pi);
         } else if (ph.kind == MK_ATTN) {
             attn_phase(mp, ph, S, pi);
+        } else if (ph.kind == MK_ATTN_MERGE) {
+            attn_merge_phase(mp, ph, S, pi);
         } else {
-            down_phase(mp, ph, S, pi, it);
+            down_phase(mp, ph, S, pi);
         }
         cp_async_wait_all();
+        fence_proxy_async();      // scratch and ring bytes this thread touched may be bulk-copy targets next
         if (tid == 0) trace_mark(mp, pi, 1);
         named_barrier(1, CT);
-        if (tid == 0 && pi + 1 < mp.nphases) {
-            __threadfence();
-            red_release_add(mp.bar, 1u);
-        }
+        // release: this block's writes (ordered before it by the block barrier) are visible to
+        // whoever acquires the new count
+        if (tid == 0 && pi + 1 < mp.nphases) red_release_add(mp.bar, 1u);
     }
     // the last block to leave resets the barrier words for the next launch
     if (tid == 0) {

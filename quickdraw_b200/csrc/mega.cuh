@@ -19,9 +19,8 @@ constexpr int kMegaMaxSeg = 10;
 constexpr int kMegaConvRows = 128;                    // conv channels one block can own
 constexpr int kMegaAttnSplits = 64;                   // context splits per KV head at most
 constexpr int kMegaDownRows = 16;                     // down-projection output rows per block at most
-constexpr int kMegaDownSlotsPerTile = 5;
 
-enum MegaKind { MK_STREAM = 0, MK_GDN = 1, MK_ATTN = 2, MK_DOWN = 3 };
+enum MegaKind { MK_STREAM = 0, MK_GDN = 1, MK_ATTN = 2, MK_DOWN = 3, MK_ATTN_MERGE = 4 };
 
 struct alignas(8) MegaSeg {
     const uint8_t* w;  const uint8_t* s;  const float* g;      // codes / bf16 rows, scales, global
@@ -71,7 +70,7 @@ struct MegaParams {
     float theta, eps;
     int conv_width, topk, experts, hidden, channels;
     int expert_lo, expert_hi;
-    unsigned long long* trace;     // optional: [phase][2][grid] timestamps (ns)
+    unsigned long long* trace;     // optional: [phase][16][grid] timestamps (ns)
 };
 
 int mega_launch(const MegaParams& p, cudaStream_t stream);

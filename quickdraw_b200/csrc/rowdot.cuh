@@ -78,6 +78,53 @@ QD_DEVINL float bf16_row_dot(const uint8_t* __restrict__ row, const uint32_t (&x
     return a0 + a1;
 }
 
+// The same dot products with the activation slice fetched from shared memory as it is used
+// (no register copy): for blocks that only see a few rows of a kind.  xf_t is the f16 vector
+// in the transposed layout where the piece of (chunk c, quarter q, lane) sits at
+// ((c * 4 + q) * 32 + lane) * 16 bytes; xs is the bf16 vector in natural order.
+template <int KC>
+QD_DEVINL float fp4_row_dot_smem(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                                 const uint8_t* __restrict__ xf_t, int lane) {
+    float acc = 0.f;
+#pragma unroll
+    for (int c = 0; c < KC; ++c) {
+        const uint4 w = lds128(codes + (c * 32 + lane) * 16);
+        const float2 s = e4m3x2_to_float2(*reinterpret_cast<const uint16_t*>(scales + (c * 32 + lane) * 2));
+        const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+        float g[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t h2[4];
+            e2m1x8_to_f16x2(words[q], h2);
+            const uint4 xq = lds128(xf_t + ((c * 4 + q) * 32 + lane) * 16);
+            const uint32_t xv[4] = {xq.x, xq.y, xq.z, xq.w};
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                g[(q >> 1) * 2] = fma_f16_lo(h2[b], xv[b], g[(q >> 1) * 2]);
+                g[(q >> 1) * 2 + 1] = fma_f16_hi(h2[b], xv[b], g[(q >> 1) * 2 + 1]);
+            }
+        }
+        acc = fmaf(s.x, g[0] + g[1], acc);
+        acc = fmaf(s.y, g[2] + g[3], acc);
+    }
+    return acc;
+}
+
+template <int NB>
+QD_DEVINL float bf16_row_dot_smem(const uint8_t* __restrict__ row, const uint8_t* __restrict__ xs, int lane) {
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        const uint4 w = lds128(row + (i * 32 + lane) * 16);
+        const uint4 x = lds128(xs + (i * 32 + lane) * 16);
+        a0 = fma_bf16_lo(w.x, x.x, a0); a1 = fma_bf16_hi(w.x, x.x, a1);
+        a0 = fma_bf16_lo(w.y, x.y, a0); a1 = fma_bf16_hi(w.y, x.y, a1);
+        a0 = fma_bf16_lo(w.z, x.z, a0); a1 = fma_bf16_hi(w.z, x.z, a1);
+        a0 = fma_bf16_lo(w.w, x.w, a0); a1 = fma_bf16_hi(w.w, x.w, a1);
+    }
+    return a0 + a1;
+}
+
 // top-k routing by one warp over at most 256 bf16 logits in global memory (written by other
 // blocks of this launch, hence the cache-global loads): fp32 softmax, lowest index wins
 // ties, weights renormalised (quickdraw/models/qwen.py:174-177).

@@ -303,14 +303,21 @@ bool mega_finish_stream(MegaPhase& ph, int grid) {
     return true;
 }
 
-int mega_phase_count(const qd_model_config& c) { return 6 * c.layers + 1; }
+
+
+// six phases per layer, one more (the split merge) per attention layer, and the LM head
+int mega_phase_count(const qd_model* m) {
+    int n = 6 * m->cfg.layers + 1;
+    for (int L = 0; L < m->cfg.layers; ++L) n += m->layers[L].is_attention ? 1 : 0;
+    return n;
+}
 
 bool mega_shape_ok(const qd_model_config& c, int grid) {
     return fused_shape_ok(c) && c.expert_lo == 0 && c.expert_hi >= c.experts && c.conv_width <= kStreamConvWidth &&
-           c.key_dim <= 128 && c.value_dim % 32 == 0 && c.value_heads * (c.value_dim / 32) <= grid &&
+           c.key_dim == 128 && c.value_dim % 32 == 0 && c.value_heads * (c.value_dim / 32) <= grid &&
            c.head_dim == 256 && c.rotary_dim <= 256 && c.kv_heads >= 1 && c.kv_heads <= grid &&
            c.q_heads / c.kv_heads <= 8 && (c.hidden + grid - 1) / grid <= kMegaDownRows &&
-           c.topk + 1 <= 2 * kMegaDownSlotsPerTile && grid <= kMaxGrid;
+           c.topk + 1 <= 9 && c.topk + 1 <= kMegaMaxSeg && c.conv_width <= 4 && grid <= kMaxGrid;
 }
 
 int mega_attn_splits(const qd_model_config& c, int grid) {
@@ -322,7 +329,7 @@ int mega_attn_splits(const qd_model_config& c, int grid) {
 
 extern "C" long long qd_program_bytes(const qd_model* model) {
     if (!model) return -1;
-    return (long long)mega_phase_count(model->cfg) * (long long)sizeof(MegaPhase);
+    return (long long)mega_phase_count(model) * (long long)sizeof(MegaPhase);
 }
 
 extern "C" int qd_program_build(const qd_model* model, void* workspace, void* host_out, long long bytes) {
@@ -369,6 +376,8 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
             m.kind = MK_ATTN;
             m.qg = w.big; m.k_new = w.mid; m.v_new = w.mid + kv_width;
             m.q_norm = (const bf16*)ly.q_norm; m.k_norm = (const bf16*)ly.k_norm;
+            out[n++] = m;
+            m.kind = MK_ATTN_MERGE;       // second half: merge of the context splits, gate
         } else {
             m.kind = MK_GDN;
             m.qkv = w.big; m.a = w.ab; m.b = w.ab + c.value_heads;
@@ -387,33 +396,36 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
         MegaPhase cc = {};
         cc.kind = MK_STREAM; cc.width = H; cc.prologue = PRO_ADD_NORM; cc.layer = L;
         cc.gamma = ly.gamma_post; cc.x = w.mixed; cc.residual = w.resid[1]; cc.residual_out = w.resid[0];
-        cc.nseg = 3;
+        cc.nseg = 2;
         cc.seg[0] = mega_seg(bf16_seg(ly.router, c.experts, w.router_logits));
         cc.seg[1] = mega_seg(bf16_seg(ly.shared_expert_gate, 1, w.strength));
-        cc.seg[2] = mega_seg(pair_seg(ly.shared_gate, ly.shared_up, c.intermediate, w.hidden + (size_t)c.topk * c.intermediate));
         if (!mega_finish_stream(cc, grid)) return QD_ERR_UNSUPPORTED;
         out[n++] = cc;
-        // ---- D: routing, then the routed gate/up pairs on the vector phase C built
+        // ---- D: routing; the shared expert's gate/up (its weights do not wait for the routing),
+        //         then the routed gate/up pairs, all on the vector phase C built
         MegaPhase d = {};
         d.kind = MK_STREAM; d.width = H; d.prologue = PRO_NONE; d.layer = L; d.keep_x = 1; d.route = 1; d.uses_ids = 1;
         d.router_logits = w.router_logits; d.ids_out = w.ids; d.weights_out = w.weights;
-        d.nseg = c.topk;
+        d.nseg = c.topk + 1;
+        d.seg[0] = mega_seg(pair_seg(ly.shared_gate, ly.shared_up, c.intermediate, w.hidden + (size_t)c.topk * c.intermediate));
         for (int s = 0; s < c.topk; ++s) {
             StreamSeg sg = pair_seg(ly.experts_gate, ly.experts_up, c.intermediate, w.hidden + (size_t)s * c.intermediate);
             sg.slot = s; sg.g_per_expert = ly.experts_global_per_expert;
             sg.w_stride = (long long)c.intermediate * (H / 2);
             sg.s_stride = (long long)c.intermediate * (H / 16);
-            d.seg[s] = mega_seg(sg);
+            d.seg[s + 1] = mega_seg(sg);
         }
         if (!mega_finish_stream(d, grid)) return QD_ERR_UNSUPPORTED;
-        out[n++] = d;
-        // ---- E: down projections and combine
+        // ---- E: down projections and combine.  Phase D carries the same weight pointers: its
+        //         producer fetches the down-projection rows as soon as the routing is known.
         MegaPhase e = {};
         e.kind = MK_DOWN; e.layer = L; e.uses_ids = 1;
         e.hidden = w.hidden; e.dw = (const uint8_t*)ly.experts_down.codes; e.ds = (const uint8_t*)ly.experts_down.scales;
         e.dg = ly.experts_down.global; e.g_per_expert = ly.experts_global_per_expert;
         e.sw = (const uint8_t*)ly.shared_down.codes; e.ss = (const uint8_t*)ly.shared_down.scales; e.sg = ly.shared_down.global;
         e.strength = w.strength; e.out = w.moe_out;
+        d.dw = e.dw; d.ds = e.ds; d.sw = e.sw; d.ss = e.ss;
+        out[n++] = d;
         out[n++] = e;
     }
     // ---- head: residual add + final norm -> LM head rows with greedy argmax
@@ -424,7 +436,7 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
     h.seg[0] = mega_seg(bf16_seg(c.lm_head, c.vocab, nullptr, EP_ARGMAX));
     if (!mega_finish_stream(h, grid)) return QD_ERR_UNSUPPORTED;
     out[n++] = h;
-    return n == mega_phase_count(c) ? QD_OK : QD_ERR_ARG;
+    return n == mega_phase_count(model) ? QD_OK : QD_ERR_ARG;
 }
 
 extern "C" int qd_decode_step_persistent(const qd_model* model, const qd_state* state, const long long* token,
@@ -440,7 +452,7 @@ extern "C" int qd_decode_step_persistent(const qd_model* model, const qd_state* 
     Workspace w = carve(c, (uint8_t*)workspace);
     MegaParams p = {};
     p.program = (const MegaPhase*)program;
-    p.nphases = mega_phase_count(c) - ((flags & QD_FLAG_NO_LOGITS) ? 1 : 0);
+    p.nphases = mega_phase_count(model) - ((flags & QD_FLAG_NO_LOGITS) ? 1 : 0);
     p.grid = grid;
     p.st = *state;
     p.token = token; p.pos_dev = position_dev; p.pos_host = position_host;

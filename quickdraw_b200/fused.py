@@ -149,7 +149,7 @@ class FusedStep:
         self.program = None
         self.trace = None
         if persistent is None:
-            persistent = False
+            persistent = expert_range is None
         if persistent:
             assert expert_range is None, "the persistent kernel needs the whole model on one GPU"
             size = self.lib.qd_program_bytes(self.model)

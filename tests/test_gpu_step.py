@@ -58,14 +58,15 @@ def real_width_case(cuda_device):
     return ckpt, ckpt_cpu, prompt, tokens, state
 
 
-def test_fused_step_single_token_matches_oracle(cuda_device, real_width_case):
+@pytest.mark.parametrize("persistent", [True, False], ids=["one-launch", "launch-per-phase"])
+def test_fused_step_single_token_matches_oracle(cuda_device, real_width_case, persistent):
     """Whole-step logits and state against the oracle.  Every block agrees with the oracle to
     a few bf16 roundings when it is fed the oracle's input (tests/test_gpu_ops.py); over a
     whole step those roundings are amplified by the bf16 rounding points of the following
     blocks, so the step is compared at a looser relative L2 than a single block."""
     from quickdraw_b200.fused import FusedStep
     ckpt, ckpt_cpu, *_ = real_width_case
-    step = FusedStep(ckpt)
+    step = FusedStep(ckpt, persistent=persistent)
     state = DecodeState.allocate(ckpt.config, 96, "cuda")
     ref = DecodeState.allocate(ckpt.config, 96, "cpu")
     for position, token in enumerate([7, 1500, 3]):
@@ -79,17 +80,69 @@ def test_fused_step_single_token_matches_oracle(cuda_device, real_width_case):
     assert O.rel_l2(state.kv_k[:, :3].cpu(), ref.kv_k[:, :3]) < 5e-2
 
 
-def test_fused_matches_composed(cuda_device, real_width_case):
+@pytest.mark.parametrize("persistent", [True, False], ids=["one-launch", "launch-per-phase"])
+def test_fused_matches_composed(cuda_device, real_width_case, persistent):
     from quickdraw_b200.fused import FusedStep
     from quickdraw_b200.kernels import bind_kernels
     ckpt = real_width_case[0]
-    fused, composed = FusedStep(ckpt), bind_kernels()["forward_step"]
+    fused, composed = FusedStep(ckpt, persistent=persistent), bind_kernels()["forward_step"]
     s1, s2 = (DecodeState.allocate(ckpt.config, 16, "cuda") for _ in range(2))
     for position, token in enumerate([9, 100, 2000, 31]):
         t = torch.tensor(token, device="cuda")
         a, b = fused(ckpt, t, position, s1), composed(ckpt, t, position, s2)
         assert O.rel_l2(a.cpu(), b.cpu()) < 1e-2
     assert O.rel_l2(s1.rec_state.cpu(), s2.rec_state.cpu()) < 1e-2
+
+
+def _random_state(cfg, capacity, seed):
+    state = DecodeState.allocate(cfg, capacity, "cuda")
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    for t, std in ((state.kv_k, 1.0), (state.kv_v, 1.0), (state.rec_state, 0.1), (state.conv_state, 1.0)):
+        t.copy_((torch.randn(t.shape, generator=g, device="cuda") * std).to(t.dtype))
+    return state
+
+
+def _clone_state(state):
+    return DecodeState(state.kv_k.clone(), state.kv_v.clone(), state.rec_state.clone(),
+                       state.conv_state.clone(), state.position)
+
+
+def test_one_launch_step_equals_launch_per_phase_without_attention(cuda_device):
+    """The persistent kernel runs the arithmetic of the separate kernels (same rounding points,
+    same summation order) for everything but attention: on a DeltaNet-only model logits, tokens
+    and state must be bit-identical."""
+    from quickdraw_b200.fused import FusedStep
+    cfg = synthetic.model_config(num_layers=3, vocab_size=4096, interval=8)
+    ckpt = synthetic.make_checkpoint(cfg, seed=3, device="cuda")
+    one, many = FusedStep(ckpt, persistent=True), FusedStep(ckpt, persistent=False)
+    s1 = _random_state(cfg, 32, 5)
+    s2 = _clone_state(s1)
+    token = torch.tensor(11, device="cuda")
+    for position in range(6):
+        a, b = one(ckpt, token, position, s1), many(ckpt, token, position, s2)
+        assert torch.equal(a, b) and int(one.next_token) == int(many.next_token)
+        token = one.next_token.clone()
+    assert one.status() == 0
+    assert torch.equal(s1.rec_state, s2.rec_state) and torch.equal(s1.conv_state, s2.conv_state)
+
+
+@pytest.mark.parametrize("position", [0, 1, 31, 32, 77, 600, 1500, 2047])
+def test_one_launch_step_attention_over_long_contexts(cuda_device, position):
+    """Attention in the persistent kernel cuts the context its own way (up to 64 splits per KV
+    head, merged by a second phase); against the separate attention kernel on the same
+    random cache the step must agree to fp32 summation-order level, at any position."""
+    from quickdraw_b200.fused import FusedStep
+    cfg = synthetic.model_config(num_layers=4, vocab_size=4096)
+    ckpt = synthetic.make_checkpoint(cfg, seed=4, device="cuda")
+    one, many = FusedStep(ckpt, persistent=True), FusedStep(ckpt, persistent=False)
+    s1 = _random_state(cfg, 2048, 6)
+    s2 = _clone_state(s1)
+    token = torch.tensor(123, device="cuda")
+    a, b = one(ckpt, token, position, s1), many(ckpt, token, position, s2)
+    assert one.status() == 0
+    assert O.rel_l2(a.cpu(), b.cpu()) < 2e-3
+    assert torch.equal(s1.kv_k, s2.kv_k) and torch.equal(s1.kv_v, s2.kv_v)
+    assert O.rel_l2(s1.rec_state.cpu(), s2.rec_state.cpu()) < 2e-3
 
 
 def test_greedy_64_tokens_against_oracle(cuda_device, real_width_case):
