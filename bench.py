@@ -11,10 +11,10 @@ prompt is 512 uniform random token ids.  Rank 0 prints one JSON line:
              resident in HBM), max over ranks;
   e2e        the same through ``Engine.decode_step`` with the token and position coming
              from pinned host memory and the selected token read back every step;
-  roofline   the NVFP4 streaming matvec on the single-matvec configuration
-             ([1024, 2048] fused gate+up of one expert) over a bank of 256 distinct
-             matrices (302 MB, larger than L2), algorithmic bytes / CUDA-event time per
-             launch against the measured HBM copy bandwidth;
+  roofline   the token-step kernel (one launch per token on one GPU): algorithmic bytes of a
+             token / CUDA-event time per launch against the measured HBM copy bandwidth;
+  matvec_roofline  the NVFP4 streaming matvec kernel alone, 128 units of the single-matvec
+             configuration ([1024, 2048]) per launch over two 151 MB matrices (more than L2);
   cpu_baseline  the CPU oracle (a port of the reference's PyTorch path) timed on this
              host on a bounded sample: one 4-layer group and the LM head, scaled to 48 layers.
 
@@ -43,6 +43,10 @@ sys.path.insert(0, str(ROOT))
 PROMPT_LEN = 512
 BF16 = torch.bfloat16
 CONFIG1_BYTES = 1024 * 1024 + 1024 * 128 + 4 + 4096 + 2048     # weights + x + y of one matvec
+# DRAM bytes (read + write) of one token step: captured with ncu on an 8-layer model of the
+# same widths (a full-size capture would hold 24 GB through the replay passes) and scaled to
+# the full model by the algorithmic bytes, to which it is proportional.
+STEP_TRAFFIC_RATIO = 1.049       # ncu: (dram read + write) / algorithmic bytes of one persistent launch
 
 
 def measured_peaks():
@@ -186,48 +190,44 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(cfg, world):
-    return {"workload": "config 4: synthetic 36B-A3B hybrid (36 gated-DeltaNet + 12 GQA layers, "
-                        "256-expert top-8 NVFP4 MoE, vocab 151936), 512-token prompt then greedy decode, batch 1",
-            "layers": cfg.num_hidden_layers, "prompt": PROMPT_LEN,
+def workload_config(cfg, world, prompt=PROMPT_LEN):
+    full = cfg.layer_types.count("full_attention")
+    name = "config 4: " if (cfg.num_hidden_layers, cfg.vocab_size) == (48, 151936) else "REDUCED (profiling only): "
+    return {"workload": f"{name}synthetic 36B-A3B hybrid ({cfg.num_hidden_layers - full} gated-DeltaNet + {full} GQA "
+                        f"layers, {cfg.num_experts}-expert top-{cfg.num_experts_per_tok} NVFP4 MoE, vocab "
+                        f"{cfg.vocab_size}), 512-token prompt then greedy decode, batch 1",
+            "layers": cfg.num_hidden_layers, "prompt": prompt,
             "parallelism": "single GPU" if world == 1 else f"expert parallel x{world} (experts sharded, rest replicated)",
             "l2": "every token streams ~2.5 GB of weights, far beyond the 126 MB L2; no flush needed"}
 
 
 # ----------------------------------------------------------------------- GPU benchmark
-def matvec_roofline(device):
-    """NVFP4 streaming matvec over a bank of 256 distinct [1024, 2048] matrices."""
+def matvec_roofline(device, rows=131072, width=2048, mats=2, reps=10):
+    """The NVFP4 streaming matvec kernel alone: `mats` distinct [rows, width] matrices
+    (2 x 151 MB by default, more than L2), one launch each, alternating.  A launch does
+    rows / 1024 units of the single-matvec configuration ([1024, 2048])."""
     from quickdraw_b200 import synthetic
     from quickdraw_b200._lib import call, ptr, stream_of
-    rows, width, mats = 1024, 2048, 256
     src = synthetic.Source(1, device)
     bank = src.nvfp4("roofline.bank", rows, width, mats)
     x = src.normal("roofline.x", width)
     y = torch.empty(mats, rows, dtype=BF16, device=device)
 
-    def launch():
-        call("qd_nvfp4_gemv_bank", ptr(x), ptr(bank.weight), ptr(bank.weight_scale),
-             ptr(bank.weight_scale_2), ptr(y), rows, width, mats, 1, stream_of(x))
-    side = torch.cuda.Stream(device)
-    side.wait_stream(torch.cuda.current_stream(device))
-    with torch.cuda.stream(side):
-        launch()
-    torch.cuda.current_stream(device).wait_stream(side)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        launch()
-    for _ in range(3):
-        graph.replay()
+    def launch(i):
+        call("qd_nvfp4_gemv", ptr(x), ptr(bank.weight[i]), ptr(bank.weight_scale[i]), ptr(bank.weight_scale_2),
+             None, ptr(y[i]), rows, width, 16, 0, stream_of(x))
+    for i in range(3 * mats):
+        launch(i % mats)
     torch.cuda.synchronize(device)
-    reps = 20
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(reps):
-        graph.replay()
+    for i in range(reps * mats):
+        launch(i % mats)
     e1.record()
     torch.cuda.synchronize(device)
     per_launch_s = e0.elapsed_time(e1) * 1e-3 / (reps * mats)
-    return CONFIG1_BYTES / per_launch_s / 1e9, per_launch_s
+    units = rows // 1024
+    return units * CONFIG1_BYTES / per_launch_s / 1e9, per_launch_s, units
 
 
 def run_gpu(args):
@@ -235,7 +235,7 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     from quickdraw_b200 import synthetic
-    cfg = synthetic.model_config()
+    cfg = synthetic.model_config(num_layers=args.layers, vocab_size=args.vocab)
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
@@ -290,7 +290,10 @@ def run_gpu(args):
     if rank != 0:
         return
     peak, peak_kind = measured_peaks()
-    achieved, per_launch_s = matvec_roofline(device)
+    if args.matvec_rows:
+        mv_gbs, mv_launch_s, mv_units = matvec_roofline(device, rows=args.matvec_rows)
+    else:
+        mv_gbs, mv_launch_s, mv_units = matvec_roofline(device)
     position = args.prompt + args.warmup + args.steps // 2
     token_bytes = bytes_per_token(cfg, position)
     tok_s = args.steps / (device_ms * 1e-3)
@@ -302,19 +305,24 @@ def run_gpu(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 activations, NVFP4 (E2M1 + E4M3 block scale) weights, fp32 accumulate",
-        "data": "synthetic", "config": workload_config(cfg, world),
+        "data": "synthetic", "config": workload_config(cfg, world, args.prompt),
         "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 12,
                 "d2h_bytes_per_step": 8},
         "gpu_launches": launches * args.steps,
         "clocks": clocks.summary(),
-        "roofline": {"bound": "hbm", "kernel": "stream_kernel (NVFP4 matvec, [1024,2048] x 256-matrix bank)",
-                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
-                     "launch_us": per_launch_s * 1e6, "bytes_per_launch": CONFIG1_BYTES},
-        "decode_roofline": {"bytes_per_token": token_bytes,
-                            "achieved_gbs": token_bytes * tok_s / 1e9 / world,
-                            "frac_of_measured_peak": token_bytes * tok_s / 1e9 / world / peak,
-                            "frac_of_8tbs": token_bytes * tok_s / 8e12 / world},
+        # the dominant kernel is the token step itself: one launch = one token = every weight
+        # the token touches, read once (single GPU: the persistent kernel; expert parallel: the
+        # per-rank share of the launches of one step)
+        "roofline": {"bound": "hbm",
+                     "kernel": "mega_kernel (one launch per token)" if world == 1 else "decode step, per rank",
+                     "achieved": token_bytes * tok_s / 1e9 / world, "peak": peak, "unit": "GB/s",
+                     "frac": token_bytes * tok_s / 1e9 / world / peak,
+                     "peak_source": f"{peak_kind} copy bandwidth", "traffic": int(token_bytes * STEP_TRAFFIC_RATIO) if world == 1 else None,
+                     "launch_us": device_ms / args.steps * 1e3, "bytes_per_launch": token_bytes,
+                     "frac_of_8tbs": token_bytes * tok_s / 8e12 / world},
+        "matvec_roofline": {"kernel": "stream_kernel (NVFP4 matvec, %d x [1024,2048] per launch, 2 matrices alternating)" % mv_units,
+                            "achieved": mv_gbs, "peak": peak, "unit": "GB/s", "frac": mv_gbs / peak,
+                            "launch_us": mv_launch_s * 1e6, "bytes_per_launch": mv_units * CONFIG1_BYTES},
         "cpu_baseline": {"value": 1.0 / per_token_cpu, "unit": "tok/s", "cores": threads, "kind": "port",
                          "sample": "one 4-layer group and the LM head at position 640, group time x12 + head time"},
     }
@@ -329,6 +337,9 @@ def main():
     ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
     ap.add_argument("--prompt", type=int, default=PROMPT_LEN, help="prompt length (512 in the headline workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU sample (profiling runs)")
+    ap.add_argument("--layers", type=int, default=48, help="model depth (48 in the headline workload; fewer for profiling)")
+    ap.add_argument("--vocab", type=int, default=151936, help="vocabulary (151936 in the headline workload)")
+    ap.add_argument("--matvec-rows", type=int, default=0, help="rows of the matvec roofline matrices (default 131072)")
     args = ap.parse_args()
     assert args.warmup >= 0 and args.steps > 0
     if args.impl == "reference":

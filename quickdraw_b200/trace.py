@@ -1,0 +1,84 @@
+"""Per-phase timeline of one token step of the persistent kernel.
+
+    python -m quickdraw_b200.trace [--layers 8] [--position 600] [--show 1,3]
+
+Runs a few steps of a synthetic model of the 36B-A3B widths, then one step with the
+kernel's timestamp buffer attached (sixteen nanosecond marks per phase and block: 0 start
+after the grid barrier, 1 end, 2 activation vector ready, 3 first weight tile landed,
+4 / 5 first and last tile issued by the producer) and prints, per phase kind, the mean
+work time (last block's end - last block's start) and the mean barrier gap (last block's
+start - last block's end of the phase before).  Phase kinds: A in-projections, M mixer core
+(a = attention layer), N attention split merge, B out-projection, C router, D gate/up,
+E down + combine, H LM head.
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import numpy as np
+import torch
+
+from . import synthetic
+from .fused import FusedStep
+from .state import DecodeState
+
+SLOTS = 16
+
+
+def phase_plan(cfg) -> list[tuple[str, int]]:
+    plan = []
+    for index, kind in enumerate(cfg.layer_types):
+        attn = kind == "full_attention"
+        for k in (["A", "M", "N", "B", "C", "D", "E"] if attn else ["A", "M", "B", "C", "D", "E"]):
+            plan.append((k + ("a" if attn and k in "AMNB" else ""), index))
+    plan.append(("H", len(cfg.layer_types)))
+    return plan
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--position", type=int, default=600)
+    ap.add_argument("--show", default="", help="comma-separated layers to print phase by phase")
+    args = ap.parse_args()
+    dev = "cuda"
+    cfg = synthetic.model_config(num_layers=args.layers, vocab_size=args.vocab)
+    ckpt = synthetic.make_checkpoint(cfg, seed=0, device=dev)
+    step = FusedStep(ckpt, persistent=True)
+    state = DecodeState.allocate(cfg, 2048, dev)
+    state.kv_k.normal_()
+    state.kv_v.normal_()
+    grid = torch.cuda.get_device_properties(0).multi_processor_count
+    plan = phase_plan(cfg)
+    token = torch.tensor(11, device=dev)
+    for position in range(args.position, args.position + 4):
+        step(ckpt, token, position, state)
+    step.trace = torch.zeros(len(plan) * SLOTS * grid, dtype=torch.int64, device=dev)
+    step(ckpt, token, args.position + 4, state)
+    torch.cuda.synchronize()
+    assert step.status() == 0
+    marks = step.trace.cpu().numpy().reshape(len(plan), SLOTS, grid).astype(np.int64)
+    origin = marks[0, 0].min()
+    marks = np.where(marks > 0, marks - origin, -1)
+    show = {int(v) for v in args.show.split(",") if v}
+    print("ns since the first block started; per phase: start(min max) x-ready(median) tile0(median) end(min median max)")
+    totals: dict[str, list[tuple[int, int]]] = {}
+    previous_end = 0
+    for index, (kind, layer) in enumerate(plan):
+        start, end = marks[index, 0], marks[index, 1]
+        if layer in show or kind == "H":
+            print(f"{index:4d} {kind:3s} L{layer:<3d} {start.min():8d} {start.max():8d}  {int(np.median(marks[index, 2])):8d} "
+                  f"{int(np.median(marks[index, 3])):8d}  {end.min():8d} {int(np.median(end)):8d} {end.max():8d}")
+        totals.setdefault(kind, []).append((int(end.max() - start.max()), int(start.max() - previous_end)))
+        previous_end = int(end.max())
+    print(f"whole step: {marks[-1, 1].max() / 1e3:.1f} us")
+    for kind, rows in totals.items():
+        a = np.array(rows[1:] if len(rows) > 1 else rows)
+        print(f"{kind:3s} x{len(rows):3d}  work {a[:, 0].mean() / 1e3:7.2f} us   barrier gap {a[:, 1].mean() / 1e3:6.2f} us")
+
+
+if __name__ == "__main__":
+    with torch.inference_mode():
+        main()
