@@ -1,13 +1,52 @@
 """Expert parallelism on two GPUs against the single-GPU engine (NCCL, one process per
-GPU).  Skipped on a box with one GPU; host-side coverage is in test_expert_parallel_cpu.py."""
+GPU).  Skipped on a box with one GPU; host-side coverage is in test_expert_parallel_cpu.py.
+The ranks are child processes with a time limit: a rank that does not finish is killed by its
+own process id and the test fails with the ranks' output."""
 
+import json
 import os
 import socket
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
 
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parents[1]
+RANK_TIMEOUT_S = 120
+
+RANK_PROGRAM = r"""
+import json, os, sys
+import torch
+import torch.distributed as dist
+rank, world, port, outdir = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
+prompt, steps = json.loads(sys.argv[5]), int(sys.argv[6])
+os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=port, NCCL_NVLS_ENABLE="0")
+from quickdraw_b200 import synthetic
+from quickdraw_b200.expert_parallel import ExpertParallelEngine
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+print("rank", rank, "group up", flush=True)
+cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
+engine = ExpertParallelEngine(cfg, seed=11, max_context=64, device=f"cuda:{rank}")
+print("rank", rank, "engine built", flush=True)
+engine.state.kv_k.zero_()
+engine.state.kv_v.zero_()
+tokens = engine.generate(prompt, steps)
+print("rank", rank, "generated", flush=True)
+with open(os.path.join(outdir, f"rank{rank}.json"), "w") as f:
+    json.dump({"tokens": tokens, "status": engine.fused.status()}, f)
+# Every collective of this rank has completed (the tokens were read back).  Leave without the
+# communicator teardown: with a captured graph that holds collectives still alive it can wait
+# for the peer indefinitely, and the result is already on disk.
+torch.cuda.synchronize()
+sys.stdout.flush()
+os._exit(0)
+"""
 
 
 def _free_port():
@@ -16,29 +55,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, prompt, steps, outdir):
-    import torch.distributed as dist
-    from quickdraw_b200 import synthetic
-    from quickdraw_b200.expert_parallel import ExpertParallelEngine
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-    cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
-    engine = ExpertParallelEngine(cfg, seed=11, max_context=64, device=f"cuda:{rank}")
-    engine.state.kv_k.zero_()
-    engine.state.kv_v.zero_()
-    tokens = engine.generate(prompt, steps)
-    import json
-    with open(os.path.join(outdir, f"rank{rank}.json"), "w") as f:
-        json.dump({"tokens": tokens, "status": engine.fused.status()}, f)
-    dist.barrier()
-    dist.destroy_process_group()
-
-
 def test_two_rank_generation_matches_single_gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as mp
     from quickdraw_b200 import synthetic
     from quickdraw_b200.engine import Engine
     prompt, steps = [5, 1900, 77, 1033], 24
@@ -48,10 +67,29 @@ def test_two_rank_generation_matches_single_gpu():
     single.state.kv_v.zero_()
     want = single.generate(prompt, steps)
     del single
-    import json
-    import tempfile
+    torch.cuda.empty_cache()
+    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0")
     with tempfile.TemporaryDirectory() as outdir:
-        mp.spawn(_rank_main, args=(2, _free_port(), prompt, steps, outdir), nprocs=2, join=True)
+        port = str(_free_port())
+        logs = [open(os.path.join(outdir, f"rank{r}.log"), "w") for r in range(2)]
+        ranks = [subprocess.Popen([sys.executable, "-c", RANK_PROGRAM, str(r), "2", port, outdir,
+                                   json.dumps(prompt), str(steps)], env=env, stdout=logs[r],
+                                  stderr=subprocess.STDOUT, cwd=str(ROOT)) for r in range(2)]
+        failed = []
+        for r, proc in enumerate(ranks):
+            try:
+                if proc.wait(timeout=RANK_TIMEOUT_S) != 0:
+                    failed.append(f"rank {r} exited with {proc.returncode}")
+            except subprocess.TimeoutExpired:
+                failed.append(f"rank {r} did not finish within {RANK_TIMEOUT_S} s")
+        for proc in ranks:
+            if proc.poll() is None:
+                proc.kill()          # this process id only
+                proc.wait()
+        for f in logs:
+            f.close()
+        text = "\n".join(f"--- rank {r}\n" + open(os.path.join(outdir, f"rank{r}.log")).read()[-2000:] for r in range(2))
+        assert not failed, "; ".join(failed) + "\n" + text
         out = [json.load(open(os.path.join(outdir, f"rank{r}.json"))) for r in range(2)]
     assert out[0]["tokens"] == out[1]["tokens"], "ranks disagree"
     assert out[0]["status"] == 0 and out[1]["status"] == 0

@@ -1,0 +1,134 @@
+"""Host-side logic that needs no GPU: the C-ABI library loads and exports every symbol the
+header declares, a missing library fails loudly (there is no fallback path), and the engine's
+request control flow (reference behaviour: quickdraw/engine/engine.py:93-148, exercised the way
+tests/engine/test_engine.py of the reference does, with an injected step)."""
+
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from quickdraw_b200 import _lib, synthetic
+from quickdraw_b200.engine import Engine
+from quickdraw_b200.weights import Checkpoint
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = ROOT / "include" / "quickdraw_b200.h"
+
+
+def declared_symbols() -> list[str]:
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(qd_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = declared_symbols()
+    assert len(names) >= 30 and "qd_decode_step_persistent" in names and "qd_attn_decode_static" in names
+    handle = _lib.lib()
+    for name in names:
+        assert hasattr(handle, name), f"{name} is declared in the header but not exported"
+    assert handle.qd_version() >= 1
+    assert handle.qd_error_string(3) == b"bounded device wait ran out"
+
+
+def test_binding_table_covers_the_header():
+    assert set(declared_symbols()) == set(_lib.exported_symbols())
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libquickdraw_b200.so")
+    with pytest.raises(_lib.LibraryMissing, match="no fallback"):
+        _lib.lib()
+    from quickdraw_b200 import kernels
+    x = torch.zeros(2048, dtype=torch.bfloat16)
+    with pytest.raises((_lib.LibraryMissing, AssertionError)):
+        kernels.rms_norm(x, torch.ones(2048), 1e-6)
+
+
+# ------------------------------------------------------------------------- engine control flow
+class CountingStep:
+    """A step that emits a fixed token sequence: logits peak at script[position]."""
+
+    def __init__(self, vocab, script):
+        self.vocab, self.script, self.calls = vocab, script, []
+
+    def __call__(self, ckpt, token_id, position, state, **kwargs):
+        self.calls.append((int(token_id), int(position)))
+        state.rec_state.add_(1.0)
+        logits = torch.zeros(self.vocab)
+        logits[self.script[int(position) % len(self.script)]] = 1.0
+        return logits
+
+
+def make_engine(script, max_context=16):
+    cfg = synthetic.model_config(num_layers=4, vocab_size=64)
+    ckpt = Checkpoint(config=cfg, embed_tokens=None, final_norm=None, lm_head=None, layers=[])
+    step = CountingStep(cfg.vocab_size, script)
+    return Engine(ckpt, max_context=max_context, device="cpu", step=step), step
+
+
+def test_custom_step_selects_custom_backend_without_graph():
+    engine, _ = make_engine([1])
+    assert engine.backend == "custom" and engine.graph is None and engine.state.position == 0
+
+
+def test_b200_backend_refuses_a_cpu_device():
+    cfg = synthetic.model_config(num_layers=4, vocab_size=64)
+    ckpt = Checkpoint(config=cfg, embed_tokens=None, final_norm=None, lm_head=None, layers=[])
+    with pytest.raises(AssertionError, match="no CPU path"):
+        Engine(ckpt, max_context=8, device="cpu")
+
+
+def test_generate_runs_the_prompt_once_then_decodes():
+    engine, step = make_engine([3, 4, 5, 6, 7, 8, 9, 10])
+    out = engine.generate([20, 21, 22], 4)
+    # prompt tokens at positions 0..2; the logits after position 2 pick script[2] = 5; every
+    # decode step feeds the previous choice at the next position
+    assert out == [5, 6, 7, 8]
+    assert step.calls == [(20, 0), (21, 1), (22, 2), (5, 3), (6, 4), (7, 5)]
+    assert engine.state.position == 6
+
+
+def test_generate_stops_at_eos_and_keeps_it():
+    engine, _ = make_engine([3, 4, 5, 6, 7, 8])
+    engine.eos_token_ids = {6}
+    assert engine.generate([1, 2], 10) == [4, 5, 6]
+
+
+def test_generate_stops_at_capacity():
+    engine, _ = make_engine([1, 2, 3, 4, 5, 6, 7, 8], max_context=5)
+    out = engine.generate([9, 9, 9], 10)
+    assert len(out) == 3 and engine.state.position == 5       # prompt 3 + two decode steps fit
+
+
+def test_generate_argument_contract():
+    engine, step = make_engine([1])
+    assert engine.generate([1, 2], 0) == [] and step.calls == []
+    with pytest.raises(AssertionError, match="nonnegative"):
+        engine.generate([1], -1)
+    with pytest.raises(AssertionError, match="prompt must fit"):
+        engine.prefill([])
+    with pytest.raises(AssertionError, match="prompt must fit"):
+        engine.prefill(list(range(17)))
+    with pytest.raises(AssertionError, match="pending token"):
+        engine.decode_step()
+
+
+def test_reset_zeroes_history_and_keeps_the_buffers():
+    engine, _ = make_engine([1, 2, 3])
+    engine.generate([5, 6], 2)
+    addresses = [t.data_ptr() for t in (engine.state.kv_k, engine.state.rec_state, engine.state.conv_state)]
+    assert float(engine.state.rec_state.abs().sum()) > 0
+    engine.reset()
+    assert engine.state.position == 0 and engine.pending_token is None
+    assert float(engine.state.rec_state.abs().sum()) == 0 and float(engine.state.conv_state.abs().sum()) == 0
+    assert addresses == [t.data_ptr() for t in (engine.state.kv_k, engine.state.rec_state, engine.state.conv_state)]
+
+
+def test_prefill_starts_a_fresh_request():
+    engine, step = make_engine([1, 2, 3, 4])
+    engine.generate([7, 7, 7], 1)
+    engine.prefill([8])
+    assert engine.state.position == 1 and step.calls[-1] == (8, 0)
