@@ -48,6 +48,7 @@ struct Smem {
     uint64_t* down_bar;                // completes once per layer, when the down-projection rows have landed
     volatile int* abort;
     int* flag;
+    float* rope;           // [2][128] bf16-rounded cos / sin of the step's position, per rotary frequency
 };
 
 extern __shared__ __align__(128) uint8_t mega_smem[];
@@ -71,11 +72,12 @@ QD_DEVINL Smem carve_smem(uint8_t* base) {
     s.down_bar = reinterpret_cast<uint64_t*>(base);   base += 8;
     s.abort = reinterpret_cast<volatile int*>(base);  base += 4;
     s.flag = reinterpret_cast<int*>(base);            base += 4;
+    s.rope = reinterpret_cast<float*>(base);          base += 2 * 128 * 4;
     return s;
 }
 constexpr size_t kSmemBytes = (size_t)NS * kStreamStageBytes + 4096 * 2 + 2048 * 4 + (size_t)kScratchFloats * 4 +
                               2 * kMegaConvRows * kStreamConvWidth * 2 + 3 * sizeof(MegaPhase) + 2 * NS * 8 +
-                              64 * 4 + 8 * 4 + 8 * 4 + 24;
+                              64 * 4 + 8 * 4 + 8 * 4 + 24 + 2 * 128 * 4;
 
 QD_DEVINL float ldcg_bf16(const bf16* p) {
     return __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(p)) << 16);
@@ -714,9 +716,10 @@ QD_DEVINL void gdn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& 
     }
 }
 
-// RMSNorm with gamma = 1 + weight and partial RoPE of one head by one warp; the rotation
-// angles come from a table of bf16-rounded cos / sin shared by all heads
-// (quickdraw/models/qwen.py:76-92).  Feature i = j * 32 + lane; one trip to L2 for the row.
+// RMSNorm with gamma = 1 + weight and partial RoPE of one head by one warp
+// (quickdraw/models/qwen.py:76-92).  Feature i = j * 32 + lane, so with rotary / 2 a multiple
+// of 32 the two features of a rotation pair sit in the same lane and nothing is exchanged.
+// cos_t / sin_t: bf16-rounded table over the rotary / 2 frequencies.
 QD_DEVINL void norm_rope_row(const bf16* __restrict__ src, const bf16* __restrict__ gamma_w, int d, int rotary,
                              float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int lane,
                              float* __restrict__ dst) {
@@ -733,29 +736,22 @@ QD_DEVINL void norm_rope_row(const bf16* __restrict__ src, const bf16* __restric
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)d + eps);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int i = j * 32 + lane;
-        if (i < d) dst[i] = round_bf16((v[j] * inv) * (1.0f + g[j]));
-    }
-    __syncwarp();
-    const int half = rotary / 2;
-    float rotated[8];
+    for (int j = 0; j < 8; ++j) v[j] = round_bf16((v[j] * inv) * (1.0f + g[j]));
+    const int hj = rotary / 64;                 // registers per half of the rotary part
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int i = j * 32 + lane;
-        if (i < rotary) {
-            const int f = i % half;
-            const float partner = i < half ? -dst[i + half] : dst[i - half];
-            rotated[j] = round_bf16(dst[i] * cos_t[f] + partner * sin_t[f]);
+    for (int j = 0; j < 4; ++j) {
+        if (j < hj) {
+            const float c = cos_t[j * 32 + lane], sn = sin_t[j * 32 + lane];
+            const float lo = v[j], hi = v[j + hj];
+            v[j] = round_bf16(lo * c + (-hi) * sn);
+            v[j + hj] = round_bf16(hi * c + lo * sn);
         }
     }
-    __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int i = j * 32 + lane;
-        if (i < rotary) dst[i] = rotated[j];
+        if (i < d) dst[i] = v[j];
     }
-    __syncwarp();
 }
 
 struct AttnSplit { int active, per; };
@@ -768,12 +764,33 @@ QD_DEVINL AttnSplit attn_split(int T, int max_splits) {
     return a;
 }
 
+constexpr int kAttnChunk = 16;                       // positions per pass = consumer warps
+constexpr int kAttnRowBytes = 256 * 2;               // one cache row of a KV head (head_dim 256, bf16)
+constexpr int kAttnBufBytes = kAttnChunk * 2 * kAttnRowBytes;    // K rows then V rows of a chunk
+
+// cache rows [c0, c0 + 16) of the split into a shared-memory buffer (the row of the step's own
+// position is not in the cache yet: it is filled in from the new key / value)
+QD_DEVINL void attn_fetch_chunk(uint8_t* buf, const bf16* k_cache, const bf16* v_cache, int c0, int t1, int position,
+                                int hkv, int kvh, int tid) {
+    for (int p = tid; p < kAttnChunk * 64; p += CT) {
+        const int tl = p >> 6, which = (p >> 5) & 1, off = (p & 31) * 16;
+        const int t = c0 + tl;
+        if (t < t1 && t != position) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>((which ? v_cache : k_cache) + ((size_t)t * hkv + kvh) * 256) + off;
+            cp_async16(buf + (which * kAttnChunk + tl) * kAttnRowBytes + off, src);
+        }
+    }
+}
+
 // Gated GQA decode attention, first half (quickdraw/models/qwen.py:66-116): block = (KV head,
-// context split); warp = (one of eight position lanes, one half of the query heads of the KV
-// head).  Writes the block's softmax partials (unnormalised sum, max, denominator per head).
+// context split).  The split is walked in chunks of sixteen positions staged in shared memory:
+// scores (one warp per position, all query heads of the KV head), softmax update (one warp per
+// head), weighted value sum (one thread per head and four features).  Writes the block's
+// partials: unnormalised sum, running max and denominator per head.
 QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int G = mp.hq / mp.hkv, D = mp.d;
+    const int G = mp.hq / mp.hkv;
+    constexpr int D = 256;
     const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
     const int T = position + 1;
     const AttnSplit cut = attn_split(T, mp.attn_splits);
@@ -782,35 +799,20 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
     const int t0 = split * cut.per, t1 = min(T, t0 + cut.per);
     const bool mine = kvh < mp.hkv;
     float* q_s = reinterpret_cast<float*>(S.xs);            // [G][D]
-    float* k_s = reinterpret_cast<float*>(S.xf);            // [D]
-    float* cos_t = k_s + 256;                               // [rotary / 2]
-    float* sin_t = cos_t + 128;
-    float* red = S.scratch;                                 // [8 position lanes][4 heads][D + 2]
-    float* wgt = red + 8 * 4 * kAttnStride;                 // [4 heads][8 lanes] merge weights
+    float* k_s = reinterpret_cast<float*>(S.xf);            // [D] the new key
+    const float* cos_t = S.rope;                            // [rotary / 2], filled at kernel start
+    const float* sin_t = S.rope + 128;
+    float* sc = k_s + 256;                                  // [8][16] scores of the chunk
+    float* pr = sc + 8 * kAttnChunk;                        // [8][16] softmax numerators
+    float* fix = pr + 8 * kAttnChunk;                       // [8] rescale of the running sums
+    uint8_t* bufs = reinterpret_cast<uint8_t*>(S.scratch);  // two chunk buffers
     const size_t layer_elems = (size_t)mp.st.capacity * mp.hkv * D;
     bf16* k_cache = reinterpret_cast<bf16*>(mp.st.kv_k) + (size_t)ph.state_index * layer_elems;
     bf16* v_cache = reinterpret_cast<bf16*>(mp.st.kv_v) + (size_t)ph.state_index * layer_elems;
-    const int pl = warp >> 1, hh = warp & 1;
-    const int f0 = lane * 8;
-    const bool lane_on = f0 < D;
 
-    // ---- before the grid barrier: the rotation table (position only) and the first cache rows
-    // (rows of earlier positions were written by earlier steps)
-    uint4 kr = make_uint4(0u, 0u, 0u, 0u), vr = kr;
-    if (mine) {
-        const int half = mp.rotary / 2;
-        for (int f = tid; f < half; f += CT) {
-            const float inv_freq = 1.0f / powf(mp.theta, (float)(2 * f) / (float)mp.rotary);
-            const float angle = (float)position * inv_freq;
-            cos_t[f] = round_bf16(cosf(angle));
-            sin_t[f] = round_bf16(sinf(angle));
-        }
-        const int t = t0 + pl;
-        if (t < t1 && t != position && lane_on) {
-            kr = *reinterpret_cast<const uint4*>(k_cache + ((size_t)t * mp.hkv + kvh) * D + f0);
-            vr = *reinterpret_cast<const uint4*>(v_cache + ((size_t)t * mp.hkv + kvh) * D + f0);
-        }
-    }
+    // ---- before the grid barrier: the first chunk (rows of earlier positions were written by
+    // earlier steps)
+    if (mine) attn_fetch_chunk(bufs, k_cache, v_cache, t0, t1, position, mp.hkv, kvh, tid);
     phase_wait(mp, S, pi, tid);
     if (tid == 0) trace_mark(mp, pi, 0);
     if (!mine) return;
@@ -820,6 +822,7 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
                       q_s + warp * D);
     if (owns_new && warp == CW - 1) {
         norm_rope_row(ph.k_new + (size_t)kvh * D, ph.k_norm, D, mp.rotary, mp.eps, cos_t, sin_t, lane, k_s);
+        __syncwarp();
         bf16* krow = k_cache + ((size_t)position * mp.hkv + kvh) * D;
         bf16* vrow = v_cache + ((size_t)position * mp.hkv + kvh) * D;
         for (int i = lane; i < D; i += 32) {
@@ -827,148 +830,158 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
             vrow[i] = __float2bfloat16_rn(ldcg_bf16(ph.v_new + (size_t)kvh * D + i));
         }
     }
-    named_barrier(1, CT);
     QD_MARK(9);
-
-    float m[4], l[4], acc[4][8];
-#pragma unroll
-    for (int h = 0; h < 4; ++h) {
-        m[h] = -INFINITY; l[h] = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
-    }
     const float scale = rsqrtf((float)D);
+    float m_run = -INFINITY, l_run = 0.f;            // warp h < G: running max / denominator of head h
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};             // thread (head tid / 64, features 4 (tid % 64) ..)
+    const int ph_head = tid >> 6, pf = (tid & 63) * 4;
+    int chunk = 0;
 #pragma unroll 1
-    for (int t = t0 + pl; t < t1; t += 8) {
-        float kf[8], vf[8];
-        if (t == position) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                kf[j] = lane_on ? k_s[f0 + j] : 0.f;
-                vf[j] = lane_on ? ldcg_bf16(ph.v_new + (size_t)kvh * D + f0 + j) : 0.f;
+    for (int c0 = t0; c0 < t1; c0 += kAttnChunk, ++chunk) {
+        uint8_t* buf = bufs + (chunk & 1) * kAttnBufBytes;
+        cp_async_wait_all();
+        if (owns_new && position >= c0 && position < c0 + kAttnChunk && warp == CW - 1) {
+            // the step's own row: key from the normalised vector, value from the projection
+            const int tl = position - c0;
+            bf16* kd = reinterpret_cast<bf16*>(buf + tl * kAttnRowBytes);
+            bf16* vd = reinterpret_cast<bf16*>(buf + (kAttnChunk + tl) * kAttnRowBytes);
+            for (int i = lane; i < D; i += 32) {
+                kd[i] = __float2bfloat16_rn(k_s[i]);
+                vd[i] = __float2bfloat16_rn(ldcg_bf16(ph.v_new + (size_t)kvh * D + i));
             }
-        } else {
-            const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
+        }
+        named_barrier(1, CT);
+        if (c0 + kAttnChunk < t1)
+            attn_fetch_chunk(bufs + ((chunk + 1) & 1) * kAttnBufBytes, k_cache, v_cache, c0 + kAttnChunk, t1, position,
+                             mp.hkv, kvh, tid);
+        // scores: warp = position of the chunk
+        {
+            const int t = c0 + warp;
+            const uint4 kr = lds128(buf + warp * kAttnRowBytes + lane * 16);
+            const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w};
+            float kf[8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                kf[2 * j] = __uint_as_float(kw[j] << 16); kf[2 * j + 1] = __uint_as_float(kw[j] & 0xffff0000u);
-                vf[2 * j] = __uint_as_float(vw[j] << 16); vf[2 * j + 1] = __uint_as_float(vw[j] & 0xffff0000u);
+                kf[2 * j] = __uint_as_float(kw[j] << 16);
+                kf[2 * j + 1] = __uint_as_float(kw[j] & 0xffff0000u);
+            }
+#pragma unroll 1
+            for (int h = 0; h < G; ++h) {
+                const float4 qa = *reinterpret_cast<const float4*>(q_s + h * D + lane * 8);
+                const float4 qb = *reinterpret_cast<const float4*>(q_s + h * D + lane * 8 + 4);
+                float dot = qa.x * kf[0];
+                dot += qa.y * kf[1]; dot += qa.z * kf[2]; dot += qa.w * kf[3];
+                dot += qb.x * kf[4]; dot += qb.y * kf[5]; dot += qb.z * kf[6]; dot += qb.w * kf[7];
+                dot = warp_sum(dot) * scale;
+                if (lane == 0) sc[h * kAttnChunk + warp] = t < t1 ? dot : -INFINITY;
             }
         }
-        // the next row of this position lane, in flight during the arithmetic
-        const int tn = t + 8;
-        if (tn < t1 && tn != position && lane_on) {
-            kr = *reinterpret_cast<const uint4*>(k_cache + ((size_t)tn * mp.hkv + kvh) * D + f0);
-            vr = *reinterpret_cast<const uint4*>(v_cache + ((size_t)tn * mp.hkv + kvh) * D + f0);
+        named_barrier(1, CT);
+        // softmax update: warp = head
+        if (warp < G) {
+            const float s_t = lane < kAttnChunk ? sc[warp * kAttnChunk + lane] : -INFINITY;
+            const float nm = fmaxf(m_run, warp_max(s_t));
+            const float p = s_t == -INFINITY ? 0.f : expf(s_t - nm);
+            const float fx = m_run == -INFINITY ? 0.f : expf(m_run - nm);
+            l_run = l_run * fx + warp_sum(p);
+            m_run = nm;
+            if (lane < kAttnChunk) pr[warp * kAttnChunk + lane] = p;
+            if (lane == 0) fix[warp] = fx;
         }
+        named_barrier(1, CT);
+        // weighted values: thread = (head, four features)
+        if (ph_head < G) {
+            const float fx = fix[ph_head];
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
-            const int head = hh * 4 + h;
-            if (head < G) {
-                float dot = 0.f;
-                if (lane_on) {
+            for (int j = 0; j < 4; ++j) acc[j] *= fx;
+            const uint8_t* vb = buf + kAttnChunk * kAttnRowBytes + pf * 2;
+            const int valid = min(kAttnChunk, t1 - c0);      // rows past the split hold stale bytes
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) dot += q_s[head * D + f0 + j] * kf[j];
-                }
-                const float sc = warp_sum(dot) * scale;
-                const float nm = fmaxf(m[h], sc);
-                const float fix = expf(m[h] - nm), pr = expf(sc - nm);
-                l[h] = l[h] * fix + pr;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[h][j] = acc[h][j] * fix + pr * vf[j];
-                m[h] = nm;
+            for (int t = 0; t < kAttnChunk; ++t) {
+                if (t >= valid) break;
+                const float p = pr[ph_head * kAttnChunk + t];
+                const uint2 vv = *reinterpret_cast<const uint2*>(vb + t * kAttnRowBytes);
+                acc[0] += p * __uint_as_float(vv.x << 16);
+                acc[1] += p * __uint_as_float(vv.x & 0xffff0000u);
+                acc[2] += p * __uint_as_float(vv.y << 16);
+                acc[3] += p * __uint_as_float(vv.y & 0xffff0000u);
             }
         }
     }
     QD_MARK(10);
-    // merge the eight position lanes, one half of the heads at a time
     float* block_out = mp.attn_partial + (((size_t)kvh * mp.attn_splits + split) * G) * kAttnStride;
-#pragma unroll 1
-    for (int pass = 0; pass < 2; ++pass) {
-        if (hh == pass) {
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-                float* dst = red + ((size_t)pl * 4 + h) * kAttnStride;
-                if (lane_on) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) dst[f0 + j] = acc[h][j];
-                }
-                if (lane == 0) { dst[256] = m[h]; dst[257] = l[h]; }
-            }
-        }
-        named_barrier(1, CT);
-        if (tid < 32) {               // weight of position lane w for head h, and the head's max / denominator
-            const int h = tid >> 3, w = tid & 7;
-            const float mw = red[((size_t)w * 4 + h) * kAttnStride + 256];
-            float mm = mw;
-            mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 1));
-            mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 2));
-            mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 4));
-            const float wv = mw == -INFINITY ? 0.f : expf(mw - mm);
-            float den = wv * red[((size_t)w * 4 + h) * kAttnStride + 257];
-            den += __shfl_xor_sync(0xffffffffu, den, 1);
-            den += __shfl_xor_sync(0xffffffffu, den, 2);
-            den += __shfl_xor_sync(0xffffffffu, den, 4);
-            wgt[tid] = wv;
-            const int head = pass * 4 + h;
-            if (w == 0 && head < G) {
-                block_out[(size_t)head * kAttnStride + 256] = mm;
-                block_out[(size_t)head * kAttnStride + 257] = den;
-            }
-        }
-        named_barrier(1, CT);
-        for (int idx = tid; idx < 4 * D; idx += CT) {
-            const int h = idx / D, f = idx % D;
-            const int head = pass * 4 + h;
-            if (head >= G) continue;
-            float num = 0.f;
-#pragma unroll
-            for (int w = 0; w < 8; ++w) num += wgt[h * 8 + w] * red[((size_t)w * 4 + h) * kAttnStride + f];
-            block_out[(size_t)head * kAttnStride + f] = num;
-        }
-        named_barrier(1, CT);
+    if (ph_head < G) {
+        float* dst = block_out + (size_t)ph_head * kAttnStride + pf;
+        *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
+        *reinterpret_cast<float2*>(dst + 2) = make_float2(acc[2], acc[3]);
+    }
+    if (warp < G && lane == 0) {
+        block_out[(size_t)warp * kAttnStride + 256] = m_run;
+        block_out[(size_t)warp * kAttnStride + 257] = l_run;
     }
     QD_MARK(11);
 }
 
-// Second half: every block merges the split partials of its share of the output features,
-// normalises and applies the sigmoid gate.  One warp per output feature, lanes over splits.
+// Second half: block = (query head, 32 output features); warp w merges the splits w, w + 16, ...
+// (all its loads in flight at once), warp 0 merges the sixteen results, normalises and applies
+// the sigmoid gate.
 QD_DEVINL void attn_merge_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int G = mp.hq / mp.hkv, D = mp.d;
+    const int G = mp.hq / mp.hkv;
+    constexpr int D = 256;
     const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
     const AttnSplit cut = attn_split(position + 1, mp.attn_splits);
-    const int total = mp.hq * D;
-    const int share = (total + gridDim.x - 1) / gridDim.x;
-    const int o0 = blockIdx.x * share, o1 = min(total, o0 + share);
+    float* part = S.scratch;                  // [16 warps][34]: 32 sums, max, denominator
     phase_wait(mp, S, pi, tid);
     if (tid == 0) trace_mark(mp, pi, 0);
+    const int units = mp.hq * (D / 32);
 #pragma unroll 1
-    for (int o = o0 + warp; o < o1; o += CW) {
-        const int qh = o / D, f = o % D;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+        const int qh = unit / (D / 32), f = (unit % (D / 32)) * 32 + lane;
         const int kvh = qh / G, h = qh % G;
         const float* base = mp.attn_partial + ((size_t)kvh * mp.attn_splits * G + h) * kAttnStride;
-        const float gate_raw = ldcg_bf16(ph.qg + (size_t)qh * 2 * D + D + f);
-        float ms[2], ls[2], as[2];
+        const float gate_raw = warp == 0 ? ldcg_bf16(ph.qg + (size_t)qh * 2 * D + D + f) : 0.f;
+        constexpr int PER = (kMegaAttnSplits + CW - 1) / CW;      // splits per warp at most
+        float ms[PER], ls[PER], as[PER];
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int s = lane + 32 * k;
-            const float* src = base + (size_t)s * G * kAttnStride;
-            const bool on = s < cut.active;
+        for (int k = 0; k < PER; ++k) {
+            const int sp = warp + CW * k;
+            const float* src = base + (size_t)sp * G * kAttnStride;
+            const bool on = sp < cut.active;
             ms[k] = on ? __ldcg(src + 256) : -INFINITY;
             ls[k] = on ? __ldcg(src + 257) : 0.f;
             as[k] = on ? __ldcg(src + f) : 0.f;
         }
-        const float mm = warp_max(fmaxf(ms[0], ms[1]));
-        const float w0 = ms[0] == -INFINITY ? 0.f : expf(ms[0] - mm);
-        const float w1 = ms[1] == -INFINITY ? 0.f : expf(ms[1] - mm);
-        const float num = warp_sum(w0 * as[0] + w1 * as[1]);
-        const float den = warp_sum(w0 * ls[0] + w1 * ls[1]);
-        if (lane == 0) {
-            const float attended = round_bf16(num / den);
-            const float gate = round_bf16(sigmoid_precise(gate_raw));
-            ph.mix_out[o] = __float2bfloat16_rn(attended * gate);
+        float mm = ms[0];
+#pragma unroll
+        for (int k = 1; k < PER; ++k) mm = fmaxf(mm, ms[k]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const float w = ms[k] == -INFINITY ? 0.f : expf(ms[k] - mm);
+            num += w * as[k];
+            den += w * ls[k];
         }
+        part[warp * 34 + lane] = num;
+        if (lane == 0) { part[warp * 34 + 32] = mm; part[warp * 34 + 33] = den; }
+        named_barrier(1, CT);
+        if (warp == 0) {
+            float top = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < CW; ++w) top = fmaxf(top, part[w * 34 + 32]);
+            float n2 = 0.f, d2 = 0.f;
+#pragma unroll
+            for (int w = 0; w < CW; ++w) {
+                const float mw = part[w * 34 + 32];
+                const float wv = mw == -INFINITY ? 0.f : expf(mw - top);
+                n2 += wv * part[w * 34 + lane];
+                d2 += wv * part[w * 34 + 33];
+            }
+            const float attended = round_bf16(n2 / d2);
+            const float gate = round_bf16(sigmoid_precise(gate_raw));
+            ph.mix_out[(size_t)qh * D + f] = __float2bfloat16_rn(attended * gate);
+        }
+        named_barrier(1, CT);
     }
 }
 
@@ -1105,6 +1118,17 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
     if (warp == CW) {
         producer(mp, S, lane);
         return;
+    }
+    // rotation table of this step's position, once for all attention layers
+    // (quickdraw/models/qwen.py:84-88: fp32 angle, cos / sin rounded to bf16)
+    if (mp.rotary > 0) {
+        const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
+        for (int f = tid; f < mp.rotary / 2; f += CT) {
+            const float inv_freq = 1.0f / powf(mp.theta, (float)(2 * f) / (float)mp.rotary);
+            const float angle = (float)position * inv_freq;
+            S.rope[f] = round_bf16(cosf(angle));
+            S.rope[128 + f] = round_bf16(sinf(angle));
+        }
     }
     // first phase parameters
     {

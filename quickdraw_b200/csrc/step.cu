@@ -315,7 +315,7 @@ int mega_phase_count(const qd_model* m) {
 bool mega_shape_ok(const qd_model_config& c, int grid) {
     return fused_shape_ok(c) && c.expert_lo == 0 && c.expert_hi >= c.experts && c.conv_width <= kStreamConvWidth &&
            c.key_dim == 128 && c.value_dim % 32 == 0 && c.value_heads * (c.value_dim / 32) <= grid &&
-           c.head_dim == 256 && c.rotary_dim <= 256 && c.kv_heads >= 1 && c.kv_heads <= grid &&
+           c.head_dim == 256 && c.rotary_dim <= 256 && c.rotary_dim % 64 == 0 && c.kv_heads >= 1 && c.kv_heads <= grid &&
            c.q_heads / c.kv_heads <= 8 && (c.hidden + grid - 1) / grid <= kMegaDownRows &&
            c.topk + 1 <= 9 && c.topk + 1 <= kMegaMaxSeg && c.conv_width <= 4 && grid <= kMaxGrid;
 }
