@@ -49,6 +49,15 @@ int qd_nvfp4_gemv(const void* x, const void* codes, const void* scales, const fl
                   const float* routing_weight, void* y, int rows, int in_features,
                   int group_size, int force_generic, void* stream);
 
+/* matmul(x, proj) for a chunk of tokens (prefill) — quickdraw/kernel/triton/matvec.py:118-163,
+ * NVFP4 branch: y[t, n] = bf16( global * sum_k x[t, k] * bf16(e2m1[n, k] * e4m3 scale) ) on the
+ * tensor cores (tcgen05, accumulator in tensor memory).  x bf16 [tokens, in_features]
+ * contiguous, y bf16 [tokens, out_features]; in_features % 64 == 0, out_features % 8 == 0,
+ * pointers 16-byte aligned.  status: device word, bit 0 is set if a bounded wait ran out. */
+int qd_nvfp4_matmul(const void* x, const void* codes, const void* scales, const float* global, void* y,
+                    int tokens, int out_features, int in_features, int group_size,
+                    unsigned int* status, void* stream);
+
 /* expert_gemv(x, proj, ids, weights=None) — quickdraw/kernel/cute/matvec.py:152-154,
  * quickdraw/kernel/triton/matvec.py:84-99.  Bank [E, rows, in/2]; y [slots, rows];
  * x [in] or, with per_slot_input, [slots, in]; global fp32 scalar or [E]. */

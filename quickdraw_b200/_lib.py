@@ -49,6 +49,7 @@ SIGNATURES = {
     "qd_stream_blocks_per_sm": [I],
     "qd_stream_trace": [P, I],
     "qd_nvfp4_gemv_bank": [P, P, P, P, P, I, I, I, I, P],
+    "qd_nvfp4_matmul": [P, P, P, P, P, I, I, I, I, P, P],
 }
 
 LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes"}

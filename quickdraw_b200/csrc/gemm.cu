@@ -1,0 +1,267 @@
+// Prefill / batched projection: Y[T, N] = X[T, K] . W[N, K]^T with NVFP4 weights on the 5th
+// generation tensor cores (tcgen05.mma, accumulator in tensor memory).
+//
+// Arithmetic (reference: quickdraw/kernel/triton/matvec.py:118-163, the prefill path of the
+// projections): every weight is expanded to bf16(e2m1 * e4m3 block scale) - exact, the product
+// has at most six significant bits - multiplied with the bf16 activations on the tensor cores
+// with fp32 accumulation, the fp32 global scale multiplies the finished sum, one bf16 rounding.
+//
+// One block computes a 128-token x 256-row tile.  Roles:
+//   warps 1..8  producers: 16-byte global loads of activations and weight codes into registers
+//               (one K step ahead), expansion to bf16, 16-byte stores into the shared-memory
+//               stage in the tensor core's K-major core-matrix layout (8 rows x 16 bytes per
+//               core matrix, no swizzle); warps 1..4 also run the epilogue
+//   warp 0      allocates 256 columns of tensor memory, issues four 128x256x16 MMAs per stage
+//               and commits them to the stage's "empty" barrier
+// Stages: 4 x (16 KB activations + 32 KB weights) guarded by full / empty mbarriers.  Every wait
+// is bounded; a wait that runs out sets the status word, the block frees its tensor memory and
+// leaves.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTileM = 128;                 // tokens per tile (tensor memory lanes)
+constexpr int kTileN = 256;                 // weight rows per tile (tensor memory columns)
+constexpr int kTileK = 64;                  // inputs per stage
+constexpr int kStages = 4;
+constexpr int kProducerWarps = 8;
+constexpr int kThreads = (1 + kProducerWarps) * 32;
+constexpr int kABytes = kTileM * kTileK * 2;          // 16 KB
+constexpr int kBBytes = kTileN * kTileK * 2;          // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 256;
+
+struct GemmParams {
+    const bf16* x; const uint8_t* codes; const uint8_t* scales; const float* global; bf16* y;
+    int tokens, out_features, in_features;
+    unsigned int* status;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------
+QD_DEVINL void tmem_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+}
+QD_DEVINL void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+QD_DEVINL void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+QD_DEVINL void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+QD_DEVINL void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+QD_DEVINL void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+QD_DEVINL void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+QD_DEVINL void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 lanes x 32 columns of fp32: thread l of the warp gets lane (quadrant * 32 + l)
+QD_DEVINL void tmem_load32(uint32_t addr, uint32_t (&v)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(addr) : "memory");
+}
+QD_DEVINL void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrix = 8 rows x 16 bytes stored
+// as 128 contiguous bytes; `lbo` = bytes between the two core matrices an MMA reads along K,
+// `sbo` = bytes between 8-row groups.  Bits: [0,14) address >> 4, [16,30) lbo >> 4, [32,46)
+// sbo >> 4, [46,48) descriptor version 1, [61,64) layout type 0.
+QD_DEVINL uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
+}
+// Instruction descriptor: fp32 accumulator (bits [4,6) = 1), bf16 A and B (bits [7,10) and
+// [10,13) = 1), both K-major (bits 15, 16 = 0), N >> 3 at [17,23), M >> 4 at [24,29).
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileN >> 3) << 17) |
+                                ((uint32_t)(kTileM >> 4) << 24);
+
+// byte offset of the 16-byte piece (row, 8-input group kg) inside a stage tile
+QD_DEVINL uint32_t core_offset(int row, int kg) { return (uint32_t)(((row >> 3) * (kTileK / 8) + kg) * 128 + (row & 7) * 16); }
+
+// eight E2M1 codes (one 32-bit word, low nibble first) times an fp32 block scale -> eight bf16
+QD_DEVINL uint4 expand8(uint32_t word, float scale) {
+    uint32_t out[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const uint32_t byte = (word >> (8 * b)) & 0xffu;
+        const __nv_bfloat162 p = __floats2bfloat162_rn(e2m1_to_float(byte & 15u) * scale, e2m1_to_float(byte >> 4) * scale);
+        out[b] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+struct StageRegs {
+    uint4 xa[4];           // four 16-byte pieces of activations
+    uint4 wc[2];           // two 16-byte pieces of codes (32 weights each)
+    uint16_t ws[2];        // their two block scales each
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* empty = full + kStages;
+    uint64_t* done = empty + kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t0 = blockIdx.x * kTileM, n0 = blockIdx.y * kTileN;
+    const int K = p.in_features, nk = K / kTileK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(full + s, kProducerWarps); mbar_init(empty + s, 1); }
+        mbar_init(done, 1);
+        mbar_fence_init();
+        *failed = 0;
+    }
+    if (warp == 0) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            bool ok = true;
+            for (int s = 0; s < nk && ok; ++s) {
+                const int st = s % kStages;
+                ok = mbar_wait(full + st, (s / kStages) & 1, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a = smem_u32(smem + st * kStageBytes), b = a + kABytes;
+#pragma unroll
+                for (int j = 0; j < kTileK / 16; ++j)
+                    umma_bf16(tmem, smem_desc(a + j * 256, 128, (kTileK / 8) * 128),
+                              smem_desc(b + j * 256, 128, (kTileK / 8) * 128), kInstrDesc, (s | j) ? 1u : 0u);
+                umma_commit(empty + st);          // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(done);
+            else *failed = 1;
+        }
+    } else {
+        // ------------------------------------------------------------------- producers
+        const int pt = tid - 32;                       // 0 .. 255
+        StageRegs cur, nxt;
+        auto fetch = [&](int s, StageRegs& r) {
+            const int k0 = s * kTileK;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {              // activations: piece = (token, 8-input group)
+                const int piece = pt + i * 256, row = piece >> 3, kg = piece & 7;
+                const int t = t0 + row;
+                r.xa[i] = t < p.tokens ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * K + k0 + kg * 8))
+                                       : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {              // weights: piece = (row, 32-input half of the stage)
+                const int piece = pt + i * 256, row = piece >> 1, half = piece & 1;
+                const int n = n0 + row;
+                if (n < p.out_features) {
+                    r.wc[i] = __ldg(reinterpret_cast<const uint4*>(p.codes + (size_t)n * (K / 2) + (k0 + half * 32) / 2));
+                    r.ws[i] = __ldg(reinterpret_cast<const uint16_t*>(p.scales + (size_t)n * (K / 16) + (k0 + half * 32) / 16));
+                } else {
+                    r.wc[i] = make_uint4(0u, 0u, 0u, 0u);
+                    r.ws[i] = 0;
+                }
+            }
+        };
+        auto store = [&](int st, const StageRegs& r) {
+            uint8_t* a = smem + st * kStageBytes;
+            uint8_t* b = a + kABytes;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int piece = pt + i * 256;
+                *reinterpret_cast<uint4*>(a + core_offset(piece >> 3, piece & 7)) = r.xa[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int piece = pt + i * 256, row = piece >> 1, half = piece & 1;
+                const float2 sc = e4m3x2_to_float2(r.ws[i]);
+                const uint32_t words[4] = {r.wc[i].x, r.wc[i].y, r.wc[i].z, r.wc[i].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    *reinterpret_cast<uint4*>(b + core_offset(row, half * 4 + q)) = expand8(words[q], q < 2 ? sc.x : sc.y);
+            }
+        };
+        bool ok = true;
+        fetch(0, cur);
+        for (int s = 0; s < nk && ok; ++s) {
+            if (s + 1 < nk) fetch(s + 1, nxt);
+            const int st = s % kStages;
+            if (s >= kStages) ok = mbar_wait(empty + st, ((s / kStages) - 1) & 1, p.status);
+            if (!ok) break;
+            store(st, cur);
+            fence_async_proxy();          // the tensor core reads shared memory through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full + st);
+            cur = nxt;
+        }
+        // --------------------------------------------------------------------- epilogue
+        if (warp <= 4) {
+            ok = ok && mbar_wait(done, 0, p.status) && !*failed;
+            tc_fence_after();
+            if (ok) {
+                const int quadrant = warp & 3;                 // the lanes this warp may read
+                const int t = t0 + quadrant * 32 + lane;
+                const float g = *p.global;
+#pragma unroll 1
+                for (int c = 0; c < kTileN; c += 32) {
+                    uint32_t v[32];
+                    tmem_load32(tmem + ((uint32_t)(quadrant * 32) << 16) + c, v);
+                    tmem_load_wait();
+                    if (t < p.tokens) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (n0 + c + j < p.out_features) {
+                                uint32_t o[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * q]) * g,
+                                                                                  __uint_as_float(v[j + 2 * q + 1]) * g);
+                                    o[q] = *reinterpret_cast<const uint32_t*>(&h);
+                                }
+                                *reinterpret_cast<uint4*>(p.y + (size_t)t * p.out_features + n0 + c + j) = make_uint4(o[0], o[1], o[2], o[3]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+
+// matmul(x, proj) for a 2-D x — quickdraw/kernel/triton/matvec.py:153-163 (NVFP4 branch).
+extern "C" int qd_nvfp4_matmul(const void* x, const void* codes, const void* scales, const float* global, void* y,
+                               int tokens, int out_features, int in_features, int group_size,
+                               unsigned int* status, void* stream) {
+    QD_CHECK_ARG(x && codes && scales && global && y && tokens > 0 && out_features > 0 && in_features > 0);
+    if (group_size != 16 || in_features % kTileK != 0 || out_features % 8 != 0) return QD_ERR_UNSUPPORTED;
+    const uintptr_t align = (uintptr_t)x | (uintptr_t)codes | (uintptr_t)y;
+    if (align & 15u) return QD_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)kStages * kStageBytes + (2 * kStages + 1) * 8 + 16;
+    static bool configured[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return QD_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    GemmParams p;
+    p.x = (const bf16*)x; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
+    p.y = (bf16*)y; p.tokens = tokens; p.out_features = out_features; p.in_features = in_features; p.status = status;
+    dim3 grid((tokens + kTileM - 1) / kTileM, (out_features + kTileN - 1) / kTileN);
+    return qd_launch(nvfp4_gemm_kernel, grid, dim3(kThreads), smem, (cudaStream_t)stream, false, p);
+}

@@ -85,6 +85,9 @@ def nvfp4_gemv(x: torch.Tensor, proj, *, routing_weight=None, force_generic: boo
     if isinstance(proj, torch.Tensor):
         assert routing_weight is None
         return bf16_gemv(x, proj)
+    if x.ndim == 2:            # a chunk of tokens (prefill): the tensor-core path
+        assert routing_weight is None
+        return matmul(x, proj)
     assert x.ndim == 1 and proj.weight.ndim == 2
     _check_fp4(x, proj)
     assert proj.weight_scale_2.numel() == 1
@@ -94,6 +97,32 @@ def nvfp4_gemv(x: torch.Tensor, proj, *, routing_weight=None, force_generic: boo
          ptr(routing), ptr(out), proj.out_features, proj.in_features, proj.group_size,
          int(force_generic), stream_of(x))
     return out
+
+
+_matmul_status: dict = {}
+
+
+def matmul(x: torch.Tensor, proj: NVFP4Linear) -> torch.Tensor:
+    """bf16 [tokens, in] times a packed NVFP4 matrix on the tensor cores (prefill projection;
+    reference: quickdraw/kernel/triton/matvec.py:153-163): weights expanded to
+    bf16(code * block scale), fp32 accumulation, global scale last, bf16 output [tokens, out]."""
+    assert isinstance(proj, NVFP4Linear) and x.ndim == 2 and proj.weight.ndim == 2
+    assert x.is_cuda and x.dtype == BF16 and x.is_contiguous() and x.shape[1] == proj.in_features
+    assert proj.weight.is_contiguous() and proj.weight_scale.is_contiguous() and proj.group_size == 16
+    assert proj.weight_scale_2.numel() == 1 and proj.in_features % 64 == 0 and proj.out_features % 8 == 0
+    status = _matmul_status.get(x.device)
+    if status is None:
+        status = _matmul_status[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    out = torch.empty((x.shape[0], proj.out_features), dtype=BF16, device=x.device)
+    call("qd_nvfp4_matmul", ptr(x), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2),
+         ptr(out), x.shape[0], proj.out_features, proj.in_features, proj.group_size, ptr(status), stream_of(x))
+    return out
+
+
+def matmul_status(device) -> int:
+    """Status word of the tensor-core matmul on ``device`` (0 = clean; bit 0 = a bounded wait ran out)."""
+    status = _matmul_status.get(torch.device(device))
+    return 0 if status is None else int(status.item())
 
 
 def expert_gemv(x, proj: NVFP4Linear, ids, weights=None, *, force_generic: bool = False):

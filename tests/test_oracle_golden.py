@@ -160,3 +160,14 @@ def test_generation_tokens(reference_outputs):
     assert tokens == gen["tokens"]
     torch.testing.assert_close(state.rec_state, gen["rec_after"], rtol=1e-3, atol=1e-5)
     assert O.rel_l2(state.kv_k, gen["k_after"]) < 1e-2
+
+
+def test_chunk_matmul_equals_token_loop():
+    """The prefill form of a projection against the single-token function it is pinned to."""
+    from quickdraw_b200 import synthetic
+    src = synthetic.Source(5, "cpu")
+    proj = src.nvfp4("w", 96, 256, global_scale=1.25)
+    x = src.normal("x", 9, 256)
+    chunk = O.nvfp4_matmul(x, proj)
+    rows = torch.stack([O.nvfp4_gemv(x[t], proj) for t in range(9)])
+    torch.testing.assert_close(chunk.float(), rows.float(), rtol=0.025, atol=0.003)
