@@ -13,7 +13,7 @@
 //               core matrix, no swizzle); warps 1..4 also run the epilogue
 //   warp 0      allocates 256 columns of tensor memory, issues four 128x256x16 MMAs per stage
 //               and commits them to the stage's "empty" barrier
-// Stages: 4 x (16 KB activations + 32 KB weights) guarded by full / empty mbarriers.  Every wait
+// Stages: 4 x (18 KB activations + 36 KB weights) guarded by full / empty mbarriers.  Every wait
 // is bounded; a wait that runs out sets the status word, the block frees its tensor memory and
 // leaves.
 #include "common.cuh"
@@ -26,8 +26,11 @@ constexpr int kTileK = 64;                  // inputs per stage
 constexpr int kStages = 4;
 constexpr int kProducerWarps = 8;
 constexpr int kThreads = (1 + kProducerWarps) * 32;
-constexpr int kABytes = kTileM * kTileK * 2;          // 16 KB
-constexpr int kBBytes = kTileN * kTileK * 2;          // 32 KB
+constexpr int kCorePitch = 144;             // bytes from one 128-byte core matrix to the next along K: the
+                                            // 16 bytes of padding spread a warp's stores over all banks
+constexpr int kGroupPitch = (kTileK / 8) * kCorePitch;      // bytes between 8-row groups
+constexpr int kABytes = (kTileM / 8) * kGroupPitch;         // 18 KB
+constexpr int kBBytes = (kTileN / 8) * kGroupPitch;         // 36 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 256;
 
@@ -83,15 +86,20 @@ constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)
                                 ((uint32_t)(kTileM >> 4) << 24);
 
 // byte offset of the 16-byte piece (row, 8-input group kg) inside a stage tile
-QD_DEVINL uint32_t core_offset(int row, int kg) { return (uint32_t)(((row >> 3) * (kTileK / 8) + kg) * 128 + (row & 7) * 16); }
+QD_DEVINL uint32_t core_offset(int row, int kg) { return (uint32_t)((row >> 3) * kGroupPitch + kg * kCorePitch + (row & 7) * 16); }
 
 // eight E2M1 codes (one 32-bit word, low nibble first) times an fp32 block scale -> eight bf16
+// (hardware convert to f16 pairs; code * scale has at most six significant bits and stays inside
+// the f16 range for every E4M3 scale, so the f16 product and the bf16 conversion are exact)
 QD_DEVINL uint4 expand8(uint32_t word, float scale) {
-    uint32_t out[4];
+    uint32_t h2[4], out[4];
+    e2m1x8_to_f16x2(word, h2);
+    const __half2 s2 = __float2half2_rn(scale);
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-        const uint32_t byte = (word >> (8 * b)) & 0xffu;
-        const __nv_bfloat162 p = __floats2bfloat162_rn(e2m1_to_float(byte & 15u) * scale, e2m1_to_float(byte >> 4) * scale);
+        const __half2 prod = __hmul2(*reinterpret_cast<const __half2*>(&h2[b]), s2);
+        const float2 f = __half22float2(prod);
+        const __nv_bfloat162 p = __floats2bfloat162_rn(f.x, f.y);
         out[b] = *reinterpret_cast<const uint32_t*>(&p);
     }
     return make_uint4(out[0], out[1], out[2], out[3]);
@@ -139,8 +147,8 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
                 const uint32_t a = smem_u32(smem + st * kStageBytes), b = a + kABytes;
 #pragma unroll
                 for (int j = 0; j < kTileK / 16; ++j)
-                    umma_bf16(tmem, smem_desc(a + j * 256, 128, (kTileK / 8) * 128),
-                              smem_desc(b + j * 256, 128, (kTileK / 8) * 128), kInstrDesc, (s | j) ? 1u : 0u);
+                    umma_bf16(tmem, smem_desc(a + j * 2 * kCorePitch, kCorePitch, kGroupPitch),
+                              smem_desc(b + j * 2 * kCorePitch, kCorePitch, kGroupPitch), kInstrDesc, (s | j) ? 1u : 0u);
                 umma_commit(empty + st);          // the stage is free once these MMAs have read it
             }
             if (ok) umma_commit(done);
