@@ -6,24 +6,25 @@
 // has at most six significant bits - multiplied with the bf16 activations on the tensor cores
 // with fp32 accumulation, the fp32 global scale multiplies the finished sum, one bf16 rounding.
 //
-// One block computes a 128-token x 256-row tile.  Roles:
+// One block computes a 256-token x 256-row tile as two 128-token accumulators that share every
+// expanded weight stage.  Roles:
 //   warps 1..8  producers: 16-byte global loads of activations and weight codes into registers
 //               (one K step ahead), expansion to bf16, 16-byte stores into the shared-memory
 //               stage in the tensor core's K-major core-matrix layout (8 rows x 16 bytes per
 //               core matrix, no swizzle); warps 1..4 also run the epilogue
-//   warp 0      allocates 256 columns of tensor memory, issues four 128x256x16 MMAs per stage
-//               and commits them to the stage's "empty" barrier
-// Stages: 4 x (18 KB activations + 36 KB weights) guarded by full / empty mbarriers.  Every wait
+//   warp 0      allocates all 512 columns of tensor memory, issues 2 x 4 MMAs of 128x256x16 per
+//               stage and commits them to the stage's "empty" barrier
+// Stages: 3 x (36 KB activations + 36 KB weights) guarded by full / empty mbarriers.  Every wait
 // is bounded; a wait that runs out sets the status word, the block frees its tensor memory and
 // leaves.
 #include "common.cuh"
 
 namespace {
 
-constexpr int kTileM = 128;                 // tokens per tile (tensor memory lanes)
+constexpr int kTileM = 256;                 // tokens per tile: two halves of 128 (tensor memory lanes)
 constexpr int kTileN = 256;                 // weight rows per tile (tensor memory columns)
 constexpr int kTileK = 64;                  // inputs per stage
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kProducerWarps = 8;
 constexpr int kThreads = (1 + kProducerWarps) * 32;
 constexpr int kCorePitch = 144;             // bytes from one 128-byte core matrix to the next along K: the
@@ -32,7 +33,7 @@ constexpr int kGroupPitch = (kTileK / 8) * kCorePitch;      // bytes between 8-r
 constexpr int kABytes = (kTileM / 8) * kGroupPitch;         // 18 KB
 constexpr int kBBytes = (kTileN / 8) * kGroupPitch;         // 36 KB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;               // one 128 x 256 fp32 accumulator per token half
 
 struct GemmParams {
     const bf16* x; const uint8_t* codes; const uint8_t* scales; const float* global; bf16* y;
@@ -83,7 +84,7 @@ QD_DEVINL uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
 // Instruction descriptor: fp32 accumulator (bits [4,6) = 1), bf16 A and B (bits [7,10) and
 // [10,13) = 1), both K-major (bits 15, 16 = 0), N >> 3 at [17,23), M >> 4 at [24,29).
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileN >> 3) << 17) |
-                                ((uint32_t)(kTileM >> 4) << 24);
+                                ((uint32_t)(128 >> 4) << 24);
 
 // byte offset of the 16-byte piece (row, 8-input group kg) inside a stage tile
 QD_DEVINL uint32_t core_offset(int row, int kg) { return (uint32_t)((row >> 3) * kGroupPitch + kg * kCorePitch + (row & 7) * 16); }
@@ -106,7 +107,7 @@ QD_DEVINL uint4 expand8(uint32_t word, float scale) {
 }
 
 struct StageRegs {
-    uint4 xa[4];           // four 16-byte pieces of activations
+    uint4 xa[8];           // eight 16-byte pieces of activations
     uint4 wc[2];           // two 16-byte pieces of codes (32 weights each)
     uint16_t ws[2];        // their two block scales each
 };
@@ -146,9 +147,11 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
                 tc_fence_after();
                 const uint32_t a = smem_u32(smem + st * kStageBytes), b = a + kABytes;
 #pragma unroll
-                for (int j = 0; j < kTileK / 16; ++j)
-                    umma_bf16(tmem, smem_desc(a + j * 2 * kCorePitch, kCorePitch, kGroupPitch),
-                              smem_desc(b + j * 2 * kCorePitch, kCorePitch, kGroupPitch), kInstrDesc, (s | j) ? 1u : 0u);
+                for (int h = 0; h < kTileM / 128; ++h)
+#pragma unroll
+                    for (int j = 0; j < kTileK / 16; ++j)
+                        umma_bf16(tmem + h * kTileN, smem_desc(a + h * (kABytes / 2) + j * 2 * kCorePitch, kCorePitch, kGroupPitch),
+                                  smem_desc(b + j * 2 * kCorePitch, kCorePitch, kGroupPitch), kInstrDesc, (s | j) ? 1u : 0u);
                 umma_commit(empty + st);          // the stage is free once these MMAs have read it
             }
             if (ok) umma_commit(done);
@@ -161,7 +164,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
         auto fetch = [&](int s, StageRegs& r) {
             const int k0 = s * kTileK;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {              // activations: piece = (token, 8-input group)
+            for (int i = 0; i < 8; ++i) {              // activations: piece = (token, 8-input group)
                 const int piece = pt + i * 256, row = piece >> 3, kg = piece & 7;
                 const int t = t0 + row;
                 r.xa[i] = t < p.tokens ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * K + k0 + kg * 8))
@@ -184,7 +187,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
             uint8_t* a = smem + st * kStageBytes;
             uint8_t* b = a + kABytes;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < 8; ++i) {
                 const int piece = pt + i * 256;
                 *reinterpret_cast<uint4*>(a + core_offset(piece >> 3, piece & 7)) = r.xa[i];
             }
@@ -217,25 +220,28 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
             tc_fence_after();
             if (ok) {
                 const int quadrant = warp & 3;                 // the lanes this warp may read
-                const int t = t0 + quadrant * 32 + lane;
                 const float g = *p.global;
 #pragma unroll 1
-                for (int c = 0; c < kTileN; c += 32) {
-                    uint32_t v[32];
-                    tmem_load32(tmem + ((uint32_t)(quadrant * 32) << 16) + c, v);
-                    tmem_load_wait();
-                    if (t < p.tokens) {
+                for (int h = 0; h < kTileM / 128; ++h) {
+                    const int t = t0 + h * 128 + quadrant * 32 + lane;
+#pragma unroll 1
+                    for (int c = 0; c < kTileN; c += 32) {
+                        uint32_t v[32];
+                        tmem_load32(tmem + ((uint32_t)(quadrant * 32) << 16) + h * kTileN + c, v);
+                        tmem_load_wait();
+                        if (t < p.tokens) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            if (n0 + c + j < p.out_features) {
-                                uint32_t o[4];
+                            for (int j = 0; j < 32; j += 8) {
+                                if (n0 + c + j < p.out_features) {
+                                    uint32_t o[4];
 #pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * q]) * g,
-                                                                                  __uint_as_float(v[j + 2 * q + 1]) * g);
-                                    o[q] = *reinterpret_cast<const uint32_t*>(&h);
+                                    for (int q = 0; q < 4; ++q) {
+                                        const __nv_bfloat162 hv = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * q]) * g,
+                                                                                       __uint_as_float(v[j + 2 * q + 1]) * g);
+                                        o[q] = *reinterpret_cast<const uint32_t*>(&hv);
+                                    }
+                                    *reinterpret_cast<uint4*>(p.y + (size_t)t * p.out_features + n0 + c + j) = make_uint4(o[0], o[1], o[2], o[3]);
                                 }
-                                *reinterpret_cast<uint4*>(p.y + (size_t)t * p.out_features + n0 + c + j) = make_uint4(o[0], o[1], o[2], o[3]);
                             }
                         }
                     }
