@@ -57,6 +57,16 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s of a cuBLAS GEMM timed alone on this pool (burst figure)."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        if "bf16_tflops" in data:
+            return float(data["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
 def bytes_per_token(cfg, position: int) -> int:
     """Algorithmic HBM bytes of one decode token: every weight the token touches once
     (selected experts only), recurrent/conv state read and written, KV history read."""
@@ -230,6 +240,28 @@ def matvec_roofline(device, rows=131072, width=2048, mats=2, reps=10):
     return units * CONFIG1_BYTES / per_launch_s / 1e9, per_launch_s, units
 
 
+def prefill_gemm_roofline(device, tokens=8192, rows=8192, width=2048, reps=10):
+    """The prefill projection on the tensor cores (tcgen05): an 8192-token chunk through the
+    largest projection shape of the model ([8192, 2048], the DeltaNet qkv / attention q
+    projection), NVFP4 weights expanded to bf16 on the fly."""
+    from quickdraw_b200 import kernels, synthetic
+    src = synthetic.Source(2, device)
+    proj = src.nvfp4("prefill.w", rows, width)
+    x = src.normal("prefill.x", tokens, width)
+    for _ in range(3):
+        kernels.matmul(x, proj)
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        kernels.matmul(x, proj)
+    e1.record()
+    torch.cuda.synchronize(device)
+    assert kernels.matmul_status(device) == 0
+    per_launch_s = e0.elapsed_time(e1) * 1e-3 / reps
+    return 2.0 * tokens * rows * width / per_launch_s / 1e12, per_launch_s
+
+
 def run_gpu(args):
     rank, local, world = dist_env()
     torch.cuda.set_device(local)
@@ -294,6 +326,8 @@ def run_gpu(args):
         mv_gbs, mv_launch_s, mv_units = matvec_roofline(device, rows=args.matvec_rows)
     else:
         mv_gbs, mv_launch_s, mv_units = matvec_roofline(device)
+    gemm_tflops, gemm_launch_s = prefill_gemm_roofline(device)
+    tensor_peak, tensor_peak_kind = measured_tensor_peak()
     position = args.prompt + args.warmup + args.steps // 2
     token_bytes = bytes_per_token(cfg, position)
     tok_s = args.steps / (device_ms * 1e-3)
@@ -323,6 +357,10 @@ def run_gpu(args):
         "matvec_roofline": {"kernel": "stream_kernel (NVFP4 matvec, %d x [1024,2048] per launch, 2 matrices alternating)" % mv_units,
                             "achieved": mv_gbs, "peak": peak, "unit": "GB/s", "frac": mv_gbs / peak,
                             "launch_us": mv_launch_s * 1e6, "bytes_per_launch": mv_units * CONFIG1_BYTES},
+        "prefill_gemm_roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_kernel (tcgen05, 8192 tokens x [8192, 2048])",
+                                  "achieved": gemm_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
+                                  "frac": gemm_tflops / tensor_peak, "peak_source": f"{tensor_peak_kind} cuBLAS bf16",
+                                  "launch_us": gemm_launch_s * 1e6},
         "cpu_baseline": {"value": 1.0 / per_token_cpu, "unit": "tok/s", "cores": threads, "kind": "port",
                          "sample": "one 4-layer group and the LM head at position 640, group time x12 + head time"},
     }
