@@ -230,6 +230,52 @@ QD_DEVINL void produce_down(const MegaParams& mp, const MegaPhase& ph, const Sme
     }
 }
 
+struct AttnSplit { int active, per; };
+// How the context [0, T) is cut into splits of `per` positions, one block per (KV head, split).
+QD_DEVINL AttnSplit attn_split(int T, int max_splits) {
+    AttnSplit a;
+    const int s = min(max_splits, T);
+    a.per = (T + s - 1) / s;
+    a.active = (T + a.per - 1) / a.per;
+    return a;
+}
+
+constexpr int kAttnChunk = 16;                       // positions per pass = consumer warps
+constexpr int kAttnRowBytes = 256 * 2;               // one cache row of a KV head (head_dim 256, bf16)
+
+// Attention: the cache rows of this block's context split, sixteen positions per ring stage (K rows
+// then V rows, one 512-byte bulk copy each).  The row of the step's own position is not in
+// the cache yet; the consumers fill it in.  Rows of earlier positions were written by earlier
+// steps, so these copies may run ahead of the grid barrier like any weight.
+QD_DEVINL bool produce_attn(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it) {
+    const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
+    const int T = position + 1;
+    const AttnSplit cut = attn_split(T, mp.attn_splits);
+    const int kvh = blockIdx.x / cut.active, split = blockIdx.x % cut.active;
+    if (kvh >= mp.hkv) return true;
+    const int t0 = split * cut.per, t1 = min(T, t0 + cut.per);
+    const size_t layer_elems = (size_t)mp.st.capacity * mp.hkv * 256;
+    const uint8_t* k_cache = reinterpret_cast<const uint8_t*>(reinterpret_cast<const bf16*>(mp.st.kv_k) + (size_t)ph.state_index * layer_elems);
+    const uint8_t* v_cache = reinterpret_cast<const uint8_t*>(reinterpret_cast<const bf16*>(mp.st.kv_v) + (size_t)ph.state_index * layer_elems);
+#pragma unroll 1
+    for (int c0 = t0; c0 < t1; c0 += kAttnChunk, ++it) {
+        const int st = it % NS;
+        if (*S.abort || !mbar_wait(S.empty + st, ((it / NS) & 1) ^ 1, mp.status)) return false;
+        uint8_t* dst = S.stages + (size_t)st * kStreamStageBytes;
+        int rows = 0;
+        for (int tl = 0; tl < kAttnChunk; ++tl) rows += (c0 + tl < t1 && c0 + tl != position) ? 1 : 0;
+        mbar_expect_tx(S.full + st, (uint32_t)rows * 2 * kAttnRowBytes);
+        for (int tl = 0; tl < kAttnChunk; ++tl) {
+            const int t = c0 + tl;
+            if (t >= t1 || t == position) continue;
+            const size_t off = ((size_t)t * mp.hkv + kvh) * kAttnRowBytes;
+            bulk_load(dst + tl * kAttnRowBytes, k_cache + off, kAttnRowBytes, S.full + st);
+            bulk_load(dst + (kAttnChunk + tl) * kAttnRowBytes, v_cache + off, kAttnRowBytes, S.full + st);
+        }
+    }
+    return true;
+}
+
 QD_DEVINL void producer(const MegaParams& mp, const Smem& S, int lane) {
     int it = 0;
     bool ok = true;
@@ -252,6 +298,9 @@ QD_DEVINL void producer(const MegaParams& mp, const Smem& S, int lane) {
                 if (ok) produce_down(mp, ph, S);
             }
             trace_mark(mp, pi, 5);
+            if (!ok) give_up(mp, S);
+        } else if (lane == 0 && ph.kind == MK_ATTN) {
+            ok = produce_attn(mp, ph, S, it);
             if (!ok) give_up(mp, S);
         }
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
@@ -754,40 +803,12 @@ QD_DEVINL void norm_rope_row(const bf16* __restrict__ src, const bf16* __restric
     }
 }
 
-struct AttnSplit { int active, per; };
-// How the context [0, T) is cut into splits of `per` positions, one block per (KV head, split).
-QD_DEVINL AttnSplit attn_split(int T, int max_splits) {
-    AttnSplit a;
-    const int s = min(max_splits, T);
-    a.per = (T + s - 1) / s;
-    a.active = (T + a.per - 1) / a.per;
-    return a;
-}
-
-constexpr int kAttnChunk = 16;                       // positions per pass = consumer warps
-constexpr int kAttnRowBytes = 256 * 2;               // one cache row of a KV head (head_dim 256, bf16)
-constexpr int kAttnBufBytes = kAttnChunk * 2 * kAttnRowBytes;    // K rows then V rows of a chunk
-
-// cache rows [c0, c0 + 16) of the split into a shared-memory buffer (the row of the step's own
-// position is not in the cache yet: it is filled in from the new key / value)
-QD_DEVINL void attn_fetch_chunk(uint8_t* buf, const bf16* k_cache, const bf16* v_cache, int c0, int t1, int position,
-                                int hkv, int kvh, int tid) {
-    for (int p = tid; p < kAttnChunk * 64; p += CT) {
-        const int tl = p >> 6, which = (p >> 5) & 1, off = (p & 31) * 16;
-        const int t = c0 + tl;
-        if (t < t1 && t != position) {
-            const uint8_t* src = reinterpret_cast<const uint8_t*>((which ? v_cache : k_cache) + ((size_t)t * hkv + kvh) * 256) + off;
-            cp_async16(buf + (which * kAttnChunk + tl) * kAttnRowBytes + off, src);
-        }
-    }
-}
-
 // Gated GQA decode attention, first half (quickdraw/models/qwen.py:66-116): block = (KV head,
 // context split).  The split is walked in chunks of sixteen positions staged in shared memory:
 // scores (one warp per position, all query heads of the KV head), softmax update (one warp per
 // head), weighted value sum (one thread per head and four features).  Writes the block's
 // partials: unnormalised sum, running max and denominator per head.
-QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
+QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi, int& it) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = mp.hq / mp.hkv;
     constexpr int D = 256;
@@ -805,14 +826,10 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
     float* sc = k_s + 256;                                  // [8][16] scores of the chunk
     float* pr = sc + 8 * kAttnChunk;                        // [8][16] softmax numerators
     float* fix = pr + 8 * kAttnChunk;                       // [8] rescale of the running sums
-    uint8_t* bufs = reinterpret_cast<uint8_t*>(S.scratch);  // two chunk buffers
     const size_t layer_elems = (size_t)mp.st.capacity * mp.hkv * D;
     bf16* k_cache = reinterpret_cast<bf16*>(mp.st.kv_k) + (size_t)ph.state_index * layer_elems;
     bf16* v_cache = reinterpret_cast<bf16*>(mp.st.kv_v) + (size_t)ph.state_index * layer_elems;
 
-    // ---- before the grid barrier: the first chunk (rows of earlier positions were written by
-    // earlier steps)
-    if (mine) attn_fetch_chunk(bufs, k_cache, v_cache, t0, t1, position, mp.hkv, kvh, tid);
     phase_wait(mp, S, pi, tid);
     if (tid == 0) trace_mark(mp, pi, 0);
     if (!mine) return;
@@ -835,11 +852,23 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
     float m_run = -INFINITY, l_run = 0.f;            // warp h < G: running max / denominator of head h
     float acc[4] = {0.f, 0.f, 0.f, 0.f};             // thread (head tid / 64, features 4 (tid % 64) ..)
     const int ph_head = tid >> 6, pf = (tid & 63) * 4;
-    int chunk = 0;
+    bool ok = !*S.abort;
+    named_barrier(1, CT);                  // q_s (and k_s) are complete
+    float qr[4][8];                        // features 8 lane .. 8 lane + 7 of this warp's four heads
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        const int head = min((warp & 1) * 4 + h, G - 1);
+        const float4 qa = *reinterpret_cast<const float4*>(q_s + head * D + lane * 8);
+        const float4 qb = *reinterpret_cast<const float4*>(q_s + head * D + lane * 8 + 4);
+        qr[h][0] = qa.x; qr[h][1] = qa.y; qr[h][2] = qa.z; qr[h][3] = qa.w;
+        qr[h][4] = qb.x; qr[h][5] = qb.y; qr[h][6] = qb.z; qr[h][7] = qb.w;
+    }
 #pragma unroll 1
-    for (int c0 = t0; c0 < t1; c0 += kAttnChunk, ++chunk) {
-        uint8_t* buf = bufs + (chunk & 1) * kAttnBufBytes;
-        cp_async_wait_all();
+    for (int c0 = t0; c0 < t1 && ok; c0 += kAttnChunk, ++it) {
+        // the producer streams the chunks of the split through the ring, ahead of this loop
+        const int st = it % NS;
+        if (!mbar_wait(S.full + st, (it / NS) & 1, mp.status)) { ok = false; break; }
+        uint8_t* buf = S.stages + (size_t)st * kStreamStageBytes;
         if (owns_new && position >= c0 && position < c0 + kAttnChunk && warp == CW - 1) {
             // the step's own row: key from the normalised vector, value from the projection
             const int tl = position - c0;
@@ -851,29 +880,38 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
             }
         }
         named_barrier(1, CT);
-        if (c0 + kAttnChunk < t1)
-            attn_fetch_chunk(bufs + ((chunk + 1) & 1) * kAttnBufBytes, k_cache, v_cache, c0 + kAttnChunk, t1, position,
-                             mp.hkv, kvh, tid);
-        // scores: warp = position of the chunk
+        // scores: warp = (two positions of the chunk, one half of the heads); its query features
+        // stay in registers for the whole split
         {
-            const int t = c0 + warp;
-            const uint4 kr = lds128(buf + warp * kAttnRowBytes + lane * 16);
-            const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w};
-            float kf[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                kf[2 * j] = __uint_as_float(kw[j] << 16);
-                kf[2 * j + 1] = __uint_as_float(kw[j] & 0xffff0000u);
-            }
-#pragma unroll 1
-            for (int h = 0; h < G; ++h) {
-                const float4 qa = *reinterpret_cast<const float4*>(q_s + h * D + lane * 8);
-                const float4 qb = *reinterpret_cast<const float4*>(q_s + h * D + lane * 8 + 4);
-                float dot = qa.x * kf[0];
-                dot += qa.y * kf[1]; dot += qa.z * kf[2]; dot += qa.w * kf[3];
-                dot += qb.x * kf[4]; dot += qb.y * kf[5]; dot += qb.z * kf[6]; dot += qb.w * kf[7];
-                dot = warp_sum(dot) * scale;
-                if (lane == 0) sc[h * kAttnChunk + warp] = t < t1 ? dot : -INFINITY;
+            for (int half = 0; half < 2; ++half) {
+                const int tl = (warp >> 1) + half * 8;
+                const int t = c0 + tl;
+                const uint4 kr = lds128(buf + tl * kAttnRowBytes + lane * 16);
+                const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w};
+                float kf[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    kf[2 * j] = __uint_as_float(kw[j] << 16);
+                    kf[2 * j + 1] = __uint_as_float(kw[j] & 0xffff0000u);
+                }
+                float dots[4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    float dot = qr[h][0] * kf[0];
+#pragma unroll
+                    for (int j = 1; j < 8; ++j) dot += qr[h][j] * kf[j];
+                    dots[h] = dot;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) dots[h] += __shfl_xor_sync(0xffffffffu, dots[h], o);
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const int head = (warp & 1) * 4 + h;
+                    if (head < G && lane == h) sc[head * kAttnChunk + tl] = t < t1 ? dots[h] * scale : -INFINITY;
+                }
             }
         }
         named_barrier(1, CT);
@@ -907,7 +945,10 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
                 acc[3] += p * __uint_as_float(vv.y & 0xffff0000u);
             }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(S.empty + st);
     }
+    if (!ok && lane == 0) give_up(mp, S);
     QD_MARK(10);
     float* block_out = mp.attn_partial + (((size_t)kvh * mp.attn_splits + split) * G) * kAttnStride;
     if (ph_head < G) {
@@ -1152,7 +1193,7 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
         } else if (ph.kind == MK_GDN) {
             gdn_phase(mp, ph, S, pi);
         } else if (ph.kind == MK_ATTN) {
-            attn_phase(mp, ph, S, pi);
+            attn_phase(mp, ph, S, pi, it);
         } else if (ph.kind == MK_ATTN_MERGE) {
             attn_merge_phase(mp, ph, S, pi);
         } else {

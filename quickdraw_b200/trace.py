@@ -41,13 +41,14 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--position", type=int, default=600)
+    ap.add_argument("--context", type=int, default=0, help="KV capacity (default: position + 64)")
     ap.add_argument("--show", default="", help="comma-separated layers to print phase by phase")
     args = ap.parse_args()
     dev = "cuda"
     cfg = synthetic.model_config(num_layers=args.layers, vocab_size=args.vocab)
     ckpt = synthetic.make_checkpoint(cfg, seed=0, device=dev)
     step = FusedStep(ckpt, persistent=True)
-    state = DecodeState.allocate(cfg, 2048, dev)
+    state = DecodeState.allocate(cfg, args.context or args.position + 64, dev)
     state.kv_k.normal_()
     state.kv_v.normal_()
     grid = torch.cuda.get_device_properties(0).multi_processor_count
@@ -74,9 +75,33 @@ def main() -> None:
         totals.setdefault(kind, []).append((int(end.max() - start.max()), int(start.max() - previous_end)))
         previous_end = int(end.max())
     print(f"whole step: {marks[-1, 1].max() / 1e3:.1f} us")
+    nbytes = phase_bytes(cfg, args.position + 4)
     for kind, rows in totals.items():
         a = np.array(rows[1:] if len(rows) > 1 else rows)
-        print(f"{kind:3s} x{len(rows):3d}  work {a[:, 0].mean() / 1e3:7.2f} us   barrier gap {a[:, 1].mean() / 1e3:6.2f} us")
+        work = a[:, 0].mean() / 1e3
+        rate = f"{nbytes[kind] / work / 1e6:7.2f} TB/s of {nbytes[kind] / 1e6:8.2f} MB" if nbytes.get(kind) else ""
+        print(f"{kind:3s} x{len(rows):3d}  work {work:7.2f} us   barrier gap {a[:, 1].mean() / 1e3:6.2f} us   {rate}")
+
+
+def phase_bytes(cfg, position: int) -> dict[str, float]:
+    """Algorithmic bytes of each phase kind (weights once, state read + write, KV history)."""
+    h, inter = cfg.hidden_size, cfg.moe_intermediate_size
+    fp4 = lambda out, inp: out * inp // 2 + out * inp // 16
+    kw = cfg.linear_num_key_heads * cfg.linear_key_head_dim
+    vw = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+    qw, kvw = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    rec = cfg.linear_num_value_heads * cfg.linear_key_head_dim * cfg.linear_value_head_dim * 4
+    return {
+        "A": fp4(2 * kw + vw, h) + fp4(vw, h) + 2 * cfg.linear_num_value_heads * h * 2,
+        "Aa": fp4(2 * qw, h) + 2 * fp4(kvw, h),
+        "M": 2 * rec,
+        "Ma": 2 * kvw * 2 * (position + 1),
+        "B": fp4(h, vw), "Ba": fp4(h, qw),
+        "C": (cfg.num_experts + 1) * h * 2,
+        "D": (cfg.num_experts_per_tok + 1) * 2 * fp4(inter, h),
+        "E": (cfg.num_experts_per_tok + 1) * fp4(h, inter),
+        "H": cfg.vocab_size * h * 2,
+    }
 
 
 if __name__ == "__main__":
