@@ -42,7 +42,7 @@ struct Smem {
     MegaPhase* cph;        // [2] consumer copies of the current and the next phase
     MegaPhase* pph;        // producer copy
     uint64_t* full; uint64_t* empty;
-    float* red;            // [64]
+    float* red;            // [96]: 0.. sums, 16.. amax, 32.. / 48.. argmax, 64.. / 80.. global scales of the segments
     int32_t* ids; float* weights;      // [8] routing of the current layer
     uint64_t* ids_bar;                 // completes once per layer, when the routing is in ids / weights
     uint64_t* down_bar;                // completes once per layer, when the down-projection rows have landed
@@ -65,7 +65,7 @@ QD_DEVINL Smem carve_smem(uint8_t* base) {
     s.pph = reinterpret_cast<MegaPhase*>(base);       base += sizeof(MegaPhase);
     s.full = reinterpret_cast<uint64_t*>(base);       base += NS * 8;
     s.empty = reinterpret_cast<uint64_t*>(base);      base += NS * 8;
-    s.red = reinterpret_cast<float*>(base);           base += 64 * 4;
+    s.red = reinterpret_cast<float*>(base);           base += 96 * 4;
     s.ids = reinterpret_cast<int32_t*>(base);         base += 8 * 4;
     s.weights = reinterpret_cast<float*>(base);       base += 8 * 4;
     s.ids_bar = reinterpret_cast<uint64_t*>(base);    base += 8;
@@ -77,7 +77,7 @@ QD_DEVINL Smem carve_smem(uint8_t* base) {
 }
 constexpr size_t kSmemBytes = (size_t)NS * kStreamStageBytes + 4096 * 2 + 2048 * 4 + (size_t)kScratchFloats * 4 +
                               2 * kMegaConvRows * kStreamConvWidth * 2 + 3 * sizeof(MegaPhase) + 2 * NS * 8 +
-                              64 * 4 + 8 * 4 + 8 * 4 + 24 + 2 * 128 * 4;
+                              96 * 4 + 8 * 4 + 8 * 4 + 24 + 2 * 128 * 4;
 
 QD_DEVINL float ldcg_bf16(const bf16* p) {
     return __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(p)) << 16);
@@ -382,6 +382,14 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
         gam[0] = g0.x; gam[1] = g0.y; gam[2] = g0.z; gam[3] = g0.w;
         gam[4] = g1.x; gam[5] = g1.y; gam[6] = g1.z; gam[7] = g1.w;
     }
+    // global scales of the segments (one per projection; per-expert scales are read at the
+    // segment, after the routing): in flight across the barrier like the other static inputs
+    float seg_scale = 1.f;
+    if (tid < 2 * kMegaMaxSeg) {
+        const MegaSeg& sg = ph.seg[tid >> 1];
+        const float* src = (tid & 1) ? sg.g2 : sg.g;
+        if ((tid >> 1) < ph.nseg && src && !sg.g_per_expert) seg_scale = *src;
+    }
     int conv_row0 = 0, conv_n = 0;
     bf16* conv_state = nullptr;
     unsigned short conv_tap_reg = 0, conv_state_reg = 0;     // one element of each per thread
@@ -406,6 +414,7 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
         }
     }
+    if (tid < 2 * kMegaMaxSeg) red[64 + (tid & 1) * 16 + (tid >> 1)] = seg_scale;
     phase_wait(mp, S, pi, tid);
     if (tid == 0) trace_mark(mp, pi, 0);
     if constexpr (KC == 2) if (ph.conv_taps) {
@@ -591,8 +600,8 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             have_xh = true;
         }
         const int tile_rows = seg_tile_rows<K>(sg.kind);
-        const float g1 = sg.g ? sg.g[sg.g_per_expert ? expert : 0] : 1.f;
-        const float g2 = sg.g2 ? sg.g2[sg.g_per_expert ? expert : 0] : 1.f;
+        const float g1 = (sg.g && sg.g_per_expert) ? sg.g[expert] : red[64 + i];
+        const float g2 = (sg.g2 && sg.g_per_expert) ? sg.g2[expert] : red[80 + i];
         bf16* y = (KC == 2 && sg.epilogue == EP_ARGMAX) ? mp.logits : sg.y;
 #pragma unroll 1
         for (int r0 = ra; r0 < rb; r0 += tile_rows, ++it) {
@@ -1059,15 +1068,19 @@ QD_DEVINL void down_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
     const int n = r1 - r0, nslots = mp.topk + 1;
     float* contrib = reinterpret_cast<float*>(S.xs);                         // [slots][kMegaDownRows]
     int* order = reinterpret_cast<int*>(contrib + kDownSlots * kMegaDownRows);   // [topk]
-    phase_wait(mp, S, pi, tid);
-    if (tid == 0) trace_mark(mp, pi, 0);
-    const float strength = tid < kMegaDownRows ? ldcg_bf16(ph.strength) : 0.f;    // in flight during the rows
+    // the routing of this layer has been in shared memory since the gate/up phase: the global
+    // scale of this warp's expert is a static input, fetched before the barrier
     const int s = warp;
     const bool worker = s < nslots;
     const bool shared = s == mp.topk;
     const int e = (worker && !shared) ? S.ids[s] : 0;
     const bool owned = worker && (shared || (e >= mp.expert_lo && e < mp.expert_hi));
     const int hl = lane & 15, half = lane >> 4;
+    float global_scale = 0.f;
+    if (worker) global_scale = shared ? ph.sg[0] : ph.dg[ph.g_per_expert ? e - mp.expert_lo : 0];
+    phase_wait(mp, S, pi, tid);
+    if (tid == 0) trace_mark(mp, pi, 0);
+    const float strength = tid < kMegaDownRows ? ldcg_bf16(ph.strength) : 0.f;    // in flight during the rows
     bool ok = !*S.abort;
     if (worker && ok) {
         uint32_t xh[16];
@@ -1092,9 +1105,7 @@ QD_DEVINL void down_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
 #pragma unroll
         for (int j = 0; j < 16; ++j) xh[j] = pack_f16x2(__uint_as_float(xh[j] << 16) * down,
                                                        __uint_as_float(xh[j] & 0xffff0000u) * down);
-        float scale;
-        if (shared) scale = ph.sg[0];
-        else scale = round_bf16(ph.dg[ph.g_per_expert ? e - mp.expert_lo : 0] * S.weights[s]);
+        const float scale = shared ? global_scale : round_bf16(global_scale * S.weights[s]);
         QD_MARK(8);
         ok = mbar_wait(S.down_bar, ph.layer & 1, mp.status);
         QD_MARK(9);
