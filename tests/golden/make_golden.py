@@ -56,7 +56,7 @@ def mini_config():
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--reference", type=Path, default=Path("/root/reference"))
+    ap.add_argument("--reference", type=Path, required=True, help="checkout of the reference project")
     args = ap.parse_args()
     sys.path.insert(0, str(args.reference))
     sys.dont_write_bytecode = True
