@@ -58,6 +58,49 @@ int qd_nvfp4_matmul(const void* x, const void* codes, const void* scales, const 
                     int tokens, int out_features, int in_features, int group_size,
                     unsigned int* status, void* stream);
 
+/* grouped_matmul(x, bank, grouping, routing=None) for the routed experts of a chunk of tokens —
+ * quickdraw/kernel/triton/moe.py:99-151.  Routes are the (token, slot) pairs of the chunk
+ * sorted by expert (stable): order[r] = route index of sorted row r, rows [boundaries[e],
+ * boundaries[e+1]) belong to expert e (int32, device).  by_token: the input row of sorted row r
+ * is order[r] / topk (gate, up), else r (down).  scatter: the output row is order[r] (down),
+ * else r.  routing (fp32 per route, or NULL) selects the routed double rounding
+ * y = bf16(bf16(acc) * bf16(global * routing)).  max_rows_per_expert bounds the rows of any
+ * one expert (routes is always a valid bound); nothing is synchronised with the host. */
+int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const void* scales, const float* global,
+                            const int32_t* order, const int32_t* boundaries, const float* routing,
+                            void* y, int routes, int experts, int topk, int out_features,
+                            int in_features, int group_size, int by_token, int scatter,
+                            int global_per_expert, int max_rows_per_expert, unsigned int* status,
+                            void* stream);
+
+/* ---- Sequence forms for a chunk of prompt tokens (the 2-D branches of
+ * quickdraw/kernel/triton/{norm,delta,attention,moe}.py, qwen.py:66-241): the single-token
+ * arithmetic row by row.  All activations bf16 [tokens, width] contiguous. */
+int qd_seq_add_rms_norm(const void* x, const void* residual, const float* gamma, void* normed,
+                        void* residual_out, int tokens, int width, float eps, void* stream);
+/* y[t, n] = bf16(x[t] . w[n]) for a small bf16 matrix (router, shared gate, DeltaNet a / b). */
+int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tokens, int rows, int width, void* stream);
+/* short convolution walked along the chunk; conv_state ends with the last width - 1 inputs */
+int qd_seq_gdn_conv(const void* mixed, const void* taps, void* conv_state, void* out, int tokens,
+                    int channels, int width, void* stream);
+/* delta-rule recurrence walked along the chunk; rec_state updated in place; a, b [tokens, value_heads] */
+int qd_seq_gdn_recurrence(const void* conv_qkv, const void* a, const void* b, const void* a_log,
+                          const void* dt_bias, float* rec_state, void* out, int tokens, int key_heads,
+                          int value_heads, int key_dim, int value_dim, void* stream);
+/* q/k norm + RoPE + cache write for positions position0 .. position0 + tokens - 1, then causal
+ * attention of every token over [0, its position], gated.  k_cache / v_cache: this layer's
+ * [capacity, kv_heads, head_dim]; q_scratch bf16 [tokens, q_heads, head_dim]. */
+int qd_seq_attention(const void* qg, const void* k_new, const void* v_new, const void* q_norm,
+                     const void* k_norm, void* k_cache, void* v_cache, void* q_scratch, void* out,
+                     int tokens, int position0, int capacity, int q_heads, int kv_heads, int head_dim,
+                     int rotary_dim, float theta, float eps, void* stream);
+int qd_seq_route_topk(const void* logits, int tokens, int experts, int topk, int32_t* ids, float* weights,
+                      void* stream);
+/* contributions bf16 [tokens, topk, hidden] in route order, ids [tokens, topk], shared
+ * [tokens, hidden], strength bf16 [tokens] */
+int qd_seq_moe_combine(const void* contributions, const int32_t* ids, const void* shared,
+                       const void* strength, void* out, int tokens, int hidden, int topk, void* stream);
+
 /* expert_gemv(x, proj, ids, weights=None) — quickdraw/kernel/cute/matvec.py:152-154,
  * quickdraw/kernel/triton/matvec.py:84-99.  Bank [E, rows, in/2]; y [slots, rows];
  * x [in] or, with per_slot_input, [slots, in]; global fp32 scalar or [E]. */

@@ -50,6 +50,14 @@ SIGNATURES = {
     "qd_stream_trace": [P, I],
     "qd_nvfp4_gemv_bank": [P, P, P, P, P, I, I, I, I, P],
     "qd_nvfp4_matmul": [P, P, P, P, P, I, I, I, I, P, P],
+    "qd_nvfp4_grouped_matmul": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
+    "qd_seq_add_rms_norm": [P, P, P, P, P, I, I, F, P],
+    "qd_seq_bf16_matmul": [P, P, P, I, I, I, P],
+    "qd_seq_gdn_conv": [P, P, P, P, I, I, I, P],
+    "qd_seq_gdn_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "qd_seq_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, P],
+    "qd_seq_route_topk": [P, I, I, I, P, P, P],
+    "qd_seq_moe_combine": [P, P, P, P, P, I, I, I, P],
 }
 
 LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes"}

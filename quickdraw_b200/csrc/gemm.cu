@@ -39,6 +39,12 @@ struct GemmParams {
     const bf16* x; const uint8_t* codes; const uint8_t* scales; const float* global; bf16* y;
     int tokens, out_features, in_features;
     unsigned int* status;
+    // grouped form (routed experts of a chunk of tokens; order == NULL: plain matmul).  Routes =
+    // (token, slot) pairs sorted by expert: order[r] = route index of sorted row r, rows
+    // [boundaries[e], boundaries[e + 1]) belong to expert e.  Block x = expert * chunks + chunk.
+    const int32_t* order; const int32_t* boundaries; const float* routing;
+    int topk, chunks, by_token, scatter, global_per_expert;
+    long long codes_stride, scales_stride;       // bytes between experts of the bank
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------
@@ -121,8 +127,20 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int t0 = blockIdx.x * kTileM, n0 = blockIdx.y * kTileN;
+    const int n0 = blockIdx.y * kTileN;
     const int K = p.in_features, nk = K / kTileK;
+    // rows of this tile: [t0, t_end) of the activations, or of the sorted routes of one expert
+    int t0 = blockIdx.x * kTileM, t_end = p.tokens, expert = 0;
+    const bool grouped = p.order != nullptr;
+    if (grouped) {
+        expert = blockIdx.x / p.chunks;
+        t0 = p.boundaries[expert] + (blockIdx.x % p.chunks) * kTileM;
+        t_end = p.boundaries[expert + 1];
+        if (t0 >= t_end) return;                       // nothing routed here (whole block, before any barrier)
+    }
+    const uint8_t* codes = p.codes + (long long)expert * p.codes_stride;
+    const uint8_t* scales = p.scales + (long long)expert * p.scales_stride;
+    const int halves = (t_end - t0 > 128) ? kTileM / 128 : 1;      // a half without rows is not multiplied
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full + s, kProducerWarps); mbar_init(empty + s, 1); }
@@ -146,8 +164,8 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a = smem_u32(smem + st * kStageBytes), b = a + kABytes;
-#pragma unroll
-                for (int h = 0; h < kTileM / 128; ++h)
+#pragma unroll 1
+                for (int h = 0; h < halves; ++h)
 #pragma unroll
                     for (int j = 0; j < kTileK / 16; ++j)
                         umma_bf16(tmem + h * kTileN, smem_desc(a + h * (kABytes / 2) + j * 2 * kCorePitch, kCorePitch, kGroupPitch),
@@ -161,22 +179,30 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
         // ------------------------------------------------------------------- producers
         const int pt = tid - 32;                       // 0 .. 255
         StageRegs cur, nxt;
+        // the eight activation rows this thread copies pieces of (piece = (row, 8-input group))
+        const bf16* xrow[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int t = t0 + ((pt + i * 256) >> 3);
+            xrow[i] = nullptr;
+            if (t < t_end) {
+                int src = t;
+                if (grouped && p.by_token) src = p.order[t] / p.topk;
+                xrow[i] = p.x + (size_t)src * K + (pt & 7) * 8;
+            }
+        }
         auto fetch = [&](int s, StageRegs& r) {
             const int k0 = s * kTileK;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {              // activations: piece = (token, 8-input group)
-                const int piece = pt + i * 256, row = piece >> 3, kg = piece & 7;
-                const int t = t0 + row;
-                r.xa[i] = t < p.tokens ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * K + k0 + kg * 8))
-                                       : make_uint4(0u, 0u, 0u, 0u);
-            }
+            for (int i = 0; i < 8; ++i)
+                r.xa[i] = xrow[i] ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k0)) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int i = 0; i < 2; ++i) {              // weights: piece = (row, 32-input half of the stage)
                 const int piece = pt + i * 256, row = piece >> 1, half = piece & 1;
                 const int n = n0 + row;
                 if (n < p.out_features) {
-                    r.wc[i] = __ldg(reinterpret_cast<const uint4*>(p.codes + (size_t)n * (K / 2) + (k0 + half * 32) / 2));
-                    r.ws[i] = __ldg(reinterpret_cast<const uint16_t*>(p.scales + (size_t)n * (K / 16) + (k0 + half * 32) / 16));
+                    r.wc[i] = __ldg(reinterpret_cast<const uint4*>(codes + (size_t)n * (K / 2) + (k0 + half * 32) / 2));
+                    r.ws[i] = __ldg(reinterpret_cast<const uint16_t*>(scales + (size_t)n * (K / 16) + (k0 + half * 32) / 16));
                 } else {
                     r.wc[i] = make_uint4(0u, 0u, 0u, 0u);
                     r.ws[i] = 0;
@@ -220,27 +246,38 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
             tc_fence_after();
             if (ok) {
                 const int quadrant = warp & 3;                 // the lanes this warp may read
-                const float g = *p.global;
+                const float g = p.global[p.global_per_expert ? expert : 0];
 #pragma unroll 1
-                for (int h = 0; h < kTileM / 128; ++h) {
+                for (int h = 0; h < halves; ++h) {
                     const int t = t0 + h * 128 + quadrant * 32 + lane;
+                    // where the row goes and, for the routed down projection, its routing weight:
+                    // y = bf16( bf16(acc) * bf16(global * routing) )  (quickdraw/models/qwen.py:44-53)
+                    int dst = t;
+                    float row_scale = g;
+                    bool routed = false;
+                    if (grouped && t < t_end) {
+                        const int route = p.order[t];
+                        if (p.scatter) dst = route;
+                        if (p.routing) { row_scale = round_bf16(g * p.routing[route]); routed = true; }
+                    }
 #pragma unroll 1
                     for (int c = 0; c < kTileN; c += 32) {
                         uint32_t v[32];
                         tmem_load32(tmem + ((uint32_t)(quadrant * 32) << 16) + h * kTileN + c, v);
                         tmem_load_wait();
-                        if (t < p.tokens) {
+                        if (t < t_end) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 8) {
                                 if (n0 + c + j < p.out_features) {
                                     uint32_t o[4];
 #pragma unroll
                                     for (int q = 0; q < 4; ++q) {
-                                        const __nv_bfloat162 hv = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * q]) * g,
-                                                                                       __uint_as_float(v[j + 2 * q + 1]) * g);
+                                        float a0 = __uint_as_float(v[j + 2 * q]), a1 = __uint_as_float(v[j + 2 * q + 1]);
+                                        if (routed) { a0 = round_bf16(a0); a1 = round_bf16(a1); }
+                                        const __nv_bfloat162 hv = __floats2bfloat162_rn(a0 * row_scale, a1 * row_scale);
                                         o[q] = *reinterpret_cast<const uint32_t*>(&hv);
                                     }
-                                    *reinterpret_cast<uint4*>(p.y + (size_t)t * p.out_features + n0 + c + j) = make_uint4(o[0], o[1], o[2], o[3]);
+                                    *reinterpret_cast<uint4*>(p.y + (size_t)dst * p.out_features + n0 + c + j) = make_uint4(o[0], o[1], o[2], o[3]);
                                 }
                             }
                         }
@@ -256,14 +293,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
 
 }  // namespace
 
-// matmul(x, proj) for a 2-D x — quickdraw/kernel/triton/matvec.py:153-163 (NVFP4 branch).
-extern "C" int qd_nvfp4_matmul(const void* x, const void* codes, const void* scales, const float* global, void* y,
-                               int tokens, int out_features, int in_features, int group_size,
-                               unsigned int* status, void* stream) {
-    QD_CHECK_ARG(x && codes && scales && global && y && tokens > 0 && out_features > 0 && in_features > 0);
-    if (group_size != 16 || in_features % kTileK != 0 || out_features % 8 != 0) return QD_ERR_UNSUPPORTED;
-    const uintptr_t align = (uintptr_t)x | (uintptr_t)codes | (uintptr_t)y;
-    if (align & 15u) return QD_ERR_UNSUPPORTED;
+static int launch_gemm(const GemmParams& p, dim3 grid, cudaStream_t stream) {
     const size_t smem = (size_t)kStages * kStageBytes + (2 * kStages + 1) * 8 + 16;
     static bool configured[64];
     int dev = 0;
@@ -273,9 +303,49 @@ extern "C" int qd_nvfp4_matmul(const void* x, const void* codes, const void* sca
             return QD_ERR_LAUNCH;
         configured[dev] = true;
     }
-    GemmParams p;
+    return qd_launch(nvfp4_gemm_kernel, grid, dim3(kThreads), smem, stream, false, p);
+}
+
+// matmul(x, proj) for a 2-D x — quickdraw/kernel/triton/matvec.py:153-163 (NVFP4 branch).
+extern "C" int qd_nvfp4_matmul(const void* x, const void* codes, const void* scales, const float* global, void* y,
+                               int tokens, int out_features, int in_features, int group_size,
+                               unsigned int* status, void* stream) {
+    QD_CHECK_ARG(x && codes && scales && global && y && tokens > 0 && out_features > 0 && in_features > 0);
+    if (group_size != 16 || in_features % kTileK != 0 || out_features % 8 != 0) return QD_ERR_UNSUPPORTED;
+    const uintptr_t align = (uintptr_t)x | (uintptr_t)codes | (uintptr_t)y;
+    if (align & 15u) return QD_ERR_UNSUPPORTED;
+    GemmParams p = {};
     p.x = (const bf16*)x; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
     p.y = (bf16*)y; p.tokens = tokens; p.out_features = out_features; p.in_features = in_features; p.status = status;
     dim3 grid((tokens + kTileM - 1) / kTileM, (out_features + kTileN - 1) / kTileN);
-    return qd_launch(nvfp4_gemm_kernel, grid, dim3(kThreads), smem, (cudaStream_t)stream, false, p);
+    return launch_gemm(p, grid, (cudaStream_t)stream);
+}
+
+// grouped_matmul(x, bank, grouping, routing=None) — quickdraw/kernel/triton/moe.py:99-151: the
+// routes (token, slot) of a chunk sorted by expert; every expert's rows go through that
+// expert's matrix.  by_token: input row = order[r] / topk (gate, up), else the sorted row r
+// (down).  scatter: output row = order[r] (down), else r.  routing (fp32 per route) selects the
+// routed double rounding.  max_rows_per_expert bounds the rows any one expert can get (the
+// number of routes is always a valid bound); no host synchronisation is needed.
+extern "C" int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const void* scales, const float* global,
+                                       const int32_t* order, const int32_t* boundaries, const float* routing,
+                                       void* y, int routes, int experts, int topk, int out_features,
+                                       int in_features, int group_size, int by_token, int scatter,
+                                       int global_per_expert, int max_rows_per_expert, unsigned int* status,
+                                       void* stream) {
+    QD_CHECK_ARG(x && codes && scales && global && order && boundaries && y);
+    QD_CHECK_ARG(routes > 0 && experts > 0 && topk > 0 && out_features > 0 && in_features > 0 && max_rows_per_expert > 0);
+    if (group_size != 16 || in_features % kTileK != 0 || out_features % 8 != 0) return QD_ERR_UNSUPPORTED;
+    const uintptr_t align = (uintptr_t)x | (uintptr_t)codes | (uintptr_t)y;
+    if (align & 15u) return QD_ERR_UNSUPPORTED;
+    GemmParams p = {};
+    p.x = (const bf16*)x; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
+    p.y = (bf16*)y; p.tokens = routes; p.out_features = out_features; p.in_features = in_features; p.status = status;
+    p.order = order; p.boundaries = boundaries; p.routing = routing; p.topk = topk;
+    p.chunks = (max_rows_per_expert + kTileM - 1) / kTileM;
+    p.by_token = by_token; p.scatter = scatter; p.global_per_expert = global_per_expert;
+    p.codes_stride = (long long)out_features * (in_features / 2);
+    p.scales_stride = (long long)out_features * (in_features / 16);
+    dim3 grid(experts * p.chunks, (out_features + kTileN - 1) / kTileN);
+    return launch_gemm(p, grid, (cudaStream_t)stream);
 }

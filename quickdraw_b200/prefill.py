@@ -1,0 +1,150 @@
+"""Prompt tokens in chunks: the sequence form of the token step (no logits).
+
+The reference prefills in chunks of 128 tokens (quickdraw/engine/engine.py:98-104): every
+projection of a chunk is one matrix product, the token-sequential parts (DeltaNet convolution
+and recurrence, causal attention) walk the chunk inside one kernel, the routed experts run as
+a grouped product over the chunk's (token, slot) routes sorted by expert
+(quickdraw/kernel/triton/moe.py:60-151).  Here the products run on the tensor cores
+(``qd_nvfp4_matmul`` / ``qd_nvfp4_grouped_matmul``, tcgen05) and the glue kernels apply the
+single-token arithmetic row by row; the state (KV cache, recurrent state, convolution
+history) ends up where the token loop would leave it, up to fp32 summation order.
+
+``ChunkPrefill.run`` advances the state over a chunk and returns nothing: the engine feeds
+the last prompt token through the decode step, which produces the logits.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ._lib import call, ptr, stream_of
+from .weights import Checkpoint, NVFP4Linear
+
+BF16 = torch.bfloat16
+
+
+class ChunkPrefill:
+    def __init__(self, ckpt: Checkpoint):
+        c = ckpt.config
+        self.ckpt, self.device = ckpt, ckpt.embed_tokens.device
+        self.gammas = [((1 + layer.input_layernorm.float()).contiguous(),
+                        (1 + layer.post_attention_layernorm.float()).contiguous()) for layer in ckpt.layers]
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.expert_index = torch.arange(c.num_experts + 1, device=self.device)
+        for layer in ckpt.layers:
+            assert layer.moe.experts_gate.weight.shape[0] == c.num_experts, "the whole model on one GPU"
+
+    # ------------------------------------------------------------------ building blocks
+    def _empty(self, *shape, dtype=BF16):
+        return torch.empty(shape, dtype=dtype, device=self.device)
+
+    def _matmul(self, x, proj: NVFP4Linear):
+        out = self._empty(x.shape[0], proj.out_features)
+        call("qd_nvfp4_matmul", ptr(x), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2),
+             ptr(out), x.shape[0], proj.out_features, proj.in_features, proj.group_size, ptr(self.status),
+             stream_of(x))
+        return out
+
+    def _small(self, x, weight):
+        rows = weight.shape[0]
+        out = self._empty(x.shape[0], rows)
+        call("qd_seq_bf16_matmul", ptr(x), ptr(weight), ptr(out), x.shape[0], rows, x.shape[1], stream_of(x))
+        return out
+
+    def _add_norm(self, x, residual, gamma, eps):
+        normed, new_residual = torch.empty_like(x), torch.empty_like(x)
+        call("qd_seq_add_rms_norm", ptr(x), ptr(residual), ptr(gamma), ptr(normed), ptr(new_residual),
+             x.shape[0], x.shape[1], eps, stream_of(x))
+        return normed, new_residual
+
+    def _swiglu(self, gate, up):
+        out = torch.empty_like(gate)
+        call("qd_swiglu", ptr(gate), ptr(up), ptr(out), gate.numel(), stream_of(gate))
+        return out
+
+    def _grouped(self, x, bank: NVFP4Linear, order, boundaries, routes, topk, *, routing=None, by_token, scatter):
+        out = self._empty(routes, bank.out_features)
+        call("qd_nvfp4_grouped_matmul", ptr(x), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
+             ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, bank.weight.shape[0], topk,
+             bank.out_features, bank.in_features, bank.group_size, int(by_token), int(scatter),
+             int(bank.weight_scale_2.numel() != 1), routes, ptr(self.status), stream_of(x))
+        return out
+
+    # --------------------------------------------------------------------------- blocks
+    def _delta_net(self, w, x, state, index):
+        c = self.ckpt.config
+        tokens = x.shape[0]
+        hv, dv = c.linear_num_value_heads, c.linear_value_head_dim
+        qkv, z = self._matmul(x, w.in_proj_qkv), self._matmul(x, w.in_proj_z)
+        a, b = self._small(x, w.in_proj_a), self._small(x, w.in_proj_b)
+        conv = torch.empty_like(qkv)
+        call("qd_seq_gdn_conv", ptr(qkv), ptr(w.conv1d), ptr(state.conv_state[index]), ptr(conv), tokens,
+             qkv.shape[1], c.linear_conv_kernel_dim, stream_of(x))
+        core = self._empty(tokens, hv * dv)
+        call("qd_seq_gdn_recurrence", ptr(conv), ptr(a), ptr(b), ptr(w.A_log), ptr(w.dt_bias),
+             ptr(state.rec_state[index]), ptr(core), tokens, c.linear_num_key_heads, hv,
+             c.linear_key_head_dim, dv, stream_of(x))
+        gated = torch.empty_like(core)
+        call("qd_gdn_gated_norm", ptr(core), ptr(z), ptr(w.norm), ptr(gated), tokens * hv, dv, c.rms_norm_eps,
+             stream_of(x))
+        return self._matmul(gated, w.out_proj)
+
+    def _attention(self, w, x, state, index, position0):
+        c = self.ckpt.config
+        tokens = x.shape[0]
+        qg, k, v = self._matmul(x, w.q_proj), self._matmul(x, w.k_proj), self._matmul(x, w.v_proj)
+        q_scratch = self._empty(tokens, c.num_attention_heads * c.head_dim)
+        out = torch.empty_like(q_scratch)
+        call("qd_seq_attention", ptr(qg), ptr(k), ptr(v), ptr(w.q_norm), ptr(w.k_norm), ptr(state.kv_k[index]),
+             ptr(state.kv_v[index]), ptr(q_scratch), ptr(out), tokens, position0, state.kv_k.shape[1],
+             c.num_attention_heads, c.num_key_value_heads, c.head_dim, int(c.head_dim * c.partial_rotary_factor),
+             c.rope_theta, c.rms_norm_eps, stream_of(x))
+        return self._matmul(out, w.o_proj)
+
+    def _moe(self, w, x):
+        c = self.ckpt.config
+        tokens, topk = x.shape[0], c.num_experts_per_tok
+        logits, strength = self._small(x, w.router), self._small(x, w.shared_expert_gate)
+        ids = self._empty(tokens, topk, dtype=torch.int32)
+        weights = self._empty(tokens, topk, dtype=torch.float32)
+        call("qd_seq_route_topk", ptr(logits), tokens, c.num_experts, topk, ptr(ids), ptr(weights), stream_of(x))
+        # the routes sorted by expert (stable), as the reference groups them
+        sorted_ids, order = ids.flatten().sort(stable=True)
+        boundaries = torch.searchsorted(sorted_ids, self.expert_index.to(sorted_ids.dtype)).to(torch.int32)
+        order = order.to(torch.int32)
+        routes = tokens * topk
+        gate = self._grouped(x, w.experts_gate, order, boundaries, routes, topk, by_token=True, scatter=False)
+        up = self._grouped(x, w.experts_up, order, boundaries, routes, topk, by_token=True, scatter=False)
+        hidden = self._swiglu(gate, up)
+        contributions = self._grouped(hidden, w.experts_down, order, boundaries, routes, topk,
+                                      routing=weights.flatten(), by_token=False, scatter=True)
+        shared_hidden = self._swiglu(self._matmul(x, w.shared_gate), self._matmul(x, w.shared_up))
+        shared = self._matmul(shared_hidden, w.shared_down)
+        out = torch.empty_like(x)
+        call("qd_seq_moe_combine", ptr(contributions), ptr(ids), ptr(shared), ptr(strength), ptr(out), tokens,
+             x.shape[1], topk, stream_of(x))
+        return out
+
+    # ------------------------------------------------------------------------------ run
+    @torch.inference_mode()
+    def run(self, token_ids: torch.Tensor, position0: int, state) -> None:
+        """Advance ``state`` over the tokens at positions position0 .. position0 + len - 1."""
+        c = self.ckpt.config
+        assert token_ids.ndim == 1 and token_ids.dtype == torch.long and token_ids.is_cuda
+        assert 0 <= position0 and position0 + token_ids.numel() <= state.kv_k.shape[1]
+        x = self.ckpt.embed_tokens[token_ids].contiguous()
+        residual = None
+        for layer, (gamma_in, gamma_post) in zip(self.ckpt.layers, self.gammas):
+            normed, residual = self._add_norm(x, residual, gamma_in, c.rms_norm_eps)
+            if layer.layer_type == "full_attention":
+                index = sum(1 for k in c.layer_types[:layer.idx] if k == "full_attention")
+                mixed = self._attention(layer.attn, normed, state, index, position0)
+            else:
+                index = sum(1 for k in c.layer_types[:layer.idx] if k != "full_attention")
+                mixed = self._delta_net(layer.attn, normed, state, index)
+            normed, residual = self._add_norm(mixed, residual, gamma_post, c.rms_norm_eps)
+            x = self._moe(layer.moe, normed)
+
+    def check(self) -> int:
+        """Status word of the tensor-core products (0 = clean)."""
+        return int(self.status.item())

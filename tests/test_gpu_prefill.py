@@ -1,0 +1,71 @@
+"""Chunked prefill (sequence kernels + tensor-core products) against the token loop through the
+decode step: same state and same logits for the next token, up to fp32 summation order — the
+reference's own criterion for its chunked path (tests/engine/test_cuda.py:132-147), loosened the
+way the whole-step tests are, because bf16 rounding points amplify last-bit differences."""
+
+import pytest
+import torch
+
+from oracle import decode_oracle as O
+from quickdraw_b200 import synthetic
+from quickdraw_b200.state import DecodeState
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("chunk", [5, 16, 39])
+def test_chunked_prefill_matches_token_loop(cuda_device, chunk):
+    from quickdraw_b200.fused import FusedStep
+    from quickdraw_b200.prefill import ChunkPrefill
+    cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
+    ckpt = synthetic.make_checkpoint(cfg, seed=11, device="cuda")
+    step, prefill = FusedStep(ckpt), ChunkPrefill(ckpt)
+    gen = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, cfg.vocab_size, (40,), generator=gen).to("cuda")
+    loop_state, chunk_state = (DecodeState.allocate(cfg, 64, "cuda") for _ in range(2))
+    for s in (loop_state, chunk_state):
+        s.kv_k.zero_()
+        s.kv_v.zero_()
+    for position in range(40):
+        want = step(ckpt, prompt[position], position, loop_state, logits=position == 39)
+    for start in range(0, 39, chunk):
+        stop = min(39, start + chunk)
+        prefill.run(prompt[start:stop], start, chunk_state)
+    got = step(ckpt, prompt[39], 39, chunk_state)
+    assert prefill.check() == 0 and step.status() == 0
+    assert O.rel_l2(chunk_state.conv_state.cpu(), loop_state.conv_state.cpu()) < 2e-2
+    assert O.rel_l2(chunk_state.rec_state.cpu(), loop_state.rec_state.cpu()) < 2e-2
+    assert O.rel_l2(chunk_state.kv_k[:, :40].cpu(), loop_state.kv_k[:, :40].cpu()) < 2e-2
+    assert O.rel_l2(chunk_state.kv_v[:, :40].cpu(), loop_state.kv_v[:, :40].cpu()) < 2e-2
+    assert O.rel_l2(got.cpu(), want.cpu()) < 5e-2
+
+
+def test_grouped_matmul_matches_per_route_matvec(cuda_device):
+    """The grouped product of the routed experts against the single-token expert matvec."""
+    from quickdraw_b200 import kernels
+    from quickdraw_b200.prefill import ChunkPrefill
+    from quickdraw_b200.synthetic import to_device
+    src = synthetic.Source(31, "cpu")
+    experts, topk, tokens, width, rows = 8, 3, 21, 512, 264
+    bank = to_device(src.nvfp4("bank", rows, width, experts, global_scale=0.5, per_expert_global=True), cuda_device)
+    x = src.normal("x", tokens, width).to(cuda_device)
+    gen = torch.Generator().manual_seed(3)
+    ids = torch.stack([torch.randperm(experts, generator=gen)[:topk] for _ in range(tokens)]).to(torch.int32).to(cuda_device)
+    weights = torch.rand(tokens, topk, generator=gen).to(cuda_device)
+    sorted_ids, order = ids.flatten().sort(stable=True)
+    boundaries = torch.searchsorted(sorted_ids, torch.arange(experts + 1, device=cuda_device, dtype=torch.int32)).to(torch.int32)
+    helper = ChunkPrefill.__new__(ChunkPrefill)
+    helper.device = cuda_device
+    helper.status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    routes = tokens * topk
+    plain = helper._grouped(x, bank, order.to(torch.int32), boundaries, routes, topk, by_token=True, scatter=False)
+    routed = helper._grouped(x.repeat_interleave(topk, 0)[order].contiguous(), bank, order.to(torch.int32), boundaries,
+                             routes, topk, routing=weights.flatten(), by_token=False, scatter=True)
+    assert int(helper.status.item()) == 0
+    for r in range(routes):
+        route = int(order[r])
+        token, expert = route // topk, int(ids.flatten()[route])
+        want = kernels.expert_gemv(x[token], bank, ids.flatten()[route:route + 1])[0]
+        torch.testing.assert_close(plain[r].float(), want.float(), rtol=0.025, atol=0.003)
+        want_routed = kernels.expert_gemv(x[token], bank, ids.flatten()[route:route + 1], weights.flatten()[route:route + 1])[0]
+        torch.testing.assert_close(routed[route].float(), want_routed.float(), rtol=0.025, atol=0.003)
