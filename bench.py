@@ -279,8 +279,12 @@ def run_gpu(args):
         engine = Engine(ckpt, max_context=2048, device=str(device))
     gen = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=gen).tolist()
+    torch.cuda.synchronize(device)
+    t_prefill = time.perf_counter()
     logits = engine.prefill(prompt)
     engine.pending_token = torch.argmax(logits)
+    torch.cuda.synchronize(device)
+    prefill_s = time.perf_counter() - t_prefill
 
     def barrier():
         torch.cuda.synchronize(device)
@@ -345,6 +349,10 @@ def run_gpu(args):
         "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 12,
                 "d2h_bytes_per_step": 8},
         "gpu_launches": launches * args.steps,
+        # outside the timed region: the prompt (chunks of 128 tokens through the tensor-core
+        # products on one GPU; token by token under expert parallelism) up to the first token
+        "prefill": {"tokens": args.prompt, "ms": prefill_s * 1e3, "tok_s": args.prompt / prefill_s,
+                    "path": "chunked" if getattr(engine, "sequence_prefill", False) else "token loop"},
         "clocks": clocks.summary(),
         # the dominant kernel is the token step itself: one launch = one token = every weight
         # the token touches, read once (single GPU: the persistent kernel; expert parallel: the

@@ -36,7 +36,8 @@ class Engine:
         assert max_context > 0 and prefill_chunk_size > 0
         self.ckpt, self.max_context, self.device, self.backend = ckpt, max_context, device, backend
         self.prefill_chunk_size = prefill_chunk_size
-        self.sequence_prefill = False      # token-loop prefill; kept for interface parity
+        self.sequence_prefill = False      # set below where the chunked path applies
+        self.chunk_prefill = None
         self.graph = None
         self.fused = None
         on_cuda = torch.device(device).type == "cuda"
@@ -53,6 +54,10 @@ class Engine:
             if kernels is None and fused.supports(ckpt):
                 self.fused = fused.FusedStep(ckpt)
                 self.step = self.fused
+                if sequence_prefill:
+                    from .prefill import ChunkPrefill
+                    self.chunk_prefill = ChunkPrefill(ckpt)
+                    self.sequence_prefill = True
             else:
                 prepared = ([(1 + l.input_layernorm.float(), 1 + l.post_attention_layernorm.float())
                              for l in ckpt.layers], 1 + ckpt.final_norm.float())
@@ -97,13 +102,22 @@ class Engine:
     # ----------------------------------------------------------------------- requests
     @torch.inference_mode()
     def prefill(self, token_ids: list[int]) -> torch.Tensor:
-        """Start a fresh request: run the prompt token by token, return the logits after
-        its last token (quickdraw/engine/engine.py:93-111)."""
+        """Start a fresh request: run the prompt, return the logits after its last token
+        (quickdraw/engine/engine.py:93-111).  With the chunked path all tokens but the last
+        go through the sequence kernels ``prefill_chunk_size`` at a time; the last one, and
+        every token otherwise, goes through the decode step."""
         assert 0 < len(token_ids) <= self.max_context, "prompt must fit within max_context"
         self.reset()
         tokens = torch.tensor(token_ids, dtype=torch.long, device=self.device)
         logits = None
-        for index, token in enumerate(tokens):
+        done = 0
+        if self.sequence_prefill and len(token_ids) > 1:
+            while done < len(token_ids) - 1:
+                stop = min(len(token_ids) - 1, done + self.prefill_chunk_size)
+                self.chunk_prefill.run(tokens[done:stop], done, self.state)
+                done = stop
+            self.state.position = done
+        for index, token in enumerate(tokens[done:], start=done):
             if self.backend == "b200":
                 logits = self.step(self.ckpt, token, self.state.position, self.state,
                                    logits=index == len(tokens) - 1)

@@ -62,7 +62,8 @@ def test_two_rank_generation_matches_single_gpu():
     from quickdraw_b200.engine import Engine
     prompt, steps = [5, 1900, 77, 1033], 24
     cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
-    single = Engine(synthetic.make_checkpoint(cfg, seed=11, device="cuda:0"), max_context=64, device="cuda:0")
+    single = Engine(synthetic.make_checkpoint(cfg, seed=11, device="cuda:0"), max_context=64, device="cuda:0",
+                    sequence_prefill=False)      # the ranks run the prompt token by token too
     single.state.kv_k.zero_()
     single.state.kv_v.zero_()
     want = single.generate(prompt, steps)
