@@ -22,7 +22,8 @@
 namespace {
 
 constexpr int kTileM = 256;                 // tokens per tile: two halves of 128 (tensor memory lanes)
-constexpr int kTileN = 256;                 // weight rows per tile (tensor memory columns)
+// weight rows per tile (tensor memory columns per accumulator): template parameter TN, 256 for
+// large problems, 128 or 64 where 256 would leave most SMs without a tile
 constexpr int kTileK = 64;                  // inputs per stage
 constexpr int kStages = 3;
 constexpr int kProducerWarps = 8;
@@ -31,9 +32,8 @@ constexpr int kCorePitch = 144;             // bytes from one 128-byte core matr
                                             // 16 bytes of padding spread a warp's stores over all banks
 constexpr int kGroupPitch = (kTileK / 8) * kCorePitch;      // bytes between 8-row groups
 constexpr int kABytes = (kTileM / 8) * kGroupPitch;         // 18 KB
-constexpr int kBBytes = (kTileN / 8) * kGroupPitch;         // 36 KB
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kTmemCols = 512;               // one 128 x 256 fp32 accumulator per token half
+constexpr int kBBytesMax = (256 / 8) * kGroupPitch;         // 36 KB at 256 rows
+constexpr int kStageBytes = kABytes + kBBytesMax;
 
 struct GemmParams {
     const bf16* x; const uint8_t* codes; const uint8_t* scales; const float* global; bf16* y;
@@ -89,8 +89,10 @@ QD_DEVINL uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
 }
 // Instruction descriptor: fp32 accumulator (bits [4,6) = 1), bf16 A and B (bits [7,10) and
 // [10,13) = 1), both K-major (bits 15, 16 = 0), N >> 3 at [17,23), M >> 4 at [24,29).
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileN >> 3) << 17) |
-                                ((uint32_t)(128 >> 4) << 24);
+template <int TN>
+constexpr uint32_t instr_desc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
 
 // byte offset of the 16-byte piece (row, 8-input group kg) inside a stage tile
 QD_DEVINL uint32_t core_offset(int row, int kg) { return (uint32_t)((row >> 3) * kGroupPitch + kg * kCorePitch + (row & 7) * 16); }
@@ -118,8 +120,13 @@ struct StageRegs {
     uint16_t ws[2];        // their two block scales each
 };
 
+template <int TN>
 __global__ void __launch_bounds__(kThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
+    constexpr int kTileN = TN;
+    constexpr int kTmemCols = 2 * TN;            // one 128 x TN fp32 accumulator per token half
+    constexpr uint32_t kInstrDesc = instr_desc<TN>();
+    constexpr int kWPieces = TN * 2;             // 16-byte code pieces of a stage: (row, 32-input half)
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
     uint64_t* empty = full + kStages;
@@ -200,7 +207,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
             for (int i = 0; i < 2; ++i) {              // weights: piece = (row, 32-input half of the stage)
                 const int piece = pt + i * 256, row = piece >> 1, half = piece & 1;
                 const int n = n0 + row;
-                if (n < p.out_features) {
+                if (piece < kWPieces && n < p.out_features) {
                     r.wc[i] = __ldg(reinterpret_cast<const uint4*>(codes + (size_t)n * (K / 2) + (k0 + half * 32) / 2));
                     r.ws[i] = __ldg(reinterpret_cast<const uint16_t*>(scales + (size_t)n * (K / 16) + (k0 + half * 32) / 16));
                 } else {
@@ -220,6 +227,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int piece = pt + i * 256, row = piece >> 1, half = piece & 1;
+                if (piece >= kWPieces) continue;
                 const float2 sc = e4m3x2_to_float2(r.ws[i]);
                 const uint32_t words[4] = {r.wc[i].x, r.wc[i].y, r.wc[i].z, r.wc[i].w};
 #pragma unroll
@@ -293,17 +301,31 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
 
 }  // namespace
 
-static int launch_gemm(const GemmParams& p, dim3 grid, cudaStream_t stream) {
+template <int TN>
+static int launch_variant(const GemmParams& p, int row_tiles, cudaStream_t stream) {
     const size_t smem = (size_t)kStages * kStageBytes + (2 * kStages + 1) * 8 + 16;
     static bool configured[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
     if (!configured[dev]) {
-        if (cudaFuncSetAttribute(nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(nvfp4_gemm_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return QD_ERR_LAUNCH;
         configured[dev] = true;
     }
-    return qd_launch(nvfp4_gemm_kernel, grid, dim3(kThreads), smem, stream, false, p);
+    dim3 grid(row_tiles, (p.out_features + TN - 1) / TN);
+    return qd_launch(nvfp4_gemm_kernel<TN>, grid, dim3(kThreads), smem, stream, false, p);
+}
+
+// The widest weight tile that still gives every SM a tile (narrower tiles expand fewer weights
+// per block, so small problems finish sooner); `busy_row_tiles`: row tiles that will have rows.
+static int launch_gemm(const GemmParams& p, int row_tiles, int busy_row_tiles, cudaStream_t stream) {
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    if ((long long)busy_row_tiles * ((p.out_features + 255) / 256) >= sms) return launch_variant<256>(p, row_tiles, stream);
+    if ((long long)busy_row_tiles * ((p.out_features + 127) / 128) >= sms) return launch_variant<128>(p, row_tiles, stream);
+    return launch_variant<64>(p, row_tiles, stream);
 }
 
 // matmul(x, proj) for a 2-D x — quickdraw/kernel/triton/matvec.py:153-163 (NVFP4 branch).
@@ -317,8 +339,8 @@ extern "C" int qd_nvfp4_matmul(const void* x, const void* codes, const void* sca
     GemmParams p = {};
     p.x = (const bf16*)x; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
     p.y = (bf16*)y; p.tokens = tokens; p.out_features = out_features; p.in_features = in_features; p.status = status;
-    dim3 grid((tokens + kTileM - 1) / kTileM, (out_features + kTileN - 1) / kTileN);
-    return launch_gemm(p, grid, (cudaStream_t)stream);
+    const int row_tiles = (tokens + kTileM - 1) / kTileM;
+    return launch_gemm(p, row_tiles, row_tiles, (cudaStream_t)stream);
 }
 
 // grouped_matmul(x, bank, grouping, routing=None) — quickdraw/kernel/triton/moe.py:99-151: the
@@ -346,6 +368,7 @@ extern "C" int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const v
     p.by_token = by_token; p.scatter = scatter; p.global_per_expert = global_per_expert;
     p.codes_stride = (long long)out_features * (in_features / 2);
     p.scales_stride = (long long)out_features * (in_features / 16);
-    dim3 grid(experts * p.chunks, (out_features + kTileN - 1) / kTileN);
-    return launch_gemm(p, grid, (cudaStream_t)stream);
+    // about one busy row tile per expert that received routes (at most min(experts, routes))
+    const int busy = experts < routes ? experts : routes;
+    return launch_gemm(p, experts * p.chunks, busy, (cudaStream_t)stream);
 }

@@ -8,6 +8,10 @@ owns ``state.position``; a step never touches it.  ``reset`` zeroes the recurren
 convolution history, keeps every buffer address (a captured graph stays valid) and leaves
 the KV cache alone (slots at or beyond the position are never read).
 
+Prompts run in chunks of ``prefill_chunk_size`` tokens through the sequence path
+(tensor-core products; the reference's default chunk is 128, here 512 because larger chunks
+amortise the expert weights better) where the fused step applies, token by token otherwise.
+
 Backends: ``"b200"`` (default) runs the fused CUDA step where the checkpoint has the
 36B-A3B widths and the composed operator table otherwise; passing ``kernels=`` or
 ``step=`` gives the ``"custom"`` backend used by tests (no graph).  There is no CPU
@@ -25,7 +29,7 @@ from .weights import Checkpoint
 class Engine:
     def __init__(self, ckpt: Checkpoint, max_context: int = 32768, device: str = "cuda",
                  backend: str | None = None, *, kernels: dict | None = None, step=None,
-                 cuda_graph: bool = True, prefill_chunk_size: int = 128,
+                 cuda_graph: bool = True, prefill_chunk_size: int = 512,
                  sequence_prefill: bool = True, _step_object=None):
         custom = kernels is not None or step is not None
         if backend is None:
