@@ -121,9 +121,9 @@ def test_expert_parallel_partition_sums_to_whole(reference_outputs):
                  for r in range(world)]
         total = torch.stack(parts).sum(0)
         torch.testing.assert_close(total, whole, rtol=1e-6, atol=1e-6)
-        assert torch.equal(O.combine_shared(moe, x, total).float().round(decimals=1),
-                           O.moe_block(moe, x, config=cfg).float().round(decimals=1)) or \
-            O.rel_l2(O.combine_shared(moe, x, total), O.moe_block(moe, x, config=cfg)) < 1e-2
+        # the partial sums add in another order than the unsharded fp32 sum: the combined
+        # block agrees to bf16 rounding level, not bit for bit
+        assert O.rel_l2(O.combine_shared(moe, x, total), O.moe_block(moe, x, config=cfg)) < 1e-2
 
 
 def test_gdn_block(reference_outputs):
