@@ -202,7 +202,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
             const int k0 = s * kTileK;
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-                r.xa[i] = xrow[i] ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k0)) : make_uint4(0u, 0u, 0u, 0u);
+                if (xrow[i]) r.xa[i] = __ldg(reinterpret_cast<const uint4*>(xrow[i] + k0));
 #pragma unroll
             for (int i = 0; i < 2; ++i) {              // weights: piece = (row, 32-input half of the stage)
                 const int piece = pt + i * 256, row = piece >> 1, half = piece & 1;
@@ -219,10 +219,12 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
         auto store = [&](int st, const StageRegs& r) {
             uint8_t* a = smem + st * kStageBytes;
             uint8_t* b = a + kABytes;
+            // rows without a token are not stored: an accumulator row depends on its own activation
+            // row only, and rows past the end are never written out
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int piece = pt + i * 256;
-                *reinterpret_cast<uint4*>(a + core_offset(piece >> 3, piece & 7)) = r.xa[i];
+                if (xrow[i]) *reinterpret_cast<uint4*>(a + core_offset(piece >> 3, piece & 7)) = r.xa[i];
             }
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
@@ -323,8 +325,9 @@ static int launch_gemm(const GemmParams& p, int row_tiles, int busy_row_tiles, c
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
-    if ((long long)busy_row_tiles * ((p.out_features + 255) / 256) >= sms) return launch_variant<256>(p, row_tiles, stream);
-    if ((long long)busy_row_tiles * ((p.out_features + 127) / 128) >= sms) return launch_variant<128>(p, row_tiles, stream);
+    const long long wide = (long long)busy_row_tiles * ((p.out_features + 255) / 256);
+    if (wide >= sms) return launch_variant<256>(p, row_tiles, stream);
+    if (4 * wide >= sms) return launch_variant<128>(p, row_tiles, stream);
     return launch_variant<64>(p, row_tiles, stream);
 }
 
