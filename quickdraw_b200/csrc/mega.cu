@@ -414,9 +414,10 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
         }
     }
-    if (tid < 2 * kMegaMaxSeg) red[64 + (tid & 1) * 16 + (tid >> 1)] = seg_scale;
     phase_wait(mp, S, pi, tid);
     if (tid == 0) trace_mark(mp, pi, 0);
+    // (stored after the wait: thread 0 polls the barrier and must not sit on this load first)
+    if (tid < 2 * kMegaMaxSeg) red[64 + (tid & 1) * 16 + (tid >> 1)] = seg_scale;
     if constexpr (KC == 2) if (ph.conv_taps) {
         if (tid < conv_n * mp.conv_width) reinterpret_cast<unsigned short*>(S.conv_taps)[tid] = conv_tap_reg;
         if (tid < conv_n * (mp.conv_width - 1)) reinterpret_cast<unsigned short*>(S.conv_state)[tid] = conv_state_reg;
@@ -863,20 +864,23 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
     const int ph_head = tid >> 6, pf = (tid & 63) * 4;
     bool ok = !*S.abort;
     named_barrier(1, CT);                  // q_s (and k_s) are complete
-    float qr[4][8];                        // features 8 lane .. 8 lane + 7 of this warp's four heads
+    uint32_t qp[4][4];                     // features 8 lane .. 8 lane + 7 of this warp's four heads, packed bf16
 #pragma unroll
     for (int h = 0; h < 4; ++h) {
         const int head = min((warp & 1) * 4 + h, G - 1);
         const float4 qa = *reinterpret_cast<const float4*>(q_s + head * D + lane * 8);
         const float4 qb = *reinterpret_cast<const float4*>(q_s + head * D + lane * 8 + 4);
-        qr[h][0] = qa.x; qr[h][1] = qa.y; qr[h][2] = qa.z; qr[h][3] = qa.w;
-        qr[h][4] = qb.x; qr[h][5] = qb.y; qr[h][6] = qb.z; qr[h][7] = qb.w;
+        const __nv_bfloat162 p0 = __floats2bfloat162_rn(qa.x, qa.y), p1 = __floats2bfloat162_rn(qa.z, qa.w);
+        const __nv_bfloat162 p2 = __floats2bfloat162_rn(qb.x, qb.y), p3 = __floats2bfloat162_rn(qb.z, qb.w);
+        qp[h][0] = *reinterpret_cast<const uint32_t*>(&p0); qp[h][1] = *reinterpret_cast<const uint32_t*>(&p1);
+        qp[h][2] = *reinterpret_cast<const uint32_t*>(&p2); qp[h][3] = *reinterpret_cast<const uint32_t*>(&p3);
     }
 #pragma unroll 1
     for (int c0 = t0; c0 < t1 && ok; c0 += kAttnChunk, ++it) {
         // the producer streams the chunks of the split through the ring, ahead of this loop
         const int st = it % NS;
         if (!mbar_wait(S.full + st, (it / NS) & 1, mp.status)) { ok = false; break; }
+        QD_MARK(12);
         uint8_t* buf = S.stages + (size_t)st * kStreamStageBytes;
         if (owns_new && position >= c0 && position < c0 + kAttnChunk && warp == CW - 1) {
             // the step's own row: key from the normalised vector, value from the projection
@@ -898,18 +902,16 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
                 const int t = c0 + tl;
                 const uint4 kr = lds128(buf + tl * kAttnRowBytes + lane * 16);
                 const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w};
-                float kf[8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    kf[2 * j] = __uint_as_float(kw[j] << 16);
-                    kf[2 * j + 1] = __uint_as_float(kw[j] & 0xffff0000u);
-                }
+                // bf16 x bf16 products are exact in the mixed-precision fma: no unpacking
                 float dots[4];
 #pragma unroll
                 for (int h = 0; h < 4; ++h) {
-                    float dot = qr[h][0] * kf[0];
+                    float dot = 0.f;
 #pragma unroll
-                    for (int j = 1; j < 8; ++j) dot += qr[h][j] * kf[j];
+                    for (int j = 0; j < 4; ++j) {
+                        dot = fma_bf16_lo(qp[h][j], kw[j], dot);
+                        dot = fma_bf16_hi(qp[h][j], kw[j], dot);
+                    }
                     dots[h] = dot;
                 }
 #pragma unroll
@@ -923,6 +925,7 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
                 }
             }
         }
+        QD_MARK(13);
         named_barrier(1, CT);
         // softmax update: warp = head
         if (warp < G) {
@@ -935,6 +938,7 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
             if (lane < kAttnChunk) pr[warp * kAttnChunk + lane] = p;
             if (lane == 0) fix[warp] = fx;
         }
+        QD_MARK(14);
         named_barrier(1, CT);
         // weighted values: thread = (head, four features)
         if (ph_head < G) {

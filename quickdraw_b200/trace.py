@@ -42,10 +42,11 @@ def main() -> None:
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--position", type=int, default=600)
     ap.add_argument("--context", type=int, default=0, help="KV capacity (default: position + 64)")
+    ap.add_argument("--interval", type=int, default=4, help="every interval-th layer is an attention layer")
     ap.add_argument("--show", default="", help="comma-separated layers to print phase by phase")
     args = ap.parse_args()
     dev = "cuda"
-    cfg = synthetic.model_config(num_layers=args.layers, vocab_size=args.vocab)
+    cfg = synthetic.model_config(num_layers=args.layers, vocab_size=args.vocab, interval=args.interval)
     ckpt = synthetic.make_checkpoint(cfg, seed=0, device=dev)
     step = FusedStep(ckpt, persistent=True)
     state = DecodeState.allocate(cfg, args.context or args.position + 64, dev)
