@@ -8,15 +8,22 @@
 //
 // One block computes a 256-token x 256-row tile as two 128-token accumulators that share every
 // expanded weight stage.  Roles:
-//   warps 1..8  producers: 16-byte global loads of activations and weight codes into registers
-//               (one K step ahead), expansion to bf16, 16-byte stores into the shared-memory
-//               stage in the tensor core's K-major core-matrix layout (8 rows x 16 bytes per
-//               core matrix, no swizzle); warps 1..4 also run the epilogue
+//   warps 1..8  producers: 16-byte global loads of weight codes into registers (one K step
+//               ahead), expansion to bf16, 16-byte stores into the shared-memory stage in the
+//               tensor core's K-major core-matrix layout (8 rows x 16 bytes per core matrix, no
+//               swizzle); warps 1..4 also run the epilogue
+//   warp 9      plain product: one thread copies the 256 x 64 activation tile of every stage
+//               with one tiled TMA load (cp.async.bulk.tensor, 128-byte swizzle; rows past the
+//               end arrive as zeros) as soon as the stage is free
+//               grouped product: idle - the rows of a tile are gathered through the route
+//               order, so the producers copy them with 16-byte loads (no-swizzle layout)
 //   warp 0      allocates all 512 columns of tensor memory, issues 2 x 4 MMAs of 128x256x16 per
 //               stage and commits them to the stage's "empty" barrier
 // Stages: 3 x (36 KB activations + 36 KB weights) guarded by full / empty mbarriers.  Every wait
 // is bounded; a wait that runs out sets the status word, the block frees its tensor memory and
 // leaves.
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace {
@@ -27,11 +34,13 @@ constexpr int kTileM = 256;                 // tokens per tile: two halves of 12
 constexpr int kTileK = 64;                  // inputs per stage
 constexpr int kStages = 3;
 constexpr int kProducerWarps = 8;
-constexpr int kThreads = (1 + kProducerWarps) * 32;
+constexpr int kLoaderWarp = 1 + kProducerWarps;
+constexpr int kThreads = (2 + kProducerWarps) * 32;
 constexpr int kCorePitch = 144;             // bytes from one 128-byte core matrix to the next along K: the
                                             // 16 bytes of padding spread a warp's stores over all banks
 constexpr int kGroupPitch = (kTileK / 8) * kCorePitch;      // bytes between 8-row groups
-constexpr int kABytes = (kTileM / 8) * kGroupPitch;         // 18 KB
+constexpr int kABytes = (kTileM / 8) * kGroupPitch;         // 36 KB (the swizzled TMA tile uses the first 32 KB)
+constexpr int kATmaBytes = kTileM * kTileK * 2;             // bytes one activation tile load delivers
 constexpr int kBBytesMax = (256 / 8) * kGroupPitch;         // 36 KB at 256 rows
 constexpr int kStageBytes = kABytes + kBBytesMax;
 
@@ -87,6 +96,19 @@ QD_DEVINL uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
     return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
            ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
 }
+// The same for a tile a TMA load wrote with the 128-byte swizzle (rows of 128 bytes, 16-byte
+// pieces XOR-ed with the row index inside every 1024-byte group of 8 rows; the tile starts on a
+// 1024-byte boundary): layout type 2, sbo = 1024, lbo unused.  A K step of 16 inputs advances
+// the start address by 32 bytes inside the row.
+QD_DEVINL uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Tiled 2-D TMA load global -> shared; c0 = innermost coordinate (elements; c0 * 2 bytes must be
+// a multiple of 16), c1 = row.  Completion is counted in bytes on the mbarrier.
+QD_DEVINL void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
 // Instruction descriptor: fp32 accumulator (bits [4,6) = 1), bf16 A and B (bits [7,10) and
 // [10,13) = 1), both K-major (bits 15, 16 = 0), N >> 3 at [17,23), M >> 4 at [24,29).
 template <int TN>
@@ -114,20 +136,24 @@ QD_DEVINL uint4 expand8(uint32_t word, float scale) {
     return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
+template <bool DENSE>
 struct StageRegs {
-    uint4 xa[8];           // eight 16-byte pieces of activations
-    uint4 wc[2];           // two 16-byte pieces of codes (32 weights each)
-    uint16_t ws[2];        // their two block scales each
+    uint4 xa[DENSE ? 1 : 8];   // grouped: eight 16-byte pieces of activations
+    uint4 wc[2];               // two 16-byte pieces of codes (32 weights each)
+    uint16_t ws[2];            // their two block scales each
 };
 
-template <int TN>
+// DENSE: plain product (activation tiles by TMA through `xmap`); otherwise the grouped product.
+template <int TN, bool DENSE, int AHEAD>
 __global__ void __launch_bounds__(kThreads, 1)
-nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
+nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
     constexpr int kTileN = TN;
     constexpr int kTmemCols = 2 * TN;            // one 128 x TN fp32 accumulator per token half
     constexpr uint32_t kInstrDesc = instr_desc<TN>();
     constexpr int kWPieces = TN * 2;             // 16-byte code pieces of a stage: (row, 32-input half)
-    extern __shared__ __align__(1024) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // the swizzled tiles need a 1024-byte boundary in the shared address space
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
     uint64_t* empty = full + kStages;
     uint64_t* done = empty + kStages;
@@ -138,7 +164,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
     const int K = p.in_features, nk = K / kTileK;
     // rows of this tile: [t0, t_end) of the activations, or of the sorted routes of one expert
     int t0 = blockIdx.x * kTileM, t_end = p.tokens, expert = 0;
-    const bool grouped = p.order != nullptr;
+    constexpr bool grouped = !DENSE;
     if (grouped) {
         expert = blockIdx.x / p.chunks;
         t0 = p.boundaries[expert] + (blockIdx.x % p.chunks) * kTileM;
@@ -150,7 +176,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
     const int halves = (t_end - t0 > 128) ? kTileM / 128 : 1;      // a half without rows is not multiplied
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(full + s, kProducerWarps); mbar_init(empty + s, 1); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(full + s, kProducerWarps + (DENSE ? 1 : 0)); mbar_init(empty + s, 1); }
         mbar_init(done, 1);
         mbar_fence_init();
         *failed = 0;
@@ -174,35 +200,51 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll 1
                 for (int h = 0; h < halves; ++h)
 #pragma unroll
-                    for (int j = 0; j < kTileK / 16; ++j)
-                        umma_bf16(tmem + h * kTileN, smem_desc(a + h * (kABytes / 2) + j * 2 * kCorePitch, kCorePitch, kGroupPitch),
-                                  smem_desc(b + j * 2 * kCorePitch, kCorePitch, kGroupPitch), kInstrDesc, (s | j) ? 1u : 0u);
+                    for (int j = 0; j < kTileK / 16; ++j) {
+                        const uint64_t a_desc = DENSE ? smem_desc_sw128(a + h * (kATmaBytes / 2) + j * 32)
+                                                      : smem_desc(a + h * (kABytes / 2) + j * 2 * kCorePitch, kCorePitch, kGroupPitch);
+                        umma_bf16(tmem + h * kTileN, a_desc, smem_desc(b + j * 2 * kCorePitch, kCorePitch, kGroupPitch),
+                                  kInstrDesc, (s | j) ? 1u : 0u);
+                    }
                 umma_commit(empty + st);          // the stage is free once these MMAs have read it
             }
             if (ok) umma_commit(done);
             else *failed = 1;
         }
+    } else if (warp == kLoaderWarp) {
+        // ------------------------------------------------------- activation tiles by TMA
+        if (DENSE && lane == 0) {
+            for (int s = 0; s < nk; ++s) {
+                const int st = s % kStages;
+                if (s >= kStages && !mbar_wait(empty + st, ((s / kStages) - 1) & 1, p.status)) break;
+                mbar_expect_tx(full + st, kATmaBytes);
+                tma_load_2d(smem + st * kStageBytes, &xmap, s * kTileK, t0, full + st);
+            }
+        }
     } else {
         // ------------------------------------------------------------------- producers
         const int pt = tid - 32;                       // 0 .. 255
-        StageRegs cur, nxt;
+        StageRegs<DENSE> cur, nxt, far;      // K steps s, s + 1 and (AHEAD == 2) s + 2
         // the eight activation rows this thread copies pieces of (piece = (row, 8-input group))
-        const bf16* xrow[8];
+        const bf16* xrow[DENSE ? 1 : 8];
+        if (!DENSE) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int t = t0 + ((pt + i * 256) >> 3);
-            xrow[i] = nullptr;
-            if (t < t_end) {
-                int src = t;
-                if (grouped && p.by_token) src = p.order[t] / p.topk;
-                xrow[i] = p.x + (size_t)src * K + (pt & 7) * 8;
+            for (int i = 0; i < (DENSE ? 1 : 8); ++i) {
+                const int t = t0 + ((pt + i * 256) >> 3);
+                xrow[i] = nullptr;
+                if (t < t_end) {
+                    const int src = p.by_token ? p.order[t] / p.topk : t;
+                    xrow[i] = p.x + (size_t)src * K + (pt & 7) * 8;
+                }
             }
         }
-        auto fetch = [&](int s, StageRegs& r) {
+        auto fetch = [&](int s, StageRegs<DENSE>& r) {
             const int k0 = s * kTileK;
+            if (!DENSE) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                if (xrow[i]) r.xa[i] = __ldg(reinterpret_cast<const uint4*>(xrow[i] + k0));
+                for (int i = 0; i < (DENSE ? 1 : 8); ++i)
+                    if (xrow[i]) r.xa[i] = __ldg(reinterpret_cast<const uint4*>(xrow[i] + k0));
+            }
 #pragma unroll
             for (int i = 0; i < 2; ++i) {              // weights: piece = (row, 32-input half of the stage)
                 const int piece = pt + i * 256, row = piece >> 1, half = piece & 1;
@@ -216,15 +258,17 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
                 }
             }
         };
-        auto store = [&](int st, const StageRegs& r) {
+        auto store = [&](int st, const StageRegs<DENSE>& r) {
             uint8_t* a = smem + st * kStageBytes;
             uint8_t* b = a + kABytes;
             // rows without a token are not stored: an accumulator row depends on its own activation
             // row only, and rows past the end are never written out
+            if (!DENSE) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int piece = pt + i * 256;
-                if (xrow[i]) *reinterpret_cast<uint4*>(a + core_offset(piece >> 3, piece & 7)) = r.xa[i];
+                for (int i = 0; i < (DENSE ? 1 : 8); ++i) {
+                    const int piece = pt + i * 256;
+                    if (xrow[i]) *reinterpret_cast<uint4*>(a + core_offset(piece >> 3, piece & 7)) = r.xa[i];
+                }
             }
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
@@ -239,8 +283,10 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
         };
         bool ok = true;
         fetch(0, cur);
+        if (AHEAD == 2 && nk > 1) fetch(1, nxt);
         for (int s = 0; s < nk && ok; ++s) {
-            if (s + 1 < nk) fetch(s + 1, nxt);
+            if (AHEAD == 2) { if (s + 2 < nk) fetch(s + 2, far); }
+            else if (s + 1 < nk) fetch(s + 1, nxt);
             const int st = s % kStages;
             if (s >= kStages) ok = mbar_wait(empty + st, ((s / kStages) - 1) & 1, p.status);
             if (!ok) break;
@@ -249,6 +295,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
             __syncwarp();
             if (lane == 0) mbar_arrive(full + st);
             cur = nxt;
+            if (AHEAD == 2) nxt = far;
         }
         // --------------------------------------------------------------------- epilogue
         if (warp <= 4) {
@@ -303,32 +350,73 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p) {
 
 }  // namespace
 
-template <int TN>
+// cuTensorMapEncodeTiled through the runtime's driver entry point table (the library does not
+// link against the driver library).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+// Tensor map of the activations X[tokens, in_features] (bf16, row-major) with a box of one
+// stage tile: 64 inputs x 256 tokens, 128-byte swizzle, zeros outside the tensor.
+static int activation_map(const GemmParams& p, CUtensorMap* map) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return QD_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)p.in_features, (cuuint64_t)p.tokens};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.in_features * sizeof(bf16)};
+    const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kTileM};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(p.x), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? QD_OK : QD_ERR_LAUNCH;
+}
+
+template <int TN, bool DENSE, int AHEAD>
 static int launch_variant(const GemmParams& p, int row_tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)kStages * kStageBytes + (2 * kStages + 1) * 8 + 16;
+    // + 1024: the kernel moves its base up to a 1024-byte boundary
+    const size_t smem = (size_t)kStages * kStageBytes + (2 * kStages + 1) * 8 + 16 + 1024;
     static bool configured[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
     if (!configured[dev]) {
-        if (cudaFuncSetAttribute(nvfp4_gemm_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(nvfp4_gemm_kernel<TN, DENSE, AHEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return QD_ERR_LAUNCH;
         configured[dev] = true;
     }
+    alignas(64) CUtensorMap map = {};
+    if (DENSE) {
+        const int rc = activation_map(p, &map);
+        if (rc != QD_OK) return rc;
+    }
     dim3 grid(row_tiles, (p.out_features + TN - 1) / TN);
-    return qd_launch(nvfp4_gemm_kernel<TN>, grid, dim3(kThreads), smem, stream, false, p);
+    return qd_launch(nvfp4_gemm_kernel<TN, DENSE, AHEAD>, grid, dim3(kThreads), smem, stream, false, p, map);
 }
 
 // The widest weight tile that still gives every SM a tile (narrower tiles expand fewer weights
 // per block, so small problems finish sooner); `busy_row_tiles`: row tiles that will have rows.
+template <bool DENSE>
 static int launch_gemm(const GemmParams& p, int row_tiles, int busy_row_tiles, cudaStream_t stream) {
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
     const long long wide = (long long)busy_row_tiles * ((p.out_features + 255) / 256);
-    if (wide >= sms) return launch_variant<256>(p, row_tiles, stream);
-    if (4 * wide >= sms) return launch_variant<128>(p, row_tiles, stream);
-    return launch_variant<64>(p, row_tiles, stream);
+    // weight codes are fetched two K steps ahead where the registers allow it (plain product)
+    constexpr int kAhead = DENSE ? 2 : 1;
+    if (wide >= sms) return launch_variant<256, DENSE, kAhead>(p, row_tiles, stream);
+    if (4 * wide >= sms) return launch_variant<128, DENSE, kAhead>(p, row_tiles, stream);
+    return launch_variant<64, DENSE, kAhead>(p, row_tiles, stream);
 }
 
 // matmul(x, proj) for a 2-D x — quickdraw/kernel/triton/matvec.py:153-163 (NVFP4 branch).
@@ -343,7 +431,7 @@ extern "C" int qd_nvfp4_matmul(const void* x, const void* codes, const void* sca
     p.x = (const bf16*)x; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
     p.y = (bf16*)y; p.tokens = tokens; p.out_features = out_features; p.in_features = in_features; p.status = status;
     const int row_tiles = (tokens + kTileM - 1) / kTileM;
-    return launch_gemm(p, row_tiles, row_tiles, (cudaStream_t)stream);
+    return launch_gemm<true>(p, row_tiles, row_tiles, (cudaStream_t)stream);
 }
 
 // grouped_matmul(x, bank, grouping, routing=None) — quickdraw/kernel/triton/moe.py:99-151: the
@@ -373,5 +461,5 @@ extern "C" int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const v
     p.scales_stride = (long long)out_features * (in_features / 16);
     // about one busy row tile per expert that received routes (at most min(experts, routes))
     const int busy = experts < routes ? experts : routes;
-    return launch_gemm(p, experts * p.chunks, busy, (cudaStream_t)stream);
+    return launch_gemm<false>(p, experts * p.chunks, busy, (cudaStream_t)stream);
 }
