@@ -96,6 +96,12 @@ int qd_seq_attention(const void* qg, const void* k_new, const void* v_new, const
                      int rotary_dim, float theta, float eps, void* stream);
 int qd_seq_route_topk(const void* logits, int tokens, int experts, int topk, int32_t* ids, float* weights,
                       void* stream);
+/* The stable order of the chunk's routes by expert (quickdraw/kernel/triton/moe.py:60-97, the
+ * grouping the reference builds with a stable sort): ids int32 [routes], every id in
+ * [0, experts); order int32 [routes] = route index of each sorted row, boundaries int32
+ * [experts + 1] = first sorted row of each expert.  experts <= 1023. */
+int qd_seq_group_routes(const int32_t* ids, int routes, int experts, int32_t* order, int32_t* boundaries,
+                        void* stream);
 /* contributions bf16 [tokens, topk, hidden] in route order, ids [tokens, topk], shared
  * [tokens, hidden], strength bf16 [tokens] */
 int qd_seq_moe_combine(const void* contributions, const int32_t* ids, const void* shared,

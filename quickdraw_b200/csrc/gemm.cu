@@ -86,6 +86,7 @@ QD_DEVINL void tmem_load32(uint32_t addr, uint32_t (&v)[32]) {
                    "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                  : "r"(addr) : "memory");
 }
+QD_DEVINL void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 QD_DEVINL void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrix = 8 rows x 16 bytes stored
@@ -236,6 +237,17 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
                     const int src = p.by_token ? p.order[t] / p.topk : t;
                     xrow[i] = p.x + (size_t)src * K + (pt & 7) * 8;
                 }
+            }
+        }
+        if (!DENSE) {
+            // an expert's weights are read once, from DRAM: ask for this thread's whole weight row
+            // now, so that the K loop's loads (one step ahead) find it in L2
+            const int n = n0 + pt;
+            if (pt < kTileN && n < p.out_features) {
+                const uint8_t* row_codes = codes + (size_t)n * (K / 2);
+                const uint8_t* row_scales = scales + (size_t)n * (K / 16);
+                for (int off = 0; off < K / 2; off += 128) prefetch_l2(row_codes + off);
+                for (int off = 0; off < K / 16; off += 128) prefetch_l2(row_scales + off);
             }
         }
         auto fetch = [&](int s, StageRegs<DENSE>& r) {

@@ -35,7 +35,8 @@ __global__ void seq_add_norm_kernel(const bf16* __restrict__ x, const bf16* __re
 }
 
 // --------------------------------------------------- small bf16 projection of every token
-// y[t, n] = bf16( sum_k x[t, k] w[n, k] ): one warp per (token, output row).
+// y[t, n] = bf16( sum_k x[t, k] w[n, k] ): one warp per (token, output row), 16-byte loads where
+// the width allows them.
 __global__ void seq_bf16_matmul_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
                                        int rows, int width) {
     const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -44,34 +45,176 @@ __global__ void seq_bf16_matmul_kernel(const bf16* __restrict__ x, const bf16* _
     const bf16* row = w + (size_t)n * width;
     const bf16* xt = x + (size_t)t * width;
     float acc = 0.f;
-    for (int i = lane; i < width; i += 32) acc += ld_bf16(row + i) * ld_bf16(xt + i);
+    if ((width & 7) == 0) {
+        for (int i = lane * 8; i < width; i += 256) {
+            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(row + i)), xv = __ldg(reinterpret_cast<const uint4*>(xt + i));
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w}, xx[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                acc += bf16_bits_to_float(ww[q] & 0xffffu) * bf16_bits_to_float(xx[q] & 0xffffu);
+                acc += bf16_bits_to_float(ww[q] >> 16) * bf16_bits_to_float(xx[q] >> 16);
+            }
+        }
+    } else {
+        for (int i = lane; i < width; i += 32) acc += ld_bf16(row + i) * ld_bf16(xt + i);
+    }
     acc = warp_sum(acc);
     if (lane == 0) y[(size_t)t * rows + n] = __float2bfloat16_rn(acc);
 }
 
 // ------------------------------------------------------------- DeltaNet short convolution
-// One thread per channel walks the chunk: window = [history | new], tap products rounded to
-// bf16, fp32 sum, SiLU, bf16; the history ends up holding the last width - 1 inputs.
-__global__ void seq_conv_kernel(const bf16* __restrict__ mixed, const bf16* __restrict__ taps, bf16* __restrict__ state,
-                                bf16* __restrict__ out, int tokens, int channels, int width) {
+// One thread per (token, channel): window = [history | new] ending at the token, tap products
+// rounded to bf16, fp32 sum from the oldest tap on, SiLU, bf16.  A second kernel then leaves the
+// last width - 1 inputs in the history (it runs after every read of the old history).
+QD_DEVINL float conv_input(const bf16* __restrict__ mixed, const bf16* __restrict__ state, int index, int c,
+                           int channels, int width) {
+    return index < 0 ? ld_bf16(state + (size_t)c * (width - 1) + index + width - 1)
+                     : ld_bf16(mixed + (size_t)index * channels + c);
+}
+__global__ void seq_conv_kernel(const bf16* __restrict__ mixed, const bf16* __restrict__ taps,
+                                const bf16* __restrict__ state, bf16* __restrict__ out, int channels, int width) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (c >= channels) return;
+    float acc = 0.f;
+    for (int k = 0; k < width; ++k)
+        acc += round_bf16(conv_input(mixed, state, t - (width - 1) + k, c, channels, width) * ld_bf16(taps + (size_t)c * width + k));
+    out[(size_t)t * channels + c] = __float2bfloat16_rn(silu_precise(acc));
+}
+__global__ void seq_conv_state_kernel(const bf16* __restrict__ mixed, bf16* state, int tokens, int channels, int width) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= channels) return;
-    float hist[8], w[8];
-    for (int t = 0; t < width - 1; ++t) hist[t] = ld_bf16(state + (size_t)c * (width - 1) + t);
-    for (int t = 0; t < width; ++t) w[t] = ld_bf16(taps + (size_t)c * width + t);
-    for (int t = 0; t < tokens; ++t) {
-        const float fresh = ld_bf16(mixed + (size_t)t * channels + c);
-        float acc = 0.f;
-        for (int k = 0; k < width - 1; ++k) acc += round_bf16(hist[k] * w[k]);
-        acc += round_bf16(fresh * w[width - 1]);
-        for (int k = 0; k + 1 < width - 1; ++k) hist[k] = hist[k + 1];
-        if (width > 1) hist[width - 2] = fresh;
-        out[(size_t)t * channels + c] = __float2bfloat16_rn(silu_precise(acc));
+    bf16 keep[8];
+    for (int j = 0; j < width - 1; ++j) {
+        const int index = tokens - (width - 1) + j;
+        keep[j] = index < 0 ? state[(size_t)c * (width - 1) + index + width - 1] : mixed[(size_t)index * channels + c];
     }
-    for (int t = 0; t < width - 1; ++t) state[(size_t)c * (width - 1) + t] = __float2bfloat16_rn(hist[t]);
+    for (int j = 0; j < width - 1; ++j) state[(size_t)c * (width - 1) + j] = keep[j];
 }
 
-// ------------------------------------------------------------------- DeltaNet recurrence
+// ------------------------------------------------- DeltaNet recurrence, key dimension 128
+// Block = (value head, 32 value columns), four warps; a warp owns 8 columns, a lane one column
+// and one quarter of the 128 keys: 32 state entries in registers for the whole chunk, the sums
+// over keys finish with two shuffles, so the token loop has no block-wide barrier.  The inputs
+// of 16 tokens at a time (normalised key and query in fp32, the gates, the value columns) are
+// prepared in shared memory by the four warps, one batch ahead of the recurrence: the global
+// loads of batch n + 1 are issued before batch n is walked and finished after it.
+// Arithmetic per token as in the single-token kernel (quickdraw/kernel/triton/delta.py:41-78):
+// S *= decay; pred = S^T k; S += k (x) beta (v - pred); out = S^T q.
+constexpr int kRecBatch = 16;
+constexpr int kRecQuarter = 36;              // floats per key quarter in shared memory (32 + 4: no bank conflicts)
+
+struct RecPrefetch { uint2 k[kRecBatch / 4], q[kRecBatch / 4]; bf16 v[kRecBatch / 4], a[kRecBatch / 4], b[kRecBatch / 4]; };
+
+__global__ void __launch_bounds__(128)
+seq_recurrence128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ a, const bf16* __restrict__ b,
+                         const bf16* __restrict__ a_log, const bf16* __restrict__ dt_bias, float* __restrict__ state,
+                         bf16* __restrict__ out, int tokens, int hk, int hv, int dv) {
+    constexpr int dk = 128;
+    __shared__ __align__(16) float skn[2][kRecBatch][4 * kRecQuarter];
+    __shared__ __align__(16) float sqn[2][kRecBatch][4 * kRecQuarter];
+    __shared__ float sv[2][kRecBatch][32];
+    __shared__ float sgate[2][kRecBatch][2];
+    const int head = blockIdx.x, c0 = blockIdx.y * 32;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quarter = lane & 3, col = warp * 8 + (lane >> 2);
+    const int key_head = head / (hv / hk);
+    const bool col_ok = c0 + col < dv;
+    const int channels = 2 * hk * dk + hv * dv;
+    const float a_decay = ld_bf16(a_log + head), bias = ld_bf16(dt_bias + head);
+    float* tile = state + (size_t)head * dk * dv + (size_t)quarter * 32 * dv + c0 + col;
+    float s[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) s[j] = col_ok ? tile[(size_t)j * dv] : 0.f;
+
+    // warp w prepares tokens w, w + 4, w + 8, w + 12 of a batch; lane l holds keys 4l .. 4l + 3
+    auto issue = [&](int batch, RecPrefetch& r) {
+#pragma unroll
+        for (int i = 0; i < kRecBatch / 4; ++i) {
+            const int t = batch * kRecBatch + warp + 4 * i;
+            if (t >= tokens) continue;
+            const bf16* row = qkv + (size_t)t * channels;
+            r.q[i] = __ldg(reinterpret_cast<const uint2*>(row + (size_t)key_head * dk + 4 * lane));
+            r.k[i] = __ldg(reinterpret_cast<const uint2*>(row + (size_t)(hk + key_head) * dk + 4 * lane));
+            r.v[i] = (c0 + lane < dv) ? row[(size_t)2 * hk * dk + (size_t)head * dv + c0 + lane] : __float2bfloat16_rn(0.f);
+            r.a[i] = a[(size_t)t * hv + head];
+            r.b[i] = b[(size_t)t * hv + head];
+        }
+    };
+    auto finish = [&](int batch, const RecPrefetch& r) {
+        const int buf = batch & 1;
+#pragma unroll
+        for (int i = 0; i < kRecBatch / 4; ++i) {
+            const int slot = warp + 4 * i;
+            if (batch * kRecBatch + slot >= tokens) continue;
+            const float q4[4] = {bf16_bits_to_float(r.q[i].x & 0xffffu), bf16_bits_to_float(r.q[i].x >> 16),
+                                 bf16_bits_to_float(r.q[i].y & 0xffffu), bf16_bits_to_float(r.q[i].y >> 16)};
+            const float k4[4] = {bf16_bits_to_float(r.k[i].x & 0xffffu), bf16_bits_to_float(r.k[i].x >> 16),
+                                 bf16_bits_to_float(r.k[i].y & 0xffffu), bf16_bits_to_float(r.k[i].y >> 16)};
+            float qq = 0.f, kk = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { qq += q4[e] * q4[e]; kk += k4[e] * k4[e]; }
+            const float qscale = rsqrtf(warp_sum(qq) + 1e-6f), kscale = rsqrtf(warp_sum(kk) + 1e-6f);
+            const int at = (lane >> 3) * kRecQuarter + (lane & 7) * 4;
+            *reinterpret_cast<float4*>(&skn[buf][slot][at]) = make_float4(k4[0] * kscale, k4[1] * kscale, k4[2] * kscale, k4[3] * kscale);
+            *reinterpret_cast<float4*>(&sqn[buf][slot][at]) =
+                make_float4((q4[0] * qscale) / sqrtf((float)dk), (q4[1] * qscale) / sqrtf((float)dk),
+                            (q4[2] * qscale) / sqrtf((float)dk), (q4[3] * qscale) / sqrtf((float)dk));
+            sv[buf][slot][lane] = __bfloat162float(r.v[i]);
+            if (lane == 0) {
+                const float alpha = __bfloat162float(r.a[i]) + bias;
+                sgate[buf][slot][0] = expf(-expf(a_decay) * softplus_precise(alpha));
+                sgate[buf][slot][1] = sigmoid_precise(__bfloat162float(r.b[i]));
+            }
+        }
+    };
+
+    const int batches = (tokens + kRecBatch - 1) / kRecBatch;
+    RecPrefetch pre;
+    issue(0, pre);
+    finish(0, pre);
+    __syncthreads();
+    for (int n = 0; n < batches; ++n) {
+        const int buf = n & 1;
+        if (n + 1 < batches) issue(n + 1, pre);
+        const int count = min(kRecBatch, tokens - n * kRecBatch);
+#pragma unroll 1
+        for (int i = 0; i < count; ++i) {
+            const float4* kp = reinterpret_cast<const float4*>(&skn[buf][i][quarter * kRecQuarter]);
+            const float4* qp = reinterpret_cast<const float4*>(&sqn[buf][i][quarter * kRecQuarter]);
+            const float decay = sgate[buf][i][0], beta = sgate[buf][i][1], v = sv[buf][i][col];
+            float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 k4 = kp[j];
+                s[4 * j] *= decay; s[4 * j + 1] *= decay; s[4 * j + 2] *= decay; s[4 * j + 3] *= decay;
+                p0 += s[4 * j] * k4.x; p1 += s[4 * j + 1] * k4.y; p2 += s[4 * j + 2] * k4.z; p3 += s[4 * j + 3] * k4.w;
+            }
+            float pred = (p0 + p1) + (p2 + p3);
+            pred += __shfl_xor_sync(0xffffffffu, pred, 1);
+            pred += __shfl_xor_sync(0xffffffffu, pred, 2);
+            const float corr = beta * (v - pred);
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 k4 = kp[j], q4 = qp[j];
+                s[4 * j] += k4.x * corr; s[4 * j + 1] += k4.y * corr; s[4 * j + 2] += k4.z * corr; s[4 * j + 3] += k4.w * corr;
+                o0 += s[4 * j] * q4.x; o1 += s[4 * j + 1] * q4.y; o2 += s[4 * j + 2] * q4.z; o3 += s[4 * j + 3] * q4.w;
+            }
+            float o = (o0 + o1) + (o2 + o3);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (quarter == 0 && col_ok)
+                out[(size_t)(n * kRecBatch + i) * hv * dv + (size_t)head * dv + c0 + col] = __float2bfloat16_rn(o);
+        }
+        if (n + 1 < batches) finish(n + 1, pre);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+        if (col_ok) tile[(size_t)j * dv] = s[j];
+}
+
+// ----------------------------------------------- DeltaNet recurrence, other key dimensions
 // The single-token kernel (block = value head x 32 columns, 8 key groups x 32 columns, 16 state
 // entries per thread) in a loop over the chunk; the state stays in registers in between.
 __global__ void __launch_bounds__(256)
@@ -279,6 +422,46 @@ __global__ void seq_route_kernel(const bf16* __restrict__ logits, int experts, i
                     threadIdx.x);
 }
 
+// --------------------------------------------------------- routes of a chunk by expert
+// The stable order of the chunk's (token, slot) routes by expert id, as the reference groups
+// them (quickdraw/kernel/triton/moe.py:60-97): order[r] = route index of sorted row r,
+// boundaries[e] = first sorted row of expert e.  One block; thread e counts and then places
+// expert e's routes in ascending route index, reading the ids through shared memory.
+constexpr int kGroupTile = 2048;
+__global__ void __launch_bounds__(1024)
+seq_group_routes_kernel(const int32_t* __restrict__ ids, int routes, int experts, int32_t* __restrict__ order,
+                        int32_t* __restrict__ boundaries) {
+    __shared__ int32_t tile[kGroupTile];
+    __shared__ int32_t start[1025];
+    const int e = threadIdx.x;
+    int count = 0;
+    for (int r0 = 0; r0 < routes; r0 += kGroupTile) {
+        const int n = min(kGroupTile, routes - r0);
+        __syncthreads();
+        for (int i = e; i < n; i += blockDim.x) tile[i] = ids[r0 + i];
+        __syncthreads();
+        if (e < experts)
+            for (int i = 0; i < n; ++i) count += tile[i] == e;
+    }
+    start[e + 1] = e < experts ? count : 0;
+    if (e == 0) start[0] = 0;
+    __syncthreads();
+    if (e == 0)
+        for (int i = 0; i < experts; ++i) start[i + 1] += start[i];
+    __syncthreads();
+    if (e <= experts) boundaries[e] = start[e];
+    int at = start[e];
+    for (int r0 = 0; r0 < routes; r0 += kGroupTile) {
+        const int n = min(kGroupTile, routes - r0);
+        __syncthreads();
+        for (int i = e; i < n; i += blockDim.x) tile[i] = ids[r0 + i];
+        __syncthreads();
+        if (e < experts)
+            for (int i = 0; i < n; ++i)
+                if (tile[i] == e) order[at++] = r0 + i;
+    }
+}
+
 // --------------------------------------------------------------------------- MoE combine
 // out[t] = bf16( bf16(sum of the token's routed rows in ascending expert id) +
 //                bf16(shared[t] * bf16(sigmoid(strength[t]))) )
@@ -327,8 +510,13 @@ extern "C" int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tok
 extern "C" int qd_seq_gdn_conv(const void* mixed, const void* taps, void* conv_state, void* out, int tokens,
                                int channels, int width, void* stream) {
     QD_CHECK_ARG(mixed && taps && out && tokens > 0 && channels > 0 && width >= 1 && width <= 8 && (width == 1 || conv_state));
-    seq_conv_kernel<<<(channels + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
-        (const bf16*)mixed, (const bf16*)taps, (bf16*)conv_state, (bf16*)out, tokens, channels, width);
+    if (tokens > 65535) return QD_ERR_UNSUPPORTED;
+    seq_conv_kernel<<<dim3((channels + 127) / 128, tokens), 128, 0, (cudaStream_t)stream>>>(
+        (const bf16*)mixed, (const bf16*)taps, (const bf16*)conv_state, (bf16*)out, channels, width);
+    if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
+    if (width > 1)
+        seq_conv_state_kernel<<<(channels + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
+            (const bf16*)mixed, (bf16*)conv_state, tokens, channels, width);
     return qd_launch_status();
 }
 
@@ -338,6 +526,12 @@ extern "C" int qd_seq_gdn_recurrence(const void* conv_qkv, const void* a, const 
     QD_CHECK_ARG(conv_qkv && a && b && a_log && dt_bias && rec_state && out && tokens > 0);
     QD_CHECK_ARG(key_heads > 0 && value_heads % key_heads == 0 && key_dim > 0 && value_dim > 0);
     if (key_dim > 128) return QD_ERR_UNSUPPORTED;
+    if (key_dim == 128) {
+        seq_recurrence128_kernel<<<dim3(value_heads, (value_dim + 31) / 32), 128, 0, (cudaStream_t)stream>>>(
+            (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
+            (bf16*)out, tokens, key_heads, value_heads, value_dim);
+        return qd_launch_status();
+    }
     seq_recurrence_kernel<<<dim3(value_heads, (value_dim + 31) / 32), 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
         (bf16*)out, tokens, key_heads, value_heads, key_dim, value_dim);
@@ -368,6 +562,15 @@ extern "C" int qd_seq_route_topk(const void* logits, int tokens, int experts, in
     QD_CHECK_ARG(logits && ids && weights && tokens > 0 && topk >= 1 && topk <= 32 && topk <= experts);
     if (experts > 256) return QD_ERR_UNSUPPORTED;
     seq_route_kernel<<<tokens, 32, 0, (cudaStream_t)stream>>>((const bf16*)logits, experts, topk, ids, weights);
+    return qd_launch_status();
+}
+
+extern "C" int qd_seq_group_routes(const int32_t* ids, int routes, int experts, int32_t* order, int32_t* boundaries,
+                                   void* stream) {
+    QD_CHECK_ARG(ids && order && boundaries && routes > 0 && experts > 0);
+    if (experts > 1023) return QD_ERR_UNSUPPORTED;
+    const int threads = ((experts + 1 + 31) / 32) * 32;
+    seq_group_routes_kernel<<<1, threads, 0, (cudaStream_t)stream>>>(ids, routes, experts, order, boundaries);
     return qd_launch_status();
 }
 

@@ -30,7 +30,6 @@ class ChunkPrefill:
         self.gammas = [((1 + layer.input_layernorm.float()).contiguous(),
                         (1 + layer.post_attention_layernorm.float()).contiguous()) for layer in ckpt.layers]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.expert_index = torch.arange(c.num_experts + 1, device=self.device)
         for layer in ckpt.layers:
             assert layer.moe.experts_gate.weight.shape[0] == c.num_experts, "the whole model on one GPU"
 
@@ -109,10 +108,10 @@ class ChunkPrefill:
         weights = self._empty(tokens, topk, dtype=torch.float32)
         call("qd_seq_route_topk", ptr(logits), tokens, c.num_experts, topk, ptr(ids), ptr(weights), stream_of(x))
         # the routes sorted by expert (stable), as the reference groups them
-        sorted_ids, order = ids.flatten().sort(stable=True)
-        boundaries = torch.searchsorted(sorted_ids, self.expert_index.to(sorted_ids.dtype)).to(torch.int32)
-        order = order.to(torch.int32)
         routes = tokens * topk
+        order = self._empty(routes, dtype=torch.int32)
+        boundaries = self._empty(c.num_experts + 1, dtype=torch.int32)
+        call("qd_seq_group_routes", ptr(ids), routes, c.num_experts, ptr(order), ptr(boundaries), stream_of(x))
         gate = self._grouped(x, w.experts_gate, order, boundaries, routes, topk, by_token=True, scatter=False)
         up = self._grouped(x, w.experts_up, order, boundaries, routes, topk, by_token=True, scatter=False)
         hidden = self._swiglu(gate, up)

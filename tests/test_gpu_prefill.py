@@ -69,3 +69,53 @@ def test_grouped_matmul_matches_per_route_matvec(cuda_device):
         torch.testing.assert_close(plain[r].float(), want.float(), rtol=0.025, atol=0.003)
         want_routed = kernels.expert_gemv(x[token], bank, ids.flatten()[route:route + 1], weights.flatten()[route:route + 1])[0]
         torch.testing.assert_close(routed[route].float(), want_routed.float(), rtol=0.025, atol=0.003)
+
+
+@pytest.mark.parametrize("key_dim,value_dim,tokens", [(128, 128, 37), (128, 128, 3), (128, 96, 16), (64, 64, 21)])
+def test_sequence_conv_and_recurrence_match_single_token_kernels(cuda_device, key_dim, value_dim, tokens):
+    """The chunk forms of the DeltaNet convolution and recurrence against the single-token
+    kernels walked over the same tokens (convolution bit-exact; recurrence up to summation
+    order).  Key dimension 128 takes the register-resident kernel, 64 the general one."""
+    from quickdraw_b200._lib import call, ptr, stream_of
+    hk, hv, width = 2, 4, 4
+    channels = 2 * hk * key_dim + hv * value_dim
+    src = synthetic.Source(17, "cpu")
+    mixed = src.normal("mixed", tokens, channels).to(cuda_device)
+    taps = src.normal("taps", channels, width, std=0.5).to(cuda_device)
+    a, b = src.normal("a", tokens, hv).to(cuda_device), src.normal("b", tokens, hv).to(cuda_device)
+    a_log, dt_bias = src.normal("alog", hv, std=0.5).to(cuda_device), src.normal("dt", hv).to(cuda_device)
+    conv0 = src.normal("conv0", channels, width - 1).to(cuda_device)
+    rec0 = src.normal("rec0", hv, key_dim, value_dim, std=0.1).float().to(cuda_device)
+    s = stream_of(mixed)
+
+    conv_loop, rec_loop = conv0.clone(), rec0.clone()
+    conv_rows, out_rows = torch.empty_like(mixed), torch.empty(tokens, hv * value_dim, dtype=torch.bfloat16, device=cuda_device)
+    for t in range(tokens):
+        call("qd_gdn_conv", ptr(mixed[t]), ptr(taps), ptr(conv_loop), ptr(conv_rows[t]), channels, width, s)
+        call("qd_gdn_recurrence", ptr(conv_rows[t]), ptr(a[t]), ptr(b[t]), ptr(a_log), ptr(dt_bias), ptr(rec_loop),
+             ptr(out_rows[t]), hk, hv, key_dim, value_dim, 0, s)
+
+    conv_seq, rec_seq = conv0.clone(), rec0.clone()
+    conv_out, out = torch.empty_like(mixed), torch.empty_like(out_rows)
+    call("qd_seq_gdn_conv", ptr(mixed), ptr(taps), ptr(conv_seq), ptr(conv_out), tokens, channels, width, s)
+    call("qd_seq_gdn_recurrence", ptr(conv_out), ptr(a), ptr(b), ptr(a_log), ptr(dt_bias), ptr(rec_seq), ptr(out),
+         tokens, hk, hv, key_dim, value_dim, s)
+    torch.cuda.synchronize()
+    assert torch.equal(conv_out, conv_rows) and torch.equal(conv_seq, conv_loop)
+    assert O.rel_l2(rec_seq.cpu(), rec_loop.cpu()) < 1e-4
+    assert O.rel_l2(out.cpu(), out_rows.cpu()) < 1e-2
+
+
+@pytest.mark.parametrize("routes,experts", [(4088, 256), (24, 16), (5000, 7), (1, 3)])
+def test_group_routes_is_the_stable_sort_by_expert(cuda_device, routes, experts):
+    from quickdraw_b200._lib import call, ptr, stream_of
+    gen = torch.Generator().manual_seed(routes)
+    ids = torch.randint(0, experts, (routes,), generator=gen).to(torch.int32).to(cuda_device)
+    if routes > 100:
+        ids[ids == 3] = 2                                   # an expert without routes
+    order = torch.empty(routes, dtype=torch.int32, device=cuda_device)
+    boundaries = torch.empty(experts + 1, dtype=torch.int32, device=cuda_device)
+    call("qd_seq_group_routes", ptr(ids), routes, experts, ptr(order), ptr(boundaries), stream_of(ids))
+    sorted_ids, want_order = ids.sort(stable=True)
+    want_boundaries = torch.searchsorted(sorted_ids, torch.arange(experts + 1, device=cuda_device, dtype=torch.int32))
+    assert torch.equal(order.long(), want_order) and torch.equal(boundaries.long(), want_boundaries)
