@@ -33,9 +33,12 @@ constexpr int kTileM = 256;                 // tokens per tile: two halves of 12
 // large problems, 128 or 64 where 256 would leave most SMs without a tile
 constexpr int kTileK = 64;                  // inputs per stage
 constexpr int kStages = 3;
-constexpr int kProducerWarps = 8;
-constexpr int kLoaderWarp = 1 + kProducerWarps;
-constexpr int kThreads = (2 + kProducerWarps) * 32;
+// Producer warps: 8 for the plain product (they only expand weights), 16 for the grouped product
+// (they also gather the activation rows, and an expert's weights come from DRAM, not from L2:
+// more warps keep more loads in flight; measured 171 -> 149 us on the gate bank of a
+// 511-token chunk).  The block is warp 0 + producers + loader warp.
+constexpr int producer_warps(bool dense) { return dense ? 8 : 16; }
+constexpr int block_threads(bool dense) { return (2 + producer_warps(dense)) * 32; }
 constexpr int kCorePitch = 144;             // bytes from one 128-byte core matrix to the next along K: the
                                             // 16 bytes of padding spread a warp's stores over all banks
 constexpr int kGroupPitch = (kTileK / 8) * kCorePitch;      // bytes between 8-row groups
@@ -50,9 +53,9 @@ struct GemmParams {
     unsigned int* status;
     // grouped form (routed experts of a chunk of tokens; order == NULL: plain matmul).  Routes =
     // (token, slot) pairs sorted by expert: order[r] = route index of sorted row r, rows
-    // [boundaries[e], boundaries[e + 1]) belong to expert e.  Block x = expert * chunks + chunk.
+    // [boundaries[e], boundaries[e + 1]) belong to expert e.
     const int32_t* order; const int32_t* boundaries; const float* routing;
-    int topk, chunks, by_token, scatter, global_per_expert;
+    int topk, experts, by_token, scatter, global_per_expert;
     long long codes_stride, scales_stride;       // bytes between experts of the bank
 };
 
@@ -110,6 +113,8 @@ QD_DEVINL void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, ui
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
+// (A and B must have the same format: a descriptor with bf16 activations and f16 weights, which
+// would save the weights' f16 -> bf16 conversion, is rejected as an illegal instruction.)
 // Instruction descriptor: fp32 accumulator (bits [4,6) = 1), bf16 A and B (bits [7,10) and
 // [10,13) = 1), both K-major (bits 15, 16 = 0), N >> 3 at [17,23), M >> 4 at [24,29).
 template <int TN>
@@ -139,15 +144,20 @@ QD_DEVINL uint4 expand8(uint32_t word, float scale) {
 
 template <bool DENSE>
 struct StageRegs {
-    uint4 xa[DENSE ? 1 : 8];   // grouped: eight 16-byte pieces of activations
-    uint4 wc[2];               // two 16-byte pieces of codes (32 weights each)
-    uint16_t ws[2];            // their two block scales each
+    static constexpr int kXPieces = kTileM * (kTileK / 8) / (producer_warps(DENSE) * 32);   // 16-byte activation pieces per thread
+    static constexpr int kWPieces = 256 * 2 / (producer_warps(DENSE) * 32);                 // 16-byte code pieces per thread
+    uint4 xa[DENSE ? 1 : kXPieces];   // grouped: 16-byte pieces of activations
+    uint4 wc[kWPieces];               // 16-byte pieces of codes (32 weights each)
+    uint16_t ws[kWPieces];            // their two block scales each
 };
 
 // DENSE: plain product (activation tiles by TMA through `xmap`); otherwise the grouped product.
 template <int TN, bool DENSE, int AHEAD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(block_threads(DENSE), 1)
 nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+    constexpr int kProducerWarps = producer_warps(DENSE), kProducerThreads = kProducerWarps * 32;
+    constexpr int kThreads = block_threads(DENSE), kLoaderWarp = 1 + kProducerWarps;
+    constexpr int kXPieces = StageRegs<DENSE>::kXPieces, kWPiecesPerThread = StageRegs<DENSE>::kWPieces;
     constexpr int kTileN = TN;
     constexpr int kTmemCols = 2 * TN;            // one 128 x TN fp32 accumulator per token half
     constexpr uint32_t kInstrDesc = instr_desc<TN>();
@@ -167,10 +177,37 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     int t0 = blockIdx.x * kTileM, t_end = p.tokens, expert = 0;
     constexpr bool grouped = !DENSE;
     if (grouped) {
-        expert = blockIdx.x / p.chunks;
-        t0 = p.boundaries[expert] + (blockIdx.x % p.chunks) * kTileM;
-        t_end = p.boundaries[expert + 1];
-        if (t0 >= t_end) return;                       // nothing routed here (whole block, before any barrier)
+        // Block x is the x-th non-empty row tile in expert order (the grid holds an upper bound of
+        // their number, not experts x tiles per expert): the boundaries go through shared memory
+        // (the first stage is not in use yet), warp 0 sums the tiles of the experts until it
+        // passes x.  Blocks past the last tile leave here, before any barrier object exists.
+        __shared__ int found[2];
+        int* bounds = reinterpret_cast<int*>(smem);
+        for (int e = tid; e <= p.experts; e += kThreads) bounds[e] = p.boundaries[e];
+        if (tid == 0) found[0] = -1;
+        __syncthreads();
+        if (warp == 0) {
+            const int want = blockIdx.x;
+            int total = 0;
+            for (int e0 = 0; e0 < p.experts && total <= want; e0 += 32) {
+                const int e = e0 + lane;
+                const int tiles = e < p.experts ? (bounds[e + 1] - bounds[e] + kTileM - 1) / kTileM : 0;
+                int incl = tiles;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, d);
+                    if (lane >= d) incl += up;
+                }
+                const int before = total + incl - tiles;
+                if (want >= before && want < before + tiles) { found[0] = e; found[1] = want - before; }
+                total += __shfl_sync(0xffffffffu, incl, 31);
+            }
+        }
+        __syncthreads();
+        expert = found[0];
+        if (expert < 0) return;
+        t0 = bounds[expert] + found[1] * kTileM;
+        t_end = bounds[expert + 1];
     }
     const uint8_t* codes = p.codes + (long long)expert * p.codes_stride;
     const uint8_t* scales = p.scales + (long long)expert * p.scales_stride;
@@ -224,14 +261,14 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         }
     } else {
         // ------------------------------------------------------------------- producers
-        const int pt = tid - 32;                       // 0 .. 255
+        const int pt = tid - 32;                       // 0 .. kProducerThreads - 1
         StageRegs<DENSE> cur, nxt, far;      // K steps s, s + 1 and (AHEAD == 2) s + 2
         // the eight activation rows this thread copies pieces of (piece = (row, 8-input group))
-        const bf16* xrow[DENSE ? 1 : 8];
+        const bf16* xrow[DENSE ? 1 : kXPieces];
         if (!DENSE) {
 #pragma unroll
-            for (int i = 0; i < (DENSE ? 1 : 8); ++i) {
-                const int t = t0 + ((pt + i * 256) >> 3);
+            for (int i = 0; i < (DENSE ? 1 : kXPieces); ++i) {
+                const int t = t0 + ((pt + i * kProducerThreads) >> 3);
                 xrow[i] = nullptr;
                 if (t < t_end) {
                     const int src = p.by_token ? p.order[t] / p.topk : t;
@@ -243,7 +280,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
             // an expert's weights are read once, from DRAM: ask for this thread's whole weight row
             // now, so that the K loop's loads (one step ahead) find it in L2
             const int n = n0 + pt;
-            if (pt < kTileN && n < p.out_features) {
+            if (pt < kTileN && n < p.out_features) {   // (at least 256 producer threads)
                 const uint8_t* row_codes = codes + (size_t)n * (K / 2);
                 const uint8_t* row_scales = scales + (size_t)n * (K / 16);
                 for (int off = 0; off < K / 2; off += 128) prefetch_l2(row_codes + off);
@@ -254,12 +291,12 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
             const int k0 = s * kTileK;
             if (!DENSE) {
 #pragma unroll
-                for (int i = 0; i < (DENSE ? 1 : 8); ++i)
+                for (int i = 0; i < (DENSE ? 1 : kXPieces); ++i)
                     if (xrow[i]) r.xa[i] = __ldg(reinterpret_cast<const uint4*>(xrow[i] + k0));
             }
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {              // weights: piece = (row, 32-input half of the stage)
-                const int piece = pt + i * 256, row = piece >> 1, half = piece & 1;
+            for (int i = 0; i < kWPiecesPerThread; ++i) {   // weights: piece = (row, 32-input half of the stage)
+                const int piece = pt + i * kProducerThreads, row = piece >> 1, half = piece & 1;
                 const int n = n0 + row;
                 if (piece < kWPieces && n < p.out_features) {
                     r.wc[i] = __ldg(reinterpret_cast<const uint4*>(codes + (size_t)n * (K / 2) + (k0 + half * 32) / 2));
@@ -277,14 +314,14 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
             // row only, and rows past the end are never written out
             if (!DENSE) {
 #pragma unroll
-                for (int i = 0; i < (DENSE ? 1 : 8); ++i) {
-                    const int piece = pt + i * 256;
+                for (int i = 0; i < (DENSE ? 1 : kXPieces); ++i) {
+                    const int piece = pt + i * kProducerThreads;
                     if (xrow[i]) *reinterpret_cast<uint4*>(a + core_offset(piece >> 3, piece & 7)) = r.xa[i];
                 }
             }
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int piece = pt + i * 256, row = piece >> 1, half = piece & 1;
+            for (int i = 0; i < kWPiecesPerThread; ++i) {
+                const int piece = pt + i * kProducerThreads, row = piece >> 1, half = piece & 1;
                 if (piece >= kWPieces) continue;
                 const float2 sc = e4m3x2_to_float2(r.ws[i]);
                 const uint32_t words[4] = {r.wc[i].x, r.wc[i].y, r.wc[i].z, r.wc[i].w};
@@ -412,7 +449,7 @@ static int launch_variant(const GemmParams& p, int row_tiles, cudaStream_t strea
         if (rc != QD_OK) return rc;
     }
     dim3 grid(row_tiles, (p.out_features + TN - 1) / TN);
-    return qd_launch(nvfp4_gemm_kernel<TN, DENSE, AHEAD>, grid, dim3(kThreads), smem, stream, false, p, map);
+    return qd_launch(nvfp4_gemm_kernel<TN, DENSE, AHEAD>, grid, dim3(block_threads(DENSE)), smem, stream, false, p, map);
 }
 
 // The widest weight tile that still gives every SM a tile (narrower tiles expand fewer weights
@@ -467,11 +504,15 @@ extern "C" int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const v
     p.x = (const bf16*)x; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
     p.y = (bf16*)y; p.tokens = routes; p.out_features = out_features; p.in_features = in_features; p.status = status;
     p.order = order; p.boundaries = boundaries; p.routing = routing; p.topk = topk;
-    p.chunks = (max_rows_per_expert + kTileM - 1) / kTileM;
+    p.experts = experts;
     p.by_token = by_token; p.scatter = scatter; p.global_per_expert = global_per_expert;
     p.codes_stride = (long long)out_features * (in_features / 2);
     p.scales_stride = (long long)out_features * (in_features / 16);
-    // about one busy row tile per expert that received routes (at most min(experts, routes))
+    // non-empty row tiles: at most one partly filled tile per expert that received routes plus
+    // the full ones, and never more than the caller's bound per expert allows
     const int busy = experts < routes ? experts : routes;
-    return launch_gemm<false>(p, experts * p.chunks, busy, (cudaStream_t)stream);
+    const long long by_bound = (long long)experts * ((max_rows_per_expert + kTileM - 1) / kTileM);
+    const long long by_count = (long long)busy + routes / kTileM;
+    const int row_tiles = (int)(by_bound < by_count ? by_bound : by_count);
+    return launch_gemm<false>(p, row_tiles, busy, (cudaStream_t)stream);
 }

@@ -431,17 +431,27 @@ constexpr int kGroupTile = 2048;
 __global__ void __launch_bounds__(1024)
 seq_group_routes_kernel(const int32_t* __restrict__ ids, int routes, int experts, int32_t* __restrict__ order,
                         int32_t* __restrict__ boundaries) {
-    __shared__ int32_t tile[kGroupTile];
+    __shared__ __align__(16) int32_t tile[kGroupTile];
     __shared__ int32_t start[1025];
     const int e = threadIdx.x;
+    // the ids of a tile, padded with -1 to a multiple of four so that the scans read 16 bytes
+    auto load_tile = [&](int r0) {
+        const int n = min(kGroupTile, routes - r0), padded = (n + 3) & ~3;
+        __syncthreads();
+        for (int i = e; i < padded; i += blockDim.x) tile[i] = i < n ? ids[r0 + i] : -1;
+        __syncthreads();
+        return padded;
+    };
     int count = 0;
     for (int r0 = 0; r0 < routes; r0 += kGroupTile) {
-        const int n = min(kGroupTile, routes - r0);
-        __syncthreads();
-        for (int i = e; i < n; i += blockDim.x) tile[i] = ids[r0 + i];
-        __syncthreads();
-        if (e < experts)
-            for (int i = 0; i < n; ++i) count += tile[i] == e;
+        const int padded = load_tile(r0);
+        if (e < experts) {
+#pragma unroll 4
+            for (int i = 0; i < padded; i += 4) {
+                const int4 v = *reinterpret_cast<const int4*>(tile + i);
+                count += (v.x == e) + (v.y == e) + (v.z == e) + (v.w == e);
+            }
+        }
     }
     start[e + 1] = e < experts ? count : 0;
     if (e == 0) start[0] = 0;
@@ -452,13 +462,17 @@ seq_group_routes_kernel(const int32_t* __restrict__ ids, int routes, int experts
     if (e <= experts) boundaries[e] = start[e];
     int at = start[e];
     for (int r0 = 0; r0 < routes; r0 += kGroupTile) {
-        const int n = min(kGroupTile, routes - r0);
-        __syncthreads();
-        for (int i = e; i < n; i += blockDim.x) tile[i] = ids[r0 + i];
-        __syncthreads();
-        if (e < experts)
-            for (int i = 0; i < n; ++i)
-                if (tile[i] == e) order[at++] = r0 + i;
+        const int padded = load_tile(r0);
+        if (e < experts && count > 0) {
+#pragma unroll 4
+            for (int i = 0; i < padded; i += 4) {
+                const int4 v = *reinterpret_cast<const int4*>(tile + i);
+                if (v.x == e) order[at++] = r0 + i;
+                if (v.y == e) order[at++] = r0 + i + 1;
+                if (v.z == e) order[at++] = r0 + i + 2;
+                if (v.w == e) order[at++] = r0 + i + 3;
+            }
+        }
     }
 }
 
