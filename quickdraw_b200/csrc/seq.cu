@@ -425,54 +425,62 @@ __global__ void seq_route_kernel(const bf16* __restrict__ logits, int experts, i
 // --------------------------------------------------------- routes of a chunk by expert
 // The stable order of the chunk's (token, slot) routes by expert id, as the reference groups
 // them (quickdraw/kernel/triton/moe.py:60-97): order[r] = route index of sorted row r,
-// boundaries[e] = first sorted row of expert e.  One block; thread e counts and then places
-// expert e's routes in ascending route index, reading the ids through shared memory.
-constexpr int kGroupTile = 2048;
+// boundaries[e] = first sorted row of expert e.  One block; every warp owns a contiguous slice
+// of the routes and a private row of per-expert counters in shared memory.  Pass 1 counts the
+// slice (32 routes at a time: lanes with the same expert find one another with match_any, the
+// lowest of them adds their number), a scan in (expert, warp) order turns the counters into
+// first positions, pass 2 walks the slice again and places every route at its expert's
+// running position plus its rank among the equal lanes below it.
 __global__ void __launch_bounds__(1024)
 seq_group_routes_kernel(const int32_t* __restrict__ ids, int routes, int experts, int32_t* __restrict__ order,
                         int32_t* __restrict__ boundaries) {
-    __shared__ __align__(16) int32_t tile[kGroupTile];
-    __shared__ int32_t start[1025];
-    const int e = threadIdx.x;
-    // the ids of a tile, padded with -1 to a multiple of four so that the scans read 16 bytes
-    auto load_tile = [&](int r0) {
-        const int n = min(kGroupTile, routes - r0), padded = (n + 3) & ~3;
-        __syncthreads();
-        for (int i = e; i < padded; i += blockDim.x) tile[i] = i < n ? ids[r0 + i] : -1;
-        __syncthreads();
-        return padded;
-    };
-    int count = 0;
-    for (int r0 = 0; r0 < routes; r0 += kGroupTile) {
-        const int padded = load_tile(r0);
-        if (e < experts) {
-#pragma unroll 4
-            for (int i = 0; i < padded; i += 4) {
-                const int4 v = *reinterpret_cast<const int4*>(tile + i);
-                count += (v.x == e) + (v.y == e) + (v.z == e) + (v.w == e);
-            }
+    extern __shared__ int32_t counters[];               // [warps][experts], then first[experts + 1]
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int32_t* first = counters + warps * experts;
+    for (int i = threadIdx.x; i < warps * experts; i += blockDim.x) counters[i] = 0;
+    __syncthreads();
+    const int slice = ((routes + warps - 1) / warps + 31) & ~31;
+    const int begin = min(routes, warp * slice), end = min(routes, begin + slice);
+    int32_t* mine = counters + warp * experts;
+    for (int r0 = begin; r0 < end; r0 += 32) {
+        const int r = r0 + lane;
+        const int e = r < end ? ids[r] : -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && lane == __ffs(same) - 1) mine[e] += __popc(same);
+        __syncwarp();
+    }
+    __syncthreads();
+    // totals per expert, their exclusive scan, then every warp's first position per expert
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        int total = 0;
+        for (int w = 0; w < warps; ++w) total += counters[w * experts + e];
+        first[e + 1] = total;
+    }
+    if (threadIdx.x == 0) first[0] = 0;
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (int e = 0; e < experts; ++e) first[e + 1] += first[e];
+    __syncthreads();
+    for (int e = threadIdx.x; e <= experts; e += blockDim.x) boundaries[e] = first[e];
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        int at = first[e];
+        for (int w = 0; w < warps; ++w) {
+            const int n = counters[w * experts + e];
+            counters[w * experts + e] = at;
+            at += n;
         }
     }
-    start[e + 1] = e < experts ? count : 0;
-    if (e == 0) start[0] = 0;
     __syncthreads();
-    if (e == 0)
-        for (int i = 0; i < experts; ++i) start[i + 1] += start[i];
-    __syncthreads();
-    if (e <= experts) boundaries[e] = start[e];
-    int at = start[e];
-    for (int r0 = 0; r0 < routes; r0 += kGroupTile) {
-        const int padded = load_tile(r0);
-        if (e < experts && count > 0) {
-#pragma unroll 4
-            for (int i = 0; i < padded; i += 4) {
-                const int4 v = *reinterpret_cast<const int4*>(tile + i);
-                if (v.x == e) order[at++] = r0 + i;
-                if (v.y == e) order[at++] = r0 + i + 1;
-                if (v.z == e) order[at++] = r0 + i + 2;
-                if (v.w == e) order[at++] = r0 + i + 3;
-            }
-        }
+    for (int r0 = begin; r0 < end; r0 += 32) {
+        const int r = r0 + lane;
+        const int e = r < end ? ids[r] : -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        int at = 0;
+        if (e >= 0) at = mine[e] + __popc(same & ((1u << lane) - 1u));
+        __syncwarp();
+        if (e >= 0 && lane == __ffs(same) - 1) mine[e] += __popc(same);
+        __syncwarp();
+        if (e >= 0) order[at] = r;
     }
 }
 
@@ -583,8 +591,11 @@ extern "C" int qd_seq_group_routes(const int32_t* ids, int routes, int experts, 
                                    void* stream) {
     QD_CHECK_ARG(ids && order && boundaries && routes > 0 && experts > 0);
     if (experts > 1023) return QD_ERR_UNSUPPORTED;
-    const int threads = ((experts + 1 + 31) / 32) * 32;
-    seq_group_routes_kernel<<<1, threads, 0, (cudaStream_t)stream>>>(ids, routes, experts, order, boundaries);
+    // as many warps as 40 KB of counters allow (32 at 256 experts, 8 at 1023)
+    int warps = 32;
+    while (warps > 1 && (size_t)warps * experts * 4 > 40960) warps >>= 1;
+    const size_t smem = ((size_t)warps * experts + experts + 1) * sizeof(int32_t);
+    seq_group_routes_kernel<<<1, warps * 32, smem, (cudaStream_t)stream>>>(ids, routes, experts, order, boundaries);
     return qd_launch_status();
 }
 
