@@ -16,10 +16,10 @@
 //               with one tiled TMA load (cp.async.bulk.tensor, 128-byte swizzle; rows past the
 //               end arrive as zeros) as soon as the stage is free
 //               grouped product: idle - the rows of a tile are gathered through the route
-//               order, so the producers copy them with 16-byte loads (no-swizzle layout)
+//               order, so the producers copy them with 16-byte loads into the same layout
 //   warp 0      allocates all 512 columns of tensor memory, issues 2 x 4 MMAs of 128x256x16 per
 //               stage and commits them to the stage's "empty" barrier
-// Stages: 3 x (36 KB activations + 36 KB weights) guarded by full / empty mbarriers.  Every wait
+// Stages: 3 x (32 KB activations + 32 KB weights) guarded by full / empty mbarriers.  Every wait
 // is bounded; a wait that runs out sets the status word, the block frees its tensor memory and
 // leaves.
 #include <cuda.h>
@@ -39,12 +39,13 @@ constexpr int kStages = 3;
 // 511-token chunk).  The block is warp 0 + producers + loader warp.
 constexpr int producer_warps(bool dense) { return dense ? 8 : 16; }
 constexpr int block_threads(bool dense) { return (2 + producer_warps(dense)) * 32; }
-constexpr int kCorePitch = 144;             // bytes from one 128-byte core matrix to the next along K: the
-                                            // 16 bytes of padding spread a warp's stores over all banks
-constexpr int kGroupPitch = (kTileK / 8) * kCorePitch;      // bytes between 8-row groups
-constexpr int kABytes = (kTileM / 8) * kGroupPitch;         // 36 KB (the swizzled TMA tile uses the first 32 KB)
-constexpr int kATmaBytes = kTileM * kTileK * 2;             // bytes one activation tile load delivers
-constexpr int kBBytesMax = (256 / 8) * kGroupPitch;         // 36 KB at 256 rows
+// Both operands of a stage use the 128-byte swizzled K-major layout: row r of the tile is 128
+// bytes (64 inputs) at r * 128, its 16-byte piece c stored at piece c ^ (r & 7).  The TMA load
+// writes it for the activations of the plain product; the producers write it themselves for
+// the weights (and for the gathered activation rows of the grouped product).
+constexpr int kABytes = kTileM * kTileK * 2;                // 32 KB
+constexpr int kATmaBytes = kABytes;                         // bytes one activation tile load delivers
+constexpr int kBBytesMax = 256 * kTileK * 2;                // 32 KB at 256 rows
 constexpr int kStageBytes = kABytes + kBBytesMax;
 
 struct GemmParams {
@@ -92,18 +93,11 @@ QD_DEVINL void tmem_load32(uint32_t addr, uint32_t (&v)[32]) {
 QD_DEVINL void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 QD_DEVINL void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, K-major, no swizzle: core matrix = 8 rows x 16 bytes stored
-// as 128 contiguous bytes; `lbo` = bytes between the two core matrices an MMA reads along K,
-// `sbo` = bytes between 8-row groups.  Bits: [0,14) address >> 4, [16,30) lbo >> 4, [32,46)
-// sbo >> 4, [46,48) descriptor version 1, [61,64) layout type 0.
-QD_DEVINL uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
-           ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
-}
-// The same for a tile a TMA load wrote with the 128-byte swizzle (rows of 128 bytes, 16-byte
-// pieces XOR-ed with the row index inside every 1024-byte group of 8 rows; the tile starts on a
-// 1024-byte boundary): layout type 2, sbo = 1024, lbo unused.  A K step of 16 inputs advances
-// the start address by 32 bytes inside the row.
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle (rows of 128 bytes, 16-byte pieces
+// XOR-ed with the row index inside every 1024-byte group of 8 rows; the tile starts on a
+// 1024-byte boundary).  Bits: [0,14) address >> 4, [16,30) leading byte offset >> 4 (unused
+// here), [32,46) bytes between 8-row groups >> 4 = 64, [46,48) descriptor version 1, [61,64)
+// layout type 2.  A K step of 16 inputs advances the start address by 32 bytes inside the row.
 QD_DEVINL uint64_t smem_desc_sw128(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
@@ -122,8 +116,8 @@ constexpr uint32_t instr_desc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
-// byte offset of the 16-byte piece (row, 8-input group kg) inside a stage tile
-QD_DEVINL uint32_t core_offset(int row, int kg) { return (uint32_t)((row >> 3) * kGroupPitch + kg * kCorePitch + (row & 7) * 16); }
+// byte offset of the 16-byte piece (row, 8-input group kg) inside a swizzled stage tile
+QD_DEVINL uint32_t piece_offset(int row, int kg) { return (uint32_t)(row * 128 + ((kg ^ (row & 7)) << 4)); }
 
 // eight E2M1 codes (one 32-bit word, low nibble first) times an fp32 block scale -> eight bf16
 // (hardware convert to f16 pairs; code * scale has at most six significant bits and stays inside
@@ -239,10 +233,8 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
                 for (int h = 0; h < halves; ++h)
 #pragma unroll
                     for (int j = 0; j < kTileK / 16; ++j) {
-                        const uint64_t a_desc = DENSE ? smem_desc_sw128(a + h * (kATmaBytes / 2) + j * 32)
-                                                      : smem_desc(a + h * (kABytes / 2) + j * 2 * kCorePitch, kCorePitch, kGroupPitch);
-                        umma_bf16(tmem + h * kTileN, a_desc, smem_desc(b + j * 2 * kCorePitch, kCorePitch, kGroupPitch),
-                                  kInstrDesc, (s | j) ? 1u : 0u);
+                        umma_bf16(tmem + h * kTileN, smem_desc_sw128(a + h * (kABytes / 2) + j * 32),
+                                  smem_desc_sw128(b + j * 32), kInstrDesc, (s | j) ? 1u : 0u);
                     }
                 umma_commit(empty + st);          // the stage is free once these MMAs have read it
             }
@@ -316,7 +308,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 #pragma unroll
                 for (int i = 0; i < (DENSE ? 1 : kXPieces); ++i) {
                     const int piece = pt + i * kProducerThreads;
-                    if (xrow[i]) *reinterpret_cast<uint4*>(a + core_offset(piece >> 3, piece & 7)) = r.xa[i];
+                    if (xrow[i]) *reinterpret_cast<uint4*>(a + piece_offset(piece >> 3, piece & 7)) = r.xa[i];
                 }
             }
 #pragma unroll
@@ -327,7 +319,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
                 const uint32_t words[4] = {r.wc[i].x, r.wc[i].y, r.wc[i].z, r.wc[i].w};
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
-                    *reinterpret_cast<uint4*>(b + core_offset(row, half * 4 + q)) = expand8(words[q], q < 2 ? sc.x : sc.y);
+                    *reinterpret_cast<uint4*>(b + piece_offset(row, half * 4 + q)) = expand8(words[q], q < 2 ? sc.x : sc.y);
             }
         };
         bool ok = true;
