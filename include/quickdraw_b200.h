@@ -96,6 +96,29 @@ int qd_seq_attention(const void* qg, const void* k_new, const void* v_new, const
                      int rotary_dim, float theta, float eps, void* stream);
 int qd_seq_route_topk(const void* logits, int tokens, int experts, int topk, int32_t* ids, float* weights,
                       void* stream);
+/* ---- Small-batch decode with per-sequence state: one token of each of `batch` independent
+ * sequences per call.  The reference decodes one sequence (quickdraw/engine/engine.py:114-127);
+ * these are its single-token operators (_conv_kernel / _delta_kernel of
+ * quickdraw/kernel/triton/delta.py:37-121, _prepare / _attend of
+ * quickdraw/kernel/triton/attention.py:10-100) with the sequence as one more grid dimension:
+ * inputs and outputs hold one row set per sequence, the state of sequence b starts
+ * `*_stride` elements after that of sequence b - 1.  The other operators of the step are the
+ * chunk forms above (rows are independent there). */
+int qd_batch_gdn_conv(const void* mixed, const void* taps, void* conv_state, long long state_stride,
+                      void* out, int batch, int channels, int width, void* stream);
+/* key_dim == 128 */
+int qd_batch_gdn_recurrence(const void* conv_qkv, const void* a, const void* b, const void* a_log,
+                            const void* dt_bias, float* rec_state, long long state_stride, void* out,
+                            int batch, int key_heads, int value_heads, int key_dim, int value_dim,
+                            void* stream);
+/* positions: device int32 [batch], each < capacity; scratch: batch * qd_attn_scratch_floats()
+ * floats; counters: batch * kv_heads zeroed uint32 (left zero). */
+int qd_batch_attn_decode(const void* qg, const void* k_new, const void* v_new, const void* q_norm,
+                         const void* k_norm, void* k_cache, void* v_cache, long long cache_stride,
+                         void* out, float* scratch, unsigned int* counters, const int* positions,
+                         int batch, int capacity, int q_heads, int kv_heads, int head_dim,
+                         int rotary_dim, float theta, float eps, int splits, void* stream);
+
 /* The stable order of the chunk's routes by expert (quickdraw/kernel/triton/moe.py:60-97, the
  * grouping the reference builds with a stable sort): ids int32 [routes], every id in
  * [0, experts); order int32 [routes] = route index of each sorted row, boundaries int32

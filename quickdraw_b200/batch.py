@@ -1,0 +1,125 @@
+"""Small-batch decode: one token of each of B independent sequences per step, every sequence
+with its own KV cache, recurrent state, convolution history and position.
+
+The reference decodes one sequence (quickdraw/engine/engine.py:114-127); its per-layer math
+(quickdraw/models/qwen.py:196-241) is applied here to B rows at a time.  Row-independent
+operators are the chunk forms of the prefill (tensor-core products with B rows, residual add +
+RMSNorm, routing, routes grouped by expert, grouped expert products, combine); the three
+operators that touch per-sequence state (DeltaNet convolution and recurrence, attention) are
+the single-token kernels with the sequence as one more grid dimension.  The LM head reads every
+weight row once for all sequences; the next token of each sequence is the greedy argmax.
+
+``BatchState`` stacks the reference's ``DecodeState`` buffers along a leading sequence axis;
+``sequence(b)`` is a ``DecodeState`` view of one sequence, so a prompt is prefilled with the
+single-sequence chunk prefill and a sequence can be continued by the single-sequence step.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ._lib import call, lib, ptr, stream_of
+from .prefill import ChunkPrefill
+from .state import DecodeState
+from .weights import Checkpoint
+
+BF16 = torch.bfloat16
+ATTN_SPLITS = 8
+
+
+class BatchState:
+    def __init__(self, config, batch: int, max_context: int, device):
+        one = DecodeState.allocate(config, 1, "meta")
+        full = one.kv_k.shape[0]
+        kv_shape = (batch, full, max_context, config.num_key_value_heads, config.head_dim)
+        self.kv_k = torch.zeros(kv_shape, dtype=BF16, device=device)
+        self.kv_v = torch.zeros(kv_shape, dtype=BF16, device=device)
+        self.rec_state = torch.zeros((batch, *one.rec_state.shape), dtype=torch.float32, device=device)
+        self.conv_state = torch.zeros((batch, *one.conv_state.shape), dtype=BF16, device=device)
+        self.positions = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.batch, self.max_context = batch, max_context
+
+    def sequence(self, b: int) -> DecodeState:
+        """The buffers of sequence b as the single-sequence container (views, no copy)."""
+        return DecodeState(self.kv_k[b], self.kv_v[b], self.rec_state[b], self.conv_state[b],
+                           int(self.positions[b].item()))
+
+    def memory_bytes(self) -> int:
+        return sum(t.nbytes for t in (self.kv_k, self.kv_v, self.rec_state, self.conv_state))
+
+
+class BatchDecode(ChunkPrefill):
+    """``step(tokens[B], state)`` -> (next tokens [B] int64, logits [B, vocab] bf16)."""
+
+    def __init__(self, ckpt: Checkpoint):
+        super().__init__(ckpt)
+        c = ckpt.config
+        self.final_gamma = (1 + ckpt.final_norm.float()).contiguous()
+        self._scratch = None
+
+    def _attn_scratch(self, batch):
+        c = self.ckpt.config
+        if self._scratch is None or self._scratch[0] < batch:
+            floats = lib().qd_attn_scratch_floats(c.num_attention_heads, c.num_key_value_heads, c.head_dim,
+                                                  ATTN_SPLITS)
+            self._scratch = (batch, torch.empty(batch * floats, dtype=torch.float32, device=self.device),
+                             torch.zeros(batch * c.num_key_value_heads, dtype=torch.int32, device=self.device))
+        return self._scratch[1], self._scratch[2]
+
+    # ------------------------------------------------------------- per-sequence-state blocks
+    def _delta_net_batch(self, w, x, state: BatchState, index):
+        c = self.ckpt.config
+        batch = x.shape[0]
+        hv, dv = c.linear_num_value_heads, c.linear_value_head_dim
+        qkv, z = self._matmul(x, w.in_proj_qkv), self._matmul(x, w.in_proj_z)
+        a, b = self._small(x, w.in_proj_a), self._small(x, w.in_proj_b)
+        conv = torch.empty_like(qkv)
+        conv_state, rec_state = state.conv_state[:, index], state.rec_state[:, index]
+        call("qd_batch_gdn_conv", ptr(qkv), ptr(w.conv1d), ptr(conv_state[0]), conv_state.stride(0), ptr(conv),
+             batch, qkv.shape[1], c.linear_conv_kernel_dim, stream_of(x))
+        core = self._empty(batch, hv * dv)
+        call("qd_batch_gdn_recurrence", ptr(conv), ptr(a), ptr(b), ptr(w.A_log), ptr(w.dt_bias),
+             ptr(rec_state[0]), rec_state.stride(0), ptr(core), batch, c.linear_num_key_heads, hv,
+             c.linear_key_head_dim, dv, stream_of(x))
+        gated = torch.empty_like(core)
+        call("qd_gdn_gated_norm", ptr(core), ptr(z), ptr(w.norm), ptr(gated), batch * hv, dv, c.rms_norm_eps,
+             stream_of(x))
+        return self._matmul(gated, w.out_proj)
+
+    def _attention_batch(self, w, x, state: BatchState, index):
+        c = self.ckpt.config
+        batch = x.shape[0]
+        qg, k, v = self._matmul(x, w.q_proj), self._matmul(x, w.k_proj), self._matmul(x, w.v_proj)
+        out = self._empty(batch, c.num_attention_heads * c.head_dim)
+        scratch, counters = self._attn_scratch(batch)
+        k_cache, v_cache = state.kv_k[:, index], state.kv_v[:, index]
+        call("qd_batch_attn_decode", ptr(qg), ptr(k), ptr(v), ptr(w.q_norm), ptr(w.k_norm), ptr(k_cache[0]),
+             ptr(v_cache[0]), k_cache.stride(0), ptr(out), ptr(scratch), ptr(counters), ptr(state.positions),
+             batch, state.max_context, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
+             int(c.head_dim * c.partial_rotary_factor), c.rope_theta, c.rms_norm_eps, ATTN_SPLITS, stream_of(x))
+        return self._matmul(out, w.o_proj)
+
+    # ------------------------------------------------------------------------------ step
+    @torch.inference_mode()
+    def step(self, tokens: torch.Tensor, state: BatchState, *, positions_checked: bool = False):
+        """Feed tokens[b] to sequence b at state.positions[b]; advances every position by one."""
+        c = self.ckpt.config
+        assert tokens.shape == (state.batch,) and tokens.dtype == torch.long and tokens.is_cuda
+        if not positions_checked:
+            assert int(state.positions.max().item()) < state.max_context, "a sequence has filled its cache"
+        x = self.ckpt.embed_tokens[tokens].contiguous()
+        residual = None
+        for layer, (gamma_in, gamma_post) in zip(self.ckpt.layers, self.gammas):
+            normed, residual = self._add_norm(x, residual, gamma_in, c.rms_norm_eps)
+            if layer.layer_type == "full_attention":
+                index = sum(1 for k in c.layer_types[:layer.idx] if k == "full_attention")
+                mixed = self._attention_batch(layer.attn, normed, state, index)
+            else:
+                index = sum(1 for k in c.layer_types[:layer.idx] if k != "full_attention")
+                mixed = self._delta_net_batch(layer.attn, normed, state, index)
+            normed, residual = self._add_norm(mixed, residual, gamma_post, c.rms_norm_eps)
+            x = self._moe(layer.moe, normed)
+        final, _ = self._add_norm(x, residual, self.final_gamma, c.rms_norm_eps)
+        logits = self._small(final, self.ckpt.lm_head)
+        state.positions += 1
+        return logits.float().argmax(dim=-1), logits

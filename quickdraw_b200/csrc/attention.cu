@@ -36,6 +36,7 @@ struct AttnParams {
     int hq, hk, d, rotary;
     float theta, eps;
     int splits;
+    long long cache_stride;   // batched form only: elements between the caches of two sequences
 };
 
 // normalise + rotate one head held as D/32 (<= 8) strided features per lane: feature i = j*32 + lane.
@@ -70,6 +71,19 @@ __global__ void __launch_bounds__(kAttnThreads)
 attn_decode_kernel(const AttnParams p) {
     extern __shared__ float sm[];
     const int G = p.hq / p.hk, D = p.d;
+    // batched form: grid z = sequence; every per-sequence array moves on by one sequence, the
+    // position comes from the sequence's entry of the device array (z = 0: no offsets)
+    const size_t z = blockIdx.z;
+    const long long cache_offset = z ? (long long)z * p.cache_stride : 0;
+    const bf16* const seq_qg = p.qg + z * (size_t)p.hq * 2 * D;
+    const bf16* const seq_k_new = p.k_new + z * (size_t)p.hk * D;
+    const bf16* const seq_v_new = p.v_new + z * (size_t)p.hk * D;
+    bf16* const seq_k_cache = p.k_cache + cache_offset;
+    bf16* const seq_v_cache = p.v_cache + cache_offset;
+    bf16* const seq_out = p.out + z * (size_t)p.hq * D;
+    float* const seq_partial = p.partial + z * (size_t)p.hk * p.splits * G * (D + 2);
+    unsigned int* const seq_counters = p.counters + z * (size_t)p.hk;
+    const int* const seq_position = p.position_dev ? p.position_dev + z : nullptr;
     float* q_s = sm;                              // [G][D] normalised, rotated, as fp32 of bf16
     float* k_s = q_s + G * D;                     // [D] new key
     float* red = k_s + D;                         // [warps][G][D + 2]
@@ -79,7 +93,7 @@ attn_decode_kernel(const AttnParams p) {
 
     grid_launch_dependents();
     grid_dependency_wait();
-    const int position = p.position_dev ? *p.position_dev : p.position_host;
+    const int position = seq_position ? *seq_position : p.position_host;
     const int T = position + 1;
     int active = (T + kAttnSplitMin - 1) / kAttnSplitMin;
     if (active > p.splits) active = p.splits;
@@ -90,16 +104,16 @@ attn_decode_kernel(const AttnParams p) {
 
     if (mine) {
         for (int h = warp; h < G; h += kAttnWarps)
-            norm_rope_head(p.qg + (size_t)(kvh * G + h) * 2 * D, p.q_norm, D, p.rotary, p.theta, p.eps,
+            norm_rope_head(seq_qg + (size_t)(kvh * G + h) * 2 * D, p.q_norm, D, p.rotary, p.theta, p.eps,
                            position, lane, q_s + h * D);
         const bool owns_new = position >= t0 && position < t1;
         if (owns_new && warp == kAttnWarps - 1) {
-            norm_rope_head(p.k_new + (size_t)kvh * D, p.k_norm, D, p.rotary, p.theta, p.eps, position, lane, k_s);
-            bf16* krow = p.k_cache + ((size_t)position * p.hk + kvh) * D;
-            bf16* vrow = p.v_cache + ((size_t)position * p.hk + kvh) * D;
+            norm_rope_head(seq_k_new + (size_t)kvh * D, p.k_norm, D, p.rotary, p.theta, p.eps, position, lane, k_s);
+            bf16* krow = seq_k_cache + ((size_t)position * p.hk + kvh) * D;
+            bf16* vrow = seq_v_cache + ((size_t)position * p.hk + kvh) * D;
             for (int i = lane; i < D; i += 32) {
                 krow[i] = __float2bfloat16_rn(k_s[i]);
-                vrow[i] = p.v_new[(size_t)kvh * D + i];
+                vrow[i] = seq_v_new[(size_t)kvh * D + i];
             }
         }
     }
@@ -125,11 +139,11 @@ attn_decode_kernel(const AttnParams p) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         kf[j] = k_s[f0 + j];
-                        vf[j] = ld_bf16(p.v_new + (size_t)kvh * D + f0 + j);
+                        vf[j] = ld_bf16(seq_v_new + (size_t)kvh * D + f0 + j);
                     }
                 } else {
-                    const uint4 kr = *reinterpret_cast<const uint4*>(p.k_cache + ((size_t)t * p.hk + kvh) * D + f0);
-                    const uint4 vr = *reinterpret_cast<const uint4*>(p.v_cache + ((size_t)t * p.hk + kvh) * D + f0);
+                    const uint4 kr = *reinterpret_cast<const uint4*>(seq_k_cache + ((size_t)t * p.hk + kvh) * D + f0);
+                    const uint4 vr = *reinterpret_cast<const uint4*>(seq_v_cache + ((size_t)t * p.hk + kvh) * D + f0);
                     const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -174,7 +188,7 @@ attn_decode_kernel(const AttnParams p) {
         }
     }
     __syncthreads();
-    float* block_out = p.partial + (((size_t)kvh * p.splits + split) * G) * stride;
+    float* block_out = seq_partial + (((size_t)kvh * p.splits + split) * G) * stride;
     for (int idx = tid; idx < G * D; idx += kAttnThreads) {
         const int h = idx / D, f = idx % D;
         float mm = -INFINITY;
@@ -192,7 +206,7 @@ attn_decode_kernel(const AttnParams p) {
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const unsigned int done = atomicAdd(p.counters + kvh, 1u);
+        const unsigned int done = atomicAdd(seq_counters + kvh, 1u);
         s_last = done == (unsigned int)p.splits - 1;
     }
     __syncthreads();
@@ -203,10 +217,10 @@ attn_decode_kernel(const AttnParams p) {
         const int h = idx / D, f = idx % D;
         float mm = -INFINITY;
         for (int s = 0; s < active; ++s)
-            mm = fmaxf(mm, __ldcg(p.partial + (((size_t)kvh * p.splits + s) * G + h) * stride + D));
+            mm = fmaxf(mm, __ldcg(seq_partial + (((size_t)kvh * p.splits + s) * G + h) * stride + D));
         float num = 0.f, den = 0.f;
         for (int s = 0; s < active; ++s) {
-            const float* src = p.partial + (((size_t)kvh * p.splits + s) * G + h) * stride;
+            const float* src = seq_partial + (((size_t)kvh * p.splits + s) * G + h) * stride;
             const float sm_ = __ldcg(src + D);
             const float wgt = sm_ == -INFINITY ? 0.f : expf(sm_ - mm);
             num += wgt * __ldcg(src + f);
@@ -214,10 +228,10 @@ attn_decode_kernel(const AttnParams p) {
         }
         const float attended = round_bf16(num / den);
         const int qh = kvh * G + h;
-        const float gate = round_bf16(sigmoid_precise(ld_bf16(p.qg + (size_t)qh * 2 * D + D + f)));
-        p.out[(size_t)qh * D + f] = __float2bfloat16_rn(attended * gate);
+        const float gate = round_bf16(sigmoid_precise(ld_bf16(seq_qg + (size_t)qh * 2 * D + D + f)));
+        seq_out[(size_t)qh * D + f] = __float2bfloat16_rn(attended * gate);
     }
-    if (tid == 0) p.counters[kvh] = 0;
+    if (tid == 0) seq_counters[kvh] = 0;
 }
 
 extern "C" int qd_attn_scratch_floats(int q_heads, int kv_heads, int head_dim, int splits) {
@@ -241,7 +255,7 @@ extern "C" int qd_attn_decode(const void* qg, const void* k_new, const void* v_n
     p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache; p.out = (bf16*)out;
     p.partial = scratch; p.counters = counters; p.position_dev = position_dev; p.position_host = position_host;
     p.capacity = capacity; p.hq = q_heads; p.hk = kv_heads; p.d = head_dim; p.rotary = rotary_dim;
-    p.theta = theta; p.eps = eps; p.splits = splits;
+    p.theta = theta; p.eps = eps; p.splits = splits; p.cache_stride = 0;
     const size_t smem = sizeof(float) * ((size_t)G * head_dim + head_dim + (size_t)kAttnWarps * G * (head_dim + 2));
     static bool configured = false;
     if (!configured) {
@@ -252,6 +266,44 @@ extern "C" int qd_attn_decode(const void* qg, const void* k_new, const void* v_n
     if (smem > 100 * 1024) return QD_ERR_UNSUPPORTED;
     return qd_launch(attn_decode_kernel, dim3(kv_heads, splits), dim3(kAttnThreads), smem, (cudaStream_t)stream,
                      pdl != 0, p);
+}
+
+// ------------------------------------------------------------------------- batched form
+// One decode step of `batch` independent sequences, each with its own cache and position
+// (per-sequence state of small-batch decode): the single-sequence kernel with the sequence as
+// grid z.  qg / k_new / v_new / out hold one row set per sequence, the caches of sequence b
+// start cache_stride elements after those of sequence b - 1, positions is a device array,
+// scratch holds batch * qd_attn_scratch_floats() floats, counters batch * kv_heads zeros.
+extern "C" int qd_batch_attn_decode(const void* qg, const void* k_new, const void* v_new, const void* q_norm,
+                                    const void* k_norm, void* k_cache, void* v_cache, long long cache_stride,
+                                    void* out, float* scratch, unsigned int* counters, const int* positions,
+                                    int batch, int capacity, int q_heads, int kv_heads, int head_dim,
+                                    int rotary_dim, float theta, float eps, int splits, void* stream) {
+    QD_CHECK_ARG(qg && k_new && v_new && q_norm && k_norm && k_cache && v_cache && out && scratch && counters && positions);
+    QD_CHECK_ARG(batch > 0 && batch <= 65535 && kv_heads > 0 && q_heads % kv_heads == 0 && splits >= 1 && capacity > 0);
+    QD_CHECK_ARG(cache_stride >= (long long)capacity * kv_heads * head_dim || batch == 1);
+    QD_CHECK_ARG(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0);
+    const int G = q_heads / kv_heads;
+    if (G > kAttnMaxGroup || head_dim > kAttnMaxDim || head_dim % 8 != 0) return QD_ERR_UNSUPPORTED;
+    AttnParams p;
+    p.qg = (const bf16*)qg; p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new;
+    p.q_norm = (const bf16*)q_norm; p.k_norm = (const bf16*)k_norm;
+    p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache; p.out = (bf16*)out;
+    p.partial = scratch; p.counters = counters; p.position_dev = positions; p.position_host = 0;
+    p.capacity = capacity; p.hq = q_heads; p.hk = kv_heads; p.d = head_dim; p.rotary = rotary_dim;
+    p.theta = theta; p.eps = eps; p.splits = splits; p.cache_stride = cache_stride;
+    const size_t smem = sizeof(float) * ((size_t)G * head_dim + head_dim + (size_t)kAttnWarps * G * (head_dim + 2));
+    if (smem > 100 * 1024) return QD_ERR_UNSUPPORTED;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
+    static bool configured[64];
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
+            return QD_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    return qd_launch(attn_decode_kernel, dim3(kv_heads, splits, batch), dim3(kAttnThreads), smem, (cudaStream_t)stream,
+                     false, p);
 }
 
 // ---------------------------------------------------------------- allocation-free variant

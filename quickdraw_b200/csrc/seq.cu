@@ -62,6 +62,78 @@ __global__ void seq_bf16_matmul_kernel(const bf16* __restrict__ x, const bf16* _
     if (lane == 0) y[(size_t)t * rows + n] = __float2bfloat16_rn(acc);
 }
 
+// The same for a tall matrix (the LM head over a batch of tokens): the activations of up to
+// 32 tokens sit in shared memory as bf16, a warp takes two weight rows at a time, reads them
+// once and multiplies them with every token of the tile (lane = eight inputs of every 256);
+// the 32 per-token partial sums of a lane are reduced across the warp by a transposing
+// butterfly (31 shuffles), after which lane t holds token t's sum.
+constexpr int kTallTokens = 32, kTallMaxChunks = 8, kTallRows = 2;
+__global__ void __launch_bounds__(256)
+seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                            int tokens, int rows, int width) {
+    extern __shared__ __align__(16) unsigned char tall_smem[];
+    bf16* xs = reinterpret_cast<bf16*>(tall_smem);                 // [32][width]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t0 = blockIdx.y * kTallTokens, nt = min(kTallTokens, tokens - t0);
+    const int pieces = width / 8, chunks = width / 256;
+    for (int i = tid; i < kTallTokens * pieces; i += 256) {
+        const int row = i / pieces, col = i % pieces;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < nt) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + row) * width) + col);
+        reinterpret_cast<uint4*>(xs)[i] = v;
+    }
+    __syncthreads();
+    for (int n0 = (blockIdx.x * 8 + warp) * kTallRows; n0 < rows; n0 += gridDim.x * 8 * kTallRows) {
+        uint4 wv[kTallRows][kTallMaxChunks];
+#pragma unroll
+        for (int r = 0; r < kTallRows; ++r)
+#pragma unroll
+            for (int c = 0; c < kTallMaxChunks; ++c)
+                wv[r][c] = (c < chunks && n0 + r < rows)
+                               ? __ldg(reinterpret_cast<const uint4*>(w + (size_t)(n0 + r) * width + c * 256 + lane * 8))
+                               : make_uint4(0u, 0u, 0u, 0u);
+        float part[kTallRows][kTallTokens];
+#pragma unroll
+        for (int t = 0; t < kTallTokens; ++t) {
+            float acc[kTallRows];
+#pragma unroll
+            for (int r = 0; r < kTallRows; ++r) acc[r] = 0.f;
+#pragma unroll
+            for (int c = 0; c < kTallMaxChunks; ++c) {
+                if (c < chunks) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)t * width + c * 256 + lane * 8);
+                    const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                    for (int r = 0; r < kTallRows; ++r) {
+                        const uint32_t ww[4] = {wv[r][c].x, wv[r][c].y, wv[r][c].z, wv[r][c].w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            acc[r] = fma_bf16_lo(ww[q], xx[q], acc[r]);
+                            acc[r] = fma_bf16_hi(ww[q], xx[q], acc[r]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kTallRows; ++r) part[r][t] = acc[r];
+        }
+#pragma unroll
+        for (int r = 0; r < kTallRows; ++r) {
+#pragma unroll
+            for (int span = 16; span >= 1; span >>= 1) {
+                const bool upper = (lane & span) != 0;
+#pragma unroll
+                for (int i = 0; i < span; ++i) {
+                    const float send = upper ? part[r][i] : part[r][i + span];
+                    const float keep = upper ? part[r][i + span] : part[r][i];
+                    part[r][i] = keep + __shfl_xor_sync(0xffffffffu, send, span);
+                }
+            }
+            if (lane < nt && n0 + r < rows) y[(size_t)(t0 + lane) * rows + n0 + r] = __float2bfloat16_rn(part[r][0]);
+        }
+    }
+}
+
 // ------------------------------------------------------------- DeltaNet short convolution
 // One thread per (token, channel): window = [history | new] ending at the token, tap products
 // rounded to bf16, fp32 sum from the oldest tap on, SiLU, bf16.  A second kernel then leaves the
@@ -91,6 +163,22 @@ __global__ void seq_conv_state_kernel(const bf16* __restrict__ mixed, bf16* stat
     for (int j = 0; j < width - 1; ++j) state[(size_t)c * (width - 1) + j] = keep[j];
 }
 
+// One decode step of `batch` independent sequences: thread = (sequence, channel), the
+// single-token arithmetic on the sequence's own history (state_stride elements apart).
+__global__ void batch_conv_kernel(const bf16* __restrict__ mixed, const bf16* __restrict__ taps, bf16* state,
+                                  bf16* __restrict__ out, int channels, int width, long long state_stride) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+    if (c >= channels) return;
+    bf16* hist = state + (size_t)b * state_stride + (size_t)c * (width - 1);
+    const float fresh = ld_bf16(mixed + (size_t)b * channels + c);
+    float acc = 0.f;
+    for (int k = 0; k < width - 1; ++k) acc += round_bf16(ld_bf16(hist + k) * ld_bf16(taps + (size_t)c * width + k));
+    acc += round_bf16(fresh * ld_bf16(taps + (size_t)c * width + width - 1));
+    for (int k = 0; k + 1 < width - 1; ++k) hist[k] = hist[k + 1];
+    if (width > 1) hist[width - 2] = mixed[(size_t)b * channels + c];
+    out[(size_t)b * channels + c] = __float2bfloat16_rn(silu_precise(acc));
+}
+
 // ------------------------------------------------- DeltaNet recurrence, key dimension 128
 // Block = (value head, 32 value columns), four warps; a warp owns 8 columns, a lane one column
 // and one quarter of the 128 keys: 32 state entries in registers for the whole chunk, the sums
@@ -108,8 +196,17 @@ struct RecPrefetch { uint2 k[kRecBatch / 4], q[kRecBatch / 4]; bf16 v[kRecBatch 
 __global__ void __launch_bounds__(128)
 seq_recurrence128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ a, const bf16* __restrict__ b,
                          const bf16* __restrict__ a_log, const bf16* __restrict__ dt_bias, float* __restrict__ state,
-                         bf16* __restrict__ out, int tokens, int hk, int hv, int dv) {
+                         bf16* __restrict__ out, int tokens, int hk, int hv, int dv, long long state_stride) {
     constexpr int dk = 128;
+    // batched decode: grid z = sequence, one token each; rows and state move on by one sequence
+    if (blockIdx.z) {
+        const size_t z = blockIdx.z;
+        qkv += z * (size_t)(2 * hk * dk + hv * dv);
+        a += z * hv;
+        b += z * hv;
+        out += z * (size_t)hv * dv;
+        state += z * state_stride;
+    }
     __shared__ __align__(16) float skn[2][kRecBatch][4 * kRecQuarter];
     __shared__ __align__(16) float sqn[2][kRecBatch][4 * kRecQuarter];
     __shared__ float sv[2][kRecBatch][32];
@@ -524,6 +621,24 @@ extern "C" int qd_seq_add_rms_norm(const void* x, const void* residual, const fl
 
 extern "C" int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tokens, int rows, int width, void* stream) {
     QD_CHECK_ARG(x && w && y && tokens > 0 && rows > 0 && width > 0);
+    const uintptr_t align = (uintptr_t)x | (uintptr_t)w;
+    if (rows >= 4096 && width % 256 == 0 && width <= 256 * kTallMaxChunks && !(align & 15u) && (tokens + 31) / 32 <= 65535) {
+        // tall matrix: read every weight row once per tile of 32 tokens
+        const size_t smem = (size_t)kTallTokens * width * sizeof(bf16);
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
+        static bool configured[64];
+        if (!configured[dev]) {
+            if (cudaFuncSetAttribute(seq_bf16_matmul_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
+                return QD_ERR_LAUNCH;
+            configured[dev] = true;
+        }
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+        seq_bf16_matmul_tall_kernel<<<dim3(sms, (tokens + 31) / 32), 256, smem, (cudaStream_t)stream>>>(
+            (const bf16*)x, (const bf16*)w, (bf16*)y, tokens, rows, width);
+        return qd_launch_status();
+    }
     seq_bf16_matmul_kernel<<<dim3((rows + 7) / 8, tokens), 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)x, (const bf16*)w, (bf16*)y, rows, width);
     return qd_launch_status();
@@ -551,12 +666,36 @@ extern "C" int qd_seq_gdn_recurrence(const void* conv_qkv, const void* a, const 
     if (key_dim == 128) {
         seq_recurrence128_kernel<<<dim3(value_heads, (value_dim + 31) / 32), 128, 0, (cudaStream_t)stream>>>(
             (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
-            (bf16*)out, tokens, key_heads, value_heads, value_dim);
+            (bf16*)out, tokens, key_heads, value_heads, value_dim, 0);
         return qd_launch_status();
     }
     seq_recurrence_kernel<<<dim3(value_heads, (value_dim + 31) / 32), 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
         (bf16*)out, tokens, key_heads, value_heads, key_dim, value_dim);
+    return qd_launch_status();
+}
+
+/* batched decode: one token of each of `batch` sequences */
+extern "C" int qd_batch_gdn_conv(const void* mixed, const void* taps, void* conv_state, long long state_stride,
+                                 void* out, int batch, int channels, int width, void* stream) {
+    QD_CHECK_ARG(mixed && taps && out && batch > 0 && batch <= 65535 && channels > 0 && width >= 1 && width <= 8);
+    QD_CHECK_ARG(width == 1 || (conv_state && (batch == 1 || state_stride >= (long long)channels * (width - 1))));
+    batch_conv_kernel<<<dim3((channels + 127) / 128, batch), 128, 0, (cudaStream_t)stream>>>(
+        (const bf16*)mixed, (const bf16*)taps, (bf16*)conv_state, (bf16*)out, channels, width, state_stride);
+    return qd_launch_status();
+}
+
+extern "C" int qd_batch_gdn_recurrence(const void* conv_qkv, const void* a, const void* b, const void* a_log,
+                                       const void* dt_bias, float* rec_state, long long state_stride, void* out,
+                                       int batch, int key_heads, int value_heads, int key_dim, int value_dim,
+                                       void* stream) {
+    QD_CHECK_ARG(conv_qkv && a && b && a_log && dt_bias && rec_state && out && batch > 0 && batch <= 65535);
+    QD_CHECK_ARG(key_heads > 0 && value_heads % key_heads == 0 && key_dim > 0 && value_dim > 0);
+    QD_CHECK_ARG(batch == 1 || state_stride >= (long long)value_heads * key_dim * value_dim);
+    if (key_dim != 128) return QD_ERR_UNSUPPORTED;
+    seq_recurrence128_kernel<<<dim3(value_heads, (value_dim + 31) / 32, batch), 128, 0, (cudaStream_t)stream>>>(
+        (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
+        (bf16*)out, 1, key_heads, value_heads, value_dim, state_stride);
     return qd_launch_status();
 }
 
