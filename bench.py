@@ -262,6 +262,33 @@ def prefill_gemm_roofline(device, tokens=8192, rows=8192, width=2048, reps=10):
     return 2.0 * tokens * rows * width / per_launch_s / 1e12, per_launch_s
 
 
+def batch_decode_leg(ckpt, cfg, device, batch=32, context=8192, steps=8, warmup=2):
+    """Small-batch decode with per-sequence state: `batch` sequences that each hold `context`
+    tokens (caches filled with N(0,1) values, as the attention configuration of the baseline
+    does), one token per sequence per step; device-timed."""
+    from quickdraw_b200.batch import BatchDecode, BatchState
+    decoder = BatchDecode(ckpt)
+    state = BatchState(cfg, batch, context + warmup + steps, device)
+    state.kv_k.normal_()
+    state.kv_v.normal_()
+    state.positions.fill_(context)
+    gen = torch.Generator().manual_seed(1)
+    tokens = torch.randint(0, cfg.vocab_size, (batch,), generator=gen).to(device)
+    for _ in range(warmup):
+        tokens, _ = decoder.step(tokens, state, positions_checked=True)
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        tokens, _ = decoder.step(tokens, state, positions_checked=True)
+    e1.record()
+    torch.cuda.synchronize(device)
+    assert decoder.check() == 0
+    ms = e0.elapsed_time(e1) / steps
+    return {"batch": batch, "context": context, "steps": steps, "ms_per_step": ms, "tok_s": batch / (ms * 1e-3),
+            "state_bytes": state.memory_bytes(), "path": "tensor-core products with %d rows + batched state kernels" % batch}
+
+
 def run_gpu(args):
     rank, local, world = dist_env()
     torch.cuda.set_device(local)
@@ -332,6 +359,9 @@ def run_gpu(args):
         mv_gbs, mv_launch_s, mv_units = matvec_roofline(device)
     gemm_tflops, gemm_launch_s = prefill_gemm_roofline(device)
     tensor_peak, tensor_peak_kind = measured_tensor_peak()
+    batch_leg = None
+    if world == 1:
+        batch_leg = batch_decode_leg(ckpt, cfg, device)
     position = args.prompt + args.warmup + args.steps // 2
     token_bytes = bytes_per_token(cfg, position)
     tok_s = args.steps / (device_ms * 1e-3)
@@ -349,7 +379,7 @@ def run_gpu(args):
         "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 12,
                 "d2h_bytes_per_step": 8},
         "gpu_launches": launches * args.steps,
-        # outside the timed region: the prompt (chunks of 128 tokens through the tensor-core
+        # outside the timed region: the prompt (chunks of 512 tokens through the tensor-core
         # products on one GPU; token by token under expert parallelism) up to the first token
         "prefill": {"tokens": args.prompt, "ms": prefill_s * 1e3, "tok_s": args.prompt / prefill_s,
                     "path": "chunked" if getattr(engine, "sequence_prefill", False) else "token loop"},
@@ -371,6 +401,9 @@ def run_gpu(args):
                                   "achieved": gemm_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
                                   "frac": gemm_tflops / tensor_peak, "peak_source": f"{tensor_peak_kind} cuBLAS bf16",
                                   "launch_us": gemm_launch_s * 1e6},
+        # widening row: batch-32 decode with per-sequence KV and DeltaNet state (tok/s over all
+        # sequences); not part of `value`
+        "batch_decode": batch_leg,
         "cpu_baseline": {"value": 1.0 / per_token_cpu, "unit": "tok/s", "cores": threads, "kind": "port",
                          "sample": "one 4-layer group and the LM head at position 640, group time x12 + head time"},
     }
