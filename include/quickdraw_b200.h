@@ -119,6 +119,17 @@ int qd_batch_attn_decode(const void* qg, const void* k_new, const void* v_new, c
                          int batch, int capacity, int q_heads, int kv_heads, int head_dim,
                          int rotary_dim, float theta, float eps, int splits, void* stream);
 
+/* The same step as qd_batch_attn_decode in two launches: the chunk form's preparation (norm,
+ * RoPE, cache rows written at every sequence's position; q_scratch bf16 [batch, q_heads,
+ * head_dim]) and a kernel that gives every lane one cache position (32 row reads in flight per
+ * warp, one warp reduction per head and 32 positions instead of one per position).  Same
+ * arithmetic up to summation order.  head_dim a multiple of 32, rotary_dim a multiple of 64. */
+int qd_batch_attention(const void* qg, const void* k_new, const void* v_new, const void* q_norm,
+                       const void* k_norm, void* k_cache, void* v_cache, long long cache_stride,
+                       void* q_scratch, void* out, float* scratch, unsigned int* counters,
+                       const int* positions, int batch, int capacity, int q_heads, int kv_heads,
+                       int head_dim, int rotary_dim, float theta, float eps, int splits, void* stream);
+
 /* The stable order of the chunk's routes by expert (quickdraw/kernel/triton/moe.py:60-97, the
  * grouping the reference builds with a stable sort): ids int32 [routes], every id in
  * [0, experts); order int32 [routes] = route index of each sorted row, boundaries int32

@@ -60,6 +60,7 @@ SIGNATURES = {
     "qd_batch_gdn_conv": [P, P, P, L, P, I, I, I, P],
     "qd_batch_gdn_recurrence": [P, P, P, P, P, P, L, P, I, I, I, I, I, P],
     "qd_batch_attn_decode": [P, P, P, P, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
+    "qd_batch_attention": [P, P, P, P, P, P, P, L, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
     "qd_seq_group_routes": [P, I, I, P, P, P],
     "qd_seq_moe_combine": [P, P, P, P, P, I, I, I, P],
 }

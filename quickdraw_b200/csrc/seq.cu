@@ -408,10 +408,14 @@ __global__ void seq_attn_prepare_kernel(const bf16* __restrict__ qg, const bf16*
                                         const bf16* __restrict__ v_new, const bf16* __restrict__ q_norm,
                                         const bf16* __restrict__ k_norm, bf16* __restrict__ k_cache,
                                         bf16* __restrict__ v_cache, bf16* __restrict__ q_out, int position0, int hq,
-                                        int hk, int d, int rotary, float theta, float eps) {
+                                        int hk, int d, int rotary, float theta, float eps,
+                                        const int* __restrict__ positions, long long cache_stride) {
     const int t = blockIdx.y, head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (head >= hq + hk) return;
-    const int position = position0 + t;
+    // a chunk of one sequence: consecutive positions of one cache; batched decode: row t is
+    // sequence t at its own position in its own cache
+    const int position = positions ? positions[t] : position0 + t;
+    if (positions) { k_cache += (size_t)t * cache_stride; v_cache += (size_t)t * cache_stride; }
     const bool is_q = head < hq;
     const bf16* src = is_q ? qg + ((size_t)t * hq + head) * 2 * d : k_new + ((size_t)t * hk + (head - hq)) * d;
     const bf16* gamma_w = is_q ? q_norm : k_norm;
@@ -509,6 +513,195 @@ seq_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ qg, const b
             out[((size_t)t * hq + head) * d + f0 + j] = __float2bfloat16_rn(attended * gate);
         }
     }
+}
+
+// ------------------------------------------------ batched decode attention, lane = position
+// One decode step of `batch` sequences over their own caches (rows already prepared by the
+// kernel above: q normalised and rotated in q, the new key/value rows in the caches).
+// Block = (KV head, context split, sequence), 8 warps; a warp walks its share of the split in
+// chunks of 32 positions:
+//   scores   lane = one position: its key row against the G query heads (bf16 pairs from
+//            shared memory, mixed-precision FMA), 32 independent row reads per warp in flight
+//   softmax  per head over the chunk: one warp max and one warp sum per 32 positions
+//   values   lane = eight features: the chunk's value rows (coalesced 512-byte rows) weighted
+//            by the probabilities that went through shared memory
+// then the warps, and across blocks the splits, are merged as in the single-sequence kernel
+// (running maximum, sum and weighted values), output = bf16(attended) * bf16(sigmoid(gate)).
+constexpr int kLaneAttnWarps = 8, kLaneAttnGroup = 8, kLaneAttnSplitMin = 256;
+
+struct LaneAttnParams {
+    const bf16* q;          // [batch, hq, d] prepared queries
+    const bf16* qg;         // [batch, hq, 2 d] projection output (the gate is its second half)
+    const bf16* k_cache; const bf16* v_cache; long long cache_stride;
+    bf16* out;              // [batch, hq * d]
+    float* partial;         // [batch, hk, splits, G, d + 2]
+    unsigned int* counters; // [batch, hk], zero on entry and on exit
+    const int* positions;
+    int hq, hk, d, splits;
+};
+
+__global__ void __launch_bounds__(kLaneAttnWarps * 32)
+batch_attn_lanes_kernel(const LaneAttnParams p) {
+    extern __shared__ __align__(16) unsigned char lane_attn_smem[];
+    const int G = p.hq / p.hk, D = p.d, stride = D + 2;
+    bf16* qs = reinterpret_cast<bf16*>(lane_attn_smem);                                  // [G][D]
+    float* pbuf = reinterpret_cast<float*>(lane_attn_smem + (size_t)G * D * sizeof(bf16)); // [warps][32][8]
+    float* red = pbuf + kLaneAttnWarps * 32 * kLaneAttnGroup;                            // [warps][G][D + 2]
+    __shared__ int s_last;
+    const int kvh = blockIdx.x, split = blockIdx.y;
+    const size_t z = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int T = p.positions[z] + 1;
+    int active = (T + kLaneAttnSplitMin - 1) / kLaneAttnSplitMin;
+    if (active > p.splits) active = p.splits;
+    const int per = ((T + active - 1) / active + 31) & ~31;
+    const int t0 = split * per, t1 = min(T, t0 + per);
+    const bool mine = split < active && t0 < t1;
+    const bf16* kc = p.k_cache + z * p.cache_stride;
+    const bf16* vc = p.v_cache + z * p.cache_stride;
+
+    if (mine) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.q + (z * p.hq + (size_t)kvh * G) * D);
+        for (int i = tid; i < G * D / 8; i += kLaneAttnWarps * 32) reinterpret_cast<uint4*>(qs)[i] = __ldg(src + i);
+    }
+    __syncthreads();
+
+    const int f0 = lane * 8;
+    const bool lane_on = f0 < D;
+    float m[kLaneAttnGroup], l[kLaneAttnGroup], acc[kLaneAttnGroup][8];
+#pragma unroll
+    for (int h = 0; h < kLaneAttnGroup; ++h) {
+        m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
+    }
+    const float scale = rsqrtf((float)D);
+    float* mine_p = pbuf + warp * 32 * kLaneAttnGroup;
+    if (mine) {
+        for (int c = t0 + warp * 32; c < t1; c += kLaneAttnWarps * 32) {
+            const int count = min(32, t1 - c);
+            // ---- scores: this lane's position against every head
+            const int tl = c + min(lane, count - 1);
+            const bf16* krow = kc + ((size_t)tl * p.hk + kvh) * D;
+            float score[kLaneAttnGroup];
+#pragma unroll
+            for (int h = 0; h < kLaneAttnGroup; ++h) score[h] = 0.f;
+            for (int fb = 0; fb < D; fb += 32) {
+                uint4 kk[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) kk[i] = __ldg(reinterpret_cast<const uint4*>(krow + fb) + i);
+#pragma unroll
+                for (int h = 0; h < kLaneAttnGroup; ++h) {
+                    if (h < G) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint4 qq = *reinterpret_cast<const uint4*>(qs + h * D + fb + 8 * i);
+                            score[h] = fma_bf16_lo(kk[i].x, qq.x, score[h]); score[h] = fma_bf16_hi(kk[i].x, qq.x, score[h]);
+                            score[h] = fma_bf16_lo(kk[i].y, qq.y, score[h]); score[h] = fma_bf16_hi(kk[i].y, qq.y, score[h]);
+                            score[h] = fma_bf16_lo(kk[i].z, qq.z, score[h]); score[h] = fma_bf16_hi(kk[i].z, qq.z, score[h]);
+                            score[h] = fma_bf16_lo(kk[i].w, qq.w, score[h]); score[h] = fma_bf16_hi(kk[i].w, qq.w, score[h]);
+                        }
+                    }
+                }
+            }
+            // ---- softmax over the chunk, per head
+            float prob[kLaneAttnGroup];
+#pragma unroll
+            for (int h = 0; h < kLaneAttnGroup; ++h) {
+                prob[h] = 0.f;
+                if (h < G) {
+                    const float sc = lane < count ? score[h] * scale : -INFINITY;
+                    const float nm = fmaxf(m[h], warp_max(sc));
+                    const float fix = expf(m[h] - nm);
+                    prob[h] = lane < count ? expf(sc - nm) : 0.f;
+                    l[h] = l[h] * fix + warp_sum(prob[h]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[h][j] *= fix;
+                    m[h] = nm;
+                }
+            }
+            __syncwarp();
+            *reinterpret_cast<float4*>(mine_p + lane * kLaneAttnGroup) = make_float4(prob[0], prob[1], prob[2], prob[3]);
+            *reinterpret_cast<float4*>(mine_p + lane * kLaneAttnGroup + 4) = make_float4(prob[4], prob[5], prob[6], prob[7]);
+            __syncwarp();
+            // ---- values: this lane's eight features of every position of the chunk
+            if (lane_on) {
+#pragma unroll 4
+                for (int j = 0; j < count; ++j) {
+                    const uint4 vr = __ldg(reinterpret_cast<const uint4*>(vc + ((size_t)(c + j) * p.hk + kvh) * D + f0));
+                    const uint32_t vw[4] = {vr.x, vr.y, vr.z, vr.w};
+                    float vf[8];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) { vf[2 * q] = __uint_as_float(vw[q] << 16); vf[2 * q + 1] = __uint_as_float(vw[q] & 0xffff0000u); }
+                    const float4 pa = *reinterpret_cast<const float4*>(mine_p + j * kLaneAttnGroup);
+                    const float4 pb = *reinterpret_cast<const float4*>(mine_p + j * kLaneAttnGroup + 4);
+                    const float pr[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+                    for (int h = 0; h < kLaneAttnGroup; ++h) {
+                        if (h < G) {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc[h][e] += pr[h] * vf[e];
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ---- merge the warps of this block
+#pragma unroll
+    for (int h = 0; h < kLaneAttnGroup; ++h) {
+        if (h < G) {
+            float* dst = red + ((size_t)warp * G + h) * stride;
+            if (lane_on) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dst[f0 + j] = acc[h][j];
+            }
+            if (lane == 0) { dst[D] = m[h]; dst[D + 1] = l[h]; }
+        }
+    }
+    __syncthreads();
+    float* partial = p.partial + z * (size_t)p.hk * p.splits * G * stride;
+    float* block_out = partial + (((size_t)kvh * p.splits + split) * G) * stride;
+    for (int idx = tid; idx < G * D; idx += kLaneAttnWarps * 32) {
+        const int h = idx / D, f = idx % D;
+        float mm = -INFINITY;
+        for (int w = 0; w < kLaneAttnWarps; ++w) mm = fmaxf(mm, red[((size_t)w * G + h) * stride + D]);
+        float num = 0.f, den = 0.f;
+        for (int w = 0; w < kLaneAttnWarps; ++w) {
+            const float* src = red + ((size_t)w * G + h) * stride;
+            const float wgt = src[D] == -INFINITY ? 0.f : expf(src[D] - mm);
+            num += wgt * src[f];
+            den += wgt * src[D + 1];
+        }
+        block_out[(size_t)h * stride + f] = num;
+        if (f == 0) { block_out[(size_t)h * stride + D] = mm; block_out[(size_t)h * stride + D + 1] = den; }
+    }
+    __threadfence();
+    __syncthreads();
+    unsigned int* counter = p.counters + z * p.hk + kvh;
+    if (tid == 0) s_last = atomicAdd(counter, 1u) == (unsigned int)p.splits - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // ---- last block of this (sequence, KV head): merge the splits, normalise, gate
+    for (int idx = tid; idx < G * D; idx += kLaneAttnWarps * 32) {
+        const int h = idx / D, f = idx % D;
+        float mm = -INFINITY;
+        for (int s = 0; s < active; ++s) mm = fmaxf(mm, __ldcg(partial + (((size_t)kvh * p.splits + s) * G + h) * stride + D));
+        float num = 0.f, den = 0.f;
+        for (int s = 0; s < active; ++s) {
+            const float* src = partial + (((size_t)kvh * p.splits + s) * G + h) * stride;
+            const float sm_ = __ldcg(src + D);
+            const float wgt = sm_ == -INFINITY ? 0.f : expf(sm_ - mm);
+            num += wgt * __ldcg(src + f);
+            den += wgt * __ldcg(src + D + 1);
+        }
+        const float attended = round_bf16(num / den);
+        const int qh = kvh * G + h;
+        const float gate = round_bf16(sigmoid_precise(ld_bf16(p.qg + (z * p.hq + qh) * 2 * (size_t)D + D + f)));
+        p.out[(z * p.hq + qh) * (size_t)D + f] = __float2bfloat16_rn(attended * gate);
+    }
+    if (tid == 0) *counter = 0;
 }
 
 // ----------------------------------------------------------------------------- routing
@@ -710,11 +903,52 @@ extern "C" int qd_seq_attention(const void* qg, const void* k_new, const void* v
     const int heads = q_heads + kv_heads;
     seq_attn_prepare_kernel<<<dim3((heads + 7) / 8, tokens), 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)qg, (const bf16*)k_new, (const bf16*)v_new, (const bf16*)q_norm, (const bf16*)k_norm,
-        (bf16*)k_cache, (bf16*)v_cache, (bf16*)q_scratch, position0, q_heads, kv_heads, head_dim, rotary_dim, theta, eps);
+        (bf16*)k_cache, (bf16*)v_cache, (bf16*)q_scratch, position0, q_heads, kv_heads, head_dim, rotary_dim, theta, eps,
+        nullptr, 0);
     if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     seq_attn_kernel<<<dim3(kv_heads, tokens), 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)q_scratch, (const bf16*)qg, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, position0,
         q_heads, kv_heads, head_dim);
+    return qd_launch_status();
+}
+
+/* batched decode attention: prepare (norm, RoPE, cache write at every sequence's position)
+ * and the lane-per-position kernel */
+extern "C" int qd_batch_attention(const void* qg, const void* k_new, const void* v_new, const void* q_norm,
+                                  const void* k_norm, void* k_cache, void* v_cache, long long cache_stride,
+                                  void* q_scratch, void* out, float* scratch, unsigned int* counters,
+                                  const int* positions, int batch, int capacity, int q_heads, int kv_heads,
+                                  int head_dim, int rotary_dim, float theta, float eps, int splits, void* stream) {
+    QD_CHECK_ARG(qg && k_new && v_new && q_norm && k_norm && k_cache && v_cache && q_scratch && out && scratch && counters && positions);
+    QD_CHECK_ARG(batch > 0 && batch <= 65535 && capacity > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && splits >= 1);
+    QD_CHECK_ARG(batch == 1 || cache_stride >= (long long)capacity * kv_heads * head_dim);
+    const int G = q_heads / kv_heads;
+    if (head_dim > 256 || head_dim % 32 != 0 || G > kLaneAttnGroup || rotary_dim % 64 != 0 || rotary_dim > head_dim)
+        return QD_ERR_UNSUPPORTED;
+    const uintptr_t align = (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q_scratch;
+    if ((align & 15u) || (cache_stride & 7)) return QD_ERR_UNSUPPORTED;
+    const int heads = q_heads + kv_heads;
+    seq_attn_prepare_kernel<<<dim3((heads + 7) / 8, batch), 256, 0, (cudaStream_t)stream>>>(
+        (const bf16*)qg, (const bf16*)k_new, (const bf16*)v_new, (const bf16*)q_norm, (const bf16*)k_norm,
+        (bf16*)k_cache, (bf16*)v_cache, (bf16*)q_scratch, 0, q_heads, kv_heads, head_dim, rotary_dim, theta, eps,
+        positions, cache_stride);
+    if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
+    LaneAttnParams p;
+    p.q = (const bf16*)q_scratch; p.qg = (const bf16*)qg; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+    p.cache_stride = cache_stride; p.out = (bf16*)out; p.partial = scratch; p.counters = counters; p.positions = positions;
+    p.hq = q_heads; p.hk = kv_heads; p.d = head_dim; p.splits = splits;
+    const size_t smem = (size_t)G * head_dim * sizeof(bf16) + sizeof(float) * (kLaneAttnWarps * 32 * kLaneAttnGroup +
+                                                                                (size_t)kLaneAttnWarps * G * (head_dim + 2));
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
+    static bool configured[64];
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(batch_attn_lanes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
+            return QD_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    if (smem > 100 * 1024) return QD_ERR_UNSUPPORTED;
+    batch_attn_lanes_kernel<<<dim3(kv_heads, splits, batch), kLaneAttnWarps * 32, smem, (cudaStream_t)stream>>>(p);
     return qd_launch_status();
 }
 

@@ -71,6 +71,19 @@ def test_batched_state_kernels_equal_single_sequence_kernels(cuda_device):
         assert torch.equal(out, out_b[i]), (i, [O.rel_l2(out.float().cpu(), out_b[j].float().cpu()) for j in range(batch)])
     assert torch.equal(kb, ks) and torch.equal(vb, vs) and int(counters.abs().sum()) == 0
 
+    # the lane-per-position form: same step up to summation order
+    kl, vl = k0.clone(), v0.clone()
+    out_l, q_scratch = torch.empty_like(out_b), torch.empty(batch, hq * d, dtype=torch.bfloat16, device=dev)
+    for lane_splits in (8, 1):
+        call("qd_batch_attention", ptr(qg), ptr(k_new), ptr(v_new), ptr(q_norm), ptr(k_norm), ptr(kl[0, layer]),
+             ptr(vl[0, layer]), kl.stride(0), ptr(q_scratch), ptr(out_l), ptr(scratch), ptr(counters), ptr(positions),
+             batch, cap, hq, hkv, d, 64, 1e6, 1e-6, lane_splits, s)
+        torch.cuda.synchronize()
+        for i in range(batch):
+            assert O.rel_l2(out_l[i].float().cpu(), out_b[i].float().cpu()) < 1e-2, (lane_splits, i)
+        assert O.rel_l2(kl.float().cpu(), kb.float().cpu()) < 1e-3 and torch.equal(vl, vb)
+        assert int(counters.abs().sum()) == 0
+
 
 def test_tall_projection_equals_row_by_row(cuda_device):
     from quickdraw_b200._lib import call, ptr, stream_of
