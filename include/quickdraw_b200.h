@@ -123,7 +123,9 @@ int qd_batch_attn_decode(const void* qg, const void* k_new, const void* v_new, c
  * RoPE, cache rows written at every sequence's position; q_scratch bf16 [batch, q_heads,
  * head_dim]) and a kernel that gives every lane one cache position (32 row reads in flight per
  * warp, one warp reduction per head and 32 positions instead of one per position).  Same
- * arithmetic up to summation order.  head_dim a multiple of 32, rotary_dim a multiple of 64. */
+ * arithmetic up to summation order.  head_dim a multiple of 32, rotary_dim a multiple of 64.
+ * cache_stride 0: the rows are the tokens of one prompt chunk (ascending positions) sharing
+ * one cache - the causal attention of the chunked prefill. */
 int qd_batch_attention(const void* qg, const void* k_new, const void* v_new, const void* q_norm,
                        const void* k_norm, void* k_cache, void* v_cache, long long cache_stride,
                        void* q_scratch, void* out, float* scratch, unsigned int* counters,

@@ -921,7 +921,9 @@ extern "C" int qd_batch_attention(const void* qg, const void* k_new, const void*
                                   int head_dim, int rotary_dim, float theta, float eps, int splits, void* stream) {
     QD_CHECK_ARG(qg && k_new && v_new && q_norm && k_norm && k_cache && v_cache && q_scratch && out && scratch && counters && positions);
     QD_CHECK_ARG(batch > 0 && batch <= 65535 && capacity > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && splits >= 1);
-    QD_CHECK_ARG(batch == 1 || cache_stride >= (long long)capacity * kv_heads * head_dim);
+    // cache_stride 0: the rows are consecutive tokens of ONE sequence (a prompt chunk; positions
+    // ascending), every row attends over the shared cache up to its own position
+    QD_CHECK_ARG(batch == 1 || cache_stride == 0 || cache_stride >= (long long)capacity * kv_heads * head_dim);
     const int G = q_heads / kv_heads;
     if (head_dim > 256 || head_dim % 32 != 0 || G > kLaneAttnGroup || rotary_dim % 64 != 0 || rotary_dim > head_dim)
         return QD_ERR_UNSUPPORTED;
