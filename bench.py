@@ -379,7 +379,7 @@ def run_gpu(args):
         "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 12,
                 "d2h_bytes_per_step": 8},
         "gpu_launches": launches * args.steps,
-        # outside the timed region: the prompt (chunks of 512 tokens through the tensor-core
+        # outside the timed region: the prompt (chunks of up to 2048 tokens through the tensor-core
         # products on one GPU; token by token under expert parallelism) up to the first token
         "prefill": {"tokens": args.prompt, "ms": prefill_s * 1e3, "tok_s": args.prompt / prefill_s,
                     "path": "chunked" if getattr(engine, "sequence_prefill", False) else "token loop"},

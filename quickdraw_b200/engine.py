@@ -29,7 +29,7 @@ from .weights import Checkpoint
 class Engine:
     def __init__(self, ckpt: Checkpoint, max_context: int = 32768, device: str = "cuda",
                  backend: str | None = None, *, kernels: dict | None = None, step=None,
-                 cuda_graph: bool = True, prefill_chunk_size: int = 512,
+                 cuda_graph: bool = True, prefill_chunk_size: int = 2048,
                  sequence_prefill: bool = True, _step_object=None):
         custom = kernels is not None or step is not None
         if backend is None:
