@@ -40,13 +40,17 @@ def test_chunked_prefill_matches_token_loop(cuda_device, chunk):
     assert O.rel_l2(got.cpu(), want.cpu()) < 5e-2
 
 
-def test_grouped_matmul_matches_per_route_matvec(cuda_device):
+@pytest.mark.parametrize("experts,topk,tokens,width,rows", [
+    (8, 3, 21, 512, 264),          # few tiles: 64-row weight tiles
+    (40, 2, 30, 256, 256),         # 128-row weight tiles
+    (64, 2, 40, 256, 768),         # every SM busy: 256-row (or balanced 128-row) weight tiles
+])
+def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tokens, width, rows):
     """The grouped product of the routed experts against the single-token expert matvec."""
     from quickdraw_b200 import kernels
     from quickdraw_b200.prefill import ChunkPrefill
     from quickdraw_b200.synthetic import to_device
     src = synthetic.Source(31, "cpu")
-    experts, topk, tokens, width, rows = 8, 3, 21, 512, 264
     bank = to_device(src.nvfp4("bank", rows, width, experts, global_scale=0.5, per_expert_global=True), cuda_device)
     x = src.normal("x", tokens, width).to(cuda_device)
     gen = torch.Generator().manual_seed(3)
