@@ -24,7 +24,7 @@ from .state import DecodeState
 from .weights import Checkpoint
 
 BF16 = torch.bfloat16
-ATTN_SPLITS = 16        # context splits per (sequence, KV head)
+MAX_ATTN_SPLITS = 16    # context splits per (sequence, KV head), at most
 
 
 class BatchState:
@@ -57,11 +57,17 @@ class BatchDecode(ChunkPrefill):
         self.final_gamma = (1 + ckpt.final_norm.float()).contiguous()
         self._scratch = None
 
+    def _attn_splits(self, batch):
+        """About two blocks per SM: every extra split costs a merge (32 sequences x 2 KV heads at
+        context 8192: 4 splits 4.4 ms, 16 splits 5.7 ms of the step)."""
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        return max(1, min(MAX_ATTN_SPLITS, 2 * sms // (batch * self.ckpt.config.num_key_value_heads)))
+
     def _attn_scratch(self, batch):
         c = self.ckpt.config
         if self._scratch is None or self._scratch[0] < batch:
             floats = lib().qd_attn_scratch_floats(c.num_attention_heads, c.num_key_value_heads, c.head_dim,
-                                                  ATTN_SPLITS)
+                                                  MAX_ATTN_SPLITS)
             self._scratch = (batch, torch.empty(batch * floats, dtype=torch.float32, device=self.device),
                              torch.zeros(batch * c.num_key_value_heads, dtype=torch.int32, device=self.device))
         return self._scratch[1], self._scratch[2]
@@ -97,7 +103,7 @@ class BatchDecode(ChunkPrefill):
         call("qd_batch_attention", ptr(qg), ptr(k), ptr(v), ptr(w.q_norm), ptr(w.k_norm), ptr(k_cache[0]),
              ptr(v_cache[0]), k_cache.stride(0), ptr(q_scratch), ptr(out), ptr(scratch), ptr(counters),
              ptr(state.positions), batch, state.max_context, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
-             int(c.head_dim * c.partial_rotary_factor), c.rope_theta, c.rms_norm_eps, ATTN_SPLITS, stream_of(x))
+             int(c.head_dim * c.partial_rotary_factor), c.rope_theta, c.rms_norm_eps, self._attn_splits(batch), stream_of(x))
         return self._matmul(out, w.o_proj)
 
     # ------------------------------------------------------------------------------ step

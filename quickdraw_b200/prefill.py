@@ -96,7 +96,8 @@ class ChunkPrefill:
         out = torch.empty_like(q_scratch)
         # the batched decode attention with every row at its own position of the one cache
         positions = torch.arange(position0, position0 + tokens, dtype=torch.int32, device=self.device)
-        splits = max(1, min(16, (position0 + tokens + 255) // 256))
+        # context splits only while the chunk's rows alone do not fill the GPU (a split costs a merge)
+        splits = max(1, min(16, (position0 + tokens + 255) // 256, 296 // (tokens * c.num_key_value_heads)))
         floats = lib().qd_attn_scratch_floats(c.num_attention_heads, c.num_key_value_heads, c.head_dim, splits)
         scratch = self._empty(tokens * floats, dtype=torch.float32)
         counters = torch.zeros(tokens * c.num_key_value_heads, dtype=torch.int32, device=self.device)
