@@ -32,28 +32,31 @@ constexpr int kTileM = 256;                 // tokens per tile: two halves of 12
 // weight rows per tile (tensor memory columns per accumulator): template parameter TN, 256 for
 // large problems, 128 or 64 where 256 would leave most SMs without a tile
 constexpr int kTileK = 64;                  // inputs per stage
-constexpr int kStages = 3;
+// Tile heights: 256 tokens (two 128-token halves; the plain product and large grouped tiles) or
+// 128 (grouped product with few rows per expert: 2 stages of 48 KB and 8 producer warps, so that
+// two blocks share an SM and one block's prologue and epilogue overlap the other's K loop).
+constexpr int stages_of(int tm) { return tm == 128 ? 2 : 3; }
+constexpr int blocks_per_sm(int tm) { return tm == 128 ? 2 : 1; }
 // Producer warps: 8 for the plain product (they only expand weights), 16 for the grouped product
 // (they also gather the activation rows, and an expert's weights come from DRAM, not from L2:
 // more warps keep more loads in flight; measured 171 -> 149 us on the gate bank of a
 // 511-token chunk).  The block is warp 0 + producers + loader warp.
-constexpr int producer_warps(bool dense) { return dense ? 8 : 16; }
-constexpr int block_threads(bool dense) { return (2 + producer_warps(dense)) * 32; }
+constexpr int producer_warps(bool dense, int tm) { return (dense || tm == 128) ? 8 : 16; }
+constexpr int block_threads(bool dense, int tm) { return (2 + producer_warps(dense, tm)) * 32; }
 // The producer warps work in kGroups groups on alternate K steps, so that two stages fill at
 // the same time (measured: plain product 1 104 -> 1 138 TFLOP/s, grouped product unchanged).
 #ifndef QD_GEMM_GROUPS
 #define QD_GEMM_GROUPS 2
 #endif
-constexpr int kGroups = QD_GEMM_GROUPS;
-constexpr int group_threads(bool dense) { return producer_warps(dense) * 32 / kGroups; }
+constexpr int groups_of(int tm) { return tm == 128 ? 1 : QD_GEMM_GROUPS; }
+constexpr int group_threads(bool dense, int tm) { return producer_warps(dense, tm) * 32 / groups_of(tm); }
 // Both operands of a stage use the 128-byte swizzled K-major layout: row r of the tile is 128
 // bytes (64 inputs) at r * 128, its 16-byte piece c stored at piece c ^ (r & 7).  The TMA load
 // writes it for the activations of the plain product; the producers write it themselves for
 // the weights (and for the gathered activation rows of the grouped product).
-constexpr int kABytes = kTileM * kTileK * 2;                // 32 KB
-constexpr int kATmaBytes = kABytes;                         // bytes one activation tile load delivers
-constexpr int kBBytesMax = 256 * kTileK * 2;                // 32 KB at 256 rows
-constexpr int kStageBytes = kABytes + kBBytesMax;
+constexpr int a_bytes(int tm) { return tm * kTileK * 2; }                  // 32 KB at 256 tokens
+constexpr int kBBytesMax = 256 * kTileK * 2;                                // 32 KB at 256 rows
+constexpr int stage_bytes(int tm) { return a_bytes(tm) + kBBytesMax; }
 
 struct GemmParams {
     const bf16* x; const uint8_t* codes; const uint8_t* scales; const float* global; bf16* y;
@@ -143,23 +146,25 @@ QD_DEVINL uint4 expand8(uint32_t word, float scale) {
     return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
-template <bool DENSE>
+template <bool DENSE, int TM>
 struct StageRegs {
-    static constexpr int kXPieces = kTileM * (kTileK / 8) / group_threads(DENSE);   // 16-byte activation pieces per thread
-    static constexpr int kWPieces = 256 * 2 / group_threads(DENSE);                 // 16-byte code pieces per thread
+    static constexpr int kXPieces = TM * (kTileK / 8) / group_threads(DENSE, TM);   // 16-byte activation pieces per thread
+    static constexpr int kWPieces = 256 * 2 / group_threads(DENSE, TM);             // 16-byte code pieces per thread
     uint4 wc[kWPieces];               // 16-byte pieces of codes (32 weights each)
     uint16_t ws[kWPieces];            // their two block scales each
 };
 
 // DENSE: plain product (activation tiles by TMA through `xmap`); otherwise the grouped product.
-template <int TN, bool DENSE, int AHEAD>
-__global__ void __launch_bounds__(block_threads(DENSE), 1)
+template <int TN, bool DENSE, int AHEAD, int TM>
+__global__ void __launch_bounds__(block_threads(DENSE, TM), blocks_per_sm(TM))
 nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
-    constexpr int kProducerWarps = producer_warps(DENSE), kProducerThreads = group_threads(DENSE);
-    constexpr int kThreads = block_threads(DENSE), kLoaderWarp = 1 + kProducerWarps;
-    constexpr int kXPieces = StageRegs<DENSE>::kXPieces, kWPiecesPerThread = StageRegs<DENSE>::kWPieces;
+    constexpr int kProducerWarps = producer_warps(DENSE, TM), kProducerThreads = group_threads(DENSE, TM);
+    constexpr int kThreads = block_threads(DENSE, TM), kLoaderWarp = 1 + kProducerWarps;
+    constexpr int kGroups = groups_of(TM), kStages = stages_of(TM), kTileM = TM;
+    constexpr int kABytes = a_bytes(TM), kATmaBytes = kABytes, kStageBytes = stage_bytes(TM);
+    constexpr int kXPieces = StageRegs<DENSE, TM>::kXPieces, kWPiecesPerThread = StageRegs<DENSE, TM>::kWPieces;
     constexpr int kTileN = TN;
-    constexpr int kTmemCols = 2 * TN;            // one 128 x TN fp32 accumulator per token half
+    constexpr int kTmemCols = (TM / 128) * TN;   // one 128 x TN fp32 accumulator per token half
     constexpr uint32_t kInstrDesc = instr_desc<TN>();
     constexpr int kWPieces = TN * 2;             // 16-byte code pieces of a stage: (row, 32-input half)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -261,7 +266,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         // ------------------------------------------------------------------- producers
         const int group = (tid - 32) / kProducerThreads;          // this warp's K steps: group, group + kGroups, ...
         const int pt = (tid - 32) % kProducerThreads;           // thread within the group
-        StageRegs<DENSE> cur, nxt, far;      // K steps s, s + 1 and (AHEAD == 2) s + 2
+        StageRegs<DENSE, TM> cur, nxt, far;      // K steps s, s + 1 and (AHEAD == 2) s + 2
         // the eight activation rows this thread copies pieces of (piece = (row, 8-input group))
         const bf16* xrow[DENSE ? 1 : kXPieces];
         if (!DENSE) {
@@ -286,7 +291,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
                 for (int off = 0; off < K / 16; off += 128) prefetch_l2(row_scales + off);
             }
         }
-        auto fetch = [&](int s, StageRegs<DENSE>& r) {
+        auto fetch = [&](int s, StageRegs<DENSE, TM>& r) {
             const int k0 = s * kTileK;
 #pragma unroll
             for (int i = 0; i < kWPiecesPerThread; ++i) {   // weights: piece = (row, 32-input half of the stage)
@@ -301,7 +306,7 @@ nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
                 }
             }
         };
-        auto store = [&](int st, int s, const StageRegs<DENSE>& r) {
+        auto store = [&](int st, int s, const StageRegs<DENSE, TM>& r) {
             uint8_t* a = smem + st * kStageBytes;
             uint8_t* b = a + kABytes;
             // rows without a token are not stored: an accumulator row depends on its own activation
@@ -429,15 +434,15 @@ static int activation_map(const GemmParams& p, CUtensorMap* map) {
     return r == CUDA_SUCCESS ? QD_OK : QD_ERR_LAUNCH;
 }
 
-template <int TN, bool DENSE, int AHEAD>
+template <int TN, bool DENSE, int AHEAD, int TM>
 static int launch_variant(const GemmParams& p, int row_tiles, cudaStream_t stream) {
     // + 1024: the kernel moves its base up to a 1024-byte boundary
-    const size_t smem = (size_t)kStages * kStageBytes + (2 * kStages + 1) * 8 + 16 + 1024;
+    const size_t smem = (size_t)stages_of(TM) * stage_bytes(TM) + (2 * stages_of(TM) + 1) * 8 + 16 + 1024;
     static bool configured[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
     if (!configured[dev]) {
-        if (cudaFuncSetAttribute(nvfp4_gemm_kernel<TN, DENSE, AHEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(nvfp4_gemm_kernel<TN, DENSE, AHEAD, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return QD_ERR_LAUNCH;
         configured[dev] = true;
     }
@@ -447,12 +452,12 @@ static int launch_variant(const GemmParams& p, int row_tiles, cudaStream_t strea
         if (rc != QD_OK) return rc;
     }
     dim3 grid(row_tiles, (p.out_features + TN - 1) / TN);
-    return qd_launch(nvfp4_gemm_kernel<TN, DENSE, AHEAD>, grid, dim3(block_threads(DENSE)), smem, stream, false, p, map);
+    return qd_launch(nvfp4_gemm_kernel<TN, DENSE, AHEAD, TM>, grid, dim3(block_threads(DENSE, TM)), smem, stream, false, p, map);
 }
 
 // The widest weight tile that still gives every SM a tile (narrower tiles expand fewer weights
 // per block, so small problems finish sooner); `busy_row_tiles`: row tiles that will have rows.
-template <bool DENSE>
+template <bool DENSE, int TM>
 static int launch_gemm(const GemmParams& p, int row_tiles, int busy_row_tiles, cudaStream_t stream) {
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
@@ -463,9 +468,9 @@ static int launch_gemm(const GemmParams& p, int row_tiles, int busy_row_tiles, c
     constexpr int kAhead = DENSE ? 2 : 1;
     // (narrower tiles to balance the last round of blocks do not pay: a 128-row block takes far
     // more than half the time of a 256-row block - gate bank of a 511-token chunk 143 -> 191 us)
-    if (wide >= sms) return launch_variant<256, DENSE, kAhead>(p, row_tiles, stream);
-    if (4 * wide >= sms) return launch_variant<128, DENSE, kAhead>(p, row_tiles, stream);
-    return launch_variant<64, DENSE, kAhead>(p, row_tiles, stream);
+    if (wide >= sms) return launch_variant<256, DENSE, kAhead, TM>(p, row_tiles, stream);
+    if (4 * wide >= sms) return launch_variant<128, DENSE, kAhead, TM>(p, row_tiles, stream);
+    return launch_variant<64, DENSE, kAhead, TM>(p, row_tiles, stream);
 }
 
 // matmul(x, proj) for a 2-D x — quickdraw/kernel/triton/matvec.py:153-163 (NVFP4 branch).
@@ -480,7 +485,7 @@ extern "C" int qd_nvfp4_matmul(const void* x, const void* codes, const void* sca
     p.x = (const bf16*)x; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
     p.y = (bf16*)y; p.tokens = tokens; p.out_features = out_features; p.in_features = in_features; p.status = status;
     const int row_tiles = (tokens + kTileM - 1) / kTileM;
-    return launch_gemm<true>(p, row_tiles, row_tiles, (cudaStream_t)stream);
+    return launch_gemm<true, 256>(p, row_tiles, row_tiles, (cudaStream_t)stream);
 }
 
 // grouped_matmul(x, bank, grouping, routing=None) — quickdraw/kernel/triton/moe.py:99-151: the
@@ -508,11 +513,16 @@ extern "C" int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const v
     p.by_token = by_token; p.scatter = scatter; p.global_per_expert = global_per_expert;
     p.codes_stride = (long long)out_features * (in_features / 2);
     p.scales_stride = (long long)out_features * (in_features / 16);
+    // Few rows per expert (a chunk of some hundred tokens, a decode batch): 128-token tiles, two
+    // blocks per SM.  Many rows: 256-token tiles, which expand an expert's weights once per 256.
+    const bool small = (long long)routes <= 64ll * experts;
+    const int tile = small ? 128 : 256;
     // non-empty row tiles: at most one partly filled tile per expert that received routes plus
     // the full ones, and never more than the caller's bound per expert allows
     const int busy = experts < routes ? experts : routes;
-    const long long by_bound = (long long)experts * ((max_rows_per_expert + kTileM - 1) / kTileM);
-    const long long by_count = (long long)busy + routes / kTileM;
+    const long long by_bound = (long long)experts * ((max_rows_per_expert + tile - 1) / tile);
+    const long long by_count = (long long)busy + routes / tile;
     const int row_tiles = (int)(by_bound < by_count ? by_bound : by_count);
-    return launch_gemm<false>(p, row_tiles, busy, (cudaStream_t)stream);
+    return small ? launch_gemm<false, 128>(p, row_tiles, busy, (cudaStream_t)stream)
+                 : launch_gemm<false, 256>(p, row_tiles, busy, (cudaStream_t)stream);
 }
