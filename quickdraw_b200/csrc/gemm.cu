@@ -420,13 +420,13 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // Tensor map of the activations X[tokens, in_features] (bf16, row-major) with a box of one
-// stage tile: 64 inputs x 256 tokens, 128-byte swizzle, zeros outside the tensor.
-static int activation_map(const GemmParams& p, CUtensorMap* map) {
+// stage tile: 64 inputs x 256 (or 128) tokens, 128-byte swizzle, zeros outside the tensor.
+static int activation_map(const GemmParams& p, CUtensorMap* map, int tile_tokens) {
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return QD_ERR_UNSUPPORTED;
     const cuuint64_t dims[2] = {(cuuint64_t)p.in_features, (cuuint64_t)p.tokens};
     const cuuint64_t strides[1] = {(cuuint64_t)p.in_features * sizeof(bf16)};
-    const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kTileM};
+    const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)tile_tokens};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(p.x), dims, strides, box, elem,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -448,7 +448,7 @@ static int launch_variant(const GemmParams& p, int row_tiles, cudaStream_t strea
     }
     alignas(64) CUtensorMap map = {};
     if (DENSE) {
-        const int rc = activation_map(p, &map);
+        const int rc = activation_map(p, &map, TM);
         if (rc != QD_OK) return rc;
     }
     dim3 grid(row_tiles, (p.out_features + TN - 1) / TN);
@@ -485,6 +485,16 @@ extern "C" int qd_nvfp4_matmul(const void* x, const void* codes, const void* sca
     p.x = (const bf16*)x; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
     p.y = (bf16*)y; p.tokens = tokens; p.out_features = out_features; p.in_features = in_features; p.status = status;
     const int row_tiles = (tokens + kTileM - 1) / kTileM;
+    // so few 256-token tiles that even 64-row weight tiles leave SMs idle: 128-token tiles, two
+    // blocks per SM (measured on a 511-token chunk: better for the projections up to 4096 rows,
+    // worse for 8192 rows, where 128-row weight tiles already fill the GPU)
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (4ll * row_tiles * ((out_features + 255) / 256) < (sms > 0 ? sms : 148)) {
+        const int small_tiles = (tokens + 127) / 128;
+        return launch_gemm<true, 128>(p, small_tiles, small_tiles, (cudaStream_t)stream);
+    }
     return launch_gemm<true, 256>(p, row_tiles, row_tiles, (cudaStream_t)stream);
 }
 
