@@ -189,7 +189,14 @@ __global__ void batch_conv_kernel(const bf16* __restrict__ mixed, const bf16* __
 // Arithmetic per token as in the single-token kernel (quickdraw/kernel/triton/delta.py:41-78):
 // S *= decay; pred = S^T k; S += k (x) beta (v - pred); out = S^T q.
 constexpr int kRecBatch = 16;
-constexpr int kRecQuarter = 36;              // floats per key quarter in shared memory (32 + 4: no bank conflicts)
+#ifndef QD_REC_PARTS
+#define QD_REC_PARTS 4
+#endif
+constexpr int kRecParts = QD_REC_PARTS;              // lanes that share a column (4 or 8), each with 128 / parts keys
+                                                     // (8 was measured: twice the blocks, same time per chunk)
+constexpr int kRecKeys = 128 / kRecParts;            // state entries per lane
+constexpr int kRecPitch = kRecKeys + 4;              // floats per part in shared memory (+ 4: no bank conflicts)
+constexpr int kRecCols = 4 * 32 / kRecParts;         // value columns per block (four warps)
 
 struct RecPrefetch { uint2 k[kRecBatch / 4], q[kRecBatch / 4]; bf16 v[kRecBatch / 4], a[kRecBatch / 4], b[kRecBatch / 4]; };
 
@@ -207,21 +214,21 @@ seq_recurrence128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ 
         out += z * (size_t)hv * dv;
         state += z * state_stride;
     }
-    __shared__ __align__(16) float skn[2][kRecBatch][4 * kRecQuarter];
-    __shared__ __align__(16) float sqn[2][kRecBatch][4 * kRecQuarter];
+    __shared__ __align__(16) float skn[2][kRecBatch][kRecParts * kRecPitch];
+    __shared__ __align__(16) float sqn[2][kRecBatch][kRecParts * kRecPitch];
     __shared__ float sv[2][kRecBatch][32];
     __shared__ float sgate[2][kRecBatch][2];
-    const int head = blockIdx.x, c0 = blockIdx.y * 32;
+    const int head = blockIdx.x, c0 = blockIdx.y * kRecCols;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int quarter = lane & 3, col = warp * 8 + (lane >> 2);
+    const int quarter = lane & (kRecParts - 1), col = warp * (32 / kRecParts) + lane / kRecParts;
     const int key_head = head / (hv / hk);
     const bool col_ok = c0 + col < dv;
     const int channels = 2 * hk * dk + hv * dv;
     const float a_decay = ld_bf16(a_log + head), bias = ld_bf16(dt_bias + head);
-    float* tile = state + (size_t)head * dk * dv + (size_t)quarter * 32 * dv + c0 + col;
-    float s[32];
+    float* tile = state + (size_t)head * dk * dv + (size_t)quarter * kRecKeys * dv + c0 + col;
+    float s[kRecKeys];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) s[j] = col_ok ? tile[(size_t)j * dv] : 0.f;
+    for (int j = 0; j < kRecKeys; ++j) s[j] = col_ok ? tile[(size_t)j * dv] : 0.f;
 
     // warp w prepares tokens w, w + 4, w + 8, w + 12 of a batch; lane l holds keys 4l .. 4l + 3
     auto issue = [&](int batch, RecPrefetch& r) {
@@ -232,7 +239,7 @@ seq_recurrence128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ 
             const bf16* row = qkv + (size_t)t * channels;
             r.q[i] = __ldg(reinterpret_cast<const uint2*>(row + (size_t)key_head * dk + 4 * lane));
             r.k[i] = __ldg(reinterpret_cast<const uint2*>(row + (size_t)(hk + key_head) * dk + 4 * lane));
-            r.v[i] = (c0 + lane < dv) ? row[(size_t)2 * hk * dk + (size_t)head * dv + c0 + lane] : __float2bfloat16_rn(0.f);
+            r.v[i] = (lane < kRecCols && c0 + lane < dv) ? row[(size_t)2 * hk * dk + (size_t)head * dv + c0 + lane] : __float2bfloat16_rn(0.f);
             r.a[i] = a[(size_t)t * hv + head];
             r.b[i] = b[(size_t)t * hv + head];
         }
@@ -251,7 +258,7 @@ seq_recurrence128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ 
 #pragma unroll
             for (int e = 0; e < 4; ++e) { qq += q4[e] * q4[e]; kk += k4[e] * k4[e]; }
             const float qscale = rsqrtf(warp_sum(qq) + 1e-6f), kscale = rsqrtf(warp_sum(kk) + 1e-6f);
-            const int at = (lane >> 3) * kRecQuarter + (lane & 7) * 4;
+            const int at = ((4 * lane) / kRecKeys) * kRecPitch + (4 * lane) % kRecKeys;
             *reinterpret_cast<float4*>(&skn[buf][slot][at]) = make_float4(k4[0] * kscale, k4[1] * kscale, k4[2] * kscale, k4[3] * kscale);
             *reinterpret_cast<float4*>(&sqn[buf][slot][at]) =
                 make_float4((q4[0] * qscale) / sqrtf((float)dk), (q4[1] * qscale) / sqrtf((float)dk),
@@ -276,30 +283,30 @@ seq_recurrence128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ 
         const int count = min(kRecBatch, tokens - n * kRecBatch);
 #pragma unroll 1
         for (int i = 0; i < count; ++i) {
-            const float4* kp = reinterpret_cast<const float4*>(&skn[buf][i][quarter * kRecQuarter]);
-            const float4* qp = reinterpret_cast<const float4*>(&sqn[buf][i][quarter * kRecQuarter]);
+            const float4* kp = reinterpret_cast<const float4*>(&skn[buf][i][quarter * kRecPitch]);
+            const float4* qp = reinterpret_cast<const float4*>(&sqn[buf][i][quarter * kRecPitch]);
             const float decay = sgate[buf][i][0], beta = sgate[buf][i][1], v = sv[buf][i][col];
             float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < kRecKeys / 4; ++j) {
                 const float4 k4 = kp[j];
                 s[4 * j] *= decay; s[4 * j + 1] *= decay; s[4 * j + 2] *= decay; s[4 * j + 3] *= decay;
                 p0 += s[4 * j] * k4.x; p1 += s[4 * j + 1] * k4.y; p2 += s[4 * j + 2] * k4.z; p3 += s[4 * j + 3] * k4.w;
             }
             float pred = (p0 + p1) + (p2 + p3);
-            pred += __shfl_xor_sync(0xffffffffu, pred, 1);
-            pred += __shfl_xor_sync(0xffffffffu, pred, 2);
+#pragma unroll
+            for (int d = 1; d < kRecParts; d <<= 1) pred += __shfl_xor_sync(0xffffffffu, pred, d);
             const float corr = beta * (v - pred);
             float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < kRecKeys / 4; ++j) {
                 const float4 k4 = kp[j], q4 = qp[j];
                 s[4 * j] += k4.x * corr; s[4 * j + 1] += k4.y * corr; s[4 * j + 2] += k4.z * corr; s[4 * j + 3] += k4.w * corr;
                 o0 += s[4 * j] * q4.x; o1 += s[4 * j + 1] * q4.y; o2 += s[4 * j + 2] * q4.z; o3 += s[4 * j + 3] * q4.w;
             }
             float o = (o0 + o1) + (o2 + o3);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+            for (int d = 1; d < kRecParts; d <<= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
             if (quarter == 0 && col_ok)
                 out[(size_t)(n * kRecBatch + i) * hv * dv + (size_t)head * dv + c0 + col] = __float2bfloat16_rn(o);
         }
@@ -307,7 +314,7 @@ seq_recurrence128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ 
         __syncthreads();
     }
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
+    for (int j = 0; j < kRecKeys; ++j)
         if (col_ok) tile[(size_t)j * dv] = s[j];
 }
 
@@ -857,7 +864,7 @@ extern "C" int qd_seq_gdn_recurrence(const void* conv_qkv, const void* a, const 
     QD_CHECK_ARG(key_heads > 0 && value_heads % key_heads == 0 && key_dim > 0 && value_dim > 0);
     if (key_dim > 128) return QD_ERR_UNSUPPORTED;
     if (key_dim == 128) {
-        seq_recurrence128_kernel<<<dim3(value_heads, (value_dim + 31) / 32), 128, 0, (cudaStream_t)stream>>>(
+        seq_recurrence128_kernel<<<dim3(value_heads, (value_dim + kRecCols - 1) / kRecCols), 128, 0, (cudaStream_t)stream>>>(
             (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
             (bf16*)out, tokens, key_heads, value_heads, value_dim, 0);
         return qd_launch_status();
@@ -886,7 +893,7 @@ extern "C" int qd_batch_gdn_recurrence(const void* conv_qkv, const void* a, cons
     QD_CHECK_ARG(key_heads > 0 && value_heads % key_heads == 0 && key_dim > 0 && value_dim > 0);
     QD_CHECK_ARG(batch == 1 || state_stride >= (long long)value_heads * key_dim * value_dim);
     if (key_dim != 128) return QD_ERR_UNSUPPORTED;
-    seq_recurrence128_kernel<<<dim3(value_heads, (value_dim + 31) / 32, batch), 128, 0, (cudaStream_t)stream>>>(
+    seq_recurrence128_kernel<<<dim3(value_heads, (value_dim + kRecCols - 1) / kRecCols, batch), 128, 0, (cudaStream_t)stream>>>(
         (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
         (bf16*)out, 1, key_heads, value_heads, value_dim, state_stride);
     return qd_launch_status();
