@@ -96,6 +96,19 @@ int qd_seq_attention(const void* qg, const void* k_new, const void* v_new, const
                      int rotary_dim, float theta, float eps, void* stream);
 int qd_seq_route_topk(const void* logits, int tokens, int experts, int topk, int32_t* ids, float* weights,
                       void* stream);
+/* ---- Expert-parallel exchange through peer memory (no counterpart in the reference, which is
+ * a single-GPU library): the sum over the ranks of one fp32 vector of n elements, left in
+ * `vector` on every rank with identical bits (slots are added in rank order).  peer_buffers:
+ * host array of `world` device addresses, entry r = rank r's symmetric buffer as mapped on this
+ * GPU (qd_peer_all_reduce_bytes() bytes each, zero-filled before the first call, 128-byte
+ * aligned); epoch: one zero-initialised device word per rank, advanced by every call, so a
+ * captured launch can be replayed; every rank must make the same sequence of calls.  The wait
+ * for the other ranks is bounded (2 s); a time-out sets QD status bit 1 in *status.
+ * world <= 8, n a multiple of 4. */
+long long qd_peer_all_reduce_bytes(int world, int n);
+int qd_peer_all_reduce(float* vector, const unsigned long long* peer_buffers, int rank, int world, int n,
+                       unsigned int* epoch, unsigned int* status, void* stream);
+
 /* ---- Small-batch decode with per-sequence state: one token of each of `batch` independent
  * sequences per call.  The reference decodes one sequence (quickdraw/engine/engine.py:114-127);
  * these are its single-token operators (_conv_kernel / _delta_kernel of

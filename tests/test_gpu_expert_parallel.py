@@ -39,7 +39,7 @@ engine.state.kv_v.zero_()
 tokens = engine.generate(prompt, steps)
 print("rank", rank, "generated", flush=True)
 with open(os.path.join(outdir, f"rank{rank}.json"), "w") as f:
-    json.dump({"tokens": tokens, "status": engine.fused.status()}, f)
+    json.dump({"tokens": tokens, "status": engine.fused.status(), "peer": engine.fused.peer is not None}, f)
 # Every collective of this rank has completed (the tokens were read back).  Leave without the
 # communicator teardown: with a captured graph that holds collectives still alive it can wait
 # for the peer indefinitely, and the result is already on disk.
@@ -55,7 +55,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def test_two_rank_generation_matches_single_gpu():
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+def test_two_rank_generation_matches_single_gpu(exchange):
+    """`exchange`: the per-layer sum over ranks by NCCL or by the library's peer-memory kernel."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     from quickdraw_b200 import synthetic
@@ -69,7 +71,7 @@ def test_two_rank_generation_matches_single_gpu():
     want = single.generate(prompt, steps)
     del single
     torch.cuda.empty_cache()
-    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0", QD_EP_EXCHANGE=exchange)
     with tempfile.TemporaryDirectory() as outdir:
         port = str(_free_port())
         logs = [open(os.path.join(outdir, f"rank{r}.log"), "w") for r in range(2)]
@@ -94,6 +96,7 @@ def test_two_rank_generation_matches_single_gpu():
         out = [json.load(open(os.path.join(outdir, f"rank{r}.json"))) for r in range(2)]
     assert out[0]["tokens"] == out[1]["tokens"], "ranks disagree"
     assert out[0]["status"] == 0 and out[1]["status"] == 0
+    assert out[0]["peer"] == out[1]["peer"] == (exchange == "peer"), "the requested exchange did not run"
     # the routed sum is added in a different order across ranks: identical tokens are
     # expected, a divergence at a near-tie is reported rather than hidden
     same = sum(a == b for a, b in zip(out[0]["tokens"], want))
