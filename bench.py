@@ -359,6 +359,8 @@ def run_gpu(args):
     if world > 1:
         torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
     device_ms, e2e_ms = times.tolist()
+    step_status = engine.fused.status() if getattr(engine, "fused", None) is not None else 0
+    assert step_status == 0, f"the decode step reported status {step_status} (a bounded wait ran out)"
     if rank != 0:
         return
     peak, peak_kind = measured_peaks()

@@ -5,11 +5,12 @@ shared expert, mixers, norms, embedding, LM head and the whole decode state are 
 so every rank runs the identical step on identical inputs and arrives at the same routing.
 A rank multiplies only the selected experts it owns; the fp32 partial sums [hidden] meet in
 one exchange per layer, after which every rank rounds the sum to bf16 and adds the gated
-shared row exactly as the single-GPU kernel does.  The exchange is one NCCL all-reduce, or,
-with ``QD_EP_EXCHANGE=peer``, the library's own kernel over peer memory (every rank stores its
-vector into every rank's symmetric buffer over NVLink, flags, bounded wait, sum in rank order:
-``qd_peer_all_reduce``).  Measured on two GPUs: 3.96 ms per token with the peer kernel, 4.00 ms
-with NCCL - the step is bound by its launches, not by the exchange - so NCCL stays the default.  The reference has no distributed
+shared row exactly as the single-GPU kernel does.  The exchange is the library's own kernel
+over peer memory (every rank stores its vector into every rank's symmetric buffer over NVLink,
+flags, bounded wait, sum in rank order: ``qd_peer_all_reduce``) when the symmetric allocation
+can be set up on every rank, else one NCCL all-reduce (``QD_EP_EXCHANGE=nccl`` forces that).
+Measured per token: 3.96 ms (peer) against 4.00 ms (NCCL) on two GPUs, 3.94 ms against 4.36 ms
+on four.  The reference has no distributed
 path (it is a single-GPU library); this module is the multi-GPU extension of its engine.
 """
 
@@ -52,7 +53,7 @@ class ExpertParallelStep:
         """Symmetric buffer + peer pointers for ``qd_peer_all_reduce``, or None (NCCL instead).
         Every rank must come to the same answer: the outcome is agreed on with an all-reduce."""
         ok, state = 1, None
-        if os.environ.get("QD_EP_EXCHANGE", "nccl") != "peer" or dist.get_backend(group) != "nccl":
+        if os.environ.get("QD_EP_EXCHANGE", "peer") == "nccl" or dist.get_backend(group) != "nccl":
             ok = 0
         else:
             try:
