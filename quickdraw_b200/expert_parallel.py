@@ -8,7 +8,9 @@ one exchange per layer, after which every rank rounds the sum to bf16 and adds t
 shared row exactly as the single-GPU kernel does.  The exchange is the library's own kernel
 over peer memory (every rank stores its vector into every rank's symmetric buffer over NVLink,
 flags, bounded wait, sum in rank order: ``qd_peer_all_reduce``) when the symmetric allocation
-can be set up on every rank, else one NCCL all-reduce (``QD_EP_EXCHANGE=nccl`` forces that).
+can be set up on every rank and the group has at most four ranks (the sizes it was run on;
+``QD_EP_EXCHANGE=peer`` asks for it on larger groups), else one NCCL all-reduce
+(``QD_EP_EXCHANGE=nccl`` forces that).
 Measured per token: 3.96 ms (peer) against 4.00 ms (NCCL) on two GPUs, 3.94 ms against 4.36 ms
 on four.  The reference has no distributed
 path (it is a single-GPU library); this module is the multi-GPU extension of its engine.
@@ -53,7 +55,9 @@ class ExpertParallelStep:
         """Symmetric buffer + peer pointers for ``qd_peer_all_reduce``, or None (NCCL instead).
         Every rank must come to the same answer: the outcome is agreed on with an all-reduce."""
         ok, state = 1, None
-        if os.environ.get("QD_EP_EXCHANGE", "peer") == "nccl" or dist.get_backend(group) != "nccl":
+        # the peer kernel was run on 2 and 4 GPUs; larger groups take NCCL unless asked otherwise
+        choice = os.environ.get("QD_EP_EXCHANGE", "peer" if self.world <= 4 else "nccl")
+        if choice != "peer" or dist.get_backend(group) != "nccl":
             ok = 0
         else:
             try:
