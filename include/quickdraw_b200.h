@@ -96,19 +96,6 @@ int qd_seq_attention(const void* qg, const void* k_new, const void* v_new, const
                      int rotary_dim, float theta, float eps, void* stream);
 int qd_seq_route_topk(const void* logits, int tokens, int experts, int topk, int32_t* ids, float* weights,
                       void* stream);
-/* ---- Expert-parallel exchange through peer memory (no counterpart in the reference, which is
- * a single-GPU library): the sum over the ranks of one fp32 vector of n elements, left in
- * `vector` on every rank with identical bits (slots are added in rank order).  peer_buffers:
- * host array of `world` device addresses, entry r = rank r's symmetric buffer as mapped on this
- * GPU (qd_peer_all_reduce_bytes() bytes each, zero-filled before the first call, 128-byte
- * aligned); epoch: one zero-initialised device word per rank, advanced by every call, so a
- * captured launch can be replayed; every rank must make the same sequence of calls.  The wait
- * for the other ranks is bounded (2 s); a time-out sets QD status bit 1 in *status.
- * world <= 8, n a multiple of 4. */
-long long qd_peer_all_reduce_bytes(int world, int n);
-int qd_peer_all_reduce(float* vector, const unsigned long long* peer_buffers, int rank, int world, int n,
-                       unsigned int* epoch, unsigned int* status, void* stream);
-
 /* ---- Small-batch decode with per-sequence state: one token of each of `batch` independent
  * sequences per call.  The reference decodes one sequence (quickdraw/engine/engine.py:114-127);
  * these are its single-token operators (_conv_kernel / _delta_kernel of
@@ -294,9 +281,10 @@ typedef struct {
     int experts, topk, intermediate;
     float eps, rope_theta;
     int expert_lo, expert_hi;                            /* owned expert range (expert parallel) */
+    int vocab_lo, vocab_hi;                              /* owned LM-head rows; vocab_hi == 0: all of them */
     const void* embed;                                   /* bf16 [vocab, hidden] */
     const float* final_gamma;                            /* fp32 [hidden] */
-    const void* lm_head;                                 /* bf16 [vocab, hidden] */
+    const void* lm_head;                                 /* bf16 rows [vocab_lo, vocab_hi) of [vocab, hidden] */
 } qd_model_config;
 
 typedef struct {
@@ -323,35 +311,41 @@ enum { QD_FLAG_PDL = 1, QD_FLAG_NO_LOGITS = 2 };
 int qd_decode_step(qd_model* model, const qd_state* state, const long long* token,
                    const int* position_dev, int position_host, void* workspace, void* logits_out,
                    long long* next_token, int flags, void* stream);
-/* Expert-parallel variant: runs layers [layer_begin, layer_end) and stops after the MoE tail
- * of the last one with the fp32 routed partial sum in `routed_partial` (hidden floats);
- * the caller all-reduces it and continues with the next call.  layer_end == layers also
- * needs the final call with layer_begin == layers for the LM head. */
-int qd_decode_layers(qd_model* model, const qd_state* state, const long long* token,
-                     const int* position_dev, int position_host, void* workspace,
-                     float* routed_partial, int layer_begin, int layer_end, void* logits_out,
-                     long long* next_token, int flags, void* stream);
-
-/* The same step as ONE cooperative launch (a persistent kernel with grid-wide barriers
- * between the phases of qwen.py:196-241 and a weight ring that runs ahead across them).
+/* The same step as ONE cooperative launch: a persistent kernel, one block per SM, that walks
+ * the phases of qwen.py:196-241 without any grid-wide barrier (blocks hand activations to each
+ * other as tagged words in `workspace` and start a phase as soon as their own inputs exist)
+ * and a weight ring that runs ahead across the phases.
  * The phase list ("program") holds device addresses of the model and of `workspace`, so it
  * is built once per (model, workspace) pair: qd_program_build fills a HOST buffer of
  * qd_program_bytes bytes, the caller copies it to the device and passes that copy here.
- * Needs a whole idle GPU (one block per SM, all resident) and a single-GPU model
- * (expert_lo == 0, expert_hi == experts).  `trace` (optional, device) receives
- * [phase][16][blocks] nanosecond timestamps. */
+ * Needs a whole idle GPU (all blocks resident).  `trace` (optional, device) receives
+ * [phase][16][blocks] nanosecond timestamps.
+ *
+ * Expert parallel (no counterpart in the reference, which is single-GPU): every rank runs
+ * this launch on the same token with its own model slice (expert_lo/hi, vocab_lo/hi in the
+ * config; banks and LM head local to the slice).  `exchange` names, per rank, the address in
+ * THIS process of that rank's exchange area (qd_exchange_bytes bytes, zero-initialised before
+ * the first step, peer-mapped, e.g. a symmetric-memory allocation).  A rank stores the routed
+ * contributions of the experts it owns into every rank's area and reads all of them from its
+ * own, so each rank adds the same eight bf16 rows in the same order as a single GPU would;
+ * the ranks' best (logit, index) pairs meet the same way and every rank ends with the same
+ * next token.  Logits: each rank writes rows [vocab_lo, vocab_hi) of `logits_out`.
+ * exchange == NULL: single GPU.  Plain peer loads and stores only. */
+typedef struct {
+    int rank, world;                       /* world <= 8 */
+    unsigned long long peer_base[8];
+} qd_exchange;
+long long qd_exchange_bytes(const qd_model* model);
 long long qd_program_bytes(const qd_model* model);
 int qd_program_build(const qd_model* model, void* workspace, void* host_out, long long bytes);
 int qd_decode_step_persistent(const qd_model* model, const qd_state* state, const long long* token,
                               const int* position_dev, int position_host, void* workspace,
-                              const void* program, void* logits_out, long long* next_token, int flags,
-                              unsigned long long* trace, void* stream);
-
-/* Profiling aid: per-block timestamps of the next `launches` streaming launches (see stream.cu). */
-int qd_stream_trace(unsigned long long* buffer, int launches);
-
-/* Tuning: blocks per SM (1 or 2) of the streaming matvec kernel when 2048 inputs wide. */
-int qd_stream_blocks_per_sm(int n);
+                              const void* program, const qd_exchange* exchange, void* logits_out,
+                              long long* next_token, int flags, unsigned long long* trace, void* stream);
+/* Bound of every device-side wait of the persistent kernel (default 200 000 us).  A wait that
+ * runs out sets bit 0 of the status word (workspace + 256) and the kernel finishes the token
+ * without waiting any further; the context stays usable. */
+int qd_set_wait_limit_us(unsigned int microseconds);
 
 /* Measurement helper: the streaming NVFP4 matvec over a bank of `matrices` equally shaped
  * [rows, in_features] matrices, one launch per matrix, so the working set can exceed L2. */

@@ -42,12 +42,11 @@ SIGNATURES = {
     "qd_model_set_layer": [P, I, P],
     "qd_decode_workspace_bytes": [P],
     "qd_decode_step": [P, P, P, P, I, P, P, P, I, P],
-    "qd_decode_layers": [P, P, P, P, I, P, P, I, I, P, P, I, P],
     "qd_program_bytes": [P],
     "qd_program_build": [P, P, P, L],
-    "qd_decode_step_persistent": [P, P, P, P, I, P, P, P, P, I, P, P],
-    "qd_stream_blocks_per_sm": [I],
-    "qd_stream_trace": [P, I],
+    "qd_decode_step_persistent": [P, P, P, P, I, P, P, P, P, P, I, P, P],
+    "qd_exchange_bytes": [P],
+    "qd_set_wait_limit_us": [ctypes.c_uint],
     "qd_nvfp4_gemv_bank": [P, P, P, P, P, I, I, I, I, P],
     "qd_nvfp4_matmul": [P, P, P, P, P, I, I, I, I, P, P],
     "qd_nvfp4_grouped_matmul": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
@@ -57,8 +56,6 @@ SIGNATURES = {
     "qd_seq_gdn_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, P],
     "qd_seq_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, P],
     "qd_seq_route_topk": [P, I, I, I, P, P, P],
-    "qd_peer_all_reduce_bytes": [I, I],
-    "qd_peer_all_reduce": [P, P, I, I, I, P, P, P],
     "qd_batch_gdn_conv": [P, P, P, L, P, I, I, I, P],
     "qd_batch_gdn_recurrence": [P, P, P, P, P, P, L, P, I, I, I, I, I, P],
     "qd_batch_attn_decode": [P, P, P, P, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
@@ -67,7 +64,7 @@ SIGNATURES = {
     "qd_seq_moe_combine": [P, P, P, P, P, I, I, I, P],
 }
 
-LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes", "qd_peer_all_reduce_bytes"}
+LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes", "qd_exchange_bytes"}
 
 _lib = None
 

@@ -31,6 +31,7 @@ struct AttnParams {
     float* partial;        // [Hk, splits, G, D + 2] scratch
     unsigned int* counters;// [Hk], zero before the first launch; reset by the kernel
     const int* position_dev;
+    unsigned int* status;  // optional status word (QD_STATUS_* bits)
     int position_host;
     int capacity;
     int hq, hk, d, rotary;
@@ -94,6 +95,14 @@ attn_decode_kernel(const AttnParams p) {
     grid_launch_dependents();
     grid_dependency_wait();
     const int position = seq_position ? *seq_position : p.position_host;
+    // A position outside the cache (possible only when it comes from the device scalar; host
+    // values are checked before the launch) touches nothing: every block of the sequence
+    // leaves, the output keeps its old contents and, where the caller gave one, the status
+    // word says so.
+    if (position < 0 || position >= p.capacity) {
+        if (p.status && tid == 0) atomicOr(p.status, QD_STATUS_BAD_ARG);
+        return;
+    }
     const int T = position + 1;
     int active = (T + kAttnSplitMin - 1) / kAttnSplitMin;
     if (active > p.splits) active = p.splits;
@@ -249,7 +258,7 @@ extern "C" int qd_attn_decode(const void* qg, const void* k_new, const void* v_n
     QD_CHECK_ARG(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0);
     const int G = q_heads / kv_heads;
     if (G > kAttnMaxGroup || head_dim > kAttnMaxDim || head_dim % 8 != 0) return QD_ERR_UNSUPPORTED;
-    AttnParams p;
+    AttnParams p = {};
     p.qg = (const bf16*)qg; p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new;
     p.q_norm = (const bf16*)q_norm; p.k_norm = (const bf16*)k_norm;
     p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache; p.out = (bf16*)out;
@@ -257,13 +266,15 @@ extern "C" int qd_attn_decode(const void* qg, const void* k_new, const void* v_n
     p.capacity = capacity; p.hq = q_heads; p.hk = kv_heads; p.d = head_dim; p.rotary = rotary_dim;
     p.theta = theta; p.eps = eps; p.splits = splits; p.cache_stride = 0;
     const size_t smem = sizeof(float) * ((size_t)G * head_dim + head_dim + (size_t)kAttnWarps * G * (head_dim + 2));
-    static bool configured = false;
-    if (!configured) {
+    if (smem > 100 * 1024) return QD_ERR_UNSUPPORTED;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
+    static bool configured[64];
+    if (!configured[dev]) {
         if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
             return QD_ERR_LAUNCH;
-        configured = true;
+        configured[dev] = true;
     }
-    if (smem > 100 * 1024) return QD_ERR_UNSUPPORTED;
     return qd_launch(attn_decode_kernel, dim3(kv_heads, splits), dim3(kAttnThreads), smem, (cudaStream_t)stream,
                      pdl != 0, p);
 }
@@ -285,7 +296,7 @@ extern "C" int qd_batch_attn_decode(const void* qg, const void* k_new, const voi
     QD_CHECK_ARG(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0);
     const int G = q_heads / kv_heads;
     if (G > kAttnMaxGroup || head_dim > kAttnMaxDim || head_dim % 8 != 0) return QD_ERR_UNSUPPORTED;
-    AttnParams p;
+    AttnParams p = {};
     p.qg = (const bf16*)qg; p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new;
     p.q_norm = (const bf16*)q_norm; p.k_norm = (const bf16*)k_norm;
     p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache; p.out = (bf16*)out;
@@ -341,13 +352,13 @@ extern "C" int qd_attn_decode_static(const void* qg, const void* k_new, const vo
     unsigned int* counters = (unsigned int*)(base + kAttnStaticBytes - kAttnStaticCounterBytes);
     // The array keeps whatever the last call left; the counters must start at zero.
     if (cudaMemsetAsync(counters, 0, kAttnStaticCounterBytes, (cudaStream_t)stream) != cudaSuccess) return QD_ERR_LAUNCH;
-    AttnParams p;
+    AttnParams p = {};
     p.qg = (const bf16*)qg; p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new;
     p.q_norm = (const bf16*)q_norm; p.k_norm = (const bf16*)k_norm;
     p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache; p.out = (bf16*)out;
     p.partial = (float*)base; p.counters = counters; p.position_dev = position_dev; p.position_host = position_host;
     p.capacity = capacity; p.hq = q_heads; p.hk = kv_heads; p.d = head_dim; p.rotary = rotary_dim;
-    p.theta = theta; p.eps = eps; p.splits = splits;
+    p.theta = theta; p.eps = eps; p.splits = splits; p.cache_stride = 0;
     const size_t smem = sizeof(float) * ((size_t)G * head_dim + head_dim + (size_t)kAttnWarps * G * (head_dim + 2));
     if (smem > 100 * 1024) return QD_ERR_UNSUPPORTED;
     static bool configured[64];

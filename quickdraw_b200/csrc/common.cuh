@@ -21,6 +21,7 @@ typedef __nv_bfloat16 bf16;
 // Status word bits written by kernels (never trapped on; the host reads them).
 #define QD_STATUS_WAIT_TIMEOUT 1u   // a bounded mbarrier/flag wait ran out
 #define QD_STATUS_BAD_SHAPE 2u      // a kernel was asked for a shape it does not cover
+#define QD_STATUS_BAD_ARG 4u        // a device-side argument (a position) was out of range; nothing was touched
 
 // --------------------------------------------------------------------- conversions
 QD_DEVINL float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }

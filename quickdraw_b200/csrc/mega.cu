@@ -1,95 +1,200 @@
-// Persistent decode kernel: one cooperative launch per token.
+// Persistent decode kernel: one cooperative launch per token, no grid-wide barrier.
 //
 // The grid is one block per SM.  A block has sixteen consumer warps and one producer warp.
 // The producer walks the program phase by phase and streams this block's share of every
-// phase's weights into a ring of shared-memory stages (1-D bulk copies, full/empty
-// mbarriers); it never waits for other blocks except where the weights to fetch depend on
-// the routing, so at a grid barrier the ring already holds the start of the next phase.
-// The consumers run the phases in order:
-//     static prefetch (what no other block writes)  ->  grid barrier  ->  build the
-//     activation vector  ->  rows of the ring  ->  arrive at the next barrier.
-// Activations written by one block and read by another travel through L2: every such read
-// is a cache-global load, every phase ends with a fence and a release on the barrier word.
+// phase's weights (and, for attention, its slice of the KV cache) into a ring of
+// shared-memory stages (bulk copies, full/empty mbarriers); it never waits for other blocks
+// except where the weights to fetch depend on the routing, so when the consumers reach a
+// phase the ring already holds its first tiles.
 //
-// The arithmetic of every phase is that of the separate kernels (stream.cu, gdn.cu,
-// moe.cu): same rounding points, same summation order; attention uses its own split of the
-// context (reference: quickdraw/models/qwen.py:66-241).
+// Blocks hand activations to each other through L2 as tagged words (mega.cuh): a consumer
+// re-reads the words it needs until they carry the tag of this launch and layer, so a phase
+// starts in a block as soon as ITS inputs exist.  The residual stream never leaves the
+// block: every block adds and normalises the whole hidden vector itself (it needs the whole
+// vector for its rows anyway) and keeps the bf16 residual in registers.
 //
-// Every wait is bounded.  A wait that runs out sets the status word and an abort bit in
-// the barrier word, which lets every other block fall through its barriers and leave.
+// NVFP4 rows run on the warp-level tensor-core instruction with the inputs split over the
+// sixteen warps (rowmma.cuh); attention is a split-context flash decode on the same
+// instruction (all query heads of a KV head share each key/value tile).
+//
+// Arithmetic follows the separate kernels (stream.cu, gdn.cu, moe.cu, attention.cu): same
+// rounding points (reference: quickdraw/models/qwen.py:66-241), fp32 sums in a different order.
+//
+// Every wait is bounded.  A wait that runs out sets the status word and the block's abort
+// flag; the block then stops waiting, finishes the token with whatever it has (its outputs
+// still carry their tags, so no other block waits for it) and leaves.
 #include "mega.cuh"
 #include "rowdot.cuh"
+#include "rowmma.cuh"
 
 namespace qd {
 namespace {
 
 constexpr int CW = kMegaConsumerWarps, CT = kMegaConsumers, NS = kMegaStages;
-constexpr unsigned kAbortBit = 0x80000000u;
 constexpr int kDownWidth = 512;
 constexpr int kDownRowBytes = kDownWidth / 2 + kDownWidth / 16;   // 288
-constexpr int kAttnStride = 256 + 2;
-constexpr int kAttnScratchFloats = 8 * 4 * kAttnStride + 3 * 8 * kMegaAttnSplits + 64;   // attention merge buffers
-constexpr int kDownSlots = 9;                                   // top-8 + shared
-constexpr int kDownBufBytes = kDownSlots * kMegaDownRows * kDownRowBytes;   // down-projection rows of one layer
-constexpr int kScratchFloats = kAttnScratchFloats > kDownBufBytes / 4 ? kAttnScratchFloats : kDownBufBytes / 4;
+constexpr int kDownSlots = 9;                                     // top-8 + shared
+constexpr int kDownSlotBytes = kMegaDownRows * kDownRowBytes;     // codes [16][256] then scales [16][32]
+constexpr int kDownBufBytes = kDownSlots * kDownSlotBytes;        // down-projection rows of one layer
+constexpr int kAttnRow = 528;                  // a 512-byte cache row of one KV head, padded against bank conflicts
+constexpr int kAttnStagePos = 32;              // positions per ring stage: K rows, then V rows
+constexpr int kAttnQRow = 576;                 // a query head in shared memory (bf16 [256], padded)
+constexpr int kAttnWarps = 8;                  // warps that walk the context (a chunk of sixteen positions each)
+constexpr int kAttnStride = 258;               // partial of one head: 256 sums, running max, denominator
+constexpr int kAttnMergeFloats = 8 * 256 + 16; // one warp's partial in shared memory during the block merge
+constexpr int kScratchBytes = kDownBufBytes > 4 * kAttnMergeFloats * 4 ? kDownBufBytes : 4 * kAttnMergeFloats * 4;
 
 struct Smem {
     uint8_t* stages;
-    bf16* xs;              // [4096] activation vector, bf16           (attention: q rows, fp32)
-    uint32_t* xf;          // [2048] the same as f16 pairs             (attention: new key, trig table)
-    float* scratch;        // attention merge / DeltaNet vectors / down contributions
+    bf16* xs;              // [4096] activation vector, bf16   (attention: query heads, new key; down: hidden vectors)
+    uint8_t* xf;           // [4096] the same as f16, natural order
+    uint8_t* scratch;      // down-projection rows / DeltaNet vectors / attention merge
+    float* partials;       // [NS][16 warps][32] partial row sums of the tile in each stage
     bf16* conv_taps; bf16* conv_state;
     MegaPhase* cph;        // [2] consumer copies of the current and the next phase
     MegaPhase* pph;        // producer copy
-    uint64_t* full; uint64_t* empty;
-    float* red;            // [96]: 0.. sums, 16.. amax, 32.. / 48.. argmax, 64.. / 80.. global scales of the segments
+    uint64_t* full; uint64_t* empty; uint64_t* ready;
+    float* red;            // [160]: reductions, per-segment global scales, the f16 scale of the kept vector
     int32_t* ids; float* weights;      // [8] routing of the current layer
     uint64_t* ids_bar;                 // completes once per layer, when the routing is in ids / weights
     uint64_t* down_bar;                // completes once per layer, when the down-projection rows have landed
     volatile int* abort;
-    int* flag;
     float* rope;           // [2][128] bf16-rounded cos / sin of the step's position, per rotary frequency
 };
 
 extern __shared__ __align__(128) uint8_t mega_smem[];
 
+constexpr size_t kSmemBytes = (size_t)NS * kStreamStageBytes + 4096 * 2 + 4096 * 2 + (size_t)kScratchBytes +
+                              (size_t)NS * kRowPartialFloats * 4 + 2 * kMegaConvRows * kStreamConvWidth * 2 +
+                              3 * sizeof(MegaPhase) + 3 * NS * 8 + 160 * 4 + 8 * 4 + 8 * 4 + 16 + 16 + 2 * 128 * 4;
+
 QD_DEVINL Smem carve_smem(uint8_t* base) {
     Smem s;
     s.stages = base;                                  base += (size_t)NS * kStreamStageBytes;
     s.xs = reinterpret_cast<bf16*>(base);             base += 4096 * 2;
-    s.xf = reinterpret_cast<uint32_t*>(base);         base += 2048 * 4;
-    s.scratch = reinterpret_cast<float*>(base);       base += (size_t)kScratchFloats * 4;
+    s.xf = base;                                      base += 4096 * 2;
+    s.scratch = base;                                 base += (size_t)kScratchBytes;
+    s.partials = reinterpret_cast<float*>(base);      base += (size_t)NS * kRowPartialFloats * 4;
     s.conv_taps = reinterpret_cast<bf16*>(base);      base += kMegaConvRows * kStreamConvWidth * 2;
     s.conv_state = reinterpret_cast<bf16*>(base);     base += kMegaConvRows * kStreamConvWidth * 2;
     s.cph = reinterpret_cast<MegaPhase*>(base);       base += 2 * sizeof(MegaPhase);
     s.pph = reinterpret_cast<MegaPhase*>(base);       base += sizeof(MegaPhase);
     s.full = reinterpret_cast<uint64_t*>(base);       base += NS * 8;
     s.empty = reinterpret_cast<uint64_t*>(base);      base += NS * 8;
-    s.red = reinterpret_cast<float*>(base);           base += 96 * 4;
+    s.ready = reinterpret_cast<uint64_t*>(base);      base += NS * 8;
+    s.red = reinterpret_cast<float*>(base);           base += 160 * 4;
     s.ids = reinterpret_cast<int32_t*>(base);         base += 8 * 4;
     s.weights = reinterpret_cast<float*>(base);       base += 8 * 4;
     s.ids_bar = reinterpret_cast<uint64_t*>(base);    base += 8;
     s.down_bar = reinterpret_cast<uint64_t*>(base);   base += 8;
-    s.abort = reinterpret_cast<volatile int*>(base);  base += 4;
-    s.flag = reinterpret_cast<int*>(base);            base += 4;
+    s.abort = reinterpret_cast<volatile int*>(base);  base += 16;
     s.rope = reinterpret_cast<float*>(base);          base += 2 * 128 * 4;
     return s;
 }
-constexpr size_t kSmemBytes = (size_t)NS * kStreamStageBytes + 4096 * 2 + 2048 * 4 + (size_t)kScratchFloats * 4 +
-                              2 * kMegaConvRows * kStreamConvWidth * 2 + 3 * sizeof(MegaPhase) + 2 * NS * 8 +
-                              96 * 4 + 8 * 4 + 8 * 4 + 24 + 2 * 128 * 4;
 
-QD_DEVINL float ldcg_bf16(const bf16* p) {
-    return __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(p)) << 16);
-}
-QD_DEVINL unsigned ld_acquire(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// ------------------------------------------------------------------ tagged words
+// Loads and stores of the words blocks exchange: relaxed, GPU scope (system scope for the words
+// other GPUs write or read), straight to and from L2.
+QD_DEVINL uint4 ld_words4(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-QD_DEVINL void red_release_add(unsigned* p, unsigned v) {
-    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+QD_DEVINL uint32_t ld_word(const void* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
+QD_DEVINL uint32_t ld_word_sys(const void* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+QD_DEVINL uint2 ld_pair(const void* p) {       // one 64-bit {value, tag} word
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return make_uint2((uint32_t)v, (uint32_t)(v >> 32));
+}
+QD_DEVINL uint2 ld_pair_sys(const void* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return make_uint2((uint32_t)v, (uint32_t)(v >> 32));
+}
+QD_DEVINL void st_word(void* p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+QD_DEVINL void st_word_sys(void* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+QD_DEVINL void st_pair_sys(void* p, uint32_t value, uint32_t tag) {
+    const unsigned long long v = (unsigned long long)value | ((unsigned long long)tag << 32);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// two {value, tag} words in one 16-byte store; each 64-bit half validates itself on the reader's side
+QD_DEVINL void st_pairs2(void* p, uint32_t v0, uint32_t v1, uint32_t tag) {
+    asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v0), "r"(tag), "r"(v1), "r"(tag) : "memory");
+}
+QD_DEVINL uint32_t make_word(bf16 v, uint32_t tag) { return (uint32_t)__bfloat16_as_ushort(v) | (tag << 16); }
+QD_DEVINL float word_value(uint32_t w) { return __uint_as_float(w << 16); }
+QD_DEVINL bool tags4(const uint4& v, uint32_t tag) {
+    return ((v.x >> 16) == tag) & ((v.y >> 16) == tag) & ((v.z >> 16) == tag) & ((v.w >> 16) == tag);
+}
+
+struct Wait {                 // what a bounded wait needs
+    unsigned int* status; volatile int* abort; unsigned long long limit_ns;
+};
+QD_DEVINL bool wait_expired(const Wait& w, unsigned long long start) {
+    if (*w.abort) return true;
+    if (global_timer_ns() - start <= w.limit_ns) return false;
+    atomicOr(w.status, QD_STATUS_WAIT_TIMEOUT);
+    *w.abort = 1;
+    return true;
+}
+static __device__ __noinline__ uint4 wait_words4_slow(const tagged* p, uint32_t tag, Wait w) {
+    const unsigned long long start = global_timer_ns();
+    uint4 v;
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) { v = ld_words4(p); if (tags4(v, tag)) return v; }
+        if (wait_expired(w, start)) return v;
+    }
+}
+// Four consecutive tagged words (16-byte aligned), re-read until all carry `tag`.
+QD_DEVINL uint4 wait_words4(const tagged* p, uint32_t tag, const Wait& w) {
+    const uint4 v = ld_words4(p);
+    if (tags4(v, tag)) return v;
+    return wait_words4_slow(p, tag, w);
+}
+static __device__ __noinline__ uint32_t wait_word_slow(const tagged* p, uint32_t tag, Wait w, bool sys) {
+    const unsigned long long start = global_timer_ns();
+    uint32_t v;
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) { v = sys ? ld_word_sys(p) : ld_word(p); if ((v >> 16) == tag) return v; }
+        if (wait_expired(w, start)) return v;
+    }
+}
+QD_DEVINL uint32_t wait_word(const tagged* p, uint32_t tag, const Wait& w, bool sys = false) {
+    const uint32_t v = sys ? ld_word_sys(p) : ld_word(p);
+    if ((v >> 16) == tag) return v;
+    return wait_word_slow(p, tag, w, sys);
+}
+static __device__ __noinline__ uint32_t wait_pair_slow(const uint2* p, uint32_t tag, Wait w, bool sys) {
+    const unsigned long long start = global_timer_ns();
+    uint2 v;
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) { v = sys ? ld_pair_sys(p) : ld_pair(p); if (v.y == tag) return v.x; }
+        if (wait_expired(w, start)) return v.x;
+    }
+}
+// One {fp32 bits, 32-bit tag} word; returns the value bits.
+QD_DEVINL uint32_t wait_pair(const uint2* p, uint32_t tag, const Wait& w, bool sys = false) {
+    const uint2 v = sys ? ld_pair_sys(p) : ld_pair(p);
+    if (v.y == tag) return v.x;
+    return wait_pair_slow(p, tag, w, sys);
+}
+
 QD_DEVINL void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
@@ -97,50 +202,12 @@ QD_DEVINL void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memo
 // Orders this thread's earlier shared-memory accesses before later bulk copies into the same bytes.
 QD_DEVINL void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// Bounded wait until the barrier word reaches `target` (the abort bit makes it larger than
-// any target).  On time-out: status bit, abort bit, false.
-// Returns the word it saw (abort bit included); on time-out: status bit, abort bit.
-__device__ __noinline__ unsigned grid_wait(unsigned* bar, unsigned target, unsigned* status) {
-    unsigned v;
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i)
-        if ((v = ld_acquire(bar)) >= target) return v;
-    const unsigned long long start = global_timer_ns();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i)
-            if ((v = ld_acquire(bar)) >= target) return v;
-        if (global_timer_ns() - start > QD_WAIT_LIMIT_NS) break;
-    }
-    atomicOr(status, QD_STATUS_WAIT_TIMEOUT);
-    atomicOr(bar, kAbortBit);
-    return kAbortBit;
-}
-// The consumers' side of the grid barrier in front of phase `pi`.
-QD_DEVINL void phase_wait(const MegaParams& mp, const Smem& S, int pi, int tid) {
-    // The acquire load orders thread 0's later reads after the other blocks' releases; the
-    // block barrier hands that order on to the rest of the block.
-    if (pi > 0 && tid == 0) {
-        if (grid_wait(mp.bar, (unsigned)pi * gridDim.x, mp.status) & kAbortBit) *S.abort = 1;
-    }
-    named_barrier(1, CT);
-}
-// Profiling: sixteen nanosecond timestamps per phase and block.  Slots: 0 phase start (after
-// the grid barrier), 1 phase end, 2 activation vector ready, 3 first tile landed, 4 / 5 first
-// and last tile of the phase issued by the producer; 8.. are free for finer marks (QD_MARK,
-// compiled in with -DQD_FINE_TRACE).
+// Profiling: sixteen nanosecond timestamps per phase and block.  Slots: 0 phase entered,
+// 1 phase left, 2 activation vector ready, 3 first tile landed, 4 / 5 first and last tile of
+// the phase issued by the producer.
 constexpr int kTraceSlots = 16;
 QD_DEVINL void trace_mark(const MegaParams& mp, int pi, int slot) {
     if (mp.trace) mp.trace[((size_t)pi * kTraceSlots + slot) * gridDim.x + blockIdx.x] = global_timer_ns();
-}
-#ifdef QD_FINE_TRACE
-#define QD_MARK(slot) do { if (tid == 0) trace_mark(mp, pi, slot); } while (0)
-#else
-#define QD_MARK(slot) do { } while (0)
-#endif
-QD_DEVINL void give_up(const MegaParams& mp, const Smem& S) {
-    *S.abort = 1;
-    atomicOr(mp.bar, kAbortBit);
 }
 
 // =========================================================================== producer
@@ -200,15 +267,15 @@ QD_DEVINL bool produce_stream(const MegaParams& mp, const MegaPhase& ph, const S
     return true;
 }
 
-// Down projections: this block's output rows of every selected expert and of the shared
-// expert, into their own buffer (the scratch area, idle between the mixer core and the MoE
-// tail).  Issued as soon as the routing is known, so the rows land during the gate/up phase.
+// Down projections: this block's output rows of every selected expert this rank owns and of
+// the shared expert, into their own buffer (the scratch area, idle between the mixer core and
+// the MoE tail).  Issued as soon as the routing is known, so the rows land during the gate/up phase.
 QD_DEVINL void produce_down(const MegaParams& mp, const MegaPhase& ph, const Smem& S) {
     const int H = mp.hidden;
     const int r0 = (int)((long long)H * blockIdx.x / gridDim.x);
     const int r1 = (int)((long long)H * (blockIdx.x + 1) / gridDim.x);
     const int n = r1 - r0, nslots = mp.topk + 1;
-    uint8_t* dst = reinterpret_cast<uint8_t*>(S.scratch);
+    uint8_t* dst = S.scratch;
     uint32_t bytes = 0;
     for (int s = 0; s < nslots; ++s) {
         const bool shared = s == mp.topk;
@@ -224,30 +291,28 @@ QD_DEVINL void produce_down(const MegaParams& mp, const MegaPhase& ph, const Sme
         const long long row = shared ? r0 : (long long)(e - mp.expert_lo) * H + r0;
         const uint8_t* w = (shared ? ph.sw : ph.dw) + row * (kDownWidth / 2);
         const uint8_t* sc = (shared ? ph.ss : ph.ds) + row * (kDownWidth / 16);
-        uint8_t* d = dst + (size_t)s * kMegaDownRows * kDownRowBytes;
+        uint8_t* d = dst + (size_t)s * kDownSlotBytes;
         bulk_load(d, w, n * (kDownWidth / 2), S.down_bar);
         bulk_load(d + kMegaDownRows * (kDownWidth / 2), sc, n * (kDownWidth / 16), S.down_bar);
     }
 }
 
 struct AttnSplit { int active, per; };
-// How the context [0, T) is cut into splits of `per` positions, one block per (KV head, split).
+// How the context [0, T) is cut into splits of `per` positions (a multiple of the stage), one
+// block per (KV head, split).
 QD_DEVINL AttnSplit attn_split(int T, int max_splits) {
     AttnSplit a;
-    const int s = min(max_splits, T);
-    a.per = (T + s - 1) / s;
+    const int per = (T + max_splits - 1) / max_splits;
+    a.per = max(kAttnStagePos, (per + kAttnStagePos - 1) / kAttnStagePos * kAttnStagePos);
     a.active = (T + a.per - 1) / a.per;
     return a;
 }
 
-constexpr int kAttnChunk = 16;                       // positions per pass = consumer warps
-constexpr int kAttnRowBytes = 256 * 2;               // one cache row of a KV head (head_dim 256, bf16)
-
-// Attention: the cache rows of this block's context split, sixteen positions per ring stage (K rows
-// then V rows, one 512-byte bulk copy each).  The row of the step's own position is not in
-// the cache yet; the consumers fill it in.  Rows of earlier positions were written by earlier
-// steps, so these copies may run ahead of the grid barrier like any weight.
-QD_DEVINL bool produce_attn(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it) {
+// Attention: the cache rows of this block's context split, thirty-two positions per ring stage
+// (K rows then V rows, one 512-byte bulk copy each, issued by the whole warp).  The row of the
+// step's own position is not in the cache yet; the consumers fill it in.  Rows of earlier
+// positions were written by earlier steps, so these copies may run ahead like any weight.
+QD_DEVINL bool produce_attn(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it, int lane) {
     const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
     const int T = position + 1;
     const AttnSplit cut = attn_split(T, mp.attn_splits);
@@ -258,19 +323,22 @@ QD_DEVINL bool produce_attn(const MegaParams& mp, const MegaPhase& ph, const Sme
     const uint8_t* k_cache = reinterpret_cast<const uint8_t*>(reinterpret_cast<const bf16*>(mp.st.kv_k) + (size_t)ph.state_index * layer_elems);
     const uint8_t* v_cache = reinterpret_cast<const uint8_t*>(reinterpret_cast<const bf16*>(mp.st.kv_v) + (size_t)ph.state_index * layer_elems);
 #pragma unroll 1
-    for (int c0 = t0; c0 < t1; c0 += kAttnChunk, ++it) {
+    for (int c0 = t0; c0 < t1; c0 += kAttnStagePos, ++it) {
         const int st = it % NS;
-        if (*S.abort || !mbar_wait(S.empty + st, ((it / NS) & 1) ^ 1, mp.status)) return false;
+        int ok = 1;
+        if (lane == 0) ok = (!*S.abort && mbar_wait(S.empty + st, ((it / NS) & 1) ^ 1, mp.status)) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return false;
         uint8_t* dst = S.stages + (size_t)st * kStreamStageBytes;
-        int rows = 0;
-        for (int tl = 0; tl < kAttnChunk; ++tl) rows += (c0 + tl < t1 && c0 + tl != position) ? 1 : 0;
-        mbar_expect_tx(S.full + st, (uint32_t)rows * 2 * kAttnRowBytes);
-        for (int tl = 0; tl < kAttnChunk; ++tl) {
-            const int t = c0 + tl;
-            if (t >= t1 || t == position) continue;
-            const size_t off = ((size_t)t * mp.hkv + kvh) * kAttnRowBytes;
-            bulk_load(dst + tl * kAttnRowBytes, k_cache + off, kAttnRowBytes, S.full + st);
-            bulk_load(dst + (kAttnChunk + tl) * kAttnRowBytes, v_cache + off, kAttnRowBytes, S.full + st);
+        const int t = c0 + lane;
+        const bool copy = t < t1 && t != position;
+        const int rows = __popc(__ballot_sync(0xffffffffu, copy));
+        if (lane == 0) mbar_expect_tx(S.full + st, (uint32_t)rows * 2 * 512);
+        __syncwarp();
+        if (copy) {
+            const size_t off = ((size_t)t * mp.hkv + kvh) * 512;
+            bulk_load(dst + lane * kAttnRow, k_cache + off, 512, S.full + st);
+            bulk_load(dst + (kAttnStagePos + lane) * kAttnRow, v_cache + off, 512, S.full + st);
         }
     }
     return true;
@@ -288,20 +356,23 @@ QD_DEVINL void producer(const MegaParams& mp, const Smem& S, int lane) {
         }
         __syncwarp();
         const MegaPhase& ph = *S.pph;
-        if (lane == 0 && ph.kind == MK_STREAM) {
-            trace_mark(mp, pi, 4);
-            if (ph.width == 2048) ok = produce_stream<2048>(mp, ph, S, it);
-            else ok = produce_stream<4096>(mp, ph, S, it);
-            // the routed gate/up phase also carries the down-projection pointers of its layer
-            if (ok && ph.route) {
-                ok = mbar_wait(S.ids_bar, ph.layer & 1, mp.status);
-                if (ok) produce_down(mp, ph, S);
+        if (ph.kind == MK_STREAM) {
+            if (lane == 0) {
+                trace_mark(mp, pi, 4);
+                if (ph.width == 2048) ok = produce_stream<2048>(mp, ph, S, it);
+                else ok = produce_stream<4096>(mp, ph, S, it);
+                // the routed gate/up phase also carries the down-projection pointers of its layer
+                if (ok && ph.route) {
+                    ok = mbar_wait(S.ids_bar, ph.layer & 1, mp.status);
+                    if (ok) produce_down(mp, ph, S);
+                }
+                trace_mark(mp, pi, 5);
+                if (!ok) *S.abort = 1;
             }
-            trace_mark(mp, pi, 5);
-            if (!ok) give_up(mp, S);
-        } else if (lane == 0 && ph.kind == MK_ATTN) {
-            ok = produce_attn(mp, ph, S, it);
-            if (!ok) give_up(mp, S);
+            it = __shfl_sync(0xffffffffu, it, 0);
+        } else if (ph.kind == MK_ATTN) {
+            ok = produce_attn(mp, ph, S, it, lane);
+            if (!ok && lane == 0) *S.abort = 1;
         }
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         __syncwarp();
@@ -316,27 +387,24 @@ QD_DEVINL void producer(const MegaParams& mp, const Smem& S, int lane) {
     }
 }
 
-// Top-k routing by one warp over at most 256 bf16 logits written by other blocks: the same
-// fp32 softmax, tie-break (lowest index) and renormalisation as route_small, with the
-// eight selections done by integer warp reductions (probabilities are non-negative, so their
+// Top-k routing by one warp; the lane holds the logits of experts 8 lane .. 8 lane + 7: fp32
+// softmax, lowest index wins ties, weights renormalised (quickdraw/models/qwen.py:174-177).
+// The eight selections are integer warp reductions (probabilities are non-negative, so their
 // bit patterns order like the values).
-QD_DEVINL void route_fast(const bf16* logits, int experts, int topk, int32_t* ids, float* weights, int lane) {
-    float p[8];
+QD_DEVINL void route_regs(float (&p)[8], int experts, int topk, int32_t* ids, float* weights, int lane) {
     float best = -INFINITY;
-    const unsigned short* raw = reinterpret_cast<const unsigned short*>(logits);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int e = i * 32 + lane;
-        p[i] = e < experts ? __uint_as_float((uint32_t)__ldcg(raw + e) << 16) : -INFINITY;
+        if (lane * 8 + i >= experts) p[i] = -INFINITY;
         best = fmaxf(best, p[i]);
     }
     best = warp_max(best);
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int e = i * 32 + lane;
-        p[i] = e < experts ? expf(p[i] - best) : -1.f;
-        if (e < experts) sum += p[i];
+        const bool on = lane * 8 + i < experts;
+        p[i] = on ? expf(p[i] - best) : -1.f;
+        if (on) sum += p[i];
     }
     sum = warp_sum(sum);
 #pragma unroll
@@ -349,50 +417,56 @@ QD_DEVINL void route_fast(const bf16* logits, int experts, int topk, int32_t* id
 #pragma unroll
         for (int i = 0; i < 8; ++i) if (p[i] > v) { v = p[i]; slot = i; }
         const int top = __reduce_max_sync(0xffffffffu, __float_as_int(v));
-        const int idx = __reduce_min_sync(0xffffffffu, __float_as_int(v) == top ? slot * 32 + lane : 0x7fffffff);
+        const int idx = __reduce_min_sync(0xffffffffu, __float_as_int(v) == top ? lane * 8 + slot : 0x7fffffff);
         const float value = __int_as_float(top);
         chosen += value;
         if (lane == s) { mine = value; my_id = idx; }
-        if ((idx & 31) == lane) {
+        if ((idx >> 3) == lane) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) if (i == (idx >> 5)) p[i] = -1.f;
+            for (int i = 0; i < 8; ++i) if (i == (idx & 7)) p[i] = -1.f;
         }
     }
     if (lane < topk) { ids[lane] = my_id; weights[lane] = mine / chosen; }
 }
 
+// Power-of-two down-scale that keeps a vector whose largest magnitude is `top` inside f16.
+QD_DEVINL void f16_scale(float top, float& down, float& up) {
+    const int exponent = (int)((__float_as_uint(top) >> 23) & 0xffu) - 127;     // |x| < 2^(exponent + 1)
+    const int shift = (exponent > 14 && exponent < 128) ? exponent - 14 : 0;
+    down = __uint_as_float((uint32_t)(127 - shift) << 23);
+    up = __uint_as_float((uint32_t)(127 + shift) << 23);
+}
+
 // ========================================================================== consumers
-// One streaming phase: activation vector -> registers, then this block's rows of the ring.
-template <int KC, bool WITH_BF16>
-QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi, int& it) {
+// One streaming phase: activation vector -> shared memory and registers, then this block's
+// rows of the ring.  res: this thread's four elements of the bf16 residual stream.
+template <int KC>
+QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, const Wait& wt, int pi, int& it,
+                            float (&res)[4], uint32_t tag_base) {
     constexpr int K = KC * 1024;
-    constexpr int EPC = K / CT;                 // elements a thread converts (4 or 8)
+    constexpr int UNITS = K / 2048;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     bf16* xs = S.xs;
-    uint32_t* xf = S.xf;
+    uint8_t* xf = S.xf;
     float* red = S.red;
+    const uint32_t tag = tag_base | (uint32_t)(ph.layer + 1);
+    const uint32_t tag_x = ph.x_prev_layer ? tag - 1u : tag;
     const unsigned lo = blockIdx.x * ph.quota + min(blockIdx.x, ph.remainder);
     const unsigned hi = (blockIdx.x + 1) * ph.quota + min(blockIdx.x + 1, ph.remainder);
 
-    // ---- static prefetch: norm gamma, conv taps and history of this block's channels
-    float gam[8];
-    if constexpr (KC == 2) if (ph.prologue == PRO_ADD_NORM && tid < 256) {
-        const float4 g0 = *reinterpret_cast<const float4*>(ph.gamma + tid * 8);
-        const float4 g1 = *reinterpret_cast<const float4*>(ph.gamma + tid * 8 + 4);
-        gam[0] = g0.x; gam[1] = g0.y; gam[2] = g0.z; gam[3] = g0.w;
-        gam[4] = g1.x; gam[5] = g1.y; gam[6] = g1.z; gam[7] = g1.w;
-    }
-    // global scales of the segments (one per projection; per-expert scales are read at the
-    // segment, after the routing): in flight across the barrier like the other static inputs
-    float seg_scale = 1.f;
+    // ---- static inputs first (nothing another block writes): norm gamma, global scales of the
+    //      segments, conv taps and history of this block's channels
+    float4 gam = make_float4(0.f, 0.f, 0.f, 0.f);
+    if constexpr (KC == 2) if (ph.prologue == PRO_ADD_NORM) gam = *reinterpret_cast<const float4*>(ph.gamma + tid * 4);
     if (tid < 2 * kMegaMaxSeg) {
         const MegaSeg& sg = ph.seg[tid >> 1];
         const float* src = (tid & 1) ? sg.g2 : sg.g;
-        if ((tid >> 1) < ph.nseg && src && !sg.g_per_expert) seg_scale = *src;
+        float v = 1.f;
+        if ((tid >> 1) < ph.nseg && src && !sg.g_per_expert) v = *src;
+        red[64 + (tid & 1) * 16 + (tid >> 1)] = v;
     }
-    int conv_row0 = 0, conv_n = 0;
+    int conv_row0 = 0;
     bf16* conv_state = nullptr;
-    unsigned short conv_tap_reg = 0, conv_state_reg = 0;     // one element of each per thread
     if constexpr (KC == 2) if (ph.conv_taps) {
         const int W = mp.conv_width;
         conv_state = reinterpret_cast<bf16*>(mp.st.conv_state) + (size_t)ph.state_index * mp.channels * (W - 1);
@@ -404,176 +478,154 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                 int ra, rb;
                 seg_range<K>(seg_start, sg.kind, sg.rows, lo, hi, ra, rb);
                 conv_row0 = ra;
-                conv_n = min(rb - ra, kMegaConvRows);
-                // in flight across the grid barrier; stored to shared memory after it
+                const int conv_n = min(rb - ra, kMegaConvRows);
                 if (tid < conv_n * W)
-                    conv_tap_reg = reinterpret_cast<const unsigned short*>(ph.conv_taps)[(size_t)ra * W + tid];
+                    reinterpret_cast<unsigned short*>(S.conv_taps)[tid] =
+                        reinterpret_cast<const unsigned short*>(ph.conv_taps)[(size_t)ra * W + tid];
                 if (tid < conv_n * (W - 1))
-                    conv_state_reg = reinterpret_cast<const unsigned short*>(conv_state)[(size_t)ra * (W - 1) + tid];
+                    reinterpret_cast<unsigned short*>(S.conv_state)[tid] =
+                        reinterpret_cast<const unsigned short*>(conv_state)[(size_t)ra * (W - 1) + tid];
             }
             seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
         }
     }
-    phase_wait(mp, S, pi, tid);
-    if (tid == 0) trace_mark(mp, pi, 0);
-    // (stored after the wait: thread 0 polls the barrier and must not sit on this load first)
-    if (tid < 2 * kMegaMaxSeg) red[64 + (tid & 1) * 16 + (tid >> 1)] = seg_scale;
-    if constexpr (KC == 2) if (ph.conv_taps) {
-        if (tid < conv_n * mp.conv_width) reinterpret_cast<unsigned short*>(S.conv_taps)[tid] = conv_tap_reg;
-        if (tid < conv_n * (mp.conv_width - 1)) reinterpret_cast<unsigned short*>(S.conv_state)[tid] = conv_state_reg;
-    }
 
-    // ---- routing for this layer (every block selects the same experts from the same logits)
+    // ---- the activation vector: bf16 (for bf16 rows) and f16 (for the tensor-core rows), the
+    //      f16 copy scaled down by a power of two only if it would overflow
+    float out_mult;
+    if (KC == 4 || !ph.keep_x) {
+        if (KC == 2) {
+            // residual add + RMSNorm, four elements per thread (quickdraw/models/qwen.py:205-217)
+            float v[4];
+            if (ph.from_token) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(mp.embed + (size_t)(*mp.token) * K + tid * 4);
+                v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
+                v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
+            } else {
+                const uint4 w4 = wait_words4(ph.x + tid * 4, tag_x, wt);
+                v[0] = word_value(w4.x) + res[0]; v[1] = word_value(w4.y) + res[1];
+                v[2] = word_value(w4.z) + res[2]; v[3] = word_value(w4.w) + res[3];
+            }
+            const float g4[4] = {gam.x, gam.y, gam.z, gam.w};
+            float ss = 0.f, top = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { ss += v[j] * v[j]; top = fmaxf(top, fabsf(v[j] * g4[j])); }
+            ss = warp_sum(ss);
+            top = warp_max(top);
+            if (lane == 0) { red[warp] = ss; red[16 + warp] = top; }
+            named_barrier(1, CT);
+            float tot = 0.f, tmax = 0.f;
+#pragma unroll
+            for (int w = 0; w < CW; ++w) { tot += red[w]; tmax = fmaxf(tmax, red[16 + w]); }
+            const float inv = rsqrtf(tot / (float)K + mp.eps);
+            float down;
+            f16_scale(tmax * inv * 1.01f, down, out_mult);
+            float nrm[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                nrm[j] = round_bf16((v[j] * inv) * g4[j]);
+                res[j] = round_bf16(v[j]);
+            }
+            const __nv_bfloat162 n01 = __floats2bfloat162_rn(nrm[0], nrm[1]), n23 = __floats2bfloat162_rn(nrm[2], nrm[3]);
+            *reinterpret_cast<uint2*>(xs + tid * 4) = make_uint2(*reinterpret_cast<const uint32_t*>(&n01),
+                                                                 *reinterpret_cast<const uint32_t*>(&n23));
+            *reinterpret_cast<uint2*>(xf + tid * 8) = make_uint2(pack_f16x2(nrm[0] * down, nrm[1] * down),
+                                                                 pack_f16x2(nrm[2] * down, nrm[3] * down));
+            if (tid == 0) red[96] = out_mult;
+        } else if (ph.prologue == PRO_GATED_NORM) {
+            // per-head RMSNorm of o, times gamma, times silu(z); a warp per 128-wide head, four
+            // consecutive features per lane (quickdraw/models/qwen.py:161-164)
+            constexpr int HPW = K / 128 / CW;
+            float nv[HPW][4];
+            const uint2 graw = *reinterpret_cast<const uint2*>(ph.head_gamma + lane * 4);
+            const float gm[4] = {__uint_as_float(graw.x << 16), __uint_as_float(graw.x & 0xffff0000u),
+                                 __uint_as_float(graw.y << 16), __uint_as_float(graw.y & 0xffff0000u)};
+            float top = 0.f;
+#pragma unroll
+            for (int a = 0; a < HPW; ++a) {
+                const int base = (warp + a * CW) * 128 + lane * 4;
+                const uint4 ow = wait_words4(ph.x + base, tag, wt);
+                const uint4 zw = wait_words4(ph.z + base, tag, wt);
+                const float o[4] = {word_value(ow.x), word_value(ow.y), word_value(ow.z), word_value(ow.w)};
+                const float zz[4] = {word_value(zw.x), word_value(zw.y), word_value(zw.z), word_value(zw.w)};
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ss += o[j] * o[j];
+                ss = warp_sum(ss);
+                const float inv = rsqrtf(ss / 128.f + mp.eps);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    nv[a][j] = round_bf16(((o[j] * inv) * gm[j]) * silu_precise(zz[j]));
+                    top = fmaxf(top, fabsf(nv[a][j]));
+                }
+            }
+            top = warp_max(top);
+            if (lane == 0) red[16 + warp] = top;
+            named_barrier(1, CT);
+            float tmax = 0.f;
+#pragma unroll
+            for (int w = 0; w < CW; ++w) tmax = fmaxf(tmax, red[16 + w]);
+            float down;
+            f16_scale(tmax, down, out_mult);
+#pragma unroll
+            for (int a = 0; a < HPW; ++a) {
+                const int base = (warp + a * CW) * 128 + lane * 4;
+                *reinterpret_cast<uint2*>(xf + base * 2) = make_uint2(pack_f16x2(nv[a][0] * down, nv[a][1] * down),
+                                                                      pack_f16x2(nv[a][2] * down, nv[a][3] * down));
+            }
+        } else {
+            // the vector as it is (attention output): eight elements per thread
+            const uint4 w0 = wait_words4(ph.x + tid * 8, tag, wt);
+            const uint4 w1 = wait_words4(ph.x + tid * 8 + 4, tag, wt);
+            const float v[8] = {word_value(w0.x), word_value(w0.y), word_value(w0.z), word_value(w0.w),
+                                word_value(w1.x), word_value(w1.y), word_value(w1.z), word_value(w1.w)};
+            float top = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) top = fmaxf(top, fabsf(v[j]));
+            top = warp_max(top);
+            if (lane == 0) red[16 + warp] = top;
+            named_barrier(1, CT);
+            float tmax = 0.f;
+#pragma unroll
+            for (int w = 0; w < CW; ++w) tmax = fmaxf(tmax, red[16 + w]);
+            float down;
+            f16_scale(tmax, down, out_mult);
+            *reinterpret_cast<uint4*>(xf + tid * 16) = make_uint4(pack_f16x2(v[0] * down, v[1] * down), pack_f16x2(v[2] * down, v[3] * down),
+                                                                  pack_f16x2(v[4] * down, v[5] * down), pack_f16x2(v[6] * down, v[7] * down));
+        }
+        named_barrier(1, CT);
+    } else {
+        named_barrier(1, CT);    // the segment scales above are in shared memory
+        out_mult = red[96];      // the vector (and its scale) the phase before left in shared memory
+    }
+    // ---- routing for this layer (every block selects the same experts from the same logits);
+    //      the other warps go on with the shared expert's rows meanwhile
     if constexpr (KC == 2) if (ph.route && warp == 0) {
-        route_fast(ph.router_logits, mp.experts, mp.topk, S.ids, S.weights, lane);
+        float p[8];
+        uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+        if (lane * 8 < mp.experts) {          // the expert count is a multiple of eight
+            a = wait_words4(ph.router_logits + lane * 8, tag, wt);
+            b = wait_words4(ph.router_logits + lane * 8 + 4, tag, wt);
+        }
+        p[0] = word_value(a.x); p[1] = word_value(a.y); p[2] = word_value(a.z); p[3] = word_value(a.w);
+        p[4] = word_value(b.x); p[5] = word_value(b.y); p[6] = word_value(b.z); p[7] = word_value(b.w);
+        route_regs(p, mp.experts, mp.topk, S.ids, S.weights, lane);
         __syncwarp();
         if (blockIdx.x == 0 && lane < mp.topk) { ph.ids_out[lane] = S.ids[lane]; ph.weights_out[lane] = S.weights[lane]; }
         if (lane == 0) mbar_arrive(S.ids_bar);
     }
 
-    if (KC == 4 || !ph.keep_x) {
-        const bf16* xin = (KC == 2 && ph.from_token) ? mp.embed + (size_t)(*mp.token) * K : ph.x;
-        uint32_t m2 = 0u;
-        if (KC == 2 && ph.prologue == PRO_ADD_NORM) {
-            // residual add + RMSNorm by the first 256 threads, eight elements each
-            // (quickdraw/models/qwen.py:205-214)
-            if (tid < 256) {
-                float v[8];
-                float ss = 0.f;
-                const uint4 xa = __ldcg(reinterpret_cast<const uint4*>(xin + tid * 8));
-                uint4 ra4 = make_uint4(0u, 0u, 0u, 0u);
-                if (ph.residual) ra4 = __ldcg(reinterpret_cast<const uint4*>(ph.residual + tid * 8));
-                const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w}, rw0[4] = {ra4.x, ra4.y, ra4.z, ra4.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    v[2 * q] = __uint_as_float(xw[q] << 16) + __uint_as_float(rw0[q] << 16);
-                    v[2 * q + 1] = __uint_as_float(xw[q] & 0xffff0000u) + __uint_as_float(rw0[q] & 0xffff0000u);
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
-                ss = warp_sum(ss);
-                QD_MARK(8);
-                if (lane == 0) red[warp] = ss;
-                named_barrier(2, 256);
-                QD_MARK(9);
-                float tot = 0.f;
-#pragma unroll
-                for (int w = 0; w < 8; ++w) tot += red[w];
-                const float inv = rsqrtf(tot / (float)K + mp.eps);
-                uint32_t nw[4], rw[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const __nv_bfloat162 n2 = __floats2bfloat162_rn((v[2 * q] * inv) * gam[2 * q],
-                                                                    (v[2 * q + 1] * inv) * gam[2 * q + 1]);
-                    const __nv_bfloat162 r2 = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
-                    nw[q] = *reinterpret_cast<const uint32_t*>(&n2);
-                    rw[q] = *reinterpret_cast<const uint32_t*>(&r2);
-                    m2 = max_u16x2(m2, nw[q] & 0x7fff7fffu);
-                }
-                const uint4 nv = make_uint4(nw[0], nw[1], nw[2], nw[3]);
-                *reinterpret_cast<uint4*>(xs + tid * 8) = nv;
-                if (blockIdx.x == 0) {
-                    if (ph.x_out) *reinterpret_cast<uint4*>(ph.x_out + tid * 8) = nv;
-                    *reinterpret_cast<uint4*>(ph.residual_out + tid * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
-                }
-            }
-        } else if (KC == 4 && ph.prologue == PRO_GATED_NORM) {
-            // per-head RMSNorm of o, times gamma, times silu(z); one warp per 128-wide head
-            // (quickdraw/models/qwen.py:161-164)
-            constexpr int HPW = K / 128 / CW;          // heads per warp
-            float o[HPW > 0 ? HPW : 1][4], zz[HPW > 0 ? HPW : 1][4], gm[4];
-#pragma unroll
-            for (int a = 0; a < HPW; ++a)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int i = (warp + a * CW) * 128 + j * 32 + lane;
-                    o[a][j] = ldcg_bf16(xin + i);
-                    zz[a][j] = ldcg_bf16(ph.z + i);
-                }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) gm[j] = ld_bf16(ph.head_gamma + j * 32 + lane);
-            QD_MARK(8);
-#pragma unroll
-            for (int a = 0; a < HPW; ++a) {
-                float ss = 0.f;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) ss += o[a][j] * o[a][j];
-                ss = warp_sum(ss);
-                const float inv = rsqrtf(ss / 128.f + mp.eps);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int i = (warp + a * CW) * 128 + j * 32 + lane;
-                    const bf16 n = __float2bfloat16_rn(((o[a][j] * inv) * gm[j]) * silu_precise(zz[a][j]));
-                    xs[i] = n;
-                    m2 = max(m2, (uint32_t)(__bfloat16_as_ushort(n) & 0x7fffu));
-                    if (blockIdx.x == 0 && ph.x_out) ph.x_out[i] = n;
-                }
-            }
-        } else {
-            for (int i = tid; i < K / 8; i += CT) {
-                const uint4 v = __ldcg(reinterpret_cast<const uint4*>(xin) + i);
-                reinterpret_cast<uint4*>(xs)[i] = v;
-                m2 = max_u16x2(m2, v.x & 0x7fff7fffu); m2 = max_u16x2(m2, v.y & 0x7fff7fffu);
-                m2 = max_u16x2(m2, v.z & 0x7fff7fffu); m2 = max_u16x2(m2, v.w & 0x7fff7fffu);
-            }
-        }
-        QD_MARK(10);
-        {
-            uint32_t m = max(m2 & 0xffffu, m2 >> 16);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
-            if (lane == 0) reinterpret_cast<uint32_t*>(red)[16 + warp] = m;
-        }
-    }
-    named_barrier(1, CT);
-    QD_MARK(11);
-    // ---- the vector as f16 pairs, scaled down by a power of two only if it would overflow f16
-    uint32_t xh[KC == 2 ? 2 : 1][16];      // 2048-wide phases keep the f16 slice in registers
-    float out_mult;
-    {
-        uint32_t m = 0u;
-#pragma unroll
-        for (int w = 0; w < CW; ++w) m = max(m, reinterpret_cast<const uint32_t*>(red)[16 + w]);
-        const int exponent = (int)(m >> 7) - 127;
-        const int shift = exponent > 14 ? exponent - 14 : 0;
-        const float down = __uint_as_float((uint32_t)(127 - shift) << 23);
-        out_mult = __uint_as_float((uint32_t)(127 + min(shift, 127)) << 23);
-        if (KC == 4 || !ph.keep_x) {
-            // f16 layout: the 16-byte piece a lane fetches as (chunk c, quarter q) sits at
-            // ((c * 4 + q) * 32 + lane) * 16, so that a warp's fetch is one contiguous 512 bytes
-            if (EPC == 8) {
-                const uint4 v = *reinterpret_cast<const uint4*>(xs + tid * 8);
-                uint4 h;
-                h.x = pack_f16x2(__uint_as_float(v.x << 16) * down, __uint_as_float(v.x & 0xffff0000u) * down);
-                h.y = pack_f16x2(__uint_as_float(v.y << 16) * down, __uint_as_float(v.y & 0xffff0000u) * down);
-                h.z = pack_f16x2(__uint_as_float(v.z << 16) * down, __uint_as_float(v.z & 0xffff0000u) * down);
-                h.w = pack_f16x2(__uint_as_float(v.w << 16) * down, __uint_as_float(v.w & 0xffff0000u) * down);
-                const int piece = tid;
-                const int pos = ((piece >> 7) * 4 + (piece & 3)) * 32 + ((piece >> 2) & 31);
-                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(xf) + pos * 16) = h;
-            } else {
-                const uint2 v = *reinterpret_cast<const uint2*>(xs + tid * 4);
-                uint2 h;
-                h.x = pack_f16x2(__uint_as_float(v.x << 16) * down, __uint_as_float(v.x & 0xffff0000u) * down);
-                h.y = pack_f16x2(__uint_as_float(v.y << 16) * down, __uint_as_float(v.y & 0xffff0000u) * down);
-                const int piece = tid >> 1;
-                const int pos = ((piece >> 7) * 4 + (piece & 3)) * 32 + ((piece >> 2) & 31);
-                *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(xf) + pos * 16 + (tid & 1) * 8) = h;
-            }
-            named_barrier(1, CT);
-            QD_MARK(12);
-        }
-    }
-    bool have_xh = false;
-    constexpr int NB = K / 256;
     if (tid == 0) trace_mark(mp, pi, 2);
+    uint32_t xh[UNITS][16];
+    load_x_fragments<UNITS>(xf, warp, lane, xh);
+
     // ---- rows
     float best_val = -INFINITY;
-    bool first_tile = true;
     int best_idx = 0x7fffffff;
+    bool first_tile = true, ids_ready = false;
     unsigned seg_start = 0;
-    int turn = 0;                      // rows handed out so far: rotates the row -> warp map
-    bool ok = !*S.abort;
+    int turn = 0;                      // bf16 rows handed out so far: rotates the row -> warp map
+    bool ok = true;
 #pragma unroll 1
     for (int i = 0; i < ph.nseg && ok; ++i) {
         const MegaSeg& sg = ph.seg[i];
@@ -583,27 +635,15 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
         if (ra >= rb) continue;
         int expert = 0;
         if (KC == 2 && sg.slot >= 0) {
+            if (!ids_ready && !mbar_wait(S.ids_bar, ph.layer & 1, mp.status)) { ok = false; break; }
+            ids_ready = true;
             expert = S.ids[sg.slot];
             if (expert < mp.expert_lo || expert >= mp.expert_hi) continue;
             expert -= mp.expert_lo;
         }
-        // 2048-wide NVFP4 rows: the lane's f16 slice goes to registers when the first such
-        // segment shows up; bf16 rows and 4096-wide rows (a block sees few of them) read the
-        // vector from shared memory as they go
-        if (KC == 2 && sg.kind != SEG_BF16 && !have_xh) {
-#pragma unroll
-            for (int c = 0; c < (KC == 2 ? 2 : 1); ++c)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint4 v = lds128(reinterpret_cast<const uint8_t*>(xf) + ((c * 4 + q) * 32 + lane) * 16);
-                    xh[c][q * 4 + 0] = v.x; xh[c][q * 4 + 1] = v.y; xh[c][q * 4 + 2] = v.z; xh[c][q * 4 + 3] = v.w;
-                }
-            have_xh = true;
-        }
         const int tile_rows = seg_tile_rows<K>(sg.kind);
         const float g1 = (sg.g && sg.g_per_expert) ? sg.g[expert] : red[64 + i];
         const float g2 = (sg.g2 && sg.g_per_expert) ? sg.g2[expert] : red[80 + i];
-        bf16* y = (KC == 2 && sg.epilogue == EP_ARGMAX) ? mp.logits : sg.y;
 #pragma unroll 1
         for (int r0 = ra; r0 < rb; r0 += tile_rows, ++it) {
             const int n = min(tile_rows, rb - r0);
@@ -612,62 +652,77 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             if (first_tile && tid == 0) trace_mark(mp, pi, 3);
             first_tile = false;
             const uint8_t* base = S.stages + (size_t)st * kStreamStageBytes;
+            if (sg.kind == SEG_BF16) {
+                if (lane == 0) mbar_arrive(S.ready + st);      // keeps the phase of `ready` in step with the ring
+                if constexpr (KC == 2) {
 #pragma unroll 1
-            for (int r = (warp - turn) & (CW - 1); r < n; r += CW) {
-                const int row = r0 + r;
-                float result;
-                if (WITH_BF16 && sg.kind == SEG_BF16) {
-                    result = warp_sum(bf16_row_dot_smem<NB>(base + (size_t)r * 2 * K, reinterpret_cast<const uint8_t*>(xs), lane));
-                } else {
-                    const int halves = (KC == 2 && sg.kind == SEG_FP4_PAIR) ? 2 : 1;
-                    const uint8_t* sc = base + halves * tile_rows * (K / 2);
-                    float acc[2] = {0.f, 0.f};
-#pragma unroll 1
-                    for (int h = 0; h < halves; ++h) {
-                        if constexpr (KC == 2)
-                            acc[h] = warp_sum(fp4_row_dot<2>(base + (h * tile_rows + r) * (K / 2),
-                                                             sc + (h * tile_rows + r) * (K / 16), xh, lane));
-                        else
-                            acc[h] = warp_sum(fp4_row_dot_smem<KC>(base + (h * tile_rows + r) * (K / 2),
-                                                                   sc + (h * tile_rows + r) * (K / 16),
-                                                                   reinterpret_cast<const uint8_t*>(xf), lane));
+                    for (int r = (warp - turn) & (CW - 1); r < n; r += CW) {
+                        const int row = r0 + r;
+                        const float result = warp_sum(bf16_row_dot_smem<K / 256>(base + (size_t)r * 2 * K,
+                                                                                 reinterpret_cast<const uint8_t*>(xs), lane));
+                        const bf16 rounded = __float2bfloat16_rn(result);
+                        if (sg.epilogue == EP_ARGMAX) {
+                            const int index = ph.row_lo + row;      // vocabulary index (the segment is this rank's shard)
+                            if (lane == 0) mp.logits[index] = rounded;
+                            const float v = __bfloat162float(rounded);
+                            if (v > best_val || (v == best_val && index < best_idx)) { best_val = v; best_idx = index; }
+                        } else if (lane == 0) {
+                            st_word(sg.y + row, make_word(rounded, tag));
+                        }
                     }
-                    result = (acc[0] * out_mult) * g1;
-                    if (halves == 2) {
-                        const float up = round_bf16((acc[1] * out_mult) * g2);
+                    turn = (turn + n) & (CW - 1);
+                }
+            } else {
+                const bool pair = KC == 2 && sg.kind == SEG_FP4_PAIR;
+                const int groups = UNITS == 2 ? 1 : ((pair || n > 16) ? 2 : 1);
+                float* mine = S.partials + st * kRowPartialFloats;
+                tile_partials<K>(base, UNITS == 2 ? 16 : 32, groups, xh, warp, lane, mine + warp * kRowSlots);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(S.ready + st);
+                if (warp == (it & (CW - 1))) {
+                    // this tile's finishing warp: lane = slot of the tile
+                    if (!mbar_wait(S.ready + st, (it / NS) & 1, mp.status)) { ok = false; break; }
+                    const float total = tile_sum(mine, lane);
+                    float result = (total * out_mult) * g1;
+                    if (pair) {
+                        const float up_raw = __shfl_down_sync(0xffffffffu, total, 16);
+                        const float up = round_bf16((up_raw * out_mult) * g2);
                         result = round_bf16(silu_precise(round_bf16(result))) * up;
                     }
-                }
-                const bf16 rounded = __float2bfloat16_rn(result);
-                if (KC == 2 && sg.epilogue == EP_CONV) {
-                    // depthwise causal conv of this channel (quickdraw/models/qwen.py:134-136)
-                    const int W = mp.conv_width, local = row - conv_row0;
-                    float val = 0.f, tap = 0.f;
-                    if (lane < W) {
-                        tap = __bfloat162float(S.conv_taps[local * W + lane]);
-                        val = lane < W - 1 ? __bfloat162float(S.conv_state[local * (W - 1) + lane]) : __bfloat162float(rounded);
-                    }
-                    // W <= 4 and lanes >= W hold zero: the last two butterfly steps are the whole sum
-                    float conv = lane < W ? round_bf16(val * tap) : 0.f;
-                    conv += __shfl_xor_sync(0xffffffffu, conv, 2);
-                    conv += __shfl_xor_sync(0xffffffffu, conv, 1);
-                    if (lane >= 1 && lane < W) conv_state[(size_t)row * (W - 1) + lane - 1] = __float2bfloat16_rn(val);
-                    if (lane == 0) y[row] = __float2bfloat16_rn(silu_precise(conv));
-                } else {
-                    if (lane == 0) y[row] = rounded;
-                    if (KC == 2 && sg.epilogue == EP_ARGMAX) {
-                        const float v = __bfloat162float(rounded);
-                        if (v > best_val || (v == best_val && row < best_idx)) { best_val = v; best_idx = row; }
+                    const bf16 rounded = __float2bfloat16_rn(result);
+                    const bool valid = lane < n && (!pair || lane < 16);
+                    const int row = r0 + lane;
+                    if (valid) {
+                        if (KC == 2 && sg.epilogue == EP_CONV) {
+                            // depthwise causal conv of this channel (quickdraw/models/qwen.py:134-136):
+                            // history taps then the new value; products rounded to bf16, fp32 sum as
+                            // (0 + 2) + (1 + 3)
+                            const int W = mp.conv_width, local = row - conv_row0;
+                            float prod[kStreamConvWidth];
+#pragma unroll
+                            for (int k = 0; k < kStreamConvWidth; ++k) {
+                                float val = 0.f, tap = 0.f;
+                                if (k < W) {
+                                    tap = __bfloat162float(S.conv_taps[local * W + k]);
+                                    val = k < W - 1 ? __bfloat162float(S.conv_state[local * (W - 1) + k]) : __bfloat162float(rounded);
+                                    if (k >= 1) conv_state[(size_t)row * (W - 1) + k - 1] = __float2bfloat16_rn(val);
+                                }
+                                prod[k] = k < W ? round_bf16(val * tap) : 0.f;
+                            }
+                            const float conv = (prod[0] + prod[2]) + (prod[1] + prod[3]);
+                            st_word(sg.y + row, make_word(__float2bfloat16_rn(silu_precise(conv)), tag));
+                        } else {
+                            st_word(sg.y + row, make_word(rounded, tag));
+                        }
                     }
                 }
             }
-            turn = (turn + n) & (CW - 1);
             __syncwarp();
             if (lane == 0) mbar_arrive(S.empty + st);
         }
     }
-    if (!ok && lane == 0) give_up(mp, S);
-    // ---- greedy argmax over the logits (ties: lowest index)
+    if (!ok && lane == 0) *S.abort = 1;
+    // ---- greedy argmax over this rank's logits (ties: lowest index), then over the ranks
     if (KC == 2 && ph.argmax) {
         if (lane == 0) { red[32 + warp] = best_val; reinterpret_cast<int*>(red)[48 + warp] = best_idx; }
         named_barrier(1, CT);
@@ -689,6 +744,24 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                     const int ix = __ldcg(mp.best_idx + b);
                     if (v > fv || (v == fv && ix < fi)) { fv = v; fi = ix; }
                 }
+                if (mp.world > 1) {
+                    // every rank tells every rank its best (value, index); two sets alternate
+                    // from launch to launch
+                    const uint32_t launch = tag_base >> 6;
+                    const uint32_t tag32 = (launch << 8) | 0xA5u;
+                    const long long slot = mp.argmax_offset + (long long)((launch & 1u) * mp.world) * 16;
+                    for (int r = 0; r < mp.world; ++r) {
+                        uint8_t* dst = reinterpret_cast<uint8_t*>(mp.peer_base[r]) + slot + (long long)mp.rank * 16;
+                        st_pair_sys(dst, __float_as_uint(fv), tag32);
+                        st_pair_sys(dst + 8, (uint32_t)fi, tag32);
+                    }
+                    const uint8_t* own = reinterpret_cast<const uint8_t*>(mp.peer_base[mp.rank]) + slot;
+                    for (int r = 0; r < mp.world; ++r) {
+                        const float v = __uint_as_float(wait_pair(reinterpret_cast<const uint2*>(own + r * 16), tag32, wt, true));
+                        const int ix = (int)wait_pair(reinterpret_cast<const uint2*>(own + r * 16 + 8), tag32, wt, true);
+                        if (v > fv || (v == fv && ix < fi)) { fv = v; fi = ix; }
+                    }
+                }
                 *mp.next_token = fi == 0x7fffffff ? 0 : fi;
                 *mp.argmax_counter = 0;
             }
@@ -698,44 +771,43 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
 
 // Gated delta-rule recurrence (quickdraw/models/qwen.py:139-160) for 128-wide key heads:
 // block = (value head, 32 value columns), 256 threads = 8 key groups x 32 columns, 16 state
-// entries per thread, fetched before the grid barrier (only this block ever touches them).
-QD_DEVINL void gdn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
+// entries per thread, fetched before the inputs are waited for (only this block ever touches them).
+QD_DEVINL void gdn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, const Wait& wt, uint32_t tag_base) {
     constexpr int DK = 128, KPT = 16;
     const int tid = threadIdx.x, col = tid & 31, kg = tid >> 5;
     const int dv = mp.dv, hk = mp.hk, hv = mp.hv;
     const int slices = dv / 32;
     const int unit = blockIdx.x;
-    const bool active = unit < hv * slices && tid < 256;
-    const int head = active ? unit / slices : 0, c0 = active ? (unit % slices) * 32 : 0;
-    float* qs = S.scratch;            // [128] q, normalised and scaled
+    if (unit >= hv * slices || tid >= 256) return;
+    const uint32_t tag = tag_base | (uint32_t)(ph.layer + 1);
+    const int head = unit / slices, c0 = (unit % slices) * 32;
+    float* qs = reinterpret_cast<float*>(S.scratch);   // [128] q, normalised and scaled
     float* ks = qs + DK;              // [128] k, normalised
     float* part = ks + DK;            // [8][32]
     float* gates = part + 256;        // decay, beta
     float* tile = mp.st.rec_state + (size_t)ph.state_index * hv * DK * dv + (size_t)head * DK * dv + c0 + col;
     float s[KPT];
-    if (active) {
 #pragma unroll
-        for (int j = 0; j < KPT; ++j) s[j] = tile[(size_t)(kg * KPT + j) * dv];
-    }
-    phase_wait(mp, S, pi, tid);
-    if (tid == 0) trace_mark(mp, pi, 0);
-    if (!active) return;
+    for (int j = 0; j < KPT; ++j) s[j] = tile[(size_t)(kg * KPT + j) * dv];
     const int key_head = head / (hv / hk);
-    // everything this thread needs from the projections, in flight together
-    const float v = ldcg_bf16(ph.qkv + (size_t)2 * hk * DK + (size_t)head * dv + c0 + col);
+    // everything this thread needs from the projections
+    const float v = word_value(wait_word(ph.qkv + (size_t)2 * hk * DK + (size_t)head * dv + c0 + col, tag, wt));
     float qv = 0.f, kv = 0.f, av = 0.f, bv = 0.f;
     if (tid < DK) {
-        qv = ldcg_bf16(ph.qkv + (size_t)key_head * DK + tid);
-        kv = ldcg_bf16(ph.qkv + (size_t)hk * DK + (size_t)key_head * DK + tid);
+        qv = word_value(wait_word(ph.qkv + (size_t)key_head * DK + tid, tag, wt));
+        kv = word_value(wait_word(ph.qkv + (size_t)hk * DK + (size_t)key_head * DK + tid, tag, wt));
     }
-    if (tid == DK) { av = ldcg_bf16(ph.a + head); bv = ldcg_bf16(ph.b + head); }
+    if (tid == DK) {
+        av = word_value(wait_word(ph.ab + head, tag, wt));
+        bv = word_value(wait_word(ph.ab + hv + head, tag, wt));
+    }
     const float qq = warp_sum(qv * qv), kk = warp_sum(kv * kv);
     if (col == 0) { part[kg * 32] = qq; part[kg * 32 + 1] = kk; }
     named_barrier(2, 256);
     if (tid < DK) {
         float tq = 0.f, tk = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) { tq += part[w * 32]; tk += part[w * 32 + 1]; }
+        for (int w = 0; w < 4; ++w) { tq += part[w * 32]; tk += part[w * 32 + 1]; }
         qs[tid] = (qv * rsqrtf(tq + 1e-6f)) / sqrtf((float)DK);
         ks[tid] = kv * rsqrtf(tk + 1e-6f);
     } else if (tid == DK) {
@@ -771,23 +843,23 @@ QD_DEVINL void gdn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& 
         float acc = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) acc += part[w * 32 + col];
-        ph.mix_out[(size_t)head * dv + c0 + col] = __float2bfloat16_rn(acc);
+        st_word(ph.mix_out + (size_t)head * dv + c0 + col, make_word(__float2bfloat16_rn(acc), tag));
     }
 }
 
 // RMSNorm with gamma = 1 + weight and partial RoPE of one head by one warp
 // (quickdraw/models/qwen.py:76-92).  Feature i = j * 32 + lane, so with rotary / 2 a multiple
 // of 32 the two features of a rotation pair sit in the same lane and nothing is exchanged.
-// cos_t / sin_t: bf16-rounded table over the rotary / 2 frequencies.
-QD_DEVINL void norm_rope_row(const bf16* __restrict__ src, const bf16* __restrict__ gamma_w, int d, int rotary,
-                             float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int lane,
-                             float* __restrict__ dst) {
+// cos_t / sin_t: bf16-rounded table over the rotary / 2 frequencies.  dst: bf16 [d].
+QD_DEVINL void norm_rope_row(const tagged* __restrict__ src, uint32_t tag, const Wait& wt, const bf16* __restrict__ gamma_w,
+                             int d, int rotary, float eps, const float* __restrict__ cos_t,
+                             const float* __restrict__ sin_t, int lane, bf16* __restrict__ dst) {
     float v[8], g[8];
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int i = j * 32 + lane;
-        v[j] = i < d ? ldcg_bf16(src + i) : 0.f;
+        v[j] = i < d ? word_value(wait_word(src + i, tag, wt)) : 0.f;
         g[j] = i < d ? ld_bf16(gamma_w + i) : 0.f;
     }
 #pragma unroll
@@ -809,16 +881,95 @@ QD_DEVINL void norm_rope_row(const bf16* __restrict__ src, const bf16* __restric
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int i = j * 32 + lane;
-        if (i < d) dst[i] = v[j];
+        if (i < d) dst[i] = __float2bfloat16_rn(v[j]);
+    }
+}
+
+QD_DEVINL void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+QD_DEVINL uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
+
+// Running state of one warp's share of the context, in MMA fragment layout.  Lane (g, t):
+// softmax statistics of query head g; out[i][c]: feature 32 g + 2 i + (c >> 1) of head 2 t + (c & 1).
+struct AttnAcc {
+    float m, l;
+    float out[16][4];
+};
+
+// Sixteen positions of the context against the (up to) eight query heads of a KV head.
+// krows / vrows: the chunk's key and value rows in shared memory (kAttnRow bytes apart);
+// first: context position of row 0; t1: end of the block's split.
+QD_DEVINL void attn_chunk(AttnAcc& acc, const uint8_t* __restrict__ q_s, const uint8_t* __restrict__ krows,
+                          const uint8_t* __restrict__ vrows, int first, int t1, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int prow = (g & 1) ? 4 + (g >> 1) : (g >> 1);      // key row behind column g of a score tile
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+        const uint4 q4 = lds128(q_s + g * kAttnQRow + m * 64 + t * 16);
+        const uint4 k0 = lds128(krows + prow * kAttnRow + m * 64 + t * 16);
+        const uint4 k1 = lds128(krows + (8 + prow) * kAttnRow + m * 64 + t * 16);
+        mma_bf16(s0, q4.x, 0u, q4.y, 0u, k0.x, k0.y);
+        mma_bf16(s0, q4.z, 0u, q4.w, 0u, k0.z, k0.w);
+        mma_bf16(s1, q4.x, 0u, q4.y, 0u, k1.x, k1.y);
+        mma_bf16(s1, q4.z, 0u, q4.w, 0u, k1.z, k1.w);
+    }
+    // the lane's four scores of head g: rows t, 4 + t, 8 + t, 12 + t of the chunk
+    float sc[4] = {s0[0], s0[1], s1[0], s1[1]};
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        sc[i] = (first + 4 * i + t < t1) ? sc[i] * 0.0625f : -INFINITY;      // 1 / sqrt(256)
+        mx = fmaxf(mx, sc[i]);
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(acc.m, mx);
+    const float alpha = acc.m == -INFINITY ? 0.f : expf(acc.m - m_new);
+    float p[4], psum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { p[i] = sc[i] == -INFINITY ? 0.f : expf(sc[i] - m_new); psum += p[i]; }
+    acc.l = acc.l * alpha + psum;
+    acc.m = m_new;
+    // probabilities as the B operand, split into two bf16 pieces (sixteen bits of mantissa)
+    const uint32_t hi0 = pack_bf16x2(p[0], p[1]), hi1 = pack_bf16x2(p[2], p[3]);
+    const uint32_t lo0 = pack_bf16x2(p[0] - __uint_as_float(hi0 << 16), p[1] - __uint_as_float(hi0 & 0xffff0000u));
+    const uint32_t lo1 = pack_bf16x2(p[2] - __uint_as_float(hi1 << 16), p[3] - __uint_as_float(hi1 & 0xffff0000u));
+    const float a_even = __shfl_sync(0xffffffffu, alpha, 8 * t), a_odd = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        acc.out[i][0] *= a_even; acc.out[i][1] *= a_odd; acc.out[i][2] *= a_even; acc.out[i][3] *= a_odd;
+    }
+    const uint8_t* vb = vrows + g * 64;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint4 r0 = lds128(vb + t * kAttnRow + q * 16);
+        const uint4 r1 = lds128(vb + (4 + t) * kAttnRow + q * 16);
+        const uint4 r2 = lds128(vb + (8 + t) * kAttnRow + q * 16);
+        const uint4 r3 = lds128(vb + (12 + t) * kAttnRow + q * 16);
+        const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w}, w1[4] = {r1.x, r1.y, r1.z, r1.w};
+        const uint32_t w2[4] = {r2.x, r2.y, r2.z, r2.w}, w3[4] = {r3.x, r3.y, r3.z, r3.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t a0 = __byte_perm(w0[e], w1[e], 0x5410), a1 = __byte_perm(w0[e], w1[e], 0x7632);
+            const uint32_t a2 = __byte_perm(w2[e], w3[e], 0x5410), a3 = __byte_perm(w2[e], w3[e], 0x7632);
+            mma_bf16(acc.out[q * 4 + e], a0, a1, a2, a3, hi0, hi1);
+            mma_bf16(acc.out[q * 4 + e], a0, a1, a2, a3, lo0, lo1);
+        }
     }
 }
 
 // Gated GQA decode attention, first half (quickdraw/models/qwen.py:66-116): block = (KV head,
-// context split).  The split is walked in chunks of sixteen positions staged in shared memory:
-// scores (one warp per position, all query heads of the KV head), softmax update (one warp per
-// head), weighted value sum (one thread per head and four features).  Writes the block's
-// partials: unnormalised sum, running max and denominator per head.
-QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi, int& it) {
+// context split).  The split arrives through the ring thirty-two positions at a time; warp
+// w < 8 takes every eighth chunk of sixteen positions, the warps' results merge in shared
+// memory, warp 0 writes the block's partial (unnormalised sums, running max, denominator).
+QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, const Wait& wt, int& it, uint32_t tag_base) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = mp.hq / mp.hkv;
     constexpr int D = 256;
@@ -827,184 +978,164 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
     const AttnSplit cut = attn_split(T, mp.attn_splits);
     const int unit = blockIdx.x;
     const int kvh = unit / cut.active, split = unit % cut.active;
+    if (kvh >= mp.hkv) return;
+    const uint32_t tag = tag_base | (uint32_t)(ph.layer + 1);
     const int t0 = split * cut.per, t1 = min(T, t0 + cut.per);
-    const bool mine = kvh < mp.hkv;
-    float* q_s = reinterpret_cast<float*>(S.xs);            // [G][D]
-    float* k_s = reinterpret_cast<float*>(S.xf);            // [D] the new key
-    const float* cos_t = S.rope;                            // [rotary / 2], filled at kernel start
+    uint8_t* q_s = reinterpret_cast<uint8_t*>(S.xs);                       // [8][kAttnQRow] bf16 query heads
+    bf16* k_s = reinterpret_cast<bf16*>(q_s + 8 * kAttnQRow);              // [256] the new key
+    bf16* v_s = k_s + D;                                                    // [256] the new value
+    const float* cos_t = S.rope;
     const float* sin_t = S.rope + 128;
-    float* sc = k_s + 256;                                  // [8][16] scores of the chunk
-    float* pr = sc + 8 * kAttnChunk;                        // [8][16] softmax numerators
-    float* fix = pr + 8 * kAttnChunk;                       // [8] rescale of the running sums
     const size_t layer_elems = (size_t)mp.st.capacity * mp.hkv * D;
     bf16* k_cache = reinterpret_cast<bf16*>(mp.st.kv_k) + (size_t)ph.state_index * layer_elems;
     bf16* v_cache = reinterpret_cast<bf16*>(mp.st.kv_v) + (size_t)ph.state_index * layer_elems;
-
-    phase_wait(mp, S, pi, tid);
-    if (tid == 0) trace_mark(mp, pi, 0);
-    if (!mine) return;
     const bool owns_new = position >= t0 && position < t1;
-    if (warp < G)
-        norm_rope_row(ph.qg + (size_t)(kvh * G + warp) * 2 * D, ph.q_norm, D, mp.rotary, mp.eps, cos_t, sin_t, lane,
-                      q_s + warp * D);
-    if (owns_new && warp == CW - 1) {
-        norm_rope_row(ph.k_new + (size_t)kvh * D, ph.k_norm, D, mp.rotary, mp.eps, cos_t, sin_t, lane, k_s);
-        __syncwarp();
+    if (warp < 8) {
+        if (warp < G) {
+            norm_rope_row(ph.qg + (size_t)(kvh * G + warp) * 2 * D, tag, wt, ph.q_norm, D, mp.rotary, mp.eps, cos_t, sin_t,
+                          lane, reinterpret_cast<bf16*>(q_s + warp * kAttnQRow));
+        } else {
+            for (int i = lane; i < D; i += 32) reinterpret_cast<bf16*>(q_s + warp * kAttnQRow)[i] = __float2bfloat16_rn(0.f);
+        }
+    } else if (owns_new && warp == CW - 1) {
+        norm_rope_row(ph.kv_new + (size_t)kvh * D, tag, wt, ph.k_norm, D, mp.rotary, mp.eps, cos_t, sin_t, lane, k_s);
         bf16* krow = k_cache + ((size_t)position * mp.hkv + kvh) * D;
         bf16* vrow = v_cache + ((size_t)position * mp.hkv + kvh) * D;
+        __syncwarp();
         for (int i = lane; i < D; i += 32) {
-            krow[i] = __float2bfloat16_rn(k_s[i]);
-            vrow[i] = __float2bfloat16_rn(ldcg_bf16(ph.v_new + (size_t)kvh * D + i));
+            const bf16 vv = __ushort_as_bfloat16((unsigned short)(wait_word(ph.kv_new + (size_t)(mp.hkv + kvh) * D + i, tag, wt) & 0xffffu));
+            v_s[i] = vv;
+            vrow[i] = vv;
+            krow[i] = k_s[i];
         }
     }
-    QD_MARK(9);
-    const float scale = rsqrtf((float)D);
-    float m_run = -INFINITY, l_run = 0.f;            // warp h < G: running max / denominator of head h
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};             // thread (head tid / 64, features 4 (tid % 64) ..)
-    const int ph_head = tid >> 6, pf = (tid & 63) * 4;
-    bool ok = !*S.abort;
-    named_barrier(1, CT);                  // q_s (and k_s) are complete
-    uint32_t qp[4][4];                     // features 8 lane .. 8 lane + 7 of this warp's four heads, packed bf16
+    named_barrier(1, CT);                  // q_s (and the new row) are complete
+    AttnAcc acc;
+    acc.m = -INFINITY; acc.l = 0.f;
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
-        const int head = min((warp & 1) * 4 + h, G - 1);
-        const float4 qa = *reinterpret_cast<const float4*>(q_s + head * D + lane * 8);
-        const float4 qb = *reinterpret_cast<const float4*>(q_s + head * D + lane * 8 + 4);
-        const __nv_bfloat162 p0 = __floats2bfloat162_rn(qa.x, qa.y), p1 = __floats2bfloat162_rn(qa.z, qa.w);
-        const __nv_bfloat162 p2 = __floats2bfloat162_rn(qb.x, qb.y), p3 = __floats2bfloat162_rn(qb.z, qb.w);
-        qp[h][0] = *reinterpret_cast<const uint32_t*>(&p0); qp[h][1] = *reinterpret_cast<const uint32_t*>(&p1);
-        qp[h][2] = *reinterpret_cast<const uint32_t*>(&p2); qp[h][3] = *reinterpret_cast<const uint32_t*>(&p3);
-    }
+    for (int i = 0; i < 16; ++i) { acc.out[i][0] = 0.f; acc.out[i][1] = 0.f; acc.out[i][2] = 0.f; acc.out[i][3] = 0.f; }
+    bool ok = true;
+    int chunk = 0;
 #pragma unroll 1
-    for (int c0 = t0; c0 < t1 && ok; c0 += kAttnChunk, ++it) {
-        // the producer streams the chunks of the split through the ring, ahead of this loop
+    for (int c0 = t0; c0 < t1 && ok; c0 += kAttnStagePos, ++it) {
         const int st = it % NS;
         if (!mbar_wait(S.full + st, (it / NS) & 1, mp.status)) { ok = false; break; }
-        QD_MARK(12);
         uint8_t* buf = S.stages + (size_t)st * kStreamStageBytes;
-        if (owns_new && position >= c0 && position < c0 + kAttnChunk && warp == CW - 1) {
-            // the step's own row: key from the normalised vector, value from the projection
-            const int tl = position - c0;
-            bf16* kd = reinterpret_cast<bf16*>(buf + tl * kAttnRowBytes);
-            bf16* vd = reinterpret_cast<bf16*>(buf + (kAttnChunk + tl) * kAttnRowBytes);
-            for (int i = lane; i < D; i += 32) {
-                kd[i] = __float2bfloat16_rn(k_s[i]);
-                vd[i] = __float2bfloat16_rn(ldcg_bf16(ph.v_new + (size_t)kvh * D + i));
+        const bool has_new = owns_new && position >= c0 && position < c0 + kAttnStagePos;
+        const bool ragged = c0 + kAttnStagePos > t1;
+        if (has_new || ragged) {
+            // the step's own row from the projections; value rows past the split hold stale bytes:
+            // clear them (their probability is zero, but zero times a stale NaN is not)
+            const int valid = min(kAttnStagePos, t1 - c0);
+            for (int e = tid; e < (kAttnStagePos - valid) * (D / 8); e += CT) {
+                const int r = valid + e / (D / 8), c = e % (D / 8);
+                *reinterpret_cast<uint4*>(buf + (kAttnStagePos + r) * kAttnRow + c * 16) = make_uint4(0u, 0u, 0u, 0u);
             }
-        }
-        named_barrier(1, CT);
-        // scores: warp = (two positions of the chunk, one half of the heads); its query features
-        // stay in registers for the whole split
-        {
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int tl = (warp >> 1) + half * 8;
-                const int t = c0 + tl;
-                const uint4 kr = lds128(buf + tl * kAttnRowBytes + lane * 16);
-                const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w};
-                // bf16 x bf16 products are exact in the mixed-precision fma: no unpacking
-                float dots[4];
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                    float dot = 0.f;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        dot = fma_bf16_lo(qp[h][j], kw[j], dot);
-                        dot = fma_bf16_hi(qp[h][j], kw[j], dot);
-                    }
-                    dots[h] = dot;
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-                    for (int h = 0; h < 4; ++h) dots[h] += __shfl_xor_sync(0xffffffffu, dots[h], o);
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                    const int head = (warp & 1) * 4 + h;
-                    if (head < G && lane == h) sc[head * kAttnChunk + tl] = t < t1 ? dots[h] * scale : -INFINITY;
+            if (has_new && warp == CW - 1) {
+                const int r = position - c0;
+                for (int i = lane; i < D; i += 32) {
+                    reinterpret_cast<bf16*>(buf + r * kAttnRow)[i] = k_s[i];
+                    reinterpret_cast<bf16*>(buf + (kAttnStagePos + r) * kAttnRow)[i] = v_s[i];
                 }
             }
+            named_barrier(1, CT);
         }
-        QD_MARK(13);
-        named_barrier(1, CT);
-        // softmax update: warp = head
-        if (warp < G) {
-            const float s_t = lane < kAttnChunk ? sc[warp * kAttnChunk + lane] : -INFINITY;
-            const float nm = fmaxf(m_run, warp_max(s_t));
-            const float p = s_t == -INFINITY ? 0.f : expf(s_t - nm);
-            const float fx = m_run == -INFINITY ? 0.f : expf(m_run - nm);
-            l_run = l_run * fx + warp_sum(p);
-            m_run = nm;
-            if (lane < kAttnChunk) pr[warp * kAttnChunk + lane] = p;
-            if (lane == 0) fix[warp] = fx;
-        }
-        QD_MARK(14);
-        named_barrier(1, CT);
-        // weighted values: thread = (head, four features)
-        if (ph_head < G) {
-            const float fx = fix[ph_head];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] *= fx;
-            const uint8_t* vb = buf + kAttnChunk * kAttnRowBytes + pf * 2;
-            const int valid = min(kAttnChunk, t1 - c0);      // rows past the split hold stale bytes
-#pragma unroll
-            for (int t = 0; t < kAttnChunk; ++t) {
-                if (t >= valid) break;
-                const float p = pr[ph_head * kAttnChunk + t];
-                const uint2 vv = *reinterpret_cast<const uint2*>(vb + t * kAttnRowBytes);
-                acc[0] += p * __uint_as_float(vv.x << 16);
-                acc[1] += p * __uint_as_float(vv.x & 0xffff0000u);
-                acc[2] += p * __uint_as_float(vv.y << 16);
-                acc[3] += p * __uint_as_float(vv.y & 0xffff0000u);
-            }
+        if (lane == 0) mbar_arrive(S.ready + st);      // keeps the phase of `ready` in step with the ring
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h, ++chunk) {
+            if (c0 + 16 * h >= t1) continue;
+            if (warp == (chunk & (kAttnWarps - 1)))
+                attn_chunk(acc, q_s, buf + (16 * h) * kAttnRow, buf + (kAttnStagePos + 16 * h) * kAttnRow, c0 + 16 * h, t1, lane);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(S.empty + st);
     }
-    if (!ok && lane == 0) give_up(mp, S);
-    QD_MARK(10);
-    float* block_out = mp.attn_partial + (((size_t)kvh * mp.attn_splits + split) * G) * kAttnStride;
-    if (ph_head < G) {
-        float* dst = block_out + (size_t)ph_head * kAttnStride + pf;
-        *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
-        *reinterpret_cast<float2*>(dst + 2) = make_float2(acc[2], acc[3]);
+    if (!ok && lane == 0) *S.abort = 1;
+    const int nchunks = (t1 - t0 + 15) / 16;
+    const int active = min(kAttnWarps, nchunks);
+    const int g = lane >> 2, t = lane & 3;
+    acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 1);
+    acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 2);
+    // ---- merge of the warps: warps [s, 2 s) hand their state to warps [0, s)
+    float* mbuf = reinterpret_cast<float*>(S.scratch);
+#pragma unroll 1
+    for (int s = kAttnWarps / 2; s >= 1; s >>= 1) {
+        if (active <= s) continue;
+        if (warp >= s && warp < 2 * s) {
+            float* dst = mbuf + (size_t)(warp - s) * kAttnMergeFloats;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                *reinterpret_cast<float2*>(dst + (2 * t) * D + 32 * g + 2 * i) = make_float2(acc.out[i][0], acc.out[i][2]);
+                *reinterpret_cast<float2*>(dst + (2 * t + 1) * D + 32 * g + 2 * i) = make_float2(acc.out[i][1], acc.out[i][3]);
+            }
+            if (t == 0) { dst[8 * D + g] = acc.m; dst[8 * D + 8 + g] = acc.l; }
+        }
+        named_barrier(1, CT);
+        if (warp < s) {
+            const float* src = mbuf + (size_t)warp * kAttnMergeFloats;
+            const float m2 = src[8 * D + g], l2 = src[8 * D + 8 + g];
+            const float m_new = fmaxf(acc.m, m2);
+            const float f1 = acc.m == -INFINITY ? 0.f : expf(acc.m - m_new);
+            const float f2 = m2 == -INFINITY ? 0.f : expf(m2 - m_new);
+            acc.l = acc.l * f1 + l2 * f2;
+            acc.m = m_new;
+            const float f1e = __shfl_sync(0xffffffffu, f1, 8 * t), f1o = __shfl_sync(0xffffffffu, f1, 8 * t + 4);
+            const float f2e = __shfl_sync(0xffffffffu, f2, 8 * t), f2o = __shfl_sync(0xffffffffu, f2, 8 * t + 4);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float2 e = *reinterpret_cast<const float2*>(src + (2 * t) * D + 32 * g + 2 * i);
+                const float2 o = *reinterpret_cast<const float2*>(src + (2 * t + 1) * D + 32 * g + 2 * i);
+                acc.out[i][0] = acc.out[i][0] * f1e + e.x * f2e;
+                acc.out[i][2] = acc.out[i][2] * f1e + e.y * f2e;
+                acc.out[i][1] = acc.out[i][1] * f1o + o.x * f2o;
+                acc.out[i][3] = acc.out[i][3] * f1o + o.y * f2o;
+            }
+        }
+        named_barrier(1, CT);
     }
-    if (warp < G && lane == 0) {
-        block_out[(size_t)warp * kAttnStride + 256] = m_run;
-        block_out[(size_t)warp * kAttnStride + 257] = l_run;
+    // ---- the block's partial: 64-bit {value, tag} words
+    if (warp == 0) {
+        const uint32_t tag32 = ((tag_base >> 6) << 8) | (uint32_t)(ph.layer + 1);
+        uint2* block_out = mp.attn_partial + (((size_t)kvh * mp.attn_splits + split) * 8) * kAttnStride;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            st_pairs2(block_out + (size_t)(2 * t) * kAttnStride + 32 * g + 2 * i, __float_as_uint(acc.out[i][0]),
+                      __float_as_uint(acc.out[i][2]), tag32);
+            st_pairs2(block_out + (size_t)(2 * t + 1) * kAttnStride + 32 * g + 2 * i, __float_as_uint(acc.out[i][1]),
+                      __float_as_uint(acc.out[i][3]), tag32);
+        }
+        if (t == 0) st_pairs2(block_out + (size_t)g * kAttnStride + 256, __float_as_uint(acc.m), __float_as_uint(acc.l), tag32);
     }
-    QD_MARK(11);
 }
 
 // Second half: block = (query head, 32 output features); warp w merges the splits w, w + 16, ...
 // (all its loads in flight at once), warp 0 merges the sixteen results, normalises and applies
 // the sigmoid gate.
-QD_DEVINL void attn_merge_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
+QD_DEVINL void attn_merge_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, const Wait& wt, uint32_t tag_base) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = mp.hq / mp.hkv;
     constexpr int D = 256;
     const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
     const AttnSplit cut = attn_split(position + 1, mp.attn_splits);
-    float* part = S.scratch;                  // [16 warps][34]: 32 sums, max, denominator
-    phase_wait(mp, S, pi, tid);
-    if (tid == 0) trace_mark(mp, pi, 0);
+    const uint32_t tag = tag_base | (uint32_t)(ph.layer + 1);
+    const uint32_t tag32 = ((tag_base >> 6) << 8) | (uint32_t)(ph.layer + 1);
+    float* part = reinterpret_cast<float*>(S.scratch);     // [16 warps][34]: 32 sums, max, denominator
     const int units = mp.hq * (D / 32);
 #pragma unroll 1
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
         const int qh = unit / (D / 32), f = (unit % (D / 32)) * 32 + lane;
         const int kvh = qh / G, h = qh % G;
-        const float* base = mp.attn_partial + ((size_t)kvh * mp.attn_splits * G + h) * kAttnStride;
-        const float gate_raw = warp == 0 ? ldcg_bf16(ph.qg + (size_t)qh * 2 * D + D + f) : 0.f;
+        const uint2* base = mp.attn_partial + ((size_t)kvh * mp.attn_splits * 8 + h) * kAttnStride;
         constexpr int PER = (kMegaAttnSplits + CW - 1) / CW;      // splits per warp at most
         float ms[PER], ls[PER], as[PER];
 #pragma unroll
         for (int k = 0; k < PER; ++k) {
             const int sp = warp + CW * k;
-            const float* src = base + (size_t)sp * G * kAttnStride;
+            const uint2* src = base + (size_t)sp * 8 * kAttnStride;
             const bool on = sp < cut.active;
-            ms[k] = on ? __ldcg(src + 256) : -INFINITY;
-            ls[k] = on ? __ldcg(src + 257) : 0.f;
-            as[k] = on ? __ldcg(src + f) : 0.f;
+            ms[k] = on ? __uint_as_float(wait_pair(src + 256, tag32, wt)) : -INFINITY;
+            ls[k] = on ? __uint_as_float(wait_pair(src + 257, tag32, wt)) : 0.f;
+            as[k] = on ? __uint_as_float(wait_pair(src + f, tag32, wt)) : 0.f;
         }
         float mm = ms[0];
 #pragma unroll
@@ -1020,6 +1151,7 @@ QD_DEVINL void attn_merge_phase(const MegaParams& mp, const MegaPhase& ph, const
         if (lane == 0) { part[warp * 34 + 32] = mm; part[warp * 34 + 33] = den; }
         named_barrier(1, CT);
         if (warp == 0) {
+            const float gate_raw = word_value(wait_word(ph.qg + (size_t)qh * 2 * D + D + f, tag, wt));
             float top = -INFINITY;
 #pragma unroll
             for (int w = 0; w < CW; ++w) top = fmaxf(top, part[w * 34 + 32]);
@@ -1033,122 +1165,153 @@ QD_DEVINL void attn_merge_phase(const MegaParams& mp, const MegaPhase& ph, const
             }
             const float attended = round_bf16(n2 / d2);
             const float gate = round_bf16(sigmoid_precise(gate_raw));
-            ph.mix_out[(size_t)qh * D + f] = __float2bfloat16_rn(attended * gate);
+            st_word(ph.mix_out + (size_t)qh * D + f, make_word(__float2bfloat16_rn(attended * gate), tag));
         }
         named_barrier(1, CT);
     }
 }
 
-// One down-projection row (512 inputs) by a half-warp: lane hl holds inputs [32 hl, 32 hl + 32).
-QD_DEVINL float down_row(const uint8_t* base, int r, int hl, const uint32_t (&xh)[16]) {
-    const uint4 w = lds128(base + r * (kDownWidth / 2) + hl * 16);
-    const float2 sc = e4m3x2_to_float2(*reinterpret_cast<const uint16_t*>(
-        base + kMegaDownRows * (kDownWidth / 2) + r * (kDownWidth / 16) + hl * 2));
-    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-    float g[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        uint32_t h2[4];
-        e2m1x8_to_f16x2(words[q], h2);
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            g[(q >> 1) * 2] = fma_f16_lo(h2[b], xh[q * 4 + b], g[(q >> 1) * 2]);
-            g[(q >> 1) * 2 + 1] = fma_f16_hi(h2[b], xh[q * 4 + b], g[(q >> 1) * 2 + 1]);
-        }
-    }
-    float acc = fmaf(sc.x, g[0] + g[1], 0.f);
-    acc = fmaf(sc.y, g[2] + g[3], acc);
-    return group_sum<16>(acc);
-}
-
-// Routed and shared down projections with the combine (quickdraw/models/qwen.py:185-193):
-// warp s works on slot s, each half-warp on alternate rows, two rows in flight; rounding
-// points as in moe.cu.  The rows were fetched into the scratch area during the gate/up phase.
-QD_DEVINL void down_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int pi) {
+// Routed and shared down projections with the combine (quickdraw/models/qwen.py:185-193).
+// The block owns up to sixteen output rows; their weight rows of every selected expert and of
+// the shared expert were fetched into the scratch area during the gate/up phase.  A unit of
+// work is (slot, span of 128 inputs): sixteen rows on the tensor cores, the units spread over
+// the warps; then one thread per (slot, row) applies the scales and rounding points of moe.cu,
+// and one thread per row adds the routed rows in ascending expert id and the gated shared row.
+// Expert parallel: a rank multiplies the slots it owns and stores those contributions into
+// every rank's copy of the layer's contribution table; the combine reads all eight slots
+// from the local copy, so every rank forms the same sum in the same order as a single GPU.
+QD_DEVINL void down_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, const Wait& wt, uint32_t tag_base) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int H = mp.hidden;
     const int r0 = (int)((long long)H * blockIdx.x / gridDim.x);
     const int r1 = (int)((long long)H * (blockIdx.x + 1) / gridDim.x);
     const int n = r1 - r0, nslots = mp.topk + 1;
-    float* contrib = reinterpret_cast<float*>(S.xs);                         // [slots][kMegaDownRows]
-    int* order = reinterpret_cast<int*>(contrib + kDownSlots * kMegaDownRows);   // [topk]
-    // the routing of this layer has been in shared memory since the gate/up phase: the global
-    // scale of this warp's expert is a static input, fetched before the barrier
-    const int s = warp;
-    const bool worker = s < nslots;
-    const bool shared = s == mp.topk;
-    const int e = (worker && !shared) ? S.ids[s] : 0;
-    const bool owned = worker && (shared || (e >= mp.expert_lo && e < mp.expert_hi));
-    const int hl = lane & 15, half = lane >> 4;
-    float global_scale = 0.f;
-    if (worker) global_scale = shared ? ph.sg[0] : ph.dg[ph.g_per_expert ? e - mp.expert_lo : 0];
-    phase_wait(mp, S, pi, tid);
-    if (tid == 0) trace_mark(mp, pi, 0);
-    const float strength = tid < kMegaDownRows ? ldcg_bf16(ph.strength) : 0.f;    // in flight during the rows
-    bool ok = !*S.abort;
-    if (worker && ok) {
-        uint32_t xh[16];
-        uint32_t m2 = 0u;          // largest |bf16| bit pattern, per 16-bit half
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(ph.hidden + (size_t)s * kDownWidth) + hl * 16;
+    const uint32_t tag = tag_base | (uint32_t)(ph.layer + 1);
+    uint8_t* hx = reinterpret_cast<uint8_t*>(S.xs);                        // [slots][512] f16 (xs and xf are adjacent)
+    float* dpart = S.partials;                                             // [36 units][16 rows]
+    float* contrib = S.partials + 36 * 16;                                 // [slots][16]
+    int* order = reinterpret_cast<int*>(contrib + kDownSlots * 16);        // [topk]
+    float* smult = reinterpret_cast<float*>(order + 8);                    // [slots] f16 scale of each hidden vector
+    float* red = S.red;
+    // ---- the hidden vectors of the owned slots, 16 bytes (four words) per load: load k of
+    //      thread tid covers words 4 (tid + 512 k) ..; slot = (tid >> 7) + 4 k
+    float hv[3][4];
+    float top[3] = {0.f, 0.f, 0.f};
+    bool have[3];
 #pragma unroll
-        for (int j = 0; j < 16; j += 4) {
-            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + j));
-            xh[j] = v.x; xh[j + 1] = v.y; xh[j + 2] = v.z; xh[j + 3] = v.w;
+    for (int k = 0; k < 3; ++k) {
+        const int idx = tid + CT * k, s = idx >> 7;
+        have[k] = false;
+        if (s < nslots) {
+            const bool shared = s == mp.topk;
+            const int e = shared ? 0 : S.ids[s];
+            have[k] = shared || (e >= mp.expert_lo && e < mp.expert_hi);
         }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) m2 = max_u16x2(m2, xh[j] & 0x7fff7fffu);
-        uint32_t m = max(m2 & 0xffffu, m2 >> 16);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
-        // |x| < 2^(exponent + 1); scale down by a power of two only if f16 would overflow
-        // (non-finite inputs are left alone)
-        const int exponent = (int)(m >> 7) - 127;
-        const int shift = (exponent > 14 && exponent < 128) ? exponent - 14 : 0;
-        const float down = __uint_as_float((uint32_t)(127 - shift) << 23);
-        const float mult = __uint_as_float((uint32_t)(127 + shift) << 23);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) xh[j] = pack_f16x2(__uint_as_float(xh[j] << 16) * down,
-                                                       __uint_as_float(xh[j] & 0xffff0000u) * down);
-        const float scale = shared ? global_scale : round_bf16(global_scale * S.weights[s]);
-        QD_MARK(8);
-        ok = mbar_wait(S.down_bar, ph.layer & 1, mp.status);
-        QD_MARK(9);
-        const uint8_t* base = reinterpret_cast<const uint8_t*>(S.scratch) + (size_t)s * kMegaDownRows * kDownRowBytes;
-        if (ok) {
-#pragma unroll 1
-            for (int rr = 0; rr < n; rr += 4) {
-                // both half-warps run the same iterations (the shuffles name all 32 lanes); a
-                // half-warp past the last row recomputes it and does not store
-                const int ra = min(rr + half, n - 1), rb = min(rr + 2 + half, n - 1);
-                float va = 0.f, vb = 0.f;
-                if (owned) {
-                    const float acc_a = down_row(base, ra, hl, xh) * mult;
-                    const float acc_b = down_row(base, rb, hl, xh) * mult;
-                    va = shared ? round_bf16(acc_a * scale) : round_bf16(round_bf16(acc_a) * scale);
-                    vb = shared ? round_bf16(acc_b * scale) : round_bf16(round_bf16(acc_b) * scale);
-                }
-                if (hl == 0 && rr + half < n) contrib[s * kMegaDownRows + ra] = va;
-                if (hl == 0 && rr + 2 + half < n) contrib[s * kMegaDownRows + rb] = vb;
-            }
+        hv[k][0] = hv[k][1] = hv[k][2] = hv[k][3] = 0.f;
+        if (have[k]) {
+            const uint4 w4 = wait_words4(ph.hidden + (size_t)idx * 4, tag, wt);
+            hv[k][0] = word_value(w4.x); hv[k][1] = word_value(w4.y); hv[k][2] = word_value(w4.z); hv[k][3] = word_value(w4.w);
+            top[k] = fmaxf(fmaxf(fabsf(hv[k][0]), fabsf(hv[k][1])), fmaxf(fabsf(hv[k][2]), fabsf(hv[k][3])));
         }
-    } else if (warp == CW - 1 && lane < mp.topk) {
+        top[k] = warp_max(top[k]);
+        if (lane == 0) red[k * 16 + warp] = top[k];
+    }
+    if (warp == CW - 1 && lane < mp.topk) {
         // slots in ascending expert id: the order the routed rows are summed in
         const int id = S.ids[lane];
         int rank = 0;
         for (int q = 0; q < mp.topk; ++q) rank += S.ids[q] < id;
         order[rank] = lane;
     }
-    QD_MARK(10);
-    if (!ok && lane == 0) give_up(mp, S);
     named_barrier(1, CT);
-    QD_MARK(11);
-    if (tid < n && ok) {
-        float routed = 0.f;
-        for (int k = 0; k < mp.topk; ++k) routed += contrib[order[k] * kMegaDownRows + tid];
-        const float gate = round_bf16(sigmoid_precise(strength));
-        const float shared_row = round_bf16(contrib[mp.topk * kMegaDownRows + tid] * gate);
-        ph.out[r0 + tid] = __float2bfloat16_rn(round_bf16(routed) + shared_row);
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        const int idx = tid + CT * k, s = idx >> 7;
+        if (s >= nslots) continue;
+        const int w0 = (s & 3) * 4;
+        const float tmax = fmaxf(fmaxf(red[k * 16 + w0], red[k * 16 + w0 + 1]), fmaxf(red[k * 16 + w0 + 2], red[k * 16 + w0 + 3]));
+        float down, up;
+        f16_scale(tmax, down, up);
+        *reinterpret_cast<uint2*>(hx + (size_t)idx * 8) = make_uint2(pack_f16x2(hv[k][0] * down, hv[k][1] * down),
+                                                                     pack_f16x2(hv[k][2] * down, hv[k][3] * down));
+        if ((idx & 127) == 0) smult[s] = up;
     }
+    bool ok = mbar_wait(S.down_bar, ph.layer & 1, mp.status);
+    named_barrier(1, CT);
+    // ---- units: (slot, span)
+    {
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll 1
+        for (int u = warp; u < nslots * 4; u += CW) {
+            const int s = u >> 2, span = (u & 3) ^ (g & 1);
+            const bool shared = s == mp.topk;
+            const int e = shared ? 0 : S.ids[s];
+            if (!shared && (e < mp.expert_lo || e >= mp.expert_hi)) continue;
+            uint32_t xh[16];
+            const uint8_t* src = hx + ((size_t)s * kDownWidth + span * 128 + t * 32) * 2;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 v = lds128(src + q * 16);
+                xh[q * 4 + 0] = v.x; xh[q * 4 + 1] = v.y; xh[q * 4 + 2] = v.z; xh[q * 4 + 3] = v.w;
+            }
+            const uint8_t* slot_base = S.scratch + (size_t)s * kDownSlotBytes;
+            float aa[4] = {0.f, 0.f, 0.f, 0.f}, ab[4] = {0.f, 0.f, 0.f, 0.f};
+            unit_mma(slot_base, slot_base + kMegaDownRows * (kDownWidth / 2), kDownWidth / 2, kDownWidth / 16, 0, span, g, t,
+                     xh, aa, ab);
+            if (t == (g >> 1)) {
+                // the partial of span (u & 3) ^ (g & 1) of rows g and g + 8
+                dpart[(s * 4 + span) * 16 + g] = (g & 1) ? aa[1] + ab[1] : aa[0] + ab[0];
+                dpart[(s * 4 + span) * 16 + g + 8] = (g & 1) ? aa[3] + ab[3] : aa[2] + ab[2];
+            }
+        }
+    }
+    named_barrier(1, CT);
+    // ---- one thread per (slot, row): scales and rounding
+    if (tid < nslots * 16) {
+        const int s = tid >> 4, r = tid & 15;
+        const bool shared = s == mp.topk;
+        const int e = shared ? 0 : S.ids[s];
+        const bool owned = shared || (e >= mp.expert_lo && e < mp.expert_hi);
+        if (owned && r < n) {
+            const float acc = (((dpart[(s * 4 + 0) * 16 + r] + dpart[(s * 4 + 1) * 16 + r]) + dpart[(s * 4 + 2) * 16 + r]) +
+                               dpart[(s * 4 + 3) * 16 + r]) * smult[s];
+            float value;
+            if (shared) {
+                value = round_bf16(acc * ph.sg[0]);
+            } else {
+                const float global_scale = ph.dg[ph.g_per_expert ? e - mp.expert_lo : 0];
+                value = round_bf16(round_bf16(acc) * round_bf16(global_scale * S.weights[s]));
+            }
+            contrib[s * 16 + r] = value;
+            if (!shared && mp.world > 1) {
+                const uint32_t word = make_word(__float2bfloat16_rn(value), tag);
+                const long long off = mp.contrib_offset + ((long long)ph.layer * mp.topk * H + (long long)s * H + r0 + r) * 4;
+                for (int rk = 0; rk < mp.world; ++rk)
+                    st_word_sys(reinterpret_cast<uint8_t*>(mp.peer_base[rk]) + off, word);
+            }
+        }
+    }
+    named_barrier(1, CT);
+    if (tid < n) {
+        float routed = 0.f;
+        if (mp.world > 1) {
+            const tagged* mine = reinterpret_cast<const tagged*>(reinterpret_cast<const uint8_t*>(mp.peer_base[mp.rank]) +
+                                                                  mp.contrib_offset) + (size_t)ph.layer * mp.topk * H;
+            float c[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                c[k] = k < mp.topk ? word_value(wait_word(mine + (size_t)order[k] * H + r0 + tid, tag, wt, true)) : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) routed += c[k];
+        } else {
+            for (int k = 0; k < mp.topk; ++k) routed += contrib[order[k] * 16 + tid];
+        }
+        const float strength = word_value(wait_word(ph.strength, tag, wt));
+        const float gate = round_bf16(sigmoid_precise(strength));
+        const float shared_row = round_bf16(contrib[mp.topk * 16 + tid] * gate);
+        st_word(ph.out + r0 + tid, make_word(__float2bfloat16_rn(round_bf16(routed) + shared_row), tag));
+    }
+    if (!ok && lane == 0) *S.abort = 1;
     // the scratch area goes back to the mixer core of the next layer and, after that, to the
     // next bulk copies: order this thread's reads and writes of it before those
     fence_proxy_async();
@@ -1163,71 +1326,82 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
         return;
     }
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(S.full + s, 1); mbar_init(S.empty + s, CW); }
+        for (int s = 0; s < NS; ++s) { mbar_init(S.full + s, 1); mbar_init(S.empty + s, CW); mbar_init(S.ready + s, CW); }
         mbar_init(S.ids_bar, 1);
         mbar_init(S.down_bar, 1);
         mbar_fence_init();
         *S.abort = 0;
-        *S.flag = 0;
     }
+    // The launch number: part of every tag.  Read by every thread before any block can leave
+    // (the last block to leave advances it).
+    const uint32_t launch = *reinterpret_cast<volatile unsigned int*>(mp.epoch) + 1u;
+    const uint32_t tag_base = (launch & 0x3ffu) << 6;
     __syncthreads();
-    if (warp == CW) {
+    // A position outside the cache (it may come from a device scalar) touches nothing: every
+    // block skips the token and the status word says so.
+    const int step_position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
+    const bool bad_position = step_position < 0 || step_position >= mp.st.capacity;
+    if (bad_position) {
+        if (tid == 0 && blockIdx.x == 0) atomicOr(mp.status, QD_STATUS_BAD_ARG);
+    } else if (warp == CW) {
         producer(mp, S, lane);
-        return;
-    }
-    // rotation table of this step's position, once for all attention layers
-    // (quickdraw/models/qwen.py:84-88: fp32 angle, cos / sin rounded to bf16)
-    if (mp.rotary > 0) {
-        const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
-        for (int f = tid; f < mp.rotary / 2; f += CT) {
-            const float inv_freq = 1.0f / powf(mp.theta, (float)(2 * f) / (float)mp.rotary);
-            const float angle = (float)position * inv_freq;
-            S.rope[f] = round_bf16(cosf(angle));
-            S.rope[128 + f] = round_bf16(sinf(angle));
+    } else {
+        Wait wt;
+        wt.status = mp.status; wt.abort = S.abort; wt.limit_ns = (unsigned long long)mp.wait_limit_us * 1000ull;
+        // rotation table of this step's position, once for all attention layers
+        // (quickdraw/models/qwen.py:84-88: fp32 angle, cos / sin rounded to bf16)
+        if (mp.rotary > 0) {
+            const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
+            for (int f = tid; f < mp.rotary / 2; f += CT) {
+                const float inv_freq = 1.0f / powf(mp.theta, (float)(2 * f) / (float)mp.rotary);
+                const float angle = (float)position * inv_freq;
+                S.rope[f] = round_bf16(cosf(angle));
+                S.rope[128 + f] = round_bf16(sinf(angle));
+            }
         }
-    }
-    // first phase parameters
-    {
-        const uint4* src = reinterpret_cast<const uint4*>(mp.program);
-        uint4* dst = reinterpret_cast<uint4*>(S.cph);
-        for (int i = tid; i < (int)(sizeof(MegaPhase) / 16); i += CT) dst[i] = __ldg(src + i);
-    }
-    named_barrier(1, CT);
-    int it = 0;
-#pragma unroll 1
-    for (int pi = 0; pi < mp.nphases; ++pi) {
-        const MegaPhase& ph = S.cph[pi & 1];
-        if (pi + 1 < mp.nphases) {
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(mp.program + pi + 1);
-            uint8_t* dst = reinterpret_cast<uint8_t*>(S.cph + ((pi + 1) & 1));
-            for (int i = tid; i < (int)(sizeof(MegaPhase) / 16); i += CT) cp_async16(dst + i * 16, src + i * 16);
+        // first phase parameters
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(mp.program);
+            uint4* dst = reinterpret_cast<uint4*>(S.cph);
+            for (int i = tid; i < (int)(sizeof(MegaPhase) / 16); i += CT) dst[i] = __ldg(src + i);
         }
-        if (ph.kind == MK_STREAM) {
-            if (ph.width == 2048) stream_phase<2, true>(mp, ph, S, pi, it);
-            else stream_phase<4, false>(mp, ph, S, pi, it);
-        } else if (ph.kind == MK_GDN) {
-            gdn_phase(mp, ph, S, pi);
-        } else if (ph.kind == MK_ATTN) {
-            attn_phase(mp, ph, S, pi, it);
-        } else if (ph.kind == MK_ATTN_MERGE) {
-            attn_merge_phase(mp, ph, S, pi);
-        } else {
-            down_phase(mp, ph, S, pi);
-        }
-        cp_async_wait_all();
-        fence_proxy_async();      // scratch and ring bytes this thread touched may be bulk-copy targets next
-        if (tid == 0) trace_mark(mp, pi, 1);
         named_barrier(1, CT);
-        // release: this block's writes (ordered before it by the block barrier) are visible to
-        // whoever acquires the new count
-        if (tid == 0 && pi + 1 < mp.nphases) red_release_add(mp.bar, 1u);
+        float res[4] = {0.f, 0.f, 0.f, 0.f};
+        int it = 0;
+#pragma unroll 1
+        for (int pi = 0; pi < mp.nphases; ++pi) {
+            const MegaPhase& ph = S.cph[pi & 1];
+            if (pi + 1 < mp.nphases) {
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(mp.program + pi + 1);
+                uint8_t* dst = reinterpret_cast<uint8_t*>(S.cph + ((pi + 1) & 1));
+                for (int i = tid; i < (int)(sizeof(MegaPhase) / 16); i += CT) cp_async16(dst + i * 16, src + i * 16);
+            }
+            if (tid == 0) trace_mark(mp, pi, 0);
+            if (ph.kind == MK_STREAM) {
+                if (ph.width == 2048) stream_phase<2>(mp, ph, S, wt, pi, it, res, tag_base);
+                else stream_phase<4>(mp, ph, S, wt, pi, it, res, tag_base);
+            } else if (ph.kind == MK_GDN) {
+                gdn_phase(mp, ph, S, wt, tag_base);
+            } else if (ph.kind == MK_ATTN) {
+                attn_phase(mp, ph, S, wt, it, tag_base);
+            } else if (ph.kind == MK_ATTN_MERGE) {
+                attn_merge_phase(mp, ph, S, wt, tag_base);
+            } else {
+                down_phase(mp, ph, S, wt, tag_base);
+            }
+            cp_async_wait_all();
+            fence_proxy_async();      // scratch and ring bytes this thread touched may be bulk-copy targets next
+            if (tid == 0) trace_mark(mp, pi, 1);
+            named_barrier(1, CT);
+        }
     }
-    // the last block to leave resets the barrier words for the next launch
+    // the last block to leave advances the launch number for the next launch
+    __syncthreads();
     if (tid == 0) {
         __threadfence();
         const unsigned int gone = atomicAdd(mp.exit_count, 1u);
         if (gone == gridDim.x - 1) {
-            *mp.bar = 0u;
+            *mp.epoch = launch;
             *mp.exit_count = 0u;
             __threadfence();
         }

@@ -194,11 +194,13 @@ extern "C" int qd_moe_down_combine(const void* hidden, const int32_t* ids, const
     p.shared_out = (bf16*)shared_out; p.H = hidden_size; p.topk = topk;
     p.expert_lo = expert_lo; p.expert_hi = expert_hi; p.status = nullptr;
     const size_t smem = (size_t)kDownSlots * kDownMaxRows * kDownRowBytes + 8 + kDownSlots * kDownMaxRows * 4 + 128;
-    static bool configured = false;
-    if (!configured) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return QD_ERR_LAUNCH;
+    static bool configured[64];
+    if (!configured[device]) {
         if (cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return QD_ERR_LAUNCH;
-        configured = true;
+        configured[device] = true;
     }
     return qd_launch(moe_down_kernel, dim3(grid), dim3(kDownThreads), smem, (cudaStream_t)stream, pdl != 0, p);
 }

@@ -416,12 +416,13 @@ __global__ void seq_attn_prepare_kernel(const bf16* __restrict__ qg, const bf16*
                                         const bf16* __restrict__ k_norm, bf16* __restrict__ k_cache,
                                         bf16* __restrict__ v_cache, bf16* __restrict__ q_out, int position0, int hq,
                                         int hk, int d, int rotary, float theta, float eps,
-                                        const int* __restrict__ positions, long long cache_stride) {
+                                        const int* __restrict__ positions, long long cache_stride, int capacity) {
     const int t = blockIdx.y, head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (head >= hq + hk) return;
     // a chunk of one sequence: consecutive positions of one cache; batched decode: row t is
     // sequence t at its own position in its own cache
     const int position = positions ? positions[t] : position0 + t;
+    if (position < 0 || position >= capacity) return;      // a position outside the cache touches nothing
     if (positions) { k_cache += (size_t)t * cache_stride; v_cache += (size_t)t * cache_stride; }
     const bool is_q = head < hq;
     const bf16* src = is_q ? qg + ((size_t)t * hq + head) * 2 * d : k_new + ((size_t)t * hk + (head - hq)) * d;
@@ -544,7 +545,7 @@ struct LaneAttnParams {
     float* partial;         // [batch, hk, splits, G, d + 2]
     unsigned int* counters; // [batch, hk], zero on entry and on exit
     const int* positions;
-    int hq, hk, d, splits;
+    int hq, hk, d, splits, capacity;
 };
 
 __global__ void __launch_bounds__(kLaneAttnWarps * 32)
@@ -559,6 +560,7 @@ batch_attn_lanes_kernel(const LaneAttnParams p) {
     const size_t z = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int T = p.positions[z] + 1;
+    if (T < 1 || T > p.capacity) return;      // a position outside the cache: the sequence's output is left alone
     int active = (T + kLaneAttnSplitMin - 1) / kLaneAttnSplitMin;
     if (active > p.splits) active = p.splits;
     const int per = ((T + active - 1) / active + 31) & ~31;
@@ -911,7 +913,7 @@ extern "C" int qd_seq_attention(const void* qg, const void* k_new, const void* v
     seq_attn_prepare_kernel<<<dim3((heads + 7) / 8, tokens), 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)qg, (const bf16*)k_new, (const bf16*)v_new, (const bf16*)q_norm, (const bf16*)k_norm,
         (bf16*)k_cache, (bf16*)v_cache, (bf16*)q_scratch, position0, q_heads, kv_heads, head_dim, rotary_dim, theta, eps,
-        nullptr, 0);
+        nullptr, 0, capacity);
     if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     seq_attn_kernel<<<dim3(kv_heads, tokens), 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)q_scratch, (const bf16*)qg, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, position0,
@@ -940,12 +942,12 @@ extern "C" int qd_batch_attention(const void* qg, const void* k_new, const void*
     seq_attn_prepare_kernel<<<dim3((heads + 7) / 8, batch), 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)qg, (const bf16*)k_new, (const bf16*)v_new, (const bf16*)q_norm, (const bf16*)k_norm,
         (bf16*)k_cache, (bf16*)v_cache, (bf16*)q_scratch, 0, q_heads, kv_heads, head_dim, rotary_dim, theta, eps,
-        positions, cache_stride);
+        positions, cache_stride, capacity);
     if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     LaneAttnParams p;
     p.q = (const bf16*)q_scratch; p.qg = (const bf16*)qg; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
     p.cache_stride = cache_stride; p.out = (bf16*)out; p.partial = scratch; p.counters = counters; p.positions = positions;
-    p.hq = q_heads; p.hk = kv_heads; p.d = head_dim; p.splits = splits;
+    p.hq = q_heads; p.hk = kv_heads; p.d = head_dim; p.splits = splits; p.capacity = capacity;
     const size_t smem = (size_t)G * head_dim * sizeof(bf16) + sizeof(float) * (kLaneAttnWarps * 32 * kLaneAttnGroup +
                                                                                 (size_t)kLaneAttnWarps * G * (head_dim + 2));
     int dev = 0;

@@ -1,4 +1,5 @@
-// One decode step of the hybrid MoE model as a fixed sequence of fused launches
+// One decode step of the hybrid MoE model as a fixed sequence of fused launches, and the
+// phase list of the same step for the persistent kernel
 // (reference: quickdraw/models/qwen.py:196-241).  Per layer:
 //   A  residual add + RMSNorm  ->  mixer input projections (+ short conv for DeltaNet)
 //   M  DeltaNet recurrence, or split-context GQA attention
@@ -29,7 +30,10 @@ struct Workspace {
     int32_t* ids; float* weights; float* routed_partial; float* attn_scratch;
     unsigned int* attn_counters; float* best_val; int* best_idx; unsigned int* argmax_counter;
     unsigned int* status; int* cursor; unsigned int* route_counter;
-    unsigned int* grid_bar; unsigned int* grid_exit; float* mega_attn_scratch;   // persistent kernel
+    // persistent kernel: the launch counter, the exit counter and the tagged activation words
+    unsigned int* epoch; unsigned int* grid_exit;
+    tagged *t_moe_out, *t_big, *t_mid, *t_ab, *t_o, *t_mixed, *t_router, *t_hidden;
+    uint2* t_attn;
     size_t bytes;
 };
 
@@ -71,9 +75,17 @@ Workspace carve(const qd_model_config& c, uint8_t* base) {
     w.attn_scratch = (float*)take(4 * (size_t)qd_attn_scratch_floats(c.q_heads, c.kv_heads, c.head_dim, kAttnSplits));
     w.best_val = (float*)take(4 * kMaxGrid);
     w.best_idx = (int*)take(4 * kMaxGrid);
-    w.grid_bar = (unsigned int*)take(4);
+    w.epoch = (unsigned int*)take(4);
     w.grid_exit = (unsigned int*)take(4);
-    w.mega_attn_scratch = (float*)take(4 * (size_t)qd_attn_scratch_floats(c.q_heads, c.kv_heads, c.head_dim, kMegaAttnSplits));
+    w.t_moe_out = (tagged*)take(4 * (size_t)c.hidden);
+    w.t_big = (tagged*)take(4 * (size_t)big);
+    w.t_mid = (tagged*)take(4 * (size_t)mid);
+    w.t_ab = (tagged*)take(4 * 2 * (size_t)c.value_heads);
+    w.t_o = (tagged*)take(4 * (size_t)owide);
+    w.t_mixed = (tagged*)take(4 * (size_t)c.hidden);
+    w.t_router = (tagged*)take(4 * ((size_t)c.experts + 4));          // logits, then the shared-expert gate logit
+    w.t_hidden = (tagged*)take(4 * (size_t)(c.topk + 1) * c.intermediate);
+    w.t_attn = (uint2*)take(8 * (size_t)c.kv_heads * kMegaAttnSplits * 8 * 258);
     w.bytes = off;
     return w;
 }
@@ -106,12 +118,11 @@ StreamSeg pair_seg(const qd_fp4& gate, const qd_fp4& up, int rows, bf16* y) {
 #define QD_TRY(expr) do { const int rc_ = (expr); if (rc_ != QD_OK) return rc_; } while (0)
 
 int run_layers(qd_model* m, const qd_state* st, const long long* token, const int* pos_dev, int pos_host,
-               void* workspace, float* routed_partial, int begin, int end, bool head, void* logits,
+               void* workspace, int begin, int end, bool head, void* logits,
                long long* next_token, int flags, cudaStream_t stream) {
     const qd_model_config& c = m->cfg;
     if (!fused_shape_ok(c)) return QD_ERR_UNSUPPORTED;
     const bool pdl = flags & QD_FLAG_PDL;
-    const bool ep = routed_partial != nullptr;
     Workspace w = carve(c, (uint8_t*)workspace);
     const int H = c.hidden;
     const int channels = 2 * c.key_heads * c.key_dim + c.value_heads * c.value_dim;
@@ -122,7 +133,6 @@ int run_layers(qd_model* m, const qd_state* st, const long long* token, const in
     for (int L = begin; L < end; ++L) {
         const qd_layer& ly = m->layers[L];
         if (!m->layer_set[L]) return QD_ERR_ARG;
-        if (ep && L > 0 && L == begin) QD_TRY(qd_moe_finish(routed_partial, w.shared_row, w.moe_out, H, pdl, stream));
         // ---- A
         StreamParams a = {};
         a.width = H; a.prologue = PRO_ADD_NORM; a.gamma = ly.gamma_in; a.eps = c.eps;
@@ -191,12 +201,10 @@ int run_layers(qd_model* m, const qd_state* st, const long long* token, const in
         // ---- E
         QD_TRY(qd_moe_down_combine(w.hidden, w.ids, w.weights, ly.experts_down.codes, ly.experts_down.scales,
                                    ly.experts_down.global, ly.shared_down.codes, ly.shared_down.scales,
-                                   ly.shared_down.global, w.strength, ep ? nullptr : w.moe_out,
-                                   ep ? routed_partial : nullptr, ep ? w.shared_row : nullptr, H, c.intermediate,
+                                   ly.shared_down.global, w.strength, w.moe_out, nullptr, nullptr, H, c.intermediate,
                                    c.topk, ly.experts_global_per_expert, c.expert_lo, c.expert_hi, pdl, stream));
     }
     if (head) {
-        if (ep) QD_TRY(qd_moe_finish(routed_partial, w.shared_row, w.moe_out, H, pdl, stream));
         StreamParams h = {};
         h.width = H; h.prologue = PRO_ADD_NORM; h.gamma = c.final_gamma; h.eps = c.eps;
         h.x = w.moe_out; h.residual = w.resid[0]; h.residual_out = w.resid[1];
@@ -245,20 +253,10 @@ extern "C" int qd_decode_step(qd_model* model, const qd_state* state, const long
                               const int* position_dev, int position_host, void* workspace, void* logits_out,
                               long long* next_token, int flags, void* stream) {
     QD_CHECK_ARG(model && state && token && workspace && logits_out && next_token);
-    return run_layers(model, state, token, position_dev, position_host, workspace, nullptr, 0, model->cfg.layers,
+    if (model->cfg.expert_lo != 0 || model->cfg.expert_hi < model->cfg.experts || model->cfg.vocab_hi != 0)
+        return QD_ERR_UNSUPPORTED;      // model slices run through the persistent kernel only
+    return run_layers(model, state, token, position_dev, position_host, workspace, 0, model->cfg.layers,
                       !(flags & QD_FLAG_NO_LOGITS), logits_out, next_token, flags, (cudaStream_t)stream);
-}
-
-extern "C" int qd_decode_layers(qd_model* model, const qd_state* state, const long long* token,
-                                const int* position_dev, int position_host, void* workspace,
-                                float* routed_partial, int layer_begin, int layer_end, void* logits_out,
-                                long long* next_token, int flags, void* stream) {
-    QD_CHECK_ARG(model && state && token && workspace && routed_partial);
-    QD_CHECK_ARG(layer_begin >= 0 && layer_begin <= layer_end && layer_end <= model->cfg.layers);
-    const bool head = layer_begin == model->cfg.layers;
-    QD_CHECK_ARG(!head || (logits_out && next_token));
-    return run_layers(model, state, token, position_dev, position_host, workspace, routed_partial, layer_begin,
-                      layer_end, head, logits_out, next_token, flags, (cudaStream_t)stream);
 }
 
 extern "C" int qd_nvfp4_gemv_bank(const void* x, const void* codes, const void* scales, const float* global,
@@ -280,9 +278,11 @@ extern "C" int qd_nvfp4_gemv_bank(const void* x, const void* codes, const void* 
 // ------------------------------------------------------------- persistent kernel program
 namespace {
 
-MegaSeg mega_seg(const StreamSeg& s) {
+unsigned int g_wait_limit_us = 200000;      // bound of every device-side wait of the persistent kernel
+
+MegaSeg mega_seg(const StreamSeg& s, tagged* y) {
     MegaSeg m = {};
-    m.w = s.w; m.s = s.s; m.g = s.g; m.w2 = s.w2; m.s2 = s.s2; m.g2 = s.g2; m.y = s.y;
+    m.w = s.w; m.s = s.s; m.g = s.g; m.w2 = s.w2; m.s2 = s.s2; m.g2 = s.g2; m.y = y;
     m.w_stride = s.w_stride; m.s_stride = s.s_stride; m.rows = s.rows;
     m.kind = (short)s.kind; m.epilogue = (short)s.epilogue; m.slot = (short)s.slot; m.g_per_expert = (short)s.g_per_expert;
     return m;
@@ -303,8 +303,6 @@ bool mega_finish_stream(MegaPhase& ph, int grid) {
     return true;
 }
 
-
-
 // six phases per layer, one more (the split merge) per attention layer, and the LM head
 int mega_phase_count(const qd_model* m) {
     int n = 6 * m->cfg.layers + 1;
@@ -313,11 +311,13 @@ int mega_phase_count(const qd_model* m) {
 }
 
 bool mega_shape_ok(const qd_model_config& c, int grid) {
-    return fused_shape_ok(c) && c.expert_lo == 0 && c.expert_hi >= c.experts && c.conv_width <= kStreamConvWidth &&
+    return fused_shape_ok(c) && c.expert_lo >= 0 && c.expert_hi > c.expert_lo && c.conv_width <= kStreamConvWidth &&
            c.key_dim == 128 && c.value_dim % 32 == 0 && c.value_heads * (c.value_dim / 32) <= grid &&
            c.head_dim == 256 && c.rotary_dim <= 256 && c.rotary_dim % 64 == 0 && c.kv_heads >= 1 && c.kv_heads <= grid &&
            c.q_heads / c.kv_heads <= 8 && (c.hidden + grid - 1) / grid <= kMegaDownRows &&
-           c.topk + 1 <= 9 && c.topk + 1 <= kMegaMaxSeg && c.conv_width <= 4 && grid <= kMaxGrid;
+           c.topk + 1 <= 9 && c.topk + 1 <= kMegaMaxSeg && c.conv_width <= 4 && grid <= kMaxGrid &&
+           c.experts % 8 == 0 && c.layers <= kMegaMaxLayers && c.vocab_lo >= 0 &&
+           (c.vocab_hi == 0 || (c.vocab_hi > c.vocab_lo && c.vocab_hi <= c.vocab));
 }
 
 int mega_attn_splits(const qd_model_config& c, int grid) {
@@ -325,7 +325,24 @@ int mega_attn_splits(const qd_model_config& c, int grid) {
     return s > kMegaAttnSplits ? kMegaAttnSplits : s;
 }
 
+// Exchange area of one rank (expert parallel): the routed contributions of every layer, then
+// two sets of per-rank (best logit, index) pairs.
+long long exchange_contrib_bytes(const qd_model_config& c) {
+    return (long long)align_up((size_t)c.layers * c.topk * c.hidden * 4);
+}
+
 }  // namespace
+
+extern "C" long long qd_exchange_bytes(const qd_model* model) {
+    if (!model) return -1;
+    return exchange_contrib_bytes(model->cfg) + 2 * kMegaMaxRanks * 16;
+}
+
+extern "C" int qd_set_wait_limit_us(unsigned int microseconds) {
+    if (microseconds == 0) return QD_ERR_ARG;
+    g_wait_limit_us = microseconds;
+    return QD_OK;
+}
 
 extern "C" long long qd_program_bytes(const qd_model* model) {
     if (!model) return -1;
@@ -351,89 +368,92 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
         // ---- A: residual add + norm -> mixer input projections
         MegaPhase a = {};
         a.kind = MK_STREAM; a.width = H; a.prologue = PRO_ADD_NORM; a.layer = L; a.state_index = ly.state_index;
-        a.gamma = ly.gamma_in; a.residual_out = w.resid[1];
-        if (L == 0) { a.from_token = 1; a.residual = nullptr; }
-        else { a.x = w.moe_out; a.residual = w.resid[0]; }
+        a.gamma = ly.gamma_in;
+        if (L == 0) a.from_token = 1;
+        else { a.x = w.t_moe_out; a.x_prev_layer = 1; }
         if (ly.is_attention) {
             a.nseg = 3;
-            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, 2 * q_width, w.big));
-            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, kv_width, w.mid));
-            a.seg[2] = mega_seg(fp4_seg(ly.proj_c, kv_width, w.mid + kv_width));
+            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, 2 * q_width, nullptr), w.t_big);
+            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, kv_width, nullptr), w.t_mid);
+            a.seg[2] = mega_seg(fp4_seg(ly.proj_c, kv_width, nullptr), w.t_mid + kv_width);
         } else {
             a.nseg = 4;
-            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, channels, w.big, EP_CONV));
-            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, value_width, w.mid));
-            a.seg[2] = mega_seg(bf16_seg(ly.in_proj_a, c.value_heads, w.ab));
-            a.seg[3] = mega_seg(bf16_seg(ly.in_proj_b, c.value_heads, w.ab + c.value_heads));
+            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, channels, nullptr, EP_CONV), w.t_big);
+            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, value_width, nullptr), w.t_mid);
+            a.seg[2] = mega_seg(bf16_seg(ly.in_proj_a, c.value_heads, nullptr), w.t_ab);
+            a.seg[3] = mega_seg(bf16_seg(ly.in_proj_b, c.value_heads, nullptr), w.t_ab + c.value_heads);
             a.conv_taps = (const bf16*)ly.conv1d;
         }
         if (!mega_finish_stream(a, grid)) return QD_ERR_UNSUPPORTED;
         out[n++] = a;
         // ---- M: mixer core
         MegaPhase m = {};
-        m.layer = L; m.state_index = ly.state_index; m.mix_out = w.o;
+        m.layer = L; m.state_index = ly.state_index; m.mix_out = w.t_o;
         if (ly.is_attention) {
             m.kind = MK_ATTN;
-            m.qg = w.big; m.k_new = w.mid; m.v_new = w.mid + kv_width;
+            m.qg = w.t_big; m.kv_new = w.t_mid;
             m.q_norm = (const bf16*)ly.q_norm; m.k_norm = (const bf16*)ly.k_norm;
             out[n++] = m;
             m.kind = MK_ATTN_MERGE;       // second half: merge of the context splits, gate
         } else {
             m.kind = MK_GDN;
-            m.qkv = w.big; m.a = w.ab; m.b = w.ab + c.value_heads;
+            m.qkv = w.t_big; m.ab = w.t_ab;
             m.a_log = (const bf16*)ly.a_log; m.dt_bias = (const bf16*)ly.dt_bias;
         }
         out[n++] = m;
         // ---- B: output projection
         MegaPhase b = {};
-        b.kind = MK_STREAM; b.width = 4096; b.layer = L; b.x = w.o;
-        b.nseg = 1; b.seg[0] = mega_seg(fp4_seg(ly.proj_out, H, w.mixed));
+        b.kind = MK_STREAM; b.width = 4096; b.layer = L; b.x = w.t_o;
+        b.nseg = 1; b.seg[0] = mega_seg(fp4_seg(ly.proj_out, H, nullptr), w.t_mixed);
         if (ly.is_attention) b.prologue = PRO_NONE;
-        else { b.prologue = PRO_GATED_NORM; b.z = w.mid; b.head_gamma = (const bf16*)ly.head_norm; }
+        else { b.prologue = PRO_GATED_NORM; b.z = w.t_mid; b.head_gamma = (const bf16*)ly.head_norm; }
         if (!mega_finish_stream(b, grid)) return QD_ERR_UNSUPPORTED;
         out[n++] = b;
-        // ---- C: residual add + norm -> router logits, shared gate logit, shared gate/up
+        // ---- C: residual add + norm -> router logits, shared gate logit
         MegaPhase cc = {};
         cc.kind = MK_STREAM; cc.width = H; cc.prologue = PRO_ADD_NORM; cc.layer = L;
-        cc.gamma = ly.gamma_post; cc.x = w.mixed; cc.residual = w.resid[1]; cc.residual_out = w.resid[0];
+        cc.gamma = ly.gamma_post; cc.x = w.t_mixed;
         cc.nseg = 2;
-        cc.seg[0] = mega_seg(bf16_seg(ly.router, c.experts, w.router_logits));
-        cc.seg[1] = mega_seg(bf16_seg(ly.shared_expert_gate, 1, w.strength));
+        cc.seg[0] = mega_seg(bf16_seg(ly.router, c.experts, nullptr), w.t_router);
+        cc.seg[1] = mega_seg(bf16_seg(ly.shared_expert_gate, 1, nullptr), w.t_router + c.experts);
         if (!mega_finish_stream(cc, grid)) return QD_ERR_UNSUPPORTED;
         out[n++] = cc;
         // ---- D: routing; the shared expert's gate/up (its weights do not wait for the routing),
         //         then the routed gate/up pairs, all on the vector phase C built
         MegaPhase d = {};
         d.kind = MK_STREAM; d.width = H; d.prologue = PRO_NONE; d.layer = L; d.keep_x = 1; d.route = 1; d.uses_ids = 1;
-        d.router_logits = w.router_logits; d.ids_out = w.ids; d.weights_out = w.weights;
+        d.router_logits = w.t_router; d.ids_out = w.ids; d.weights_out = w.weights;
         d.nseg = c.topk + 1;
-        d.seg[0] = mega_seg(pair_seg(ly.shared_gate, ly.shared_up, c.intermediate, w.hidden + (size_t)c.topk * c.intermediate));
+        d.seg[0] = mega_seg(pair_seg(ly.shared_gate, ly.shared_up, c.intermediate, nullptr),
+                            w.t_hidden + (size_t)c.topk * c.intermediate);
         for (int s = 0; s < c.topk; ++s) {
-            StreamSeg sg = pair_seg(ly.experts_gate, ly.experts_up, c.intermediate, w.hidden + (size_t)s * c.intermediate);
+            StreamSeg sg = pair_seg(ly.experts_gate, ly.experts_up, c.intermediate, nullptr);
             sg.slot = s; sg.g_per_expert = ly.experts_global_per_expert;
             sg.w_stride = (long long)c.intermediate * (H / 2);
             sg.s_stride = (long long)c.intermediate * (H / 16);
-            d.seg[s + 1] = mega_seg(sg);
+            d.seg[s + 1] = mega_seg(sg, w.t_hidden + (size_t)s * c.intermediate);
         }
         if (!mega_finish_stream(d, grid)) return QD_ERR_UNSUPPORTED;
         // ---- E: down projections and combine.  Phase D carries the same weight pointers: its
         //         producer fetches the down-projection rows as soon as the routing is known.
         MegaPhase e = {};
         e.kind = MK_DOWN; e.layer = L; e.uses_ids = 1;
-        e.hidden = w.hidden; e.dw = (const uint8_t*)ly.experts_down.codes; e.ds = (const uint8_t*)ly.experts_down.scales;
+        e.hidden = w.t_hidden; e.dw = (const uint8_t*)ly.experts_down.codes; e.ds = (const uint8_t*)ly.experts_down.scales;
         e.dg = ly.experts_down.global; e.g_per_expert = ly.experts_global_per_expert;
         e.sw = (const uint8_t*)ly.shared_down.codes; e.ss = (const uint8_t*)ly.shared_down.scales; e.sg = ly.shared_down.global;
-        e.strength = w.strength; e.out = w.moe_out;
+        e.strength = w.t_router + c.experts; e.out = w.t_moe_out;
         d.dw = e.dw; d.ds = e.ds; d.sw = e.sw; d.ss = e.ss;
         out[n++] = d;
         out[n++] = e;
     }
-    // ---- head: residual add + final norm -> LM head rows with greedy argmax
+    // ---- head: residual add + final norm -> this rank's LM head rows with greedy argmax
     MegaPhase h = {};
     h.kind = MK_STREAM; h.width = H; h.prologue = PRO_ADD_NORM; h.layer = c.layers; h.argmax = 1;
-    h.gamma = c.final_gamma; h.x = w.moe_out; h.residual = w.resid[0]; h.residual_out = w.resid[1];
+    h.gamma = c.final_gamma; h.x = w.t_moe_out; h.x_prev_layer = 1;
     h.nseg = 1;
-    h.seg[0] = mega_seg(bf16_seg(c.lm_head, c.vocab, nullptr, EP_ARGMAX));
+    const int vocab_lo = c.vocab_hi ? c.vocab_lo : 0, vocab_hi = c.vocab_hi ? c.vocab_hi : c.vocab;
+    h.seg[0] = mega_seg(bf16_seg(c.lm_head, vocab_hi - vocab_lo, nullptr, EP_ARGMAX), nullptr);
+    h.row_lo = vocab_lo;
     if (!mega_finish_stream(h, grid)) return QD_ERR_UNSUPPORTED;
     out[n++] = h;
     return n == mega_phase_count(model) ? QD_OK : QD_ERR_ARG;
@@ -441,31 +461,50 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
 
 extern "C" int qd_decode_step_persistent(const qd_model* model, const qd_state* state, const long long* token,
                                          const int* position_dev, int position_host, void* workspace,
-                                         const void* program, void* logits_out, long long* next_token,
-                                         int flags, unsigned long long* trace, void* stream) {
+                                         const void* program, const qd_exchange* exchange, void* logits_out,
+                                         long long* next_token, int flags, unsigned long long* trace, void* stream) {
     QD_CHECK_ARG(model && state && token && workspace && program && next_token);
     QD_CHECK_ARG((flags & QD_FLAG_NO_LOGITS) || logits_out);
     QD_CHECK_ARG(position_dev || (position_host >= 0 && position_host < state->capacity));
     const qd_model_config& c = model->cfg;
     const int grid = stream_sm_count();
     if (!mega_shape_ok(c, grid)) return QD_ERR_UNSUPPORTED;
+    const bool sharded = c.expert_lo != 0 || c.expert_hi < c.experts || c.vocab_hi != 0;
+    QD_CHECK_ARG(!sharded || (exchange && exchange->world > 1));
     Workspace w = carve(c, (uint8_t*)workspace);
     MegaParams p = {};
     p.program = (const MegaPhase*)program;
-    p.nphases = mega_phase_count(model) - ((flags & QD_FLAG_NO_LOGITS) ? 1 : 0);
+    // Under expert parallelism the LM head always runs: its exchange of the ranks' best logits is
+    // also what keeps a rank from starting the next token while another still reads this one's
+    // contributions.
+    const bool skip_head = (flags & QD_FLAG_NO_LOGITS) && !(exchange && exchange->world > 1);
+    QD_CHECK_ARG(skip_head || logits_out);
+    p.nphases = mega_phase_count(model) - (skip_head ? 1 : 0);
     p.grid = grid;
     p.st = *state;
     p.token = token; p.pos_dev = position_dev; p.pos_host = position_host;
     p.embed = (const bf16*)c.embed; p.logits = (bf16*)logits_out; p.next_token = next_token;
     p.best_val = w.best_val; p.best_idx = w.best_idx; p.argmax_counter = w.argmax_counter;
-    p.bar = w.grid_bar; p.exit_count = w.grid_exit; p.status = w.status;
-    p.attn_partial = w.mega_attn_scratch; p.attn_counters = w.attn_counters; p.attn_splits = mega_attn_splits(c, grid);
+    p.epoch = w.epoch; p.exit_count = w.grid_exit; p.status = w.status;
+    p.attn_partial = w.t_attn; p.attn_splits = mega_attn_splits(c, grid);
     p.hk = c.key_heads; p.hv = c.value_heads; p.dk = c.key_dim; p.dv = c.value_dim;
     p.hq = c.q_heads; p.hkv = c.kv_heads; p.d = c.head_dim; p.rotary = c.rotary_dim;
     p.theta = c.rope_theta; p.eps = c.eps;
     p.conv_width = c.conv_width; p.topk = c.topk; p.experts = c.experts; p.hidden = c.hidden;
     p.channels = 2 * c.key_heads * c.key_dim + c.value_heads * c.value_dim;
     p.expert_lo = c.expert_lo; p.expert_hi = c.expert_hi;
+    p.rank = 0; p.world = 1;
+    if (exchange && exchange->world > 1) {
+        QD_CHECK_ARG(exchange->world <= kMegaMaxRanks && exchange->rank >= 0 && exchange->rank < exchange->world);
+        p.rank = exchange->rank; p.world = exchange->world;
+        for (int r = 0; r < p.world; ++r) {
+            QD_CHECK_ARG(exchange->peer_base[r] != 0 && (exchange->peer_base[r] & 15ull) == 0);
+            p.peer_base[r] = exchange->peer_base[r];
+        }
+        p.contrib_offset = 0;
+        p.argmax_offset = exchange_contrib_bytes(c);
+    }
+    p.wait_limit_us = g_wait_limit_us;
     p.trace = trace;
     return mega_launch(p, (cudaStream_t)stream);
 }

@@ -4,63 +4,56 @@
 // walks its range in tiles of whole rows.  A producer warp issues the bulk copies of a
 // tile (codes and block scales are contiguous row blocks in the reference layout, so no
 // repacking is needed) into a ring of shared-memory stages guarded by full/empty
-// mbarriers; eight consumer warps take rows of the tile round-robin.  Each lane owns a
-// fixed set of input positions, so its slice of the activation vector stays in
-// registers for the whole kernel as packed f16 (scaled by a power of two when it would
-// overflow f16; products of an E2M1 weight and a bf16 activation are exact in the
-// mixed-precision fma, sums are fp32).
+// mbarriers.  The sixteen consumer warps share every NVFP4 tile: each warp multiplies its
+// slice of the inputs of all rows of the tile on the tensor cores (rowmma.cuh), the partial
+// sums meet in shared memory and one warp per tile (rotating) finishes the rows.  bf16 rows
+// (router, LM head, small projections) go row by row, a warp each.
 //
 // Everything that does not depend on the previous launch (weights, norm gamma, conv taps
-// and history) is fetched before the programmatic dependency wait; the code that runs once
-// per block is kept short, because a block's first pass over cold code dominates the
-// latency of a launch that only has a few tiles of work.
+// and history) is fetched before the programmatic dependency wait.
 //
 // Arithmetic contract (reference: quickdraw/models/qwen.py:36-54 and the rounding points
-// of quickdraw/kernel/cute/matvec.py:62-77): fp32 accumulation, global scale applied to
-// the finished sum, one bf16 rounding; SwiGLU rounds gate, up, silu(gate) and the product.
+// of quickdraw/kernel/cute/matvec.py:62-77): weights dequantised exactly (code x block
+// scale in f16), fp32 accumulation, global scale applied to the finished sum, one bf16
+// rounding; SwiGLU rounds gate, up, silu(gate) and the product.
 #include "stream.cuh"
 #include "rowdot.cuh"
+#include "rowmma.cuh"
 
 namespace qd {
 
-int g_blocks_per_sm = 2;
-unsigned long long* g_trace = nullptr;   // profiling: timestamps of every launch
-int g_trace_launches = 0, g_trace_next = 0;
-constexpr int kTraceStride = 1024 * 16;
-
 namespace {
 
-
 template <int KC, bool WITH_BF16>
-__global__ void __launch_bounds__(kStreamThreads, KC == 2 ? 2 : 1)
+__global__ void __launch_bounds__(kStreamThreads, 1)
 stream_kernel(const __grid_constant__ StreamParams p) {
     constexpr int K = KC * 1024;
     constexpr int CW = kStreamConsumerWarps, CT = CW * 32, NS = kStreamStages;
-    constexpr int EPT = K / CT;                       // prologue elements per thread (8 or 16)
+    constexpr int EPT = K / CT;                       // prologue elements per thread (4 or 8)
+    constexpr int UNITS = K / 2048;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* stages = smem;
-    bf16* xs = reinterpret_cast<bf16*>(smem + NS * kStreamStageBytes);                // [K]
-    bf16* conv_taps_s = xs + K;                                                          // [rows][W]
+    bf16* xs = reinterpret_cast<bf16*>(smem + NS * kStreamStageBytes);                // [K] bf16
+    uint8_t* xf = reinterpret_cast<uint8_t*>(xs + K);                                   // [K] f16
+    float* partials = reinterpret_cast<float*>(xf + K * 2);                              // [NS][16 warps][32]
+    bf16* conv_taps_s = reinterpret_cast<bf16*>(partials + NS * kRowPartialFloats);      // [rows][W]
     bf16* conv_state_s = conv_taps_s + kStreamConvRows * kStreamConvWidth;               // [rows][W-1]
-    uint32_t* xf = reinterpret_cast<uint32_t*>(conv_state_s + kStreamConvRows * kStreamConvWidth);   // [K/2] f16 pairs
-    uint64_t* full = reinterpret_cast<uint64_t*>(xf + K / 2);
+    uint64_t* full = reinterpret_cast<uint64_t*>(conv_state_s + kStreamConvRows * kStreamConvWidth);
     uint64_t* empty = full + NS;
-    float* red = reinterpret_cast<float*>(empty + NS);      // [32]
-    int32_t* s_ids = reinterpret_cast<int32_t*>(red + 32);  // [32]
+    uint64_t* ready = empty + NS;                             // partial sums of a tile are complete
+    float* red = reinterpret_cast<float*>(ready + NS);       // [64]
+    int32_t* s_ids = reinterpret_cast<int32_t*>(red + 64);   // [64]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, CW); }
+        for (int s = 0; s < NS; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, CW); mbar_init(ready + s, CW); }
         mbar_fence_init();
     }
     __syncthreads();
     grid_launch_dependents();
-#define QD_TRACE(slot) do { if (p.trace && (tid == 0 || tid == CT)) p.trace[blockIdx.x * 16 + (tid ? 8 : 0) + (slot)] = global_timer_ns(); } while (0)
-    QD_TRACE(0);
 
-    // byte range of this block
-    // total cost = quota * gridDim.x + remainder, split on the host
+    // byte range of this block: total cost = quota * gridDim.x + remainder, split on the host
     const unsigned lo = blockIdx.x * p.quota + min(blockIdx.x, p.remainder);
     const unsigned hi = (blockIdx.x + 1) * p.quota + min(blockIdx.x + 1, p.remainder);
 
@@ -95,7 +88,6 @@ stream_kernel(const __grid_constant__ StreamParams p) {
                     const int st = it % NS;
                     if (!mbar_wait(empty + st, ((it / NS) & 1) ^ 1, p.status)) { ok = false; break; }
                     uint8_t* dst = stages + st * kStreamStageBytes;
-                    if (it == 0) QD_TRACE(1);
                     if (sg.kind == SEG_BF16) {
                         mbar_expect_tx(full + st, n * 2 * K);
                         bulk_load(dst, w + (long long)r0 * 2 * K, n * 2 * K, full + st);
@@ -113,7 +105,6 @@ stream_kernel(const __grid_constant__ StreamParams p) {
                     }
                 }
             }
-            QD_TRACE(2);
             // Do not leave while copies are in flight: wait for the consumers to drain the ring
             // (bounded); every stage is empty again once its last tile has been released.
             for (int back = 1; back <= NS && back <= it; ++back) {
@@ -153,7 +144,6 @@ stream_kernel(const __grid_constant__ StreamParams p) {
         }
     }
     grid_dependency_wait();
-    QD_TRACE(5);
     const bf16* xin = p.token ? p.embed + (size_t)(*p.token) * K : p.x;
     uint32_t m2 = 0u;      // largest |bf16| bit pattern this thread produced, per 16-bit half
     // 1. activation vector into shared memory (bf16); thread i owns elements [EPT*i, EPT*i + EPT)
@@ -161,13 +151,13 @@ stream_kernel(const __grid_constant__ StreamParams p) {
         float v[EPT];
         float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < EPT; j += 8) {
-            const uint4 xa = *reinterpret_cast<const uint4*>(xin + tid * EPT + j);
-            uint4 ra4 = make_uint4(0u, 0u, 0u, 0u);
-            if (p.residual) ra4 = *reinterpret_cast<const uint4*>(p.residual + tid * EPT + j);
-            const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w}, rw[4] = {ra4.x, ra4.y, ra4.z, ra4.w};
+        for (int j = 0; j < EPT; j += 4) {
+            const uint2 xa = *reinterpret_cast<const uint2*>(xin + tid * EPT + j);
+            uint2 ra2 = make_uint2(0u, 0u);
+            if (p.residual) ra2 = *reinterpret_cast<const uint2*>(p.residual + tid * EPT + j);
+            const uint32_t xw[2] = {xa.x, xa.y}, rw[2] = {ra2.x, ra2.y};
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < 2; ++q) {
                 v[j + 2 * q] = __uint_as_float(xw[q] << 16) + __uint_as_float(rw[q] << 16);
                 v[j + 2 * q + 1] = __uint_as_float(xw[q] & 0xffff0000u) + __uint_as_float(rw[q] & 0xffff0000u);
             }
@@ -177,16 +167,15 @@ stream_kernel(const __grid_constant__ StreamParams p) {
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
         named_barrier(1, CT);
-        QD_TRACE(6);
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < CW; ++w) tot += red[w];
         const float inv = rsqrtf(tot / (float)K + p.eps);
 #pragma unroll
-        for (int j = 0; j < EPT; j += 8) {
-            uint32_t nw[4], rw[4];
+        for (int j = 0; j < EPT; j += 4) {
+            uint32_t nw[2], rw[2];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < 2; ++q) {
                 const __nv_bfloat162 n2 = __floats2bfloat162_rn((v[j + 2 * q] * inv) * gam[j + 2 * q],
                                                                 (v[j + 2 * q + 1] * inv) * gam[j + 2 * q + 1]);
                 const __nv_bfloat162 r2 = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
@@ -194,11 +183,11 @@ stream_kernel(const __grid_constant__ StreamParams p) {
                 rw[q] = *reinterpret_cast<const uint32_t*>(&r2);
                 m2 = max_u16x2(m2, nw[q] & 0x7fff7fffu);
             }
-            const uint4 nv = make_uint4(nw[0], nw[1], nw[2], nw[3]);
-            *reinterpret_cast<uint4*>(xs + tid * EPT + j) = nv;
+            const uint2 nv = make_uint2(nw[0], nw[1]);
+            *reinterpret_cast<uint2*>(xs + tid * EPT + j) = nv;
             if (blockIdx.x == 0) {
-                if (p.x_out) *reinterpret_cast<uint4*>(p.x_out + tid * EPT + j) = nv;
-                *reinterpret_cast<uint4*>(p.residual_out + tid * EPT + j) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                if (p.x_out) *reinterpret_cast<uint2*>(p.x_out + tid * EPT + j) = nv;
+                *reinterpret_cast<uint2*>(p.residual_out + tid * EPT + j) = make_uint2(rw[0], rw[1]);
             }
         }
     } else if (p.prologue == PRO_GATED_NORM) {
@@ -232,60 +221,40 @@ stream_kernel(const __grid_constant__ StreamParams p) {
         uint32_t m = max(m2 & 0xffffu, m2 >> 16);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (lane == 0) reinterpret_cast<uint32_t*>(red)[8 + warp] = m;
+        if (lane == 0) reinterpret_cast<uint32_t*>(red)[32 + warp] = m;
     }
     if (p.ids_in && warp == 0 && lane < p.topk) s_ids[lane] = __ldcg(p.ids_in + lane);
-    QD_TRACE(7);
     named_barrier(1, CT);
-    QD_TRACE(1);
-    // 2. the vector as f16 pairs.  The largest bf16 magnitude (compared as a bit pattern)
-    //    decides a common power-of-two down-scale so that nothing overflows f16 (one in the
-    //    usual range); every thread converts its own slice into shared memory once, then each
-    //    lane fetches the slices of its input positions.
-    uint32_t xh[KC][16];
+    // 2. the vector as f16 in natural order.  The largest bf16 magnitude (compared as a bit
+    //    pattern) decides a common power-of-two down-scale so that nothing overflows f16 (one in
+    //    the usual range); every thread converts its own slice, then each lane fetches the
+    //    slices of its spans.
+    uint32_t xh[UNITS][16];
     float out_mult;
     {
         uint32_t m = 0u;
 #pragma unroll
-        for (int w = 0; w < CW; ++w) m = max(m, reinterpret_cast<const uint32_t*>(red)[8 + w]);
+        for (int w = 0; w < CW; ++w) m = max(m, reinterpret_cast<const uint32_t*>(red)[32 + w]);
         const int exponent = (int)(m >> 7) - 127;            // |x| < 2^(exponent + 1)
-        const int shift = exponent > 14 ? exponent - 14 : 0;
+        const int shift = (exponent > 14 && exponent < 128) ? exponent - 14 : 0;
         const float down = __uint_as_float((uint32_t)(127 - shift) << 23);
-        out_mult = __uint_as_float((uint32_t)(127 + min(shift, 127)) << 23);
+        out_mult = __uint_as_float((uint32_t)(127 + shift) << 23);
 #pragma unroll
-        for (int j = 0; j < EPT; j += 8) {
-            const uint4 v = *reinterpret_cast<const uint4*>(xs + tid * EPT + j);
-            uint4 h;
+        for (int j = 0; j < EPT; j += 4) {
+            const uint2 v = *reinterpret_cast<const uint2*>(xs + tid * EPT + j);
+            uint2 h;
             h.x = pack_f16x2(__uint_as_float(v.x << 16) * down, __uint_as_float(v.x & 0xffff0000u) * down);
             h.y = pack_f16x2(__uint_as_float(v.y << 16) * down, __uint_as_float(v.y & 0xffff0000u) * down);
-            h.z = pack_f16x2(__uint_as_float(v.z << 16) * down, __uint_as_float(v.z & 0xffff0000u) * down);
-            h.w = pack_f16x2(__uint_as_float(v.w << 16) * down, __uint_as_float(v.w & 0xffff0000u) * down);
-            *reinterpret_cast<uint4*>(xf + (tid * EPT + j) / 2) = h;
+            *reinterpret_cast<uint2*>(xf + (tid * EPT + j) * 2) = h;
         }
         named_barrier(1, CT);
-#pragma unroll
-        for (int c = 0; c < KC; ++c)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const uint4 v = lds128(reinterpret_cast<const uint8_t*>(xf) + (c * 32 + lane) * 64 + q * 16);
-                xh[c][q * 4 + 0] = v.x; xh[c][q * 4 + 1] = v.y; xh[c][q * 4 + 2] = v.z; xh[c][q * 4 + 3] = v.w;
-            }
+        load_x_fragments<UNITS>(xf, warp, lane, xh);
     }
-    constexpr int NB = WITH_BF16 ? K / 256 : 1;
-    uint32_t xb[NB * 4];
-    if (WITH_BF16) {
-#pragma unroll
-        for (int i = 0; i < NB; ++i) {
-            const uint4 v = lds128(reinterpret_cast<const uint8_t*>(xs) + (i * 32 + lane) * 16);
-            xb[i * 4 + 0] = v.x; xb[i * 4 + 1] = v.y; xb[i * 4 + 2] = v.z; xb[i * 4 + 3] = v.w;
-        }
-    }
-    QD_TRACE(2);
 
     // 3. tiles
     float best_val = -INFINITY;
     int best_idx = 0x7fffffff;
-    int it = 0;
+    int it = 0, turn = 0;
     unsigned seg_start = 0;
     bool ok = true;
 #pragma unroll 1
@@ -309,49 +278,67 @@ stream_kernel(const __grid_constant__ StreamParams p) {
             const int n = min(tile_rows, rb - r0);
             const int st = it % NS;
             if (!mbar_wait(full + st, (it / NS) & 1, p.status)) { ok = false; break; }
-            if (it == 0) QD_TRACE(3);
             const uint8_t* base = stages + st * kStreamStageBytes;
+            if (sg.kind == SEG_BF16) {
+                if (lane == 0) mbar_arrive(ready + st);      // keeps the phase of `ready` in step with the ring
+                if (WITH_BF16) {
+                    // rows rotate over the warps from tile to tile, so that consecutive tiles overlap
 #pragma unroll 1
-            for (int r = warp; r < n; r += CW) {
-                const int row = r0 + r;
-                float result;
-                if (sg.kind == SEG_BF16) {
-                    if (WITH_BF16) result = warp_sum(bf16_row_dot<NB>(base + (size_t)r * 2 * K, xb, lane));
-                    else result = 0.f;
-                } else {
-                    // one code path for plain rows and gate/up pairs: the pair's second half
-                    // sits tile_rows rows further in both the code and the scale block
-                    const int halves = sg.kind == SEG_FP4_PAIR ? 2 : 1;
-                    const uint8_t* sc = base + halves * tile_rows * (K / 2);
-                    float acc[2] = {0.f, 0.f};
-#pragma unroll 1
-                    for (int h = 0; h < halves; ++h)
-                        acc[h] = warp_sum(fp4_row_dot<KC>(base + (h * tile_rows + r) * (K / 2),
-                                                          sc + (h * tile_rows + r) * (K / 16), xh, lane));
-                    result = (acc[0] * out_mult) * g1;
-                    if (halves == 2) {
-                        const float up = round_bf16((acc[1] * out_mult) * g2);
+                    for (int r = (warp - turn) & (CW - 1); r < n; r += CW) {
+                        const int row = r0 + r;
+                        const float result = warp_sum(bf16_row_dot_smem<K / 256>(base + (size_t)r * 2 * K,
+                                                                                 reinterpret_cast<const uint8_t*>(xs), lane));
+                        const bf16 rounded = __float2bfloat16_rn(result);
+                        if (lane == 0) sg.y[row] = rounded;
+                        if (sg.epilogue == EP_ARGMAX) {
+                            const float v = __bfloat162float(rounded);
+                            if (v > best_val || (v == best_val && row < best_idx)) { best_val = v; best_idx = row; }
+                        }
+                    }
+                    turn = (turn + n) & (CW - 1);
+                }
+            } else {
+                const bool pair = sg.kind == SEG_FP4_PAIR;
+                const int groups = UNITS == 2 ? 1 : ((pair || n > 16) ? 2 : 1);
+                float* mine = partials + st * kRowPartialFloats;
+                tile_partials<K>(base, UNITS == 2 ? 16 : 32, groups, xh, warp, lane, mine + warp * kRowSlots);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ready + st);
+                if (warp == (it & (CW - 1))) {
+                    // this tile's finishing warp: lane = slot of the tile
+                    if (!mbar_wait(ready + st, (it / NS) & 1, p.status)) { ok = false; break; }
+                    const float total = tile_sum(mine, lane);
+                    float result = (total * out_mult) * g1;
+                    if (pair) {
+                        const float up_raw = __shfl_down_sync(0xffffffffu, total, 16);
+                        const float up = round_bf16((up_raw * out_mult) * g2);
                         result = round_bf16(silu_precise(round_bf16(result))) * up;
                     }
-                }
-                const bf16 rounded = __float2bfloat16_rn(result);
-                if (sg.epilogue == EP_CONV) {
-                    // depthwise causal conv for this channel (quickdraw/models/qwen.py:134-136):
-                    // lane t < W-1 holds history tap t, lane W-1 the new value.
-                    const int W = p.conv_width, local = row - conv_row0;
-                    float val = 0.f, tap = 0.f;
-                    if (lane < W) {
-                        tap = __bfloat162float(conv_taps_s[local * W + lane]);
-                        val = lane < W - 1 ? __bfloat162float(conv_state_s[local * (W - 1) + lane]) : __bfloat162float(rounded);
-                    }
-                    const float conv = warp_sum(lane < W ? round_bf16(val * tap) : 0.f);
-                    if (lane >= 1 && lane < W) p.conv_state[(size_t)row * (W - 1) + lane - 1] = __float2bfloat16_rn(val);
-                    if (lane == 0) sg.y[row] = __float2bfloat16_rn(silu_precise(conv));
-                } else {
-                    if (lane == 0) sg.y[row] = rounded;
-                    if (sg.epilogue == EP_ARGMAX) {
-                        const float v = __bfloat162float(rounded);
-                        if (v > best_val || (v == best_val && row < best_idx)) { best_val = v; best_idx = row; }
+                    const bf16 rounded = __float2bfloat16_rn(result);
+                    const bool valid = lane < n && (!pair || lane < 16);
+                    const int row = r0 + lane;
+                    if (valid) {
+                        if (sg.epilogue == EP_CONV) {
+                            // depthwise causal conv for this channel (quickdraw/models/qwen.py:134-136):
+                            // history taps then the new value; products rounded to bf16, fp32 sum in the
+                            // order of a two-step butterfly ((0 + 2) + (1 + 3) for four taps)
+                            const int W = p.conv_width, local = row - conv_row0;
+                            float prod[kStreamConvWidth];
+#pragma unroll
+                            for (int k = 0; k < kStreamConvWidth; ++k) {
+                                float val = 0.f, tap = 0.f;
+                                if (k < W) {
+                                    tap = __bfloat162float(conv_taps_s[local * W + k]);
+                                    val = k < W - 1 ? __bfloat162float(conv_state_s[local * (W - 1) + k]) : __bfloat162float(rounded);
+                                    if (k >= 1) p.conv_state[(size_t)row * (W - 1) + k - 1] = __float2bfloat16_rn(val);
+                                }
+                                prod[k] = k < W ? round_bf16(val * tap) : 0.f;
+                            }
+                            const float conv = (prod[0] + prod[2]) + (prod[1] + prod[3]);
+                            sg.y[row] = __float2bfloat16_rn(silu_precise(conv));
+                        } else {
+                            sg.y[row] = rounded;
+                        }
                     }
                 }
             }
@@ -377,15 +364,14 @@ stream_kernel(const __grid_constant__ StreamParams p) {
             }
         }
     }
-    QD_TRACE(4);
     // 4. greedy argmax over the EP_ARGMAX segment (ties: lowest index)
     if (p.best_val != nullptr) {
-        if (lane == 0) { red[warp] = best_val; s_ids[warp + 16] = best_idx; }   // s_ids[16..] is free
+        if (lane == 0) { red[warp] = best_val; s_ids[warp + 32] = best_idx; }
         named_barrier(1, CT);
         if (tid == 0) {
-            float bv = red[0]; int bi = s_ids[16];
+            float bv = red[0]; int bi = s_ids[32];
             for (int w = 1; w < CW; ++w) {
-                const float v = red[w]; const int ix = s_ids[16 + w];
+                const float v = red[w]; const int ix = s_ids[32 + w];
                 if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
             }
             p.best_val[blockIdx.x] = bv;
@@ -407,18 +393,18 @@ stream_kernel(const __grid_constant__ StreamParams p) {
     }
 }
 
-int g_sm_count = 0;
-
 template <int KC, bool WITH_BF16>
 int launch_variant(const StreamParams& p, int grid, cudaStream_t stream, bool pdl) {
     constexpr int K = KC * 1024;
-    const size_t smem = kStreamStages * kStreamStageBytes + K * 4 + 2 * kStreamConvRows * kStreamConvWidth * 2 +
-                        2 * kStreamStages * 8 + 32 * 4 * 2 + 64;
-    static bool configured = false;
-    if (!configured) {
+    const size_t smem = (size_t)kStreamStages * kStreamStageBytes + K * 4 + (size_t)kStreamStages * kRowPartialFloats * 4 +
+                        2 * kStreamConvRows * kStreamConvWidth * 2 + 3 * kStreamStages * 8 + 64 * 4 * 2 + 64;
+    static bool configured[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
+    if (!configured[dev]) {
         if (cudaFuncSetAttribute(stream_kernel<KC, WITH_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) return QD_ERR_LAUNCH;
-        configured = true;
+        configured[dev] = true;
     }
     return qd_launch(stream_kernel<KC, WITH_BF16>, dim3(grid), dim3(kStreamThreads), smem, stream, pdl, p);
 }
@@ -426,19 +412,19 @@ int launch_variant(const StreamParams& p, int grid, cudaStream_t stream, bool pd
 }  // namespace
 
 int stream_sm_count() {
-    if (g_sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sm_count <= 0) g_sm_count = 148;
+    static int counts[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (counts[dev] == 0) {
+        cudaDeviceGetAttribute(&counts[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (counts[dev] <= 0) counts[dev] = 148;
     }
-    return g_sm_count;
+    return counts[dev];
 }
 
 int stream_launch(const StreamParams& p_in, int grid, cudaStream_t stream, bool pdl) {
     StreamParams p = p_in;
-    if (g_trace && g_trace_next < g_trace_launches) p.trace = g_trace + (size_t)(g_trace_next++) * kTraceStride;
-    if (grid <= 0) grid = stream_sm_count() * (p.width == 2048 ? g_blocks_per_sm : 1);
+    if (grid <= 0) grid = stream_sm_count();
     if (grid > 1024) grid = 1024;
     {
         unsigned long long total = 0;
@@ -468,22 +454,6 @@ int stream_launch(const StreamParams& p_in, int grid, cudaStream_t stream, bool 
 }
 
 }  // namespace qd
-
-// Profiling aid: after this call every streaming launch writes per-block timestamps (ns) into
-// buffer + launch_index * 16384 (16 per block: 8 consumer slots, 8 producer slots), for the
-// next `launches` launches.  buffer NULL switches it off.
-extern "C" int qd_stream_trace(unsigned long long* buffer, int launches) {
-    qd::g_trace = buffer; qd::g_trace_launches = launches; qd::g_trace_next = 0;
-    return QD_OK;
-}
-
-// Tuning knob: blocks per SM the streaming kernel is launched with when the caller gives no
-// grid (2048-wide inputs; 1 or 2).
-extern "C" int qd_stream_blocks_per_sm(int n) {
-    if (n < 1 || n > 2) return QD_ERR_ARG;
-    qd::g_blocks_per_sm = n;
-    return QD_OK;
-}
 
 // ------------------------------------------------------------ op-table entry (ops.cu)
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -3,7 +3,8 @@
 // One launch multiplies ONE activation vector with a list of weight segments that share
 // its width: NVFP4 row blocks, NVFP4 gate/up pairs (SwiGLU fused) and bf16 row blocks, all
 // in the reference's checkpoint layout.  Weights travel global -> shared memory as 1-D
-// bulk copies (TMA) through a ring of stages; the activation vector lives in registers.
+// bulk copies (TMA) through a ring of stages; every consumer warp keeps its slice of the
+// activation vector in registers.
 // A prologue can build the vector (residual add + RMSNorm, or the DeltaNet per-head gated
 // norm), an epilogue can post-process each output row (short convolution, greedy argmax),
 // and the block that completes the router rows can do the top-k routing for the next launch.
@@ -23,10 +24,10 @@ struct Fp4Args {
 namespace qd {
 
 constexpr int kStreamMaxSeg = 10;
-constexpr int kStreamConsumerWarps = 8;
+constexpr int kStreamConsumerWarps = 16;   // they split the inputs of every NVFP4 row between them (rowmma.cuh)
 constexpr int kStreamThreads = (kStreamConsumerWarps + 1) * 32;   // + one producer warp
-constexpr int kStreamStages = 3;
-constexpr int kStreamStageBytes = 27648;   // 24 NVFP4 rows of 2048 inputs (codes + scales)
+constexpr int kStreamStages = 5;
+constexpr int kStreamStageBytes = 36864;   // 32 NVFP4 rows of 2048 inputs, or 16 of 4096 (codes + scales)
 constexpr int kStreamConvRows = 256;       // conv rows one block can stage
 constexpr int kStreamConvWidth = 4;        // widest short convolution the fused epilogue takes
 
@@ -74,7 +75,6 @@ struct StreamParams {
     float* best_val; int* best_idx; unsigned int* counter; long long* token_out;
     unsigned int* status;
     unsigned int quota, remainder;   // filled by stream_launch: total cost = quota * grid + remainder
-    unsigned long long* trace;   // optional: 16 timestamps (ns) per block, for profiling
 };
 
 // grid <= 0 picks the default number of blocks per SM.  Returns a QD_* code.

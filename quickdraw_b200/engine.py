@@ -9,7 +9,7 @@ convolution history, keeps every buffer address (a captured graph stays valid) a
 the KV cache alone (slots at or beyond the position are never read).
 
 Prompts run in chunks of ``prefill_chunk_size`` tokens through the sequence path
-(tensor-core products; the reference's default chunk is 128, here 512 because larger chunks
+(tensor-core products; the reference's default chunk is 128, here 2048 because larger chunks
 amortise the expert weights better) where the fused step applies, token by token otherwise.
 
 Backends: ``"b200"`` (default) runs the fused CUDA step where the checkpoint has the
@@ -93,6 +93,11 @@ class Engine:
                 self.step(self.ckpt, self._decode_input, self._device_position, scratch)
         torch.cuda.current_stream(dev).wait_stream(stream)
         self.graph = torch.cuda.CUDAGraph()
+        # an expert-parallel step leaves the greedy token on every rank without assembling the
+        # full logits: keep the all-gather of the vocabulary shards out of the replayed step
+        gathers = getattr(self.step, "gather_logits", None)
+        if gathers is not None:
+            self.step.gather_logits = False
         with torch.cuda.graph(self.graph, stream=stream):
             logits = self.step(self.ckpt, self._decode_input, self._device_position, self.state)
             if self.fused is not None:
@@ -100,6 +105,8 @@ class Engine:
             else:
                 torch.argmax(logits, out=self._decode_output)
             self._decode_logits = logits
+        if gathers is not None:
+            self.step.gather_logits = gathers
         del scratch
         self.reset()
 

@@ -45,7 +45,12 @@ class QdModelConfig(Structure):
                 ("key_heads", c_int), ("value_heads", c_int), ("key_dim", c_int), ("value_dim", c_int),
                 ("conv_width", c_int), ("experts", c_int), ("topk", c_int), ("intermediate", c_int),
                 ("eps", c_float), ("rope_theta", c_float), ("expert_lo", c_int), ("expert_hi", c_int),
+                ("vocab_lo", c_int), ("vocab_hi", c_int),
                 ("embed", c_void_p), ("final_gamma", c_void_p), ("lm_head", c_void_p)]
+
+
+class QdExchange(Structure):
+    _fields_ = [("rank", c_int), ("world", c_int), ("peer_base", ctypes.c_ulonglong * 8)]
 
 
 class QdState(Structure):
@@ -81,8 +86,12 @@ def supports(ckpt: Checkpoint) -> bool:
 
 
 class FusedStep:
+    """``expert_range`` / ``vocab_range``: the slice of the routed experts and of the LM-head
+    rows this checkpoint holds (expert parallel; banks and ``lm_head`` are local to the slice).
+    A sliced model runs through the persistent kernel only and needs ``set_exchange``."""
+
     def __init__(self, ckpt: Checkpoint, *, expert_range: tuple[int, int] | None = None,
-                 pdl: bool = True, persistent: bool | None = None):
+                 vocab_range: tuple[int, int] | None = None, pdl: bool = True, persistent: bool | None = None):
         assert supports(ckpt), "checkpoint shapes are outside the fused step; use kernels.forward_step"
         self.ckpt, self.pdl = ckpt, pdl
         c = ckpt.config
@@ -90,6 +99,9 @@ class FusedStep:
         self.device = ckpt.embed_tokens.device
         lo, hi = expert_range or (0, c.num_experts)
         self.expert_range = (lo, hi)
+        self.vocab_range = vocab_range
+        self.sliced = expert_range is not None or vocab_range is not None
+        self.exchange = None
         self._keep = []      # fp32 gammas and anything else the pointer table refers to
 
         def gamma(weight):
@@ -99,6 +111,8 @@ class FusedStep:
 
         assert ckpt.embed_tokens.dtype == BF16 and ckpt.lm_head.dtype == BF16
         assert ckpt.embed_tokens.is_contiguous() and ckpt.lm_head.is_contiguous()
+        assert ckpt.lm_head.shape[0] == ((vocab_range[1] - vocab_range[0]) if vocab_range else c.vocab_size), \
+            "lm_head must hold exactly the owned rows"
         cfg = QdModelConfig(
             hidden=c.hidden_size, layers=c.num_hidden_layers, vocab=c.vocab_size,
             q_heads=c.num_attention_heads, kv_heads=c.num_key_value_heads, head_dim=c.head_dim,
@@ -107,6 +121,7 @@ class FusedStep:
             value_dim=c.linear_value_head_dim, conv_width=c.linear_conv_kernel_dim,
             experts=c.num_experts, topk=c.num_experts_per_tok, intermediate=c.moe_intermediate_size,
             eps=c.rms_norm_eps, rope_theta=c.rope_theta, expert_lo=lo, expert_hi=hi,
+            vocab_lo=vocab_range[0] if vocab_range else 0, vocab_hi=vocab_range[1] if vocab_range else 0,
             embed=ckpt.embed_tokens.data_ptr(), final_gamma=gamma(ckpt.final_norm),
             lm_head=ckpt.lm_head.data_ptr())
         self.model = c_void_p()
@@ -141,17 +156,16 @@ class FusedStep:
             check(self.lib.qd_model_set_layer(self.model, layer.idx, byref(d)), "qd_model_set_layer")
         nbytes = self.lib.qd_decode_workspace_bytes(self.model)
         self.workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
-        self.routed_partial = torch.zeros(c.hidden_size, dtype=torch.float32, device=self.device)
         self.next_token = torch.zeros((), dtype=torch.long, device=self.device)
         self.launches_per_step = 6 * c.num_hidden_layers + 1
-        # One cooperative launch per token where the model is whole on this GPU; the
-        # launch-per-phase path stays for expert-parallel slices and as a cross-check.
+        # One cooperative launch per token; the launch-per-phase path stays as a cross-check
+        # (whole models only).
         self.program = None
         self.trace = None
         if persistent is None:
-            persistent = expert_range is None
+            persistent = True
+        assert persistent or not self.sliced, "a model slice runs through the persistent kernel only"
         if persistent:
-            assert expert_range is None, "the persistent kernel needs the whole model on one GPU"
             size = self.lib.qd_program_bytes(self.model)
             host = torch.zeros(size, dtype=torch.uint8)
             check(self.lib.qd_program_build(self.model, ptr(self.workspace), c_void_p(host.data_ptr()), size),
@@ -191,28 +205,33 @@ class FusedStep:
         flags = (FLAG_PDL if self.pdl else 0) | (0 if logits else FLAG_NO_LOGITS)
         stream = c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         if self.persistent:
+            assert self.exchange is not None or not self.sliced, "a model slice needs set_exchange() first"
+            if self.exchange is not None and out is None:
+                out = self._scratch_logits      # the LM head (and its exchange) runs on every token
             check(self.lib.qd_decode_step_persistent(
                 self.model, byref(st), ptr(token_id), pos_dev, pos_host, ptr(self.workspace),
-                ptr(self.program), ptr(out), ptr(self.next_token), flags, ptr(self.trace), stream),
+                ptr(self.program), byref(self.exchange) if self.exchange is not None else None, ptr(out),
+                ptr(self.next_token), flags, ptr(self.trace), stream),
                 "qd_decode_step_persistent")
-            return out
+            return out if logits else None
         check(self.lib.qd_decode_step(self.model, byref(st), ptr(token_id), pos_dev, pos_host,
                                       ptr(self.workspace), ptr(out) if logits else ptr(self.workspace),
                                       ptr(self.next_token), flags, stream), "qd_decode_step")
         return out
 
-    def run_layers(self, token_id, position, state, begin: int, end: int, logits_out=None):
-        """Expert-parallel slice: layers [begin, end), leaving the fp32 routed partial sum of
-        layer end-1 in ``self.routed_partial`` for the caller's all-reduce; with
-        begin == end == num_layers it finishes the last MoE block and runs the LM head."""
-        pos_dev, pos_host = self._position(position, state)
-        st = self._state(state)
-        flags = FLAG_PDL if self.pdl else 0
-        stream = c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        check(self.lib.qd_decode_layers(self.model, byref(st), ptr(token_id), pos_dev, pos_host,
-                                        ptr(self.workspace), ptr(self.routed_partial), begin, end,
-                                        ptr(logits_out), ptr(self.next_token), flags, stream),
-              "qd_decode_layers")
+    def exchange_bytes(self) -> int:
+        """Bytes of this rank's exchange area (expert parallel)."""
+        return int(self.lib.qd_exchange_bytes(self.model))
+
+    def set_exchange(self, rank: int, world: int, peer_addresses: list[int]) -> None:
+        """Expert parallel: ``peer_addresses[r]`` = address in this process of rank r's
+        zero-initialised exchange area (``exchange_bytes()`` bytes, peer-mapped)."""
+        assert 1 < world <= 8 and 0 <= rank < world and len(peer_addresses) == world
+        ex = QdExchange(rank=rank, world=world)
+        for r, address in enumerate(peer_addresses):
+            ex.peer_base[r] = int(address)
+        self.exchange = ex
+        self._scratch_logits = torch.empty(self.ckpt.config.vocab_size, dtype=BF16, device=self.device)
 
     def status(self) -> int:
         """Device status word (0 = clean; bit 0 = a bounded wait ran out)."""

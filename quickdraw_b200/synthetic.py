@@ -142,15 +142,20 @@ def make_layer(cfg: ModelConfig, src: Source, idx: int, expert_range=None) -> La
         attn=mixer, moe=make_moe(cfg, src, f"{tag}.moe", expert_range))
 
 
-def make_checkpoint(cfg: ModelConfig, seed: int = 0, device="cuda", expert_range=None) -> Checkpoint:
+def make_checkpoint(cfg: ModelConfig, seed: int = 0, device="cuda", expert_range=None,
+                    vocab_range=None) -> Checkpoint:
     """Whole model with a bf16 embedding and a bf16 LM head (about 23 GB at 48 layers);
-    with ``expert_range`` only that slice of every expert bank is kept."""
+    with ``expert_range`` only that slice of every expert bank is kept, with ``vocab_range``
+    only those rows of the LM head (the values are those of the whole model)."""
     src = Source(seed, device)
+    lm_head = src.normal("lm_head", cfg.vocab_size, cfg.hidden_size, std=0.02)
+    if vocab_range is not None:
+        lm_head = lm_head[vocab_range[0]:vocab_range[1]].clone()
     return Checkpoint(
         config=cfg,
         embed_tokens=src.normal("embed_tokens", cfg.vocab_size, cfg.hidden_size, std=0.02),
         final_norm=src.normal("final_norm", cfg.hidden_size, std=0.02),
-        lm_head=src.normal("lm_head", cfg.vocab_size, cfg.hidden_size, std=0.02),
+        lm_head=lm_head,
         layers=[make_layer(cfg, src, i, expert_range) for i in range(cfg.num_hidden_layers)])
 
 
