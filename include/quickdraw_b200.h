@@ -43,8 +43,12 @@ int qd_add_rms_norm(const void* x, const void* residual, const float* gamma, voi
 
 /* nvfp4_gemv(x, proj, routing_weight=None) — quickdraw/kernel/cute/matvec.py:146-149,
  * quickdraw/kernel/triton/matvec.py:65-81, arithmetic qwen.py:36-54.
- * routing_weight: device fp32 scalar or NULL.  force_generic != 0 selects the
- * shape-generic kernel even where the streaming kernel applies. */
+ * routing_weight: device fp32 scalar or NULL.  force_generic: 0 = the fastest kernel that
+ * covers the shape (2048 / 4096 inputs, rows a multiple of 8, non-negative block scales: the
+ * block-scaled FP4 tensor-core kernel, tcgen05 kind::mxf4nvf4, which reads codes and scales
+ * straight from this layout and takes the activations as eight exact 2-bit digit planes;
+ * else the streaming kernel), 2 = the streaming kernel (weights dequantised in registers,
+ * mma.sync), 1 = the shape-generic kernel. */
 int qd_nvfp4_gemv(const void* x, const void* codes, const void* scales, const float* global,
                   const float* routing_weight, void* y, int rows, int in_features,
                   int group_size, int force_generic, void* stream);

@@ -121,6 +121,7 @@ __global__ void nvfp4_generic_kernel(const Fp4Args a) {
 }
 
 int qd_stream_matvec_try(const Fp4Args& a, cudaStream_t stream);  // stream.cu; QD_ERR_UNSUPPORTED if not covered
+int qd_umma_matvec_try(const Fp4Args& a, cudaStream_t stream);    // umma.cu; QD_ERR_UNSUPPORTED if not covered
 
 static int nvfp4_dispatch(const Fp4Args& a, cudaStream_t stream, int force_generic) {
     QD_CHECK_ARG(a.x && a.codes && a.scales && a.global && a.y);
@@ -130,7 +131,13 @@ static int nvfp4_dispatch(const Fp4Args& a, cudaStream_t stream, int force_gener
     QD_CHECK_ARG(!a.up_codes || (a.up_scales && a.up_global));
     QD_CHECK_ARG(a.ids || (a.slots == 1 && !a.global_per_expert));
     if (a.rows == 0) return QD_OK;
-    if (!force_generic) {
+    // 0: the fastest kernel that covers the shape (FP4 tensor core, then the streaming kernel);
+    // 2: the streaming kernel (cross-check); any other value: the shape-generic kernel
+    if (force_generic == 0) {
+        const int rc = qd_umma_matvec_try(a, stream);
+        if (rc != QD_ERR_UNSUPPORTED) return rc;
+    }
+    if (force_generic == 0 || force_generic == 2) {
         const int rc = qd_stream_matvec_try(a, stream);
         if (rc != QD_ERR_UNSUPPORTED) return rc;
     }
