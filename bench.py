@@ -11,17 +11,22 @@ prompt is 512 uniform random token ids.  Rank 0 prints one JSON line:
              resident in HBM), max over ranks;
   e2e        the same through ``Engine.decode_step`` with the token and position coming
              from pinned host memory and the selected token read back every step;
-  roofline   the token-step kernel (one launch per token on one GPU): algorithmic bytes of a
-             token / CUDA-event time per launch against the measured HBM copy bandwidth;
-  matvec_roofline  the NVFP4 streaming matvec kernel alone, 128 units of the single-matvec
-             configuration ([1024, 2048]) per launch over two 151 MB matrices (more than L2);
-  cpu_baseline  the CPU oracle (a port of the reference's PyTorch path) timed on this
-             host on a bounded sample: one 4-layer group and the LM head, scaled to 48 layers.
+  roofline   the token-step kernel (one launch per token): algorithmic bytes of a token /
+             CUDA-event time per launch against the measured HBM copy bandwidth;
+  matvec_roofline  the NVFP4 matvec kernel alone (FP4 tensor core), 128 units of the
+             single-matvec configuration ([1024, 2048]) per launch over two 151 MB matrices;
+  kernels    per-kernel legs: the phases of the token step from the kernel's own timestamps
+             (MoE layer = router + gate/up + down phases, DeltaNet state update, attention,
+             LM head), and decode attention alone at contexts 8192 and 32768;
+  cpu_baseline  the reference's PyTorch path on this host's cores on a bounded sample: one
+             4-layer group and the LM head, scaled to 48 layers (extrapolated, said so).
 
-``--impl reference`` times only that CPU path and prints the same line shape.
-With N > 1 (torchrun) the routed experts are sharded across ranks (expert parallel);
-every rank runs the replicated parts, one fp32 all-reduce of the routed partial sum per
-layer goes over NCCL.
+``--impl reference`` times only that CPU path and prints the same line shape: the
+reference's own ``quickdraw.models.qwen`` when a checkout is importable (``baseline/_ref``),
+else the oracle port of it.
+With N > 1 (torchrun) the routed experts and the LM-head rows are sharded across ranks
+(expert parallel); the step stays one launch per token on every rank, the ranks exchange
+their routed contributions and best logits through peer memory inside that launch.
 """
 
 from __future__ import annotations
@@ -134,9 +139,23 @@ def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
-# ------------------------------------------------------------------ CPU oracle timing
+# ------------------------------------------------------------------ CPU baseline timing
+def reference_module():
+    """The reference's own step function when a checkout is importable, else None."""
+    for root in (ROOT / "baseline" / "_ref", Path("/root/reference")):
+        if (root / "quickdraw" / "models" / "qwen.py").exists():
+            sys.path.insert(0, str(root))
+            try:
+                from quickdraw.models import qwen      # noqa: PLC0415
+                return qwen
+            except Exception:                           # missing dependency of the checkout
+                sys.path.remove(str(root))
+    return None
+
+
 def cpu_sample(cfg, threads: int):
-    """Seconds per token of the CPU oracle, from one 4-layer group and the LM head."""
+    """Seconds per token of the CPU path, from one 4-layer group and the LM head.  Returns
+    (seconds per token, seconds actually timed, kind)."""
     from oracle import decode_oracle as O
     from quickdraw_b200 import synthetic
     from quickdraw_b200.state import DecodeState
@@ -147,17 +166,32 @@ def cpu_sample(cfg, threads: int):
     state = DecodeState.allocate(sub, 1024, "cpu")
     state.kv_k.normal_()
     state.kv_v.normal_()
+    ref = reference_module()
+    kind = "reference" if ref is not None else "port"
+    step_fn = O.forward_step
+    if ref is not None:
+        # the reference's own functions; its blocks take the projection as an argument, and this
+        # model's mixer projections are NVFP4 (the LM head, bf16 here, is timed below)
+        import functools
+        step_fn = functools.partial(
+            ref.forward_step,
+            attention=functools.partial(ref.full_attention_block, project_fp8=ref.nvfp4_gemv),
+            delta_net=functools.partial(ref.gated_delta_net_block, project_fp8=ref.nvfp4_gemv))
     with torch.inference_mode():
         x = torch.nn.functional.embedding(torch.tensor(7), ckpt.embed_tokens)
 
         def layers_once():
-            step = O.forward_step(ckpt, torch.tensor(7), PROMPT_LEN + 128, state, logits=False)
-            return step
+            return step_fn(ckpt, torch.tensor(7), PROMPT_LEN + 128, state, logits=False)
 
         def head_once():
             normed, _ = O.add_norm(x, torch.zeros_like(x), 1 + ckpt.final_norm.float(), sub.rms_norm_eps)
             return O.project(normed, ckpt.lm_head)
-        layers_once()
+        t_all = time.perf_counter()
+        try:
+            layers_once()
+        except Exception:                                # the checkout does not take these containers
+            kind, step_fn = "port", O.forward_step
+            layers_once()
         times = []
         for _ in range(2):
             t = time.perf_counter()
@@ -166,8 +200,9 @@ def cpu_sample(cfg, threads: int):
         t = time.perf_counter()
         head_once()
         head = time.perf_counter() - t
+        timed = time.perf_counter() - t_all
     per_group = sorted(times)[0]
-    return per_group * (cfg.num_hidden_layers / group) + head, per_group, head
+    return per_group * (cfg.num_hidden_layers / group) + head, timed, kind
 
 
 def run_reference(args):
@@ -178,10 +213,11 @@ def run_reference(args):
     cfg = synthetic.model_config()
     threads = len(os.sched_getaffinity(0))
     t0 = time.perf_counter()
-    samples = []
+    samples, timed, kind = [], 0.0, "port"
     for _ in range(max(1, min(args.steps, 3))):
-        per_token, per_group, head = cpu_sample(cfg, threads)
+        per_token, seconds, kind = cpu_sample(cfg, threads)
         samples.append(per_token)
+        timed += seconds
         if time.perf_counter() - t0 > 150:
             break
     per_token = sorted(samples)[len(samples) // 2]
@@ -194,7 +230,10 @@ def run_reference(args):
         "ms_per_step": per_token * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 activations, NVFP4 (E2M1 + E4M3 block scale) weights, fp32 accumulate",
         "data": "synthetic", "config": workload_config(cfg, world),
-        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        # a token is extrapolated from the sample: value = 1 / (group time x 12 + head time)
+        "extrapolated": True, "seconds_timed": timed,
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": kind, "sample": sample,
+                         "extrapolated": True},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -262,6 +301,73 @@ def prefill_gemm_roofline(device, tokens=8192, rows=8192, width=2048, reps=10):
     return 2.0 * tokens * rows * width / per_launch_s / 1e12, per_launch_s
 
 
+def attention_leg(cfg, device, context, peak, reps=24):
+    """Decode attention alone (the split-context kernel of the operator table) at one context
+    length: 16 query / 2 KV heads of 256, bf16 cache ~ N(0, 1); the caches rotate over more than
+    L2 holds.  Algorithmic bytes per launch: the K and V rows of the history, 2048 B per position."""
+    from quickdraw_b200._lib import call, lib, ptr, stream_of
+    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    per_cache = 2 * context * hkv * d * 2
+    n = max(2, -(-(300 << 20) // per_cache))
+    gen = torch.Generator(device=device).manual_seed(7)
+    k = torch.randn(n, context, hkv, d, generator=gen, device=device).to(BF16)
+    v = torch.randn(n, context, hkv, d, generator=gen, device=device).to(BF16)
+    qg = torch.randn(hq, 2 * d, generator=gen, device=device).to(BF16)
+    kn = torch.randn(hkv, d, generator=gen, device=device).to(BF16)
+    vn = torch.randn(hkv, d, generator=gen, device=device).to(BF16)
+    norm = torch.zeros(d, dtype=BF16, device=device)
+    out = torch.empty(hq * d, dtype=BF16, device=device)
+    splits = 32
+    scratch = torch.empty(lib().qd_attn_scratch_floats(hq, hkv, d, splits), dtype=torch.float32, device=device)
+    counters = torch.zeros(hkv, dtype=torch.int32, device=device)
+
+    def launch(i):
+        call("qd_attn_decode", ptr(qg), ptr(kn), ptr(vn), ptr(norm), ptr(norm), ptr(k[i % n]), ptr(v[i % n]), ptr(out),
+             ptr(scratch), ptr(counters), None, context - 1, context, hq, hkv, d, int(d * cfg.partial_rotary_factor),
+             float(cfg.rope_theta), float(cfg.rms_norm_eps), splits, 0, stream_of(out))
+    for i in range(n):
+        launch(i)
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        launch(i)
+    e1.record()
+    torch.cuda.synchronize(device)
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    nbytes = 2 * context * hkv * d * 2
+    return {"kernel": "attn_decode_kernel (split-context decode attention alone)", "context": context, "launch_us": us,
+            "bytes_per_launch": nbytes, "achieved": nbytes / us / 1e3, "peak": peak, "unit": "GB/s",
+            "frac": nbytes / us / 1e3 / peak, "caches_rotated": n}
+
+
+def kernel_legs(engine, ckpt, cfg, device, peak):
+    """Per-kernel legs: the phases of one token step from the persistent kernel's own timestamps
+    (time on the critical path per phase kind; algorithmic bytes / that time), and decode
+    attention alone at the baseline's contexts."""
+    from quickdraw_b200.trace import phase_summary, traced_step
+    position = engine.state.position
+    marks = traced_step(engine.fused, ckpt, engine.pending_token, position, engine.state)
+    phases = phase_summary(cfg, marks, position)
+
+    def leg(kinds, what):
+        us = sum(phases[k]["us"] for k in kinds if k in phases)
+        nbytes = sum(phases[k]["bytes"] for k in kinds if k in phases)
+        return {"what": what, "us": us, "bytes": nbytes, "achieved": nbytes / us / 1e3 if us else None, "peak": peak,
+                "unit": "GB/s", "frac": nbytes / us / 1e3 / peak if us else None}
+    return {
+        "source": "timestamps inside the token-step kernel, one traced step at position %d" % position,
+        "moe_layer": leg(["C", "D", "E"], "router + gate/up + down/combine phases of one layer (256 experts, top-8 + shared)"),
+        "deltanet_step": leg(["M"], "gated-DeltaNet recurrence of one layer: fp32 state [32,128,128] read + written"),
+        "deltanet_in_projections": leg(["A"], "qkv + z + a/b projections with the short convolution"),
+        "out_projection": leg(["B"], "gated norm + out projection (4096 inputs)"),
+        "attention_layer_core": leg(["Ma", "Na"], "split-context attention + merge of one layer at this position"),
+        "lm_head": leg(["H"], "final norm + bf16 LM head + greedy argmax"),
+        "attention_8192": attention_leg(cfg, device, 8192, peak),
+        "attention_32768": attention_leg(cfg, device, 32768, peak),
+    }
+
+
 def batch_decode_leg(ckpt, cfg, device, batch=32, context=8192, steps=8, warmup=2):
     """Small-batch decode with per-sequence state: `batch` sequences that each hold `context`
     tokens (caches filled with N(0,1) values, as the attention configuration of the baseline
@@ -299,11 +405,11 @@ def run_gpu(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
         from quickdraw_b200.expert_parallel import ExpertParallelEngine
-        engine = ExpertParallelEngine(cfg, seed=0, max_context=2048, device=device)
+        engine = ExpertParallelEngine(cfg, seed=0, max_context=args.context, device=device)
     else:
         from quickdraw_b200.engine import Engine
         ckpt = synthetic.make_checkpoint(cfg, seed=0, device=device)
-        engine = Engine(ckpt, max_context=2048, device=str(device))
+        engine = Engine(ckpt, max_context=args.context, device=str(device))
     gen = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=gen).tolist()
     torch.cuda.synchronize(device)
@@ -340,19 +446,18 @@ def run_gpu(args):
         e1.record()
         barrier()
     device_ms = e0.elapsed_time(e1)
-    # ---- end to end: host token and position in, selected token out, every step
+    # ---- end to end through the engine's own API: the pending token comes from pinned host
+    #      memory every step, the selected token is read back to the host every step
     token_host = torch.zeros((), dtype=torch.long).pin_memory()
-    pos_host = torch.zeros((), dtype=torch.int32).pin_memory()
     token_host.fill_(int(engine.pending_token.item()))
+    generated = []
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        pos_host.fill_(engine.state.position)
-        engine._decode_input.copy_(token_host, non_blocking=True)
-        engine._device_position.copy_(pos_host, non_blocking=True)
-        engine.graph.replay()
-        engine.state.position += 1
-        token_host.fill_(int(engine._decode_output.item()))
+        engine.pending_token = token_host.to(device, non_blocking=True)
+        token = int(engine.decode_step().item())
+        token_host.fill_(token)
+        generated.append(token)
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     times = torch.tensor([device_ms, e2e_ms], device=device)
@@ -361,6 +466,16 @@ def run_gpu(args):
     device_ms, e2e_ms = times.tolist()
     step_status = engine.fused.status() if getattr(engine, "fused", None) is not None else 0
     assert step_status == 0, f"the decode step reported status {step_status} (a bounded wait ran out)"
+    tokens_match = None
+    if world > 1:
+        # every rank must have generated the same tokens (they never talk about tokens: each
+        # rank derives them from the exchanged contributions and best logits)
+        mine = torch.tensor(generated[:64], dtype=torch.long, device=device)
+        lo, hi = mine.clone(), mine.clone()
+        torch.distributed.all_reduce(lo, op=torch.distributed.ReduceOp.MIN)
+        torch.distributed.all_reduce(hi, op=torch.distributed.ReduceOp.MAX)
+        tokens_match = bool(torch.equal(lo, hi))
+        engine.close()
     if rank != 0:
         return
     peak, peak_kind = measured_peaks()
@@ -370,14 +485,15 @@ def run_gpu(args):
         mv_gbs, mv_launch_s, mv_units = matvec_roofline(device)
     gemm_tflops, gemm_launch_s = prefill_gemm_roofline(device)
     tensor_peak, tensor_peak_kind = measured_tensor_peak()
-    batch_leg = None
+    batch_leg = legs = None
     if world == 1:
+        legs = kernel_legs(engine, ckpt, cfg, device, peak)
         batch_leg = batch_decode_leg(ckpt, cfg, device)
     position = args.prompt + args.warmup + args.steps // 2
     token_bytes = bytes_per_token(cfg, position)
     tok_s = args.steps / (device_ms * 1e-3)
     threads = len(os.sched_getaffinity(0))
-    per_token_cpu = float('nan') if args.no_cpu_baseline else cpu_sample(cfg, threads)[0]
+    per_token_cpu, cpu_seconds, cpu_kind = (float('nan'), 0.0, "port") if args.no_cpu_baseline else cpu_sample(cfg, threads)
     launches = getattr(engine, "launches_per_step", None) or engine.fused.launches_per_step
     line = {
         "metric": "batch-1 decode tok/s (36B-A3B NVFP4 MoE)", "value": tok_s, "unit": "tok/s",
@@ -387,8 +503,9 @@ def run_gpu(args):
         "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 activations, NVFP4 (E2M1 + E4M3 block scale) weights, fp32 accumulate",
         "data": "synthetic", "config": workload_config(cfg, world, args.prompt),
-        "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 12,
+        "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8},
+        "tokens_match": tokens_match,
         "gpu_launches": launches * args.steps,
         # outside the timed region: the prompt (chunks of up to 2048 tokens through the tensor-core
         # products on one GPU; token by token under expert parallelism) up to the first token
@@ -406,7 +523,7 @@ def run_gpu(args):
                      "peak_source": f"{peak_kind} copy bandwidth", "traffic": int(token_bytes * STEP_TRAFFIC_RATIO) if world == 1 else None,
                      "launch_us": device_ms / args.steps * 1e3, "bytes_per_launch": token_bytes,
                      "frac_of_8tbs": token_bytes * tok_s / 8e12 / world},
-        "matvec_roofline": {"kernel": "stream_kernel (NVFP4 matvec, %d x [1024,2048] per launch, 2 matrices alternating)" % mv_units,
+        "matvec_roofline": {"kernel": "nvfp4_umma_matvec_kernel (tcgen05 kind::mxf4nvf4, %d x [1024,2048] per launch, 2 matrices alternating)" % mv_units,
                             "achieved": mv_gbs, "peak": peak, "unit": "GB/s", "frac": mv_gbs / peak,
                             "launch_us": mv_launch_s * 1e6, "bytes_per_launch": mv_units * CONFIG1_BYTES},
         "prefill_gemm_roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_kernel (tcgen05, 8192 tokens x [8192, 2048])",
@@ -416,8 +533,10 @@ def run_gpu(args):
         # widening row: batch-32 decode with per-sequence KV and DeltaNet state (tok/s over all
         # sequences); not part of `value`
         "batch_decode": batch_leg,
-        "cpu_baseline": {"value": 1.0 / per_token_cpu, "unit": "tok/s", "cores": threads, "kind": "port",
-                         "sample": "one 4-layer group and the LM head at position 640, group time x12 + head time"},
+        "kernels": legs,
+        "cpu_baseline": {"value": 1.0 / per_token_cpu, "unit": "tok/s", "cores": threads, "kind": cpu_kind,
+                         "sample": "one 4-layer group and the LM head at position 640, group time x12 + head time",
+                         "extrapolated": True, "seconds_timed": cpu_seconds},
     }
     print(json.dumps(line), flush=True)
 
@@ -433,6 +552,7 @@ def main():
     ap.add_argument("--layers", type=int, default=48, help="model depth (48 in the headline workload; fewer for profiling)")
     ap.add_argument("--vocab", type=int, default=151936, help="vocabulary (151936 in the headline workload)")
     ap.add_argument("--matvec-rows", type=int, default=0, help="rows of the matvec roofline matrices (default 131072)")
+    ap.add_argument("--context", type=int, default=2048, help="KV-cache capacity of the decode engine")
     args = ap.parse_args()
     assert args.warmup >= 0 and args.steps > 0
     if args.impl == "reference":

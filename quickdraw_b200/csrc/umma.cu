@@ -5,8 +5,8 @@
 // instruction at all: the weight codes travel HBM -> shared memory as 2-D tiled TMA loads
 // straight from the checkpoint layout (128-byte swizzle, the layout the MMA reads), the
 // E4M3 block scales travel the same way and are moved into tensor memory by the four worker
-// warps, and the activation vector enters as eight E2M1 digit planes (umma.cuh).  Per 128
-// weight rows and 64 inputs one MMA of shape 128 x 8 x 64 does what 256 convert and 512
+// warps, and the activation vector enters as sixteen E2M1 digit planes (umma.cuh).  Per 128
+// weight rows and 64 inputs one MMA of shape 128 x 16 x 64 does what 256 convert and 512
 // multiply-add lane-operations did.
 //
 // Block = 4 worker warps (digit planes, scale factors into tensor memory, epilogue: one
@@ -54,9 +54,9 @@ constexpr int kStages = 8;                    // 128 rows x 128 bytes (256 input
 constexpr int kStageBytes = 128 * 128;
 constexpr int kMaxK = 4096;
 constexpr int kTmemCols = 512;
-constexpr int kColD = 0;                      // two accumulators of 8 columns
-constexpr int kColSfb = 16;                   // two columns per 64-input step (the first one is read)
-constexpr int kColSfa = 144;                  // K / 16 columns per buffer
+constexpr int kColD = 0;                      // two accumulators of 16 columns
+constexpr int kColSfb = 32;                   // two columns per 64-input step (the first one is read)
+constexpr int kColSfa = 160;                  // K / 16 columns per buffer
 
 struct UmmaParams {
     const bf16* x; const float* global; bf16* y;
@@ -76,8 +76,8 @@ nvfp4_umma_matvec_kernel(const __grid_constant__ UmmaParams p, const __grid_cons
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(umma_smem_raw) + 1023) & ~uintptr_t(1023));
     const int K = p.k, chunks = K / 256, halves = K / 2048;   // 256-input chunks; 128-byte groups of a scale row
     uint8_t* stages = smem;                                                   // [kStages][128 rows][128 B]
-    uint8_t* planes = stages + kStages * kStageBytes;                         // [chunks][8 rows][128 B]
-    uint8_t* scales = planes + (kMaxK / 256) * 1024;                          // [2][halves][128 rows][128 B]
+    uint8_t* planes = stages + kStages * kStageBytes;                         // [chunks][16 rows][128 B]
+    uint8_t* scales = planes + (kMaxK / 256) * kPlaneChunkBytes;                          // [2][halves][128 rows][128 B]
     Bars* bars = reinterpret_cast<Bars*>(scales + 2 * 2 * 128 * 128);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
     float* red = reinterpret_cast<float*>(tmem_slot + 4);                     // [8]
@@ -139,12 +139,12 @@ nvfp4_umma_matvec_kernel(const __grid_constant__ UmmaParams p, const __grid_cons
                 if (!mbar_wait(bars->sfa_ready + fb, (ti / nbuf) & 1, p.status)) break;
                 if (ti >= 2 && !mbar_wait(bars->d_free + db, ((ti >> 1) - 1) & 1, p.status)) break;
                 tc_fence_after();
-                const uint32_t d_col = tmem + kColD + db * 8;
+                const uint32_t d_col = tmem + kColD + db * 16;
                 for (int c = 0; c < chunks; ++c, ++it) {
                     const int st = it % kStages;
                     if (!mbar_wait(bars->full + st, (it / kStages) & 1, p.status)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(stages + st * kStageBytes), b_addr = smem_u32(planes + c * 1024);
+                    const uint32_t a_addr = smem_u32(stages + st * kStageBytes), b_addr = smem_u32(planes + c * kPlaneChunkBytes);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int step = c * 4 + j;       // 64-input step of the row
@@ -171,21 +171,16 @@ nvfp4_umma_matvec_kernel(const __grid_constant__ UmmaParams p, const __grid_cons
         named_barrier(1, kWorkers);
         m2 = max(max(reinterpret_cast<uint32_t*>(red)[0], reinterpret_cast<uint32_t*>(red)[1]),
                  max(reinterpret_cast<uint32_t*>(red)[2], reinterpret_cast<uint32_t*>(red)[3]));
-        const int E = plane_exponent(m2);
-        for (int i = tid; i < K / 8; i += kWorkers) {
-            const uint4 v = reinterpret_cast<const uint4*>(p.x)[i];
-            const uint32_t xw[4] = {v.x, v.y, v.z, v.w};
-            uint32_t pw[8];
-            plane_words(xw, E, pw);
-            // elements 8 i .. 8 i + 7: chunk (8 i) / 256, 16-byte piece ((8 i) % 256) / 32, 4 bytes at ((8 i) % 32) / 2
-            const int chunk = i >> 5, piece = (i >> 2) & 7, sub = (i & 3) * 4;
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<uint32_t*>(planes + chunk * 1024 + plane_piece_offset(q, piece) + sub) = pw[q];
+        const int E = plane_exponent_of(__uint_as_float(m2 << 16));      // the largest |bf16| of the vector
+        for (int i = tid; i < K / 4; i += kWorkers) {
+            const uint2 v = reinterpret_cast<const uint2*>(p.x)[i];
+            const float xv[4] = {__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                                 __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u)};
+            store_planes4(planes, 4 * i, xv, E);
         }
-        // lanes 0..7 of every 32-lane quarter of tensor memory: plane p's scale, one column per 64-input step
+        // lanes 0..15 of every 32-lane quarter of tensor memory: plane p's scale, per 64-input step
         for (int step = 0; step < K / 64; ++step)
-            tmem_store1(tmem + ((uint32_t)(warp * 32) << 16) + kColSfb + step * 2, plane_scale_word(lane & 7));
+            tmem_store1(tmem + ((uint32_t)(warp * 32) << 16) + kColSfb + step * 2, plane_scale_word(lane & 15));
         tmem_store_wait();
         tc_fence_before();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the plane bytes are read by the MMA (async proxy)
@@ -198,15 +193,13 @@ nvfp4_umma_matvec_kernel(const __grid_constant__ UmmaParams p, const __grid_cons
             const int db = ti & 1;
             if (!mbar_wait(bars->d_full + db, (ti >> 1) & 1, p.status)) return;
             tc_fence_after();
-            uint32_t v[8];
-            tmem_load8(tmem + ((uint32_t)(warp * 32) << 16) + kColD + db * 8, v);
+            uint32_t v[16];
+            tmem_load16(tmem + ((uint32_t)(warp * 32) << 16) + kColD + db * 16, v);
             tmem_load_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars->d_free + db);
-            float sum = 0.f;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) sum += __uint_as_float(v[q]);
+            const float sum = plane_sum(v);
             const int row = r_begin + ti * 128 + tid;
             if (row < r_end) p.y[row] = __float2bfloat16_rn(sum * out_scale);
         };
@@ -269,7 +262,7 @@ int qd_umma_matvec_try(const Fp4Args& a, cudaStream_t stream) {
     if (rc != QD_OK) return rc;
     rc = umma_make_map(&scale_map, a.scales, a.rows, a.in_features / 16, 128, p.box_rows);
     if (rc != QD_OK) return rc;
-    const size_t smem = (size_t)kStages * kStageBytes + (kMaxK / 256) * 1024 + 2 * 2 * 128 * 128 + sizeof(Bars) + 64 + 1024;
+    const size_t smem = (size_t)kStages * kStageBytes + (kMaxK / 256) * kPlaneChunkBytes + 2 * 2 * 128 * 128 + sizeof(Bars) + 64 + 1024;
     static bool configured[64];
     if (!configured[dev]) {
         if (cudaFuncSetAttribute(nvfp4_umma_matvec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

@@ -213,7 +213,7 @@ def route(logits: torch.Tensor, topk: int):
     return ids, weights
 
 
-def moe_block(w, x: torch.Tensor, *, config, expert_range=None, routed_partial=None) -> torch.Tensor:
+def moe_block(w, x: torch.Tensor, *, config) -> torch.Tensor:
     """Router, top-k NVFP4 experts, gated shared expert (quickdraw/models/qwen.py:168-193).
 
     Launch plan: router and shared-gate logits, routing, fused gate/up of the selected
@@ -232,7 +232,7 @@ def moe_block(w, x: torch.Tensor, *, config, expert_range=None, routed_partial=N
     out = torch.empty_like(x)
     per_expert = int(w.experts_down.weight_scale_2.numel() != 1)
     if inter == 512 and k <= 8 and w.shared_down.in_features == 512:
-        lo, hi = (0, config.num_experts) if expert_range is None else expert_range
+        lo, hi = 0, config.num_experts
         call("qd_moe_down_combine", ptr(hidden), ptr(ids), ptr(weights), ptr(w.experts_down.weight),
              ptr(w.experts_down.weight_scale), ptr(w.experts_down.weight_scale_2),
              ptr(w.shared_down.weight), ptr(w.shared_down.weight_scale), ptr(w.shared_down.weight_scale_2),

@@ -36,6 +36,40 @@ def phase_plan(cfg) -> list[tuple[str, int]]:
     return plan
 
 
+def traced_step(step, ckpt, token, position: int, state) -> np.ndarray:
+    """One step with the kernel's timestamp buffer attached: marks [phase][16][blocks], ns."""
+    cfg = ckpt.config
+    grid = torch.cuda.get_device_properties(step.device).multi_processor_count
+    plan = phase_plan(cfg)
+    step.trace = torch.zeros(len(plan) * SLOTS * grid, dtype=torch.int64, device=step.device)
+    try:
+        step(ckpt, token, position, state)
+        torch.cuda.synchronize(step.device)
+        return step.trace.cpu().numpy().reshape(len(plan), SLOTS, grid).astype(np.int64)
+    finally:
+        step.trace = None
+
+
+def phase_summary(cfg, marks: np.ndarray, position: int) -> dict[str, dict]:
+    """Per phase kind: mean time on the critical path (the last block's end minus the last
+    block's end of the phase before: these add up to the whole step), algorithmic bytes and
+    the bandwidth that makes."""
+    plan = phase_plan(cfg)
+    nbytes = phase_bytes(cfg, position)
+    spans: dict[str, list[int]] = {}
+    previous_end = int(marks[0, 0].min())
+    for index, (kind, _) in enumerate(plan):
+        end = int(marks[index, 1].max())
+        spans.setdefault(kind, []).append(end - previous_end)
+        previous_end = end
+    out = {}
+    for kind, values in spans.items():
+        us = float(np.mean(values)) / 1e3
+        out[kind] = {"count": len(values), "us": us, "bytes": int(nbytes.get(kind, 0)),
+                     "gbs": (nbytes[kind] / us / 1e3) if nbytes.get(kind) else None}
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--layers", type=int, default=8)
@@ -44,6 +78,7 @@ def main() -> None:
     ap.add_argument("--context", type=int, default=0, help="KV capacity (default: position + 64)")
     ap.add_argument("--interval", type=int, default=4, help="every interval-th layer is an attention layer")
     ap.add_argument("--show", default="", help="comma-separated layers to print phase by phase")
+    ap.add_argument("--dump", default="", help="save the raw marks [phase][16][blocks] to this .npy file")
     args = ap.parse_args()
     dev = "cuda"
     cfg = synthetic.model_config(num_layers=args.layers, vocab_size=args.vocab, interval=args.interval)
@@ -62,6 +97,8 @@ def main() -> None:
     torch.cuda.synchronize()
     assert step.status() == 0
     marks = step.trace.cpu().numpy().reshape(len(plan), SLOTS, grid).astype(np.int64)
+    if args.dump:
+        np.save(args.dump, marks)
     origin = marks[0, 0].min()
     marks = np.where(marks > 0, marks - origin, -1)
     show = {int(v) for v in args.show.split(",") if v}

@@ -250,6 +250,28 @@ def test_attention_full_width(K, cuda_device, position):
     assert torch.equal(v[position].cpu(), vc[position])
 
 
+@pytest.mark.parametrize("capacity,position", [(8192, 8191), (8192, 5000), (32768, 32767), (32768, 20011)])
+def test_attention_long_context(K, cuda_device, capacity, position):
+    """The attention configurations of the baseline: 16 query / 2 KV heads of 256, bf16 cache of
+    8192 and 32768 positions ~ N(0, 1), decode at the last position and at one in the middle;
+    against the oracle within 1e-2 relative L2 (fp32 softmax over the whole history on the CPU)."""
+    cfg = synthetic.model_config(num_layers=4)
+    src = synthetic.Source(9, cuda_device)
+    w = synthetic.make_attention(cfg, src)
+    k = src.normal("k", capacity, 2, 256)
+    v = src.normal("v", capacity, 2, 256)
+    x = src.normal("x", cfg.hidden_size)
+    kc, vc = k.cpu().clone(), v.cpu().clone()
+    got = K.full_attention_block(w, x, (k, v), position, config=cfg)
+    want = O.full_attention_block(to_device(w, "cpu"), x.cpu(), (kc, vc), position, config=cfg)
+    assert O.rel_l2(got.cpu(), want) < 1e-2
+    assert O.rel_l2(k[position].cpu(), kc[position]) < 1e-2
+    assert torch.equal(v[position].cpu(), vc[position])
+    untouched = [position - 1, 0] if position else []
+    for t in untouched:
+        assert torch.equal(k[t].cpu(), kc[t]) and torch.equal(v[t].cpu(), vc[t])
+
+
 # ----------------------------------------------------- the reference's saved fixtures
 def test_reference_fixtures_through_the_operator_table(K, cuda_device, reference_fixtures):
     """The 15 saved block/step fixtures (tiny shapes, FP8 mixer projections) through
