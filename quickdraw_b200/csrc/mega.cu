@@ -13,14 +13,9 @@
 // block: every block adds and normalises the whole hidden vector itself (it needs the whole
 // vector for its rows anyway) and keeps the bf16 residual in registers.
 //
-// NVFP4 rows run on the block-scaled FP4 tensor core (tcgen05.mma kind::mxf4nvf4, umma.cuh):
-// a block's rows of a phase form ONE tile of up to 128 rows, loaded as 8-row TMA boxes straight
-// from the checkpoint layout; the activation vector enters as eight exact digit planes, the
-// block scales go to tensor memory, one thread issues the MMAs, four warps read the
-// accumulator back (a thread per row) and apply the row epilogue.  The MoE down projections
-// (512 inputs, nine experts per row) stay on the warp-level tensor-core instruction
-// (rowmma.cuh); attention is a split-context flash decode on the same instruction (all query
-// heads of a KV head share each key/value tile).
+// NVFP4 rows run on the warp-level tensor-core instruction with the inputs split over the
+// sixteen warps (rowmma.cuh); attention is a split-context flash decode on the same
+// instruction (all query heads of a KV head share each key/value tile).
 //
 // Arithmetic follows the separate kernels (stream.cu, gdn.cu, moe.cu, attention.cu): same
 // rounding points (reference: quickdraw/models/qwen.py:66-241), fp32 sums in a different order.
@@ -35,104 +30,64 @@
 namespace qd {
 namespace {
 
-constexpr int CW = kMegaConsumerWarps, CT = kMegaConsumers;
-constexpr int NA = kMegaCodeStages, NB = kMegaRowStages;
+constexpr int CW = kMegaConsumerWarps, CT = kMegaConsumers, NS = kMegaStages;
 constexpr int kDownWidth = 512;
 constexpr int kDownRowBytes = kDownWidth / 2 + kDownWidth / 16;   // 288
 constexpr int kDownSlots = 9;                                     // top-8 + shared
 constexpr int kDownSlotBytes = kMegaDownRows * kDownRowBytes;     // codes [16][256] then scales [16][32]
 constexpr int kDownBufBytes = kDownSlots * kDownSlotBytes;        // down-projection rows of one layer
 constexpr int kAttnRow = 528;                  // a 512-byte cache row of one KV head, padded against bank conflicts
-constexpr int kAttnStagePos = 16;              // positions per ring stage: K rows, then V rows
+constexpr int kAttnStagePos = 32;              // positions per ring stage: K rows, then V rows
 constexpr int kAttnQRow = 576;                 // a query head in shared memory (bf16 [256], padded)
 constexpr int kAttnWarps = 8;                  // warps that walk the context (a chunk of sixteen positions each)
 constexpr int kAttnStride = 258;               // partial of one head: 256 sums, running max, denominator
 constexpr int kAttnMergeFloats = 8 * 256 + 16; // one warp's partial in shared memory during the block merge
 constexpr int kScratchBytes = kDownBufBytes > 4 * kAttnMergeFloats * 4 ? kDownBufBytes : 4 * kAttnMergeFloats * 4;
-constexpr int kScaleBufBytes = 96 * 128;       // block scales of one tile: [halves][rows][128 B], 128-byte swizzle
-constexpr int kBf16TileRows = kMegaRowStageBytes / 4096;          // bf16 rows of 2048 inputs per ring stage
-// tensor memory columns: two accumulators of sixteen, the plane scales (two columns per 64-input
-// step, written once), the block scales of the current tile (four columns per step)
-constexpr int kTmemCols = 512, kColD = 0, kColSfb = 32, kColSfa = 160;
-
-struct Box {              // one 8-row TMA box of a tile
-    short seg, m;         // segment of the phase; first row inside the 128-row tile
-    int row;              // first row inside the segment
-    int src;              // first row inside the tensor map (bank entries: expert * rows + row)
-    int map;              // tensor map of the codes (scales: map + 1)
-};
 
 struct Smem {
-    uint8_t* codes;        // [NA][96 rows][128 B] NVFP4 code tiles (TMA, 128-byte swizzle)
-    uint8_t* rows;         // [NB][kMegaRowStageBytes] bf16 rows / KV-cache rows
-    bf16* xs;              // 6 KB: activation vector, bf16 [2048] (attention: query heads, new key and value)
-    uint8_t* planes;       // [16][16 rows][128 B] digit planes of the activation vector (B operand); down: hidden vectors, f16
-    uint8_t* scales;       // [2][kScaleBufBytes] block scales of the current and the next tile
+    uint8_t* stages;
+    bf16* xs;              // [4096] activation vector, bf16   (attention: query heads, new key; down: hidden vectors)
+    uint8_t* xf;           // [4096] the same as f16, natural order
     uint8_t* scratch;      // down-projection rows / DeltaNet vectors / attention merge
-    float* partials;       // down phase: partial sums, contributions
+    float* partials;       // [NS][16 warps][32] partial row sums of the tile in each stage
     bf16* conv_taps; bf16* conv_state;
     MegaPhase* cph;        // [2] consumer copies of the current and the next phase
     MegaPhase* pph;        // producer copy
-    MegaPhase* mph;        // MMA warp copy
-    Box* boxes;            // [3][kMegaMaxBoxes]: consumers, producer, MMA warp
-    uint64_t* code_full; uint64_t* code_empty;     // [NA]
-    uint64_t* row_full; uint64_t* row_empty;       // [NB]
-    uint64_t* wide_full; uint64_t* wide_empty;     // [NA + NB]: the LM head streams through both rings' memory
-    uint64_t* sc_full; uint64_t* sc_free; uint64_t* d_full; uint64_t* d_free;   // [2] each
-    uint64_t* sfa_ready; uint64_t* b_ready;        // one completion per tile
-    float* red;            // [160]: reductions, per-segment global scales, the scale of the kept vector
+    uint64_t* full; uint64_t* empty; uint64_t* ready;
+    float* red;            // [160]: reductions, per-segment global scales, the f16 scale of the kept vector
     int32_t* ids; float* weights;      // [8] routing of the current layer
     uint64_t* ids_bar;                 // completes once per layer, when the routing is in ids / weights
     uint64_t* down_bar;                // completes once per layer, when the down-projection rows have landed
     volatile int* abort;
-    uint32_t* tmem_slot;
     float* rope;           // [2][128] bf16-rounded cos / sin of the step's position, per rotary frequency
 };
 
-extern __shared__ __align__(1024) uint8_t mega_smem[];
+extern __shared__ __align__(128) uint8_t mega_smem[];
 
-constexpr size_t kSmemBytes = 1024 + (size_t)NA * kMegaCodeStageBytes + (size_t)NB * kMegaRowStageBytes + 6144 + 16 * kPlaneChunkBytes +
-                              2 * kScaleBufBytes + (size_t)kScratchBytes + 3072 + 2 * kMegaConvRows * kStreamConvWidth * 2 +
-                              4 * sizeof(MegaPhase) + 3 * kMegaMaxBoxes * sizeof(Box) + (4 * NA + 4 * NB + 10) * 8 + 160 * 4 +
-                              8 * 4 + 8 * 4 + 16 + 16 + 16 + 2 * 128 * 4;
+constexpr size_t kSmemBytes = (size_t)NS * kStreamStageBytes + 4096 * 2 + 4096 * 2 + (size_t)kScratchBytes +
+                              (size_t)NS * kRowPartialFloats * 4 + 2 * kMegaConvRows * kStreamConvWidth * 2 +
+                              3 * sizeof(MegaPhase) + 3 * NS * 8 + 160 * 4 + 8 * 4 + 8 * 4 + 16 + 16 + 2 * 128 * 4;
 
-static_assert(kSmemBytes <= 232448, "the block's shared memory must fit the opt-in limit of one SM");
-
-QD_DEVINL Smem carve_smem(uint8_t* raw) {
-    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+QD_DEVINL Smem carve_smem(uint8_t* base) {
     Smem s;
-    s.codes = base;                                   base += (size_t)NA * kMegaCodeStageBytes;
-    s.planes = base;                                  base += 16 * kPlaneChunkBytes;
-    s.scales = base;                                  base += 2 * kScaleBufBytes;
-    s.rows = base;                                    base += (size_t)NB * kMegaRowStageBytes;
-    s.xs = reinterpret_cast<bf16*>(base);             base += 6144;
+    s.stages = base;                                  base += (size_t)NS * kStreamStageBytes;
+    s.xs = reinterpret_cast<bf16*>(base);             base += 4096 * 2;
+    s.xf = base;                                      base += 4096 * 2;
     s.scratch = base;                                 base += (size_t)kScratchBytes;
-    s.partials = reinterpret_cast<float*>(base);      base += 3072;
+    s.partials = reinterpret_cast<float*>(base);      base += (size_t)NS * kRowPartialFloats * 4;
     s.conv_taps = reinterpret_cast<bf16*>(base);      base += kMegaConvRows * kStreamConvWidth * 2;
     s.conv_state = reinterpret_cast<bf16*>(base);     base += kMegaConvRows * kStreamConvWidth * 2;
     s.cph = reinterpret_cast<MegaPhase*>(base);       base += 2 * sizeof(MegaPhase);
     s.pph = reinterpret_cast<MegaPhase*>(base);       base += sizeof(MegaPhase);
-    s.mph = reinterpret_cast<MegaPhase*>(base);       base += sizeof(MegaPhase);
-    s.boxes = reinterpret_cast<Box*>(base);           base += 3 * kMegaMaxBoxes * sizeof(Box);
-    s.code_full = reinterpret_cast<uint64_t*>(base);  base += NA * 8;
-    s.code_empty = reinterpret_cast<uint64_t*>(base); base += NA * 8;
-    s.row_full = reinterpret_cast<uint64_t*>(base);   base += NB * 8;
-    s.row_empty = reinterpret_cast<uint64_t*>(base);  base += NB * 8;
-    s.wide_full = reinterpret_cast<uint64_t*>(base);  base += (NA + NB) * 8;
-    s.wide_empty = reinterpret_cast<uint64_t*>(base); base += (NA + NB) * 8;
-    s.sc_full = reinterpret_cast<uint64_t*>(base);    base += 2 * 8;
-    s.sc_free = reinterpret_cast<uint64_t*>(base);    base += 2 * 8;
-    s.d_full = reinterpret_cast<uint64_t*>(base);     base += 2 * 8;
-    s.d_free = reinterpret_cast<uint64_t*>(base);     base += 2 * 8;
-    s.sfa_ready = reinterpret_cast<uint64_t*>(base);  base += 8;
-    s.b_ready = reinterpret_cast<uint64_t*>(base);    base += 8;
+    s.full = reinterpret_cast<uint64_t*>(base);       base += NS * 8;
+    s.empty = reinterpret_cast<uint64_t*>(base);      base += NS * 8;
+    s.ready = reinterpret_cast<uint64_t*>(base);      base += NS * 8;
     s.red = reinterpret_cast<float*>(base);           base += 160 * 4;
     s.ids = reinterpret_cast<int32_t*>(base);         base += 8 * 4;
     s.weights = reinterpret_cast<float*>(base);       base += 8 * 4;
     s.ids_bar = reinterpret_cast<uint64_t*>(base);    base += 8;
     s.down_bar = reinterpret_cast<uint64_t*>(base);   base += 8;
     s.abort = reinterpret_cast<volatile int*>(base);  base += 16;
-    s.tmem_slot = reinterpret_cast<uint32_t*>(base);  base += 16;
     s.rope = reinterpret_cast<float*>(base);          base += 2 * 128 * 4;
     return s;
 }
@@ -331,161 +286,65 @@ QD_DEVINL void trace_mark(const MegaParams& mp, int pi, int slot) {
     if (mp.trace) mp.trace[((size_t)pi * kTraceSlots + slot) * gridDim.x + blockIdx.x] = global_timer_ns();
 }
 
-// A bounded mbarrier wait that gives up at once when the block has already given up.
-QD_DEVINL bool bar_wait(const Smem& S, uint64_t* bar, uint32_t parity, unsigned int* status) {
-    if (*S.abort) return false;
-    const bool ok = mbar_wait(bar, parity, status);
-    if (!ok) *S.abort = 1;
-    return ok;
-}
-
-// ================================================================= partition of a phase
-// The NVFP4 rows of a streaming phase are counted in units of 8 rows (one TMA box; 8 gate rows
-// + 8 up rows for a pair segment), over the segments this rank owns; the units are cut evenly
-// over the blocks, and so are the bf16 rows.  Every thread can work out any box of its
-// block's tile by itself, so nobody waits for a table.
-QD_DEVINL void even_range(int n, int& a, int& b) {
-    a = (int)((long long)n * blockIdx.x / gridDim.x);
-    b = (int)((long long)n * (blockIdx.x + 1) / gridDim.x);
-}
-QD_DEVINL bool seg_owned(const MegaParams& mp, const MegaSeg& sg, const int32_t* ids, int& expert) {
-    expert = 0;
-    if (sg.slot < 0) return true;
-    const int e = ids[sg.slot];
-    expert = e - mp.expert_lo;
-    return e >= mp.expert_lo && e < mp.expert_hi;
-}
-// Box `index` of this block's tile (out is left alone when index is not a box).  Plain rows fill
-// the tile from row 0; of pair segments the gate boxes come first and the up boxes follow them
-// (the up row of tile row m is row m + rows / 2).  ids: the routing (needed when the phase has
-// bank segments).  Returns the number of boxes (rows = 8 x boxes), or -1 if the tile does not fit.
-QD_DEVINL int tile_box(const MegaParams& mp, const MegaPhase& ph, const int32_t* ids, int index, Box& out) {
-    int total = 0, expert;
-#pragma unroll 1
-    for (int i = 0; i < ph.nseg; ++i) {
-        const MegaSeg& sg = ph.seg[i];
-        if (sg.kind != SEG_BF16 && seg_owned(mp, sg, ids, expert)) total += sg.rows >> 3;
-    }
-    int u0, u1;
-    even_range(total, u0, u1);
-    const int units = u1 - u0;
-    const bool pair = ph.seg[0].kind == SEG_FP4_PAIR;
-    const int nb = pair ? 2 * units : units;
-    if (nb > kMegaMaxBoxes || (ph.width > 2048 && nb > kMegaMaxBoxes / 2)) return -1;
-    if (index < 0 || index >= nb) return nb;
-    const bool upper = pair && index >= units;
-    int g = u0 + (upper ? index - units : index), base = 0;
-#pragma unroll 1
-    for (int i = 0; i < ph.nseg; ++i) {
-        const MegaSeg& sg = ph.seg[i];
-        if (sg.kind == SEG_BF16 || !seg_owned(mp, sg, ids, expert)) continue;
-        const int n = sg.rows >> 3;
-        if (g < base + n) {
-            const int u = g - base;
-            out = Box{(short)i, (short)(8 * index), 8 * u, expert * sg.rows + 8 * u, upper ? sg.map2 : sg.map};
-            break;
-        }
-        base += n;
-    }
-    return nb;
-}
-// The block's share [r0, r1) of the phase's bf16 rows, counted over the bf16 segments in order.
-QD_DEVINL void bf16_rows_range(const MegaPhase& ph, int& r0, int& r1) {
-    int total = 0;
-#pragma unroll 1
-    for (int i = 0; i < ph.nseg; ++i) if (ph.seg[i].kind == SEG_BF16) total += ph.seg[i].rows;
-    even_range(total, r0, r1);
-}
-// 256-input chunks of a tile that share one stage of the code ring.
-QD_DEVINL int chunks_per_stage(int boxes, int chunks) { return max(1, min(chunks, kMegaMaxBoxes / boxes)); }
-
-// The row ring of a phase: the LM head (the last phase, nothing but bf16 rows) streams through
-// the memory of both rings, 4 rows per stage; every other phase through the small row ring.
-constexpr int kWideCodeStages = NA * kMegaCodeStageBytes / (kBf16TileRows * 4096);   // bf16 tiles that fit the code ring
-constexpr int NW = kWideCodeStages + NB;
-struct RowRing { int stages; uint64_t* full; uint64_t* empty; };
-QD_DEVINL RowRing row_ring(const Smem& S, bool wide) {
-    RowRing r;
-    r.stages = wide ? NW : NB;
-    r.full = wide ? S.wide_full : S.row_full;
-    r.empty = wide ? S.wide_empty : S.row_empty;
-    return r;
-}
-QD_DEVINL uint8_t* row_stage(const Smem& S, bool wide, int st) {
-    if (wide && st < kWideCodeStages) return S.codes + (size_t)st * (kBf16TileRows * 4096);
-    return S.rows + (size_t)(wide ? st - kWideCodeStages : st) * kMegaRowStageBytes;
+// Slots 9..14 (thread 160 of the streaming phases): cycles since the phase was entered.
+QD_DEVINL void trace_cycles(const MegaParams& mp, int pi, int slot, long long c0) {
+    if (mp.trace) mp.trace[((size_t)pi * kTraceSlots + slot) * gridDim.x + blockIdx.x] = (unsigned long long)(clock64() - c0);
 }
 
 // =========================================================================== producer
-// bf16 rows of a streaming phase: tiles of kBf16TileRows rows through the row ring.
-QD_DEVINL bool produce_rows(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it, bool wide) {
-    const int K = ph.width;
-    const RowRing ring = row_ring(S, wide);
-    int b0, b1, seg_first = 0;
-    bf16_rows_range(ph, b0, b1);
+template <int K>
+QD_DEVINL bool produce_stream(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it) {
+    bool ids_ready = false;
+    const unsigned lo = blockIdx.x * ph.quota + min(blockIdx.x, ph.remainder);
+    const unsigned hi = (blockIdx.x + 1) * ph.quota + min(blockIdx.x + 1, ph.remainder);
+    unsigned seg_start = 0;
 #pragma unroll 1
     for (int i = 0; i < ph.nseg; ++i) {
         const MegaSeg& sg = ph.seg[i];
-        if (sg.kind != SEG_BF16) continue;
-        const int ra = max(b0, seg_first) - seg_first, rb = min(b1, seg_first + sg.rows) - seg_first;
-        seg_first += sg.rows;
+        int ra, rb;
+        seg_range<K>(seg_start, sg.kind, sg.rows, lo, hi, ra, rb);
+        seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
         if (ra >= rb) continue;
+        int expert = 0;
+        if (sg.slot >= 0) {
+            // The routing of layer L completes phase L of the barrier; the producer is never
+            // more than one layer away from it, so the parity names the phase.  Segments in
+            // front of the first routed one have been issued by now.
+            if (!ids_ready && !mbar_wait(S.ids_bar, ph.layer & 1, mp.status)) return false;
+            ids_ready = true;
+            expert = S.ids[sg.slot];
+            if (expert < mp.expert_lo || expert >= mp.expert_hi) continue;
+            expert -= mp.expert_lo;
+        }
+        const int tile_rows = seg_tile_rows<K>(sg.kind);
+        const uint8_t* w = sg.w + (long long)expert * sg.w_stride;
+        const uint8_t* s = sg.s ? sg.s + (long long)expert * sg.s_stride : nullptr;
+        const uint8_t* w2 = sg.w2 ? sg.w2 + (long long)expert * sg.w_stride : nullptr;
+        const uint8_t* s2 = sg.s2 ? sg.s2 + (long long)expert * sg.s_stride : nullptr;
 #pragma unroll 1
-        for (int r0 = ra; r0 < rb; r0 += kBf16TileRows, ++it) {
-            const int n = min(kBf16TileRows, rb - r0);
-            const int st = it % ring.stages;
-            if (!bar_wait(S, ring.empty + st, ((it / ring.stages) & 1) ^ 1, mp.status)) return false;
-            mbar_expect_tx(ring.full + st, n * 2 * K);
-            bulk_load(row_stage(S, wide, st), sg.w + (long long)r0 * 2 * K, n * 2 * K, ring.full + st);
+        for (int r0 = ra; r0 < rb; r0 += tile_rows, ++it) {
+            const int n = min(tile_rows, rb - r0);
+            const int st = it % NS;
+            if (*S.abort || !mbar_wait(S.empty + st, ((it / NS) & 1) ^ 1, mp.status)) return false;
+            uint8_t* dst = S.stages + (size_t)st * kStreamStageBytes;
+            uint64_t* full = S.full + st;
+            if (sg.kind == SEG_BF16) {
+                mbar_expect_tx(full, n * 2 * K);
+                bulk_load(dst, w + (long long)r0 * 2 * K, n * 2 * K, full);
+            } else if (sg.kind == SEG_FP4) {
+                mbar_expect_tx(full, n * (K / 2 + K / 16));
+                bulk_load(dst, w + (long long)r0 * (K / 2), n * (K / 2), full);
+                bulk_load(dst + tile_rows * (K / 2), s + (long long)r0 * (K / 16), n * (K / 16), full);
+            } else {
+                mbar_expect_tx(full, 2 * n * (K / 2 + K / 16));
+                uint8_t* sc = dst + 2 * tile_rows * (K / 2);
+                bulk_load(dst, w + (long long)r0 * (K / 2), n * (K / 2), full);
+                bulk_load(dst + tile_rows * (K / 2), w2 + (long long)r0 * (K / 2), n * (K / 2), full);
+                bulk_load(sc, s + (long long)r0 * (K / 16), n * (K / 16), full);
+                bulk_load(sc + tile_rows * (K / 16), s2 + (long long)r0 * (K / 16), n * (K / 16), full);
+            }
         }
     }
-    return true;
-}
-
-// The NVFP4 tile of a streaming phase: block scales into the scale buffer of this tile, then
-// the codes 256 inputs at a time through the code ring; lane b issues box b.
-QD_DEVINL bool produce_tile(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it, int& tile, int lane) {
-    const int K = ph.width, chunks = K / 256, halves = K / 2048;
-    int ok = 1;
-    if (ph.uses_ids) {
-        if (lane == 0) ok = bar_wait(S, S.ids_bar, ph.layer & 1, mp.status) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) return false;
-    }
-    Box box = {};
-    const int nb = tile_box(mp, ph, S.ids, lane, box);
-    if (nb < 0) return false;
-    if (nb == 0) return true;
-    const int buf = tile & 1;
-    const int sc_rows = halves == 1 ? 96 : 48;       // rows of a half in the scale buffer
-    if (lane == 0) {
-        if (tile >= 2) ok = bar_wait(S, S.sc_free + buf, ((tile >> 1) - 1) & 1, mp.status) ? 1 : 0;
-        if (ok) mbar_expect_tx(S.sc_full + buf, (uint32_t)nb * 8 * (K / 16));
-    }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (!ok) return false;
-    const CUtensorMap* code_map = mp.maps + box.map;
-    if (lane < nb) {
-        for (int h = 0; h < halves; ++h)
-            tma_load_2d(S.scales + (size_t)buf * kScaleBufBytes + (h * sc_rows + box.m) * 128, code_map + 1, h * 128, box.src,
-                        S.sc_full + buf);
-    }
-    const int cps = chunks_per_stage(nb, chunks);
-#pragma unroll 1
-    for (int c0 = 0; c0 < chunks; c0 += cps, ++it) {
-        const int st = it % NA, here = min(cps, chunks - c0);
-        if (lane == 0) {
-            ok = bar_wait(S, S.code_empty + st, ((it / NA) & 1) ^ 1, mp.status) ? 1 : 0;
-            if (ok) mbar_expect_tx(S.code_full + st, (uint32_t)(nb * here) * 1024);
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) return false;
-        if (lane < nb)
-            for (int j = 0; j < here; ++j)
-                tma_load_2d(S.codes + (size_t)st * kMegaCodeStageBytes + (j * nb * 8 + box.m) * 128, code_map, (c0 + j) * 128, box.src,
-                            S.code_full + st);
-    }
-    ++tile;
     return true;
 }
 
@@ -520,18 +379,18 @@ QD_DEVINL void produce_down(const MegaParams& mp, const MegaPhase& ph, const Sme
 }
 
 struct AttnSplit { int active, per; };
-// How the context [0, T) is cut into splits of `per` positions (a multiple of 32), one block
-// per (KV head, split).
+// How the context [0, T) is cut into splits of `per` positions (a multiple of the stage), one
+// block per (KV head, split).
 QD_DEVINL AttnSplit attn_split(int T, int max_splits) {
     AttnSplit a;
     const int per = (T + max_splits - 1) / max_splits;
-    a.per = max(32, (per + 31) / 32 * 32);
+    a.per = max(kAttnStagePos, (per + kAttnStagePos - 1) / kAttnStagePos * kAttnStagePos);
     a.active = (T + a.per - 1) / a.per;
     return a;
 }
 
-// Attention: the cache rows of this block's context split, sixteen positions per ring stage
-// (K rows then V rows, one 512-byte bulk copy each, issued by sixteen lanes).  The row of the
+// Attention: the cache rows of this block's context split, thirty-two positions per ring stage
+// (K rows then V rows, one 512-byte bulk copy each, issued by the whole warp).  The row of the
 // step's own position is not in the cache yet; the consumers fill it in.  Rows of earlier
 // positions were written by earlier steps, so these copies may run ahead like any weight.
 QD_DEVINL bool produce_attn(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it, int lane) {
@@ -546,143 +405,67 @@ QD_DEVINL bool produce_attn(const MegaParams& mp, const MegaPhase& ph, const Sme
     const uint8_t* v_cache = reinterpret_cast<const uint8_t*>(reinterpret_cast<const bf16*>(mp.st.kv_v) + (size_t)ph.state_index * layer_elems);
 #pragma unroll 1
     for (int c0 = t0; c0 < t1; c0 += kAttnStagePos, ++it) {
-        const int st = it % NB;
+        const int st = it % NS;
         int ok = 1;
-        if (lane == 0) ok = (!*S.abort && bar_wait(S, S.row_empty + st, ((it / NB) & 1) ^ 1, mp.status)) ? 1 : 0;
+        if (lane == 0) ok = (!*S.abort && mbar_wait(S.empty + st, ((it / NS) & 1) ^ 1, mp.status)) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) return false;
-        uint8_t* dst = S.rows + (size_t)st * kMegaRowStageBytes;
+        uint8_t* dst = S.stages + (size_t)st * kStreamStageBytes;
         const int t = c0 + lane;
-        const bool copy = lane < kAttnStagePos && t < t1 && t != position;
+        const bool copy = t < t1 && t != position;
         const int rows = __popc(__ballot_sync(0xffffffffu, copy));
-        if (lane == 0) mbar_expect_tx(S.row_full + st, (uint32_t)rows * 2 * 512);
+        if (lane == 0) mbar_expect_tx(S.full + st, (uint32_t)rows * 2 * 512);
         __syncwarp();
         if (copy) {
             const size_t off = ((size_t)t * mp.hkv + kvh) * 512;
-            bulk_load(dst + lane * kAttnRow, k_cache + off, 512, S.row_full + st);
-            bulk_load(dst + (kAttnStagePos + lane) * kAttnRow, v_cache + off, 512, S.row_full + st);
+            bulk_load(dst + lane * kAttnRow, k_cache + off, 512, S.full + st);
+            bulk_load(dst + (kAttnStagePos + lane) * kAttnRow, v_cache + off, 512, S.full + st);
         }
     }
     return true;
 }
 
-QD_DEVINL void load_phase(MegaPhase* dst, const MegaPhase* src, int lane) {
-    const uint4* s4 = reinterpret_cast<const uint4*>(src);
-    uint4* d4 = reinterpret_cast<uint4*>(dst);
-    for (int i = lane; i < (int)(sizeof(MegaPhase) / 16); i += 32) d4[i] = __ldg(s4 + i);
-    __syncwarp();
-}
-
 QD_DEVINL void producer(const MegaParams& mp, const Smem& S, int lane) {
-    int code_it = 0, row_it = 0, wide_it = 0, tile = 0;
+    int it = 0;
     bool ok = true;
 #pragma unroll 1
     for (int pi = 0; pi < mp.nphases && ok; ++pi) {
-        load_phase(S.pph, mp.program + pi, lane);
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(mp.program + pi);
+            uint4* dst = reinterpret_cast<uint4*>(S.pph);
+            for (int i = lane; i < (int)(sizeof(MegaPhase) / 16); i += 32) dst[i] = __ldg(src + i);
+        }
+        __syncwarp();
         const MegaPhase& ph = *S.pph;
         if (ph.kind == MK_STREAM) {
-            if (lane == 0) trace_mark(mp, pi, 4);
-            ok = produce_tile(mp, ph, S, code_it, tile, lane);
             if (lane == 0) {
-                if (ok && ph.argmax) {
-                    // the LM head takes over the memory of both rings: everything in them must have been used
-                    for (int back = 1; back <= NA && back <= code_it && ok; ++back)
-                        ok = bar_wait(S, S.code_empty + ((code_it - back) % NA), ((code_it - back) / NA) & 1, mp.status);
-                    for (int back = 1; back <= NB && back <= row_it && ok; ++back)
-                        ok = bar_wait(S, S.row_empty + ((row_it - back) % NB), ((row_it - back) / NB) & 1, mp.status);
-                    if (ok) ok = produce_rows(mp, ph, S, wide_it, true);
-                } else if (ok) {
-                    ok = produce_rows(mp, ph, S, row_it, false);
-                }
+                trace_mark(mp, pi, 4);
+                if (ph.width == 2048) ok = produce_stream<2048>(mp, ph, S, it);
+                else ok = produce_stream<4096>(mp, ph, S, it);
                 // the routed gate/up phase also carries the down-projection pointers of its layer
                 if (ok && ph.route) {
-                    ok = bar_wait(S, S.ids_bar, ph.layer & 1, mp.status);
+                    ok = mbar_wait(S.ids_bar, ph.layer & 1, mp.status);
                     if (ok) produce_down(mp, ph, S);
                 }
                 trace_mark(mp, pi, 5);
+                if (!ok) *S.abort = 1;
             }
-            row_it = __shfl_sync(0xffffffffu, row_it, 0);
+            it = __shfl_sync(0xffffffffu, it, 0);
         } else if (ph.kind == MK_ATTN) {
-            ok = produce_attn(mp, ph, S, row_it, lane);
+            ok = produce_attn(mp, ph, S, it, lane);
+            if (!ok && lane == 0) *S.abort = 1;
         }
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        if (!ok && lane == 0) *S.abort = 1;
         __syncwarp();
     }
     // Never leave with copies in flight: the full barrier of a stage completes when its bytes
     // have landed, whether or not the consumers have used them (bounded).
     if (lane == 0) {
-        for (int back = 1; back <= NA && back <= code_it; ++back) {
-            const int j = code_it - back;
-            mbar_wait(S.code_full + (j % NA), (j / NA) & 1, nullptr);
-        }
-        for (int back = 1; back <= NB && back <= row_it; ++back) {
-            const int j = row_it - back;
-            mbar_wait(S.row_full + (j % NB), (j / NB) & 1, nullptr);
-        }
-        for (int back = 1; back <= NW && back <= wide_it; ++back) {
-            const int j = wide_it - back;
-            mbar_wait(S.wide_full + (j % NW), (j / NW) & 1, nullptr);
+        for (int back = 1; back <= NS && back <= it; ++back) {
+            const int j = it - back;
+            mbar_wait(S.full + (j % NS), (j / NS) & 1, nullptr);
         }
     }
-}
-
-// ============================================================================ MMA warp
-// One thread issues the MMAs of every tile: K / 64 steps of 128 x 8 x 64 on the code stages as
-// they land, block scales and digit planes as the workers leave them.  A stage goes back to
-// the producer when its four MMAs have read it; the accumulator is handed to the workers
-// when the last MMA of the tile is done.
-QD_DEVINL bool mma_tile(const MegaParams& mp, const MegaPhase& ph, const Smem& S, uint32_t tmem, Box* boxes, int& it, int& tile, int pi) {
-    if (ph.uses_ids && !bar_wait(S, S.ids_bar, ph.layer & 1, mp.status)) return false;
-    Box unused;
-    const int nb = tile_box(mp, ph, S.ids, -1, unused);
-    if (nb < 0) return false;
-    if (nb == 0) return true;
-    const int K = ph.width, chunks = K / 256, db = tile & 1;
-    if (!bar_wait(S, S.sfa_ready, tile & 1, mp.status) || !bar_wait(S, S.b_ready, tile & 1, mp.status)) return false;
-    if (tile >= 2 && !bar_wait(S, S.d_free + db, ((tile >> 1) - 1) & 1, mp.status)) return false;
-    trace_mark(mp, pi, 9);
-    tc_fence_after();
-    const uint32_t d_col = tmem + kColD + db * 16;
-    const int cps = chunks_per_stage(nb, chunks);
-#pragma unroll 1
-    for (int c0 = 0; c0 < chunks; c0 += cps, ++it) {
-        const int st = it % NA, here = min(cps, chunks - c0);
-        if (!bar_wait(S, S.code_full + st, (it / NA) & 1, mp.status)) return false;
-        if (c0 == 0) trace_mark(mp, pi, 10);
-        tc_fence_after();
-#pragma unroll 1
-        for (int jc = 0; jc < here; ++jc) {
-            const int c = c0 + jc;
-            const uint32_t a_lo = desc_lo_sw128(smem_u32(S.codes + (size_t)st * kMegaCodeStageBytes + jc * nb * 1024));
-            const uint32_t b_lo = desc_lo_sw128(smem_u32(S.planes + c * kPlaneChunkBytes));
-            const uint32_t sfa = tmem + kColSfa + c * 16, sfb = tmem + kColSfb + c * 8;
-#pragma unroll
-            for (int j = 0; j < 4; ++j)      // a 64-input step: 32 bytes further in both operands
-                umma_nvfp4_lo(d_col, a_lo + 2 * j, b_lo + 2 * j, kUmmaNvfp4Desc, sfa + j * 4, sfb + j * 2, (c | j) ? 1u : 0u);
-        }
-        umma_commit(S.code_empty + st);
-    }
-    umma_commit(S.d_full + db);
-    trace_mark(mp, pi, 11);
-    ++tile;
-    return true;
-}
-
-QD_DEVINL void mma_warp(const MegaParams& mp, const Smem& S, uint32_t tmem, int lane) {
-    int it = 0, tile = 0;
-    bool ok = true;
-    Box* boxes = S.boxes + 2 * kMegaMaxBoxes;
-#pragma unroll 1
-    for (int pi = 0; pi < mp.nphases && ok; ++pi) {
-        load_phase(S.mph, mp.program + pi, lane);
-        const MegaPhase& ph = *S.mph;
-        if (ph.kind == MK_STREAM && lane == 0) ok = mma_tile(mp, ph, S, tmem, boxes, it, tile, pi);
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        __syncwarp();
-    }
-    if (!ok && lane == 0) *S.abort = 1;
-    __syncwarp();
 }
 
 // Top-k routing by one warp; the lane holds the logits of experts 8 lane .. 8 lane + 7: fp32
@@ -736,57 +519,28 @@ QD_DEVINL void f16_scale(float top, float& down, float& up) {
 }
 
 // ========================================================================== consumers
-// One streaming phase.  The block's NVFP4 rows are one tile on the FP4 tensor core: the four
-// worker warps move its block scales into tensor memory, everybody builds the activation
-// vector (bf16 for the bf16 rows, digit planes for the MMAs), the MMA warp multiplies, the
-// workers read the accumulator back, a thread per row.  bf16 rows go warp by warp from the
-// row ring.  res: this thread's four elements of the bf16 residual stream.
-QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, const Wait& wt, int pi, int& row_it,
-                            int& tile, float (&res)[4], uint32_t tag_base, uint32_t tmem) {
-    const int K = ph.width;
+// One streaming phase: activation vector -> shared memory and registers, then this block's
+// rows of the ring.  res: this thread's four elements of the bf16 residual stream.
+template <int KC>
+QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Smem& S, const Wait& wt, int pi, int& it,
+                            float (&res)[4], uint32_t tag_base) {
+    constexpr int K = KC * 1024;
+    constexpr int UNITS = K / 2048;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     bf16* xs = S.xs;
+    uint8_t* xf = S.xf;
     float* red = S.red;
-    int* redi = reinterpret_cast<int*>(S.red);
     const uint32_t tag = tag_base | (uint32_t)(ph.layer + 1);
     const uint32_t tag_x = ph.x_prev_layer ? tag - 1u : tag;
-    const bool worker = warp < 4;
-    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);     // this warp's quarter of tensor memory
+    const unsigned lo = blockIdx.x * ph.quota + min(blockIdx.x, ph.remainder);
+    const unsigned hi = (blockIdx.x + 1) * ph.quota + min(blockIdx.x + 1, ph.remainder);
 
-    // ---- static inputs first (nothing another block writes): norm gamma, global scales of the
-    //      segments, conv taps and history of this block's channels, the tile's boxes
-    float4 gam = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (K == 2048 && ph.prologue == PRO_ADD_NORM) gam = *reinterpret_cast<const float4*>(ph.gamma + tid * 4);
-    // (every global load of the prologue is issued before anything waits: their trips to L2 overlap
-    // each other and the staging of the block scales)
-    float seg_scale = 1.f;
-    if (tid < 2 * kMegaMaxSeg) {
-        const MegaSeg& sg = ph.seg[tid >> 1];
-        const float* src = (tid & 1) ? sg.g2 : sg.g;
-        if ((tid >> 1) < ph.nseg && src && !sg.g_per_expert) seg_scale = *src;
-    }
-    int conv_row0 = 0, conv_n = 0;
-    bf16* conv_state = nullptr;
-    unsigned short tap_reg = 0, state_reg = 0;
-    if (ph.conv_taps) {
-        // the conv segment is the first one: this block's units of it are the first boxes of its tile
-        const int W = mp.conv_width;
-        conv_state = reinterpret_cast<bf16*>(mp.st.conv_state) + (size_t)ph.state_index * mp.channels * (W - 1);
-        int total = 0;
-#pragma unroll 1
-        for (int i = 0; i < ph.nseg; ++i) if (ph.seg[i].kind != SEG_BF16) total += ph.seg[i].rows >> 3;
-        int u0, u1;
-        even_range(total, u0, u1);
-        const int conv_units = ph.seg[0].rows >> 3;
-        conv_row0 = 8 * min(u0, conv_units);
-        conv_n = min(8 * (min(u1, conv_units) - min(u0, conv_units)), kMegaConvRows);
-        if (tid < conv_n * W) tap_reg = reinterpret_cast<const unsigned short*>(ph.conv_taps)[(size_t)conv_row0 * W + tid];
-        if (tid < conv_n * (W - 1)) state_reg = reinterpret_cast<const unsigned short*>(conv_state)[(size_t)conv_row0 * (W - 1) + tid];
-    }
-    // first read of the activation words this thread will need (they are checked, and read again
-    // if they have not arrived, after the block scales are staged)
+    // ---- first read of the activation words this thread needs: their trip to L2 overlaps the
+    //      static loads below; they are checked, and read again if they have not arrived, later
+    const long long c0 = clock64();
+    const bool probe = tid == 160;
     uint4 xin[4];
-    const int mode = ph.keep_x ? 0 : (K == 2048 ? (ph.from_token ? 0 : 1) : (ph.prologue == PRO_GATED_NORM ? 2 : 3));
+    const int mode = KC == 2 ? ((ph.keep_x || ph.from_token) ? 0 : 1) : (ph.prologue == PRO_GATED_NORM ? 2 : 3);
     const tagged* xsrc[4] = {ph.x, ph.x, ph.x, ph.x};
     bool xon[4] = {false, false, false, false};
     if (mode == 1) { xsrc[0] = ph.x + tid * 4; xon[0] = true; }
@@ -798,49 +552,52 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
     if (mode == 3) { xsrc[0] = ph.x + tid * 8; xsrc[1] = ph.x + tid * 8 + 4; xon[0] = xon[1] = true; }
 #pragma unroll
     for (int i = 0; i < 4; ++i) if (xon[i]) xin[i] = ld_words4(xsrc[i]);
-    // Block scales of the tile: shared memory -> tensor memory, all sixteen warps (four per
-    // quarter of tensor memory, each a quarter of the 256-input chunks).  Lane l of a quarter
-    // holds, for every 64-input step, the scale words of rows l, l + 32, l + 64, l + 96 in four
-    // consecutive columns.  With bank segments the tile has to wait for the routing.
-    int nb = 0;
-    auto stage_scales = [&]() {
-        Box unused;
-        nb = tile_box(mp, ph, S.ids, -1, unused);
-        if (nb <= 0) return;
-        const int buf = tile & 1, chunks = K / 256, sc_rows = K == 2048 ? 96 : 48;
-        if (!bar_wait(S, S.sc_full + buf, (tile >> 1) & 1, mp.status)) return;
-        const uint8_t* sc = S.scales + (size_t)buf * kScaleBufBytes;
-#pragma unroll 1
-        for (int c = warp >> 2; c < chunks; c += 4) {
-            uint32_t w[16];
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const int r = lane + 32 * g;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (r < sc_rows) v = *reinterpret_cast<const uint4*>(sc + ((c >> 3) * sc_rows + r) * 128 + (((c & 7) ^ (r & 7)) << 4));
-                w[0 + g] = v.x; w[4 + g] = v.y; w[8 + g] = v.z; w[12 + g] = v.w;
-            }
-            tmem_store16(lane_base + kColSfa + c * 16, w);
-        }
-        tmem_store_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) { mbar_arrive(S.sfa_ready); mbar_arrive(S.sc_free + buf); }
-        if (tid == 0) trace_mark(mp, pi, 6);
-    };
-    if (!ph.uses_ids) stage_scales();
-    // the static inputs loaded above, now into shared memory
-    if (tid < 2 * kMegaMaxSeg) red[64 + (tid & 1) * 16 + (tid >> 1)] = seg_scale;
-    if (ph.conv_taps) {
-        if (tid < conv_n * mp.conv_width) reinterpret_cast<unsigned short*>(S.conv_taps)[tid] = tap_reg;
-        if (tid < conv_n * (mp.conv_width - 1)) reinterpret_cast<unsigned short*>(S.conv_state)[tid] = state_reg;
-    }
-    wait_words4_n<4, true>(xsrc, xon, mode == 1 ? tag_x : tag, xin, wt);
 
-    // ---- the activation vector: bf16 (for the bf16 rows) and digit planes (for the MMAs)
-    float out_scale;
-    if (!ph.keep_x) {
-        if (K == 2048) {
+    // ---- static inputs (nothing another block writes): norm gamma, global scales of the
+    //      segments, conv taps and history of this block's channels
+    float4 gam = make_float4(0.f, 0.f, 0.f, 0.f);
+    if constexpr (KC == 2) if (ph.prologue == PRO_ADD_NORM) gam = *reinterpret_cast<const float4*>(ph.gamma + tid * 4);
+    if (tid < 2 * kMegaMaxSeg) {
+        const MegaSeg& sg = ph.seg[tid >> 1];
+        const float* src = (tid & 1) ? sg.g2 : sg.g;
+        float v = 1.f;
+        if ((tid >> 1) < ph.nseg && src && !sg.g_per_expert) v = *src;
+        red[64 + (tid & 1) * 16 + (tid >> 1)] = v;
+    }
+    int conv_row0 = 0;
+    bf16* conv_state = nullptr;
+    if constexpr (KC == 2) if (ph.conv_taps) {
+        const int W = mp.conv_width;
+        conv_state = reinterpret_cast<bf16*>(mp.st.conv_state) + (size_t)ph.state_index * mp.channels * (W - 1);
+        unsigned seg_start = 0;
+#pragma unroll 1
+        for (int i = 0; i < ph.nseg; ++i) {
+            const MegaSeg& sg = ph.seg[i];
+            if (sg.epilogue == EP_CONV) {
+                int ra, rb;
+                seg_range<K>(seg_start, sg.kind, sg.rows, lo, hi, ra, rb);
+                conv_row0 = ra;
+                const int conv_n = min(rb - ra, kMegaConvRows);
+                if (tid < conv_n * W)
+                    reinterpret_cast<unsigned short*>(S.conv_taps)[tid] =
+                        reinterpret_cast<const unsigned short*>(ph.conv_taps)[(size_t)ra * W + tid];
+                if (tid < conv_n * (W - 1))
+                    reinterpret_cast<unsigned short*>(S.conv_state)[tid] =
+                        reinterpret_cast<const unsigned short*>(conv_state)[(size_t)ra * (W - 1) + tid];
+            }
+            seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
+        }
+    }
+
+    wait_words4_n<4, true>(xsrc, xon, mode == 1 ? tag_x : tag, xin, wt);
+    if (tid == 0) trace_mark(mp, pi, 6);
+    if (probe) trace_cycles(mp, pi, 9, c0);
+
+    // ---- the activation vector: bf16 (for bf16 rows) and f16 (for the tensor-core rows), the
+    //      f16 copy scaled down by a power of two only if it would overflow
+    float out_mult;
+    if (KC == 4 || !ph.keep_x) {
+        if (KC == 2) {
             // residual add + RMSNorm, four elements per thread (quickdraw/models/qwen.py:205-217)
             float v[4];
             if (ph.from_token) {
@@ -864,8 +621,8 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
 #pragma unroll
             for (int w = 0; w < CW; ++w) { tot += red[w]; tmax = fmaxf(tmax, red[16 + w]); }
             const float inv = rsqrtf(tot / (float)K + mp.eps);
-            const int E = plane_exponent_of(tmax * inv * 1.01f);
-            out_scale = plane_out_scale(E);
+            float down;
+            f16_scale(tmax * inv * 1.01f, down, out_mult);
             float nrm[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -875,17 +632,20 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             const __nv_bfloat162 n01 = __floats2bfloat162_rn(nrm[0], nrm[1]), n23 = __floats2bfloat162_rn(nrm[2], nrm[3]);
             *reinterpret_cast<uint2*>(xs + tid * 4) = make_uint2(*reinterpret_cast<const uint32_t*>(&n01),
                                                                  *reinterpret_cast<const uint32_t*>(&n23));
-            store_planes4(S.planes, tid * 4, nrm, E);
+            *reinterpret_cast<uint2*>(xf + tid * 8) = make_uint2(pack_f16x2(nrm[0] * down, nrm[1] * down),
+                                                                 pack_f16x2(nrm[2] * down, nrm[3] * down));
+            if (tid == 0) red[96] = out_mult;
         } else if (ph.prologue == PRO_GATED_NORM) {
             // per-head RMSNorm of o, times gamma, times silu(z); a warp per 128-wide head, four
             // consecutive features per lane (quickdraw/models/qwen.py:161-164)
-            float nv[2][4];
+            constexpr int HPW = K / 128 / CW;
+            float nv[HPW][4];
             const uint2 graw = *reinterpret_cast<const uint2*>(ph.head_gamma + lane * 4);
             const float gm[4] = {__uint_as_float(graw.x << 16), __uint_as_float(graw.x & 0xffff0000u),
                                  __uint_as_float(graw.y << 16), __uint_as_float(graw.y & 0xffff0000u)};
             float top = 0.f;
 #pragma unroll
-            for (int a = 0; a < 2; ++a) {
+            for (int a = 0; a < HPW; ++a) {
                 const uint4 ow = xin[2 * a], zw = xin[2 * a + 1];
                 const float o[4] = {word_value(ow.x), word_value(ow.y), word_value(ow.z), word_value(ow.w)};
                 const float zz[4] = {word_value(zw.x), word_value(zw.y), word_value(zw.z), word_value(zw.w)};
@@ -906,46 +666,46 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             float tmax = 0.f;
 #pragma unroll
             for (int w = 0; w < CW; ++w) tmax = fmaxf(tmax, red[16 + w]);
-            const int E = plane_exponent_of(tmax * 1.01f);
-            out_scale = plane_out_scale(E);
+            float down;
+            f16_scale(tmax, down, out_mult);
 #pragma unroll
-            for (int a = 0; a < 2; ++a) store_planes4(S.planes, (warp + a * CW) * 128 + lane * 4, nv[a], E);
+            for (int a = 0; a < HPW; ++a) {
+                const int base = (warp + a * CW) * 128 + lane * 4;
+                *reinterpret_cast<uint2*>(xf + base * 2) = make_uint2(pack_f16x2(nv[a][0] * down, nv[a][1] * down),
+                                                                      pack_f16x2(nv[a][2] * down, nv[a][3] * down));
+            }
         } else {
             // the vector as it is (attention output): eight elements per thread
             const uint4 w0 = xin[0], w1 = xin[1];
-            const float va[4] = {word_value(w0.x), word_value(w0.y), word_value(w0.z), word_value(w0.w)};
-            const float vb[4] = {word_value(w1.x), word_value(w1.y), word_value(w1.z), word_value(w1.w)};
+            const float v[8] = {word_value(w0.x), word_value(w0.y), word_value(w0.z), word_value(w0.w),
+                                word_value(w1.x), word_value(w1.y), word_value(w1.z), word_value(w1.w)};
             float top = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) top = fmaxf(top, fmaxf(fabsf(va[j]), fabsf(vb[j])));
+            for (int j = 0; j < 8; ++j) top = fmaxf(top, fabsf(v[j]));
             top = warp_max(top);
             if (lane == 0) red[16 + warp] = top;
             named_barrier(1, CT);
             float tmax = 0.f;
 #pragma unroll
             for (int w = 0; w < CW; ++w) tmax = fmaxf(tmax, red[16 + w]);
-            const int E = plane_exponent_of(tmax * 1.01f);
-            out_scale = plane_out_scale(E);
-            store_planes4(S.planes, tid * 8, va, E);
-            store_planes4(S.planes, tid * 8 + 4, vb, E);
+            float down;
+            f16_scale(tmax, down, out_mult);
+            *reinterpret_cast<uint4*>(xf + tid * 16) = make_uint4(pack_f16x2(v[0] * down, v[1] * down), pack_f16x2(v[2] * down, v[3] * down),
+                                                                  pack_f16x2(v[4] * down, v[5] * down), pack_f16x2(v[6] * down, v[7] * down));
         }
-        fence_proxy_async();          // the planes are read by the MMAs (async proxy)
-        if (tid == 0) red[96] = out_scale;
         named_barrier(1, CT);
     } else {
         named_barrier(1, CT);    // the segment scales above are in shared memory
-        out_scale = red[96];     // the vector (and its scale) the phase before left in shared memory
+        out_mult = red[96];      // the vector (and its scale) the phase before left in shared memory
     }
-    if (tid == 0) trace_mark(mp, pi, 2);
-
-    // ---- routing for this layer (every block selects the same experts from the same logits),
-    //      then the tile (its boxes depend on the routing)
-    if (ph.route && warp == 0) {
+    // ---- routing for this layer (every block selects the same experts from the same logits);
+    //      the other warps go on with the shared expert's rows meanwhile
+    if constexpr (KC == 2) if (ph.route && warp == 0) {
         float p[8];
         uint4 ab[2];
         {
             const bool have = lane * 8 < mp.experts;          // the expert count is a multiple of eight
-            const tagged* const src[2] = {ph.router_logits + lane * 8, ph.router_logits + lane * 8 + 4};
+            const tagged* const src[2] = {ph.router_logits + (have ? lane * 8 : 0), ph.router_logits + (have ? lane * 8 + 4 : 0)};
             const bool on[2] = {have, have};
             wait_words4_n<2>(src, on, tag, ab, wt);
         }
@@ -955,131 +715,131 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
         route_regs(p, mp.experts, mp.topk, S.ids, S.weights, lane);
         __syncwarp();
         if (blockIdx.x == 0 && lane < mp.topk) { ph.ids_out[lane] = S.ids[lane]; ph.weights_out[lane] = S.weights[lane]; }
-        if (lane == 0) mbar_arrive(S.ids_bar);
+        if (lane == 0) { mbar_arrive(S.ids_bar); trace_mark(mp, pi, 7); }
     }
-    if (ph.uses_ids) {
-        bar_wait(S, S.ids_bar, ph.layer & 1, mp.status);      // completes even when the routing warp gave up waiting
-        stage_scales();
-    }
-    // the digit planes are in place (just built, or kept from the phase before)
-    if (tid == 0 && nb > 0) { mbar_arrive(S.b_ready); trace_mark(mp, pi, 7); }
 
-    // ---- bf16 rows
+    if (tid == 0) trace_mark(mp, pi, 2);
+    if (probe) trace_cycles(mp, pi, 10, c0);
+    uint32_t xh[UNITS][16];
+    load_x_fragments<UNITS>(xf, warp, lane, xh);
+
+    // ---- rows
     float best_val = -INFINITY;
     int best_idx = 0x7fffffff;
+    bool first_tile = true, ids_ready = false;
+    unsigned seg_start = 0;
+    int turn = 0;                      // bf16 rows handed out so far: rotates the row -> warp map
     bool ok = true;
-    if (K == 2048) {
-        int turn = 0;                      // rows handed out so far: rotates the row -> warp map
-        const bool wide = ph.argmax != 0;
-        const RowRing ring = row_ring(S, wide);
-        int wide_it = 0;
-        int& rit = wide ? wide_it : row_it;
-        int b0, b1, seg_first = 0;
-        bf16_rows_range(ph, b0, b1);
 #pragma unroll 1
-        for (int i = 0; i < ph.nseg && ok; ++i) {
-            const MegaSeg& sg = ph.seg[i];
-            if (sg.kind != SEG_BF16) continue;
-            const int ra = max(b0, seg_first) - seg_first, rb = min(b1, seg_first + sg.rows) - seg_first;
-            seg_first += sg.rows;
-            if (ra >= rb) continue;
-#pragma unroll 1
-            for (int r0 = ra; r0 < rb; r0 += kBf16TileRows, ++rit) {
-                const int n = min(kBf16TileRows, rb - r0);
-                const int st = rit % ring.stages;
-                if (!bar_wait(S, ring.full + st, (rit / ring.stages) & 1, mp.status)) { ok = false; break; }
-                const uint8_t* base = row_stage(S, wide, st);
-#pragma unroll 1
-                for (int r = (warp - turn) & (CW - 1); r < n; r += CW) {
-                    const int row = r0 + r;
-                    const float result = warp_sum(bf16_row_dot_smem<8>(base + (size_t)r * 4096, reinterpret_cast<const uint8_t*>(xs), lane));
-                    const bf16 rounded = __float2bfloat16_rn(result);
-                    if (sg.epilogue == EP_ARGMAX) {
-                        const int index = ph.row_lo + row;      // vocabulary index (the segment is this rank's shard)
-                        if (lane == 0) mp.logits[index] = rounded;
-                        const float v = __bfloat162float(rounded);
-                        if (v > best_val || (v == best_val && index < best_idx)) { best_val = v; best_idx = index; }
-                    } else if (lane == 0) {
-                        st_word(sg.y + row, make_word(rounded, tag));
-                    }
-                }
-                turn = (turn + n) & (CW - 1);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(ring.empty + st);
-            }
-        }
-    }
-    if (!ok && lane == 0) *S.abort = 1;
-
-    // ---- the tile's accumulator: one worker thread per row
-    if (worker && nb > 0) {
-        const int db = tile & 1;
-        // the row's box, segment and global scale first: none of it needs the accumulator
-        Box box = {};
-        const int bi = (tid >> 3) < nb ? (tid >> 3) : -1;
-        tile_box(mp, ph, S.ids, bi, box);
-        const MegaSeg& sg = ph.seg[box.seg];
-        const bool pair = sg.kind == SEG_FP4_PAIR;
+    for (int i = 0; i < ph.nseg && ok; ++i) {
+        const MegaSeg& sg = ph.seg[i];
+        int ra, rb;
+        seg_range<K>(seg_start, sg.kind, sg.rows, lo, hi, ra, rb);
+        seg_start += (unsigned)sg.rows * seg_cost<K>(sg.kind);
+        if (ra >= rb) continue;
         int expert = 0;
-        if (sg.slot >= 0) expert = S.ids[sg.slot] - mp.expert_lo;
-        const int half_rows = 4 * nb;                  // pair tiles: gate rows [0, 4 nb), up rows [4 nb, 8 nb)
-        const bool upper = pair && tid >= half_rows;
-        const float* gsrc = upper ? sg.g2 : sg.g;
-        const float g = (gsrc && sg.g_per_expert) ? gsrc[expert] : red[64 + (upper ? 16 : 0) + box.seg];
-        const bool landed = bar_wait(S, S.d_full + db, (tile >> 1) & 1, mp.status);
-        if (tid == 0) trace_mark(mp, pi, 8);
-        tc_fence_after();
-        uint32_t v[16];
-        tmem_load16(lane_base + kColD + db * 16, v);
-        tmem_load_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(S.d_free + db);
-        const float sum = plane_sum(v);
-        float result = (sum * out_scale) * g;
-        if (ph.seg[0].kind == SEG_FP4_PAIR) {
-            // SwiGLU: the up row of a gate row sits half a tile above it
-            float* exch = S.partials;     // [64]
-            if (tid >= half_rows && tid < 2 * half_rows) exch[tid - half_rows] = round_bf16(result);
-            named_barrier(3, 128);
-            if (tid < half_rows) result = round_bf16(silu_precise(round_bf16(result))) * exch[tid];
+        if (KC == 2 && sg.slot >= 0) {
+            if (!ids_ready && !mbar_wait(S.ids_bar, ph.layer & 1, mp.status)) { ok = false; break; }
+            ids_ready = true;
+            expert = S.ids[sg.slot];
+            if (expert < mp.expert_lo || expert >= mp.expert_hi) continue;
+            expert -= mp.expert_lo;
         }
-        const bf16 rounded = __float2bfloat16_rn(result);
-        const int row = box.row + (tid & 7);
-        if (bi >= 0 && landed && !upper) {
-            if (sg.epilogue == EP_CONV) {
-                // depthwise causal conv of this channel (quickdraw/models/qwen.py:134-136): history
-                // taps then the new value; products rounded to bf16, fp32 sum as (0 + 2) + (1 + 3)
-                const int W = mp.conv_width, local = row - conv_row0;
-                float prod[kStreamConvWidth];
-#pragma unroll
-                for (int k = 0; k < kStreamConvWidth; ++k) {
-                    float val = 0.f, tap = 0.f;
-                    if (k < W) {
-                        tap = __bfloat162float(S.conv_taps[local * W + k]);
-                        val = k < W - 1 ? __bfloat162float(S.conv_state[local * (W - 1) + k]) : __bfloat162float(rounded);
-                        if (k >= 1) conv_state[(size_t)row * (W - 1) + k - 1] = __float2bfloat16_rn(val);
+        const int tile_rows = seg_tile_rows<K>(sg.kind);
+        const float g1 = (sg.g && sg.g_per_expert) ? sg.g[expert] : red[64 + i];
+        const float g2 = (sg.g2 && sg.g_per_expert) ? sg.g2[expert] : red[80 + i];
+#pragma unroll 1
+        for (int r0 = ra; r0 < rb; r0 += tile_rows, ++it) {
+            const int n = min(tile_rows, rb - r0);
+            const int st = it % NS;
+            if (first_tile && probe) trace_cycles(mp, pi, 11, c0);
+            if (!mbar_wait(S.full + st, (it / NS) & 1, mp.status)) { ok = false; break; }
+            if (first_tile && tid == 0) trace_mark(mp, pi, 3);
+            if (first_tile && probe) trace_cycles(mp, pi, 12, c0);
+            const bool was_first = first_tile;
+            first_tile = false;
+            const uint8_t* base = S.stages + (size_t)st * kStreamStageBytes;
+            if (sg.kind == SEG_BF16) {
+                if (lane == 0) mbar_arrive(S.ready + st);      // keeps the phase of `ready` in step with the ring
+                if constexpr (KC == 2) {
+#pragma unroll 1
+                    for (int r = (warp - turn) & (CW - 1); r < n; r += CW) {
+                        const int row = r0 + r;
+                        const float result = warp_sum(bf16_row_dot_smem<K / 256>(base + (size_t)r * 2 * K,
+                                                                                 reinterpret_cast<const uint8_t*>(xs), lane));
+                        const bf16 rounded = __float2bfloat16_rn(result);
+                        if (sg.epilogue == EP_ARGMAX) {
+                            const int index = ph.row_lo + row;      // vocabulary index (the segment is this rank's shard)
+                            if (lane == 0) mp.logits[index] = rounded;
+                            const float v = __bfloat162float(rounded);
+                            if (v > best_val || (v == best_val && index < best_idx)) { best_val = v; best_idx = index; }
+                        } else if (lane == 0) {
+                            st_word(sg.y + row, make_word(rounded, tag));
+                        }
                     }
-                    prod[k] = k < W ? round_bf16(val * tap) : 0.f;
+                    turn = (turn + n) & (CW - 1);
                 }
-                const float conv = (prod[0] + prod[2]) + (prod[1] + prod[3]);
-                st_word(sg.y + row, make_word(__float2bfloat16_rn(silu_precise(conv)), tag));
             } else {
-                st_word(sg.y + row, make_word(rounded, tag));
+                const bool pair = KC == 2 && sg.kind == SEG_FP4_PAIR;
+                const int groups = UNITS == 2 ? 1 : ((pair || n > 16) ? 2 : 1);
+                float* mine = S.partials + st * kRowPartialFloats;
+                tile_partials<K>(base, UNITS == 2 ? 16 : 32, groups, xh, warp, lane, mine + warp * kRowSlots);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(S.ready + st);
+                if (warp == (it & (CW - 1))) {
+                    // this tile's finishing warp: lane = slot of the tile
+                    if (!mbar_wait(S.ready + st, (it / NS) & 1, mp.status)) { ok = false; break; }
+                    const float total = tile_sum(mine, lane);
+                    float result = (total * out_mult) * g1;
+                    if (pair) {
+                        const float up_raw = __shfl_down_sync(0xffffffffu, total, 16);
+                        const float up = round_bf16((up_raw * out_mult) * g2);
+                        result = round_bf16(silu_precise(round_bf16(result))) * up;
+                    }
+                    const bf16 rounded = __float2bfloat16_rn(result);
+                    const bool valid = lane < n && (!pair || lane < 16);
+                    const int row = r0 + lane;
+                    if (valid) {
+                        if (KC == 2 && sg.epilogue == EP_CONV) {
+                            // depthwise causal conv of this channel (quickdraw/models/qwen.py:134-136):
+                            // history taps then the new value; products rounded to bf16, fp32 sum as
+                            // (0 + 2) + (1 + 3)
+                            const int W = mp.conv_width, local = row - conv_row0;
+                            float prod[kStreamConvWidth];
+#pragma unroll
+                            for (int k = 0; k < kStreamConvWidth; ++k) {
+                                float val = 0.f, tap = 0.f;
+                                if (k < W) {
+                                    tap = __bfloat162float(S.conv_taps[local * W + k]);
+                                    val = k < W - 1 ? __bfloat162float(S.conv_state[local * (W - 1) + k]) : __bfloat162float(rounded);
+                                    if (k >= 1) conv_state[(size_t)row * (W - 1) + k - 1] = __float2bfloat16_rn(val);
+                                }
+                                prod[k] = k < W ? round_bf16(val * tap) : 0.f;
+                            }
+                            const float conv = (prod[0] + prod[2]) + (prod[1] + prod[3]);
+                            st_word(sg.y + row, make_word(__float2bfloat16_rn(silu_precise(conv)), tag));
+                        } else {
+                            st_word(sg.y + row, make_word(rounded, tag));
+                        }
+                    }
+                }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(S.empty + st);
+            if (was_first && probe) trace_cycles(mp, pi, 13, c0);
         }
-        if (!landed && lane == 0) *S.abort = 1;
     }
-    if (nb > 0) ++tile;
-
+    if (tid == 0) trace_mark(mp, pi, 8);
+    if (probe) trace_cycles(mp, pi, 14, c0);
+    if (!ok && lane == 0) *S.abort = 1;
     // ---- greedy argmax over this rank's logits (ties: lowest index), then over the ranks
-    if (ph.argmax) {
-        if (lane == 0) { red[32 + warp] = best_val; redi[48 + warp] = best_idx; }
+    if (KC == 2 && ph.argmax) {
+        if (lane == 0) { red[32 + warp] = best_val; reinterpret_cast<int*>(red)[48 + warp] = best_idx; }
         named_barrier(1, CT);
         if (tid == 0) {
-            float bv = red[32]; int bi = redi[48];
+            float bv = red[32]; int bi = reinterpret_cast<int*>(red)[48];
             for (int w = 1; w < CW; ++w) {
-                const float v = red[32 + w]; const int ix = redi[48 + w];
+                const float v = red[32 + w]; const int ix = reinterpret_cast<int*>(red)[48 + w];
                 if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
             }
             mp.best_val[blockIdx.x] = bv;
@@ -1388,10 +1148,10 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
     bool ok = true;
     int chunk = 0;
 #pragma unroll 1
-    for (int c0 = t0; c0 < t1 && ok; c0 += kAttnStagePos, ++it, ++chunk) {
-        const int st = it % NB;
-        if (!bar_wait(S, S.row_full + st, (it / NB) & 1, mp.status)) { ok = false; break; }
-        uint8_t* buf = S.rows + (size_t)st * kMegaRowStageBytes;
+    for (int c0 = t0; c0 < t1 && ok; c0 += kAttnStagePos, ++it) {
+        const int st = it % NS;
+        if (!mbar_wait(S.full + st, (it / NS) & 1, mp.status)) { ok = false; break; }
+        uint8_t* buf = S.stages + (size_t)st * kStreamStageBytes;
         const bool has_new = owns_new && position >= c0 && position < c0 + kAttnStagePos;
         const bool ragged = c0 + kAttnStagePos > t1;
         if (has_new || ragged) {
@@ -1411,10 +1171,15 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
             }
             named_barrier(1, CT);
         }
-        if (warp == (chunk & (kAttnWarps - 1)))
-            attn_chunk(acc, q_s, buf, buf + kAttnStagePos * kAttnRow, c0, t1, lane);
+        if (lane == 0) mbar_arrive(S.ready + st);      // keeps the phase of `ready` in step with the ring
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h, ++chunk) {
+            if (c0 + 16 * h >= t1) continue;
+            if (warp == (chunk & (kAttnWarps - 1)))
+                attn_chunk(acc, q_s, buf + (16 * h) * kAttnRow, buf + (kAttnStagePos + 16 * h) * kAttnRow, c0 + 16 * h, t1, lane);
+        }
         __syncwarp();
-        if (lane == 0) mbar_arrive(S.row_empty + st);
+        if (lane == 0) mbar_arrive(S.empty + st);
     }
     if (!ok && lane == 0) *S.abort = 1;
     const int nchunks = (t1 - t0 + 15) / 16;
@@ -1565,7 +1330,7 @@ QD_DEVINL void down_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
     const int r1 = (int)((long long)H * (blockIdx.x + 1) / gridDim.x);
     const int n = r1 - r0, nslots = mp.topk + 1;
     const uint32_t tag = tag_base | (uint32_t)(ph.layer + 1);
-    uint8_t* hx = S.planes;                                                // [slots][512] f16 (the plane region is idle here)
+    uint8_t* hx = reinterpret_cast<uint8_t*>(S.xs);                        // [slots][512] f16 (xs and xf are adjacent)
     float* dpart = S.partials;                                             // [36 units][16 rows]
     float* contrib = S.partials + 36 * 16;                                 // [slots][16]
     int* order = reinterpret_cast<int*>(contrib + kDownSlots * 16);        // [topk]
@@ -1623,7 +1388,7 @@ QD_DEVINL void down_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
                                                                      pack_f16x2(hv[k][2] * down, hv[k][3] * down));
         if ((idx & 127) == 0) smult[s] = up;
     }
-    bool ok = bar_wait(S, S.down_bar, ph.layer & 1, mp.status);
+    bool ok = mbar_wait(S.down_bar, ph.layer & 1, mp.status);
     named_barrier(1, CT);
     // ---- units: (slot, span)
     {
@@ -1720,30 +1485,17 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
         return;
     }
     if (tid == 0) {
-        for (int s = 0; s < NA; ++s) { mbar_init(S.code_full + s, 1); mbar_init(S.code_empty + s, 1); }
-        for (int s = 0; s < NB; ++s) { mbar_init(S.row_full + s, 1); mbar_init(S.row_empty + s, CW); }
-        for (int s = 0; s < NA + NB; ++s) { mbar_init(S.wide_full + s, 1); mbar_init(S.wide_empty + s, CW); }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(S.sc_full + b, 1); mbar_init(S.sc_free + b, CW);
-            mbar_init(S.d_full + b, 1); mbar_init(S.d_free + b, 4);
-        }
-        mbar_init(S.sfa_ready, CW);
-        mbar_init(S.b_ready, 1);
+        for (int s = 0; s < NS; ++s) { mbar_init(S.full + s, 1); mbar_init(S.empty + s, CW); mbar_init(S.ready + s, CW); }
         mbar_init(S.ids_bar, 1);
         mbar_init(S.down_bar, 1);
         mbar_fence_init();
         *S.abort = 0;
     }
-    // all of tensor memory: one block per SM
-    if (warp == 0) { tmem_alloc(S.tmem_slot, kTmemCols); tmem_relinquish(); }
     // The launch number: part of every tag.  Read by every thread before any block can leave
     // (the last block to leave advances it).
     const uint32_t launch = *reinterpret_cast<volatile unsigned int*>(mp.epoch) + 1u;
     const uint32_t tag_base = (launch & 0x3ffu) << 6;
-    tc_fence_before();
     __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *S.tmem_slot;
     // A position outside the cache (it may come from a device scalar) touches nothing: every
     // block skips the token and the status word says so.
     const int step_position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
@@ -1752,25 +1504,16 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
         if (tid == 0 && blockIdx.x == 0) atomicOr(mp.status, QD_STATUS_BAD_ARG);
     } else if (warp == CW) {
         producer(mp, S, lane);
-    } else if (warp == CW + 1) {
-        mma_warp(mp, S, tmem, lane);
     } else {
         Wait wt;
         wt.status = mp.status; wt.abort = S.abort; wt.limit_ns = (unsigned long long)mp.wait_limit_us * 1000ull;
-        // block scales of the digit planes: the same for every tile (lanes 0..7 of each quarter of
-        // tensor memory, plane p = lane), two columns per 64-input step
-        if (warp < 4) {
-            for (int step = 0; step < 64; ++step)
-                tmem_store1(tmem + ((uint32_t)(warp * 32) << 16) + kColSfb + step * 2, plane_scale_word(lane & 15));
-            tmem_store_wait();
-            tc_fence_before();
-        }
         // rotation table of this step's position, once for all attention layers
         // (quickdraw/models/qwen.py:84-88: fp32 angle, cos / sin rounded to bf16)
         if (mp.rotary > 0) {
+            const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
             for (int f = tid; f < mp.rotary / 2; f += CT) {
                 const float inv_freq = 1.0f / powf(mp.theta, (float)(2 * f) / (float)mp.rotary);
-                const float angle = (float)step_position * inv_freq;
+                const float angle = (float)position * inv_freq;
                 S.rope[f] = round_bf16(cosf(angle));
                 S.rope[128 + f] = round_bf16(sinf(angle));
             }
@@ -1783,7 +1526,7 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
         }
         named_barrier(1, CT);
         float res[4] = {0.f, 0.f, 0.f, 0.f};
-        int row_it = 0, tile = 0;
+        int it = 0;
 #pragma unroll 1
         for (int pi = 0; pi < mp.nphases; ++pi) {
             const MegaPhase& ph = S.cph[pi & 1];
@@ -1794,11 +1537,12 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
             }
             if (tid == 0) trace_mark(mp, pi, 0);
             if (ph.kind == MK_STREAM) {
-                stream_phase(mp, ph, S, wt, pi, row_it, tile, res, tag_base, tmem);
+                if (ph.width == 2048) stream_phase<2>(mp, ph, S, wt, pi, it, res, tag_base);
+                else stream_phase<4>(mp, ph, S, wt, pi, it, res, tag_base);
             } else if (ph.kind == MK_GDN) {
                 gdn_phase(mp, ph, S, wt, tag_base);
             } else if (ph.kind == MK_ATTN) {
-                attn_phase(mp, ph, S, wt, row_it, tag_base);
+                attn_phase(mp, ph, S, wt, it, tag_base);
             } else if (ph.kind == MK_ATTN_MERGE) {
                 attn_merge_phase(mp, ph, S, wt, tag_base);
             } else {
@@ -1811,9 +1555,7 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
         }
     }
     // the last block to leave advances the launch number for the next launch
-    tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
     if (tid == 0) {
         __threadfence();
         const unsigned int gone = atomicAdd(mp.exit_count, 1u);

@@ -8,24 +8,17 @@
 // them carry the tag it expects (fp32 partial sums of the attention splits travel as 64-bit
 // {value, tag} words).  A block therefore starts a phase as soon as the words it needs
 // have arrived, and the wait costs one trip to L2 instead of a fence, an atomic and a poll.
-// NVFP4 weights reach shared memory as tiled TMA loads (the layout the FP4 tensor core reads;
-// umma.cuh) through one ring, bf16 rows and KV-cache rows as bulk copies through a second one;
-// the producer warp runs ahead of the consumers across phase boundaries.
+// Weights reach shared memory through one ring of bulk copies per block whose producer warp
+// runs ahead of the consumers across phase boundaries.
 #pragma once
 #include "stream.cuh"
-#include "umma.cuh"
 
 namespace qd {
 
 constexpr int kMegaConsumerWarps = 16;
 constexpr int kMegaConsumers = kMegaConsumerWarps * 32;
-constexpr int kMegaThreads = kMegaConsumers + 64;     // + one producer warp + one MMA warp
-constexpr int kMegaCodeStages = 6;                    // ring of NVFP4 code tiles: 12 KB each (96 rows x 256 inputs, or several
-                                                      // 256-input chunks of a shorter tile)
-constexpr int kMegaCodeStageBytes = 96 * 128;
-constexpr int kMegaRowStages = 2;                     // ring of bf16 rows / KV-cache rows
-constexpr int kMegaRowStageBytes = 16896;             // 4 bf16 rows of 2048, or 16 positions of padded K and V rows
-constexpr int kMegaMaxBoxes = 12;                     // 8-row TMA boxes of one MMA tile (96 of its 128 rows)
+constexpr int kMegaThreads = kMegaConsumers + 32;     // + one producer warp
+constexpr int kMegaStages = 4;                        // ring stages of kStreamStageBytes
 constexpr int kMegaMaxSeg = 10;
 constexpr int kMegaConvRows = 128;                    // conv channels one block can own
 constexpr int kMegaAttnSplits = 80;                   // context splits per KV head at most
@@ -45,7 +38,6 @@ struct alignas(8) MegaSeg {
     int rows;
     short kind, epilogue;                                       // SegKind, SegEpilogue
     short slot, g_per_expert;                                   // slot >= 0: bank entry = ids[slot]
-    int map, map2;                                              // tensor maps of the codes (w, w2); the scales' maps follow each
 };
 
 struct alignas(16) MegaPhase {
@@ -95,7 +87,6 @@ struct MegaParams {
     unsigned long long peer_base[kMegaMaxRanks];
     long long contrib_offset;      // tagged [topk][hidden] per rank: routed contributions of the layer
     long long argmax_offset;       // uint2 [2][world] per rank: {value bits, index} and tag of the rank's best logit
-    const CUtensorMap* maps;       // tensor maps of every NVFP4 matrix (device memory, 64-byte aligned)
     unsigned int wait_limit_us;    // bound of every wait, microseconds
     unsigned long long* trace;     // optional: [phase][16][grid] timestamps (ns)
 };

@@ -10,7 +10,6 @@
 // then   residual add + final RMSNorm -> bf16 LM head with greedy argmax.
 // Every launch can be a programmatic dependent of the one before it, so its weight
 // fetches overlap the predecessor's tail.  The model object is a host-side pointer table.
-#include <cstring>
 #include <new>
 #include <vector>
 
@@ -281,53 +280,26 @@ namespace {
 
 unsigned int g_wait_limit_us = 200000;      // bound of every device-side wait of the persistent kernel
 
-// Tensor maps of the program: two per NVFP4 matrix (codes, then block scales), boxes of 8 rows
-// x 128 bytes, 128-byte swizzle.
-struct MapList {
-    std::vector<CUtensorMap> maps;
-    bool ok = true;
-    // rows: rows of the whole matrix (all experts of a bank); returns the index of the codes' map
-    int add(const void* codes, const void* scales, long long rows, int K) {
-        CUtensorMap m;
-        const int index = (int)maps.size();
-        if (umma_make_map(&m, codes, rows, K / 2, 128, 8) != QD_OK) ok = false;
-        maps.push_back(m);
-        if (umma_make_map(&m, scales, rows, K / 16, 128, 8) != QD_OK) ok = false;
-        maps.push_back(m);
-        return index;
-    }
-};
-
-MegaSeg mega_seg(const StreamSeg& s, tagged* y, MapList* maps = nullptr, int K = 0, long long bank = 1) {
+MegaSeg mega_seg(const StreamSeg& s, tagged* y) {
     MegaSeg m = {};
-    if (maps && s.kind != SEG_BF16) {
-        m.map = maps->add(s.w, s.s, bank * s.rows, K);
-        if (s.kind == SEG_FP4_PAIR) m.map2 = maps->add(s.w2, s.s2, bank * s.rows, K);
-    }
     m.w = s.w; m.s = s.s; m.g = s.g; m.w2 = s.w2; m.s2 = s.s2; m.g2 = s.g2; m.y = y;
     m.w_stride = s.w_stride; m.s_stride = s.s_stride; m.rows = s.rows;
     m.kind = (short)s.kind; m.epilogue = (short)s.epilogue; m.slot = (short)s.slot; m.g_per_expert = (short)s.g_per_expert;
     return m;
 }
 
-// Checks that a streaming phase fits the kernel's partition (the NVFP4 rows are cut evenly over
-// the blocks in units of 8 rows, the bf16 rows one by one): every block's tile must fit the
-// code stages, its conv rows the staging area.
+// Cost partition of a streaming phase over `grid` blocks; false if it does not fit.
 bool mega_finish_stream(MegaPhase& ph, int grid) {
-    long long units = 0;
+    unsigned long long total = 0;
+    const unsigned fp4_row = (ph.width / 2 + ph.width / 16) / 16;
     for (int i = 0; i < ph.nseg; ++i) {
-        const int kind = ph.seg[i].kind;
-        if (kind != SEG_BF16 && ph.seg[i].rows % 8 != 0) return false;
-        if (kind == SEG_BF16 && ph.width != 2048) return false;
-        if (kind != SEG_BF16 && (ph.seg[0].kind == SEG_FP4_PAIR) != (kind == SEG_FP4_PAIR)) return false;
-        if (ph.seg[i].epilogue == EP_CONV && i != 0) return false;
-        if (kind != SEG_BF16) units += ph.seg[i].rows / 8;
+        const unsigned cost = ph.seg[i].kind == SEG_BF16 ? 2u * ph.width / 16 : ph.seg[i].kind == SEG_FP4_PAIR ? 2 * fp4_row : fp4_row;
+        total += (unsigned long long)ph.seg[i].rows * cost;
+        if (ph.seg[i].epilogue == EP_CONV && ph.seg[i].rows / grid + 2 > kMegaConvRows) return false;
     }
-    const long long per_block = (units + grid - 1) / grid;
-    const long long boxes = ph.nseg > 0 && ph.seg[0].kind == SEG_FP4_PAIR ? 2 * per_block : per_block;
-    if (boxes > kMegaMaxBoxes || (ph.width > 2048 && boxes > kMegaMaxBoxes / 2)) return false;
-    if (8 * per_block > kMegaConvRows) return false;
-    ph.quota = 0; ph.remainder = 0;
+    if (total + 1024 >= 0xffffffffull) return false;
+    ph.quota = (unsigned)(total / grid);
+    ph.remainder = (unsigned)(total % grid);
     return true;
 }
 
@@ -372,18 +344,9 @@ extern "C" int qd_set_wait_limit_us(unsigned int microseconds) {
     return QD_OK;
 }
 
-// The program buffer: the phases, then (64-byte aligned) the tensor maps.
-static long long program_map_offset(const qd_model* model) {
-    return ((long long)mega_phase_count(model) * (long long)sizeof(MegaPhase) + 63) & ~63ll;
-}
-static int program_map_count(const qd_model* model) {
-    int n = 0;      // per layer: 3 or 4 mixer matrices, shared gate / up and routed gate / up banks
-    for (int L = 0; L < model->cfg.layers; ++L) n += 2 * ((model->layers[L].is_attention ? 4 : 3) + 4);
-    return n;
-}
 extern "C" long long qd_program_bytes(const qd_model* model) {
     if (!model) return -1;
-    return program_map_offset(model) + (long long)program_map_count(model) * (long long)sizeof(CUtensorMap);
+    return (long long)mega_phase_count(model) * (long long)sizeof(MegaPhase);
 }
 
 extern "C" int qd_program_build(const qd_model* model, void* workspace, void* host_out, long long bytes) {
@@ -394,8 +357,6 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
     if (bytes < qd_program_bytes(model)) return QD_ERR_ARG;
     Workspace w = carve(c, (uint8_t*)workspace);
     MegaPhase* out = (MegaPhase*)host_out;
-    MapList maps;
-    const int owned = c.expert_hi - c.expert_lo;
     const int H = c.hidden;
     const int channels = 2 * c.key_heads * c.key_dim + c.value_heads * c.value_dim;
     const int value_width = c.value_heads * c.value_dim;
@@ -412,13 +373,13 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
         else { a.x = w.t_moe_out; a.x_prev_layer = 1; }
         if (ly.is_attention) {
             a.nseg = 3;
-            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, 2 * q_width, nullptr), w.t_big, &maps, H);
-            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, kv_width, nullptr), w.t_mid, &maps, H);
-            a.seg[2] = mega_seg(fp4_seg(ly.proj_c, kv_width, nullptr), w.t_mid + kv_width, &maps, H);
+            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, 2 * q_width, nullptr), w.t_big);
+            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, kv_width, nullptr), w.t_mid);
+            a.seg[2] = mega_seg(fp4_seg(ly.proj_c, kv_width, nullptr), w.t_mid + kv_width);
         } else {
             a.nseg = 4;
-            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, channels, nullptr, EP_CONV), w.t_big, &maps, H);
-            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, value_width, nullptr), w.t_mid, &maps, H);
+            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, channels, nullptr, EP_CONV), w.t_big);
+            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, value_width, nullptr), w.t_mid);
             a.seg[2] = mega_seg(bf16_seg(ly.in_proj_a, c.value_heads, nullptr), w.t_ab);
             a.seg[3] = mega_seg(bf16_seg(ly.in_proj_b, c.value_heads, nullptr), w.t_ab + c.value_heads);
             a.conv_taps = (const bf16*)ly.conv1d;
@@ -443,7 +404,7 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
         // ---- B: output projection
         MegaPhase b = {};
         b.kind = MK_STREAM; b.width = 4096; b.layer = L; b.x = w.t_o;
-        b.nseg = 1; b.seg[0] = mega_seg(fp4_seg(ly.proj_out, H, nullptr), w.t_mixed, &maps, 4096);
+        b.nseg = 1; b.seg[0] = mega_seg(fp4_seg(ly.proj_out, H, nullptr), w.t_mixed);
         if (ly.is_attention) b.prologue = PRO_NONE;
         else { b.prologue = PRO_GATED_NORM; b.z = w.t_mid; b.head_gamma = (const bf16*)ly.head_norm; }
         if (!mega_finish_stream(b, grid)) return QD_ERR_UNSUPPORTED;
@@ -464,17 +425,13 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
         d.router_logits = w.t_router; d.ids_out = w.ids; d.weights_out = w.weights;
         d.nseg = c.topk + 1;
         d.seg[0] = mega_seg(pair_seg(ly.shared_gate, ly.shared_up, c.intermediate, nullptr),
-                            w.t_hidden + (size_t)c.topk * c.intermediate, &maps, H);
-        int bank_map = -1, bank_map2 = -1;
+                            w.t_hidden + (size_t)c.topk * c.intermediate);
         for (int s = 0; s < c.topk; ++s) {
             StreamSeg sg = pair_seg(ly.experts_gate, ly.experts_up, c.intermediate, nullptr);
             sg.slot = s; sg.g_per_expert = ly.experts_global_per_expert;
             sg.w_stride = (long long)c.intermediate * (H / 2);
             sg.s_stride = (long long)c.intermediate * (H / 16);
-            // the eight slots share the bank's tensor maps
-            d.seg[s + 1] = mega_seg(sg, w.t_hidden + (size_t)s * c.intermediate, s == 0 ? &maps : nullptr, H, owned);
-            if (s == 0) { bank_map = d.seg[1].map; bank_map2 = d.seg[1].map2; }
-            d.seg[s + 1].map = bank_map; d.seg[s + 1].map2 = bank_map2;
+            d.seg[s + 1] = mega_seg(sg, w.t_hidden + (size_t)s * c.intermediate);
         }
         if (!mega_finish_stream(d, grid)) return QD_ERR_UNSUPPORTED;
         // ---- E: down projections and combine.  Phase D carries the same weight pointers: its
@@ -499,8 +456,6 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
     h.row_lo = vocab_lo;
     if (!mega_finish_stream(h, grid)) return QD_ERR_UNSUPPORTED;
     out[n++] = h;
-    if (!maps.ok || (int)maps.maps.size() != program_map_count(model)) return QD_ERR_UNSUPPORTED;
-    memcpy((uint8_t*)host_out + program_map_offset(model), maps.maps.data(), maps.maps.size() * sizeof(CUtensorMap));
     return n == mega_phase_count(model) ? QD_OK : QD_ERR_ARG;
 }
 
@@ -549,7 +504,6 @@ extern "C" int qd_decode_step_persistent(const qd_model* model, const qd_state* 
         p.contrib_offset = 0;
         p.argmax_offset = exchange_contrib_bytes(c);
     }
-    p.maps = (const CUtensorMap*)((const uint8_t*)program + program_map_offset(model));
     p.wait_limit_us = g_wait_limit_us;
     p.trace = trace;
     return mega_launch(p, (cudaStream_t)stream);

@@ -146,6 +146,9 @@ class Engine:
             logits = self.step(self.ckpt, self.pending_token, self.state.position, self.state)
             self.pending_token = torch.argmax(logits)
         else:
+            watchdog = getattr(self.step, "watchdog", None)
+            if watchdog is not None:
+                watchdog.check()        # expert parallel: a lost peer raises here, before the launch
             self._decode_input.copy_(self.pending_token)
             self._device_position.fill_(self.state.position)
             self.graph.replay()

@@ -21,6 +21,8 @@ multi-GPU extension of its engine.
 from __future__ import annotations
 
 import os
+import threading
+import time
 
 import torch
 import torch.distributed as dist
@@ -42,12 +44,74 @@ def vocab_range(rank: int, world: int, vocab: int) -> tuple[int, int]:
     return rank * per, (rank + 1) * per
 
 
+class PeerLost(RuntimeError):
+    """A rank of the group stopped answering (or said goodbye) between steps."""
+
+
+class RankWatchdog:
+    """Host-side liveness of the ranks of one group, over a key-value store (a
+    ``torch.distributed`` ``TCPStore`` or anything with ``set`` / ``get`` / ``add``).
+
+    Every rank bumps its own counter from a daemon thread every ``interval`` seconds;
+    ``check()`` (called before a launch) reads every peer's counter and raises ``PeerLost``
+    when a counter has not moved for ``timeout`` seconds, when its rank has left with
+    ``leave()``, or when the store itself is gone (the rank that hosts it died).  A launch
+    that a lost peer would have stalled is therefore never issued; the bounded waits inside
+    the kernel (status bit 0) cover a peer lost in mid-step.  Nothing here touches a GPU.
+    """
+
+    def __init__(self, store, rank: int, world: int, *, interval: float = 0.05, timeout: float = 1.0):
+        self.store, self.rank, self.world = store, rank, world
+        self.interval, self.timeout = interval, timeout
+        self._stop = threading.Event()
+        self._seen = {r: (-1, time.monotonic()) for r in range(world) if r != rank}
+        self.store.add(f"qd/alive/{rank}", 1)
+        self._thread = threading.Thread(target=self._beat, name="qd-watchdog", daemon=True)
+        self._thread.start()
+
+    def _beat(self) -> None:
+        while not self._stop.wait(self.interval):
+            try:
+                self.store.add(f"qd/alive/{self.rank}", 1)
+            except Exception:       # the store is gone: check() reports it
+                return
+
+    def check(self) -> None:
+        now = time.monotonic()
+        for peer, (count, since) in self._seen.items():
+            try:
+                if int(self.store.add(f"qd/left/{peer}", 0)) > 0:
+                    raise PeerLost(f"rank {peer} left the group")
+                current = int(self.store.add(f"qd/alive/{peer}", 0))
+            except PeerLost:
+                raise
+            except Exception as error:
+                raise PeerLost(f"the group's store stopped answering ({type(error).__name__}): "
+                               f"the rank that hosts it is gone") from error
+            if current != count:
+                self._seen[peer] = (current, now)
+            elif now - since > self.timeout:
+                raise PeerLost(f"rank {peer} has not answered for {now - since:.2f} s")
+
+    def leave(self) -> None:
+        """Ordered goodbye: the peers' next ``check()`` names this rank."""
+        self._stop.set()
+        try:
+            self.store.add(f"qd/left/{self.rank}", 1)
+        except Exception:
+            pass
+
+    def stop(self) -> None:
+        self._stop.set()
+
+
 class ExpertParallelStep:
     """``step(ckpt, token_id, position, state, *, logits=True)`` over a model slice."""
 
-    def __init__(self, ckpt: Checkpoint, rank: int, world: int, group=None):
+    def __init__(self, ckpt: Checkpoint, rank: int, world: int, group=None, watchdog: RankWatchdog | None = None):
         cfg = ckpt.config
         self.rank, self.world, self.group = rank, world, group
+        self.watchdog = watchdog
         self.ckpt = ckpt
         self.vocab = vocab_range(rank, world, cfg.vocab_size)
         self.fused = FusedStep(ckpt, expert_range=expert_range(rank, world, cfg.num_experts),
@@ -74,6 +138,8 @@ class ExpertParallelStep:
 
     def __call__(self, ckpt, token_id, position, state, *, logits=True):
         assert ckpt is self.ckpt
+        if self.watchdog is not None:
+            self.watchdog.check()                 # raises PeerLost instead of launching into a stall
         out = self.fused(ckpt, token_id, position, state, logits=logits)
         if out is None or not self.gather_logits:
             return out
@@ -89,6 +155,8 @@ class ExpertParallelStep:
         """Ordered teardown: call on every rank, between steps, before the process group goes."""
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
+        if self.watchdog is not None:
+            self.watchdog.stop()
         self.fused.exchange = None
         self._keep = None
 
@@ -99,14 +167,14 @@ class ExpertParallelEngine(Engine):
     generates its own slice (pass ``ckpt=`` to supply an already sliced checkpoint)."""
 
     def __init__(self, cfg, seed: int = 0, max_context: int = 32768, device="cuda", *, ckpt=None,
-                 group=None, cuda_graph: bool = True):
+                 group=None, cuda_graph: bool = True, watchdog: RankWatchdog | None = None):
         from . import synthetic
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         if ckpt is None:
             ckpt = synthetic.make_checkpoint(cfg, seed, device,
                                              expert_range=expert_range(rank, world, cfg.num_experts),
                                              vocab_range=vocab_range(rank, world, cfg.vocab_size))
-        step = ExpertParallelStep(ckpt, rank, world, group)
+        step = ExpertParallelStep(ckpt, rank, world, group, watchdog)
         super().__init__(ckpt, max_context, str(device), "b200", cuda_graph=cuda_graph, _step_object=step)
         self.launches_per_step = step.launches_per_step
 

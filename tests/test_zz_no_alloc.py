@@ -48,6 +48,15 @@ def test_static_scratch_matches_regular_entry_point_twice(cuda_device):
         assert torch.equal(gk, wk) and torch.equal(gv, wv)
 
 
+def test_static_scratch_at_a_long_context(cuda_device):
+    """8192 cached positions: every one of the 32 context splits is many chunks long."""
+    case = _case(cuda_device, 4, capacity=8192)
+    want, wk, wv = _run("regular", case, 8191, cuda_device)
+    got, gk, gv = _run("static", case, 8191, cuda_device)
+    torch.testing.assert_close(got.float(), want.float(), rtol=0.02, atol=0.002)
+    assert torch.equal(gk, wk) and torch.equal(gv, wv)
+
+
 def test_static_scratch_rejects_oversized_shapes(cuda_device):
     from quickdraw_b200 import _lib
     from quickdraw_b200._lib import ptr, stream_of
