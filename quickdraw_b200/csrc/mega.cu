@@ -286,17 +286,25 @@ QD_DEVINL void trace_mark(const MegaParams& mp, int pi, int slot) {
     if (mp.trace) mp.trace[((size_t)pi * kTraceSlots + slot) * gridDim.x + blockIdx.x] = global_timer_ns();
 }
 
-// Slots 9..14 (thread 160 of the streaming phases): cycles since the phase was entered.
-QD_DEVINL void trace_cycles(const MegaParams& mp, int pi, int slot, long long c0) {
-    if (mp.trace) mp.trace[((size_t)pi * kTraceSlots + slot) * gridDim.x + blockIdx.x] = (unsigned long long)(clock64() - c0);
+// This block's share [lo, hi) of a streaming phase, in cost units over the concatenated segments.
+QD_DEVINL void block_cost_range(const MegaPhase& ph, unsigned& lo, unsigned& hi) {
+    if (ph.seg_blocks) {
+        const unsigned s = blockIdx.x / ph.seg_blocks, j = blockIdx.x % ph.seg_blocks;
+        const unsigned end = (min(s, (unsigned)ph.nseg - 1u) + 1u) * ph.seg_cost;
+        lo = s < (unsigned)ph.nseg ? min(s * ph.seg_cost + j * ph.block_cost, end) : end;
+        hi = min(lo + ph.block_cost, end);
+    } else {
+        lo = blockIdx.x * ph.quota + min(blockIdx.x, ph.remainder);
+        hi = (blockIdx.x + 1) * ph.quota + min(blockIdx.x + 1, ph.remainder);
+    }
 }
 
 // =========================================================================== producer
 template <int K>
 QD_DEVINL bool produce_stream(const MegaParams& mp, const MegaPhase& ph, const Smem& S, int& it) {
     bool ids_ready = false;
-    const unsigned lo = blockIdx.x * ph.quota + min(blockIdx.x, ph.remainder);
-    const unsigned hi = (blockIdx.x + 1) * ph.quota + min(blockIdx.x + 1, ph.remainder);
+    unsigned lo, hi;
+    block_cost_range(ph, lo, hi);
     unsigned seg_start = 0;
 #pragma unroll 1
     for (int i = 0; i < ph.nseg; ++i) {
@@ -518,6 +526,58 @@ QD_DEVINL void f16_scale(float top, float& down, float& up) {
     up = __uint_as_float((uint32_t)(127 + shift) << 23);
 }
 
+// Greedy choice at the end of the LM head: this block's best (value, index) over its warps, the
+// last block to arrive reduces over the blocks and, expert parallel, over the ranks (ties: lowest
+// index).  Out of line: it runs once per token, the streaming phase once per phase.
+static __device__ __noinline__ void head_argmax(const MegaParams& mp, const Smem& S, const Wait& wt, uint32_t tag_base,
+                                                float best_val, int best_idx) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float* red = S.red;
+
+    if (lane == 0) { red[32 + warp] = best_val; reinterpret_cast<int*>(red)[48 + warp] = best_idx; }
+    named_barrier(1, CT);
+    if (tid == 0) {
+        float bv = red[32]; int bi = reinterpret_cast<int*>(red)[48];
+        for (int w = 1; w < CW; ++w) {
+            const float v = red[32 + w]; const int ix = reinterpret_cast<int*>(red)[48 + w];
+            if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+        }
+        mp.best_val[blockIdx.x] = bv;
+        mp.best_idx[blockIdx.x] = bi;
+        __threadfence();
+        const unsigned int done = atomicAdd(mp.argmax_counter, 1u);
+        if (done == gridDim.x - 1) {
+            __threadfence();
+            float fv = -INFINITY; int fi = 0x7fffffff;
+            for (int b = 0; b < (int)gridDim.x; ++b) {
+                const float v = __ldcg(mp.best_val + b);
+                const int ix = __ldcg(mp.best_idx + b);
+                if (v > fv || (v == fv && ix < fi)) { fv = v; fi = ix; }
+            }
+            if (mp.world > 1) {
+                // every rank tells every rank its best (value, index); two sets alternate
+                // from launch to launch
+                const uint32_t launch = tag_base >> 6;
+                const uint32_t tag32 = (launch << 8) | 0xA5u;
+                const long long slot = mp.argmax_offset + (long long)((launch & 1u) * mp.world) * 16;
+                for (int r = 0; r < mp.world; ++r) {
+                    uint8_t* dst = reinterpret_cast<uint8_t*>(mp.peer_base[r]) + slot + (long long)mp.rank * 16;
+                    st_pair_sys(dst, __float_as_uint(fv), tag32);
+                    st_pair_sys(dst + 8, (uint32_t)fi, tag32);
+                }
+                const uint8_t* own = reinterpret_cast<const uint8_t*>(mp.peer_base[mp.rank]) + slot;
+                for (int r = 0; r < mp.world; ++r) {
+                    const float v = __uint_as_float(wait_pair(reinterpret_cast<const uint2*>(own + r * 16), tag32, wt, true));
+                    const int ix = (int)wait_pair(reinterpret_cast<const uint2*>(own + r * 16 + 8), tag32, wt, true);
+                    if (v > fv || (v == fv && ix < fi)) { fv = v; fi = ix; }
+                }
+            }
+            *mp.next_token = fi == 0x7fffffff ? 0 : fi;
+            *mp.argmax_counter = 0;
+        }
+    }
+}
+
 // ========================================================================== consumers
 // One streaming phase: activation vector -> shared memory and registers, then this block's
 // rows of the ring.  res: this thread's four elements of the bf16 residual stream.
@@ -532,13 +592,11 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
     float* red = S.red;
     const uint32_t tag = tag_base | (uint32_t)(ph.layer + 1);
     const uint32_t tag_x = ph.x_prev_layer ? tag - 1u : tag;
-    const unsigned lo = blockIdx.x * ph.quota + min(blockIdx.x, ph.remainder);
-    const unsigned hi = (blockIdx.x + 1) * ph.quota + min(blockIdx.x + 1, ph.remainder);
+    unsigned lo, hi;
+    block_cost_range(ph, lo, hi);
 
     // ---- first read of the activation words this thread needs: their trip to L2 overlaps the
     //      static loads below; they are checked, and read again if they have not arrived, later
-    const long long c0 = clock64();
-    const bool probe = tid == 160;
     uint4 xin[4];
     const int mode = KC == 2 ? ((ph.keep_x || ph.from_token) ? 0 : 1) : (ph.prologue == PRO_GATED_NORM ? 2 : 3);
     const tagged* xsrc[4] = {ph.x, ph.x, ph.x, ph.x};
@@ -591,7 +649,6 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
 
     wait_words4_n<4, true>(xsrc, xon, mode == 1 ? tag_x : tag, xin, wt);
     if (tid == 0) trace_mark(mp, pi, 6);
-    if (probe) trace_cycles(mp, pi, 9, c0);
 
     // ---- the activation vector: bf16 (for bf16 rows) and f16 (for the tensor-core rows), the
     //      f16 copy scaled down by a power of two only if it would overflow
@@ -635,7 +692,7 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             *reinterpret_cast<uint2*>(xf + tid * 8) = make_uint2(pack_f16x2(nrm[0] * down, nrm[1] * down),
                                                                  pack_f16x2(nrm[2] * down, nrm[3] * down));
             if (tid == 0) red[96] = out_mult;
-        } else if (ph.prologue == PRO_GATED_NORM) {
+        } else if (KC == 4 && ph.prologue == PRO_GATED_NORM) {
             // per-head RMSNorm of o, times gamma, times silu(z); a warp per 128-wide head, four
             // consecutive features per lane (quickdraw/models/qwen.py:161-164)
             constexpr int HPW = K / 128 / CW;
@@ -719,7 +776,6 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
     }
 
     if (tid == 0) trace_mark(mp, pi, 2);
-    if (probe) trace_cycles(mp, pi, 10, c0);
     uint32_t xh[UNITS][16];
     load_x_fragments<UNITS>(xf, warp, lane, xh);
 
@@ -752,11 +808,8 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
         for (int r0 = ra; r0 < rb; r0 += tile_rows, ++it) {
             const int n = min(tile_rows, rb - r0);
             const int st = it % NS;
-            if (first_tile && probe) trace_cycles(mp, pi, 11, c0);
             if (!mbar_wait(S.full + st, (it / NS) & 1, mp.status)) { ok = false; break; }
             if (first_tile && tid == 0) trace_mark(mp, pi, 3);
-            if (first_tile && probe) trace_cycles(mp, pi, 12, c0);
-            const bool was_first = first_tile;
             first_tile = false;
             const uint8_t* base = S.stages + (size_t)st * kStreamStageBytes;
             if (sg.kind == SEG_BF16) {
@@ -826,57 +879,11 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(S.empty + st);
-            if (was_first && probe) trace_cycles(mp, pi, 13, c0);
         }
     }
     if (tid == 0) trace_mark(mp, pi, 8);
-    if (probe) trace_cycles(mp, pi, 14, c0);
     if (!ok && lane == 0) *S.abort = 1;
-    // ---- greedy argmax over this rank's logits (ties: lowest index), then over the ranks
-    if (KC == 2 && ph.argmax) {
-        if (lane == 0) { red[32 + warp] = best_val; reinterpret_cast<int*>(red)[48 + warp] = best_idx; }
-        named_barrier(1, CT);
-        if (tid == 0) {
-            float bv = red[32]; int bi = reinterpret_cast<int*>(red)[48];
-            for (int w = 1; w < CW; ++w) {
-                const float v = red[32 + w]; const int ix = reinterpret_cast<int*>(red)[48 + w];
-                if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
-            }
-            mp.best_val[blockIdx.x] = bv;
-            mp.best_idx[blockIdx.x] = bi;
-            __threadfence();
-            const unsigned int done = atomicAdd(mp.argmax_counter, 1u);
-            if (done == gridDim.x - 1) {
-                __threadfence();
-                float fv = -INFINITY; int fi = 0x7fffffff;
-                for (int b = 0; b < (int)gridDim.x; ++b) {
-                    const float v = __ldcg(mp.best_val + b);
-                    const int ix = __ldcg(mp.best_idx + b);
-                    if (v > fv || (v == fv && ix < fi)) { fv = v; fi = ix; }
-                }
-                if (mp.world > 1) {
-                    // every rank tells every rank its best (value, index); two sets alternate
-                    // from launch to launch
-                    const uint32_t launch = tag_base >> 6;
-                    const uint32_t tag32 = (launch << 8) | 0xA5u;
-                    const long long slot = mp.argmax_offset + (long long)((launch & 1u) * mp.world) * 16;
-                    for (int r = 0; r < mp.world; ++r) {
-                        uint8_t* dst = reinterpret_cast<uint8_t*>(mp.peer_base[r]) + slot + (long long)mp.rank * 16;
-                        st_pair_sys(dst, __float_as_uint(fv), tag32);
-                        st_pair_sys(dst + 8, (uint32_t)fi, tag32);
-                    }
-                    const uint8_t* own = reinterpret_cast<const uint8_t*>(mp.peer_base[mp.rank]) + slot;
-                    for (int r = 0; r < mp.world; ++r) {
-                        const float v = __uint_as_float(wait_pair(reinterpret_cast<const uint2*>(own + r * 16), tag32, wt, true));
-                        const int ix = (int)wait_pair(reinterpret_cast<const uint2*>(own + r * 16 + 8), tag32, wt, true);
-                        if (v > fv || (v == fv && ix < fi)) { fv = v; fi = ix; }
-                    }
-                }
-                *mp.next_token = fi == 0x7fffffff ? 0 : fi;
-                *mp.argmax_counter = 0;
-            }
-        }
-    }
+    if (KC == 2 && ph.argmax) head_argmax(mp, S, wt, tag_base, best_val, best_idx);
 }
 
 // Gated delta-rule recurrence (quickdraw/models/qwen.py:139-160) for 128-wide key heads:

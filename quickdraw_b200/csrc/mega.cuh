@@ -51,6 +51,10 @@ struct alignas(16) MegaPhase {
     int keep_x;               // x is the vector the previous streaming phase built
     int x_prev_layer;         // x carries the tag of the layer before (the MoE output)
     unsigned quota, remainder;   // total cost = quota * grid + remainder
+    // equal segments (the routed gate/up phase): segment s belongs to blocks [s * seg_blocks,
+    // (s + 1) * seg_blocks), block_cost of its seg_cost each, so that no block straddles two
+    // experts and every block's share is whole tiles; seg_blocks == 0: the cost partition above
+    unsigned seg_blocks, seg_cost, block_cost, pad1;
     int g_per_expert, argmax;
     int row_lo, pad0;         // LM head: vocabulary index of the segment's first row (this rank's shard)
     // streaming phases

@@ -300,6 +300,21 @@ bool mega_finish_stream(MegaPhase& ph, int grid) {
     if (total + 1024 >= 0xffffffffull) return false;
     ph.quota = (unsigned)(total / grid);
     ph.remainder = (unsigned)(total % grid);
+    // Equal NVFP4 pair segments (shared expert + routed slots): a group of blocks per segment,
+    // whole 16-pair tiles per block.  A block that straddles two experts would run a partial tile
+    // of each, one tile more than its neighbours, and the phase ends with its slowest block.
+    ph.seg_blocks = ph.seg_cost = ph.block_cost = 0;
+    bool equal = ph.nseg > 1 && ph.nseg <= grid;
+    for (int i = 0; i < ph.nseg && equal; ++i)
+        equal = ph.seg[i].kind == SEG_FP4_PAIR && ph.seg[i].rows == ph.seg[0].rows;
+    if (equal) {
+        const unsigned blocks = (unsigned)(grid / ph.nseg), rows = (unsigned)ph.seg[0].rows;
+        unsigned per = (rows + blocks - 1) / blocks;
+        per = (per + 15) / 16 * 16;                      // pairs per block: whole tiles
+        ph.seg_blocks = blocks;
+        ph.seg_cost = rows * 2 * fp4_row;
+        ph.block_cost = per * 2 * fp4_row;
+    }
     return true;
 }
 
