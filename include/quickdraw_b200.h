@@ -62,6 +62,26 @@ int qd_nvfp4_matmul(const void* x, const void* codes, const void* scales, const 
                     int tokens, int out_features, int in_features, int group_size,
                     unsigned int* status, void* stream);
 
+/* Activation quantiser of the FP4 x FP4 ("W4A4") product that quickdraw's todo.md:13 asks to
+ * validate separately from the W4A16 path: x bf16 [tokens, in_features] -> E2M1 codes
+ * [tokens, in_features / 2] (low nibble = even input), one E4M3 scale per sixteen inputs
+ * [tokens, in_features / 16] and one fp32 scale for the chunk, i.e. the NVFP4Linear layout of
+ * quickdraw/models/weights.py:29-47 for the activation operand.  global = amax / (6 * 448),
+ * block scale = e4m3(block amax / (6 global)), code = e2m1(x / (scale * global)), all round to
+ * nearest even.  amax_scratch: one device word.  in_features % 16 == 0, 16-byte aligned pointers. */
+int qd_nvfp4_quantize_act(const void* x, int tokens, int in_features, void* codes, void* scales,
+                          float* global, unsigned int* amax_scratch, void* stream);
+
+/* matmul with both operands NVFP4 on the block-scaled tensor core (tcgen05.mma kind::mxf4nvf4,
+ * one E4M3 scale per sixteen inputs of either operand read from tensor memory): y[t, n] =
+ * bf16( x_global * w_global * sum_k xq[t, k] * wq[n, k] ), fp32 accumulation in tensor memory.
+ * The prefill projection of quickdraw/kernel/triton/matvec.py:118-163 with the activations
+ * quantised by qd_nvfp4_quantize_act.  in_features % 256 == 0, out_features % 128 == 0,
+ * pointers 16-byte aligned.  status: device word, bit 0 is set if a bounded wait ran out. */
+int qd_nvfp4_matmul_w4a4(const void* x_codes, const void* x_scales, const float* x_global,
+                         const void* w_codes, const void* w_scales, const float* w_global, void* y,
+                         int tokens, int out_features, int in_features, unsigned int* status, void* stream);
+
 /* grouped_matmul(x, bank, grouping, routing=None) for the routed experts of a chunk of tokens —
  * quickdraw/kernel/triton/moe.py:99-151.  Routes are the (token, slot) pairs of the chunk
  * sorted by expert (stable): order[r] = route index of sorted row r, rows [boundaries[e],

@@ -119,6 +119,40 @@ def matmul(x: torch.Tensor, proj: NVFP4Linear) -> torch.Tensor:
     return out
 
 
+def quantize_act(x: torch.Tensor):
+    """bf16 [tokens, in] -> the activation operand of the FP4 x FP4 product: (codes uint8
+    [tokens, in/2], E4M3 block scales [tokens, in/16], fp32 tensor scale), the layout of an
+    ``NVFP4Linear`` (quickdraw/models/weights.py:29-47); every rounding to nearest even."""
+    assert x.is_cuda and x.dtype == BF16 and x.ndim == 2 and x.is_contiguous() and x.shape[1] % 16 == 0
+    tokens, width = x.shape
+    codes = torch.empty((tokens, width // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((tokens, width // 16), dtype=torch.float8_e4m3fn, device=x.device)
+    scale_2 = torch.empty((), dtype=torch.float32, device=x.device)
+    scratch = torch.empty(1, dtype=torch.int32, device=x.device)
+    call("qd_nvfp4_quantize_act", ptr(x), tokens, width, ptr(codes), ptr(scales), ptr(scale_2), ptr(scratch), stream_of(x))
+    return codes, scales, scale_2
+
+
+def matmul_w4a4(xq, proj: NVFP4Linear) -> torch.Tensor:
+    """Quantised activations (``quantize_act``) times a packed NVFP4 matrix on the block-scaled
+    FP4 tensor core: neither operand is expanded.  Differs from ``matmul`` by the activation
+    rounding only (the W4A4 variant quickdraw's notes ask to validate separately from W4A16);
+    in_features a multiple of 256, out_features a multiple of 128."""
+    codes, scales, scale_2 = xq
+    assert isinstance(proj, NVFP4Linear) and proj.weight.ndim == 2 and proj.group_size == 16
+    assert codes.is_cuda and codes.dtype == torch.uint8 and codes.is_contiguous() and scales.is_contiguous()
+    assert codes.shape[1] * 2 == proj.in_features and proj.in_features % 256 == 0 and proj.out_features % 128 == 0
+    assert proj.weight.is_contiguous() and proj.weight_scale.is_contiguous() and proj.weight_scale_2.numel() == 1
+    status = _matmul_status.get(codes.device)
+    if status is None:
+        status = _matmul_status[codes.device] = torch.zeros(1, dtype=torch.int32, device=codes.device)
+    out = torch.empty((codes.shape[0], proj.out_features), dtype=BF16, device=codes.device)
+    call("qd_nvfp4_matmul_w4a4", ptr(codes), ptr(scales), ptr(scale_2), ptr(proj.weight), ptr(proj.weight_scale),
+         ptr(proj.weight_scale_2), ptr(out), codes.shape[0], proj.out_features, proj.in_features, ptr(status),
+         stream_of(codes))
+    return out
+
+
 def matmul_status(device) -> int:
     """Status word of the tensor-core matmul on ``device`` (0 = clean; bit 0 = a bounded wait ran out)."""
     status = _matmul_status.get(torch.device(device))

@@ -43,3 +43,47 @@ def test_two_dimensional_input_takes_the_matmul_path(cuda_device):
     for t in range(5):
         single = kernels.nvfp4_gemv(x[t].to(cuda_device), dev_proj).cpu()
         torch.testing.assert_close(chunk[t].float(), single.float(), rtol=0.025, atol=0.003)
+
+
+W4A4_SHAPES = [(1, 128, 256), (7, 256, 512), (128, 256, 2048), (129, 1024, 2048), (300, 2048, 4096), (515, 512, 2048)]
+
+
+@pytest.mark.parametrize("tokens,width", [(1, 256), (5, 2048), (130, 4096), (64, 512)])
+def test_activation_quantiser_is_bit_exact(cuda_device, tokens, width):
+    """Codes, block scales and tensor scale of the activation operand against the oracle's
+    restatement: identical bytes (round to nearest even everywhere), incl. an all-zero block,
+    a block of equal magnitudes and values on rounding ties."""
+    from quickdraw_b200 import kernels
+    src = synthetic.Source(31, "cpu")
+    x = src.normal(f"x{tokens}x{width}", tokens, width)
+    x[0, :16] = 0
+    x[0, 16:32] = 0.375
+    x[-1, -16:] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0])
+    codes, scales, g = kernels.quantize_act(x.to(cuda_device))
+    want_codes, want_scales, want_g = O.quantize_act_nvfp4(x)
+    assert float(g.cpu()) == float(want_g)
+    assert torch.equal(scales.cpu().view(torch.uint8), want_scales)
+    assert torch.equal(codes.cpu(), want_codes)
+    # the quantised chunk is the input within FP4's resolution
+    back = O.dequantize_act_nvfp4(want_codes, want_scales, want_g) * want_g
+    assert O.rel_l2(back, x.float()) < 0.12
+
+
+@pytest.mark.parametrize("tokens,out_features,in_features", W4A4_SHAPES)
+def test_w4a4_matmul_matches_oracle(cuda_device, tokens, out_features, in_features):
+    """The block-scaled FP4 x FP4 product against the oracle's product of the same quantised
+    operands (fp32-accumulation tolerance), and its distance from the exact W4A16 product (the
+    activation rounding: about one tenth relative L2 for Gaussian inputs)."""
+    from quickdraw_b200 import kernels
+    src = synthetic.Source(32, "cpu")
+    proj = src.nvfp4(f"w{out_features}x{in_features}", out_features, in_features, global_scale=0.75)
+    x = src.normal(f"x{tokens}", tokens, in_features)
+    xq = kernels.quantize_act(x.to(cuda_device))
+    got = kernels.matmul_w4a4(xq, to_device(proj, cuda_device)).cpu()
+    assert kernels.matmul_status(cuda_device) == 0
+    want = O.nvfp4_matmul_w4a4(*O.quantize_act_nvfp4(x), proj)
+    assert got.shape == want.shape
+    torch.testing.assert_close(got.float(), want.float(), rtol=0.02, atol=0.002)
+    assert O.rel_l2(got, want) < 2e-3
+    exact = O.nvfp4_matmul(x, proj)
+    assert O.rel_l2(got, exact) < 0.2
