@@ -51,7 +51,7 @@ CONFIG1_BYTES = 1024 * 1024 + 1024 * 128 + 4 + 4096 + 2048     # weights + x + y
 # DRAM bytes (read + write) of one token step: captured with ncu on an 8-layer model of the
 # same widths (a full-size capture would hold 24 GB through the replay passes) and scaled to
 # the full model by the algorithmic bytes, to which it is proportional.
-STEP_TRAFFIC_RATIO = 1.049       # ncu: (dram read + write) / algorithmic bytes of one persistent launch
+STEP_TRAFFIC_RATIO = 1.035       # ncu: (dram read + write) / algorithmic bytes of one persistent launch
 
 
 def measured_peaks():
@@ -301,6 +301,32 @@ def prefill_gemm_roofline(device, tokens=8192, rows=8192, width=2048, reps=10):
     return 2.0 * tokens * rows * width / per_launch_s / 1e12, per_launch_s
 
 
+def w4a4_gemm_roofline(device, tokens=8192, rows=8192, width=2048, reps=10):
+    """The same projection with BOTH operands NVFP4 on the block-scaled FP4 tensor core
+    (tcgen05 kind::mxf4nvf4): the activation chunk quantised once (timed apart), weights and
+    activations multiplied without any expansion.  Returns TFLOP/s and seconds of the product,
+    and seconds of the quantiser."""
+    from quickdraw_b200 import kernels, synthetic
+    src = synthetic.Source(2, device)
+    proj = src.nvfp4("prefill.w", rows, width)
+    x = src.normal("prefill.x", tokens, width)
+    xq = kernels.quantize_act(x)
+    out = {}
+    for name, fn in (("product", lambda: kernels.matmul_w4a4(xq, proj)), ("quantiser", lambda: kernels.quantize_act(x))):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        out[name] = e0.elapsed_time(e1) * 1e-3 / reps
+    assert kernels.matmul_status(device) == 0
+    return 2.0 * tokens * rows * width / out["product"] / 1e12, out["product"], out["quantiser"]
+
+
 def attention_leg(cfg, device, context, peak, reps=24):
     """Decode attention alone (the split-context kernel of the operator table) at one context
     length: 16 query / 2 KV heads of 256, bf16 cache ~ N(0, 1); the caches rotate over more than
@@ -484,6 +510,7 @@ def run_gpu(args):
     else:
         mv_gbs, mv_launch_s, mv_units = matvec_roofline(device)
     gemm_tflops, gemm_launch_s = prefill_gemm_roofline(device)
+    w4a4_tflops, w4a4_launch_s, w4a4_quant_s = w4a4_gemm_roofline(device)
     tensor_peak, tensor_peak_kind = measured_tensor_peak()
     batch_leg = legs = None
     if world == 1:
@@ -530,6 +557,14 @@ def run_gpu(args):
                                   "achieved": gemm_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
                                   "frac": gemm_tflops / tensor_peak, "peak_source": f"{tensor_peak_kind} cuBLAS bf16",
                                   "launch_us": gemm_launch_s * 1e6},
+        # both operands NVFP4 (activations quantised per chunk): no measured FP4 peak exists on this
+        # pool, so the fraction is given against the measured bf16 burst (the nominal FP4 dense
+        # rate is four times the bf16 one) and against the nominal 9 PFLOP/s
+        "w4a4_gemm_roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_w4a4_kernel (tcgen05 kind::mxf4nvf4, 8192 tokens x [8192, 2048])",
+                               "achieved": w4a4_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
+                               "frac": w4a4_tflops / tensor_peak, "peak_source": f"{tensor_peak_kind} cuBLAS bf16",
+                               "frac_of_nominal_fp4": w4a4_tflops / 9000.0, "launch_us": w4a4_launch_s * 1e6,
+                               "quantiser_us": w4a4_quant_s * 1e6},
         # widening row: batch-32 decode with per-sequence KV and DeltaNet state (tok/s over all
         # sequences); not part of `value`
         "batch_decode": batch_leg,

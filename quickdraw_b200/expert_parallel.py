@@ -177,6 +177,10 @@ class ExpertParallelEngine(Engine):
         step = ExpertParallelStep(ckpt, rank, world, group, watchdog)
         super().__init__(ckpt, max_context, str(device), "b200", cuda_graph=cuda_graph, _step_object=step)
         self.launches_per_step = step.launches_per_step
+        # prompts in chunks through the sequence kernels, the routed experts split over the ranks
+        from .prefill import ChunkPrefill
+        self.chunk_prefill = ChunkPrefill(ckpt, expert_range=expert_range(rank, world, ckpt.config.num_experts), group=group)
+        self.sequence_prefill = True
 
     def close(self) -> None:
         self.graph = None

@@ -24,14 +24,24 @@ BF16 = torch.bfloat16
 
 
 class ChunkPrefill:
-    def __init__(self, ckpt: Checkpoint):
+    """``expert_range`` / ``group``: expert parallel.  The checkpoint holds the banks of experts
+    [lo, hi) only; every rank routes all tokens (the router is replicated), multiplies the routes
+    of its own experts and leaves zero rows for the others; one all-reduce per layer moves the
+    bf16 contribution rows (every row has exactly one writer, so the sum is a copy) and every
+    rank combines them in ascending expert id like a single GPU."""
+
+    def __init__(self, ckpt: Checkpoint, expert_range: tuple[int, int] | None = None, group=None):
         c = ckpt.config
         self.ckpt, self.device = ckpt, ckpt.embed_tokens.device
+        self.expert_range = expert_range or (0, c.num_experts)
+        self.sliced = self.expert_range != (0, c.num_experts)
+        self.group = group
         self.gammas = [((1 + layer.input_layernorm.float()).contiguous(),
                         (1 + layer.post_attention_layernorm.float()).contiguous()) for layer in ckpt.layers]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         for layer in ckpt.layers:
-            assert layer.moe.experts_gate.weight.shape[0] == c.num_experts, "the whole model on one GPU"
+            assert layer.moe.experts_gate.weight.shape[0] == self.expert_range[1] - self.expert_range[0], \
+                "the expert banks must hold exactly the owned range"
 
     # ------------------------------------------------------------------ building blocks
     def _empty(self, *shape, dtype=BF16):
@@ -62,7 +72,8 @@ class ChunkPrefill:
         return out
 
     def _grouped(self, x, bank: NVFP4Linear, order, boundaries, routes, topk, *, routing=None, by_token, scatter):
-        out = self._empty(routes, bank.out_features)
+        # rows of experts another rank owns stay zero in the scattered (route-order) output
+        out = (torch.zeros if self.sliced and scatter else torch.empty)((routes, bank.out_features), dtype=BF16, device=self.device)
         call("qd_nvfp4_grouped_matmul", ptr(x), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
              ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, bank.weight.shape[0], topk,
              bank.out_features, bank.in_features, bank.group_size, int(by_token), int(scatter),
@@ -119,11 +130,16 @@ class ChunkPrefill:
         order = self._empty(routes, dtype=torch.int32)
         boundaries = self._empty(c.num_experts + 1, dtype=torch.int32)
         call("qd_seq_group_routes", ptr(ids), routes, c.num_experts, ptr(order), ptr(boundaries), stream_of(x))
+        if self.sliced:      # this rank's experts: their slice of the boundaries, indices local to the bank
+            boundaries = boundaries[self.expert_range[0]:self.expert_range[1] + 1]
         gate = self._grouped(x, w.experts_gate, order, boundaries, routes, topk, by_token=True, scatter=False)
         up = self._grouped(x, w.experts_up, order, boundaries, routes, topk, by_token=True, scatter=False)
         hidden = self._swiglu(gate, up)
         contributions = self._grouped(hidden, w.experts_down, order, boundaries, routes, topk,
                                       routing=weights.flatten(), by_token=False, scatter=True)
+        if self.sliced:
+            import torch.distributed as dist
+            dist.all_reduce(contributions, group=self.group)
         shared_hidden = self._swiglu(self._matmul(x, w.shared_gate), self._matmul(x, w.shared_up))
         shared = self._matmul(shared_hidden, w.shared_down)
         out = torch.empty_like(x)

@@ -40,7 +40,7 @@ cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
 engine = ExpertParallelEngine(cfg, seed=11, max_context=64, device=f"cuda:{rank}")
 engine.state.kv_k.zero_()
 engine.state.kv_v.zero_()
-tokens = engine.generate(prompt, steps)            # prompt token by token, then the captured graph
+tokens = engine.generate(prompt, steps)            # prompt through the chunked prefill, then the captured graph
 print("rank", rank, "generated", flush=True)
 # the full logits of the last prompt token, gathered from the ranks' vocabulary shards
 engine.reset()
@@ -70,15 +70,16 @@ def _free_port():
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_generation_matches_single_gpu(world):
     """Tokens and the gathered logits of the expert-parallel engine are the single GPU's, bit
-    for bit: every rank adds the same eight bf16 contribution rows in the same order."""
+    for bit: every rank adds the same eight bf16 contribution rows in the same order, in the
+    chunked prefill of the prompt (one all-reduce of the contribution rows per layer) as in the
+    one-launch decode step (rows stored into every rank's exchange area)."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from quickdraw_b200 import synthetic
     from quickdraw_b200.engine import Engine
-    prompt, steps = [5, 1900, 77, 1033], 24
+    prompt, steps = [5, 1900, 77, 1033, 8, 640, 12, 2001, 333, 90, 1500, 41, 7, 7, 1999, 250, 3], 24
     cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
-    single = Engine(synthetic.make_checkpoint(cfg, seed=11, device="cuda:0"), max_context=64, device="cuda:0",
-                    sequence_prefill=False)      # the ranks run the prompt token by token too
+    single = Engine(synthetic.make_checkpoint(cfg, seed=11, device="cuda:0"), max_context=64, device="cuda:0")
     single.state.kv_k.zero_()
     single.state.kv_v.zero_()
     want = single.generate(prompt, steps)
