@@ -394,12 +394,12 @@ def kernel_legs(engine, ckpt, cfg, device, peak):
     }
 
 
-def batch_decode_leg(ckpt, cfg, device, batch=32, context=8192, steps=8, warmup=2):
+def batch_decode_leg(ckpt, cfg, device, batch=32, context=8192, steps=8, warmup=2, slices=None, group=None):
     """Small-batch decode with per-sequence state: `batch` sequences that each hold `context`
     tokens (caches filled with N(0,1) values, as the attention configuration of the baseline
     does), one token per sequence per step; device-timed."""
     from quickdraw_b200.batch import BatchDecode, BatchState
-    decoder = BatchDecode(ckpt)
+    decoder = BatchDecode(ckpt, **(slices or {}), group=group)
     state = BatchState(cfg, batch, context + warmup + steps, device)
     state.kv_k.normal_()
     state.kv_v.normal_()
@@ -417,8 +417,13 @@ def batch_decode_leg(ckpt, cfg, device, batch=32, context=8192, steps=8, warmup=
     torch.cuda.synchronize(device)
     assert decoder.check() == 0
     ms = e0.elapsed_time(e1) / steps
+    if slices:      # every rank runs the same sequences: the slowest rank's time counts
+        worst = torch.tensor([ms], device=device)
+        torch.distributed.all_reduce(worst, op=torch.distributed.ReduceOp.MAX, group=group)
+        ms = float(worst.item())
     return {"batch": batch, "context": context, "steps": steps, "ms_per_step": ms, "tok_s": batch / (ms * 1e-3),
-            "state_bytes": state.memory_bytes(), "path": "tensor-core products with %d rows + batched state kernels" % batch}
+            "state_bytes": state.memory_bytes(), "path": "tensor-core products with %d rows + batched state kernels" % batch
+            + (", routed experts and LM head split over the ranks" if slices else "")}
 
 
 def run_gpu(args):
@@ -501,6 +506,11 @@ def run_gpu(args):
         torch.distributed.all_reduce(lo, op=torch.distributed.ReduceOp.MIN)
         torch.distributed.all_reduce(hi, op=torch.distributed.ReduceOp.MAX)
         tokens_match = bool(torch.equal(lo, hi))
+        # the batch-32 leg under expert parallelism: every rank steps the same 32 sequences
+        from quickdraw_b200.expert_parallel import expert_range, vocab_range
+        ep_batch_leg = batch_decode_leg(engine.ckpt, cfg, device, slices={
+            "expert_range": expert_range(rank, world, cfg.num_experts),
+            "vocab_range": vocab_range(rank, world, cfg.vocab_size)})
         engine.close()
     if rank != 0:
         return
@@ -512,7 +522,7 @@ def run_gpu(args):
     gemm_tflops, gemm_launch_s = prefill_gemm_roofline(device)
     w4a4_tflops, w4a4_launch_s, w4a4_quant_s = w4a4_gemm_roofline(device)
     tensor_peak, tensor_peak_kind = measured_tensor_peak()
-    batch_leg = legs = None
+    batch_leg, legs = (ep_batch_leg if world > 1 else None), None
     if world == 1:
         legs = kernel_legs(engine, ckpt, cfg, device, peak)
         batch_leg = batch_decode_leg(ckpt, cfg, device)

@@ -51,8 +51,13 @@ class BatchState:
 class BatchDecode(ChunkPrefill):
     """``step(tokens[B], state)`` -> (next tokens [B] int64, logits [B, vocab] bf16)."""
 
-    def __init__(self, ckpt: Checkpoint):
-        super().__init__(ckpt)
+    def __init__(self, ckpt: Checkpoint, expert_range: tuple[int, int] | None = None,
+                 vocab_range: tuple[int, int] | None = None, group=None):
+        """``expert_range`` / ``vocab_range`` / ``group``: expert parallel (the checkpoint is this
+        rank's slice): the routed experts as in ``ChunkPrefill``, the LM head by vocabulary rows
+        with one all-gather of the logit shards."""
+        super().__init__(ckpt, expert_range=expert_range, group=group)
+        self.vocab_range = vocab_range
         c = ckpt.config
         self.final_gamma = (1 + ckpt.final_norm.float()).contiguous()
         self._scratch = None
@@ -128,5 +133,11 @@ class BatchDecode(ChunkPrefill):
             x = self._moe(layer.moe, normed)
         final, _ = self._add_norm(x, residual, self.final_gamma, c.rms_norm_eps)
         logits = self._small(final, self.ckpt.lm_head)
+        if self.vocab_range is not None and logits.shape[1] != c.vocab_size:
+            import torch.distributed as dist
+            world = dist.get_world_size(self.group)
+            shards = torch.empty((world, *logits.shape), dtype=logits.dtype, device=logits.device)
+            dist.all_gather_into_tensor(shards, logits.contiguous(), group=self.group)
+            logits = shards.permute(1, 0, 2).reshape(logits.shape[0], c.vocab_size)
         state.positions += 1
         return logits.float().argmax(dim=-1), logits

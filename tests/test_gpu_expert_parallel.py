@@ -49,10 +49,20 @@ engine.state.kv_v.zero_()
 with torch.inference_mode():
     for position, token in enumerate(prompt):
         logits = engine.step(engine.ckpt, torch.tensor(token, device=f"cuda:{rank}"), position, engine.state)
+# three sequences stepped together (the batched decode), experts and LM head split the same way
+from quickdraw_b200.batch import BatchDecode, BatchState
+from quickdraw_b200.expert_parallel import expert_range, vocab_range
+batch = BatchDecode(engine.ckpt, expert_range=expert_range(rank, world, cfg.num_experts),
+                    vocab_range=vocab_range(rank, world, cfg.vocab_size))
+sequences = BatchState(cfg, 3, 64, f"cuda:{rank}")
+fed = torch.tensor([5, 77, 1900], device=f"cuda:{rank}")
+for _ in range(3):
+    fed, batch_logits = batch.step(fed, sequences)
 torch.cuda.synchronize()
 with open(os.path.join(outdir, f"rank{rank}.json"), "w") as f:
     json.dump({"tokens": tokens, "status": engine.fused.status(), "launches": engine.launches_per_step,
-               "logits": logits.float().cpu().tolist()}, f)
+               "logits": logits.float().cpu().tolist(), "batch_logits": batch_logits.float().cpu().tolist(),
+               "batch_status": batch.check()}, f)
 # ordered teardown: every rank is between steps; the exchange areas go before the group does
 engine.close()
 dist.barrier()
@@ -90,7 +100,14 @@ def test_generation_matches_single_gpu(world):
         for position, token in enumerate(prompt):
             want_logits = single.step(single.ckpt, torch.tensor(token, device="cuda:0"), position, single.state)
     want_logits = want_logits.float().cpu().tolist()
-    del single
+    from quickdraw_b200.batch import BatchDecode, BatchState
+    batch = BatchDecode(single.ckpt)
+    sequences = BatchState(cfg, 3, 64, "cuda:0")
+    fed = torch.tensor([5, 77, 1900], device="cuda:0")
+    for _ in range(3):
+        fed, batch_logits = batch.step(fed, sequences)
+    want_batch = batch_logits.float().cpu().tolist()
+    del single, batch, sequences
     torch.cuda.empty_cache()
     env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     with tempfile.TemporaryDirectory() as outdir:
@@ -121,6 +138,8 @@ def test_generation_matches_single_gpu(world):
         assert out[r]["launches"] == 1, "the expert-parallel step is one launch per token"
         assert out[r]["tokens"] == want, f"rank {r}: {out[r]['tokens']} vs single GPU {want}"
         assert out[r]["logits"] == want_logits, f"rank {r}: gathered logits differ from the single GPU's"
+        assert out[r]["batch_status"] == 0
+        assert out[r]["batch_logits"] == want_batch, f"rank {r}: batched-decode logits differ from the single GPU's"
 
 
 def test_a_wait_that_nothing_answers_runs_out_and_the_next_call_works(cuda_device):
