@@ -137,6 +137,16 @@ class Engine:
             self.state.position += 1
         return logits
 
+    @classmethod
+    def from_pretrained(cls, path: str, **kwargs) -> "Engine":
+        """Load a checkpoint directory (safetensors shards), merge the static FP8 scales of the
+        projections that share an activation, and build the engine (reference:
+        quickdraw/engine/engine.py:85-90)."""
+        from .loader import load_checkpoint, merge_fp8_scales
+        ckpt = load_checkpoint(path, device=kwargs.get("device", "cuda"))
+        merge_fp8_scales(ckpt)
+        return cls(ckpt, **kwargs)
+
     @torch.inference_mode()
     def decode_step(self) -> torch.Tensor:
         """Process the pending token, select and return its successor (0-d int64)."""
