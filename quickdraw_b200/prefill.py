@@ -30,6 +30,8 @@ class ChunkPrefill:
     bf16 contribution rows (every row has exactly one writer, so the sum is a copy) and every
     rank combines them in ascending expert id like a single GPU."""
 
+    sliced, group, expert_range = False, None, None      # defaults of a whole model on one GPU
+
     def __init__(self, ckpt: Checkpoint, expert_range: tuple[int, int] | None = None, group=None):
         c = ckpt.config
         self.ckpt, self.device = ckpt, ckpt.embed_tokens.device
