@@ -251,7 +251,7 @@ def workload_config(cfg, world, prompt=PROMPT_LEN):
 
 
 # ----------------------------------------------------------------------- GPU benchmark
-def matvec_roofline(device, rows=131072, width=2048, mats=2, reps=10):
+def matvec_roofline(device, rows=131072, width=2048, mats=2, reps=10, kernel=0):
     """The NVFP4 streaming matvec kernel alone: `mats` distinct [rows, width] matrices
     (2 x 151 MB by default, more than L2), one launch each, alternating.  A launch does
     rows / 1024 units of the single-matvec configuration ([1024, 2048])."""
@@ -264,7 +264,7 @@ def matvec_roofline(device, rows=131072, width=2048, mats=2, reps=10):
 
     def launch(i):
         call("qd_nvfp4_gemv", ptr(x), ptr(bank.weight[i]), ptr(bank.weight_scale[i]), ptr(bank.weight_scale_2),
-             None, ptr(y[i]), rows, width, 16, 0, stream_of(x))
+             None, ptr(y[i]), rows, width, 16, kernel, stream_of(x))
     for i in range(3 * mats):
         launch(i % mats)
     torch.cuda.synchronize(device)
@@ -381,16 +381,34 @@ def kernel_legs(engine, ckpt, cfg, device, peak):
         nbytes = sum(phases[k]["bytes"] for k in kinds if k in phases)
         return {"what": what, "us": us, "bytes": nbytes, "achieved": nbytes / us / 1e3 if us else None, "peak": peak,
                 "unit": "GB/s", "frac": nbytes / us / 1e3 / peak if us else None}
+    def attention_phase(context):
+        """The attention phases of the token-step kernel (the product path) with `context` cached
+        positions: a traced step at position context - 1 on a state of that capacity whose caches
+        hold N(0, 1) values; mean over the model's attention layers."""
+        from quickdraw_b200.state import DecodeState
+        state = DecodeState.allocate(cfg, context, device)
+        state.kv_k.normal_()
+        state.kv_v.normal_()
+        for _ in range(2):
+            engine.fused(ckpt, engine.pending_token, context - 1, state, logits=False)
+        long_marks = traced_step(engine.fused, ckpt, engine.pending_token, context - 1, state)
+        ph = phase_summary(cfg, long_marks, context - 1)
+        us, nbytes = ph["Ma"]["us"] + ph["Na"]["us"], ph["Ma"]["bytes"]
+        return {"what": "split-context attention + merge phases of the token-step kernel, %d cached positions" % context,
+                "us": us, "bytes": nbytes, "achieved": nbytes / us / 1e3, "peak": peak, "unit": "GB/s", "frac": nbytes / us / 1e3 / peak}
     return {
         "source": "timestamps inside the token-step kernel, one traced step at position %d" % position,
+        "attention_phase_8192": attention_phase(8192),
+        "attention_phase_32768": attention_phase(32768),
         "moe_layer": leg(["C", "D", "E"], "router + gate/up + down/combine phases of one layer (256 experts, top-8 + shared)"),
         "deltanet_step": leg(["M"], "gated-DeltaNet recurrence of one layer: fp32 state [32,128,128] read + written"),
         "deltanet_in_projections": leg(["A"], "qkv + z + a/b projections with the short convolution"),
         "out_projection": leg(["B"], "gated norm + out projection (4096 inputs)"),
         "attention_layer_core": leg(["Ma", "Na"], "split-context attention + merge of one layer at this position"),
         "lm_head": leg(["H"], "final norm + bf16 LM head + greedy argmax"),
-        "attention_8192": attention_leg(cfg, device, 8192, peak),
-        "attention_32768": attention_leg(cfg, device, 32768, peak),
+        # the operator-table kernel (composed path, cross-check), not on the product path
+        "attention_operator_8192": attention_leg(cfg, device, 8192, peak),
+        "attention_operator_32768": attention_leg(cfg, device, 32768, peak),
     }
 
 
@@ -515,10 +533,8 @@ def run_gpu(args):
     if rank != 0:
         return
     peak, peak_kind = measured_peaks()
-    if args.matvec_rows:
-        mv_gbs, mv_launch_s, mv_units = matvec_roofline(device, rows=args.matvec_rows)
-    else:
-        mv_gbs, mv_launch_s, mv_units = matvec_roofline(device)
+    mv_gbs, mv_launch_s, mv_units = matvec_roofline(device, rows=args.matvec_rows or 131072)
+    stream_gbs, stream_launch_s, _ = matvec_roofline(device, rows=args.matvec_rows or 131072, kernel=2)
     gemm_tflops, gemm_launch_s = prefill_gemm_roofline(device)
     w4a4_tflops, w4a4_launch_s, w4a4_quant_s = w4a4_gemm_roofline(device)
     tensor_peak, tensor_peak_kind = measured_tensor_peak()
@@ -563,6 +579,10 @@ def run_gpu(args):
         "matvec_roofline": {"kernel": "nvfp4_umma_matvec_kernel (tcgen05 kind::mxf4nvf4, %d x [1024,2048] per launch, 2 matrices alternating)" % mv_units,
                             "achieved": mv_gbs, "peak": peak, "unit": "GB/s", "frac": mv_gbs / peak,
                             "launch_us": mv_launch_s * 1e6, "bytes_per_launch": mv_units * CONFIG1_BYTES},
+        # the second matvec kernel (operands the tensor-core kernel does not cover take it: expert
+        # banks, gate/up pairs, fused prologues and epilogues)
+        "stream_matvec_roofline": {"kernel": "stream_kernel (mma.sync row engine), same matrices", "achieved": stream_gbs,
+                                   "peak": peak, "unit": "GB/s", "frac": stream_gbs / peak, "launch_us": stream_launch_s * 1e6},
         "prefill_gemm_roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_kernel (tcgen05, 8192 tokens x [8192, 2048])",
                                   "achieved": gemm_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
                                   "frac": gemm_tflops / tensor_peak, "peak_source": f"{tensor_peak_kind} cuBLAS bf16",
