@@ -77,10 +77,13 @@ int qd_nvfp4_quantize_act(const void* x, int tokens, int in_features, void* code
  * bf16( x_global * w_global * sum_k xq[t, k] * wq[n, k] ), fp32 accumulation in tensor memory.
  * The prefill projection of quickdraw/kernel/triton/matvec.py:118-163 with the activations
  * quantised by qd_nvfp4_quantize_act.  in_features % 256 == 0, out_features % 128 == 0,
- * pointers 16-byte aligned.  status: device word, bit 0 is set if a bounded wait ran out. */
+ * pointers 16-byte aligned.  wide_tiles: 1 = 256 weight rows per block and MMA (out_features
+ * % 256 == 0), 0 = 128, -1 = the library chooses.  status: device word, bit 0 is set if a
+ * bounded wait ran out. */
 int qd_nvfp4_matmul_w4a4(const void* x_codes, const void* x_scales, const float* x_global,
                          const void* w_codes, const void* w_scales, const float* w_global, void* y,
-                         int tokens, int out_features, int in_features, unsigned int* status, void* stream);
+                         int tokens, int out_features, int in_features, int wide_tiles,
+                         unsigned int* status, void* stream);
 
 /* grouped_matmul(x, bank, grouping, routing=None) for the routed experts of a chunk of tokens —
  * quickdraw/kernel/triton/moe.py:99-151.  Routes are the (token, slot) pairs of the chunk

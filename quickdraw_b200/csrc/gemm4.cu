@@ -28,15 +28,21 @@
 namespace qd {
 namespace {
 
-constexpr int kTile = 128;                    // tokens and weight rows per block
-constexpr int kStages4 = 3;
+constexpr int kTile = 128;                    // tokens per block (tensor-memory lanes)
+// Weight rows per block = columns of one MMA: template parameter TN.  128: 3 stages of 36 KB and
+// 256 tensor-memory columns, two blocks per SM.  256: 4 stages of 54 KB, all 512 columns, one block
+// per SM; a block-scaled MMA takes the same 152 clocks for 256 columns as for 128.
+constexpr int stages_of(int tn) { return tn == 128 ? 3 : 4; }
 constexpr int kCodeBytes = kTile * 128;       // 128 rows x 256 inputs
 constexpr int kScaleBytes = kTile * 16;       // 128 rows x 16 scales
-constexpr int kStage4Bytes = 2 * kCodeBytes + 2 * kScaleBytes;      // 36 KB
+constexpr int stage_bytes(int tn) { return (1 + tn / 128) * (kCodeBytes + kScaleBytes); }      // 36 / 54 KB
 constexpr int kThreads4 = 6 * 32;
-constexpr uint32_t kCols4 = 256;              // accumulator 128 + per stage 16 (tokens) + 16 (rows) scale columns
-constexpr uint32_t kColAcc = 0, kColSf = 128;
-constexpr uint32_t kDesc128 = (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t tmem_cols(int tn) { return tn == 128 ? 256u : 512u; }
+constexpr uint32_t kColAcc = 0;
+// scale columns of a stage: 16 for the 128 tokens (four per 64-input step: rows l, l + 32, l + 64,
+// l + 96 of lane l), then four per step and 128 weight rows
+constexpr uint32_t sf_cols(int tn) { return 16u + 16u * (tn / 128); }
+constexpr uint32_t desc_of(int tn) { return (1u << 7) | (1u << 10) | (((uint32_t)tn >> 3) << 17) | ((128u >> 4) << 24); }
 
 struct Gemm4Params {
     const float* x_global; const float* w_global; bf16* y;
@@ -44,18 +50,21 @@ struct Gemm4Params {
     unsigned int* status;
 };
 
-struct Bars4 { uint64_t full[kStages4], empty[kStages4], sf_ready[kStages4], done; };
+struct Bars4 { uint64_t full[4], empty[4], sf_ready[4], done; };
 
-__global__ void __launch_bounds__(kThreads4, 2)
+template <int TN>
+__global__ void __launch_bounds__(kThreads4, TN == 128 ? 2 : 1)
 nvfp4_gemm_w4a4_kernel(const __grid_constant__ Gemm4Params p, const __grid_constant__ CUtensorMap x_codes,
                        const __grid_constant__ CUtensorMap x_scales, const __grid_constant__ CUtensorMap w_codes,
                        const __grid_constant__ CUtensorMap w_scales) {
     extern __shared__ __align__(1024) uint8_t gemm4_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm4_smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int kStages4 = stages_of(TN), kStage4Bytes = stage_bytes(TN), kHalves = TN / 128;
+    constexpr uint32_t kCols4 = tmem_cols(TN), kColSf = TN, kSfCols = sf_cols(TN);
     Bars4* bars = reinterpret_cast<Bars4*>(smem + kStages4 * kStage4Bytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int t0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
+    const int t0 = blockIdx.y * kTile, n0 = blockIdx.x * TN;
     const int chunks = p.in_features / 256;
 
     if (tid == 0) {
@@ -79,10 +88,15 @@ nvfp4_gemm_w4a4_kernel(const __grid_constant__ Gemm4Params p, const __grid_const
                 // rows past the end of a matrix arrive as zeros; a box always counts in full
                 mbar_expect_tx(bars->full + st, kStage4Bytes);
                 uint8_t* base = stage(st);
+                // codes: tokens, then the weight rows (128 at a time); scales in the same order
+                uint8_t* sc = base + (1 + kHalves) * kCodeBytes;
                 tma_load_2d(base, &x_codes, c * 128, t0, bars->full + st);
-                tma_load_2d(base + kCodeBytes, &w_codes, c * 128, n0, bars->full + st);
-                tma_load_2d(base + 2 * kCodeBytes, &x_scales, c * 16, t0, bars->full + st);
-                tma_load_2d(base + 2 * kCodeBytes + kScaleBytes, &w_scales, c * 16, n0, bars->full + st);
+                tma_load_2d(sc, &x_scales, c * 16, t0, bars->full + st);
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h) {
+                    tma_load_2d(base + (1 + h) * kCodeBytes, &w_codes, c * 128, n0 + h * 128, bars->full + st);
+                    tma_load_2d(sc + (1 + h) * kScaleBytes, &w_scales, c * 16, n0 + h * 128, bars->full + st);
+                }
             }
         }
     } else if (warp == 1) {
@@ -95,10 +109,11 @@ nvfp4_gemm_w4a4_kernel(const __grid_constant__ Gemm4Params p, const __grid_const
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_lo = desc_lo_sw128(smem_u32(stage(st))), b_lo = desc_lo_sw128(smem_u32(stage(st) + kCodeBytes));
-                const uint32_t sfa = tmem + kColSf + st * 32, sfb = sfa + 16;
+                const uint32_t sfa = tmem + kColSf + st * kSfCols, sfb = sfa + 16;
 #pragma unroll
                 for (int j = 0; j < 4; ++j)       // a 64-input step: 32 bytes further in both operands
-                    umma_nvfp4_lo(tmem + kColAcc, a_lo + 2 * j, b_lo + 2 * j, kDesc128, sfa + j * 4, sfb + j * 4, (c | j) ? 1u : 0u);
+                    umma_nvfp4_lo(tmem + kColAcc, a_lo + 2 * j, b_lo + 2 * j, desc_of(TN), sfa + j * 4, sfb + j * 4 * kHalves,
+                                  (c | j) ? 1u : 0u);
                 umma_commit(bars->empty + st);    // the stage (and its scale columns) is free once these MMAs are done
             }
             if (ok) umma_commit(&bars->done);
@@ -111,16 +126,28 @@ nvfp4_gemm_w4a4_kernel(const __grid_constant__ Gemm4Params p, const __grid_const
         for (int c = 0; c < chunks && ok; ++c) {
             const int st = c % kStages4;
             if (!mbar_wait(bars->full + st, (c / kStages4) & 1, p.status)) { ok = false; break; }
-#pragma unroll
-            for (int operand = 0; operand < 2; ++operand) {
-                const uint8_t* sc = stage(st) + 2 * kCodeBytes + operand * kScaleBytes;
+            const uint8_t* sc = stage(st) + (1 + kHalves) * kCodeBytes;
+            {   // the tokens' scales: four columns per 64-input step
                 uint32_t w[16];
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     const uint4 v = *reinterpret_cast<const uint4*>(sc + (lane + 32 * g) * 16);
                     w[0 + g] = v.x; w[4 + g] = v.y; w[8 + g] = v.z; w[12 + g] = v.w;
                 }
-                tmem_store16(quarter + kColSf + st * 32 + operand * 16, w);
+                tmem_store16(quarter + kColSf + st * kSfCols, w);
+            }
+            // the weight rows' scales: 4 * kHalves columns per step (row l + 32 g of lane l in column g)
+#pragma unroll
+            for (int pair = 0; pair < kHalves; ++pair) {      // steps 2 pair, 2 pair + 1 (256 rows) or all four (128 rows)
+                uint32_t w[16];
+#pragma unroll
+                for (int g = 0; g < 4 * kHalves; ++g) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(sc + kScaleBytes + (lane + 32 * g) * 16);
+                    const uint32_t word[4] = {v.x, v.y, v.z, v.w};
+                    if (kHalves == 1) { w[0 + g] = word[0]; w[4 + g] = word[1]; w[8 + g] = word[2]; w[12 + g] = word[3]; }
+                    else { w[g] = word[2 * pair]; w[8 + g] = word[2 * pair + 1]; }
+                }
+                tmem_store16(quarter + kColSf + st * kSfCols + 16 + pair * 16, w);
             }
             tmem_store_wait();
             tc_fence_before();
@@ -134,7 +161,7 @@ nvfp4_gemm_w4a4_kernel(const __grid_constant__ Gemm4Params p, const __grid_const
             const int token = t0 + (warp & 3) * 32 + lane;
             bf16* out = p.y + (size_t)token * p.out_features + n0;
 #pragma unroll 1
-            for (int col = 0; col < kTile; col += 16) {
+            for (int col = 0; col < TN; col += 16) {
                 uint32_t v[16];
                 tmem_load16(quarter + kColAcc + col, v);
                 tmem_load_wait();
@@ -253,10 +280,10 @@ extern "C" int qd_nvfp4_quantize_act(const void* x, int tokens, int in_features,
 
 extern "C" int qd_nvfp4_matmul_w4a4(const void* x_codes, const void* x_scales, const float* x_global, const void* w_codes,
                                     const void* w_scales, const float* w_global, void* y, int tokens, int out_features,
-                                    int in_features, unsigned int* status, void* stream) {
+                                    int in_features, int wide_tiles, unsigned int* status, void* stream) {
     using namespace qd;
     QD_CHECK_ARG(x_codes && x_scales && x_global && w_codes && w_scales && w_global && y && tokens > 0);
-    QD_CHECK_ARG(in_features > 0 && in_features % 256 == 0 && out_features > 0 && out_features % kTile == 0);
+    QD_CHECK_ARG(in_features > 0 && in_features % 256 == 0 && out_features > 0 && out_features % 128 == 0);
     QD_CHECK_ARG(((reinterpret_cast<uintptr_t>(x_codes) | reinterpret_cast<uintptr_t>(x_scales) | reinterpret_cast<uintptr_t>(w_codes) |
                    reinterpret_cast<uintptr_t>(w_scales) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0);
     alignas(64) CUtensorMap xc, xs, wc, ws;
@@ -268,16 +295,22 @@ extern "C" int qd_nvfp4_matmul_w4a4(const void* x_codes, const void* x_scales, c
     Gemm4Params p = {};
     p.x_global = x_global; p.w_global = w_global; p.y = reinterpret_cast<bf16*>(y);
     p.tokens = tokens; p.out_features = out_features; p.in_features = in_features; p.status = status;
-    const size_t smem = (size_t)kStages4 * kStage4Bytes + sizeof(Bars4) + 64 + 1024;
-    int dev = 0;
+    // 256-row weight tiles where they still give every SM a tile or more; 128-row tiles otherwise
+    int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
-    static bool configured[64];
-    if (!configured[dev]) {
-        if (cudaFuncSetAttribute(nvfp4_gemm_w4a4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return QD_ERR_LAUNCH;
-        configured[dev] = true;
-    }
-    const dim3 grid((unsigned)(out_features / kTile), (unsigned)((tokens + kTile - 1) / kTile));
-    nvfp4_gemm_w4a4_kernel<<<grid, kThreads4, smem, (cudaStream_t)stream>>>(p, xc, xs, wc, ws);
-    return qd_launch_status();
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long token_tiles = (tokens + kTile - 1) / kTile;
+    const bool wide = wide_tiles >= 0 ? wide_tiles != 0 : (out_features % 256 == 0 && token_tiles * (out_features / 256) >= 2ll * sms);
+    static bool configured[2][64];
+    auto launch = [&](auto kernel, int tn) -> int {
+        const size_t smem = (size_t)stages_of(tn) * stage_bytes(tn) + sizeof(Bars4) + 64 + 1024;
+        if (!configured[tn == 256][dev]) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return QD_ERR_LAUNCH;
+            configured[tn == 256][dev] = true;
+        }
+        const dim3 grid((unsigned)(out_features / tn), (unsigned)token_tiles);
+        kernel<<<grid, kThreads4, smem, (cudaStream_t)stream>>>(p, xc, xs, wc, ws);
+        return qd_launch_status();
+    };
+    return wide ? launch(nvfp4_gemm_w4a4_kernel<256>, 256) : launch(nvfp4_gemm_w4a4_kernel<128>, 128);
 }

@@ -20,10 +20,30 @@ backend: on a CPU device only a caller-supplied ``step`` can run.
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import torch
 
 from .state import DecodeState
 from .weights import Checkpoint
+
+
+@dataclass
+class Snapshot:
+    """A request's history at one point: the token ids processed so far, the recurrent and
+    convolution tensors (copies), the position and the pending token.  The KV cache is not
+    copied: its rows below ``position`` stay valid as long as the engine only continues from a
+    restored snapshot or starts over (rows at or beyond the position are rewritten before they
+    are read).  Bound to the checkpoint and the execution settings it was taken under."""
+    tokens: tuple[int, ...]
+    position: int
+    pending_token: torch.Tensor | None
+    rec_state: torch.Tensor
+    conv_state: torch.Tensor
+    binding: tuple
+
+    def nbytes(self) -> int:
+        return self.rec_state.nbytes + self.conv_state.nbytes
 
 
 class Engine:
@@ -67,6 +87,9 @@ class Engine:
                              for l in ckpt.layers], 1 + ckpt.final_norm.float())
                 self.step = bind_kernels(prepared=prepared, **(kernels or {}))["forward_step"]
         self.state = DecodeState.allocate(ckpt.config, max_context, device)
+        self.history: list[int] = []            # token ids processed since the last reset (prompt part; see _fold)
+        self._decoded: list[torch.Tensor] = []  # tokens processed by decode steps, still on the device
+        self._kv_tokens: list[int] = []         # the token sequence the cache rows [0, n) were computed from
         self.pending_token: torch.Tensor | None = None
         self.eos_token_ids: set[int] = set()
         if backend == "b200" and cuda_graph:
@@ -119,15 +142,20 @@ class Engine:
         every token otherwise, goes through the decode step."""
         assert 0 < len(token_ids) <= self.max_context, "prompt must fit within max_context"
         self.reset()
+        return self._extend(list(token_ids))
+
+    def _extend(self, token_ids: list[int]) -> torch.Tensor:
+        """Process ``token_ids`` after the current position; logits after the last one."""
+        start = self.state.position
         tokens = torch.tensor(token_ids, dtype=torch.long, device=self.device)
         logits = None
         done = 0
         if self.sequence_prefill and len(token_ids) > 1:
             while done < len(token_ids) - 1:
                 stop = min(len(token_ids) - 1, done + self.prefill_chunk_size)
-                self.chunk_prefill.run(tokens[done:stop], done, self.state)
+                self.chunk_prefill.run(tokens[done:stop], start + done, self.state)
                 done = stop
-            self.state.position = done
+            self.state.position = start + done
         for index, token in enumerate(tokens[done:], start=done):
             if self.backend == "b200":
                 logits = self.step(self.ckpt, token, self.state.position, self.state,
@@ -135,6 +163,77 @@ class Engine:
             else:
                 logits = self.step(self.ckpt, token, self.state.position, self.state)
             self.state.position += 1
+        self._note([int(t) for t in token_ids])
+        return logits
+
+    def _note(self, ids: list[int]) -> None:
+        """Record tokens processed at the positions after ``history`` and what that did to the
+        cache: a row is rewritten with the same content exactly when the whole prefix is the same."""
+        for token in ids:
+            at = len(self.history)
+            if not (at < len(self._kv_tokens) and self._kv_tokens[at] == token):
+                del self._kv_tokens[at:]
+                self._kv_tokens.append(token)
+            self.history.append(token)
+
+    def _fold(self) -> None:
+        """Bring ``history`` up to date with the decode steps taken (their tokens stay on the
+        device until somebody needs them as numbers: one transfer here, none per step)."""
+        if self._decoded:
+            ids = torch.stack([t.reshape(()) for t in self._decoded]).tolist()
+            self._decoded = []
+            self._note([int(t) for t in ids])
+
+    # ------------------------------------------------------------- conversation reuse
+    def _binding(self) -> tuple:
+        return (id(self.ckpt), self.backend, str(self.device), self.max_context, self.sequence_prefill)
+
+    @torch.inference_mode()
+    def snapshot(self) -> Snapshot:
+        """The history of the current request, to come back to later (the reference plans this:
+        todo.md "Conversation reuse").  75 MB of copies for the 36B-A3B model, no KV copy."""
+        self._fold()
+        pending = None if self.pending_token is None else self.pending_token.clone()
+        return Snapshot(tuple(self.history), self.state.position, pending, self.state.rec_state.clone(),
+                        self.state.conv_state.clone(), self._binding())
+
+    @torch.inference_mode()
+    def restore(self, snap: Snapshot) -> None:
+        """Copy a snapshot back into the existing buffers (a captured graph stays valid).  Refused
+        when the snapshot belongs to another checkpoint or other execution settings, or when the
+        cache rows it relies on have been overwritten by a different prefix since."""
+        self._fold()
+        assert snap.binding == self._binding(), "snapshot taken under another checkpoint or other settings"
+        assert self._kv_covers(snap.tokens), "the cache rows of this snapshot have been overwritten"
+        self.state.rec_state.copy_(snap.rec_state)
+        self.state.conv_state.copy_(snap.conv_state)
+        self.state.position = snap.position
+        self.pending_token = None if snap.pending_token is None else snap.pending_token.clone()
+        self.history = list(snap.tokens)
+
+    def _kv_covers(self, tokens) -> bool:
+        return len(tokens) <= len(self._kv_tokens) and list(tokens) == self._kv_tokens[:len(tokens)]
+
+    @torch.inference_mode()
+    def prefill_reuse(self, token_ids: list[int], snap: Snapshot | None = None) -> torch.Tensor:
+        """Like ``prefill``, but when ``snap`` (default: the snapshot this method took after the
+        previous prompt) holds a proper prefix of ``token_ids`` only the new suffix is processed.
+        Anything else - no snapshot, different tokens, foreign binding, overwritten cache rows -
+        is a fresh ``prefill``.  Leaves a snapshot of the whole prompt in ``last_snapshot``."""
+        assert 0 < len(token_ids) <= self.max_context, "prompt must fit within max_context"
+        self._fold()
+        snap = snap if snap is not None else getattr(self, "last_snapshot", None)
+        usable = (snap is not None and snap.binding == self._binding() and 0 < len(snap.tokens) < len(token_ids)
+                  and list(token_ids[:len(snap.tokens)]) == list(snap.tokens) and snap.position == len(snap.tokens)
+                  and self._kv_covers(snap.tokens))
+        if usable:
+            self.restore(snap)
+            self.reused_tokens = len(snap.tokens)
+            logits = self._extend(list(token_ids[len(snap.tokens):]))
+        else:
+            self.reused_tokens = 0
+            logits = self.prefill(token_ids)
+        self.last_snapshot = self.snapshot()
         return logits
 
     @classmethod
@@ -152,6 +251,7 @@ class Engine:
         """Process the pending token, select and return its successor (0-d int64)."""
         assert self.pending_token is not None, "select a pending token before decode"
         assert self.state.position < self.max_context, "context capacity reached"
+        self._decoded.append(self.pending_token)          # becomes a number only when a snapshot asks
         if self.graph is None:
             logits = self.step(self.ckpt, self.pending_token, self.state.position, self.state)
             self.pending_token = torch.argmax(logits)
@@ -185,3 +285,5 @@ class Engine:
         self.state.conv_state.zero_()
         self.state.position = 0
         self.pending_token = None
+        self._fold()                # what the cache rows hold outlives the request
+        self.history = []

@@ -133,11 +133,12 @@ def quantize_act(x: torch.Tensor):
     return codes, scales, scale_2
 
 
-def matmul_w4a4(xq, proj: NVFP4Linear) -> torch.Tensor:
+def matmul_w4a4(xq, proj: NVFP4Linear, *, wide_tiles: bool | None = None) -> torch.Tensor:
     """Quantised activations (``quantize_act``) times a packed NVFP4 matrix on the block-scaled
     FP4 tensor core: neither operand is expanded.  Differs from ``matmul`` by the activation
     rounding only (the W4A4 variant quickdraw's notes ask to validate separately from W4A16);
-    in_features a multiple of 256, out_features a multiple of 128."""
+    in_features a multiple of 256, out_features a multiple of 128.  ``wide_tiles``: 256 weight rows
+    per block and MMA (needs out_features % 256 == 0) instead of 128; None lets the library choose."""
     codes, scales, scale_2 = xq
     assert isinstance(proj, NVFP4Linear) and proj.weight.ndim == 2 and proj.group_size == 16
     assert codes.is_cuda and codes.dtype == torch.uint8 and codes.is_contiguous() and scales.is_contiguous()
@@ -148,8 +149,8 @@ def matmul_w4a4(xq, proj: NVFP4Linear) -> torch.Tensor:
         status = _matmul_status[codes.device] = torch.zeros(1, dtype=torch.int32, device=codes.device)
     out = torch.empty((codes.shape[0], proj.out_features), dtype=BF16, device=codes.device)
     call("qd_nvfp4_matmul_w4a4", ptr(codes), ptr(scales), ptr(scale_2), ptr(proj.weight), ptr(proj.weight_scale),
-         ptr(proj.weight_scale_2), ptr(out), codes.shape[0], proj.out_features, proj.in_features, ptr(status),
-         stream_of(codes))
+         ptr(proj.weight_scale_2), ptr(out), codes.shape[0], proj.out_features, proj.in_features,
+         -1 if wide_tiles is None else int(wide_tiles), ptr(status), stream_of(codes))
     return out
 
 

@@ -69,8 +69,9 @@ def test_activation_quantiser_is_bit_exact(cuda_device, tokens, width):
     assert O.rel_l2(back, x.float()) < 0.12
 
 
+@pytest.mark.parametrize("wide", [False, True])
 @pytest.mark.parametrize("tokens,out_features,in_features", W4A4_SHAPES)
-def test_w4a4_matmul_matches_oracle(cuda_device, tokens, out_features, in_features):
+def test_w4a4_matmul_matches_oracle(cuda_device, tokens, out_features, in_features, wide):
     """The block-scaled FP4 x FP4 product against the oracle's product of the same quantised
     operands (fp32-accumulation tolerance), and its distance from the exact W4A16 product (the
     activation rounding: about one tenth relative L2 for Gaussian inputs)."""
@@ -78,8 +79,10 @@ def test_w4a4_matmul_matches_oracle(cuda_device, tokens, out_features, in_featur
     src = synthetic.Source(32, "cpu")
     proj = src.nvfp4(f"w{out_features}x{in_features}", out_features, in_features, global_scale=0.75)
     x = src.normal(f"x{tokens}", tokens, in_features)
+    if wide and out_features % 256:
+        pytest.skip("256-row tiles need out_features % 256 == 0")
     xq = kernels.quantize_act(x.to(cuda_device))
-    got = kernels.matmul_w4a4(xq, to_device(proj, cuda_device)).cpu()
+    got = kernels.matmul_w4a4(xq, to_device(proj, cuda_device), wide_tiles=wide).cpu()
     assert kernels.matmul_status(cuda_device) == 0
     want = O.nvfp4_matmul_w4a4(*O.quantize_act_nvfp4(x), proj)
     assert got.shape == want.shape

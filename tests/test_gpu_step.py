@@ -339,3 +339,37 @@ def test_engine_capacity_and_eos(cuda_device, real_width_case):
     assert engine.generate(prompt, 50) == want[:3]
     with pytest.raises(AssertionError):
         engine.generate(list(range(engine.max_context + 1)), 1)
+
+
+def test_prefix_reuse_against_a_fresh_prefill(cuda_device):
+    """Conversation reuse on the device: a prompt that extends the previous one is continued from
+    the snapshot (recurrent and convolution tensors restored, cache rows kept) and must land where
+    a fresh prefill of the whole prompt lands, up to the summation order of the chunk kernels; a
+    divergent prompt falls back to a fresh prefill and is bit-identical to one."""
+    from quickdraw_b200.engine import Engine
+    cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
+    ckpt = synthetic.make_checkpoint(cfg, seed=9, device="cuda")
+    gen = torch.Generator().manual_seed(2)
+    first = torch.randint(0, cfg.vocab_size, (24,), generator=gen).tolist()
+    longer = first + torch.randint(0, cfg.vocab_size, (9,), generator=gen).tolist()
+    reuse, fresh = Engine(ckpt, max_context=64, device="cuda"), Engine(ckpt, max_context=64, device="cuda")
+    for engine in (reuse, fresh):
+        engine.state.kv_k.zero_()
+        engine.state.kv_v.zero_()
+    reuse.prefill_reuse(first)
+    got = reuse.prefill_reuse(longer)
+    assert reuse.reused_tokens == len(first) and reuse.state.position == len(longer)
+    want = fresh.prefill(longer)
+    assert O.rel_l2(got.cpu(), want.cpu()) < 2e-2
+    n = len(longer)
+    assert O.rel_l2(reuse.state.rec_state.cpu(), fresh.state.rec_state.cpu()) < 2e-2
+    assert O.rel_l2(reuse.state.kv_k[:, :n].cpu(), fresh.state.kv_k[:, :n].cpu()) < 2e-2
+    # generation continues from the reused state through the captured graph
+    reuse.pending_token = torch.argmax(got)
+    assert int(reuse.decode_step()) >= 0 and reuse.state.position == n + 1
+    # a prompt that diverges inside the old one: fresh prefill, identical to a new engine's
+    other = first[:10] + [7, 8, 9]
+    a = reuse.prefill_reuse(other)
+    b = fresh.prefill(other)
+    assert reuse.reused_tokens == 0 and torch.equal(a, b)
+    assert torch.equal(reuse.state.rec_state, fresh.state.rec_state)

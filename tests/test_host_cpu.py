@@ -132,3 +132,51 @@ def test_prefill_starts_a_fresh_request():
     engine.generate([7, 7, 7], 1)
     engine.prefill([8])
     assert engine.state.position == 1 and step.calls[-1] == (8, 0)
+
+
+# ----------------------------------------------------------------- conversation reuse (host logic)
+def test_prefix_reuse_processes_only_the_new_suffix():
+    engine, step = make_engine([3, 4, 5, 6, 7, 8, 9, 10], max_context=32)
+    engine.prefill_reuse([20, 21, 22])
+    assert engine.reused_tokens == 0 and [c for c in step.calls] == [(20, 0), (21, 1), (22, 2)]
+    before = engine.state.rec_state.clone()
+    step.calls.clear()
+    logits = engine.prefill_reuse([20, 21, 22, 30, 31])                # extends the previous prompt
+    assert engine.reused_tokens == 3 and step.calls == [(30, 3), (31, 4)]
+    assert engine.state.position == 5 and int(logits.argmax()) == 7    # script[4]
+    assert torch.equal(engine.state.rec_state, before + 2)             # restored, then two more steps
+    step.calls.clear()
+    engine.prefill_reuse([20, 21, 99, 30])                             # diverges inside the old prompt: fresh
+    assert engine.reused_tokens == 0 and step.calls[0] == (20, 0) and len(step.calls) == 4
+    assert torch.equal(engine.state.rec_state, torch.full_like(before, 4.0))
+
+
+def test_snapshot_restore_round_trip_and_binding():
+    engine, step = make_engine([3, 4, 5, 6, 7, 8, 9, 10], max_context=32)
+    first = engine.generate([1, 2], 3)                                  # prompt 2 + decode steps at positions 2, 3
+    snap = engine.snapshot()
+    assert snap.tokens == (1, 2, first[0], first[1]) and snap.position == 4
+    assert snap.nbytes() == engine.state.rec_state.nbytes + engine.state.conv_state.nbytes
+    rec = engine.state.rec_state.clone()
+    engine.decode_step()
+    engine.decode_step()
+    engine.restore(snap)                                                # back to the snapshot: buffers reused
+    assert engine.state.position == 4 and torch.equal(engine.state.rec_state, rec)
+    assert int(engine.pending_token) == first[2]
+    assert int(engine.decode_step()) == 7                               # continues as it did the first time (script[4])
+    # a new conversation overwrites the cache rows the snapshot relies on
+    engine.prefill([9, 9, 9, 9, 9])
+    with pytest.raises(AssertionError, match="overwritten"):
+        engine.restore(snap)
+    other, _ = make_engine([1], max_context=32)
+    with pytest.raises(AssertionError, match="another checkpoint"):
+        other.restore(snap)
+
+
+def test_reuse_survives_a_reset_when_the_cache_rows_are_intact():
+    engine, step = make_engine([3, 4, 5, 6], max_context=32)
+    engine.prefill_reuse([5, 6, 7])
+    engine.reset()                                                      # history cleared, cache rows untouched
+    step.calls.clear()
+    engine.prefill_reuse([5, 6, 7, 8])
+    assert engine.reused_tokens == 3 and step.calls == [(8, 3)]
