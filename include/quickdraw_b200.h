@@ -299,6 +299,12 @@ typedef struct {
     qd_fp4 shared_gate, shared_up, shared_down;
     int experts_global_per_expert;
     int state_index;                                     /* index into rec/conv or kv arrays */
+    /* Static FP8 mixers (FP8Linear, quickdraw/models/weights.py:58-74; fp8_gemv, qwen.py:25-33):
+     * proj_a/b/c/out then hold E4M3 weights [out, in] in `codes`, NULL in `scales` and the fp32
+     * weight scale in `global`; the projections that read the layer input share one activation
+     * scale (merge_fp8_scales), the output projection has its own.  Persistent step only. */
+    int mixers_fp8;
+    const float* mixer_input_scale; const float* out_input_scale;
 } qd_layer;
 
 typedef struct {

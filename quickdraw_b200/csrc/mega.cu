@@ -339,6 +339,9 @@ QD_DEVINL bool produce_stream(const MegaParams& mp, const MegaPhase& ph, const S
             if (sg.kind == SEG_BF16) {
                 mbar_expect_tx(full, n * 2 * K);
                 bulk_load(dst, w + (long long)r0 * 2 * K, n * 2 * K, full);
+            } else if (sg.kind == SEG_FP8) {
+                mbar_expect_tx(full, n * K);
+                bulk_load(dst, w + (long long)r0 * K, n * K, full);
             } else if (sg.kind == SEG_FP4) {
                 mbar_expect_tx(full, n * (K / 2 + K / 16));
                 bulk_load(dst, w + (long long)r0 * (K / 2), n * (K / 2), full);
@@ -578,6 +581,13 @@ static __device__ __noinline__ void head_argmax(const MegaParams& mp, const Smem
     }
 }
 
+// Static FP8 activation (quickdraw/models/qwen.py:25-26): x / scale, clamped to the E4M3 range,
+// rounded to nearest even; returned as the f16 that holds the E4M3 value exactly.
+QD_DEVINL float fp8_quantised(float v, float in_scale) {
+    const __nv_fp8_storage_t q = __nv_cvt_float_to_fp8(__fdiv_rn(v, in_scale), __NV_SATFINITE, __NV_E4M3);
+    return __half2float(__half(__nv_cvt_fp8_to_halfraw(q, __NV_E4M3)));
+}
+
 // ========================================================================== consumers
 // One streaming phase: activation vector -> shared memory and registers, then this block's
 // rows of the ring.  res: this thread's four elements of the bf16 residual stream.
@@ -613,6 +623,8 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
 
     // ---- static inputs (nothing another block writes): norm gamma, global scales of the
     //      segments, conv taps and history of this block's channels
+    const bool q8 = ph.in_scale != nullptr;          // static FP8 projections: the vector is quantised first
+    const float in_scale = q8 ? *ph.in_scale : 1.f;
     float4 gam = make_float4(0.f, 0.f, 0.f, 0.f);
     if constexpr (KC == 2) if (ph.prologue == PRO_ADD_NORM) gam = *reinterpret_cast<const float4*>(ph.gamma + tid * 4);
     if (tid < 2 * kMegaMaxSeg) {
@@ -689,8 +701,11 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             const __nv_bfloat162 n01 = __floats2bfloat162_rn(nrm[0], nrm[1]), n23 = __floats2bfloat162_rn(nrm[2], nrm[3]);
             *reinterpret_cast<uint2*>(xs + tid * 4) = make_uint2(*reinterpret_cast<const uint32_t*>(&n01),
                                                                  *reinterpret_cast<const uint32_t*>(&n23));
-            *reinterpret_cast<uint2*>(xf + tid * 8) = make_uint2(pack_f16x2(nrm[0] * down, nrm[1] * down),
-                                                                 pack_f16x2(nrm[2] * down, nrm[3] * down));
+            float f[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[j] = q8 ? fp8_quantised(nrm[j], in_scale) : nrm[j] * down;
+            if (q8) out_mult = in_scale;
+            *reinterpret_cast<uint2*>(xf + tid * 8) = make_uint2(pack_f16x2(f[0], f[1]), pack_f16x2(f[2], f[3]));
             if (tid == 0) red[96] = out_mult;
         } else if (KC == 4 && ph.prologue == PRO_GATED_NORM) {
             // per-head RMSNorm of o, times gamma, times silu(z); a warp per 128-wide head, four
@@ -726,10 +741,14 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             float down;
             f16_scale(tmax, down, out_mult);
 #pragma unroll
+            if (q8) out_mult = in_scale;
+#pragma unroll
             for (int a = 0; a < HPW; ++a) {
                 const int base = (warp + a * CW) * 128 + lane * 4;
-                *reinterpret_cast<uint2*>(xf + base * 2) = make_uint2(pack_f16x2(nv[a][0] * down, nv[a][1] * down),
-                                                                      pack_f16x2(nv[a][2] * down, nv[a][3] * down));
+                float f[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) f[j] = q8 ? fp8_quantised(nv[a][j], in_scale) : nv[a][j] * down;
+                *reinterpret_cast<uint2*>(xf + base * 2) = make_uint2(pack_f16x2(f[0], f[1]), pack_f16x2(f[2], f[3]));
             }
         } else {
             // the vector as it is (attention output): eight elements per thread
@@ -747,8 +766,12 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
             for (int w = 0; w < CW; ++w) tmax = fmaxf(tmax, red[16 + w]);
             float down;
             f16_scale(tmax, down, out_mult);
-            *reinterpret_cast<uint4*>(xf + tid * 16) = make_uint4(pack_f16x2(v[0] * down, v[1] * down), pack_f16x2(v[2] * down, v[3] * down),
-                                                                  pack_f16x2(v[4] * down, v[5] * down), pack_f16x2(v[6] * down, v[7] * down));
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = q8 ? fp8_quantised(v[j], in_scale) : v[j] * down;
+            if (q8) out_mult = in_scale;
+            *reinterpret_cast<uint4*>(xf + tid * 16) = make_uint4(pack_f16x2(f[0], f[1]), pack_f16x2(f[2], f[3]),
+                                                                  pack_f16x2(f[4], f[5]), pack_f16x2(f[6], f[7]));
         }
         named_barrier(1, CT);
     } else {
@@ -836,7 +859,8 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                 const bool pair = KC == 2 && sg.kind == SEG_FP4_PAIR;
                 const int groups = UNITS == 2 ? 1 : ((pair || n > 16) ? 2 : 1);
                 float* mine = S.partials + st * kRowPartialFloats;
-                tile_partials<K>(base, UNITS == 2 ? 16 : 32, groups, xh, warp, lane, mine + warp * kRowSlots);
+                if (sg.kind == SEG_FP8) tile_partials_fp8<K>(base, xh, warp, lane, mine + warp * kRowSlots);
+                else tile_partials<K>(base, UNITS == 2 ? 16 : 32, groups, xh, warp, lane, mine + warp * kRowSlots);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(S.ready + st);
                 if (warp == (it & (CW - 1))) {

@@ -58,6 +58,7 @@ struct alignas(16) MegaPhase {
     int g_per_expert, argmax;
     int row_lo, pad0;         // LM head: vocabulary index of the segment's first row (this rank's shard)
     // streaming phases
+    const float* in_scale;    // static FP8 projections of this phase: the activation scale (NULL: none)
     const tagged* x; const float* gamma;
     const tagged* z; const bf16* head_gamma; const bf16* conv_taps;
     const tagged* router_logits; int32_t* ids_out; float* weights_out;

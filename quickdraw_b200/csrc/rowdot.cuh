@@ -9,12 +9,17 @@ namespace qd {
 // Costs are counted in units of 16 bytes so that a whole launch fits 32-bit arithmetic.
 template <int K> QD_DEVINL int seg_cost(int kind) {
     constexpr int fp4_row = (K / 2 + K / 16) / 16;
-    return kind == SEG_BF16 ? 2 * K / 16 : (kind == SEG_FP4_PAIR ? 2 * fp4_row : fp4_row);
+    return kind == SEG_BF16 ? 2 * K / 16 : kind == SEG_FP8 ? K / 16 : (kind == SEG_FP4_PAIR ? 2 * fp4_row : fp4_row);
 }
-template <int K> QD_DEVINL int seg_tile_rows(int kind) { return (kStreamStageBytes / 16) / seg_cost<K>(kind); }
+// Rows of one ring stage; FP8 rows go sixteen (2048 inputs) or eight (4096) at a time: one group
+// of the row engine.
+template <int K> QD_DEVINL int seg_tile_rows(int kind) {
+    return kind == SEG_FP8 ? (K == 2048 ? 16 : 8) : (kStreamStageBytes / 16) / seg_cost<K>(kind);
+}
 template <int K> QD_DEVINL unsigned ceil_div_cost(unsigned v, int kind) {   // constant divisors only
     constexpr unsigned fp4_row = (K / 2 + K / 16) / 16;
     return kind == SEG_BF16 ? (v + 2 * K / 16 - 1) / (2 * K / 16)
+         : kind == SEG_FP8 ? (v + K / 16 - 1) / (K / 16)
          : kind == SEG_FP4_PAIR ? (v + 2 * fp4_row - 1) / (2 * fp4_row) : (v + fp4_row - 1) / fp4_row;
 }
 // Row range [ra, rb) of a segment that falls into the block's cost range [lo, hi).

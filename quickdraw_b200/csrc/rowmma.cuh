@@ -89,6 +89,39 @@ QD_DEVINL void unit_mma(const uint8_t* __restrict__ codes, const uint8_t* __rest
     }
 }
 
+// The same for static-E4M3 rows (one byte per weight, no block scales: the matrix scale and the
+// activation scale multiply the finished sum): lane (g, t) takes 32 weights of rows g and g + 8
+// of its span, converts them to f16 (exact) and feeds the same sixteen MMAs.
+QD_DEVINL void unit_mma_fp8(const uint8_t* __restrict__ rows, int row_bytes, int span, int g, int t,
+                            const uint32_t (&xh)[16], float (&acc_a)[4], float (&acc_b)[4]) {
+    const uint8_t* c0 = rows + g * row_bytes + span * 128 + t * 32;
+    const uint4 a0 = lds128(c0), a1 = lds128(c0 + 16), b0 = lds128(c0 + 8 * row_bytes), b1 = lds128(c0 + 8 * row_bytes + 16);
+    const uint32_t r0[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const uint32_t r1[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {        // four weights of either row per word: one MMA
+        const uint32_t h0 = e4m3x2_to_f16x2((uint16_t)(r0[j] & 0xffffu)), h1 = e4m3x2_to_f16x2((uint16_t)(r0[j] >> 16));
+        const uint32_t k0 = e4m3x2_to_f16x2((uint16_t)(r1[j] & 0xffffu)), k1 = e4m3x2_to_f16x2((uint16_t)(r1[j] >> 16));
+        if (j & 1) mma_f16(acc_b, h0, k0, h1, k1, xh[2 * j], xh[2 * j + 1]);
+        else mma_f16(acc_a, h0, k0, h1, k1, xh[2 * j], xh[2 * j + 1]);
+    }
+}
+
+// A warp's partial sums of a tile of up to sixteen FP8 rows ([rows][K] bytes).
+template <int K>
+QD_DEVINL void tile_partials_fp8(const uint8_t* __restrict__ base, const uint32_t (&xh)[K / 2048][16], int warp, int lane,
+                                 float* __restrict__ partial) {
+    constexpr int UNITS = K / 2048;
+    const int g = lane >> 2, t = lane & 3;
+    float aa[4] = {0.f, 0.f, 0.f, 0.f}, ab[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) unit_mma_fp8(base, K, row_span<UNITS>(warp, u, g), g, t, xh[u], aa, ab);
+    if (t == (g >> 1)) {
+        partial[g] = (g & 1) ? aa[1] + ab[1] : aa[0] + ab[0];
+        partial[g + 8] = (g & 1) ? aa[3] + ab[3] : aa[2] + ab[2];
+    }
+}
+
 // A warp's partial sums of one tile: K = 2048 -> up to two groups of sixteen rows, one span
 // each; K = 4096 -> one group, two spans.  partial: this warp's kRowSlots floats.
 template <int K>

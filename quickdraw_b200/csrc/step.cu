@@ -103,6 +103,12 @@ StreamSeg fp4_seg(const qd_fp4& w, int rows, bf16* y, int epilogue = EP_PLAIN) {
     s.y = y; s.rows = rows; s.kind = SEG_FP4; s.epilogue = epilogue; s.slot = -1;
     return s;
 }
+// a mixer projection: NVFP4, or static FP8 when the layer says so
+StreamSeg mixer_seg(const qd_layer& ly, const qd_fp4& w, int rows, int epilogue = EP_PLAIN) {
+    StreamSeg s = fp4_seg(w, rows, nullptr, epilogue);
+    if (ly.mixers_fp8) { s.kind = SEG_FP8; s.s = nullptr; }
+    return s;
+}
 StreamSeg bf16_seg(const void* w, int rows, bf16* y, int epilogue = EP_PLAIN) {
     StreamSeg s = {};
     s.w = (const uint8_t*)w; s.y = y; s.rows = rows; s.kind = SEG_BF16; s.epilogue = epilogue; s.slot = -1;
@@ -122,6 +128,8 @@ int run_layers(qd_model* m, const qd_state* st, const long long* token, const in
                long long* next_token, int flags, cudaStream_t stream) {
     const qd_model_config& c = m->cfg;
     if (!fused_shape_ok(c)) return QD_ERR_UNSUPPORTED;
+    for (int L = begin; L < end; ++L)
+        if (m->layers[L].mixers_fp8) return QD_ERR_UNSUPPORTED;      // static FP8 mixers: persistent step only
     const bool pdl = flags & QD_FLAG_PDL;
     Workspace w = carve(c, (uint8_t*)workspace);
     const int H = c.hidden;
@@ -293,7 +301,8 @@ bool mega_finish_stream(MegaPhase& ph, int grid) {
     unsigned long long total = 0;
     const unsigned fp4_row = (ph.width / 2 + ph.width / 16) / 16;
     for (int i = 0; i < ph.nseg; ++i) {
-        const unsigned cost = ph.seg[i].kind == SEG_BF16 ? 2u * ph.width / 16 : ph.seg[i].kind == SEG_FP4_PAIR ? 2 * fp4_row : fp4_row;
+        const unsigned cost = ph.seg[i].kind == SEG_BF16 ? 2u * ph.width / 16 : ph.seg[i].kind == SEG_FP8 ? (unsigned)ph.width / 16
+                              : ph.seg[i].kind == SEG_FP4_PAIR ? 2 * fp4_row : fp4_row;
         total += (unsigned long long)ph.seg[i].rows * cost;
         if (ph.seg[i].epilogue == EP_CONV && ph.seg[i].rows / grid + 2 > kMegaConvRows) return false;
     }
@@ -388,16 +397,20 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
         else { a.x = w.t_moe_out; a.x_prev_layer = 1; }
         if (ly.is_attention) {
             a.nseg = 3;
-            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, 2 * q_width, nullptr), w.t_big);
-            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, kv_width, nullptr), w.t_mid);
-            a.seg[2] = mega_seg(fp4_seg(ly.proj_c, kv_width, nullptr), w.t_mid + kv_width);
+            a.seg[0] = mega_seg(mixer_seg(ly, ly.proj_a, 2 * q_width), w.t_big);
+            a.seg[1] = mega_seg(mixer_seg(ly, ly.proj_b, kv_width), w.t_mid);
+            a.seg[2] = mega_seg(mixer_seg(ly, ly.proj_c, kv_width), w.t_mid + kv_width);
         } else {
             a.nseg = 4;
-            a.seg[0] = mega_seg(fp4_seg(ly.proj_a, channels, nullptr, EP_CONV), w.t_big);
-            a.seg[1] = mega_seg(fp4_seg(ly.proj_b, value_width, nullptr), w.t_mid);
+            a.seg[0] = mega_seg(mixer_seg(ly, ly.proj_a, channels, EP_CONV), w.t_big);
+            a.seg[1] = mega_seg(mixer_seg(ly, ly.proj_b, value_width), w.t_mid);
             a.seg[2] = mega_seg(bf16_seg(ly.in_proj_a, c.value_heads, nullptr), w.t_ab);
             a.seg[3] = mega_seg(bf16_seg(ly.in_proj_b, c.value_heads, nullptr), w.t_ab + c.value_heads);
             a.conv_taps = (const bf16*)ly.conv1d;
+        }
+        if (ly.mixers_fp8) {
+            if (!ly.mixer_input_scale || !ly.out_input_scale) return QD_ERR_ARG;
+            a.in_scale = ly.mixer_input_scale;
         }
         if (!mega_finish_stream(a, grid)) return QD_ERR_UNSUPPORTED;
         out[n++] = a;
@@ -419,7 +432,8 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
         // ---- B: output projection
         MegaPhase b = {};
         b.kind = MK_STREAM; b.width = 4096; b.layer = L; b.x = w.t_o;
-        b.nseg = 1; b.seg[0] = mega_seg(fp4_seg(ly.proj_out, H, nullptr), w.t_mixed);
+        b.nseg = 1; b.seg[0] = mega_seg(mixer_seg(ly, ly.proj_out, H), w.t_mixed);
+        if (ly.mixers_fp8) b.in_scale = ly.out_input_scale;
         if (ly.is_attention) b.prologue = PRO_NONE;
         else { b.prologue = PRO_GATED_NORM; b.z = w.t_mid; b.head_gamma = (const bf16*)ly.head_norm; }
         if (!mega_finish_stream(b, grid)) return QD_ERR_UNSUPPORTED;

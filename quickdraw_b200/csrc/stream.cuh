@@ -31,7 +31,8 @@ constexpr int kStreamStageBytes = 36864;   // 32 NVFP4 rows of 2048 inputs, or 1
 constexpr int kStreamConvRows = 256;       // conv rows one block can stage
 constexpr int kStreamConvWidth = 4;        // widest short convolution the fused epilogue takes
 
-enum SegKind { SEG_FP4 = 0, SEG_FP4_PAIR = 1, SEG_BF16 = 2 };
+// SEG_FP8: static E4M3 rows [out][K] bytes with one fp32 scale per matrix (persistent kernel only)
+enum SegKind { SEG_FP4 = 0, SEG_FP4_PAIR = 1, SEG_BF16 = 2, SEG_FP8 = 3 };
 enum SegEpilogue { EP_PLAIN = 0, EP_CONV = 1, EP_ARGMAX = 2, EP_ROUTE = 3 };
 enum Prologue { PRO_NONE = 0, PRO_ADD_NORM = 1, PRO_GATED_NORM = 2 };
 

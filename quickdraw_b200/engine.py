@@ -78,8 +78,8 @@ class Engine:
             if kernels is None and fused.supports(ckpt):
                 self.fused = fused.FusedStep(ckpt)
                 self.step = self.fused
-                if sequence_prefill:
-                    from .prefill import ChunkPrefill
+                if sequence_prefill and all(fused.mixer_format(layer) == "nvfp4" for layer in ckpt.layers):
+                    from .prefill import ChunkPrefill     # (FP8 mixers: the prompt goes token by token)
                     self.chunk_prefill = ChunkPrefill(ckpt)
                     self.sequence_prefill = True
             else:

@@ -36,7 +36,8 @@ class QdLayer(Structure):
                 ("router", c_void_p), ("shared_expert_gate", c_void_p),
                 ("experts_gate", QdFp4), ("experts_up", QdFp4), ("experts_down", QdFp4),
                 ("shared_gate", QdFp4), ("shared_up", QdFp4), ("shared_down", QdFp4),
-                ("experts_global_per_expert", c_int), ("state_index", c_int)]
+                ("experts_global_per_expert", c_int), ("state_index", c_int),
+                ("mixers_fp8", c_int), ("mixer_input_scale", c_void_p), ("out_input_scale", c_void_p)]
 
 
 class QdModelConfig(Structure):
@@ -68,9 +69,38 @@ def _fp4(proj: NVFP4Linear) -> QdFp4:
     return QdFp4(proj.weight.data_ptr(), proj.weight_scale.data_ptr(), proj.weight_scale_2.data_ptr())
 
 
+def _fp8(proj) -> QdFp4:
+    """A static FP8 projection in the descriptor of a mixer projection: E4M3 weights in ``codes``,
+    no block scales, the fp32 weight scale in ``global``."""
+    assert proj.weight.is_cuda and proj.weight.is_contiguous() and proj.weight.dtype == torch.float8_e4m3fn
+    assert proj.weight_scale.dtype == torch.float32 and proj.weight_scale.numel() == 1
+    assert proj.input_scale is not None and proj.input_scale.dtype == torch.float32 and proj.input_scale.numel() == 1
+    assert proj.weight.data_ptr() % 16 == 0
+    return QdFp4(proj.weight.data_ptr(), None, proj.weight_scale.data_ptr())
+
+
+MIXER_NAMES = {"full_attention": ("q_proj", "k_proj", "v_proj", "o_proj"),
+               "linear_attention": ("in_proj_qkv", "in_proj_z", "out_proj")}
+
+
+def mixer_format(layer) -> str:
+    """'nvfp4', 'fp8' (all projections of the mixer static FP8 with one input scale for those
+    that read the layer input) or 'mixed' (not covered by the fused step)."""
+    from .weights import FP8Linear
+    projections = [getattr(layer.attn, name) for name in MIXER_NAMES[layer.layer_type]]
+    if all(isinstance(p, NVFP4Linear) for p in projections):
+        return "nvfp4"
+    if all(isinstance(p, FP8Linear) and p.input_scale is not None for p in projections):
+        readers = projections[:-1]
+        if all(float(p.input_scale) == float(readers[0].input_scale) for p in readers):
+            return "fp8"
+    return "mixed"
+
+
 def supports(ckpt: Checkpoint) -> bool:
     """Shapes the fused step covers: the 36B-A3B widths (any depth, vocabulary, expert
-    count up to 256, top-k up to 8)."""
+    count up to 256, top-k up to 8); mixers NVFP4 or static FP8 whose input-reading projections
+    share one activation scale (``loader.merge_fp8_scales``), NVFP4 experts, bf16 LM head."""
     c = ckpt.config
     return (isinstance(ckpt.lm_head, torch.Tensor) and c.hidden_size == 2048
             and c.linear_num_value_heads * c.linear_value_head_dim == 4096
@@ -78,11 +108,7 @@ def supports(ckpt: Checkpoint) -> bool:
             and c.shared_expert_intermediate_size == 512 and c.linear_value_head_dim == 128
             and c.linear_key_head_dim <= 128 and c.num_experts <= 256 and c.num_experts_per_tok <= 8
             and c.head_dim <= 256 and c.num_attention_heads // c.num_key_value_heads <= 8
-            and all(isinstance(getattr(layer.attn, name), NVFP4Linear)
-                    for layer in ckpt.layers
-                    for name in (("q_proj", "k_proj", "v_proj", "o_proj")
-                                 if layer.layer_type == "full_attention"
-                                 else ("in_proj_qkv", "in_proj_z", "out_proj"))))
+            and all(mixer_format(layer) != "mixed" for layer in ckpt.layers))
 
 
 class FusedStep:
@@ -132,14 +158,21 @@ class FusedStep:
             assert moe.experts_gate.weight.shape[0] == hi - lo, "expert banks must hold the owned range"
             d = QdLayer()
             d.gamma_in, d.gamma_post = gamma(layer.input_layernorm), gamma(layer.post_attention_layernorm)
+            fp8 = mixer_format(layer) == "fp8"
+            describe = _fp8 if fp8 else _fp4
+            if fp8:
+                names = MIXER_NAMES[layer.layer_type]
+                d.mixers_fp8 = 1
+                d.mixer_input_scale = getattr(at, names[0]).input_scale.data_ptr()
+                d.out_input_scale = getattr(at, names[-1]).input_scale.data_ptr()
             if layer.layer_type == "full_attention":
                 d.is_attention = 1
-                d.proj_a, d.proj_b, d.proj_c, d.proj_out = map(_fp4, (at.q_proj, at.k_proj, at.v_proj, at.o_proj))
+                d.proj_a, d.proj_b, d.proj_c, d.proj_out = map(describe, (at.q_proj, at.k_proj, at.v_proj, at.o_proj))
                 d.q_norm, d.k_norm = at.q_norm.data_ptr(), at.k_norm.data_ptr()
                 d.state_index, full = full, full + 1
             else:
                 d.is_attention = 0
-                d.proj_a, d.proj_b, d.proj_out = _fp4(at.in_proj_qkv), _fp4(at.in_proj_z), _fp4(at.out_proj)
+                d.proj_a, d.proj_b, d.proj_out = describe(at.in_proj_qkv), describe(at.in_proj_z), describe(at.out_proj)
                 for name in ("in_proj_a", "in_proj_b", "conv1d", "A_log", "dt_bias", "norm"):
                     t = getattr(at, name)
                     assert t.dtype == BF16 and t.is_contiguous() and t.is_cuda
@@ -165,6 +198,8 @@ class FusedStep:
         if persistent is None:
             persistent = True
         assert persistent or not self.sliced, "a model slice runs through the persistent kernel only"
+        assert persistent or all(mixer_format(layer) == "nvfp4" for layer in ckpt.layers), \
+            "static FP8 mixers run through the persistent kernel only"
         if persistent:
             size = self.lib.qd_program_bytes(self.model)
             host = torch.zeros(size, dtype=torch.uint8)

@@ -18,7 +18,7 @@ import zlib
 
 import torch
 
-from .weights import (Checkpoint, FullAttnWeights, GDNWeights, LayerWeights, ModelConfig,
+from .weights import (Checkpoint, FP8Linear, FullAttnWeights, GDNWeights, LayerWeights, ModelConfig,
                       MoEWeights, NVFP4Linear)
 
 BF16 = torch.bfloat16
@@ -71,6 +71,15 @@ class Source:
         return NVFP4Linear(codes, scales.to(torch.float8_e4m3fn), gs)
 
 
+def _fp8(src: "Source", name: str, out: int, inp: int, input_scale: float = 4.0 / 448.0) -> FP8Linear:
+    """Static E4M3 projection of about the same real magnitude as the NVFP4 ones (weights ~
+    N(0, 0.1)); activations up to +-4 fill the E4M3 range, larger ones clamp."""
+    g = src._gen(name)
+    w = torch.randn((out, inp), generator=g, device=src.device, dtype=torch.float32).mul_(64.0).clamp_(-448, 448)
+    return FP8Linear(w.to(torch.float8_e4m3fn), torch.tensor(0.1 / 64.0, dtype=torch.float32, device=src.device),
+                     torch.tensor(input_scale, dtype=torch.float32, device=src.device))
+
+
 def expert_slice(bank: NVFP4Linear, lo: int, hi: int) -> NVFP4Linear:
     """Experts [lo, hi) of a bank as an independent (contiguous) bank."""
     g = bank.weight_scale_2
@@ -99,41 +108,43 @@ def make_moe(cfg: ModelConfig, src: Source, tag: str = "moe",
         shared_down=src.nvfp4(f"{tag}.shared_down", h, s))
 
 
-def make_gdn(cfg: ModelConfig, src: Source, tag: str = "gdn") -> GDNWeights:
+def make_gdn(cfg: ModelConfig, src: Source, tag: str = "gdn", fp8: bool = False) -> GDNWeights:
     h = cfg.hidden_size
+    linear = (lambda name, out, inp: _fp8(src, name, out, inp)) if fp8 else src.nvfp4
     kw = cfg.linear_num_key_heads * cfg.linear_key_head_dim
     vw = cfg.linear_num_value_heads * cfg.linear_value_head_dim
     hv = cfg.linear_num_value_heads
     return GDNWeights(
-        in_proj_qkv=src.nvfp4(f"{tag}.in_proj_qkv", 2 * kw + vw, h),
-        in_proj_z=src.nvfp4(f"{tag}.in_proj_z", vw, h),
+        in_proj_qkv=linear(f"{tag}.in_proj_qkv", 2 * kw + vw, h),
+        in_proj_z=linear(f"{tag}.in_proj_z", vw, h),
         in_proj_a=src.normal(f"{tag}.in_proj_a", hv, h, std=0.02),
         in_proj_b=src.normal(f"{tag}.in_proj_b", hv, h, std=0.02),
         conv1d=src.normal(f"{tag}.conv1d", 2 * kw + vw, 1, cfg.linear_conv_kernel_dim, std=0.5),
         A_log=src.normal(f"{tag}.A_log", hv, std=0.5),
         dt_bias=src.normal(f"{tag}.dt_bias", hv, std=0.5),
         norm=src.normal(f"{tag}.norm", cfg.linear_value_head_dim, std=0.02, mean=1.0),
-        out_proj=src.nvfp4(f"{tag}.out_proj", h, vw))
+        out_proj=linear(f"{tag}.out_proj", h, vw))
 
 
-def make_attention(cfg: ModelConfig, src: Source, tag: str = "attn") -> FullAttnWeights:
+def make_attention(cfg: ModelConfig, src: Source, tag: str = "attn", fp8: bool = False) -> FullAttnWeights:
     h = cfg.hidden_size
+    linear = (lambda name, out, inp: _fp8(src, name, out, inp)) if fp8 else src.nvfp4
     qw = cfg.num_attention_heads * cfg.head_dim
     kvw = cfg.num_key_value_heads * cfg.head_dim
     return FullAttnWeights(
-        q_proj=src.nvfp4(f"{tag}.q_proj", 2 * qw, h),
-        k_proj=src.nvfp4(f"{tag}.k_proj", kvw, h),
-        v_proj=src.nvfp4(f"{tag}.v_proj", kvw, h),
-        o_proj=src.nvfp4(f"{tag}.o_proj", h, qw),
+        q_proj=linear(f"{tag}.q_proj", 2 * qw, h),
+        k_proj=linear(f"{tag}.k_proj", kvw, h),
+        v_proj=linear(f"{tag}.v_proj", kvw, h),
+        o_proj=linear(f"{tag}.o_proj", h, qw),
         q_norm=src.normal(f"{tag}.q_norm", cfg.head_dim, std=0.02),
         k_norm=src.normal(f"{tag}.k_norm", cfg.head_dim, std=0.02))
 
 
-def make_layer(cfg: ModelConfig, src: Source, idx: int, expert_range=None) -> LayerWeights:
+def make_layer(cfg: ModelConfig, src: Source, idx: int, expert_range=None, fp8_mixers: bool = False) -> LayerWeights:
     kind = cfg.layer_types[idx]
     tag = f"layer{idx}"
-    mixer = (make_attention(cfg, src, f"{tag}.attn") if kind == "full_attention"
-             else make_gdn(cfg, src, f"{tag}.gdn"))
+    mixer = (make_attention(cfg, src, f"{tag}.attn", fp8_mixers) if kind == "full_attention"
+             else make_gdn(cfg, src, f"{tag}.gdn", fp8_mixers))
     return LayerWeights(
         idx=idx, layer_type=kind,
         input_layernorm=src.normal(f"{tag}.input_layernorm", cfg.hidden_size, std=0.02),
@@ -143,7 +154,7 @@ def make_layer(cfg: ModelConfig, src: Source, idx: int, expert_range=None) -> La
 
 
 def make_checkpoint(cfg: ModelConfig, seed: int = 0, device="cuda", expert_range=None,
-                    vocab_range=None) -> Checkpoint:
+                    vocab_range=None, fp8_mixers: bool = False) -> Checkpoint:
     """Whole model with a bf16 embedding and a bf16 LM head (about 23 GB at 48 layers);
     with ``expert_range`` only that slice of every expert bank is kept, with ``vocab_range``
     only those rows of the LM head (the values are those of the whole model)."""
@@ -156,7 +167,7 @@ def make_checkpoint(cfg: ModelConfig, seed: int = 0, device="cuda", expert_range
         embed_tokens=src.normal("embed_tokens", cfg.vocab_size, cfg.hidden_size, std=0.02),
         final_norm=src.normal("final_norm", cfg.hidden_size, std=0.02),
         lm_head=lm_head,
-        layers=[make_layer(cfg, src, i, expert_range) for i in range(cfg.num_hidden_layers)])
+        layers=[make_layer(cfg, src, i, expert_range, fp8_mixers) for i in range(cfg.num_hidden_layers)])
 
 
 def to_device(obj, device):

@@ -373,3 +373,40 @@ def test_prefix_reuse_against_a_fresh_prefill(cuda_device):
     b = fresh.prefill(other)
     assert reuse.reused_tokens == 0 and torch.equal(a, b)
     assert torch.equal(reuse.state.rec_state, fresh.state.rec_state)
+
+
+def test_static_fp8_mixers_in_the_one_launch_step(cuda_device):
+    """The published checkpoint's mixer format (FP8Linear, quickdraw/models/weights.py:58-74;
+    fp8_gemv, qwen.py:25-33) inside the persistent step: E4M3 weights, the activation vector
+    quantised with the static input scale in the phase prologue, matrix and activation scales
+    after the sum.  Against the oracle (whole step and state) and against this library's
+    composed operator table, whose FP8 projection is a separate kernel."""
+    from quickdraw_b200.engine import Engine
+    from quickdraw_b200.fused import FusedStep, mixer_format, supports
+    from quickdraw_b200.kernels import bind_kernels
+    cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
+    ckpt = synthetic.make_checkpoint(cfg, seed=13, device="cuda", fp8_mixers=True)
+    assert supports(ckpt) and {mixer_format(layer) for layer in ckpt.layers} == {"fp8"}
+    cpu = to_device(ckpt, "cpu")
+    step, composed = FusedStep(ckpt), bind_kernels()["forward_step"]
+    state, other = (DecodeState.allocate(cfg, 32, "cuda") for _ in range(2))
+    ref = DecodeState.allocate(cfg, 32, "cpu")
+    for s in (state, other, ref):
+        s.kv_k.zero_()
+        s.kv_v.zero_()
+    for position, token in enumerate([7, 1500, 3, 900, 41]):
+        got = step(ckpt, torch.tensor(token, device="cuda"), position, state)
+        want = O.forward_step(cpu, torch.tensor(token), position, ref)
+        also = composed(ckpt, torch.tensor(token, device="cuda"), position, other)
+        assert O.rel_l2(got.cpu(), want) < 5e-2, position
+        assert O.rel_l2(got.cpu(), also.cpu()) < 5e-2, position
+    assert step.status() == 0
+    assert O.rel_l2(state.rec_state.cpu(), ref.rec_state) < 5e-2
+    assert O.rel_l2(state.conv_state.cpu(), ref.conv_state) < 5e-2
+    assert O.rel_l2(state.kv_k[:, :5].cpu(), ref.kv_k[:, :5]) < 5e-2
+    # the engine takes the one-launch step for such a model (prompt token by token) and generates
+    engine = Engine(ckpt, max_context=32, device="cuda")
+    assert engine.fused is not None and not engine.sequence_prefill
+    engine.state.kv_k.zero_()
+    engine.state.kv_v.zero_()
+    assert len(engine.generate([7, 1500, 3], 6)) == 6
