@@ -318,6 +318,9 @@ typedef struct {
     const void* embed;                                   /* bf16 [vocab, hidden] */
     const float* final_gamma;                            /* fp32 [hidden] */
     const void* lm_head;                                 /* bf16 rows [vocab_lo, vocab_hi) of [vocab, hidden] */
+    /* The published checkpoint's LM head is NVFP4 (quickdraw/models/weights.py:164): when
+     * lm_head_fp4.codes is set it replaces lm_head (same row range).  Persistent step only. */
+    qd_fp4 lm_head_fp4;
 } qd_model_config;
 
 typedef struct {

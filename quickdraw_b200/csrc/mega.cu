@@ -537,6 +537,13 @@ static __device__ __noinline__ void head_argmax(const MegaParams& mp, const Smem
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* red = S.red;
 
+    // over the lanes first (NVFP4 head rows end in different lanes; bf16 rows leave every lane equal)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best_val, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
+        if (ov > best_val || (ov == best_val && oi < best_idx)) { best_val = ov; best_idx = oi; }
+    }
     if (lane == 0) { red[32 + warp] = best_val; reinterpret_cast<int*>(red)[48 + warp] = best_idx; }
     named_barrier(1, CT);
     if (tid == 0) {
@@ -895,6 +902,12 @@ QD_DEVINL void stream_phase(const MegaParams& mp, const MegaPhase& ph, const Sme
                             }
                             const float conv = (prod[0] + prod[2]) + (prod[1] + prod[3]);
                             st_word(sg.y + row, make_word(__float2bfloat16_rn(silu_precise(conv)), tag));
+                        } else if (KC == 2 && sg.epilogue == EP_ARGMAX) {
+                            // an NVFP4 LM head: this lane's row is a vocabulary entry
+                            const int index = ph.row_lo + row;
+                            mp.logits[index] = rounded;
+                            const float v = __bfloat162float(rounded);
+                            if (v > best_val || (v == best_val && index < best_idx)) { best_val = v; best_idx = index; }
                         } else {
                             st_word(sg.y + row, make_word(rounded, tag));
                         }

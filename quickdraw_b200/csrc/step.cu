@@ -130,6 +130,7 @@ int run_layers(qd_model* m, const qd_state* st, const long long* token, const in
     if (!fused_shape_ok(c)) return QD_ERR_UNSUPPORTED;
     for (int L = begin; L < end; ++L)
         if (m->layers[L].mixers_fp8) return QD_ERR_UNSUPPORTED;      // static FP8 mixers: persistent step only
+    if (head && c.lm_head_fp4.codes) return QD_ERR_UNSUPPORTED;      // NVFP4 LM head: persistent step only
     const bool pdl = flags & QD_FLAG_PDL;
     Workspace w = carve(c, (uint8_t*)workspace);
     const int H = c.hidden;
@@ -481,7 +482,8 @@ extern "C" int qd_program_build(const qd_model* model, void* workspace, void* ho
     h.gamma = c.final_gamma; h.x = w.t_moe_out; h.x_prev_layer = 1;
     h.nseg = 1;
     const int vocab_lo = c.vocab_hi ? c.vocab_lo : 0, vocab_hi = c.vocab_hi ? c.vocab_hi : c.vocab;
-    h.seg[0] = mega_seg(bf16_seg(c.lm_head, vocab_hi - vocab_lo, nullptr, EP_ARGMAX), nullptr);
+    h.seg[0] = c.lm_head_fp4.codes ? mega_seg(fp4_seg(c.lm_head_fp4, vocab_hi - vocab_lo, nullptr, EP_ARGMAX), nullptr)
+                                   : mega_seg(bf16_seg(c.lm_head, vocab_hi - vocab_lo, nullptr, EP_ARGMAX), nullptr);
     h.row_lo = vocab_lo;
     if (!mega_finish_stream(h, grid)) return QD_ERR_UNSUPPORTED;
     out[n++] = h;

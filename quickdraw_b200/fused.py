@@ -47,7 +47,7 @@ class QdModelConfig(Structure):
                 ("conv_width", c_int), ("experts", c_int), ("topk", c_int), ("intermediate", c_int),
                 ("eps", c_float), ("rope_theta", c_float), ("expert_lo", c_int), ("expert_hi", c_int),
                 ("vocab_lo", c_int), ("vocab_hi", c_int),
-                ("embed", c_void_p), ("final_gamma", c_void_p), ("lm_head", c_void_p)]
+                ("embed", c_void_p), ("final_gamma", c_void_p), ("lm_head", c_void_p), ("lm_head_fp4", QdFp4)]
 
 
 class QdExchange(Structure):
@@ -100,9 +100,11 @@ def mixer_format(layer) -> str:
 def supports(ckpt: Checkpoint) -> bool:
     """Shapes the fused step covers: the 36B-A3B widths (any depth, vocabulary, expert
     count up to 256, top-k up to 8); mixers NVFP4 or static FP8 whose input-reading projections
-    share one activation scale (``loader.merge_fp8_scales``), NVFP4 experts, bf16 LM head."""
+    share one activation scale (``loader.merge_fp8_scales``), NVFP4 experts, a bf16 or NVFP4 LM head."""
     c = ckpt.config
-    return (isinstance(ckpt.lm_head, torch.Tensor) and c.hidden_size == 2048
+    head_ok = isinstance(ckpt.lm_head, torch.Tensor) or (isinstance(ckpt.lm_head, NVFP4Linear) and ckpt.lm_head.weight.ndim == 2
+                                                         and ckpt.lm_head.weight_scale_2.numel() == 1)
+    return (head_ok and c.hidden_size == 2048
             and c.linear_num_value_heads * c.linear_value_head_dim == 4096
             and c.num_attention_heads * c.head_dim == 4096 and c.moe_intermediate_size == 512
             and c.shared_expert_intermediate_size == 512 and c.linear_value_head_dim == 128
@@ -135,9 +137,11 @@ class FusedStep:
             self._keep.append(g)
             return g.data_ptr()
 
-        assert ckpt.embed_tokens.dtype == BF16 and ckpt.lm_head.dtype == BF16
-        assert ckpt.embed_tokens.is_contiguous() and ckpt.lm_head.is_contiguous()
-        assert ckpt.lm_head.shape[0] == ((vocab_range[1] - vocab_range[0]) if vocab_range else c.vocab_size), \
+        self.head_fp4 = isinstance(ckpt.lm_head, NVFP4Linear)
+        head_rows = ckpt.lm_head.out_features if self.head_fp4 else ckpt.lm_head.shape[0]
+        assert ckpt.embed_tokens.dtype == BF16 and ckpt.embed_tokens.is_contiguous()
+        assert self.head_fp4 or (ckpt.lm_head.dtype == BF16 and ckpt.lm_head.is_contiguous())
+        assert head_rows == ((vocab_range[1] - vocab_range[0]) if vocab_range else c.vocab_size), \
             "lm_head must hold exactly the owned rows"
         cfg = QdModelConfig(
             hidden=c.hidden_size, layers=c.num_hidden_layers, vocab=c.vocab_size,
@@ -149,7 +153,8 @@ class FusedStep:
             eps=c.rms_norm_eps, rope_theta=c.rope_theta, expert_lo=lo, expert_hi=hi,
             vocab_lo=vocab_range[0] if vocab_range else 0, vocab_hi=vocab_range[1] if vocab_range else 0,
             embed=ckpt.embed_tokens.data_ptr(), final_gamma=gamma(ckpt.final_norm),
-            lm_head=ckpt.lm_head.data_ptr())
+            lm_head=None if self.head_fp4 else ckpt.lm_head.data_ptr(),
+            lm_head_fp4=_fp4(ckpt.lm_head) if self.head_fp4 else QdFp4())
         self.model = c_void_p()
         check(self.lib.qd_model_create(byref(cfg), byref(self.model)), "qd_model_create")
         full = linear = 0
@@ -198,8 +203,8 @@ class FusedStep:
         if persistent is None:
             persistent = True
         assert persistent or not self.sliced, "a model slice runs through the persistent kernel only"
-        assert persistent or all(mixer_format(layer) == "nvfp4" for layer in ckpt.layers), \
-            "static FP8 mixers run through the persistent kernel only"
+        assert persistent or (not self.head_fp4 and all(mixer_format(layer) == "nvfp4" for layer in ckpt.layers)), \
+            "static FP8 mixers and an NVFP4 LM head run through the persistent kernel only"
         if persistent:
             size = self.lib.qd_program_bytes(self.model)
             host = torch.zeros(size, dtype=torch.uint8)

@@ -154,12 +154,16 @@ def make_layer(cfg: ModelConfig, src: Source, idx: int, expert_range=None, fp8_m
 
 
 def make_checkpoint(cfg: ModelConfig, seed: int = 0, device="cuda", expert_range=None,
-                    vocab_range=None, fp8_mixers: bool = False) -> Checkpoint:
+                    vocab_range=None, fp8_mixers: bool = False, nvfp4_head: bool = False) -> Checkpoint:
     """Whole model with a bf16 embedding and a bf16 LM head (about 23 GB at 48 layers);
     with ``expert_range`` only that slice of every expert bank is kept, with ``vocab_range``
     only those rows of the LM head (the values are those of the whole model)."""
     src = Source(seed, device)
-    lm_head = src.normal("lm_head", cfg.vocab_size, cfg.hidden_size, std=0.02)
+    if nvfp4_head:      # the published checkpoint's head format; weights of about the bf16 head's magnitude
+        assert vocab_range is None
+        lm_head = src.nvfp4("lm_head.fp4", cfg.vocab_size, cfg.hidden_size, global_scale=0.2)
+    else:
+        lm_head = src.normal("lm_head", cfg.vocab_size, cfg.hidden_size, std=0.02)
     if vocab_range is not None:
         lm_head = lm_head[vocab_range[0]:vocab_range[1]].clone()
     return Checkpoint(

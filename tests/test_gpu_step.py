@@ -410,3 +410,26 @@ def test_static_fp8_mixers_in_the_one_launch_step(cuda_device):
     engine.state.kv_k.zero_()
     engine.state.kv_v.zero_()
     assert len(engine.generate([7, 1500, 3], 6)) == 6
+
+
+def test_published_checkpoint_formats_in_the_one_launch_step(cuda_device):
+    """FP8 mixers, NVFP4 experts and an NVFP4 LM head together (the formats of the published
+    checkpoint, quickdraw/models/weights.py:160-166) through the persistent step: logits, greedy
+    token and state against the oracle."""
+    from quickdraw_b200.fused import FusedStep, supports
+    cfg = synthetic.model_config(num_layers=4, vocab_size=4096, experts=16, topk=8)
+    ckpt = synthetic.make_checkpoint(cfg, seed=17, device="cuda", fp8_mixers=True, nvfp4_head=True)
+    assert supports(ckpt)
+    cpu = to_device(ckpt, "cpu")
+    step = FusedStep(ckpt)
+    state, ref = DecodeState.allocate(cfg, 32, "cuda"), DecodeState.allocate(cfg, 32, "cpu")
+    for s in (state, ref):
+        s.kv_k.zero_()
+        s.kv_v.zero_()
+    for position, token in enumerate([7, 1500, 3, 900]):
+        got = step(ckpt, torch.tensor(token, device="cuda"), position, state)
+        want = O.forward_step(cpu, torch.tensor(token), position, ref)
+        assert O.rel_l2(got.cpu(), want) < 5e-2, position
+        assert int(step.next_token) == int(got.float().argmax())
+    assert step.status() == 0
+    assert O.rel_l2(state.rec_state.cpu(), ref.rec_state) < 5e-2
