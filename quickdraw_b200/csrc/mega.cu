@@ -140,8 +140,9 @@ QD_DEVINL bool tags4(const uint4& v, uint32_t tag) {
     return ((v.x >> 16) == tag) & ((v.y >> 16) == tag) & ((v.z >> 16) == tag) & ((v.w >> 16) == tag);
 }
 
-struct Wait {                 // what a bounded wait needs
+struct Wait {                 // what a bounded wait needs, and the launch number for 32-bit tags
     unsigned int* status; volatile int* abort; unsigned long long limit_ns;
+    unsigned int launch;
 };
 QD_DEVINL bool wait_expired(const Wait& w, unsigned long long start) {
     if (*w.abort) return true;
@@ -1270,7 +1271,8 @@ QD_DEVINL void attn_phase(const MegaParams& mp, const MegaPhase& ph, const Smem&
     }
     // ---- the block's partial: 64-bit {value, tag} words
     if (warp == 0) {
-        const uint32_t tag32 = ((tag_base >> 6) << 8) | (uint32_t)(ph.layer + 1);
+        const uint32_t tag32 = (wt.launch << 8) | (uint32_t)(ph.layer + 1);      // 24 bits of launch number: a split that is
+        // not written for many launches (shorter contexts in between) must not be mistaken for a fresh one
         uint2* block_out = mp.attn_partial + (((size_t)kvh * mp.attn_splits + split) * 8) * kAttnStride;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -1293,7 +1295,8 @@ QD_DEVINL void attn_merge_phase(const MegaParams& mp, const MegaPhase& ph, const
     const int position = mp.pos_dev ? *mp.pos_dev : mp.pos_host;
     const AttnSplit cut = attn_split(position + 1, mp.attn_splits);
     const uint32_t tag = tag_base | (uint32_t)(ph.layer + 1);
-    const uint32_t tag32 = ((tag_base >> 6) << 8) | (uint32_t)(ph.layer + 1);
+    const uint32_t tag32 = (wt.launch << 8) | (uint32_t)(ph.layer + 1);      // 24 bits of launch number: a split that is
+        // not written for many launches (shorter contexts in between) must not be mistaken for a fresh one
     float* part = reinterpret_cast<float*>(S.scratch);     // [16 warps][34]: 32 sums, max, denominator
     const int units = mp.hq * (D / 32);
 #pragma unroll 1
@@ -1550,7 +1553,7 @@ mega_kernel(const __grid_constant__ MegaParams mp) {
         producer(mp, S, lane);
     } else {
         Wait wt;
-        wt.status = mp.status; wt.abort = S.abort; wt.limit_ns = (unsigned long long)mp.wait_limit_us * 1000ull;
+        wt.status = mp.status; wt.abort = S.abort; wt.limit_ns = (unsigned long long)mp.wait_limit_us * 1000ull; wt.launch = launch;
         // rotation table of this step's position, once for all attention layers
         // (quickdraw/models/qwen.py:84-88: fp32 angle, cos / sin rounded to bf16)
         if (mp.rotary > 0) {
