@@ -6,9 +6,15 @@
 // causal attention over cache + chunk, routing and the MoE combine.
 // Reference: the 2-D branches of quickdraw/kernel/triton/{delta,attention,moe,norm}.py and
 // quickdraw/models/qwen.py:66-241.
+#include "attn_mma.cuh"
 #include "rowdot.cuh"
 
 namespace {
+
+using qd::AttnAcc;
+using qd::attn_chunk;
+using qd::kAttnQRow;
+using qd::kAttnRow;
 
 // ------------------------------------------------------------------ residual add + RMSNorm
 __global__ void seq_add_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual,
@@ -713,6 +719,96 @@ batch_attn_lanes_kernel(const LaneAttnParams p) {
     if (tid == 0) *counter = 0;
 }
 
+// ------------------------------------------------ causal attention of a prompt chunk on the tensor cores
+// The chunk's tokens sit at consecutive positions position0 .. position0 + tokens - 1 of ONE
+// cache (rows already prepared by seq_attn_prepare_kernel).  Block = (sixteen consecutive tokens,
+// KV head); a warp owns one token and its (up to eight) query heads of that KV head.  The block
+// walks the cache in tiles of 64 positions: key and value rows of the tile are copied to shared
+// memory once (cp.async, two tiles in flight) and read by all sixteen warps, which is what the
+// lane-per-position kernel cannot do (there every token streams its whole history from L2).  A
+// warp multiplies its heads with sixteen positions at a time on mma.sync (attn_mma.cuh: scores
+// S^T = K Q^T, running softmax, O^T += V^T P^T with the probabilities as two bf16 pieces) up to its
+// own position; output = bf16(attended) * bf16(sigmoid(gate)) as in the decode kernels
+// (quickdraw/kernel/triton/attention.py:53-100).  Head dimension 256, group of at most 8.
+constexpr int kFlashTokens = 16, kFlashTile = 64, kFlashThreads = kFlashTokens * 32;
+constexpr int kFlashTileBytes = 2 * kFlashTile * kAttnRow;      // key rows, then value rows
+constexpr size_t kFlashSmem = (size_t)kFlashTokens * 8 * kAttnQRow + 2 * (size_t)kFlashTileBytes;
+
+__global__ void __launch_bounds__(kFlashThreads, 1)
+seq_flash_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ qg, const bf16* __restrict__ k_cache,
+                           const bf16* __restrict__ v_cache, bf16* __restrict__ out, int tokens, int position0, int hq, int hk) {
+    extern __shared__ __align__(16) unsigned char flash_smem[];
+    constexpr int D = 256;
+    const int G = hq / hk, kvh = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int token0 = blockIdx.x * kFlashTokens, token = token0 + warp;
+    const bool live = token < tokens;
+    uint8_t* q_s = flash_smem + (size_t)warp * 8 * kAttnQRow;                      // this warp's query heads
+    uint8_t* tiles = flash_smem + (size_t)kFlashTokens * 8 * kAttnQRow;
+    // query heads of the warp's token (heads beyond the group, and a token beyond the chunk: zeros)
+    for (int h = 0; h < 8; ++h) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (live && h < G) v = reinterpret_cast<const uint4*>(q + ((size_t)token * hq + kvh * G + h) * D)[lane];
+        reinterpret_cast<uint4*>(q_s + h * kAttnQRow)[lane] = v;
+    }
+    // positions every token of the block may see: [0, last]; the warp's own limit is its position
+    const int last = position0 + min(tokens, token0 + kFlashTokens) - 1;
+    const int mine = live ? position0 + token + 1 : 0;                             // end of the warp's range
+    const int ntiles = last / kFlashTile + 1;
+    auto fetch = [&](int tile) {
+        // 64 key rows and 64 value rows of 512 bytes: 32 sixteen-byte pieces per row, 4096 pieces in all
+        uint8_t* dst = tiles + (size_t)(tile & 1) * kFlashTileBytes;
+        const int first = tile * kFlashTile;
+        for (int piece = tid; piece < 2 * kFlashTile * 32; piece += kFlashThreads) {
+            const int row = piece >> 5, c = piece & 31, pos = first + (row & (kFlashTile - 1));
+            const bf16* src = (row < kFlashTile ? k_cache : v_cache) + ((size_t)min(pos, last) * hk + kvh) * D;
+            const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst + (size_t)row * kAttnRow + c * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(reinterpret_cast<const uint8_t*>(src) + c * 16) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    AttnAcc acc;
+    acc.m = -INFINITY; acc.l = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { acc.out[i][0] = 0.f; acc.out[i][1] = 0.f; acc.out[i][2] = 0.f; acc.out[i][3] = 0.f; }
+    fetch(0);
+    for (int tile = 0; tile < ntiles; ++tile) {
+        if (tile + 1 < ntiles) { fetch(tile + 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                   // the tile (and, the first time, the queries) are in place
+        const uint8_t* buf = tiles + (size_t)(tile & 1) * kFlashTileBytes;
+        const int first = tile * kFlashTile;
+#pragma unroll 1
+        for (int c = 0; c < kFlashTile / 16; ++c) {
+            const int start = first + 16 * c;
+            if (start < mine)
+                attn_chunk(acc, q_s, buf + (size_t)(16 * c) * kAttnRow, buf + (size_t)(kFlashTile + 16 * c) * kAttnRow, start, mine, lane);
+        }
+        __syncthreads();                                   // everybody is done with this buffer before it is refilled
+    }
+    if (!live) return;
+    // ---- normalise and gate: lane (g, t) holds out[i][c] = feature 32 g + 2 i + (c >> 1) of head 2 t + (c & 1)
+    const int g = lane >> 2, t = lane & 3;
+    acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 1);
+    acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 2);
+    const float l_even = __shfl_sync(0xffffffffu, acc.l, 8 * t), l_odd = __shfl_sync(0xffffffffu, acc.l, 8 * t + 4);
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+        const int h = 2 * t + cc;
+        if (h >= G) continue;
+        const int qh = kvh * G + h;
+        const float den = cc ? l_odd : l_even;
+        const bf16* gate_row = qg + ((size_t)token * hq + qh) * 2 * D + D;
+        bf16* dst = out + ((size_t)token * hq + qh) * D;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int f = 32 * g + 2 * i;
+            const float a0 = round_bf16(acc.out[i][cc] / den), a1 = round_bf16(acc.out[i][2 + cc] / den);
+            const float g0 = round_bf16(sigmoid_precise(ld_bf16(gate_row + f))), g1 = round_bf16(sigmoid_precise(ld_bf16(gate_row + f + 1)));
+            *reinterpret_cast<__nv_bfloat162*>(dst + f) = __floats2bfloat162_rn(a0 * g0, a1 * g1);
+        }
+    }
+}
+
 // ----------------------------------------------------------------------------- routing
 __global__ void seq_route_kernel(const bf16* __restrict__ logits, int experts, int topk, int32_t* __restrict__ ids,
                                  float* __restrict__ weights) {
@@ -915,6 +1011,21 @@ extern "C" int qd_seq_attention(const void* qg, const void* k_new, const void* v
         (bf16*)k_cache, (bf16*)v_cache, (bf16*)q_scratch, position0, q_heads, kv_heads, head_dim, rotary_dim, theta, eps,
         nullptr, 0, capacity);
     if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
+    if (head_dim == 256 && tokens >= 2) {
+        // the tensor-core kernel: every cache tile is shared by sixteen tokens
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
+        static bool flash_configured[64];
+        if (!flash_configured[dev]) {
+            if (cudaFuncSetAttribute(seq_flash_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFlashSmem) != cudaSuccess)
+                return QD_ERR_LAUNCH;
+            flash_configured[dev] = true;
+        }
+        seq_flash_attention_kernel<<<dim3((tokens + kFlashTokens - 1) / kFlashTokens, kv_heads), kFlashThreads, kFlashSmem,
+                                     (cudaStream_t)stream>>>((const bf16*)q_scratch, (const bf16*)qg, (const bf16*)k_cache,
+                                                             (const bf16*)v_cache, (bf16*)out, tokens, position0, q_heads, kv_heads);
+        return qd_launch_status();
+    }
     seq_attn_kernel<<<dim3(kv_heads, tokens), 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)q_scratch, (const bf16*)qg, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, position0,
         q_heads, kv_heads, head_dim);

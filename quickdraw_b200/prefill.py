@@ -107,17 +107,12 @@ class ChunkPrefill:
         qg, k, v = self._matmul(x, w.q_proj), self._matmul(x, w.k_proj), self._matmul(x, w.v_proj)
         q_scratch = self._empty(tokens, c.num_attention_heads * c.head_dim)
         out = torch.empty_like(q_scratch)
-        # the batched decode attention with every row at its own position of the one cache
-        positions = torch.arange(position0, position0 + tokens, dtype=torch.int32, device=self.device)
-        # context splits only while the chunk's rows alone do not fill the GPU (a split costs a merge)
-        splits = max(1, min(16, (position0 + tokens + 255) // 256, 296 // (tokens * c.num_key_value_heads)))
-        floats = lib().qd_attn_scratch_floats(c.num_attention_heads, c.num_key_value_heads, c.head_dim, splits)
-        scratch = self._empty(tokens * floats, dtype=torch.float32)
-        counters = torch.zeros(tokens * c.num_key_value_heads, dtype=torch.int32, device=self.device)
-        call("qd_batch_attention", ptr(qg), ptr(k), ptr(v), ptr(w.q_norm), ptr(w.k_norm), ptr(state.kv_k[index]),
-             ptr(state.kv_v[index]), 0, ptr(q_scratch), ptr(out), ptr(scratch), ptr(counters), ptr(positions), tokens,
-             state.kv_k.shape[1], c.num_attention_heads, c.num_key_value_heads, c.head_dim,
-             int(c.head_dim * c.partial_rotary_factor), c.rope_theta, c.rms_norm_eps, splits, stream_of(x))
+        # q/k norm + RoPE + cache rows, then causal attention on the tensor cores: every cache tile
+        # is read once per sixteen tokens
+        call("qd_seq_attention", ptr(qg), ptr(k), ptr(v), ptr(w.q_norm), ptr(w.k_norm), ptr(state.kv_k[index]),
+             ptr(state.kv_v[index]), ptr(q_scratch), ptr(out), tokens, position0, state.kv_k.shape[1],
+             c.num_attention_heads, c.num_key_value_heads, c.head_dim, int(c.head_dim * c.partial_rotary_factor),
+             c.rope_theta, c.rms_norm_eps, stream_of(x))
         return self._matmul(out, w.o_proj)
 
     def _moe(self, w, x):
