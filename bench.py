@@ -418,19 +418,19 @@ def batch_decode_leg(ckpt, cfg, device, batch=32, context=8192, steps=8, warmup=
     does), one token per sequence per step; device-timed."""
     from quickdraw_b200.batch import BatchDecode, BatchState
     decoder = BatchDecode(ckpt, **(slices or {}), group=group)
-    state = BatchState(cfg, batch, context + warmup + steps, device)
+    state = BatchState(cfg, batch, context + max(warmup, 3) + steps, device)
     state.kv_k.normal_()
     state.kv_v.normal_()
     state.positions.fill_(context)
     gen = torch.Generator().manual_seed(1)
     tokens = torch.randint(0, cfg.vocab_size, (batch,), generator=gen).to(device)
-    for _ in range(warmup):
-        tokens, _ = decoder.step(tokens, state, positions_checked=True)
+    for _ in range(max(warmup, 3)):      # eager, capture, first replay
+        tokens, _ = decoder.graph_step(tokens, state)
     torch.cuda.synchronize(device)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        tokens, _ = decoder.step(tokens, state, positions_checked=True)
+        tokens, _ = decoder.graph_step(tokens, state)
     e1.record()
     torch.cuda.synchronize(device)
     assert decoder.check() == 0
@@ -440,7 +440,7 @@ def batch_decode_leg(ckpt, cfg, device, batch=32, context=8192, steps=8, warmup=
         torch.distributed.all_reduce(worst, op=torch.distributed.ReduceOp.MAX, group=group)
         ms = float(worst.item())
     return {"batch": batch, "context": context, "steps": steps, "ms_per_step": ms, "tok_s": batch / (ms * 1e-3),
-            "state_bytes": state.memory_bytes(), "path": "tensor-core products with %d rows + batched state kernels" % batch
+            "state_bytes": state.memory_bytes(), "path": "one CUDA graph per step: tensor-core products with %d rows + batched state kernels" % batch
             + (", routed experts and LM head split over the ranks" if slices else "")}
 
 

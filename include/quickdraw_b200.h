@@ -62,6 +62,17 @@ int qd_nvfp4_matmul(const void* x, const void* codes, const void* scales, const 
                     int tokens, int out_features, int in_features, int group_size,
                     unsigned int* status, void* stream);
 
+/* The same product for at most 32 token rows (the dense projections of a decode batch): every
+ * weight tile is decoded once on the warp-level tensor-core instruction with the tokens as
+ * columns; no 128-token tiles.  scratch: qd_nvfp4_matmul_rows_scratch_bytes(in_features) bytes,
+ * 16-byte aligned, receives the token rows as f16; convert = 0 reuses what the previous call with
+ * this scratch area converted (several projections of one input).  in_features % 512 == 0,
+ * out_features % 16 == 0, else QD_ERR_UNSUPPORTED. */
+long long qd_nvfp4_matmul_rows_scratch_bytes(int in_features);
+int qd_nvfp4_matmul_rows(const void* x, const void* codes, const void* scales, const float* global, void* y,
+                         int tokens, int out_features, int in_features, int group_size, void* scratch,
+                         int convert, void* stream);
+
 /* Activation quantiser of the FP4 x FP4 ("W4A4") product that quickdraw's todo.md:13 asks to
  * validate separately from the W4A16 path: x bf16 [tokens, in_features] -> E2M1 codes
  * [tokens, in_features / 2] (low nibble = even input), one E4M3 scale per sixteen inputs
@@ -99,6 +110,16 @@ int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const void* scales
                             int in_features, int group_size, int by_token, int scatter,
                             int global_per_expert, int max_rows_per_expert, unsigned int* status,
                             void* stream);
+
+/* The same product when an expert receives only a few rows (a short chunk, a decode batch):
+ * every expert that got routes is read once, its NVFP4 rows decoded once per eight routes and
+ * multiplied on the warp-level tensor-core instruction (the grouped branch of
+ * quickdraw/kernel/triton/moe.py:99-151 at small M).  Arguments as above; in_features
+ * 512, 1024 or 2048, out_features a multiple of 16, else QD_ERR_UNSUPPORTED. */
+int qd_nvfp4_expert_rows(const void* x, const void* codes, const void* scales, const float* global,
+                         const int32_t* order, const int32_t* boundaries, const float* routing, void* y,
+                         int routes, int experts, int topk, int out_features, int in_features,
+                         int group_size, int by_token, int scatter, int global_per_expert, void* stream);
 
 /* ---- Sequence forms for a chunk of prompt tokens (the 2-D branches of
  * quickdraw/kernel/triton/{norm,delta,attention,moe}.py, qwen.py:66-241): the single-token

@@ -49,9 +49,12 @@ SIGNATURES = {
     "qd_set_wait_limit_us": [ctypes.c_uint],
     "qd_nvfp4_gemv_bank": [P, P, P, P, P, I, I, I, I, P],
     "qd_nvfp4_matmul": [P, P, P, P, P, I, I, I, I, P, P],
+    "qd_nvfp4_matmul_rows_scratch_bytes": [I],
+    "qd_nvfp4_matmul_rows": [P, P, P, P, P, I, I, I, I, P, I, P],
     "qd_nvfp4_quantize_act": [P, I, I, P, P, P, P, P],
     "qd_nvfp4_matmul_w4a4": [P, P, P, P, P, P, P, I, I, I, I, P, P],
     "qd_nvfp4_grouped_matmul": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
+    "qd_nvfp4_expert_rows": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
     "qd_seq_add_rms_norm": [P, P, P, P, P, I, I, F, P],
     "qd_seq_bf16_matmul": [P, P, P, I, I, I, P],
     "qd_seq_gdn_conv": [P, P, P, P, I, I, I, P],
@@ -66,7 +69,8 @@ SIGNATURES = {
     "qd_seq_moe_combine": [P, P, P, P, P, I, I, I, P],
 }
 
-LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes", "qd_exchange_bytes"}
+LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes", "qd_exchange_bytes",
+                "qd_nvfp4_matmul_rows_scratch_bytes"}
 
 _lib = None
 

@@ -61,6 +61,7 @@ class BatchDecode(ChunkPrefill):
         c = ckpt.config
         self.final_gamma = (1 + ckpt.final_norm.float()).contiguous()
         self._scratch = None
+        self._graphs = {}
 
     def _attn_splits(self, batch):
         """About two blocks per SM: every extra split costs a merge (32 sequences x 2 KV heads at
@@ -141,3 +142,35 @@ class BatchDecode(ChunkPrefill):
             logits = shards.permute(1, 0, 2).reshape(logits.shape[0], c.vocab_size)
         state.positions += 1
         return logits.float().argmax(dim=-1), logits
+
+    def graph_step(self, tokens: torch.Tensor, state: BatchState):
+        """``step`` replayed from a CUDA graph: a step is some 1 100 launches, which the host
+        issues more slowly than the GPU runs them.  The first call with a state runs eagerly (it
+        also loads and configures every kernel), the second captures, later ones replay; the
+        results live in buffers that the next call overwrites.  ``state.positions`` may only be
+        written by the steps themselves once a state has been captured (call ``forget`` after
+        writing them)."""
+        entry = self._graphs.get(id(state))
+        if entry is None:
+            out = self.step(tokens, state)
+            # host-side bound of the largest position: the device value is read again only when
+            # the bound reaches the end of the cache
+            self._graphs[id(state)] = {"state": state, "bound": int(state.positions.max().item()), "graph": None}
+            return out
+        if entry["bound"] >= state.max_context:
+            entry["bound"] = int(state.positions.max().item())
+            assert entry["bound"] < state.max_context, "a sequence has filled its cache"
+        if entry["graph"] is None:
+            entry["tokens"] = tokens.clone()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                entry["out"] = self.step(entry["tokens"], state, positions_checked=True)
+            entry["graph"] = graph
+        entry["tokens"].copy_(tokens)
+        entry["graph"].replay()
+        entry["bound"] += 1
+        return entry["out"]
+
+    def forget(self, state: BatchState) -> None:
+        """Drop the captured graph of a state (its positions were written from outside)."""
+        self._graphs.pop(id(state), None)

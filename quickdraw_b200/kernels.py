@@ -119,6 +119,30 @@ def matmul(x: torch.Tensor, proj: NVFP4Linear) -> torch.Tensor:
     return out
 
 
+def matmul_rows(x: torch.Tensor, proj: NVFP4Linear, scratch: torch.Tensor | None = None, *, convert: bool = True):
+    """``matmul`` for at most 32 token rows (a decode batch): the weights are decoded once on the
+    warp-level tensor-core instruction with the tokens as columns.  ``scratch`` (uint8,
+    ``rows_scratch_bytes(in_features)``) receives the f16 copy of the rows; ``convert=False``
+    reuses what the previous call left there (several projections of the same input).
+    in_features a multiple of 512, out_features of 16.  Returns (y, scratch)."""
+    assert isinstance(proj, NVFP4Linear) and x.ndim == 2 and proj.weight.ndim == 2 and x.shape[0] <= 32
+    assert x.is_cuda and x.dtype == BF16 and x.is_contiguous() and x.shape[1] == proj.in_features
+    assert proj.weight.is_contiguous() and proj.weight_scale.is_contiguous() and proj.group_size == 16
+    assert proj.weight_scale_2.numel() == 1 and proj.in_features % 512 == 0 and proj.out_features % 16 == 0
+    if scratch is None:
+        assert convert
+        scratch = torch.empty(rows_scratch_bytes(proj.in_features), dtype=torch.uint8, device=x.device)
+    assert scratch.is_cuda and scratch.numel() >= rows_scratch_bytes(proj.in_features)
+    out = torch.empty((x.shape[0], proj.out_features), dtype=BF16, device=x.device)
+    call("qd_nvfp4_matmul_rows", ptr(x), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2), ptr(out),
+         x.shape[0], proj.out_features, proj.in_features, proj.group_size, ptr(scratch), int(convert), stream_of(x))
+    return out, scratch
+
+
+def rows_scratch_bytes(in_features: int) -> int:
+    return int(_lib.lib().qd_nvfp4_matmul_rows_scratch_bytes(in_features))
+
+
 def quantize_act(x: torch.Tensor):
     """bf16 [tokens, in] -> the activation operand of the FP4 x FP4 product: (codes uint8
     [tokens, in/2], E4M3 block scales [tokens, in/16], fp32 tensor scale), the layout of an

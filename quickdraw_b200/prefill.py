@@ -31,16 +31,22 @@ class ChunkPrefill:
     rank combines them in ascending expert id like a single GPU."""
 
     sliced, group, expert_range = False, None, None      # defaults of a whole model on one GPU
+    total_experts = None                                  # experts of the whole model (None: the bank's own count)
+    _rows_scratch = None
+    FEW_TOKENS = 32                                       # token rows up to which a dense product takes the mma.sync form
+    FEW_ROWS = 32                                         # mean routes per expert up to which the mma.sync form is used
 
     def __init__(self, ckpt: Checkpoint, expert_range: tuple[int, int] | None = None, group=None):
         c = ckpt.config
         self.ckpt, self.device = ckpt, ckpt.embed_tokens.device
         self.expert_range = expert_range or (0, c.num_experts)
         self.sliced = self.expert_range != (0, c.num_experts)
+        self.total_experts = c.num_experts
         self.group = group
         self.gammas = [((1 + layer.input_layernorm.float()).contiguous(),
                         (1 + layer.post_attention_layernorm.float()).contiguous()) for layer in ckpt.layers]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._rows_scratch = {}
         for layer in ckpt.layers:
             assert layer.moe.experts_gate.weight.shape[0] == self.expert_range[1] - self.expert_range[0], \
                 "the expert banks must hold exactly the owned range"
@@ -51,6 +57,20 @@ class ChunkPrefill:
 
     def _matmul(self, x, proj: NVFP4Linear):
         out = self._empty(x.shape[0], proj.out_features)
+        if x.shape[0] <= self.FEW_TOKENS and proj.in_features % 512 == 0 and proj.out_features % 16 == 0:
+            # a decode batch: weights decoded once on mma.sync with the tokens as columns; the f16
+            # copy of the token rows is shared by the projections of the same input
+            if self._rows_scratch is None:
+                self._rows_scratch = {}
+            scratch, source = self._rows_scratch.get(proj.in_features, (None, None))
+            if scratch is None:
+                size = lib().qd_nvfp4_matmul_rows_scratch_bytes(proj.in_features)
+                scratch = torch.empty(size, dtype=torch.uint8, device=self.device)
+            call("qd_nvfp4_matmul_rows", ptr(x), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2),
+                 ptr(out), x.shape[0], proj.out_features, proj.in_features, proj.group_size, ptr(scratch),
+                 int(source is not x), stream_of(x))
+            self._rows_scratch[proj.in_features] = (scratch, x)
+            return out
         call("qd_nvfp4_matmul", ptr(x), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2),
              ptr(out), x.shape[0], proj.out_features, proj.in_features, proj.group_size, ptr(self.status),
              stream_of(x))
@@ -76,6 +96,14 @@ class ChunkPrefill:
     def _grouped(self, x, bank: NVFP4Linear, order, boundaries, routes, topk, *, routing=None, by_token, scatter):
         # rows of experts another rank owns stay zero in the scattered (route-order) output
         out = (torch.zeros if self.sliced and scatter else torch.empty)((routes, bank.out_features), dtype=BF16, device=self.device)
+        experts = bank.weight.shape[0]
+        if routes <= self.FEW_ROWS * (self.total_experts or experts) and bank.in_features in (512, 1024, 2048) and bank.out_features % 16 == 0:
+            # few rows per expert: weights decoded once per eight routes on mma.sync, no 128-token tiles
+            call("qd_nvfp4_expert_rows", ptr(x), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
+                 ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, experts, topk, bank.out_features,
+                 bank.in_features, bank.group_size, int(by_token), int(scatter),
+                 int(bank.weight_scale_2.numel() != 1), stream_of(x))
+            return out
         call("qd_nvfp4_grouped_matmul", ptr(x), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
              ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, bank.weight.shape[0], topk,
              bank.out_features, bank.in_features, bank.group_size, int(by_token), int(scatter),

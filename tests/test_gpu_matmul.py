@@ -33,6 +33,33 @@ def test_matmul_matches_oracle(cuda_device, tokens, out_features, in_features):
     assert O.rel_l2(got, exact) < 1e-2
 
 
+ROWS_SHAPES = [(1, 16, 512), (7, 528, 2048), (32, 8192, 2048), (32, 2048, 4096), (19, 96, 1024), (32, 9472, 512)]
+
+
+@pytest.mark.parametrize("tokens,out_features,in_features", ROWS_SHAPES)
+def test_few_rows_matmul_matches_oracle(cuda_device, tokens, out_features, in_features):
+    """The decode-batch form (mma.sync, tokens as columns; 32- and 64-row weight tiles, ragged
+    last tiles) against the restated matmul and the single-token matvec; a second projection
+    reuses the converted rows."""
+    from quickdraw_b200 import kernels
+    src = synthetic.Source(23, "cpu")
+    proj = src.nvfp4(f"w{out_features}x{in_features}", out_features, in_features, global_scale=0.75)
+    other = src.nvfp4(f"v{in_features}", 64, in_features, global_scale=1.5)
+    x = src.normal(f"x{tokens}", tokens, in_features)
+    x[0, :5] = torch.tensor([7.0e4, -3.0e5, 1.0e-6, 0.0, 2.5])       # a row that would leave f16
+    got, scratch = kernels.matmul_rows(x.to(cuda_device), to_device(proj, cuda_device))
+    again, _ = kernels.matmul_rows(x.to(cuda_device), to_device(other, cuda_device), scratch, convert=False)
+    got, again = got.cpu(), again.cpu()
+    want = O.nvfp4_matmul(x, proj)
+    assert got.shape == want.shape and torch.isfinite(got.float()).all()
+    torch.testing.assert_close(got[1:].float(), want[1:].float(), rtol=0.02, atol=0.002)
+    assert O.rel_l2(got, want) < 2e-3
+    assert O.rel_l2(again, O.nvfp4_matmul(x, other)) < 2e-3
+    for t in sorted({0, tokens // 2, tokens - 1}):
+        row = O.nvfp4_gemv(x[t], proj)
+        assert O.rel_l2(got[t], row) < 2e-3
+
+
 def test_two_dimensional_input_takes_the_matmul_path(cuda_device):
     from quickdraw_b200 import kernels
     src = synthetic.Source(22, "cpu")

@@ -40,13 +40,18 @@ def test_chunked_prefill_matches_token_loop(cuda_device, chunk):
     assert O.rel_l2(got.cpu(), want.cpu()) < 5e-2
 
 
-@pytest.mark.parametrize("experts,topk,tokens,width,rows", [
-    (8, 3, 21, 512, 264),          # few tiles: 64-row weight tiles
-    (40, 2, 30, 256, 256),         # 128-row weight tiles
-    (64, 2, 40, 256, 768),         # every SM busy: 256-row (or balanced 128-row) weight tiles
+@pytest.mark.parametrize("experts,topk,tokens,width,rows,few_rows", [
+    (8, 3, 21, 512, 264, 0),       # few tiles: 64-row weight tiles
+    (40, 2, 30, 256, 256, 0),      # 128-row weight tiles
+    (64, 2, 40, 256, 768, 0),      # every SM busy: 256-row (or balanced 128-row) weight tiles
+    (8, 3, 21, 512, 272, 32),      # the few-rows form: up to eight routes per expert, a ragged last weight tile
+    (4, 2, 50, 2048, 512, 32),     # ... 25 routes per expert: four groups of eight, the last one with a single route
+    (40, 8, 3, 512, 2048, 32),     # ... most experts without a route
+    (8, 3, 21, 512, 272, 0),       # the same shape through the tcgen05 form
 ])
-def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tokens, width, rows):
-    """The grouped product of the routed experts against the single-token expert matvec."""
+def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tokens, width, rows, few_rows):
+    """The grouped product of the routed experts (tcgen05 tiles, or the mma.sync form for few
+    routes per expert) against the single-token expert matvec."""
     from quickdraw_b200 import kernels
     from quickdraw_b200.prefill import ChunkPrefill
     from quickdraw_b200.synthetic import to_device
@@ -61,6 +66,7 @@ def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tok
     helper = ChunkPrefill.__new__(ChunkPrefill)
     helper.device = cuda_device
     helper.status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    helper.FEW_ROWS = few_rows
     routes = tokens * topk
     plain = helper._grouped(x, bank, order.to(torch.int32), boundaries, routes, topk, by_token=True, scatter=False)
     routed = helper._grouped(x.repeat_interleave(topk, 0)[order].contiguous(), bank, order.to(torch.int32), boundaries,
