@@ -63,11 +63,13 @@ class BatchDecode(ChunkPrefill):
         self._scratch = None
         self._graphs = {}
 
-    def _attn_splits(self, batch):
-        """About two blocks per SM: every extra split costs a merge (32 sequences x 2 KV heads at
-        context 8192: 4 splits 4.4 ms, 16 splits 5.7 ms of the step)."""
+    def _attn_splits(self, batch, context):
+        """Context splits per (sequence, KV head): the count whose blocks fill whole waves of the
+        GPU best (one block per SM; a split costs a merge, 16 at most)."""
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        return max(1, min(MAX_ATTN_SPLITS, 2 * sms // (batch * self.ckpt.config.num_key_value_heads)))
+        pairs = batch * self.ckpt.config.num_key_value_heads
+        cost = lambda s: -(-pairs * s // sms) * (-(-context // s) + 64)
+        return min(range(1, MAX_ATTN_SPLITS + 1), key=cost)
 
     def _attn_scratch(self, batch):
         c = self.ckpt.config
@@ -109,7 +111,8 @@ class BatchDecode(ChunkPrefill):
         call("qd_batch_attention", ptr(qg), ptr(k), ptr(v), ptr(w.q_norm), ptr(w.k_norm), ptr(k_cache[0]),
              ptr(v_cache[0]), k_cache.stride(0), ptr(q_scratch), ptr(out), ptr(scratch), ptr(counters),
              ptr(state.positions), batch, state.max_context, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
-             int(c.head_dim * c.partial_rotary_factor), c.rope_theta, c.rms_norm_eps, self._attn_splits(batch), stream_of(x))
+             int(c.head_dim * c.partial_rotary_factor), c.rope_theta, c.rms_norm_eps,
+             self._attn_splits(batch, state.max_context), stream_of(x))
         return self._matmul(out, w.o_proj)
 
     # ------------------------------------------------------------------------------ step

@@ -32,24 +32,25 @@ struct AttnAcc {
     float out[16][4];
 };
 
-// Sixteen positions of the context against the (up to) eight query heads of a KV head.
-// krows / vrows: the chunk's key and value rows in shared memory (kAttnRow bytes apart);
-// first: context position of row 0; t1: end of the block's split.
-QD_DEVINL void attn_chunk(AttnAcc& acc, const uint8_t* __restrict__ q_s, const uint8_t* __restrict__ krows,
-                          const uint8_t* __restrict__ vrows, int first, int t1, int lane) {
-    const int g = lane >> 2, t = lane & 3;
-    const int prow = (g & 1) ? 4 + (g >> 1) : (g >> 1);      // key row behind column g of a score tile
-    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int m = 0; m < 8; ++m) {
-        const uint4 q4 = lds128(q_s + g * kAttnQRow + m * 64 + t * 16);
-        const uint4 k0 = lds128(krows + prow * kAttnRow + m * 64 + t * 16);
-        const uint4 k1 = lds128(krows + (8 + prow) * kAttnRow + m * 64 + t * 16);
-        mma_bf16(s0, q4.x, 0u, q4.y, 0u, k0.x, k0.y);
-        mma_bf16(s0, q4.z, 0u, q4.w, 0u, k0.z, k0.w);
-        mma_bf16(s1, q4.x, 0u, q4.y, 0u, k1.x, k1.y);
-        mma_bf16(s1, q4.z, 0u, q4.w, 0u, k1.z, k1.w);
-    }
+// Key row behind column g of a score tile (rows prow and 8 + prow of the chunk are lane (g, t)'s).
+QD_DEVINL int attn_key_row(int g) { return (g & 1) ? 4 + (g >> 1) : (g >> 1); }
+
+// Scores: 64 bytes of the query heads against the same bytes of the lane's two key rows.
+QD_DEVINL void attn_score_step(float (&s0)[4], float (&s1)[4], const uint4& q4, const uint4& k0, const uint4& k1) {
+    mma_bf16(s0, q4.x, 0u, q4.y, 0u, k0.x, k0.y);
+    mma_bf16(s0, q4.z, 0u, q4.w, 0u, k0.z, k0.w);
+    mma_bf16(s1, q4.x, 0u, q4.y, 0u, k1.x, k1.y);
+    mma_bf16(s1, q4.z, 0u, q4.w, 0u, k1.z, k1.w);
+}
+
+// Probabilities of a chunk as the B operand of the value product, split into two bf16 pieces
+// (sixteen bits of mantissa).
+struct AttnProbs { uint32_t hi0, hi1, lo0, lo1; };
+
+// Running softmax over the chunk's scores; rescales the accumulator.  first: context position of
+// row 0 of the chunk; t1: end of the range (rows at or past it are masked).
+QD_DEVINL AttnProbs attn_softmax(AttnAcc& acc, const float (&s0)[4], const float (&s1)[4], int first, int t1, int lane) {
+    const int t = lane & 3;
     // the lane's four scores of head g: rows t, 4 + t, 8 + t, 12 + t of the chunk
     float sc[4] = {s0[0], s0[1], s1[0], s1[1]};
     float mx = -INFINITY;
@@ -67,15 +68,48 @@ QD_DEVINL void attn_chunk(AttnAcc& acc, const uint8_t* __restrict__ q_s, const u
     for (int i = 0; i < 4; ++i) { p[i] = sc[i] == -INFINITY ? 0.f : expf(sc[i] - m_new); psum += p[i]; }
     acc.l = acc.l * alpha + psum;
     acc.m = m_new;
-    // probabilities as the B operand, split into two bf16 pieces (sixteen bits of mantissa)
-    const uint32_t hi0 = pack_bf16x2(p[0], p[1]), hi1 = pack_bf16x2(p[2], p[3]);
-    const uint32_t lo0 = pack_bf16x2(p[0] - __uint_as_float(hi0 << 16), p[1] - __uint_as_float(hi0 & 0xffff0000u));
-    const uint32_t lo1 = pack_bf16x2(p[2] - __uint_as_float(hi1 << 16), p[3] - __uint_as_float(hi1 & 0xffff0000u));
+    AttnProbs pr;
+    pr.hi0 = pack_bf16x2(p[0], p[1]); pr.hi1 = pack_bf16x2(p[2], p[3]);
+    pr.lo0 = pack_bf16x2(p[0] - __uint_as_float(pr.hi0 << 16), p[1] - __uint_as_float(pr.hi0 & 0xffff0000u));
+    pr.lo1 = pack_bf16x2(p[2] - __uint_as_float(pr.hi1 << 16), p[3] - __uint_as_float(pr.hi1 & 0xffff0000u));
     const float a_even = __shfl_sync(0xffffffffu, alpha, 8 * t), a_odd = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         acc.out[i][0] *= a_even; acc.out[i][1] *= a_odd; acc.out[i][2] *= a_even; acc.out[i][3] *= a_odd;
     }
+    return pr;
+}
+
+// Values: bytes 64 g + 16 q .. + 15 of the value rows t, 4 + t, 8 + t, 12 + t of the chunk.
+QD_DEVINL void attn_value_step(AttnAcc& acc, int q, const uint4& r0, const uint4& r1, const uint4& r2, const uint4& r3,
+                               const AttnProbs& pr) {
+    const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w}, w1[4] = {r1.x, r1.y, r1.z, r1.w};
+    const uint32_t w2[4] = {r2.x, r2.y, r2.z, r2.w}, w3[4] = {r3.x, r3.y, r3.z, r3.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const uint32_t a0 = __byte_perm(w0[e], w1[e], 0x5410), a1 = __byte_perm(w0[e], w1[e], 0x7632);
+        const uint32_t a2 = __byte_perm(w2[e], w3[e], 0x5410), a3 = __byte_perm(w2[e], w3[e], 0x7632);
+        mma_bf16(acc.out[q * 4 + e], a0, a1, a2, a3, pr.hi0, pr.hi1);
+        mma_bf16(acc.out[q * 4 + e], a0, a1, a2, a3, pr.lo0, pr.lo1);
+    }
+}
+
+// Sixteen positions of the context against the (up to) eight query heads of a KV head.
+// krows / vrows: the chunk's key and value rows in shared memory (kAttnRow bytes apart);
+// first: context position of row 0; t1: end of the block's split.
+QD_DEVINL void attn_chunk(AttnAcc& acc, const uint8_t* __restrict__ q_s, const uint8_t* __restrict__ krows,
+                          const uint8_t* __restrict__ vrows, int first, int t1, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int prow = attn_key_row(g);
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+        const uint4 q4 = lds128(q_s + g * kAttnQRow + m * 64 + t * 16);
+        const uint4 k0 = lds128(krows + prow * kAttnRow + m * 64 + t * 16);
+        const uint4 k1 = lds128(krows + (8 + prow) * kAttnRow + m * 64 + t * 16);
+        attn_score_step(s0, s1, q4, k0, k1);
+    }
+    const AttnProbs pr = attn_softmax(acc, s0, s1, first, t1, lane);
     const uint8_t* vb = vrows + g * 64;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -83,15 +117,7 @@ QD_DEVINL void attn_chunk(AttnAcc& acc, const uint8_t* __restrict__ q_s, const u
         const uint4 r1 = lds128(vb + (4 + t) * kAttnRow + q * 16);
         const uint4 r2 = lds128(vb + (8 + t) * kAttnRow + q * 16);
         const uint4 r3 = lds128(vb + (12 + t) * kAttnRow + q * 16);
-        const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w}, w1[4] = {r1.x, r1.y, r1.z, r1.w};
-        const uint32_t w2[4] = {r2.x, r2.y, r2.z, r2.w}, w3[4] = {r3.x, r3.y, r3.z, r3.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const uint32_t a0 = __byte_perm(w0[e], w1[e], 0x5410), a1 = __byte_perm(w0[e], w1[e], 0x7632);
-            const uint32_t a2 = __byte_perm(w2[e], w3[e], 0x5410), a3 = __byte_perm(w2[e], w3[e], 0x7632);
-            mma_bf16(acc.out[q * 4 + e], a0, a1, a2, a3, hi0, hi1);
-            mma_bf16(acc.out[q * 4 + e], a0, a1, a2, a3, lo0, lo1);
-        }
+        attn_value_step(acc, q, r0, r1, r2, r3, pr);
     }
 }
 

@@ -15,6 +15,7 @@ using qd::AttnAcc;
 using qd::attn_chunk;
 using qd::kAttnQRow;
 using qd::kAttnRow;
+using qd::mma_bf16;
 
 // ------------------------------------------------------------------ residual add + RMSNorm
 __global__ void seq_add_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual,
@@ -68,75 +69,70 @@ __global__ void seq_bf16_matmul_kernel(const bf16* __restrict__ x, const bf16* _
     if (lane == 0) y[(size_t)t * rows + n] = __float2bfloat16_rn(acc);
 }
 
-// The same for a tall matrix (the LM head over a batch of tokens): the activations of up to
-// 32 tokens sit in shared memory as bf16, a warp takes two weight rows at a time, reads them
-// once and multiplies them with every token of the tile (lane = eight inputs of every 256);
-// the 32 per-token partial sums of a lane are reduced across the warp by a transposing
-// butterfly (31 shuffles), after which lane t holds token t's sum.
-constexpr int kTallTokens = 32, kTallMaxChunks = 8, kTallRows = 2;
-__global__ void __launch_bounds__(256)
+// The same for a tall matrix (the LM head over a batch of tokens) on the warp-level tensor-core
+// instruction: the activations of up to 32 tokens sit in shared memory as bf16 (rows padded by
+// 16 bytes against bank conflicts); a warp takes sixteen weight rows at a time and reads them
+// once, straight from global memory into A fragments: lane (g, t) loads the 32 bytes of rows g
+// and g + 8 at inputs 64 s + 16 t .. + 15 of step s (a quarter-warp reads two whole 128-byte
+// lines), and the 16 inputs of token 8 nt + g at the same offsets are its B fragments, so every
+// element of the 16 x 32 result is used.  fp32 accumulators, one bf16 rounding.
+constexpr int kTallTokens = 32, kTallMaxWidth = 3072, kTallUnroll = 4, kTallWarps = 16;
+__global__ void __launch_bounds__(kTallWarps * 32, 1)
 seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
                             int tokens, int rows, int width) {
     extern __shared__ __align__(16) unsigned char tall_smem[];
-    bf16* xs = reinterpret_cast<bf16*>(tall_smem);                 // [32][width]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int t0 = blockIdx.y * kTallTokens, nt = min(kTallTokens, tokens - t0);
-    const int pieces = width / 8, chunks = width / 256;
-    for (int i = tid; i < kTallTokens * pieces; i += 256) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int t0 = blockIdx.y * kTallTokens, nt_rows = min(kTallTokens, tokens - t0);
+    const int pieces = width / 8, x_row = 2 * width + 16;
+    for (int i = tid; i < kTallTokens * pieces; i += kTallWarps * 32) {
         const int row = i / pieces, col = i % pieces;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (row < nt) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + row) * width) + col);
-        reinterpret_cast<uint4*>(xs)[i] = v;
+        if (row < nt_rows) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + row) * width) + col);
+        *reinterpret_cast<uint4*>(tall_smem + (size_t)row * x_row + col * 16) = v;
     }
     __syncthreads();
-    for (int n0 = (blockIdx.x * 8 + warp) * kTallRows; n0 < rows; n0 += gridDim.x * 8 * kTallRows) {
-        uint4 wv[kTallRows][kTallMaxChunks];
+    const unsigned char* xs = tall_smem + (size_t)g * x_row + t * 32;
+    const int steps = width / 64;
+    for (int n0 = (blockIdx.x * kTallWarps + warp) * 16; n0 < rows; n0 += gridDim.x * kTallWarps * 16) {
+        // rows past the matrix read its last row and store nothing
+        const uint4* lo = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + g, rows - 1) * width + t * 16);
+        const uint4* hi = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + g + 8, rows - 1) * width + t * 16);
+        float acc[4][4];
 #pragma unroll
-        for (int r = 0; r < kTallRows; ++r)
+        for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-            for (int c = 0; c < kTallMaxChunks; ++c)
-                wv[r][c] = (c < chunks && n0 + r < rows)
-                               ? __ldg(reinterpret_cast<const uint4*>(w + (size_t)(n0 + r) * width + c * 256 + lane * 8))
-                               : make_uint4(0u, 0u, 0u, 0u);
-        float part[kTallRows][kTallTokens];
+            for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
+#pragma unroll 1
+        for (int s0 = 0; s0 < steps; s0 += kTallUnroll) {
+            uint4 a[kTallUnroll][4];
 #pragma unroll
-        for (int t = 0; t < kTallTokens; ++t) {
-            float acc[kTallRows];
-#pragma unroll
-            for (int r = 0; r < kTallRows; ++r) acc[r] = 0.f;
-#pragma unroll
-            for (int c = 0; c < kTallMaxChunks; ++c) {
-                if (c < chunks) {
-                    const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)t * width + c * 256 + lane * 8);
-                    const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                    for (int r = 0; r < kTallRows; ++r) {
-                        const uint32_t ww[4] = {wv[r][c].x, wv[r][c].y, wv[r][c].z, wv[r][c].w};
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            acc[r] = fma_bf16_lo(ww[q], xx[q], acc[r]);
-                            acc[r] = fma_bf16_hi(ww[q], xx[q], acc[r]);
-                        }
-                    }
-                }
+            for (int u = 0; u < kTallUnroll; ++u) {
+                const int s = min(s0 + u, steps - 1);
+                a[u][0] = __ldg(lo + s * 8); a[u][1] = __ldg(lo + s * 8 + 1);
+                a[u][2] = __ldg(hi + s * 8); a[u][3] = __ldg(hi + s * 8 + 1);
             }
 #pragma unroll
-            for (int r = 0; r < kTallRows; ++r) part[r][t] = acc[r];
-        }
+            for (int u = 0; u < kTallUnroll; ++u) {
+                if (s0 + u >= steps) break;
 #pragma unroll
-        for (int r = 0; r < kTallRows; ++r) {
-#pragma unroll
-            for (int span = 16; span >= 1; span >>= 1) {
-                const bool upper = (lane & span) != 0;
-#pragma unroll
-                for (int i = 0; i < span; ++i) {
-                    const float send = upper ? part[r][i] : part[r][i + span];
-                    const float keep = upper ? part[r][i + span] : part[r][i];
-                    part[r][i] = keep + __shfl_xor_sync(0xffffffffu, send, span);
+                for (int nt = 0; nt < 4; ++nt) {
+                    const unsigned char* src = xs + (size_t)nt * 8 * x_row + (s0 + u) * 128;
+                    const uint4 b0 = lds128(src), b1 = lds128(src + 16);
+                    mma_bf16(acc[nt], a[u][0].x, a[u][2].x, a[u][0].y, a[u][2].y, b0.x, b0.y);
+                    mma_bf16(acc[nt], a[u][0].z, a[u][2].z, a[u][0].w, a[u][2].w, b0.z, b0.w);
+                    mma_bf16(acc[nt], a[u][1].x, a[u][3].x, a[u][1].y, a[u][3].y, b1.x, b1.y);
+                    mma_bf16(acc[nt], a[u][1].z, a[u][3].z, a[u][1].w, a[u][3].w, b1.z, b1.w);
                 }
             }
-            if (lane < nt && n0 + r < rows) y[(size_t)(t0 + lane) * rows + n0 + r] = __float2bfloat16_rn(part[r][0]);
         }
+        // acc[nt][0..1] = row n0 + g, tokens 8 nt + 2 t and + 1; [2..3] = row n0 + g + 8
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int token = 8 * nt + 2 * t + (c & 1), row = n0 + g + 8 * (c >> 1);
+                if (token < nt_rows && row < rows) y[(size_t)(t0 + token) * rows + row] = __float2bfloat16_rn(acc[nt][c]);
+            }
     }
 }
 
@@ -554,6 +550,57 @@ struct LaneAttnParams {
     int hq, hk, d, splits, capacity;
 };
 
+// The warps' running states (red: [warps][G][d + 2] = weighted values, maximum, sum) become the
+// block's partial result; the last block of a (sequence, KV head) merges the splits, normalises
+// and gates.  Every thread of the block calls it.
+__device__ void lane_attn_finish(const LaneAttnParams& p, const float* __restrict__ red, size_t z, int kvh, int split,
+                                 int active, int tid) {
+    __shared__ int s_last;
+    const int G = p.hq / p.hk, D = p.d, stride = D + 2;
+    float* partial = p.partial + z * (size_t)p.hk * p.splits * G * stride;
+    float* block_out = partial + (((size_t)kvh * p.splits + split) * G) * stride;
+    for (int idx = tid; idx < G * D; idx += kLaneAttnWarps * 32) {
+        const int h = idx / D, f = idx % D;
+        float mm = -INFINITY;
+        for (int w = 0; w < kLaneAttnWarps; ++w) mm = fmaxf(mm, red[((size_t)w * G + h) * stride + D]);
+        float num = 0.f, den = 0.f;
+        for (int w = 0; w < kLaneAttnWarps; ++w) {
+            const float* src = red + ((size_t)w * G + h) * stride;
+            const float wgt = src[D] == -INFINITY ? 0.f : expf(src[D] - mm);
+            num += wgt * src[f];
+            den += wgt * src[D + 1];
+        }
+        block_out[(size_t)h * stride + f] = num;
+        if (f == 0) { block_out[(size_t)h * stride + D] = mm; block_out[(size_t)h * stride + D + 1] = den; }
+    }
+    __threadfence();
+    __syncthreads();
+    unsigned int* counter = p.counters + z * p.hk + kvh;
+    if (tid == 0) s_last = atomicAdd(counter, 1u) == (unsigned int)p.splits - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // ---- last block of this (sequence, KV head): merge the splits, normalise, gate
+    for (int idx = tid; idx < G * D; idx += kLaneAttnWarps * 32) {
+        const int h = idx / D, f = idx % D;
+        float mm = -INFINITY;
+        for (int s = 0; s < active; ++s) mm = fmaxf(mm, __ldcg(partial + (((size_t)kvh * p.splits + s) * G + h) * stride + D));
+        float num = 0.f, den = 0.f;
+        for (int s = 0; s < active; ++s) {
+            const float* src = partial + (((size_t)kvh * p.splits + s) * G + h) * stride;
+            const float sm_ = __ldcg(src + D);
+            const float wgt = sm_ == -INFINITY ? 0.f : expf(sm_ - mm);
+            num += wgt * __ldcg(src + f);
+            den += wgt * __ldcg(src + D + 1);
+        }
+        const float attended = round_bf16(num / den);
+        const int qh = kvh * G + h;
+        const float gate = round_bf16(sigmoid_precise(ld_bf16(p.qg + (z * p.hq + qh) * 2 * (size_t)D + D + f)));
+        p.out[(z * p.hq + qh) * (size_t)D + f] = __float2bfloat16_rn(attended * gate);
+    }
+    if (tid == 0) *counter = 0;
+}
+
 __global__ void __launch_bounds__(kLaneAttnWarps * 32)
 batch_attn_lanes_kernel(const LaneAttnParams p) {
     extern __shared__ __align__(16) unsigned char lane_attn_smem[];
@@ -561,7 +608,6 @@ batch_attn_lanes_kernel(const LaneAttnParams p) {
     bf16* qs = reinterpret_cast<bf16*>(lane_attn_smem);                                  // [G][D]
     float* pbuf = reinterpret_cast<float*>(lane_attn_smem + (size_t)G * D * sizeof(bf16)); // [warps][32][8]
     float* red = pbuf + kLaneAttnWarps * 32 * kLaneAttnGroup;                            // [warps][G][D + 2]
-    __shared__ int s_last;
     const int kvh = blockIdx.x, split = blockIdx.y;
     const size_t z = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -675,48 +721,110 @@ batch_attn_lanes_kernel(const LaneAttnParams p) {
         }
     }
     __syncthreads();
-    float* partial = p.partial + z * (size_t)p.hk * p.splits * G * stride;
-    float* block_out = partial + (((size_t)kvh * p.splits + split) * G) * stride;
-    for (int idx = tid; idx < G * D; idx += kLaneAttnWarps * 32) {
-        const int h = idx / D, f = idx % D;
-        float mm = -INFINITY;
-        for (int w = 0; w < kLaneAttnWarps; ++w) mm = fmaxf(mm, red[((size_t)w * G + h) * stride + D]);
-        float num = 0.f, den = 0.f;
-        for (int w = 0; w < kLaneAttnWarps; ++w) {
-            const float* src = red + ((size_t)w * G + h) * stride;
-            const float wgt = src[D] == -INFINITY ? 0.f : expf(src[D] - mm);
-            num += wgt * src[f];
-            den += wgt * src[D + 1];
+    lane_attn_finish(p, red, z, kvh, split, active, tid);
+}
+
+// ------------------------------------------------ batched decode attention on the tensor cores
+// The same block layout (KV head, context split, sequence; 8 warps) for head dimension 256: a
+// warp walks its share of the split sixteen positions at a time with the fragment arithmetic of
+// attn_mma.cuh (scores S^T = K Q^T, running softmax, O^T += V^T P^T).  Every key and value
+// element is needed by exactly one lane of the warp, so the rows go from the cache straight
+// into the MMA fragments (no staging in shared memory): per chunk a lane loads 16 x 16 bytes of
+// its two key rows, and, once the scores are out, 16 x 16 bytes of four value rows while the
+// next chunk's keys are already on their way.  The lane-per-position kernel above spends its
+// time in scalar FMAs (28 % of the HBM bandwidth at 32 sequences x 8192 positions).
+struct AttnKeys { uint4 a[8], b[8]; };      // bytes 64 m + 16 t .. + 15 of key rows prow and 8 + prow
+
+QD_DEVINL uint4 ld_stream16(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+// rows past `last` (masked positions of the final chunk) read row `last`, which is initialised
+QD_DEVINL void attn_load_keys(AttnKeys& k, const uint8_t* __restrict__ base, size_t row_bytes, int first, int last, int lane) {
+    const int g = lane >> 2, t = lane & 3, prow = qd::attn_key_row(g);
+    const uint8_t* r0 = base + (size_t)min(first + prow, last) * row_bytes + t * 16;
+    const uint8_t* r1 = base + (size_t)min(first + 8 + prow, last) * row_bytes + t * 16;
+#pragma unroll
+    for (int m = 0; m < 8; ++m) { k.a[m] = ld_stream16(r0 + m * 64); k.b[m] = ld_stream16(r1 + m * 64); }
+}
+
+__global__ void __launch_bounds__(kLaneAttnWarps * 32, 1)
+batch_attn_mma_kernel(const LaneAttnParams p) {
+    extern __shared__ __align__(16) unsigned char mma_attn_smem[];
+    constexpr int D = 256;
+    const int G = p.hq / p.hk, stride = D + 2;
+    uint8_t* q_s = mma_attn_smem;                                                       // [8][kAttnQRow]
+    float* red = reinterpret_cast<float*>(mma_attn_smem + 8 * kAttnQRow);               // [warps][G][D + 2]
+    const int kvh = blockIdx.x, split = blockIdx.y;
+    const size_t z = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int T = p.positions[z] + 1;
+    if (T < 1 || T > p.capacity) return;      // a position outside the cache: the sequence's output is left alone
+    int active = (T + kLaneAttnSplitMin - 1) / kLaneAttnSplitMin;
+    if (active > p.splits) active = p.splits;
+    const int per = ((T + active - 1) / active + 31) & ~31;
+    const int t0 = split * per, t1 = min(T, t0 + per);
+    const bool mine = split < active && t0 < t1;
+    const size_t row_bytes = (size_t)p.hk * D * sizeof(bf16);
+    const uint8_t* kc = reinterpret_cast<const uint8_t*>(p.k_cache + z * p.cache_stride + (size_t)kvh * D);
+    const uint8_t* vc = reinterpret_cast<const uint8_t*>(p.v_cache + z * p.cache_stride + (size_t)kvh * D);
+
+    AttnAcc acc;
+    acc.m = -INFINITY; acc.l = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { acc.out[i][0] = 0.f; acc.out[i][1] = 0.f; acc.out[i][2] = 0.f; acc.out[i][3] = 0.f; }
+    if (mine) {
+        AttnKeys keys;
+        int c = t0 + warp * 16;
+        if (c < t1) attn_load_keys(keys, kc, row_bytes, c, T - 1, lane);
+        // query heads of this KV head (heads beyond the group: zeros)
+        for (int i = tid; i < 8 * 32; i += kLaneAttnWarps * 32) {
+            const int h = i >> 5, piece = i & 31;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (h < G) v = __ldg(reinterpret_cast<const uint4*>(p.q + (z * p.hq + (size_t)kvh * G + h) * D) + piece);
+            reinterpret_cast<uint4*>(q_s + h * kAttnQRow)[piece] = v;
         }
-        block_out[(size_t)h * stride + f] = num;
-        if (f == 0) { block_out[(size_t)h * stride + D] = mm; block_out[(size_t)h * stride + D + 1] = den; }
-    }
-    __threadfence();
-    __syncthreads();
-    unsigned int* counter = p.counters + z * p.hk + kvh;
-    if (tid == 0) s_last = atomicAdd(counter, 1u) == (unsigned int)p.splits - 1;
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    // ---- last block of this (sequence, KV head): merge the splits, normalise, gate
-    for (int idx = tid; idx < G * D; idx += kLaneAttnWarps * 32) {
-        const int h = idx / D, f = idx % D;
-        float mm = -INFINITY;
-        for (int s = 0; s < active; ++s) mm = fmaxf(mm, __ldcg(partial + (((size_t)kvh * p.splits + s) * G + h) * stride + D));
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < active; ++s) {
-            const float* src = partial + (((size_t)kvh * p.splits + s) * G + h) * stride;
-            const float sm_ = __ldcg(src + D);
-            const float wgt = sm_ == -INFINITY ? 0.f : expf(sm_ - mm);
-            num += wgt * __ldcg(src + f);
-            den += wgt * __ldcg(src + D + 1);
+        __syncthreads();
+#pragma unroll 1
+        for (; c < t1; c += kLaneAttnWarps * 16) {
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int m = 0; m < 8; ++m)
+                qd::attn_score_step(s0, s1, lds128(q_s + g * kAttnQRow + m * 64 + t * 16), keys.a[m], keys.b[m]);
+            uint4 values[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint8_t* row = vc + (size_t)min(c + 4 * i + t, T - 1) * row_bytes + g * 64;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) values[q][i] = ld_stream16(row + q * 16);
+            }
+            if (c + kLaneAttnWarps * 16 < t1) attn_load_keys(keys, kc, row_bytes, c + kLaneAttnWarps * 16, T - 1, lane);
+            const qd::AttnProbs pr = qd::attn_softmax(acc, s0, s1, c, t1, lane);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) qd::attn_value_step(acc, q, values[q][0], values[q][1], values[q][2], values[q][3], pr);
         }
-        const float attended = round_bf16(num / den);
-        const int qh = kvh * G + h;
-        const float gate = round_bf16(sigmoid_precise(ld_bf16(p.qg + (z * p.hq + qh) * 2 * (size_t)D + D + f)));
-        p.out[(z * p.hq + qh) * (size_t)D + f] = __float2bfloat16_rn(attended * gate);
+    } else {
+        __syncthreads();
     }
-    if (tid == 0) *counter = 0;
+    // ---- the warp's state in the layout of the merge: lane (g, t) holds the statistics of head g
+    // (the sum still spread over its four lanes) and out[i][c] = feature 32 g + 2 i + (c >> 1) of head 2 t + (c & 1)
+    acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 1);
+    acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 2);
+    if (t == 0 && g < G) {
+        float* dst = red + ((size_t)warp * G + g) * stride;
+        dst[D] = acc.m; dst[D + 1] = acc.l;
+    }
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+        const int h = 2 * t + cc;
+        if (h >= G) continue;
+        float* dst = red + ((size_t)warp * G + h) * stride + 32 * g;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { dst[2 * i] = acc.out[i][cc]; dst[2 * i + 1] = acc.out[i][2 + cc]; }
+    }
+    __syncthreads();
+    lane_attn_finish(p, red, z, kvh, split, active, tid);
 }
 
 // ------------------------------------------------ causal attention of a prompt chunk on the tensor cores
@@ -920,20 +1028,20 @@ extern "C" int qd_seq_add_rms_norm(const void* x, const void* residual, const fl
 extern "C" int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tokens, int rows, int width, void* stream) {
     QD_CHECK_ARG(x && w && y && tokens > 0 && rows > 0 && width > 0);
     const uintptr_t align = (uintptr_t)x | (uintptr_t)w;
-    if (rows >= 4096 && width % 256 == 0 && width <= 256 * kTallMaxChunks && !(align & 15u) && (tokens + 31) / 32 <= 65535) {
+    if (rows >= 4096 && width % 64 == 0 && width <= kTallMaxWidth && !(align & 15u) && (tokens + 31) / 32 <= 65535) {
         // tall matrix: read every weight row once per tile of 32 tokens
-        const size_t smem = (size_t)kTallTokens * width * sizeof(bf16);
+        const size_t smem = (size_t)kTallTokens * (width * sizeof(bf16) + 16);
         int dev = 0, sms = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
         static bool configured[64];
         if (!configured[dev]) {
-            if (cudaFuncSetAttribute(seq_bf16_matmul_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
+            if (cudaFuncSetAttribute(seq_bf16_matmul_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTallTokens * (kTallMaxWidth * 2 + 16)) != cudaSuccess)
                 return QD_ERR_LAUNCH;
             configured[dev] = true;
         }
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        seq_bf16_matmul_tall_kernel<<<dim3(sms, (tokens + 31) / 32), 256, smem, (cudaStream_t)stream>>>(
+        seq_bf16_matmul_tall_kernel<<<dim3(sms, (tokens + 31) / 32), kTallWarps * 32, smem, (cudaStream_t)stream>>>(
             (const bf16*)x, (const bf16*)w, (bf16*)y, tokens, rows, width);
         return qd_launch_status();
     }
@@ -1070,6 +1178,17 @@ extern "C" int qd_batch_attention(const void* qg, const void* k_new, const void*
         configured[dev] = true;
     }
     if (smem > 100 * 1024) return QD_ERR_UNSUPPORTED;
+    if (head_dim == 256) {          // tensor-core form
+        const size_t mma_smem = 8 * kAttnQRow + sizeof(float) * (size_t)kLaneAttnWarps * G * (head_dim + 2);
+        static bool mma_configured[64];
+        if (!mma_configured[dev]) {
+            if (cudaFuncSetAttribute(batch_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
+                return QD_ERR_LAUNCH;
+            mma_configured[dev] = true;
+        }
+        batch_attn_mma_kernel<<<dim3(kv_heads, splits, batch), kLaneAttnWarps * 32, mma_smem, (cudaStream_t)stream>>>(p);
+        return qd_launch_status();
+    }
     batch_attn_lanes_kernel<<<dim3(kv_heads, splits, batch), kLaneAttnWarps * 32, smem, (cudaStream_t)stream>>>(p);
     return qd_launch_status();
 }

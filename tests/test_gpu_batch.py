@@ -88,7 +88,7 @@ def test_batched_state_kernels_equal_single_sequence_kernels(cuda_device):
 def test_tall_projection_equals_row_by_row(cuda_device):
     from quickdraw_b200._lib import call, ptr, stream_of
     src = synthetic.Source(29, cuda_device)
-    for tokens, rows, width in ((5, 4100, 2048), (33, 4096, 512)):
+    for tokens, rows, width in ((5, 4100, 2048), (33, 4096, 512), (32, 4112, 320)):
         x, w = src.normal(f"x{tokens}", tokens, width), src.normal(f"w{rows}", rows, width, std=0.05)
         y = torch.empty(tokens, rows, dtype=torch.bfloat16, device=cuda_device)
         call("qd_seq_bf16_matmul", ptr(x), ptr(w), ptr(y), tokens, rows, width, stream_of(x))
@@ -166,3 +166,45 @@ def test_graph_replay_equals_eager_steps(cuda_device):
     assert eager.positions.tolist() == replayed.positions.tolist() == [5, 8, 12, 6]
     for name in ("kv_k", "kv_v", "rec_state", "conv_state"):
         assert torch.equal(getattr(eager, name), getattr(replayed, name)), name
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(16, 2, 256), (8, 2, 128)])
+def test_batch_attention_forms_against_the_single_sequence_kernel(cuda_device, hq, hkv, d):
+    """``qd_batch_attention`` (head dimension 256: tensor-core form with a full group of eight
+    heads; 128: lane-per-position form) against the single-sequence decode attention, for
+    sequences whose contexts end inside the first chunk, on a chunk boundary and deep in the cache."""
+    from quickdraw_b200._lib import call, lib, ptr, stream_of
+    dev, cap = cuda_device, 1024
+    src = synthetic.Source(41, "cpu")
+    positions = torch.tensor([0, 15, 16, 700, 1023], dtype=torch.int32, device=dev)
+    batch = positions.numel()
+    qg = src.normal("qg", batch, hq, 2 * d).to(dev)
+    k_new, v_new = src.normal("k", batch, hkv, d).to(dev), src.normal("v", batch, hkv, d).to(dev)
+    q_norm, k_norm = src.normal("qn", d, std=0.1).to(dev), src.normal("kn", d, std=0.1).to(dev)
+    k0, v0 = src.normal("kc", batch, cap, hkv, d).to(dev), src.normal("vc", batch, cap, hkv, d).to(dev)
+    floats = lib().qd_attn_scratch_floats(hq, hkv, d, 16)
+    scratch = torch.empty(batch * floats, dtype=torch.float32, device=dev)
+    counters = torch.zeros(batch * hkv, dtype=torch.int32, device=dev)
+    s = stream_of(qg)
+    ks, vs, want = k0.clone(), v0.clone(), []
+    for i in range(batch):
+        out = torch.empty(hq * d, dtype=torch.bfloat16, device=dev)
+        call("qd_attn_decode", ptr(qg[i]), ptr(k_new[i]), ptr(v_new[i]), ptr(q_norm), ptr(k_norm), ptr(ks[i]), ptr(vs[i]),
+             ptr(out), ptr(scratch), ptr(counters), None, int(positions[i]), cap, hq, hkv, d, 64, 1e6, 1e-6, 4, 0, s)
+        want.append(out)
+    for splits in (1, 5, 16):
+        kb, vb = k0.clone(), v0.clone()
+        # rows past every sequence's position are never read: poison them
+        for i in range(batch):
+            kb[i, int(positions[i]) + 1:] = float("nan")
+            vb[i, int(positions[i]) + 1:] = float("nan")
+        out_b, q_scratch = torch.empty(batch, hq * d, dtype=torch.bfloat16, device=dev), torch.empty(batch, hq * d, dtype=torch.bfloat16, device=dev)
+        call("qd_batch_attention", ptr(qg), ptr(k_new), ptr(v_new), ptr(q_norm), ptr(k_norm), ptr(kb[0]), ptr(vb[0]),
+             kb.stride(0), ptr(q_scratch), ptr(out_b), ptr(scratch), ptr(counters), ptr(positions), batch, cap, hq, hkv, d,
+             64, 1e6, 1e-6, splits, s)
+        torch.cuda.synchronize()
+        assert int(counters.abs().sum()) == 0
+        for i in range(batch):
+            assert O.rel_l2(out_b[i].float().cpu(), want[i].float().cpu()) < 1e-2, (splits, i)
+            n = int(positions[i]) + 1
+            assert O.rel_l2(kb[i, :n].float().cpu(), ks[i, :n].float().cpu()) < 1e-3 and torch.equal(vb[i, :n], vs[i, :n])
