@@ -135,6 +135,15 @@ int qd_seq_gdn_conv(const void* mixed, const void* taps, void* conv_state, void*
 int qd_seq_gdn_recurrence(const void* conv_qkv, const void* a, const void* b, const void* a_log,
                           const void* dt_bias, float* rec_state, void* out, int tokens, int key_heads,
                           int value_heads, int key_dim, int value_dim, void* stream);
+/* The same recurrence for a long run of tokens, 64 at a time on the tensor cores (closed form of
+ * the delta rule within a chunk; the reference walks the run token by token,
+ * quickdraw/kernel/triton/delta.py:57-81): tf32 operands, fp32 sums, about 1e-3 relative from
+ * the token-by-token form.  key_dim 128, value_dim % 32 == 0, else QD_ERR_UNSUPPORTED.
+ * scratch: qd_seq_gdn_chunk_scratch_bytes(tokens, value_heads) bytes, 16-byte aligned. */
+long long qd_seq_gdn_chunk_scratch_bytes(int tokens, int value_heads);
+int qd_seq_gdn_recurrence_chunked(const void* conv_qkv, const void* a, const void* b, const void* a_log,
+                                  const void* dt_bias, float* rec_state, void* out, int tokens, int key_heads,
+                                  int value_heads, int key_dim, int value_dim, void* scratch, void* stream);
 /* q/k norm + RoPE + cache write for positions position0 .. position0 + tokens - 1, then causal
  * attention of every token over [0, its position], gated.  k_cache / v_cache: this layer's
  * [capacity, kv_heads, head_dim]; q_scratch bf16 [tokens, q_heads, head_dim]. */

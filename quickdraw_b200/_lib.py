@@ -59,6 +59,8 @@ SIGNATURES = {
     "qd_seq_bf16_matmul": [P, P, P, I, I, I, P],
     "qd_seq_gdn_conv": [P, P, P, P, I, I, I, P],
     "qd_seq_gdn_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "qd_seq_gdn_chunk_scratch_bytes": [I, I],
+    "qd_seq_gdn_recurrence_chunked": [P, P, P, P, P, P, P, I, I, I, I, I, P, P],
     "qd_seq_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, P],
     "qd_seq_route_topk": [P, I, I, I, P, P, P],
     "qd_batch_gdn_conv": [P, P, P, L, P, I, I, I, P],
@@ -70,7 +72,7 @@ SIGNATURES = {
 }
 
 LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes", "qd_exchange_bytes",
-                "qd_nvfp4_matmul_rows_scratch_bytes"}
+                "qd_nvfp4_matmul_rows_scratch_bytes", "qd_seq_gdn_chunk_scratch_bytes"}
 
 _lib = None
 

@@ -385,10 +385,29 @@ __global__ void swiglu_kernel(const bf16* gate, const bf16* up, bf16* out, int n
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __float2bfloat16_rn(round_bf16(silu_precise(ld_bf16(gate + i))) * ld_bf16(up + i));
 }
+// eight elements per thread (16-byte accesses)
+__global__ void swiglu8_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out, int n8) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const uint4 g = gate[i], u = up[i];
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float lo = round_bf16(silu_precise(__uint_as_float(gw[q] << 16))) * __uint_as_float(uw[q] << 16);
+        const float hi = round_bf16(silu_precise(__uint_as_float(gw[q] & 0xffff0000u))) * __uint_as_float(uw[q] & 0xffff0000u);
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+        o[q] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
 extern "C" int qd_swiglu(const void* gate, const void* up, void* out, int n, void* stream) {
     QD_CHECK_ARG(gate && up && out && n >= 0);
     if (n == 0) return QD_OK;
-    swiglu_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const bf16*)gate, (const bf16*)up, (bf16*)out, n);
+    if (n % 8 == 0 && !(((uintptr_t)gate | (uintptr_t)up | (uintptr_t)out) & 15u))
+        swiglu8_kernel<<<(n / 8 + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const uint4*)gate, (const uint4*)up, (uint4*)out, n / 8);
+    else
+        swiglu_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const bf16*)gate, (const bf16*)up, (bf16*)out, n);
     return qd_launch_status();
 }
 

@@ -76,24 +76,34 @@ __global__ void seq_bf16_matmul_kernel(const bf16* __restrict__ x, const bf16* _
 // and g + 8 at inputs 64 s + 16 t .. + 15 of step s (a quarter-warp reads two whole 128-byte
 // lines), and the 16 inputs of token 8 nt + g at the same offsets are its B fragments, so every
 // element of the 16 x 32 result is used.  fp32 accumulators, one bf16 rounding.
-constexpr int kTallTokens = 32, kTallMaxWidth = 3072, kTallUnroll = 4, kTallWarps = 16;
+constexpr int kTallTokens = 32, kTallMaxWidth = 3072, kTallUnroll = 2, kTallWarps = 16;
 __global__ void __launch_bounds__(kTallWarps * 32, 1)
 seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
-                            int tokens, int rows, int width) {
+                            int tokens, int rows, int width, int groups_per_block) {
     extern __shared__ __align__(16) unsigned char tall_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int t0 = blockIdx.y * kTallTokens, nt_rows = min(kTallTokens, tokens - t0);
     const int pieces = width / 8, x_row = 2 * width + 16;
-    for (int i = tid; i < kTallTokens * pieces; i += kTallWarps * 32) {
-        const int row = i / pieces, col = i % pieces;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (row < nt_rows) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + row) * width) + col);
-        *reinterpret_cast<uint4*>(tall_smem + (size_t)row * x_row + col * 16) = v;
+    for (int i0 = tid; i0 < kTallTokens * pieces; i0 += kTallWarps * 32 * 8) {      // eight loads in flight per thread
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * kTallWarps * 32, row = i / pieces, col = i % pieces;
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (i < kTallTokens * pieces && row < nt_rows) v[u] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + row) * width) + col);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * kTallWarps * 32, row = i / pieces, col = i % pieces;
+            if (i < kTallTokens * pieces) *reinterpret_cast<uint4*>(tall_smem + (size_t)row * x_row + col * 16) = v[u];
+        }
     }
     __syncthreads();
     const unsigned char* xs = tall_smem + (size_t)g * x_row + t * 32;
     const int steps = width / 64;
-    for (int n0 = (blockIdx.x * kTallWarps + warp) * 16; n0 < rows; n0 += gridDim.x * kTallWarps * 16) {
+    // few rows: only the first groups_per_block warps multiply (more blocks share the rows)
+    for (int n0 = warp < groups_per_block ? (blockIdx.x * groups_per_block + warp) * 16 : rows; n0 < rows;
+         n0 += gridDim.x * groups_per_block * 16) {
         // rows past the matrix read its last row and store nothing
         const uint4* lo = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + g, rows - 1) * width + t * 16);
         const uint4* hi = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + g + 8, rows - 1) * width + t * 16);
@@ -102,15 +112,17 @@ seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
-#pragma unroll 1
-        for (int s0 = 0; s0 < steps; s0 += kTallUnroll) {
-            uint4 a[kTallUnroll][4];
+        // two register buffers of kTallUnroll steps: the loads of one are in flight while the
+        // other is multiplied (the warps of a block run in step, so nothing else would hide them)
+        auto load = [&](uint4 (&a)[kTallUnroll][4], int s0) {
 #pragma unroll
             for (int u = 0; u < kTallUnroll; ++u) {
                 const int s = min(s0 + u, steps - 1);
                 a[u][0] = __ldg(lo + s * 8); a[u][1] = __ldg(lo + s * 8 + 1);
                 a[u][2] = __ldg(hi + s * 8); a[u][3] = __ldg(hi + s * 8 + 1);
             }
+        };
+        auto multiply = [&](const uint4 (&a)[kTallUnroll][4], int s0) {
 #pragma unroll
             for (int u = 0; u < kTallUnroll; ++u) {
                 if (s0 + u >= steps) break;
@@ -124,6 +136,15 @@ seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__
                     mma_bf16(acc[nt], a[u][1].z, a[u][3].z, a[u][1].w, a[u][3].w, b1.z, b1.w);
                 }
             }
+        };
+        uint4 even[kTallUnroll][4], odd[kTallUnroll][4];
+        load(even, 0);
+#pragma unroll 1
+        for (int s0 = 0; s0 < steps; s0 += 2 * kTallUnroll) {
+            if (s0 + kTallUnroll < steps) load(odd, s0 + kTallUnroll);
+            multiply(even, s0);
+            if (s0 + 2 * kTallUnroll < steps) load(even, s0 + 2 * kTallUnroll);
+            if (s0 + kTallUnroll < steps) multiply(odd, s0 + kTallUnroll);
         }
         // acc[nt][0..1] = row n0 + g, tokens 8 nt + 2 t and + 1; [2..3] = row n0 + g + 8
 #pragma unroll
@@ -153,6 +174,49 @@ __global__ void seq_conv_kernel(const bf16* __restrict__ mixed, const bf16* __re
     for (int k = 0; k < width; ++k)
         acc += round_bf16(conv_input(mixed, state, t - (width - 1) + k, c, channels, width) * ld_bf16(taps + (size_t)c * width + k));
     out[(size_t)t * channels + c] = __float2bfloat16_rn(silu_precise(acc));
+}
+// The same arithmetic for width 4 with a thread per (pair of channels, run of sixteen tokens):
+// the window slides through registers, so every input row is loaded once per run (4-byte loads,
+// 128 bytes per warp) instead of once per tap.
+constexpr int kConvRun = 16;
+__global__ void __launch_bounds__(128)
+seq_conv4_kernel(const bf16* __restrict__ mixed, const bf16* __restrict__ taps, const bf16* __restrict__ state,
+                 bf16* __restrict__ out, int tokens, int channels) {
+    const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x), t0 = blockIdx.y * kConvRun;
+    if (c >= channels) return;
+    const uint2 tp0 = *reinterpret_cast<const uint2*>(taps + (size_t)c * 4), tp1 = *reinterpret_cast<const uint2*>(taps + (size_t)c * 4 + 4);
+    const float ta[4] = {bf16_bits_to_float(tp0.x & 0xffffu), bf16_bits_to_float(tp0.x >> 16),
+                         bf16_bits_to_float(tp0.y & 0xffffu), bf16_bits_to_float(tp0.y >> 16)};
+    const float tb[4] = {bf16_bits_to_float(tp1.x & 0xffffu), bf16_bits_to_float(tp1.x >> 16),
+                         bf16_bits_to_float(tp1.y & 0xffffu), bf16_bits_to_float(tp1.y >> 16)};
+    float wa[4], wb[4];                  // inputs t - 3 .. t of either channel
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        const int index = t0 - 3 + k;
+        if (index < 0) {
+            wa[k + 1] = ld_bf16(state + (size_t)c * 3 + index + 3);
+            wb[k + 1] = ld_bf16(state + (size_t)(c + 1) * 3 + index + 3);
+        } else {
+            const uint32_t pair = *reinterpret_cast<const uint32_t*>(mixed + (size_t)index * channels + c);
+            wa[k + 1] = bf16_bits_to_float(pair & 0xffffu); wb[k + 1] = bf16_bits_to_float(pair >> 16);
+        }
+    }
+    const int count = min(kConvRun, tokens - t0);
+    uint32_t fresh[kConvRun];
+#pragma unroll
+    for (int i = 0; i < kConvRun; ++i)
+        fresh[i] = i < count ? __ldg(reinterpret_cast<const uint32_t*>(mixed + (size_t)(t0 + i) * channels + c)) : 0u;
+#pragma unroll
+    for (int i = 0; i < kConvRun; ++i) {
+        if (i >= count) break;
+        wa[0] = wa[1]; wa[1] = wa[2]; wa[2] = wa[3]; wa[3] = bf16_bits_to_float(fresh[i] & 0xffffu);
+        wb[0] = wb[1]; wb[1] = wb[2]; wb[2] = wb[3]; wb[3] = bf16_bits_to_float(fresh[i] >> 16);
+        float acc_a = 0.f, acc_b = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { acc_a += round_bf16(wa[k] * ta[k]); acc_b += round_bf16(wb[k] * tb[k]); }
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(t0 + i) * channels + c) =
+            __floats2bfloat162_rn(silu_precise(acc_a), silu_precise(acc_b));
+    }
 }
 __global__ void seq_conv_state_kernel(const bf16* __restrict__ mixed, bf16* state, int tokens, int channels, int width) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -990,29 +1054,53 @@ seq_group_routes_kernel(const int32_t* __restrict__ ids, int routes, int experts
 // --------------------------------------------------------------------------- MoE combine
 // out[t] = bf16( bf16(sum of the token's routed rows in ascending expert id) +
 //                bf16(shared[t] * bf16(sigmoid(strength[t]))) )
-__global__ void seq_combine_kernel(const bf16* __restrict__ contributions, const int32_t* __restrict__ ids,
-                                   const bf16* __restrict__ shared, const bf16* __restrict__ strength,
-                                   bf16* __restrict__ out, int hidden, int topk) {
-    const int t = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= hidden) return;
+__global__ void __launch_bounds__(256)
+seq_combine_kernel(const bf16* __restrict__ contributions, const int32_t* __restrict__ ids,
+                   const bf16* __restrict__ shared, const bf16* __restrict__ strength,
+                   bf16* __restrict__ out, int hidden, int topk) {
+    // block = one token; slot_of[n] = the slot with the n-th smallest expert id; a thread then
+    // adds eight features of the token's rows in that order (16-byte loads)
+    __shared__ int slot_of[32];
+    const int t = blockIdx.x, tid = threadIdx.x;
     const int32_t* my = ids + (size_t)t * topk;
-    const bf16* rows = contributions + (size_t)t * topk * hidden;
-    float routed = 0.f;
-    int last = -1;
-    for (int n = 0; n < topk; ++n) {
-        int pick = -1, pick_id = 0x7fffffff;
-        for (int s = 0; s < topk; ++s) {
-            const int e = my[s];
-            if (e > last && e < pick_id) { pick = s; pick_id = e; }
-        }
-        if (pick < 0) break;
-        last = pick_id;
-        routed += ld_bf16(rows + (size_t)pick * hidden + i);
+    if (tid < topk) {
+        const int e = my[tid];
+        int rank = 0;
+        for (int s = 0; s < topk; ++s) { const int o = my[s]; rank += (o < e) || (o == e && s < tid); }
+        slot_of[rank] = tid;
     }
+    __syncthreads();
+    const bf16* rows = contributions + (size_t)t * topk * hidden;
     const float gate = round_bf16(sigmoid_precise(ld_bf16(strength + t)));
-    const float gated = round_bf16(ld_bf16(shared + (size_t)t * hidden + i) * gate);
-    out[(size_t)t * hidden + i] = __float2bfloat16_rn(round_bf16(routed) + gated);
+    if (hidden % 8 == 0 && !(((uintptr_t)contributions | (uintptr_t)shared | (uintptr_t)out) & 15u)) {
+        for (int i = tid * 8; i < hidden; i += 256 * 8) {
+            float routed[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+            for (int n = 0; n < topk; ++n) {
+                const uint4 v = *reinterpret_cast<const uint4*>(rows + (size_t)slot_of[n] * hidden + i);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { routed[2 * q] += bf16_bits_to_float(w[q] & 0xffffu); routed[2 * q + 1] += bf16_bits_to_float(w[q] >> 16); }
+            }
+            const uint4 sh = *reinterpret_cast<const uint4*>(shared + (size_t)t * hidden + i);
+            const uint32_t sw[4] = {sh.x, sh.y, sh.z, sh.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float lo = round_bf16(routed[2 * q]) + round_bf16(bf16_bits_to_float(sw[q] & 0xffffu) * gate);
+                const float hi = round_bf16(routed[2 * q + 1]) + round_bf16(bf16_bits_to_float(sw[q] >> 16) * gate);
+                o[q] = qd::pack_bf16x2(lo, hi);
+            }
+            *reinterpret_cast<uint4*>(out + (size_t)t * hidden + i) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        return;
+    }
+    for (int i = tid; i < hidden; i += 256) {
+        float routed = 0.f;
+        for (int n = 0; n < topk; ++n) routed += ld_bf16(rows + (size_t)slot_of[n] * hidden + i);
+        const float gated = round_bf16(ld_bf16(shared + (size_t)t * hidden + i) * gate);
+        out[(size_t)t * hidden + i] = __float2bfloat16_rn(round_bf16(routed) + gated);
+    }
 }
 
 }  // namespace
@@ -1028,8 +1116,8 @@ extern "C" int qd_seq_add_rms_norm(const void* x, const void* residual, const fl
 extern "C" int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tokens, int rows, int width, void* stream) {
     QD_CHECK_ARG(x && w && y && tokens > 0 && rows > 0 && width > 0);
     const uintptr_t align = (uintptr_t)x | (uintptr_t)w;
-    if (rows >= 4096 && width % 64 == 0 && width <= kTallMaxWidth && !(align & 15u) && (tokens + 31) / 32 <= 65535) {
-        // tall matrix: read every weight row once per tile of 32 tokens
+    if ((rows >= 4096 || tokens >= 64) && width % 64 == 0 && width <= kTallMaxWidth && !(align & 15u) && (tokens + 31) / 32 <= 65535) {
+        // tall matrix or many tokens: every weight row is read once per tile of 32 tokens (tensor-core form)
         const size_t smem = (size_t)kTallTokens * (width * sizeof(bf16) + 16);
         int dev = 0, sms = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
@@ -1041,8 +1129,13 @@ extern "C" int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tok
         }
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        seq_bf16_matmul_tall_kernel<<<dim3(sms, (tokens + 31) / 32), kTallWarps * 32, smem, (cudaStream_t)stream>>>(
-            (const bf16*)x, (const bf16*)w, (bf16*)y, tokens, rows, width);
+        // sixteen row groups per block, fewer while the blocks do not fill the GPU
+        const int row_groups = (rows + 15) / 16, token_tiles = (tokens + 31) / 32;
+        int per_block = kTallWarps;
+        while (per_block > 2 && (long long)((row_groups + per_block - 1) / per_block) * token_tiles < sms) per_block >>= 1;
+        const int row_blocks = (row_groups + per_block - 1) / per_block;
+        seq_bf16_matmul_tall_kernel<<<dim3(row_blocks < sms ? row_blocks : sms, token_tiles), kTallWarps * 32, smem, (cudaStream_t)stream>>>(
+            (const bf16*)x, (const bf16*)w, (bf16*)y, tokens, rows, width, per_block);
         return qd_launch_status();
     }
     seq_bf16_matmul_kernel<<<dim3((rows + 7) / 8, tokens), 256, 0, (cudaStream_t)stream>>>(
@@ -1054,8 +1147,12 @@ extern "C" int qd_seq_gdn_conv(const void* mixed, const void* taps, void* conv_s
                                int channels, int width, void* stream) {
     QD_CHECK_ARG(mixed && taps && out && tokens > 0 && channels > 0 && width >= 1 && width <= 8 && (width == 1 || conv_state));
     if (tokens > 65535) return QD_ERR_UNSUPPORTED;
-    seq_conv_kernel<<<dim3((channels + 127) / 128, tokens), 128, 0, (cudaStream_t)stream>>>(
-        (const bf16*)mixed, (const bf16*)taps, (const bf16*)conv_state, (bf16*)out, channels, width);
+    if (width == 4 && channels % 2 == 0 && tokens >= kConvRun && !(((uintptr_t)mixed | (uintptr_t)out) & 3u) && !((uintptr_t)taps & 7u))
+        seq_conv4_kernel<<<dim3((channels / 2 + 127) / 128, (tokens + kConvRun - 1) / kConvRun), 128, 0, (cudaStream_t)stream>>>(
+            (const bf16*)mixed, (const bf16*)taps, (const bf16*)conv_state, (bf16*)out, tokens, channels);
+    else
+        seq_conv_kernel<<<dim3((channels + 127) / 128, tokens), 128, 0, (cudaStream_t)stream>>>(
+            (const bf16*)mixed, (const bf16*)taps, (const bf16*)conv_state, (bf16*)out, channels, width);
     if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     if (width > 1)
         seq_conv_state_kernel<<<(channels + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
@@ -1216,7 +1313,8 @@ extern "C" int qd_seq_group_routes(const int32_t* ids, int routes, int experts, 
 extern "C" int qd_seq_moe_combine(const void* contributions, const int32_t* ids, const void* shared,
                                   const void* strength, void* out, int tokens, int hidden, int topk, void* stream) {
     QD_CHECK_ARG(contributions && ids && shared && strength && out && tokens > 0 && hidden > 0 && topk > 0);
-    seq_combine_kernel<<<dim3((hidden + 255) / 256, tokens), 256, 0, (cudaStream_t)stream>>>(
+    if (topk > 32) return QD_ERR_UNSUPPORTED;
+    seq_combine_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>(
         (const bf16*)contributions, ids, (const bf16*)shared, (const bf16*)strength, (bf16*)out, hidden, topk);
     return qd_launch_status();
 }

@@ -33,6 +33,7 @@ class ChunkPrefill:
     sliced, group, expert_range = False, None, None      # defaults of a whole model on one GPU
     total_experts = None                                  # experts of the whole model (None: the bank's own count)
     _rows_scratch = None
+    CHUNKED_FROM = 64                                     # tokens from which the DeltaNet recurrence takes the chunked form
     FEW_TOKENS = 32                                       # token rows up to which a dense product takes the mma.sync form
     FEW_ROWS = 32                                         # mean routes per expert up to which the mma.sync form is used
 
@@ -121,9 +122,16 @@ class ChunkPrefill:
         call("qd_seq_gdn_conv", ptr(qkv), ptr(w.conv1d), ptr(state.conv_state[index]), ptr(conv), tokens,
              qkv.shape[1], c.linear_conv_kernel_dim, stream_of(x))
         core = self._empty(tokens, hv * dv)
-        call("qd_seq_gdn_recurrence", ptr(conv), ptr(a), ptr(b), ptr(w.A_log), ptr(w.dt_bias),
-             ptr(state.rec_state[index]), ptr(core), tokens, c.linear_num_key_heads, hv,
-             c.linear_key_head_dim, dv, stream_of(x))
+        if tokens >= self.CHUNKED_FROM and c.linear_key_head_dim == 128 and dv % 32 == 0:
+            # 64 tokens at a time on the tensor cores (closed form of the delta rule within a chunk)
+            scratch = torch.empty(lib().qd_seq_gdn_chunk_scratch_bytes(tokens, hv), dtype=torch.uint8, device=self.device)
+            call("qd_seq_gdn_recurrence_chunked", ptr(conv), ptr(a), ptr(b), ptr(w.A_log), ptr(w.dt_bias),
+                 ptr(state.rec_state[index]), ptr(core), tokens, c.linear_num_key_heads, hv,
+                 c.linear_key_head_dim, dv, ptr(scratch), stream_of(x))
+        else:
+            call("qd_seq_gdn_recurrence", ptr(conv), ptr(a), ptr(b), ptr(w.A_log), ptr(w.dt_bias),
+                 ptr(state.rec_state[index]), ptr(core), tokens, c.linear_num_key_heads, hv,
+                 c.linear_key_head_dim, dv, stream_of(x))
         gated = torch.empty_like(core)
         call("qd_gdn_gated_norm", ptr(core), ptr(z), ptr(w.norm), ptr(gated), tokens * hv, dv, c.rms_norm_eps,
              stream_of(x))

@@ -116,6 +116,37 @@ def test_sequence_conv_and_recurrence_match_single_token_kernels(cuda_device, ke
     assert O.rel_l2(out.cpu(), out_rows.cpu()) < 1e-2
 
 
+@pytest.mark.parametrize("value_dim,tokens", [(128, 64), (128, 100), (96, 515), (128, 1030)])
+def test_chunked_recurrence_matches_token_by_token(cuda_device, value_dim, tokens):
+    """The chunked form of the delta rule (64 tokens at a time, tf32 operands on the tensor
+    cores) against the token-by-token sequence kernel: outputs and final state within 5e-3
+    (tf32 rounding), for runs that end on a chunk boundary and inside a chunk."""
+    from quickdraw_b200._lib import call, lib, ptr, stream_of
+    hk, hv, key_dim = 2, 4, 128
+    channels = 2 * hk * key_dim + hv * value_dim
+    src = synthetic.Source(19, "cpu")
+    conv = src.normal("conv", tokens, channels).to(cuda_device)
+    a, b = src.normal("a", tokens, hv).to(cuda_device), src.normal("b", tokens, hv).to(cuda_device)
+    a_log, dt_bias = src.normal("alog", hv, std=0.5).to(cuda_device), src.normal("dt", hv).to(cuda_device)
+    rec0 = src.normal("rec0", hv, key_dim, value_dim, std=0.1).float().to(cuda_device)
+    s = stream_of(conv)
+    rec_seq, rec_chunk = rec0.clone(), rec0.clone()
+    out_seq = torch.empty(tokens, hv * value_dim, dtype=torch.bfloat16, device=cuda_device)
+    out_chunk = torch.full_like(out_seq, float("nan"))
+    call("qd_seq_gdn_recurrence", ptr(conv), ptr(a), ptr(b), ptr(a_log), ptr(dt_bias), ptr(rec_seq), ptr(out_seq),
+         tokens, hk, hv, key_dim, value_dim, s)
+    scratch = torch.empty(lib().qd_seq_gdn_chunk_scratch_bytes(tokens, hv), dtype=torch.uint8, device=cuda_device)
+    call("qd_seq_gdn_recurrence_chunked", ptr(conv), ptr(a), ptr(b), ptr(a_log), ptr(dt_bias), ptr(rec_chunk),
+         ptr(out_chunk), tokens, hk, hv, key_dim, value_dim, ptr(scratch), s)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out_chunk.float()).all() and torch.isfinite(rec_chunk).all()
+    errors = (O.rel_l2(out_chunk.cpu(), out_seq.cpu()), O.rel_l2(rec_chunk.cpu(), rec_seq.cpu()))
+    assert max(errors) < 5e-3, errors
+    # token by token as well: no single row is far off
+    rows = (out_chunk.float() - out_seq.float()).norm(dim=1) / out_seq.float().norm(dim=1).clamp_min(1e-6)
+    assert float(rows.max()) < 3e-2, float(rows.max())
+
+
 @pytest.mark.parametrize("routes,experts", [(4088, 256), (24, 16), (5000, 7), (1, 3)])
 def test_group_routes_is_the_stable_sort_by_expert(cuda_device, routes, experts):
     from quickdraw_b200._lib import call, ptr, stream_of
