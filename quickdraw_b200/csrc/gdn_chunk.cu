@@ -14,10 +14,12 @@
 //               K K^T and Q K^T on mma.sync (tf32), L and A, T = (I + L)^-1 by forward substitution
 //               in fp32 (a column per four lanes), T B and A written to a scratch area;
 //   recurrence  block = (value head, 32 value columns), chunks in order: R = V - (G K) S_0,
-//               U = (T B) R, O = (G Q) S_0 + A U, S = g_C S + K'^T U, all on mma.sync (tf32
-//               operands, fp32 accumulation); the state stays in accumulator registers, its
-//               tf32 copy in shared memory is the B operand; the next chunk's rows are loaded
-//               into registers and its T B / A tiles by cp.async while this chunk is multiplied.
+//               U = (T B) R, O = (G Q) S_0 + A U, S = g_C S + K^T (U scaled by g_C / g_t), all on
+//               mma.sync (tf32 operands, fp32 accumulation; row scalings applied to the sums,
+//               not to the operands); the state stays in accumulator registers, its tf32 copy in
+//               shared memory (transposed, like R and U: every operand fragment is one 16-byte
+//               load) is the B operand; the next chunk's rows are loaded into registers and its
+//               T B / A tiles by cp.async while this chunk is multiplied.
 // Operands are rounded to tf32 (10 bits of mantissa), sums are fp32: the result differs from the
 // token-by-token kernel by about 1e-3 relative, inside the tolerance the sequence forms are
 // tested with.
@@ -29,9 +31,10 @@ namespace {
 constexpr int kC = 64;             // tokens per chunk
 constexpr int kDK = 128;           // key dimension
 constexpr int kCols = 32;          // value columns per recurrence block
-constexpr int kKP = kDK + 4;       // floats per row of a [64][128] tile in shared memory (no bank conflicts)
-constexpr int kTP = kC + 4;        // ... of a [64][64] tile
-constexpr int kSP = kCols + 8;     // ... of a [*][32] tile
+// Row strides in shared memory: 16 floats of padding, so that the 16-byte fragment loads of a
+// quarter-warp (rows g, g + 1; floats 4 t .. 4 t + 3) fall on different banks.
+constexpr int kKP = kDK + 16;      // floats per row of a [*][128] tile
+constexpr int kTP = kC + 16;       // ... of a [*][64] tile
 constexpr int kTileFloats = kC * kTP;
 
 QD_DEVINL float tf32(float v) {
@@ -67,7 +70,7 @@ QD_DEVINL void load_rows(ChunkRows& r, const bf16* __restrict__ qkv, int t_base,
         }
     }
 }
-// L2-normalised keys and queries (queries also divided by sqrt(128)) as tf32 values.
+// L2-normalised keys and queries (queries also scaled by 1 / sqrt(128)) as tf32 values.
 QD_DEVINL void store_rows(const ChunkRows& r, float* __restrict__ Kn, float* __restrict__ Qn, int warp, int lane) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -78,13 +81,21 @@ QD_DEVINL void store_rows(const ChunkRows& r, float* __restrict__ Kn, float* __r
         float qq = 0.f, kk = 0.f;
 #pragma unroll
         for (int e = 0; e < 4; ++e) { qq += q4[e] * q4[e]; kk += k4[e] * k4[e]; }
-        const float qscale = rsqrtf(warp_sum(qq) + 1e-6f), kscale = rsqrtf(warp_sum(kk) + 1e-6f);
+        const float qscale = rsqrtf(warp_sum(qq) + 1e-6f) * 0.08838834764831845f, kscale = rsqrtf(warp_sum(kk) + 1e-6f);
         const int at = (8 * warp + i) * kKP + 4 * lane;
         *reinterpret_cast<float4*>(Kn + at) = make_float4(tf32(k4[0] * kscale), tf32(k4[1] * kscale), tf32(k4[2] * kscale), tf32(k4[3] * kscale));
-        *reinterpret_cast<float4*>(Qn + at) =
-            make_float4(tf32((q4[0] * qscale) / sqrtf((float)kDK)), tf32((q4[1] * qscale) / sqrtf((float)kDK)),
-                        tf32((q4[2] * qscale) / sqrtf((float)kDK)), tf32((q4[3] * qscale) / sqrtf((float)kDK)));
+        *reinterpret_cast<float4*>(Qn + at) = make_float4(tf32(q4[0] * qscale), tf32(q4[1] * qscale), tf32(q4[2] * qscale), tf32(q4[3] * qscale));
     }
+}
+QD_DEVINL float4 lds4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+
+// Two k-steps of an MMA tile from 16-byte fragments.  The contraction index is permuted the same
+// way on both sides: lane (g, t) supplies elements 4 t, 4 t + 1 (first step) and 4 t + 2, 4 t + 3
+// (second step) of every 16, so one 16-byte load per row (A: rows g and g + 8; B: column g)
+// feeds two MMAs.
+QD_DEVINL void mma_pair(float (&d)[4], const float4& a_lo, const float4& a_hi, const float4& b) {
+    mma_tf32(d, a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+    mma_tf32(d, a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
 }
 
 // ------------------------------------------------------------------------------- prepare
@@ -125,18 +136,15 @@ gdn_chunk_prepare_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ 
     for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int c = 0; c < 4; ++c) { g1[j][c] = 0.f; g2[j][c] = 0.f; }
-#pragma unroll 4
-    for (int ks = 0; ks < kDK / 8; ++ks) {
-        const float* ka = Kn + (16 * mt + g) * kKP + 8 * ks + t;
-        const float* qa = Qn + (16 * mt + g) * kKP + 8 * ks + t;
-        const float k0 = ka[0], k1 = ka[8 * kKP], k2 = ka[4], k3 = ka[8 * kKP + 4];
-        const float q0 = qa[0], q1 = qa[8 * kKP], q2 = qa[4], q3 = qa[8 * kKP + 4];
+#pragma unroll 2
+    for (int kk = 0; kk < kDK / 16; ++kk) {
+        const int at = (16 * mt + g) * kKP + 16 * kk + 4 * t;
+        const float4 k_lo = lds4(Kn + at), k_hi = lds4(Kn + at + 8 * kKP), q_lo = lds4(Qn + at), q_hi = lds4(Qn + at + 8 * kKP);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float* kb = Kn + ((nq * 4 + j) * 8 + g) * kKP + 8 * ks + t;
-            const float b0 = kb[0], b1 = kb[4];
-            mma_tf32(g1[j], k0, k1, k2, k3, b0, b1);
-            mma_tf32(g2[j], q0, q1, q2, q3, b0, b1);
+            const float4 bk = lds4(Kn + ((nq * 4 + j) * 8 + g) * kKP + 16 * kk + 4 * t);
+            mma_pair(g1[j], k_lo, k_hi, bk);
+            mma_pair(g2[j], q_lo, q_hi, bk);
         }
     }
     __syncthreads();                           // cum is complete
@@ -179,17 +187,20 @@ gdn_chunk_prepare_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------- recurrence
+constexpr int kVP = kCols + 8;     // floats per row of the [64][32] value tile
 __global__ void __launch_bounds__(256, 1)
 gdn_chunk_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ a, const bf16* __restrict__ a_log,
                             const bf16* __restrict__ dt_bias, float* __restrict__ state, bf16* __restrict__ out,
                             const float* __restrict__ scratch, int tokens, int hk, int hv, int dv) {
     extern __shared__ __align__(16) float rec_smem[];
-    float* Kn = rec_smem;                      // [64][kKP]
+    float* Kn = rec_smem;                      // [64 tokens][kKP]
     float* Qn = Kn + kC * kKP;
     float* TA = Qn + kC * kKP;                 // [2][T B | A][64][kTP]
-    float* Ss = TA + 4 * kTileFloats;          // [128][kSP]: the state at the start of the chunk, tf32
-    float* Rs = Ss + kDK * kSP;                // [64][kSP]: V, then R
-    float* Us = Rs + kC * kSP;                 // [64][kSP]
+    float* St = TA + 4 * kTileFloats;          // [32 columns][kKP]: the state at the start of the chunk, transposed, tf32
+    float* Rt = St + kCols * kKP;              // [32 columns][kTP]: R transposed
+    float* Ut = Rt + kCols * kTP;              // ... U
+    float* Wt = Ut + kCols * kTP;              // ... U with row t scaled by g_C / g_t
+    float* Vs = Wt + kCols * kTP;              // [64 tokens][kVP]: the value columns
     __shared__ float gam[kC], gend[kC], lg_s[kC];
     __shared__ float g_end;
     const int head = blockIdx.x, c0 = blockIdx.y * kCols;
@@ -228,19 +239,19 @@ gdn_chunk_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict
     auto finish = [&]() {                      // registers -> shared memory: rows, values, decays; the state's tf32 copy
         store_rows(rows, Kn, Qn, warp, lane);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) Rs[(8 * warp + i) * kSP + lane] = __bfloat162float(vals[i]);
+        for (int i = 0; i < 8; ++i) Vs[(8 * warp + i) * kVP + lane] = __bfloat162float(vals[i]);
         if (tid < kC) lg_s[tid] = lg;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) Ss[(16 * warp + g + 8 * (c >> 1)) * kSP + 8 * nt + 2 * t + (c & 1)] = tf32(acc[nt][c]);
+            for (int c = 0; c < 4; ++c) St[(8 * nt + 2 * t + (c & 1)) * kKP + 16 * warp + g + 8 * (c >> 1)] = tf32(acc[nt][c]);
     };
     issue(0);
     finish();
     __syncthreads();
 #pragma unroll 1
     for (int chunk = 0; chunk < chunks; ++chunk) {
-        // ---- decays of the chunk: g_t (rows of K and Q), g_C / g_t (rows of K for the state), g_C
+        // ---- decays of the chunk: g_t (rows of K S and Q S), g_C / g_t (rows of U for the state), g_C
         if (warp == 0) {
             float v0 = lg_s[2 * lane], v1 = lg_s[2 * lane + 1] + v0, run = v1;
 #pragma unroll
@@ -256,24 +267,24 @@ gdn_chunk_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict
         const float* Tb = TA + (size_t)(chunk & 1) * 2 * kTileFloats;
         const float* Am = Tb + kTileFloats;
         const int mt = warp & 3, n0 = (warp >> 2) * 16;          // stages on [64][32]: 16 rows x 16 columns per warp
-        const float row_g0 = gam[16 * mt + g], row_g1 = gam[16 * mt + g + 8];
-        // ---- R = V - (G K) S_0
+        const int row0 = 16 * mt + g;
+        const float row_g[2] = {gam[row0], gam[row0 + 8]}, row_e[2] = {gend[row0], gend[row0 + 8]};
+        const int frag = 4 * t;                                  // the lane's four elements of every sixteen
+        // ---- R = V - G (K S_0)
         {
             float r[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll 4
-            for (int ks = 0; ks < kDK / 8; ++ks) {
-                const float* ka = Kn + (16 * mt + g) * kKP + 8 * ks + t;
-                const float a0 = tf32(ka[0] * row_g0), a1 = tf32(ka[8 * kKP] * row_g1), a2 = tf32(ka[4] * row_g0), a3 = tf32(ka[8 * kKP + 4] * row_g1);
-                const float* sb = Ss + (8 * ks + t) * kSP + n0 + g;
-                mma_tf32(r[0], a0, a1, a2, a3, sb[0], sb[4 * kSP]);
-                mma_tf32(r[1], a0, a1, a2, a3, sb[8], sb[4 * kSP + 8]);
+#pragma unroll
+            for (int kk = 0; kk < kDK / 16; ++kk) {
+                const float4 a_lo = lds4(Kn + row0 * kKP + 16 * kk + frag), a_hi = lds4(Kn + (row0 + 8) * kKP + 16 * kk + frag);
+                mma_pair(r[0], a_lo, a_hi, lds4(St + (n0 + g) * kKP + 16 * kk + frag));
+                mma_pair(r[1], a_lo, a_hi, lds4(St + (n0 + 8 + g) * kKP + 16 * kk + frag));
             }
 #pragma unroll
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    float* at = Rs + (16 * mt + g + 8 * (c >> 1)) * kSP + n0 + 8 * j + 2 * t + (c & 1);
-                    *at = tf32(*at - r[j][c]);
+                    const int row = row0 + 8 * (c >> 1), col = n0 + 8 * j + 2 * t + (c & 1);
+                    Rt[col * kTP + row] = tf32(Vs[row * kVP + col] - row_g[c >> 1] * r[j][c]);
                 }
         }
         asm volatile("cp.async.wait_group 1;" ::: "memory");     // this chunk's T B and A (the next chunk's may be in flight)
@@ -281,60 +292,63 @@ gdn_chunk_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict
         // ---- U = (T B) R: T is lower triangular, so only the tokens up to the warp's rows count
         {
             float u[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            for (int ks = 0; ks < 2 * (mt + 1); ++ks) {
-                const float* ta = Tb + (16 * mt + g) * kTP + 8 * ks + t;
-                const float* rb = Rs + (8 * ks + t) * kSP + n0 + g;
-                mma_tf32(u[0], ta[0], ta[8 * kTP], ta[4], ta[8 * kTP + 4], rb[0], rb[4 * kSP]);
-                mma_tf32(u[1], ta[0], ta[8 * kTP], ta[4], ta[8 * kTP + 4], rb[8], rb[4 * kSP + 8]);
+            for (int kk = 0; kk <= mt; ++kk) {
+                const float4 a_lo = lds4(Tb + row0 * kTP + 16 * kk + frag), a_hi = lds4(Tb + (row0 + 8) * kTP + 16 * kk + frag);
+                mma_pair(u[0], a_lo, a_hi, lds4(Rt + (n0 + g) * kTP + 16 * kk + frag));
+                mma_pair(u[1], a_lo, a_hi, lds4(Rt + (n0 + 8 + g) * kTP + 16 * kk + frag));
             }
 #pragma unroll
             for (int j = 0; j < 2; ++j)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) Us[(16 * mt + g + 8 * (c >> 1)) * kSP + n0 + 8 * j + 2 * t + (c & 1)] = tf32(u[j][c]);
+                for (int c = 0; c < 4; ++c) {
+                    const int row = row0 + 8 * (c >> 1), col = n0 + 8 * j + 2 * t + (c & 1);
+                    Ut[col * kTP + row] = tf32(u[j][c]);
+                    Wt[col * kTP + row] = tf32(u[j][c] * row_e[c >> 1]);
+                }
         }
         __syncthreads();
-        // ---- O = (G Q) S_0 + A U
+        // ---- O = G (Q S_0) + A U
         {
             float o[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll 4
-            for (int ks = 0; ks < kDK / 8; ++ks) {
-                const float* qa = Qn + (16 * mt + g) * kKP + 8 * ks + t;
-                const float a0 = tf32(qa[0] * row_g0), a1 = tf32(qa[8 * kKP] * row_g1), a2 = tf32(qa[4] * row_g0), a3 = tf32(qa[8 * kKP + 4] * row_g1);
-                const float* sb = Ss + (8 * ks + t) * kSP + n0 + g;
-                mma_tf32(o[0], a0, a1, a2, a3, sb[0], sb[4 * kSP]);
-                mma_tf32(o[1], a0, a1, a2, a3, sb[8], sb[4 * kSP + 8]);
+#pragma unroll
+            for (int kk = 0; kk < kDK / 16; ++kk) {
+                const float4 a_lo = lds4(Qn + row0 * kKP + 16 * kk + frag), a_hi = lds4(Qn + (row0 + 8) * kKP + 16 * kk + frag);
+                mma_pair(o[0], a_lo, a_hi, lds4(St + (n0 + g) * kKP + 16 * kk + frag));
+                mma_pair(o[1], a_lo, a_hi, lds4(St + (n0 + 8 + g) * kKP + 16 * kk + frag));
             }
-            for (int ks = 0; ks < 2 * (mt + 1); ++ks) {
-                const float* aa = Am + (16 * mt + g) * kTP + 8 * ks + t;
-                const float* ub = Us + (8 * ks + t) * kSP + n0 + g;
-                mma_tf32(o[0], aa[0], aa[8 * kTP], aa[4], aa[8 * kTP + 4], ub[0], ub[4 * kSP]);
-                mma_tf32(o[1], aa[0], aa[8 * kTP], aa[4], aa[8 * kTP + 4], ub[8], ub[4 * kSP + 8]);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[j][c] *= row_g[c >> 1];
+            for (int kk = 0; kk <= mt; ++kk) {
+                const float4 a_lo = lds4(Am + row0 * kTP + 16 * kk + frag), a_hi = lds4(Am + (row0 + 8) * kTP + 16 * kk + frag);
+                mma_pair(o[0], a_lo, a_hi, lds4(Ut + (n0 + g) * kTP + 16 * kk + frag));
+                mma_pair(o[1], a_lo, a_hi, lds4(Ut + (n0 + 8 + g) * kTP + 16 * kk + frag));
             }
 #pragma unroll
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    const int tok = chunk * kC + 16 * mt + g + 8 * half;
+                    const int tok = chunk * kC + row0 + 8 * half;
                     if (tok < tokens)
                         *reinterpret_cast<__nv_bfloat162*>(out + (size_t)tok * hv * dv + (size_t)head * dv + c0 + n0 + 8 * j + 2 * t) =
                             __floats2bfloat162_rn(o[j][2 * half], o[j][2 * half + 1]);
                 }
         }
-        // ---- S = g_C S + (K scaled by g_C / g_t)^T U: warp w = keys 16 w .. 16 w + 15, all 32 columns
+        // ---- S = g_C S + K^T W: warp w = keys 16 w .. 16 w + 15, all 32 columns; contraction over the tokens
         {
             const float scale = g_end;
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) acc[nt][c] *= scale;
-#pragma unroll 2
-            for (int ks = 0; ks < kC / 8; ++ks) {
-                const float e0 = gend[8 * ks + t], e1 = gend[8 * ks + t + 4];
-                const float* ka = Kn + (8 * ks + t) * kKP + 16 * warp + g;
-                const float a0 = tf32(ka[0] * e0), a1 = tf32(ka[8] * e0), a2 = tf32(ka[4 * kKP] * e1), a3 = tf32(ka[4 * kKP + 8] * e1);
-                const float* ub = Us + (8 * ks + t) * kSP + g;
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) mma_tf32(acc[nt], a0, a1, a2, a3, ub[8 * nt], ub[4 * kSP + 8 * nt]);
+            for (int kk = 0; kk < kC / 16; ++kk) {
+                const float* ka = Kn + (16 * kk + frag) * kKP + 16 * warp + g;     // tokens 16 kk + 4 t .. + 3, keys g and g + 8
+                const float4 a_lo = make_float4(ka[0], ka[kKP], ka[2 * kKP], ka[3 * kKP]);
+                const float4 a_hi = make_float4(ka[8], ka[kKP + 8], ka[2 * kKP + 8], ka[3 * kKP + 8]);
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) mma_pair(acc[nt], a_lo, a_hi, lds4(Wt + (8 * nt + g) * kTP + 16 * kk + frag));
             }
         }
         __syncthreads();                       // every warp is done with this chunk's tiles
@@ -349,7 +363,7 @@ gdn_chunk_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict
 }
 
 constexpr size_t kPrepSmem = sizeof(float) * (2 * kC * kKP + 2 * kTileFloats);
-constexpr size_t kRecSmem = sizeof(float) * (2 * kC * kKP + 4 * kTileFloats + kDK * kSP + 2 * kC * kSP);
+constexpr size_t kRecSmem = sizeof(float) * (2 * kC * kKP + 4 * kTileFloats + kCols * kKP + 3 * kCols * kTP + kC * kVP);
 
 }  // namespace
 }  // namespace qd
