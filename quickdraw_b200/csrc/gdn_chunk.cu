@@ -219,7 +219,8 @@ gdn_chunk_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict
 
     ChunkRows rows;
     bf16 vals[8];
-    float lg = 0.f;
+    bf16 gate_raw = __float2bfloat16_rn(0.f);
+    bool gate_on = false;
     auto issue = [&](int chunk) {              // the chunk's rows into registers, its T B / A tiles by cp.async
         const int t_base = chunk * kC;
         load_rows(rows, qkv, t_base, tokens, channels, hk, key_head, warp, lane);
@@ -229,8 +230,8 @@ gdn_chunk_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict
             vals[i] = tok < tokens ? qkv[(size_t)tok * channels + (size_t)2 * hk * kDK + (size_t)head * dv + c0 + lane]
                                    : __float2bfloat16_rn(0.f);
         }
-        lg = 0.f;
-        if (tid < kC && t_base + tid < tokens) lg = log_decay(ld_bf16(a + (size_t)(t_base + tid) * hv + head), a_decay, bias);
+        gate_on = tid < kC && t_base + tid < tokens;             // the value is used in finish(): nothing waits for it here
+        if (gate_on) gate_raw = a[(size_t)(t_base + tid) * hv + head];
         const float* src = scratch + ((size_t)head * chunks + chunk) * 2 * kTileFloats;
         float* dst = TA + (size_t)(chunk & 1) * 2 * kTileFloats;
         for (int i = tid; i < 2 * kTileFloats / 4; i += 256) chunk_cp16(dst + 4 * i, src + 4 * i);
@@ -240,7 +241,7 @@ gdn_chunk_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict
         store_rows(rows, Kn, Qn, warp, lane);
 #pragma unroll
         for (int i = 0; i < 8; ++i) Vs[(8 * warp + i) * kVP + lane] = __bfloat162float(vals[i]);
-        if (tid < kC) lg_s[tid] = lg;
+        if (tid < kC) lg_s[tid] = gate_on ? log_decay(__bfloat162float(gate_raw), a_decay, bias) : 0.f;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
