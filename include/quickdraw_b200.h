@@ -112,14 +112,16 @@ int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const void* scales
                             void* stream);
 
 /* The same product when an expert receives only a few rows (a short chunk, a decode batch):
- * every expert that got routes is read once, its NVFP4 rows decoded once per eight routes and
+ * every expert that got routes is read once, its NVFP4 rows decoded once per routes_per_pass
+ * routes (8 or 32; 0 = the library's choice) and
  * multiplied on the warp-level tensor-core instruction (the grouped branch of
  * quickdraw/kernel/triton/moe.py:99-151 at small M).  Arguments as above; in_features
  * 512, 1024 or 2048, out_features a multiple of 16, else QD_ERR_UNSUPPORTED. */
 int qd_nvfp4_expert_rows(const void* x, const void* codes, const void* scales, const float* global,
                          const int32_t* order, const int32_t* boundaries, const float* routing, void* y,
                          int routes, int experts, int topk, int out_features, int in_features,
-                         int group_size, int by_token, int scatter, int global_per_expert, void* stream);
+                         int group_size, int by_token, int scatter, int global_per_expert,
+                         int routes_per_pass, void* stream);
 
 /* ---- Sequence forms for a chunk of prompt tokens (the 2-D branches of
  * quickdraw/kernel/triton/{norm,delta,attention,moe}.py, qwen.py:66-241): the single-token

@@ -35,7 +35,8 @@ class ChunkPrefill:
     _rows_scratch = None
     CHUNKED_FROM = 64                                     # tokens from which the DeltaNet recurrence takes the chunked form
     FEW_TOKENS = 32                                       # token rows up to which a dense product takes the mma.sync form
-    FEW_ROWS = 32                                         # mean routes per expert up to which the mma.sync form is used
+    ROUTES_PER_PASS = 0                                   # 8 / 32 routes per decoding of a weight tile; 0: the library chooses
+    FEW_ROWS = 20                                         # mean routes per expert up to which the mma.sync form is used
 
     def __init__(self, ckpt: Checkpoint, expert_range: tuple[int, int] | None = None, group=None):
         c = ckpt.config
@@ -99,11 +100,11 @@ class ChunkPrefill:
         out = (torch.zeros if self.sliced and scatter else torch.empty)((routes, bank.out_features), dtype=BF16, device=self.device)
         experts = bank.weight.shape[0]
         if routes <= self.FEW_ROWS * (self.total_experts or experts) and bank.in_features in (512, 1024, 2048) and bank.out_features % 16 == 0:
-            # few rows per expert: weights decoded once per eight routes on mma.sync, no 128-token tiles
+            # few rows per expert: weights decoded once per 8 or 32 routes on mma.sync, no 128-token tiles
             call("qd_nvfp4_expert_rows", ptr(x), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
                  ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, experts, topk, bank.out_features,
                  bank.in_features, bank.group_size, int(by_token), int(scatter),
-                 int(bank.weight_scale_2.numel() != 1), stream_of(x))
+                 int(bank.weight_scale_2.numel() != 1), self.ROUTES_PER_PASS, stream_of(x))
             return out
         call("qd_nvfp4_grouped_matmul", ptr(x), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
              ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, bank.weight.shape[0], topk,

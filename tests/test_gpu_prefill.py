@@ -48,6 +48,9 @@ def test_chunked_prefill_matches_token_loop(cuda_device, chunk):
     (4, 2, 50, 2048, 512, 32),     # ... 25 routes per expert: four groups of eight, the last one with a single route
     (40, 8, 3, 512, 2048, 32),     # ... most experts without a route
     (8, 3, 21, 512, 272, 0),       # the same shape through the tcgen05 form
+    (4, 2, 50, 2048, 512, -32),    # 32 routes per pass: 25 routes per expert in one pass
+    (3, 2, 100, 1024, 144, -32),   # ... 67 routes per expert: three passes, the last one with three routes
+    (40, 8, 3, 512, 2048, -32),    # ... most experts without a route
 ])
 def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tokens, width, rows, few_rows):
     """The grouped product of the routed experts (tcgen05 tiles, or the mma.sync form for few
@@ -66,7 +69,10 @@ def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tok
     helper = ChunkPrefill.__new__(ChunkPrefill)
     helper.device = cuda_device
     helper.status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
-    helper.FEW_ROWS = few_rows
+    helper.FEW_ROWS = abs(few_rows) or 0
+    helper.ROUTES_PER_PASS = 32 if few_rows < 0 else (8 if few_rows > 0 else 0)
+    if few_rows < 0:
+        helper.FEW_ROWS = 10 ** 6
     routes = tokens * topk
     plain = helper._grouped(x, bank, order.to(torch.int32), boundaries, routes, topk, by_token=True, scatter=False)
     routed = helper._grouped(x.repeat_interleave(topk, 0)[order].contiguous(), bank, order.to(torch.int32), boundaries,
