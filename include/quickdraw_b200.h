@@ -66,10 +66,12 @@ int qd_nvfp4_matmul(const void* x, const void* codes, const void* scales, const 
  * weight tile is decoded once on the warp-level tensor-core instruction with the tokens as
  * columns; no 128-token tiles.  scratch: qd_nvfp4_matmul_rows_scratch_bytes(in_features) bytes,
  * 16-byte aligned, receives the token rows as f16; convert = 0 reuses what the previous call with
- * this scratch area converted (several projections of one input).  in_features % 512 == 0,
+ * this scratch area converted (several projections of one input).  x_up (or NULL): the input rows
+ * are bf16(bf16(silu(x)) * x_up), the SwiGLU of two projections (qwen.py:184, 191), formed on the
+ * way in.  in_features % 512 == 0,
  * out_features % 16 == 0, else QD_ERR_UNSUPPORTED. */
 long long qd_nvfp4_matmul_rows_scratch_bytes(int in_features);
-int qd_nvfp4_matmul_rows(const void* x, const void* codes, const void* scales, const float* global, void* y,
+int qd_nvfp4_matmul_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global, void* y,
                          int tokens, int out_features, int in_features, int group_size, void* scratch,
                          int convert, void* stream);
 
@@ -115,9 +117,10 @@ int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const void* scales
  * every expert that got routes is read once, its NVFP4 rows decoded once per routes_per_pass
  * routes (8 or 32; 0 = the library's choice) and
  * multiplied on the warp-level tensor-core instruction (the grouped branch of
- * quickdraw/kernel/triton/moe.py:99-151 at small M).  Arguments as above; in_features
+ * quickdraw/kernel/triton/moe.py:99-151 at small M).  Arguments as above; x_up (or NULL) as in
+ * qd_nvfp4_matmul_rows; in_features
  * 512, 1024 or 2048, out_features a multiple of 16, else QD_ERR_UNSUPPORTED. */
-int qd_nvfp4_expert_rows(const void* x, const void* codes, const void* scales, const float* global,
+int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global,
                          const int32_t* order, const int32_t* boundaries, const float* routing, void* y,
                          int routes, int experts, int topk, int out_features, int in_features,
                          int group_size, int by_token, int scatter, int global_per_expert,

@@ -50,11 +50,11 @@ SIGNATURES = {
     "qd_nvfp4_gemv_bank": [P, P, P, P, P, I, I, I, I, P],
     "qd_nvfp4_matmul": [P, P, P, P, P, I, I, I, I, P, P],
     "qd_nvfp4_matmul_rows_scratch_bytes": [I],
-    "qd_nvfp4_matmul_rows": [P, P, P, P, P, I, I, I, I, P, I, P],
+    "qd_nvfp4_matmul_rows": [P, P, P, P, P, P, I, I, I, I, P, I, P],
     "qd_nvfp4_quantize_act": [P, I, I, P, P, P, P, P],
     "qd_nvfp4_matmul_w4a4": [P, P, P, P, P, P, P, I, I, I, I, P, P],
     "qd_nvfp4_grouped_matmul": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
-    "qd_nvfp4_expert_rows": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
+    "qd_nvfp4_expert_rows": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
     "qd_seq_add_rms_norm": [P, P, P, P, P, I, I, F, P],
     "qd_seq_bf16_matmul": [P, P, P, I, I, I, P],
     "qd_seq_gdn_conv": [P, P, P, P, I, I, I, P],

@@ -43,7 +43,20 @@ QD_DEVINL int dense_piece(int c) { return c ^ ((c >> 2) & 2); }
 
 // Token rows as f16: xf [32][K] (rows past `tokens` zero), up[t] = the power of two that undoes
 // row t's down-scale.
-__global__ void __launch_bounds__(256) rows_to_f16_kernel(const bf16* __restrict__ x, int tokens, int K,
+QD_DEVINL uint4 swiglu8(const uint4& g, const uint4& u) {         // bf16(bf16(silu(g)) * u), eight values
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float lo = round_bf16(silu_precise(__uint_as_float(gw[q] << 16))) * __uint_as_float(uw[q] << 16);
+        const float hi = round_bf16(silu_precise(__uint_as_float(gw[q] & 0xffff0000u))) * __uint_as_float(uw[q] & 0xffff0000u);
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+        o[q] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+// x_up (or NULL): the rows are the SwiGLU of x (gate) and x_up.
+__global__ void __launch_bounds__(256) rows_to_f16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ x_up, int tokens, int K,
                                                           uint8_t* __restrict__ xf, float* __restrict__ up) {
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint4* out = reinterpret_cast<uint4*>(xf + (size_t)row * K * 2);
@@ -54,9 +67,10 @@ __global__ void __launch_bounds__(256) rows_to_f16_kernel(const bf16* __restrict
     }
     __shared__ float red[8];
     const uint4* in = reinterpret_cast<const uint4*>(x + (size_t)row * K);
+    const uint4* in_up = x_up ? reinterpret_cast<const uint4*>(x_up + (size_t)row * K) : nullptr;
     uint32_t biggest = 0u;
     for (int c = tid; c < K / 8; c += 256) {
-        const uint4 v = in[c];
+        const uint4 v = in_up ? swiglu8(in[c], in_up[c]) : in[c];
         biggest = max(max(biggest, max(v.x & 0x7fffu, (v.x >> 16) & 0x7fffu)), max(v.y & 0x7fffu, (v.y >> 16) & 0x7fffu));
         biggest = max(max(biggest, max(v.z & 0x7fffu, (v.z >> 16) & 0x7fffu)), max(v.w & 0x7fffu, (v.w >> 16) & 0x7fffu));
     }
@@ -68,7 +82,7 @@ __global__ void __launch_bounds__(256) rows_to_f16_kernel(const bf16* __restrict
     const int shift = (exponent > 14 && exponent < 128) ? exponent - 14 : 0;
     const float down = __uint_as_float((uint32_t)(127 - shift) << 23);
     for (int c = tid; c < K / 8; c += 256) {
-        const uint4 v = in[c];
+        const uint4 v = in_up ? swiglu8(in[c], in_up[c]) : in[c];
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
         uint32_t o[4];
 #pragma unroll
@@ -219,27 +233,28 @@ extern "C" long long qd_nvfp4_matmul_rows_scratch_bytes(int in_features) {
 // y [tokens, out_features] = x [tokens, in_features] W^T for tokens <= 32 (the contract of
 // qd_nvfp4_matmul).  scratch: qd_nvfp4_matmul_rows_scratch_bytes(in_features) bytes, 16-byte
 // aligned; convert = 0 reuses the token rows that the previous call with this scratch area
-// converted (several projections of the same input).  in_features a multiple of 512,
+// converted (several projections of the same input).  x_up (or NULL): the input rows are
+// bf16(bf16(silu(x)) * x_up), the SwiGLU of two projections.  in_features a multiple of 512,
 // out_features of 16, group size 16; QD_ERR_UNSUPPORTED otherwise.
-extern "C" int qd_nvfp4_matmul_rows(const void* x, const void* codes, const void* scales, const float* global, void* y,
+extern "C" int qd_nvfp4_matmul_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global, void* y,
                                     int tokens, int out_features, int in_features, int group_size, void* scratch,
                                     int convert, void* stream) {
     using namespace qd;
     QD_CHECK_ARG(x && codes && scales && global && y && scratch && tokens > 0 && out_features > 0 && in_features > 0);
     if (tokens > kDenseTokens || group_size != 16 || in_features % kDenseChunk != 0 || out_features % 16 != 0)
         return QD_ERR_UNSUPPORTED;
-    if (((uintptr_t)x | (uintptr_t)codes | (uintptr_t)scales | (uintptr_t)scratch) & 15u) return QD_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)x_up | (uintptr_t)codes | (uintptr_t)scales | (uintptr_t)scratch) & 15u) return QD_ERR_UNSUPPORTED;
     uint8_t* xf = (uint8_t*)scratch;
     float* up = reinterpret_cast<float*>(xf + (size_t)kDenseTokens * in_features * 2);
     if (convert) {
-        rows_to_f16_kernel<<<kDenseTokens, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, tokens, in_features, xf, up);
+        rows_to_f16_kernel<<<kDenseTokens, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)x_up, tokens, in_features, xf, up);
         if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     }
     DenseParams p = {xf, up, (const uint8_t*)codes, (const uint8_t*)scales, global, (bf16*)y, tokens, out_features, in_features};
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    // 64-row tiles once they fill the GPU, else 32-row tiles (twice the blocks)
-    return (out_features + 63) / 64 >= (sms > 0 ? sms : 148) ? launch_dense<4>(p, (cudaStream_t)stream)
+    // 32-row tiles while they fit one wave of the GPU (twice the blocks, half the chain), else 64-row tiles
+    return (out_features + 31) / 32 > (sms > 0 ? sms : 148) ? launch_dense<4>(p, (cudaStream_t)stream)
                                                             : launch_dense<2>(p, (cudaStream_t)stream);
 }

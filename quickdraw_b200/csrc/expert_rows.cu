@@ -42,7 +42,7 @@ template <int K, int NT> struct RowsShape {
 };
 
 struct RowsParams {
-    const bf16* x; const uint8_t* codes; const uint8_t* scales; const float* global;
+    const bf16* x; const bf16* x_up; const uint8_t* codes; const uint8_t* scales; const float* global;
     const int32_t* order; const int32_t* boundaries; const float* routing; bf16* y;
     int routes, experts, topk, out_features, by_token, scatter, global_per_expert;
     long long codes_stride, scales_stride;
@@ -127,6 +127,24 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
                 for (int i = 0; i < kBatch; ++i) {
                     const int idx = base + tid + i * kRowsThreads, j = idx / kPieces, c = idx % kPieces, row = source[j];
                     v[i] = row >= 0 ? reinterpret_cast<const uint4*>(p.x + (size_t)row * K)[c] : make_uint4(0u, 0u, 0u, 0u);
+                }
+                if (p.x_up) {             // the input is bf16(bf16(silu(x)) * x_up): SwiGLU of the gate / up rows on the way in
+#pragma unroll
+                    for (int i = 0; i < kBatch; ++i) {
+                        const int idx = base + tid + i * kRowsThreads, j = idx / kPieces, c = idx % kPieces, row = source[j];
+                        if (row < 0) continue;
+                        const uint4 u = reinterpret_cast<const uint4*>(p.x_up + (size_t)row * K)[c];
+                        const uint32_t gw[4] = {v[i].x, v[i].y, v[i].z, v[i].w}, uw[4] = {u.x, u.y, u.z, u.w};
+                        uint32_t o[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float lo = round_bf16(silu_precise(__uint_as_float(gw[q] << 16))) * __uint_as_float(uw[q] << 16);
+                            const float hi = round_bf16(silu_precise(__uint_as_float(gw[q] & 0xffff0000u))) * __uint_as_float(uw[q] & 0xffff0000u);
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+                            o[q] = *reinterpret_cast<const uint32_t*>(&pair);
+                        }
+                        v[i] = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
                 }
 #pragma unroll
                 for (int i = 0; i < kBatch; ++i) {
@@ -259,11 +277,13 @@ template <int K> int launch_rows_for(const RowsParams& p, bool many, cudaStream_
 }  // namespace
 }  // namespace qd
 
-// The grouped product for few rows per expert (the contract of qd_nvfp4_grouped_matmul).
+// The grouped product for few rows per expert (the contract of qd_nvfp4_grouped_matmul).  x_up (or NULL):
+// the input rows are bf16(bf16(silu(x)) * x_up), the SwiGLU of the gate and up products
+// (quickdraw/models/qwen.py:184, 191), computed while the rows are staged.
 // in_features 512, 1024 or 2048, out_features a multiple of 16, group size 16, 16-byte aligned
 // pointers; QD_ERR_UNSUPPORTED otherwise.  routes_per_pass: 8 or 32 routes multiplied per decoding of
 // a weight tile, 0 = the library's choice (8).
-extern "C" int qd_nvfp4_expert_rows(const void* x, const void* codes, const void* scales, const float* global,
+extern "C" int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global,
                                     const int32_t* order, const int32_t* boundaries, const float* routing, void* y,
                                     int routes, int experts, int topk, int out_features, int in_features,
                                     int group_size, int by_token, int scatter, int global_per_expert,
@@ -273,9 +293,9 @@ extern "C" int qd_nvfp4_expert_rows(const void* x, const void* codes, const void
     QD_CHECK_ARG(routes > 0 && experts > 0 && experts <= 65535 && topk > 0 && out_features > 0 && in_features > 0);
     QD_CHECK_ARG(routes_per_pass == 0 || routes_per_pass == 8 || routes_per_pass == 32);
     if (group_size != 16 || out_features % 16 != 0) return QD_ERR_UNSUPPORTED;
-    if (((uintptr_t)x | (uintptr_t)codes | (uintptr_t)scales) & 15u) return QD_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)x_up | (uintptr_t)codes | (uintptr_t)scales) & 15u) return QD_ERR_UNSUPPORTED;
     RowsParams p = {};
-    p.x = (const bf16*)x; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
+    p.x = (const bf16*)x; p.x_up = (const bf16*)x_up; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
     p.order = order; p.boundaries = boundaries; p.routing = routing; p.y = (bf16*)y;
     p.routes = routes; p.experts = experts; p.topk = topk; p.out_features = out_features;
     p.by_token = by_token; p.scatter = scatter; p.global_per_expert = global_per_expert;

@@ -119,11 +119,13 @@ def matmul(x: torch.Tensor, proj: NVFP4Linear) -> torch.Tensor:
     return out
 
 
-def matmul_rows(x: torch.Tensor, proj: NVFP4Linear, scratch: torch.Tensor | None = None, *, convert: bool = True):
+def matmul_rows(x: torch.Tensor, proj: NVFP4Linear, scratch: torch.Tensor | None = None, *, convert: bool = True,
+                x_up: torch.Tensor | None = None):
     """``matmul`` for at most 32 token rows (a decode batch): the weights are decoded once on the
     warp-level tensor-core instruction with the tokens as columns.  ``scratch`` (uint8,
     ``rows_scratch_bytes(in_features)``) receives the f16 copy of the rows; ``convert=False``
     reuses what the previous call left there (several projections of the same input).
+    ``x_up``: the input rows are bf16(bf16(silu(x)) * x_up), formed on the way in.
     in_features a multiple of 512, out_features of 16.  Returns (y, scratch)."""
     assert isinstance(proj, NVFP4Linear) and x.ndim == 2 and proj.weight.ndim == 2 and x.shape[0] <= 32
     assert x.is_cuda and x.dtype == BF16 and x.is_contiguous() and x.shape[1] == proj.in_features
@@ -134,7 +136,8 @@ def matmul_rows(x: torch.Tensor, proj: NVFP4Linear, scratch: torch.Tensor | None
         scratch = torch.empty(rows_scratch_bytes(proj.in_features), dtype=torch.uint8, device=x.device)
     assert scratch.is_cuda and scratch.numel() >= rows_scratch_bytes(proj.in_features)
     out = torch.empty((x.shape[0], proj.out_features), dtype=BF16, device=x.device)
-    call("qd_nvfp4_matmul_rows", ptr(x), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2), ptr(out),
+    assert x_up is None or (x_up.shape == x.shape and x_up.dtype == BF16 and x_up.is_contiguous() and x_up.device == x.device)
+    call("qd_nvfp4_matmul_rows", ptr(x), ptr(x_up), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2), ptr(out),
          x.shape[0], proj.out_features, proj.in_features, proj.group_size, ptr(scratch), int(convert), stream_of(x))
     return out, scratch
 

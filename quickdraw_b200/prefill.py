@@ -57,22 +57,30 @@ class ChunkPrefill:
     def _empty(self, *shape, dtype=BF16):
         return torch.empty(shape, dtype=dtype, device=self.device)
 
-    def _matmul(self, x, proj: NVFP4Linear):
+    def _rows_form(self, tokens, proj):
+        return tokens <= self.FEW_TOKENS and proj.in_features % 512 == 0 and proj.out_features % 16 == 0
+
+    def _matmul(self, x, proj: NVFP4Linear, x_up=None):
+        """x W^T; with ``x_up`` the input is the SwiGLU of (x, x_up), formed on the way in by the
+        decode-batch form and by a separate kernel otherwise."""
         out = self._empty(x.shape[0], proj.out_features)
-        if x.shape[0] <= self.FEW_TOKENS and proj.in_features % 512 == 0 and proj.out_features % 16 == 0:
+        if self._rows_form(x.shape[0], proj):
             # a decode batch: weights decoded once on mma.sync with the tokens as columns; the f16
             # copy of the token rows is shared by the projections of the same input
             if self._rows_scratch is None:
                 self._rows_scratch = {}
             scratch, source = self._rows_scratch.get(proj.in_features, (None, None))
+            fresh = x_up is not None or source is not x      # a SwiGLU input is converted every time
             if scratch is None:
                 size = lib().qd_nvfp4_matmul_rows_scratch_bytes(proj.in_features)
                 scratch = torch.empty(size, dtype=torch.uint8, device=self.device)
-            call("qd_nvfp4_matmul_rows", ptr(x), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2),
+            call("qd_nvfp4_matmul_rows", ptr(x), ptr(x_up), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2),
                  ptr(out), x.shape[0], proj.out_features, proj.in_features, proj.group_size, ptr(scratch),
-                 int(source is not x), stream_of(x))
-            self._rows_scratch[proj.in_features] = (scratch, x)
+                 int(fresh), stream_of(x))
+            self._rows_scratch[proj.in_features] = (scratch, None if x_up is not None else x)
             return out
+        if x_up is not None:
+            x = self._swiglu(x, x_up)
         call("qd_nvfp4_matmul", ptr(x), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2),
              ptr(out), x.shape[0], proj.out_features, proj.in_features, proj.group_size, ptr(self.status),
              stream_of(x))
@@ -95,17 +103,19 @@ class ChunkPrefill:
         call("qd_swiglu", ptr(gate), ptr(up), ptr(out), gate.numel(), stream_of(gate))
         return out
 
-    def _grouped(self, x, bank: NVFP4Linear, order, boundaries, routes, topk, *, routing=None, by_token, scatter):
+    def _grouped(self, x, bank: NVFP4Linear, order, boundaries, routes, topk, *, routing=None, by_token, scatter, x_up=None):
         # rows of experts another rank owns stay zero in the scattered (route-order) output
         out = (torch.zeros if self.sliced and scatter else torch.empty)((routes, bank.out_features), dtype=BF16, device=self.device)
         experts = bank.weight.shape[0]
         if routes <= self.FEW_ROWS * (self.total_experts or experts) and bank.in_features in (512, 1024, 2048) and bank.out_features % 16 == 0:
             # few rows per expert: weights decoded once per 8 or 32 routes on mma.sync, no 128-token tiles
-            call("qd_nvfp4_expert_rows", ptr(x), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
+            call("qd_nvfp4_expert_rows", ptr(x), ptr(x_up), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
                  ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, experts, topk, bank.out_features,
                  bank.in_features, bank.group_size, int(by_token), int(scatter),
                  int(bank.weight_scale_2.numel() != 1), self.ROUTES_PER_PASS, stream_of(x))
             return out
+        if x_up is not None:
+            x = self._swiglu(x, x_up)
         call("qd_nvfp4_grouped_matmul", ptr(x), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
              ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, bank.weight.shape[0], topk,
              bank.out_features, bank.in_features, bank.group_size, int(by_token), int(scatter),
@@ -168,14 +178,12 @@ class ChunkPrefill:
             boundaries = boundaries[self.expert_range[0]:self.expert_range[1] + 1]
         gate = self._grouped(x, w.experts_gate, order, boundaries, routes, topk, by_token=True, scatter=False)
         up = self._grouped(x, w.experts_up, order, boundaries, routes, topk, by_token=True, scatter=False)
-        hidden = self._swiglu(gate, up)
-        contributions = self._grouped(hidden, w.experts_down, order, boundaries, routes, topk,
-                                      routing=weights.flatten(), by_token=False, scatter=True)
+        contributions = self._grouped(gate, w.experts_down, order, boundaries, routes, topk,
+                                      routing=weights.flatten(), by_token=False, scatter=True, x_up=up)
         if self.sliced:
             import torch.distributed as dist
             dist.all_reduce(contributions, group=self.group)
-        shared_hidden = self._swiglu(self._matmul(x, w.shared_gate), self._matmul(x, w.shared_up))
-        shared = self._matmul(shared_hidden, w.shared_down)
+        shared = self._matmul(self._matmul(x, w.shared_gate), w.shared_down, x_up=self._matmul(x, w.shared_up))
         out = torch.empty_like(x)
         call("qd_seq_moe_combine", ptr(contributions), ptr(ids), ptr(shared), ptr(strength), ptr(out), tokens,
              x.shape[1], topk, stream_of(x))

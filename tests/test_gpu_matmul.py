@@ -58,6 +58,12 @@ def test_few_rows_matmul_matches_oracle(cuda_device, tokens, out_features, in_fe
     for t in sorted({0, tokens // 2, tokens - 1}):
         row = O.nvfp4_gemv(x[t], proj)
         assert O.rel_l2(got[t], row) < 2e-3
+    # SwiGLU of two inputs formed on the way in: the same as the product of the explicit SwiGLU rows
+    gate, up = src.normal(f"g{tokens}", tokens, in_features), src.normal(f"u{tokens}", tokens, in_features)
+    hidden = (torch.nn.functional.silu(gate.float()).to(torch.bfloat16).float() * up.float()).to(torch.bfloat16)
+    fused, _ = kernels.matmul_rows(gate.to(cuda_device), to_device(proj, cuda_device), x_up=up.to(cuda_device))
+    plain, _ = kernels.matmul_rows(hidden.to(cuda_device), to_device(proj, cuda_device))
+    assert O.rel_l2(fused.cpu(), plain.cpu()) < 2e-3
 
 
 def test_two_dimensional_input_takes_the_matmul_path(cuda_device):
