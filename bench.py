@@ -96,13 +96,18 @@ def bytes_per_token(cfg, position: int) -> int:
 
 
 class ClockSampler:
-    """nvidia-smi SM clock / throttle-reason samples while a timed region runs."""
+    """nvidia-smi SM clock / throttle-reason samples while a timed region runs.  The process is
+    started ahead of the region (it needs some hundred milliseconds to come up, longer with eight
+    of them on one host); every sample carries its arrival time and `summary()` keeps those of the
+    marked window.  A region too short for two samples is followed by untimed replays of the same
+    step until there are three (`extended` then counts the samples taken after the region)."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.begin = self.end = None
 
     def __enter__(self):
         try:
@@ -118,7 +123,19 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def mark_begin(self):
+        self.begin = time.perf_counter()
+
+    def mark_end(self):
+        self.end = time.perf_counter()
+
+    def in_window(self, extended=False):
+        if self.begin is None:
+            return [r for _, r in self.rows]
+        stop = float("inf") if extended or self.end is None else self.end + 0.05
+        return [r for at, r in self.rows if self.begin <= at <= stop]
 
     def __exit__(self, *exc):
         if self.proc:
@@ -126,13 +143,15 @@ class ClockSampler:
             self.thread.join(timeout=2)
 
     def summary(self):
-        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        timed = self.in_window()
+        rows = timed if len(timed) >= 2 else self.in_window(extended=True)
+        sm = sorted(int(r[0]) for r in rows if r and r[0].isdigit())
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = sorted({n for r in self.rows if len(r) >= 6
+        reasons = sorted({n for r in rows if len(r) >= 6
                           for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
-        mx = max((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), default=None)
+        mx = max((int(r[1]) for r in rows if len(r) > 1 and r[1].isdigit()), default=None)
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons,
-                "samples": len(sm)}
+                "samples": len(sm), "extended": len(rows) - len(timed)}
 
 
 def dist_env():
@@ -484,17 +503,35 @@ def run_gpu(args):
             torch.cuda.synchronize(device)
 
     # ---- device-timed decode: graph replays with the token fed back on the device
+    clocks = ClockSampler(local).__enter__()          # ahead of the timed region: nvidia-smi takes a while to start
     for _ in range(args.warmup):
         engine.decode_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        e0.record()
-        for _ in range(args.steps):
-            engine.decode_step()
-        e1.record()
-        barrier()
+    clocks.mark_begin()
+    e0.record()
+    for _ in range(args.steps):
+        engine.decode_step()
+    e1.record()
+    barrier()
+    clocks.mark_end()
     device_ms = e0.elapsed_time(e1)
+    # a region too short for two clock samples: the same step, untimed, until there are three
+    more, extra = time.perf_counter(), 0
+    room = args.context - int(engine.state.position) - args.steps - 4      # the e2e leg below still needs its rows
+    while extra + 16 <= room:
+        need = len(clocks.in_window(extended=True)) < 3 and time.perf_counter() - more < 3.0 and clocks.proc is not None
+        if world > 1:       # every rank takes the same number of steps (they meet inside the step)
+            flag = torch.tensor([int(need)], device=device)
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MAX)
+            need = bool(flag.item())
+        if not need:
+            break
+        for _ in range(16):
+            engine.decode_step()
+        torch.cuda.synchronize(device)
+        extra += 16
+    clocks.__exit__()
     # ---- end to end through the engine's own API: the pending token comes from pinned host
     #      memory every step, the selected token is read back to the host every step
     token_host = torch.zeros((), dtype=torch.long).pin_memory()
