@@ -20,8 +20,7 @@
 // with routing weights the routed double rounding (quickdraw/models/qwen.py:44-53).
 #include <algorithm>
 
-#include "rowdot.cuh"
-#include "rowmma.cuh"
+#include "expert_rows.cuh"
 
 namespace qd {
 namespace {
@@ -41,23 +40,6 @@ template <int K, int NT> struct RowsShape {
     static constexpr int kBlocksPerSM = NT == 1 ? 2 : 1;
 };
 
-struct RowsParams {
-    const bf16* x; const bf16* x_up; const uint8_t* codes; const uint8_t* scales; const float* global;
-    const int32_t* order; const int32_t* boundaries; const float* routing; bf16* y;
-    int routes, experts, topk, out_features, by_token, scatter, global_per_expert;
-    long long codes_stride, scales_stride;
-};
-
-QD_DEVINL void cp16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-// 16-byte piece c of an input row sits at piece c ^ (bit 3 of c << 1): the four pieces a
-// quarter-warp reads at once (c = 4 t + q) then fall on different banks
-QD_DEVINL int x_piece(int c) { return c ^ ((c >> 2) & 2); }
-
-template <int K> constexpr int rows_code_row() { return K / 2 + 64; }      // padded row strides, bytes
-template <int K> constexpr int rows_scale_row() { return K / 16 + 16; }
-template <int K> constexpr int rows_x_row() { return 2 * K + 16; }
 template <int K, int NT> constexpr size_t rows_smem_bytes() {
     return (size_t)RowsShape<K, NT>::kTile * (rows_code_row<K>() + rows_scale_row<K>()) + (size_t)8 * NT * rows_x_row<K>();
 }
@@ -92,14 +74,14 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
     const uint8_t* scales = p.scales + (long long)e * p.scales_stride + (long long)r0 * (K / 16);
     for (int piece = tid; piece < rows * (K / 256); piece += kRowsThreads) {
         const int r = piece / (K / 256), c = piece % (K / 256);
-        cp16(w_scales + (size_t)r * scale_row + c * 16, scales + (size_t)r * (K / 16) + c * 16);
+        rows_cp16(w_scales + (size_t)r * scale_row + c * 16, scales + (size_t)r * (K / 16) + c * 16);
     }
     constexpr int half = K / 64;          // 16-byte pieces of a row's codes per half
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         for (int piece = tid; piece < rows * half; piece += kRowsThreads) {
             const int r = piece / half, c = h * half + piece % half;
-            cp16(w_codes + (size_t)r * code_row + c * 16, codes + (size_t)r * (K / 2) + c * 16);
+            rows_cp16(w_codes + (size_t)r * code_row + c * 16, codes + (size_t)r * (K / 2) + c * 16);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }

@@ -178,8 +178,10 @@ class ChunkPrefill:
             boundaries = boundaries[self.expert_range[0]:self.expert_range[1] + 1]
         gate = self._grouped(x, w.experts_gate, order, boundaries, routes, topk, by_token=True, scatter=False)
         up = self._grouped(x, w.experts_up, order, boundaries, routes, topk, by_token=True, scatter=False)
-        contributions = self._grouped(gate, w.experts_down, order, boundaries, routes, topk,
-                                      routing=weights.flatten(), by_token=False, scatter=True, x_up=up)
+        # SwiGLU as its own kernel here: fused into the down product, each of an expert's row tiles would redo
+        # it for the same rows (measured at 511 tokens: +30 us per layer against 13 us for the kernel)
+        contributions = self._grouped(self._swiglu(gate, up), w.experts_down, order, boundaries, routes, topk,
+                                      routing=weights.flatten(), by_token=False, scatter=True)
         if self.sliced:
             import torch.distributed as dist
             dist.all_reduce(contributions, group=self.group)

@@ -51,6 +51,7 @@ def test_chunked_prefill_matches_token_loop(cuda_device, chunk):
     (4, 2, 50, 2048, 512, -32),    # 32 routes per pass: 25 routes per expert in one pass
     (3, 2, 100, 1024, 144, -32),   # ... 67 routes per expert: three passes, the last one with three routes
     (40, 8, 3, 512, 2048, -32),    # ... most experts without a route
+    (300, 8, 40, 2048, 1024, 32),  # more experts than SMs
 ])
 def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tokens, width, rows, few_rows):
     """The grouped product of the routed experts (tcgen05 tiles, or the mma.sync form for few
@@ -75,8 +76,9 @@ def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tok
         helper.FEW_ROWS = 10 ** 6
     routes = tokens * topk
     plain = helper._grouped(x, bank, order.to(torch.int32), boundaries, routes, topk, by_token=True, scatter=False)
-    routed = helper._grouped(x.repeat_interleave(topk, 0)[order].contiguous(), bank, order.to(torch.int32), boundaries,
-                             routes, topk, routing=weights.flatten(), by_token=False, scatter=True)
+    sorted_rows = x.repeat_interleave(topk, 0)[order].contiguous()
+    routed = helper._grouped(sorted_rows, bank, order.to(torch.int32), boundaries, routes, topk, routing=weights.flatten(),
+                             by_token=False, scatter=True)
     assert int(helper.status.item()) == 0
     for r in range(routes):
         route = int(order[r])
@@ -85,6 +87,12 @@ def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tok
         torch.testing.assert_close(plain[r].float(), want.float(), rtol=0.025, atol=0.003)
         want_routed = kernels.expert_gemv(x[token], bank, ids.flatten()[route:route + 1], weights.flatten()[route:route + 1])[0]
         torch.testing.assert_close(routed[route].float(), want_routed.float(), rtol=0.025, atol=0.003)
+    # SwiGLU of two inputs formed on the way in (either form; the tcgen05 form runs the SwiGLU kernel first)
+    up = src.normal("up", routes, width).to(cuda_device)
+    hidden = (torch.nn.functional.silu(sorted_rows.float()).to(torch.bfloat16).float() * up.float()).to(torch.bfloat16)
+    fused = helper._grouped(sorted_rows, bank, order.to(torch.int32), boundaries, routes, topk, by_token=False, scatter=True, x_up=up)
+    explicit = helper._grouped(hidden, bank, order.to(torch.int32), boundaries, routes, topk, by_token=False, scatter=True)
+    assert O.rel_l2(fused.cpu(), explicit.cpu()) < 2e-3
 
 
 @pytest.mark.parametrize("key_dim,value_dim,tokens", [(128, 128, 37), (128, 128, 3), (128, 96, 16), (64, 64, 21)])
