@@ -95,6 +95,30 @@ def bytes_per_token(cfg, position: int) -> int:
             + cfg.vocab_size * h * 2 + norms + h * 2)
 
 
+def bytes_per_batch_step(cfg, batch: int, context: int) -> int:
+    """Algorithmic HBM bytes of one batched decode step: every weight once (of the routed experts the
+    expected number of distinct ones that `batch` tokens with top-k routing touch), every
+    sequence's recurrent / convolution state read and written and its KV history read."""
+    h, inter = cfg.hidden_size, cfg.moe_intermediate_size
+    fp4 = lambda out, inp: out * inp // 2 + out * inp // 16 + 4
+    expert = 2 * fp4(inter, h) + fp4(h, inter)
+    distinct = cfg.num_experts * (1.0 - (1.0 - cfg.num_experts_per_tok / cfg.num_experts) ** batch)
+    moe = cfg.num_experts * h * 2 + h * 2 + (distinct + 1) * expert
+    kw = cfg.linear_num_key_heads * cfg.linear_key_head_dim
+    vw = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+    gdn_w = fp4(2 * kw + vw, h) + fp4(vw, h) + fp4(h, vw) + 2 * cfg.linear_num_value_heads * h * 2 \
+        + (2 * kw + vw) * cfg.linear_conv_kernel_dim * 2
+    rec = cfg.linear_num_value_heads * cfg.linear_key_head_dim * cfg.linear_value_head_dim * 4
+    conv = (2 * kw + vw) * (cfg.linear_conv_kernel_dim - 1) * 2
+    qw, kvw = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    attn_w = fp4(2 * qw, h) + 2 * fp4(kvw, h) + fp4(h, qw)
+    kv = 2 * kvw * 2 * (context + 1)
+    n_full = cfg.layer_types.count("full_attention")
+    n_lin = cfg.num_hidden_layers - n_full
+    return int(cfg.num_hidden_layers * moe + n_lin * (gdn_w + batch * 2 * (rec + conv)) + n_full * (attn_w + batch * kv)
+               + cfg.vocab_size * h * 2)
+
+
 class ClockSampler:
     """nvidia-smi SM clock / throttle-reason samples while a timed region runs.  The process is
     started ahead of the region (it needs some hundred milliseconds to come up, longer with eight
@@ -458,7 +482,11 @@ def batch_decode_leg(ckpt, cfg, device, batch=32, context=8192, steps=8, warmup=
         worst = torch.tensor([ms], device=device)
         torch.distributed.all_reduce(worst, op=torch.distributed.ReduceOp.MAX, group=group)
         ms = float(worst.item())
+    step_bytes = bytes_per_batch_step(cfg, batch, context)
+    peak, _ = measured_peaks()
     return {"batch": batch, "context": context, "steps": steps, "ms_per_step": ms, "tok_s": batch / (ms * 1e-3),
+            "bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms * 1e-3) / 1e9,
+            "frac_of_measured_hbm": (step_bytes / (ms * 1e-3) / 1e9 / peak) if not slices else None,
             "state_bytes": state.memory_bytes(), "path": "one CUDA graph per step: tensor-core products with %d rows + batched state kernels" % batch
             + (", routed experts and LM head split over the ranks" if slices else "")}
 
