@@ -41,6 +41,56 @@ __global__ void seq_add_norm_kernel(const bf16* __restrict__ x, const bf16* __re
     }
 }
 
+// The same with 16-byte accesses and the row kept in registers between the two passes (widths that
+// are a multiple of 8, up to 4096; the sum of squares is taken in another order than above).
+constexpr int kNormVecs = 2;            // 16-byte pieces per thread: 256 threads x 2 x 8 values
+__global__ void __launch_bounds__(256)
+seq_add_norm8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, const float* __restrict__ gamma,
+                     bf16* __restrict__ normed, bf16* __restrict__ residual_out, int width, float eps) {
+    __shared__ float partial[8];
+    const size_t base = (size_t)blockIdx.x * width;
+    const int tid = threadIdx.x, pieces = width / 8;
+    float v[kNormVecs][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kNormVecs; ++k) {
+        const int c = tid + k * 256;
+        if (c >= pieces) break;
+        const uint4 a = *reinterpret_cast<const uint4*>(x + base + 8 * c);
+        uint4 r = make_uint4(0u, 0u, 0u, 0u);
+        if (residual) r = *reinterpret_cast<const uint4*>(residual + base + 8 * c);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            v[k][2 * q] = __uint_as_float(aw[q] << 16) + __uint_as_float(rw[q] << 16);
+            v[k][2 * q + 1] = __uint_as_float(aw[q] & 0xffff0000u) + __uint_as_float(rw[q] & 0xffff0000u);
+            ss += v[k][2 * q] * v[k][2 * q] + v[k][2 * q + 1] * v[k][2 * q + 1];
+        }
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) partial[tid >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += partial[w];
+    const float inv = rsqrtf(total / (float)width + eps);
+#pragma unroll
+    for (int k = 0; k < kNormVecs; ++k) {
+        const int c = tid + k * 256;
+        if (c >= pieces) break;
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + 8 * c), g1 = *reinterpret_cast<const float4*>(gamma + 8 * c + 4);
+        const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        uint32_t n[4], o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            n[q] = qd::pack_bf16x2((v[k][2 * q] * inv) * gm[2 * q], (v[k][2 * q + 1] * inv) * gm[2 * q + 1]);
+            o[q] = qd::pack_bf16x2(v[k][2 * q], v[k][2 * q + 1]);
+        }
+        *reinterpret_cast<uint4*>(normed + base + 8 * c) = make_uint4(n[0], n[1], n[2], n[3]);
+        *reinterpret_cast<uint4*>(residual_out + base + 8 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 // --------------------------------------------------- small bf16 projection of every token
 // y[t, n] = bf16( sum_k x[t, k] w[n, k] ): one warp per (token, output row), 16-byte loads where
 // the width allows them.
@@ -1108,8 +1158,13 @@ seq_combine_kernel(const bf16* __restrict__ contributions, const int32_t* __rest
 extern "C" int qd_seq_add_rms_norm(const void* x, const void* residual, const float* gamma, void* normed,
                                    void* residual_out, int tokens, int width, float eps, void* stream) {
     QD_CHECK_ARG(x && gamma && normed && residual_out && tokens > 0 && width > 0);
-    seq_add_norm_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)residual, gamma,
-                                                                  (bf16*)normed, (bf16*)residual_out, width, eps);
+    const uintptr_t align = (uintptr_t)x | (uintptr_t)residual | (uintptr_t)gamma | (uintptr_t)normed | (uintptr_t)residual_out;
+    if (width % 8 == 0 && width <= 8 * 256 * kNormVecs && !(align & 15u))
+        seq_add_norm8_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)residual, gamma,
+                                                                       (bf16*)normed, (bf16*)residual_out, width, eps);
+    else
+        seq_add_norm_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)residual, gamma,
+                                                                      (bf16*)normed, (bf16*)residual_out, width, eps);
     return qd_launch_status();
 }
 
