@@ -235,6 +235,14 @@ int qd_bf16_gemv(const void* x, const void* w, void* y, int rows, int width, voi
 /* fp8_gemv(x, proj) — quickdraw/kernel/triton/matvec.py:102-115, qwen.py:25-33. */
 int qd_fp8_gemv(const void* x, const void* w, const float* w_scale, const float* in_scale, void* y,
                 int rows, int width, int is_fp32, void* stream);
+/* The same projection for a chunk of tokens or a decode batch (no counterpart in the reference, whose
+ * prompt chunks go through fp8_gemv row by row): activations quantised once to E4M3 bytes
+ * (q_scratch: tokens * in_features bytes, 16-byte aligned; convert = 0 reuses what the previous call
+ * left there, for projections that share input and input scale), E4M3 x E4M3 products on
+ * mma.sync.m16n8k32, fp32 sum, y = bf16((sum * in_scale) * w_scale).  in_features % 128 == 0,
+ * out_features even, else QD_ERR_UNSUPPORTED. */
+int qd_fp8_matmul(const void* x, const void* w, const float* w_scale, const float* in_scale, void* y,
+                  int tokens, int out_features, int in_features, void* q_scratch, int convert, void* stream);
 
 /* route(logits, topk) -> (int32 ids, fp32 weights) — quickdraw/kernel/cute/moe.py:87-98,
  * quickdraw/kernel/triton/moe.py:11-30, qwen.py:174-177.  experts <= 1024, topk <= 32. */

@@ -26,6 +26,7 @@ SIGNATURES = {
     "qd_nvfp4_dequantize": [P, P, F, P, L, I, I, I, P],
     "qd_bf16_gemv": [P, P, P, I, I, P],
     "qd_fp8_gemv": [P, P, P, P, P, I, I, I, P],
+    "qd_fp8_matmul": [P, P, P, P, P, I, I, I, P, I, P],
     "qd_route_topk": [P, I, I, I, P, P, P],
     "qd_moe_combine": [P, P, P, P, P, I, I, P],
     "qd_swiglu": [P, P, P, I, P],

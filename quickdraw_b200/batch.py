@@ -136,7 +136,8 @@ class BatchDecode(ChunkPrefill):
             normed, residual = self._add_norm(mixed, residual, gamma_post, c.rms_norm_eps)
             x = self._moe(layer.moe, normed)
         final, _ = self._add_norm(x, residual, self.final_gamma, c.rms_norm_eps)
-        logits = self._small(final, self.ckpt.lm_head)
+        head = self.ckpt.lm_head
+        logits = self._small(final, head) if isinstance(head, torch.Tensor) else self._matmul(final, head)   # bf16 / NVFP4 head
         if self.vocab_range is not None and logits.shape[1] != c.vocab_size:
             import torch.distributed as dist
             world = dist.get_world_size(self.group)

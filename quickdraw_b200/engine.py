@@ -78,8 +78,8 @@ class Engine:
             if kernels is None and fused.supports(ckpt):
                 self.fused = fused.FusedStep(ckpt)
                 self.step = self.fused
-                if sequence_prefill and all(fused.mixer_format(layer) == "nvfp4" for layer in ckpt.layers):
-                    from .prefill import ChunkPrefill     # (FP8 mixers: the prompt goes token by token)
+                if sequence_prefill and all(fused.mixer_format(layer) in ("nvfp4", "fp8") for layer in ckpt.layers):
+                    from .prefill import ChunkPrefill     # NVFP4 or static-FP8 mixers; the last token goes through the step
                     self.chunk_prefill = ChunkPrefill(ckpt)
                     self.sequence_prefill = True
             else:

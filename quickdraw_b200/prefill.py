@@ -18,7 +18,7 @@ from __future__ import annotations
 import torch
 
 from ._lib import call, lib, ptr, stream_of
-from .weights import Checkpoint, NVFP4Linear
+from .weights import Checkpoint, FP8Linear, NVFP4Linear
 
 BF16 = torch.bfloat16
 
@@ -33,6 +33,7 @@ class ChunkPrefill:
     sliced, group, expert_range = False, None, None      # defaults of a whole model on one GPU
     total_experts = None                                  # experts of the whole model (None: the bank's own count)
     _rows_scratch = None
+    _fp8_rows = None
     CHUNKED_FROM = 64                                     # tokens from which the DeltaNet recurrence takes the chunked form
     FEW_TOKENS = 32                                       # token rows up to which a dense product takes the mma.sync form
     ROUTES_PER_PASS = 0                                   # 8 / 32 routes per decoding of a weight tile; 0: the library chooses
@@ -64,6 +65,19 @@ class ChunkPrefill:
         """x W^T; with ``x_up`` the input is the SwiGLU of (x, x_up), formed on the way in by the
         decode-batch form and by a separate kernel otherwise."""
         out = self._empty(x.shape[0], proj.out_features)
+        if isinstance(proj, FP8Linear):
+            # a static-FP8 mixer projection: the rows are quantised once per input and input scale
+            if x_up is not None:
+                x = self._swiglu(x, x_up)
+            scratch, source, scale = self._fp8_rows or (None, None, None)
+            if scratch is None or scratch.numel() < x.numel():
+                scratch = torch.empty(x.numel(), dtype=torch.uint8, device=self.device)
+                source = None
+            fresh = source is not x or scale != proj.input_scale.data_ptr()      # (no host read of the scale: capturable)
+            call("qd_fp8_matmul", ptr(x), ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.input_scale), ptr(out),
+                 x.shape[0], proj.out_features, proj.in_features, ptr(scratch), int(fresh), stream_of(x))
+            self._fp8_rows = (scratch, x, proj.input_scale.data_ptr())
+            return out
         if self._rows_form(x.shape[0], proj):
             # a decode batch: weights decoded once on mma.sync with the tokens as columns; the f16
             # copy of the token rows is shared by the projections of the same input

@@ -208,3 +208,28 @@ def test_batch_attention_forms_against_the_single_sequence_kernel(cuda_device, h
             assert O.rel_l2(out_b[i].float().cpu(), want[i].float().cpu()) < 1e-2, (splits, i)
             n = int(positions[i]) + 1
             assert O.rel_l2(kb[i, :n].float().cpu(), ks[i, :n].float().cpu()) < 1e-3 and torch.equal(vb[i, :n], vs[i, :n])
+
+
+def test_batch_decode_with_the_published_checkpoint_formats(cuda_device):
+    """FP8 mixers and an NVFP4 LM head in the batched step (E4M3 x E4M3 product, NVFP4 rows form):
+    the first step of two sequences from empty state against the single-sequence step (one step:
+    E4M3 rounding steps and router ties do not propagate)."""
+    from quickdraw_b200.batch import BatchDecode, BatchState
+    from quickdraw_b200.fused import FusedStep
+    from quickdraw_b200.state import DecodeState
+    cfg = synthetic.model_config(num_layers=2, vocab_size=2048, experts=16, topk=8, interval=2)     # one DeltaNet, one attention layer
+    ckpt = synthetic.make_checkpoint(cfg, seed=21, device="cuda", fp8_mixers=True, nvfp4_head=True)
+    single, batched = FusedStep(ckpt), BatchDecode(ckpt)
+    state = BatchState(cfg, 2, 16, "cuda")
+    tokens = torch.tensor([17, 1200], device="cuda")
+    picked, logits = batched.step(tokens, state)
+    assert batched.check() == 0
+    for b in range(2):
+        ref = DecodeState.allocate(cfg, 16, "cuda")
+        for t in (ref.kv_k, ref.kv_v, ref.rec_state, ref.conv_state):
+            t.zero_()
+        want = single(ckpt, tokens[b], 0, ref)
+        assert O.rel_l2(logits[b].float().cpu(), want.float().cpu()) < 5e-2, b
+        seq = state.sequence(b)
+        assert O.rel_l2(seq.rec_state.cpu(), ref.rec_state.cpu()) < 1e-2 and O.rel_l2(seq.conv_state.cpu(), ref.conv_state.cpu()) < 1e-3
+    assert single.status() == 0

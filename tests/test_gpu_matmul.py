@@ -66,6 +66,36 @@ def test_few_rows_matmul_matches_oracle(cuda_device, tokens, out_features, in_fe
     assert O.rel_l2(fused.cpu(), plain.cpu()) < 2e-3
 
 
+@pytest.mark.parametrize("tokens,out_features,in_features", [(1, 2, 128), (37, 514, 2048), (128, 128, 256), (300, 2048, 4096)])
+def test_fp8_matmul_matches_row_by_row_oracle(cuda_device, tokens, out_features, in_features):
+    """The static-FP8 projection of a chunk (E4M3 x E4M3 on mma.sync, ragged tiles on both sides)
+    against the oracle's fp8_gemv row by row; activations beyond the E4M3 range saturate."""
+    from quickdraw_b200._lib import call, ptr, stream_of
+    from quickdraw_b200.weights import FP8Linear
+    gen = torch.Generator().manual_seed(33)
+    w = (torch.randn(out_features, in_features, generator=gen) * 64).clamp(-448, 448).to(torch.float8_e4m3fn)
+    proj = FP8Linear(w, torch.tensor(0.1 / 64), torch.tensor(4.0 / 448))
+    x = (torch.randn(tokens, in_features, generator=gen) * 1.5).to(torch.bfloat16)
+    x[0, :3] = torch.tensor([9.0, -30.0, 4.0])          # saturate at +-448 input-scale units
+    dev = cuda_device
+    xd, wd = x.to(dev), w.to(dev)
+    ws, xs = proj.weight_scale.to(dev), proj.input_scale.to(dev)
+    y = torch.empty(tokens, out_features, dtype=torch.bfloat16, device=dev)
+    scratch = torch.empty(tokens * in_features, dtype=torch.uint8, device=dev)
+    call("qd_fp8_matmul", ptr(xd), ptr(wd), ptr(ws), ptr(xs), ptr(y), tokens, out_features, in_features, ptr(scratch), 1,
+         stream_of(xd))
+    again = torch.empty_like(y)
+    call("qd_fp8_matmul", ptr(xd), ptr(wd), ptr(ws), ptr(xs), ptr(again), tokens, out_features, in_features, ptr(scratch), 0,
+         stream_of(xd))
+    torch.cuda.synchronize()
+    want_q, _ = O.quantize_fp8(x, proj.input_scale)
+    assert torch.equal(scratch.view(tokens, in_features).cpu(), want_q.view(torch.uint8))
+    assert torch.equal(y, again)
+    for t in sorted({0, tokens // 2, tokens - 1}):
+        row = O.fp8_gemv(x[t], proj)
+        assert O.rel_l2(y[t].cpu(), row) < 2e-3, t
+
+
 def test_two_dimensional_input_takes_the_matmul_path(cuda_device):
     from quickdraw_b200 import kernels
     src = synthetic.Source(22, "cpu")

@@ -13,12 +13,14 @@ from quickdraw_b200.state import DecodeState
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("chunk", [5, 16, 39])
-def test_chunked_prefill_matches_token_loop(cuda_device, chunk):
+@pytest.mark.parametrize("chunk,fp8_mixers", [(5, False), (16, False), (39, False), (16, True), (39, True)])
+def test_chunked_prefill_matches_token_loop(cuda_device, chunk, fp8_mixers):
+    """NVFP4 mixers, and the published checkpoint's static-FP8 mixers (the chunk takes them through
+    the E4M3 x E4M3 product, the token loop quantises the vector in the step's phase prologue)."""
     from quickdraw_b200.fused import FusedStep
     from quickdraw_b200.prefill import ChunkPrefill
     cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
-    ckpt = synthetic.make_checkpoint(cfg, seed=11, device="cuda")
+    ckpt = synthetic.make_checkpoint(cfg, seed=11, device="cuda", fp8_mixers=fp8_mixers)
     step, prefill = FusedStep(ckpt), ChunkPrefill(ckpt)
     gen = torch.Generator().manual_seed(2)
     prompt = torch.randint(0, cfg.vocab_size, (40,), generator=gen).to("cuda")
@@ -33,11 +35,51 @@ def test_chunked_prefill_matches_token_loop(cuda_device, chunk):
         prefill.run(prompt[start:stop], start, chunk_state)
     got = step(ckpt, prompt[39], 39, chunk_state)
     assert prefill.check() == 0 and step.status() == 0
+    if fp8_mixers:
+        # E4M3 activations turn last-bit differences of a layer's output into 6 % steps of single inputs of
+        # the next, and a router near-tie that falls the other way into a different expert: the first layer
+        # agrees to rounding, the whole model only loosely (the blocks are compared one by one below)
+        assert O.rel_l2(chunk_state.conv_state[0].cpu(), loop_state.conv_state[0].cpu()) < 1e-3
+        assert O.rel_l2(chunk_state.rec_state[0].cpu(), loop_state.rec_state[0].cpu()) < 1e-3
+        assert O.rel_l2(chunk_state.kv_k[:, :40].cpu(), loop_state.kv_k[:, :40].cpu()) < 0.35
+        assert O.rel_l2(got.cpu(), want.cpu()) < 0.35
+        return
     assert O.rel_l2(chunk_state.conv_state.cpu(), loop_state.conv_state.cpu()) < 2e-2
     assert O.rel_l2(chunk_state.rec_state.cpu(), loop_state.rec_state.cpu()) < 2e-2
     assert O.rel_l2(chunk_state.kv_k[:, :40].cpu(), loop_state.kv_k[:, :40].cpu()) < 2e-2
     assert O.rel_l2(chunk_state.kv_v[:, :40].cpu(), loop_state.kv_v[:, :40].cpu()) < 2e-2
     assert O.rel_l2(got.cpu(), want.cpu()) < 5e-2
+
+
+def test_fp8_mixer_blocks_of_a_chunk_match_the_oracle(cuda_device):
+    """Static-FP8 mixers in the chunk forms, block by block on the same inputs (no propagation through
+    E4M3 rounding steps and router ties): a DeltaNet block and an attention block over 20 tokens
+    against the oracle's single-token blocks walked over the tokens."""
+    from quickdraw_b200.prefill import ChunkPrefill
+    from quickdraw_b200.synthetic import to_device
+    cfg = synthetic.model_config(num_layers=4, vocab_size=2048, experts=16, topk=8)
+    ckpt = synthetic.make_checkpoint(cfg, seed=11, device="cuda", fp8_mixers=True)
+    cpu = to_device(ckpt, "cpu")
+    prefill = ChunkPrefill(ckpt)
+    tokens = 20
+    x = synthetic.Source(3, "cpu").normal("x", tokens, cfg.hidden_size)
+    state, ref = DecodeState.allocate(cfg, 32, "cuda"), DecodeState.allocate(cfg, 32, "cpu")
+    for s in (state, ref):
+        for t in (s.kv_k, s.kv_v, s.rec_state, s.conv_state):
+            t.zero_()
+    got = prefill._delta_net(ckpt.layers[0].attn, x.to("cuda"), state, 0).cpu()
+    for t in range(tokens):
+        want = O.gated_delta_net_block(cpu.layers[0].attn, x[t], ref.rec_state[0], ref.conv_state[0], t, config=cfg)
+        assert O.rel_l2(got[t], want) < 1e-2, t
+    assert O.rel_l2(state.rec_state[0].cpu(), ref.rec_state[0]) < 1e-2
+    assert O.rel_l2(state.conv_state[0].cpu(), ref.conv_state[0]) < 1e-3
+    attention = next(layer for layer in ckpt.layers if layer.layer_type == "full_attention")
+    got = prefill._attention(attention.attn, x.to("cuda"), state, 0, 0).cpu()
+    for t in range(tokens):
+        want = O.full_attention_block(cpu.layers[attention.idx].attn, x[t], (ref.kv_k[0], ref.kv_v[0]), t, config=cfg)
+        assert O.rel_l2(got[t], want) < 1e-2, t
+    assert O.rel_l2(state.kv_k[0, :tokens].cpu(), ref.kv_k[0, :tokens]) < 1e-3
+    assert prefill.check() == 0
 
 
 @pytest.mark.parametrize("experts,topk,tokens,width,rows,few_rows", [

@@ -404,9 +404,9 @@ def test_static_fp8_mixers_in_the_one_launch_step(cuda_device):
     assert O.rel_l2(state.rec_state.cpu(), ref.rec_state) < 5e-2
     assert O.rel_l2(state.conv_state.cpu(), ref.conv_state) < 5e-2
     assert O.rel_l2(state.kv_k[:, :5].cpu(), ref.kv_k[:, :5]) < 5e-2
-    # the engine takes the one-launch step for such a model (prompt token by token) and generates
+    # the engine takes the one-launch step for such a model (the prompt in chunks through the FP8 product) and generates
     engine = Engine(ckpt, max_context=32, device="cuda")
-    assert engine.fused is not None and not engine.sequence_prefill
+    assert engine.fused is not None and engine.sequence_prefill
     engine.state.kv_k.zero_()
     engine.state.kv_v.zero_()
     assert len(engine.generate([7, 1500, 3], 6)) == 6
