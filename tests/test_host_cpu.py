@@ -180,3 +180,24 @@ def test_reuse_survives_a_reset_when_the_cache_rows_are_intact():
     step.calls.clear()
     engine.prefill_reuse([5, 6, 7, 8])
     assert engine.reused_tokens == 3 and step.calls == [(8, 3)]
+
+
+def test_bench_byte_counts_of_a_step_and_of_a_batched_step():
+    """The algorithmic bytes bench.py divides by: one sequence of the batched count is the single-token
+    count (up to the norm vectors and the embedding row), more sequences add their own state and KV
+    history and touch more distinct experts, never more than all of them."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench", Path(__file__).resolve().parents[1] / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    cfg = synthetic.model_config()
+    one, single = bench.bytes_per_batch_step(cfg, 1, 639), bench.bytes_per_token(cfg, 639)
+    assert abs(one - single) < 1e-3 * single
+    small, large = bench.bytes_per_batch_step(cfg, 32, 8192), bench.bytes_per_batch_step(cfg, 64, 8192)
+    assert one < small < large
+    # 32 more sequences: their state and KV history, and fewer than 32 x 8 more experts per layer
+    h, inter = cfg.hidden_size, cfg.moe_intermediate_size
+    expert = 3 * (inter * h // 2 + inter * h // 16 + 4)
+    per_sequence = (large - small) / 32
+    state = 36 * 2 * (32 * 128 * 128 * 4 + 8192 * 3 * 2) + 12 * 2 * 2 * 256 * 2 * 8193
+    assert state < per_sequence < state + cfg.num_hidden_layers * 8 * expert
