@@ -129,7 +129,7 @@ __global__ void seq_bf16_matmul_kernel(const bf16* __restrict__ x, const bf16* _
 constexpr int kTallTokens = 32, kTallMaxWidth = 3072, kTallUnroll = 2, kTallWarps = 16;
 __global__ void __launch_bounds__(kTallWarps * 32, 1)
 seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
-                            int tokens, int rows, int width, int groups_per_block) {
+                            int tokens, int rows, int width, int groups_per_block, int input_parts) {
     extern __shared__ __align__(16) unsigned char tall_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int t0 = blockIdx.y * kTallTokens, nt_rows = min(kTallTokens, tokens - t0);
@@ -151,23 +151,17 @@ seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__
     __syncthreads();
     const unsigned char* xs = tall_smem + (size_t)g * x_row + t * 32;
     const int steps = width / 64;
-    // few rows: only the first groups_per_block warps multiply (more blocks share the rows)
-    for (int n0 = warp < groups_per_block ? (blockIdx.x * groups_per_block + warp) * 16 : rows; n0 < rows;
-         n0 += gridDim.x * groups_per_block * 16) {
+    // sixteen weight rows (n0 ..) against the tile's tokens over steps [s_begin, s_end) of 64 inputs
+    auto rows_times_tokens = [&](int n0, int s_begin, int s_end, float (&acc)[4][4]) {
         // rows past the matrix read its last row and store nothing
         const uint4* lo = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + g, rows - 1) * width + t * 16);
         const uint4* hi = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + g + 8, rows - 1) * width + t * 16);
-        float acc[4][4];
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
         // two register buffers of kTallUnroll steps: the loads of one are in flight while the
         // other is multiplied (the warps of a block run in step, so nothing else would hide them)
         auto load = [&](uint4 (&a)[kTallUnroll][4], int s0) {
 #pragma unroll
             for (int u = 0; u < kTallUnroll; ++u) {
-                const int s = min(s0 + u, steps - 1);
+                const int s = min(s0 + u, s_end - 1);
                 a[u][0] = __ldg(lo + s * 8); a[u][1] = __ldg(lo + s * 8 + 1);
                 a[u][2] = __ldg(hi + s * 8); a[u][3] = __ldg(hi + s * 8 + 1);
             }
@@ -175,7 +169,7 @@ seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__
         auto multiply = [&](const uint4 (&a)[kTallUnroll][4], int s0) {
 #pragma unroll
             for (int u = 0; u < kTallUnroll; ++u) {
-                if (s0 + u >= steps) break;
+                if (s0 + u >= s_end) break;
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
                     const unsigned char* src = xs + (size_t)nt * 8 * x_row + (s0 + u) * 128;
@@ -188,15 +182,17 @@ seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__
             }
         };
         uint4 even[kTallUnroll][4], odd[kTallUnroll][4];
-        load(even, 0);
+        load(even, s_begin);
 #pragma unroll 1
-        for (int s0 = 0; s0 < steps; s0 += 2 * kTallUnroll) {
-            if (s0 + kTallUnroll < steps) load(odd, s0 + kTallUnroll);
+        for (int s0 = s_begin; s0 < s_end; s0 += 2 * kTallUnroll) {
+            if (s0 + kTallUnroll < s_end) load(odd, s0 + kTallUnroll);
             multiply(even, s0);
-            if (s0 + 2 * kTallUnroll < steps) load(even, s0 + 2 * kTallUnroll);
-            if (s0 + kTallUnroll < steps) multiply(odd, s0 + kTallUnroll);
+            if (s0 + 2 * kTallUnroll < s_end) load(even, s0 + 2 * kTallUnroll);
+            if (s0 + kTallUnroll < s_end) multiply(odd, s0 + kTallUnroll);
         }
-        // acc[nt][0..1] = row n0 + g, tokens 8 nt + 2 t and + 1; [2..3] = row n0 + g + 8
+    };
+    // acc[nt][0..1] = row n0 + g, tokens 8 nt + 2 t and + 1; [2..3] = row n0 + g + 8
+    auto store = [&](int n0, const float (&acc)[4][4]) {
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -204,6 +200,47 @@ seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__
                 const int token = 8 * nt + 2 * t + (c & 1), row = n0 + g + 8 * (c >> 1);
                 if (token < nt_rows && row < rows) y[(size_t)(t0 + token) * rows + row] = __float2bfloat16_rn(acc[nt][c]);
             }
+    };
+    if (input_parts > 1) {
+        // few rows (one pass per block): the warps beyond the row groups take parts of the inputs, the parts'
+        // sums meet in shared memory behind the tokens and are added in order
+        const int slot = warp % groups_per_block, part = warp / groups_per_block;
+        const int n0 = (blockIdx.x * groups_per_block + slot) * 16;
+        const bool active = n0 < rows && part < input_parts;
+        float acc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
+        if (active) rows_times_tokens(n0, part * steps / input_parts, (part + 1) * steps / input_parts, acc);
+        float4* meet = reinterpret_cast<float4*>(tall_smem + (size_t)kTallTokens * x_row);     // [part - 1][slot][nt][lane]
+        if (active && part > 0) {
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+                meet[(((part - 1) * groups_per_block + slot) * 4 + nt) * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+        }
+        __syncthreads();
+        if (active && part == 0) {
+            for (int other = 1; other < input_parts; ++other)
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const float4 v = meet[(((other - 1) * groups_per_block + slot) * 4 + nt) * 32 + lane];
+                    acc[nt][0] += v.x; acc[nt][1] += v.y; acc[nt][2] += v.z; acc[nt][3] += v.w;
+                }
+            store(n0, acc);
+        }
+        return;
+    }
+    // many rows: only the first groups_per_block warps multiply (more blocks share the rows)
+    for (int n0 = warp < groups_per_block ? (blockIdx.x * groups_per_block + warp) * 16 : rows; n0 < rows;
+         n0 += gridDim.x * groups_per_block * 16) {
+        float acc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
+        rows_times_tokens(n0, 0, steps, acc);
+        store(n0, acc);
     }
 }
 
@@ -1184,13 +1221,25 @@ extern "C" int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tok
         }
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        // sixteen row groups per block, fewer while the blocks do not fill the GPU
+        // sixteen row groups per block, fewer while the blocks do not fill the GPU; then the idle warps take
+        // parts of the inputs (a power of two that divides the steps of 64 inputs), if the sums fit behind the tokens
         const int row_groups = (rows + 15) / 16, token_tiles = (tokens + 31) / 32;
         int per_block = kTallWarps;
-        while (per_block > 2 && (long long)((row_groups + per_block - 1) / per_block) * token_tiles < sms) per_block >>= 1;
+        while (per_block > 1 && (long long)((row_groups + per_block - 1) / per_block) * token_tiles < sms &&
+               (per_block > 2 || row_groups == 1)) per_block >>= 1;
         const int row_blocks = (row_groups + per_block - 1) / per_block;
-        seq_bf16_matmul_tall_kernel<<<dim3(row_blocks < sms ? row_blocks : sms, token_tiles), kTallWarps * 32, smem, (cudaStream_t)stream>>>(
-            (const bf16*)x, (const bf16*)w, (bf16*)y, tokens, rows, width, per_block);
+        int parts = 1;
+        if (row_blocks <= sms && per_block < kTallWarps) {
+            parts = kTallWarps / per_block;
+            while (parts > 1 && (width / 64) % parts != 0) parts >>= 1;
+        }
+        size_t launch_smem = smem;
+        if (parts > 1) {
+            launch_smem += (size_t)(parts - 1) * per_block * 4 * 32 * 16;
+            if (launch_smem > (size_t)kTallTokens * (kTallMaxWidth * 2 + 16)) { parts = 1; launch_smem = smem; }
+        }
+        seq_bf16_matmul_tall_kernel<<<dim3(row_blocks < sms ? row_blocks : sms, token_tiles), kTallWarps * 32, launch_smem, (cudaStream_t)stream>>>(
+            (const bf16*)x, (const bf16*)w, (bf16*)y, tokens, rows, width, per_block, parts);
         return qd_launch_status();
     }
     seq_bf16_matmul_kernel<<<dim3((rows + 7) / 8, tokens), 256, 0, (cudaStream_t)stream>>>(

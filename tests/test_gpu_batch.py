@@ -88,7 +88,7 @@ def test_batched_state_kernels_equal_single_sequence_kernels(cuda_device):
 def test_tall_projection_equals_row_by_row(cuda_device):
     from quickdraw_b200._lib import call, ptr, stream_of
     src = synthetic.Source(29, cuda_device)
-    for tokens, rows, width in ((5, 4100, 2048), (33, 4096, 512), (32, 4112, 320)):
+    for tokens, rows, width in ((5, 4100, 2048), (33, 4096, 512), (32, 4112, 320), (200, 1, 2048), (130, 32, 2048), (64, 256, 2048), (70, 40, 192)):
         x, w = src.normal(f"x{tokens}", tokens, width), src.normal(f"w{rows}", rows, width, std=0.05)
         y = torch.empty(tokens, rows, dtype=torch.bfloat16, device=cuda_device)
         call("qd_seq_bf16_matmul", ptr(x), ptr(w), ptr(y), tokens, rows, width, stream_of(x))
