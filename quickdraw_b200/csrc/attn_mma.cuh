@@ -81,6 +81,9 @@ QD_DEVINL AttnProbs attn_softmax(AttnAcc& acc, const float (&s0)[4], const float
 }
 
 // Values: bytes 64 g + 16 q .. + 15 of the value rows t, 4 + t, 8 + t, 12 + t of the chunk.
+// TWO_PIECES = false: the probabilities as one bf16 piece (eight bits of mantissa), half the MMAs: the
+// form for long prompt chunks, where the value product is most of the arithmetic.
+template <bool TWO_PIECES = true>
 QD_DEVINL void attn_value_step(AttnAcc& acc, int q, const uint4& r0, const uint4& r1, const uint4& r2, const uint4& r3,
                                const AttnProbs& pr) {
     const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w}, w1[4] = {r1.x, r1.y, r1.z, r1.w};
@@ -90,13 +93,14 @@ QD_DEVINL void attn_value_step(AttnAcc& acc, int q, const uint4& r0, const uint4
         const uint32_t a0 = __byte_perm(w0[e], w1[e], 0x5410), a1 = __byte_perm(w0[e], w1[e], 0x7632);
         const uint32_t a2 = __byte_perm(w2[e], w3[e], 0x5410), a3 = __byte_perm(w2[e], w3[e], 0x7632);
         mma_bf16(acc.out[q * 4 + e], a0, a1, a2, a3, pr.hi0, pr.hi1);
-        mma_bf16(acc.out[q * 4 + e], a0, a1, a2, a3, pr.lo0, pr.lo1);
+        if (TWO_PIECES) mma_bf16(acc.out[q * 4 + e], a0, a1, a2, a3, pr.lo0, pr.lo1);
     }
 }
 
 // Sixteen positions of the context against the (up to) eight query heads of a KV head.
 // krows / vrows: the chunk's key and value rows in shared memory (kAttnRow bytes apart);
 // first: context position of row 0; t1: end of the block's split.
+template <bool TWO_PIECES = true>
 QD_DEVINL void attn_chunk(AttnAcc& acc, const uint8_t* __restrict__ q_s, const uint8_t* __restrict__ krows,
                           const uint8_t* __restrict__ vrows, int first, int t1, int lane) {
     const int g = lane >> 2, t = lane & 3;
@@ -117,7 +121,7 @@ QD_DEVINL void attn_chunk(AttnAcc& acc, const uint8_t* __restrict__ q_s, const u
         const uint4 r1 = lds128(vb + (4 + t) * kAttnRow + q * 16);
         const uint4 r2 = lds128(vb + (8 + t) * kAttnRow + q * 16);
         const uint4 r3 = lds128(vb + (12 + t) * kAttnRow + q * 16);
-        attn_value_step(acc, q, r0, r1, r2, r3, pr);
+        attn_value_step<TWO_PIECES>(acc, q, r0, r1, r2, r3, pr);
     }
 }
 

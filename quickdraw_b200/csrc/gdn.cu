@@ -146,6 +146,26 @@ __global__ void gdn_gated_norm_kernel(const bf16* __restrict__ o, const bf16* __
                                       int dv, float eps) {
     const int head = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (head >= heads) return;
+    if (dv == 128 && !(((uintptr_t)o | (uintptr_t)z | (uintptr_t)gamma | (uintptr_t)out) & 7u)) {
+        // four values per lane, 8-byte accesses
+        const size_t at = (size_t)head * dv + 4 * lane;
+        const uint2 ov = *reinterpret_cast<const uint2*>(o + at), zv = *reinterpret_cast<const uint2*>(z + at);
+        const uint2 gv = *reinterpret_cast<const uint2*>(gamma + 4 * lane);
+        const float v[4] = {bf16_bits_to_float(ov.x & 0xffffu), bf16_bits_to_float(ov.x >> 16), bf16_bits_to_float(ov.y & 0xffffu), bf16_bits_to_float(ov.y >> 16)};
+        const float zz[4] = {bf16_bits_to_float(zv.x & 0xffffu), bf16_bits_to_float(zv.x >> 16), bf16_bits_to_float(zv.y & 0xffffu), bf16_bits_to_float(zv.y >> 16)};
+        const float gg[4] = {bf16_bits_to_float(gv.x & 0xffffu), bf16_bits_to_float(gv.x >> 16), bf16_bits_to_float(gv.y & 0xffffu), bf16_bits_to_float(gv.y >> 16)};
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ss += v[i] * v[i];
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)dv + eps);
+        float r[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r[i] = ((v[i] * inv) * gg[i]) * silu_precise(zz[i]);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+        *reinterpret_cast<uint2*>(out + at) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        return;
+    }
     float ss = 0.f;
     for (int i = lane; i < dv; i += 32) { const float v = ld_bf16(o + (size_t)head * dv + i); ss += v * v; }
     ss = warp_sum(ss);

@@ -986,7 +986,7 @@ batch_attn_mma_kernel(const LaneAttnParams p) {
 // memory once (cp.async, two tiles in flight) and read by all sixteen warps, which is what the
 // lane-per-position kernel cannot do (there every token streams its whole history from L2).  A
 // warp multiplies its heads with sixteen positions at a time on mma.sync (attn_mma.cuh: scores
-// S^T = K Q^T, running softmax, O^T += V^T P^T with the probabilities as two bf16 pieces) up to its
+// S^T = K Q^T, running softmax, O^T += V^T P^T with the probabilities as one bf16 piece) up to its
 // own position; output = bf16(attended) * bf16(sigmoid(gate)) as in the decode kernels
 // (quickdraw/kernel/triton/attention.py:53-100).  Head dimension 256, group of at most 8.
 constexpr int kFlashTokens = 16, kFlashTile = 64, kFlashThreads = kFlashTokens * 32;
@@ -1040,7 +1040,7 @@ seq_flash_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
         for (int c = 0; c < kFlashTile / 16; ++c) {
             const int start = first + 16 * c;
             if (start < mine)
-                attn_chunk(acc, q_s, buf + (size_t)(16 * c) * kAttnRow, buf + (size_t)(kFlashTile + 16 * c) * kAttnRow, start, mine, lane);
+                attn_chunk<false>(acc, q_s, buf + (size_t)(16 * c) * kAttnRow, buf + (size_t)(kFlashTile + 16 * c) * kAttnRow, start, mine, lane);
         }
         __syncthreads();                                   // everybody is done with this buffer before it is refilled
     }
