@@ -410,6 +410,47 @@ def attention_leg(cfg, device, context, peak, reps=24):
             "frac": nbytes / us / 1e3 / peak, "caches_rotated": n}
 
 
+def batch_attention_leg(cfg, device, batch, context, peak, reps=12):
+    """The batched decode attention alone (tensor-core form, `qd_batch_attention`): `batch` sequences
+    with `context` cached positions each, caches ~ N(0, 1), 2 x 537 MB of them alternating (beyond L2)."""
+    from quickdraw_b200._lib import call, lib, ptr, stream_of
+    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    capacity = context + 1
+    gen = torch.Generator(device=device).manual_seed(9)
+    k = torch.randn(2, batch, capacity, hkv, d, generator=gen, device=device).to(BF16)
+    v = torch.randn(2, batch, capacity, hkv, d, generator=gen, device=device).to(BF16)
+    qg = torch.randn(batch, hq, 2 * d, generator=gen, device=device).to(BF16)
+    kn = torch.randn(batch, hkv, d, generator=gen, device=device).to(BF16)
+    vn = torch.randn(batch, hkv, d, generator=gen, device=device).to(BF16)
+    norm = torch.zeros(d, dtype=BF16, device=device)
+    out, q_scratch = (torch.empty(batch, hq * d, dtype=BF16, device=device) for _ in range(2))
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    pairs = batch * hkv
+    splits = min(range(1, 17), key=lambda s: -(-pairs * s // sms) * (-(-context // s) + 64))
+    scratch = torch.empty(batch * lib().qd_attn_scratch_floats(hq, hkv, d, 16), dtype=torch.float32, device=device)
+    counters = torch.zeros(batch * hkv, dtype=torch.int32, device=device)
+    positions = torch.full((batch,), context, dtype=torch.int32, device=device)
+
+    def launch(i):
+        call("qd_batch_attention", ptr(qg), ptr(kn), ptr(vn), ptr(norm), ptr(norm), ptr(k[i % 2]), ptr(v[i % 2]),
+             k.stride(1), ptr(q_scratch), ptr(out), ptr(scratch), ptr(counters), ptr(positions), batch, capacity, hq, hkv, d,
+             int(d * cfg.partial_rotary_factor), float(cfg.rope_theta), float(cfg.rms_norm_eps), splits, stream_of(out))
+    for i in range(3):
+        launch(i)
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        launch(i)
+    e1.record()
+    torch.cuda.synchronize(device)
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    nbytes = batch * 2 * (context + 1) * hkv * d * 2
+    return {"kernel": "seq_attn_prepare_kernel + batch_attn_mma_kernel (mma.sync, rows straight from the cache)", "batch": batch,
+            "context": context, "splits": splits, "launch_us": us, "bytes_per_launch": nbytes, "achieved": nbytes / us / 1e3,
+            "peak": peak, "unit": "GB/s", "frac": nbytes / us / 1e3 / peak}
+
+
 def kernel_legs(engine, ckpt, cfg, device, peak):
     """Per-kernel legs: the phases of one token step from the persistent kernel's own timestamps
     (time on the critical path per phase kind; algorithmic bytes / that time), and decode
@@ -450,6 +491,7 @@ def kernel_legs(engine, ckpt, cfg, device, peak):
         "attention_layer_core": leg(["Ma", "Na"], "split-context attention + merge of one layer at this position"),
         "lm_head": leg(["H"], "final norm + bf16 LM head + greedy argmax"),
         # the operator-table kernel (composed path, cross-check), not on the product path
+        "attention_batch_32x8192": batch_attention_leg(cfg, device, 32, 8192, peak),
         "attention_operator_8192": attention_leg(cfg, device, 8192, peak),
         "attention_operator_32768": attention_leg(cfg, device, 32768, peak),
     }
