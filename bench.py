@@ -184,8 +184,8 @@ def dist_env():
 
 # ------------------------------------------------------------------ CPU baseline timing
 def reference_module():
-    """The reference's own step function when a checkout is importable, else None."""
-    for root in (ROOT / "baseline" / "_ref", Path("/root/reference")):
+    """The reference's own step function when the installed copy under baseline/_ref is importable, else None."""
+    for root in (ROOT / "baseline" / "_ref",):
         if (root / "quickdraw" / "models" / "qwen.py").exists():
             sys.path.insert(0, str(root))
             try:
