@@ -74,6 +74,14 @@ long long qd_nvfp4_matmul_rows_scratch_bytes(int in_features);
 int qd_nvfp4_matmul_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global, void* y,
                          int tokens, int out_features, int in_features, int group_size, void* scratch,
                          int convert, void* stream);
+/* The same for up to three matrices that read the same input (q | k | v, qkv | z, gate | up) in one
+ * launch; matrices past `count` are ignored (NULL). */
+int qd_nvfp4_matmul_rows3(const void* x, const void* x_up, int tokens, int in_features, int group_size,
+                          void* scratch, int convert, int count,
+                          const void* codes0, const void* scales0, const float* global0, void* y0, int out0,
+                          const void* codes1, const void* scales1, const float* global1, void* y1, int out1,
+                          const void* codes2, const void* scales2, const float* global2, void* y2, int out2,
+                          void* stream);
 
 /* Activation quantiser of the FP4 x FP4 ("W4A4") product that quickdraw's todo.md:13 asks to
  * validate separately from the W4A16 path: x bf16 [tokens, in_features] -> E2M1 codes

@@ -52,6 +52,7 @@ SIGNATURES = {
     "qd_nvfp4_matmul": [P, P, P, P, P, I, I, I, I, P, P],
     "qd_nvfp4_matmul_rows_scratch_bytes": [I],
     "qd_nvfp4_matmul_rows": [P, P, P, P, P, P, I, I, I, I, P, I, P],
+    "qd_nvfp4_matmul_rows3": [P, P, I, I, I, P, I, I, P, P, P, P, I, P, P, P, P, I, P, P, P, P, I, P],
     "qd_nvfp4_quantize_act": [P, I, I, P, P, P, P, P],
     "qd_nvfp4_matmul_w4a4": [P, P, P, P, P, P, P, I, I, I, I, P, P],
     "qd_nvfp4_grouped_matmul": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],

@@ -85,7 +85,7 @@ class BatchDecode(ChunkPrefill):
         c = self.ckpt.config
         batch = x.shape[0]
         hv, dv = c.linear_num_value_heads, c.linear_value_head_dim
-        qkv, z = self._matmul(x, w.in_proj_qkv), self._matmul(x, w.in_proj_z)
+        qkv, z = self._matmul_many(x, [w.in_proj_qkv, w.in_proj_z])
         a, b = self._small(x, w.in_proj_a), self._small(x, w.in_proj_b)
         conv = torch.empty_like(qkv)
         conv_state, rec_state = state.conv_state[:, index], state.rec_state[:, index]
@@ -103,7 +103,7 @@ class BatchDecode(ChunkPrefill):
     def _attention_batch(self, w, x, state: BatchState, index):
         c = self.ckpt.config
         batch = x.shape[0]
-        qg, k, v = self._matmul(x, w.q_proj), self._matmul(x, w.k_proj), self._matmul(x, w.v_proj)
+        qg, k, v = self._matmul_many(x, [w.q_proj, w.k_proj, w.v_proj])
         out = self._empty(batch, c.num_attention_heads * c.head_dim)
         q_scratch = torch.empty_like(out)
         scratch, counters = self._attn_scratch(batch)

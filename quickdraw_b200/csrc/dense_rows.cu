@@ -29,9 +29,17 @@ template <int GROUPS> constexpr int dense_stage_bytes() {
     return 16 * GROUPS * (kDenseCodeRow + kDenseScaleRow) + kDenseTokens * kDenseXRow;
 }
 
+// Up to three matrices that read the same token rows share a launch (q | k | v, qkv | z, gate | up):
+// the blocks are the tiles of the first matrix, then those of the second, ...
+constexpr int kDenseMatrices = 3;
+struct DenseMatrix {
+    const uint8_t* codes; const uint8_t* scales; const float* global; bf16* y;
+    int out_features, first_tile;     // first_tile: the block that holds rows 0 .. of this matrix (a huge value: unused)
+};
 struct DenseParams {
-    const uint8_t* xf; const float* up; const uint8_t* codes; const uint8_t* scales; const float* global; bf16* y;
-    int tokens, out_features, in_features;
+    const uint8_t* xf; const float* up;
+    DenseMatrix m[kDenseMatrices];
+    int tokens, in_features;
 };
 
 QD_DEVINL void dense_cp16(void* dst, const void* src) {
@@ -99,14 +107,16 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_rows_kernel(const Dens
     constexpr int kStage = dense_stage_bytes<GROUPS>();
     static_assert(PARTS <= 4 && (PARTS - 1) * GROUPS * 4 * 32 * 16 <= kStage, "parts of a chunk; meeting area");
     extern __shared__ __align__(16) uint8_t dense_smem[];
-    const int K = p.in_features, R = p.out_features, chunks = K / kDenseChunk;
-    const int r0 = blockIdx.x * TILE, rows = min(TILE, R - r0);
+    const int which = ((int)blockIdx.x >= p.m[1].first_tile) + ((int)blockIdx.x >= p.m[2].first_tile);
+    const DenseMatrix& mx = p.m[which];
+    const int K = p.in_features, R = mx.out_features, chunks = K / kDenseChunk;
+    const int r0 = ((int)blockIdx.x - mx.first_tile) * TILE, rows = min(TILE, R - r0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int group = warp % GROUPS, part = warp / GROUPS;
     const bool live = group * 16 < rows;              // a warp without rows computes on rows 0..15 and stores nothing
     const int slot0 = live ? group * 16 : 0;
-    const uint8_t* codes = p.codes + (size_t)r0 * (K / 2);
-    const uint8_t* scales = p.scales + (size_t)r0 * (K / 16);
+    const uint8_t* codes = mx.codes + (size_t)r0 * (K / 2);
+    const uint8_t* scales = mx.scales + (size_t)r0 * (K / 16);
 
     auto issue = [&](int c) {             // chunk c of the inputs into its stage of the ring
         uint8_t* st = dense_smem + (size_t)(c % kDenseStages) * kStage;
@@ -196,18 +206,18 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_rows_kernel(const Dens
             acc[nt][0] += v.x; acc[nt][1] += v.y; acc[nt][2] += v.z; acc[nt][3] += v.w;
         }
     // acc[nt][0..1] = row slot0 + g, tokens 8 nt + 2 t and + 1; [2..3] = row + 8
-    const float global = *p.global;
+    const float global = *mx.global;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const int token = 8 * nt + 2 * t + (c & 1), row = r0 + slot0 + g + 8 * (c >> 1);
             if (token >= p.tokens || row >= R) continue;
-            p.y[(size_t)token * R + row] = __float2bfloat16_rn(acc[nt][c] * p.up[token] * global);
+            mx.y[(size_t)token * R + row] = __float2bfloat16_rn(acc[nt][c] * p.up[token] * global);
         }
 }
 
-template <int GROUPS> int launch_dense(const DenseParams& p, cudaStream_t stream) {
+template <int GROUPS> int launch_dense(DenseParams p, int count, cudaStream_t stream) {
     constexpr int smem = kDenseStages * dense_stage_bytes<GROUPS>();
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
@@ -218,7 +228,12 @@ template <int GROUPS> int launch_dense(const DenseParams& p, cudaStream_t stream
         configured[dev] = true;
     }
     const int tile = 16 * GROUPS;
-    dense_rows_kernel<GROUPS><<<(p.out_features + tile - 1) / tile, kDenseThreads, smem, stream>>>(p);
+    int tiles = 0;
+    for (int i = 0; i < kDenseMatrices; ++i) {
+        p.m[i].first_tile = i < count ? tiles : 0x7fffffff;
+        if (i < count) tiles += (p.m[i].out_features + tile - 1) / tile;
+    }
+    dense_rows_kernel<GROUPS><<<tiles, kDenseThreads, smem, stream>>>(p);
     return qd_launch_status();
 }
 
@@ -230,31 +245,55 @@ extern "C" long long qd_nvfp4_matmul_rows_scratch_bytes(int in_features) {
     return in_features > 0 ? (long long)qd::kDenseTokens * in_features * 2 + qd::kDenseTokens * (long long)sizeof(float) : 0;
 }
 
-// y [tokens, out_features] = x [tokens, in_features] W^T for tokens <= 32 (the contract of
-// qd_nvfp4_matmul).  scratch: qd_nvfp4_matmul_rows_scratch_bytes(in_features) bytes, 16-byte
-// aligned; convert = 0 reuses the token rows that the previous call with this scratch area
-// converted (several projections of the same input).  x_up (or NULL): the input rows are
-// bf16(bf16(silu(x)) * x_up), the SwiGLU of two projections.  in_features a multiple of 512,
-// out_features of 16, group size 16; QD_ERR_UNSUPPORTED otherwise.
-extern "C" int qd_nvfp4_matmul_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global, void* y,
-                                    int tokens, int out_features, int in_features, int group_size, void* scratch,
-                                    int convert, void* stream) {
+// y_i [tokens, out_i] = x [tokens, in_features] W_i^T for tokens <= 32 and up to three matrices that
+// read the same input (the contract of qd_nvfp4_matmul for each).  scratch:
+// qd_nvfp4_matmul_rows_scratch_bytes(in_features) bytes, 16-byte aligned; convert = 0 reuses the token
+// rows that the previous call with this scratch area converted.  x_up (or NULL): the input rows are
+// bf16(bf16(silu(x)) * x_up), the SwiGLU of two projections.  Matrices past `count` are ignored (NULL).
+// in_features a multiple of 512, out_features of 16, group size 16; QD_ERR_UNSUPPORTED otherwise.
+extern "C" int qd_nvfp4_matmul_rows3(const void* x, const void* x_up, int tokens, int in_features, int group_size,
+                                     void* scratch, int convert, int count,
+                                     const void* codes0, const void* scales0, const float* global0, void* y0, int out0,
+                                     const void* codes1, const void* scales1, const float* global1, void* y1, int out1,
+                                     const void* codes2, const void* scales2, const float* global2, void* y2, int out2,
+                                     void* stream) {
     using namespace qd;
-    QD_CHECK_ARG(x && codes && scales && global && y && scratch && tokens > 0 && out_features > 0 && in_features > 0);
-    if (tokens > kDenseTokens || group_size != 16 || in_features % kDenseChunk != 0 || out_features % 16 != 0)
-        return QD_ERR_UNSUPPORTED;
-    if (((uintptr_t)x | (uintptr_t)x_up | (uintptr_t)codes | (uintptr_t)scales | (uintptr_t)scratch) & 15u) return QD_ERR_UNSUPPORTED;
+    QD_CHECK_ARG(x && scratch && tokens > 0 && in_features > 0 && count >= 1 && count <= kDenseMatrices);
+    if (tokens > kDenseTokens || group_size != 16 || in_features % kDenseChunk != 0) return QD_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)x_up | (uintptr_t)scratch) & 15u) return QD_ERR_UNSUPPORTED;
+    const void* codes[3] = {codes0, codes1, codes2};
+    const void* scales[3] = {scales0, scales1, scales2};
+    const float* globals[3] = {global0, global1, global2};
+    void* ys[3] = {y0, y1, y2};
+    const int outs[3] = {out0, out1, out2};
     uint8_t* xf = (uint8_t*)scratch;
     float* up = reinterpret_cast<float*>(xf + (size_t)kDenseTokens * in_features * 2);
+    DenseParams p = {};
+    p.xf = xf; p.up = up; p.tokens = tokens; p.in_features = in_features;
+    long long rows = 0;
+    for (int i = 0; i < count; ++i) {
+        QD_CHECK_ARG(codes[i] && scales[i] && globals[i] && ys[i] && outs[i] > 0);
+        if (outs[i] % 16 != 0 || (((uintptr_t)codes[i] | (uintptr_t)scales[i]) & 15u)) return QD_ERR_UNSUPPORTED;
+        p.m[i].codes = (const uint8_t*)codes[i]; p.m[i].scales = (const uint8_t*)scales[i]; p.m[i].global = globals[i];
+        p.m[i].y = (bf16*)ys[i]; p.m[i].out_features = outs[i];
+        rows += outs[i];
+    }
     if (convert) {
         rows_to_f16_kernel<<<kDenseTokens, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)x_up, tokens, in_features, xf, up);
         if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     }
-    DenseParams p = {xf, up, (const uint8_t*)codes, (const uint8_t*)scales, global, (bf16*)y, tokens, out_features, in_features};
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // 32-row tiles while they fit one wave of the GPU (twice the blocks, half the chain), else 64-row tiles
-    return (out_features + 31) / 32 > (sms > 0 ? sms : 148) ? launch_dense<4>(p, (cudaStream_t)stream)
-                                                            : launch_dense<2>(p, (cudaStream_t)stream);
+    return (rows + 31) / 32 > (sms > 0 ? sms : 148) ? launch_dense<4>(p, count, (cudaStream_t)stream)
+                                                    : launch_dense<2>(p, count, (cudaStream_t)stream);
+}
+
+// One matrix: see qd_nvfp4_matmul_rows3.
+extern "C" int qd_nvfp4_matmul_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global, void* y,
+                                    int tokens, int out_features, int in_features, int group_size, void* scratch,
+                                    int convert, void* stream) {
+    return qd_nvfp4_matmul_rows3(x, x_up, tokens, in_features, group_size, scratch, convert, 1, codes, scales, global, y, out_features,
+                                 nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr, 0, stream);
 }

@@ -100,6 +100,27 @@ class ChunkPrefill:
              stream_of(x))
         return out
 
+    def _matmul_many(self, x, projections):
+        """The products of one input with up to three matrices; in the decode-batch form they share a launch."""
+        if not (len(projections) <= 3 and all(isinstance(proj, NVFP4Linear) and self._rows_form(x.shape[0], proj)
+                                              and proj.in_features == projections[0].in_features for proj in projections)):
+            return [self._matmul(x, proj) for proj in projections]
+        first = projections[0]
+        if self._rows_scratch is None:
+            self._rows_scratch = {}
+        scratch, source = self._rows_scratch.get(first.in_features, (None, None))
+        if scratch is None:
+            scratch = torch.empty(lib().qd_nvfp4_matmul_rows_scratch_bytes(first.in_features), dtype=torch.uint8, device=self.device)
+        outs = [self._empty(x.shape[0], proj.out_features) for proj in projections]
+        args = []
+        for proj, out in zip(projections, outs):
+            args += [ptr(proj.weight), ptr(proj.weight_scale), ptr(proj.weight_scale_2), ptr(out), proj.out_features]
+        args += [None, None, None, None, 0] * (3 - len(projections))
+        call("qd_nvfp4_matmul_rows3", ptr(x), None, x.shape[0], first.in_features, first.group_size, ptr(scratch),
+             int(source is not x), len(projections), *args, stream_of(x))
+        self._rows_scratch[first.in_features] = (scratch, x)
+        return outs
+
     def _small(self, x, weight):
         rows = weight.shape[0]
         out = self._empty(x.shape[0], rows)
@@ -141,7 +162,7 @@ class ChunkPrefill:
         c = self.ckpt.config
         tokens = x.shape[0]
         hv, dv = c.linear_num_value_heads, c.linear_value_head_dim
-        qkv, z = self._matmul(x, w.in_proj_qkv), self._matmul(x, w.in_proj_z)
+        qkv, z = self._matmul_many(x, [w.in_proj_qkv, w.in_proj_z])
         a, b = self._small(x, w.in_proj_a), self._small(x, w.in_proj_b)
         conv = torch.empty_like(qkv)
         call("qd_seq_gdn_conv", ptr(qkv), ptr(w.conv1d), ptr(state.conv_state[index]), ptr(conv), tokens,
@@ -165,7 +186,7 @@ class ChunkPrefill:
     def _attention(self, w, x, state, index, position0):
         c = self.ckpt.config
         tokens = x.shape[0]
-        qg, k, v = self._matmul(x, w.q_proj), self._matmul(x, w.k_proj), self._matmul(x, w.v_proj)
+        qg, k, v = self._matmul_many(x, [w.q_proj, w.k_proj, w.v_proj])
         q_scratch = self._empty(tokens, c.num_attention_heads * c.head_dim)
         out = torch.empty_like(q_scratch)
         # q/k norm + RoPE + cache rows, then causal attention on the tensor cores: every cache tile
@@ -199,7 +220,8 @@ class ChunkPrefill:
         if self.sliced:
             import torch.distributed as dist
             dist.all_reduce(contributions, group=self.group)
-        shared = self._matmul(self._matmul(x, w.shared_gate), w.shared_down, x_up=self._matmul(x, w.shared_up))
+        shared_gate, shared_up = self._matmul_many(x, [w.shared_gate, w.shared_up])
+        shared = self._matmul(shared_gate, w.shared_down, x_up=shared_up)
         out = torch.empty_like(x)
         call("qd_seq_moe_combine", ptr(contributions), ptr(ids), ptr(shared), ptr(strength), ptr(out), tokens,
              x.shape[1], topk, stream_of(x))

@@ -58,6 +58,18 @@ def test_few_rows_matmul_matches_oracle(cuda_device, tokens, out_features, in_fe
     for t in sorted({0, tokens // 2, tokens - 1}):
         row = O.nvfp4_gemv(x[t], proj)
         assert O.rel_l2(got[t], row) < 2e-3
+    # three matrices of one input in one launch: bit-identical to the single launches
+    from quickdraw_b200._lib import call, lib, ptr, stream_of
+    third = src.nvfp4(f"u{in_features}", 48, in_features, global_scale=0.3)
+    devs = [to_device(p_, cuda_device) for p_ in (proj, other, third)]
+    xd = x.to(cuda_device)
+    outs = [torch.empty(tokens, p_.out_features, dtype=torch.bfloat16, device=cuda_device) for p_ in devs]
+    args = []
+    for p_, out in zip(devs, outs):
+        args += [ptr(p_.weight), ptr(p_.weight_scale), ptr(p_.weight_scale_2), ptr(out), p_.out_features]
+    call("qd_nvfp4_matmul_rows3", ptr(xd), None, tokens, in_features, 16, ptr(scratch), 1, 3, *args, stream_of(xd))
+    single, _ = kernels.matmul_rows(xd, devs[2], scratch, convert=False)
+    assert torch.equal(outs[0].cpu(), got) and torch.equal(outs[1].cpu(), again) and torch.equal(outs[2], single)
     # SwiGLU of two inputs formed on the way in: the same as the product of the explicit SwiGLU rows
     gate, up = src.normal(f"g{tokens}", tokens, in_features), src.normal(f"u{tokens}", tokens, in_features)
     hidden = (torch.nn.functional.silu(gate.float()).to(torch.bfloat16).float() * up.float()).to(torch.bfloat16)
