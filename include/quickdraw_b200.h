@@ -126,13 +126,17 @@ int qd_nvfp4_grouped_matmul(const void* x, const void* codes, const void* scales
  * routes (8 or 32; 0 = the library's choice) and
  * multiplied on the warp-level tensor-core instruction (the grouped branch of
  * quickdraw/kernel/triton/moe.py:99-151 at small M).  Arguments as above; x_up (or NULL) as in
- * qd_nvfp4_matmul_rows; in_features
+ * qd_nvfp4_matmul_rows.  scratch: qd_nvfp4_expert_rows_scratch_bytes(input rows, in_features) bytes,
+ * 16-byte aligned, receives the input rows as f16 (input rows = routes / topk with by_token, else
+ * routes); convert = 0 reuses what the previous call left there (the gate and up products of the
+ * same tokens).  in_features
  * 512, 1024 or 2048, out_features a multiple of 16, else QD_ERR_UNSUPPORTED. */
+long long qd_nvfp4_expert_rows_scratch_bytes(int rows, int in_features);
 int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global,
                          const int32_t* order, const int32_t* boundaries, const float* routing, void* y,
                          int routes, int experts, int topk, int out_features, int in_features,
                          int group_size, int by_token, int scatter, int global_per_expert,
-                         int routes_per_pass, void* stream);
+                         int routes_per_pass, void* scratch, int convert, void* stream);
 
 /* ---- Sequence forms for a chunk of prompt tokens (the 2-D branches of
  * quickdraw/kernel/triton/{norm,delta,attention,moe}.py, qwen.py:66-241): the single-token

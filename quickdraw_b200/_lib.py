@@ -56,7 +56,8 @@ SIGNATURES = {
     "qd_nvfp4_quantize_act": [P, I, I, P, P, P, P, P],
     "qd_nvfp4_matmul_w4a4": [P, P, P, P, P, P, P, I, I, I, I, P, P],
     "qd_nvfp4_grouped_matmul": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
-    "qd_nvfp4_expert_rows": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
+    "qd_nvfp4_expert_rows_scratch_bytes": [I, I],
+    "qd_nvfp4_expert_rows": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P],
     "qd_seq_add_rms_norm": [P, P, P, P, P, I, I, F, P],
     "qd_seq_bf16_matmul": [P, P, P, I, I, I, P],
     "qd_seq_gdn_conv": [P, P, P, P, I, I, I, P],
@@ -74,7 +75,8 @@ SIGNATURES = {
 }
 
 LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes", "qd_exchange_bytes",
-                "qd_nvfp4_matmul_rows_scratch_bytes", "qd_seq_gdn_chunk_scratch_bytes"}
+                "qd_nvfp4_matmul_rows_scratch_bytes", "qd_seq_gdn_chunk_scratch_bytes",
+                "qd_nvfp4_expert_rows_scratch_bytes"}
 
 _lib = None
 

@@ -15,8 +15,7 @@
 //   scale) and feeds 8 MMAs (m16n8k16) per group of eight tokens; fp32 accumulators; the parts of
 //   a row group meet in shared memory at the end.
 // Rounding as everywhere: fp32 sum, global scale last, one bf16 rounding.
-#include "rowdot.cuh"
-#include "rowmma.cuh"
+#include "expert_rows.cuh"
 
 namespace qd {
 namespace {
@@ -48,58 +47,6 @@ QD_DEVINL void dense_cp16(void* dst, const void* src) {
 // 16-byte piece c of a token row sits at piece c ^ (bit 3 of c << 1): the four pieces a
 // quarter-warp reads at once (c = 4 t + j) then fall on different banks
 QD_DEVINL int dense_piece(int c) { return c ^ ((c >> 2) & 2); }
-
-// Token rows as f16: xf [32][K] (rows past `tokens` zero), up[t] = the power of two that undoes
-// row t's down-scale.
-QD_DEVINL uint4 swiglu8(const uint4& g, const uint4& u) {         // bf16(bf16(silu(g)) * u), eight values
-    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
-    uint32_t o[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float lo = round_bf16(silu_precise(__uint_as_float(gw[q] << 16))) * __uint_as_float(uw[q] << 16);
-        const float hi = round_bf16(silu_precise(__uint_as_float(gw[q] & 0xffff0000u))) * __uint_as_float(uw[q] & 0xffff0000u);
-        const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
-        o[q] = *reinterpret_cast<const uint32_t*>(&pair);
-    }
-    return make_uint4(o[0], o[1], o[2], o[3]);
-}
-// x_up (or NULL): the rows are the SwiGLU of x (gate) and x_up.
-__global__ void __launch_bounds__(256) rows_to_f16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ x_up, int tokens, int K,
-                                                          uint8_t* __restrict__ xf, float* __restrict__ up) {
-    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    uint4* out = reinterpret_cast<uint4*>(xf + (size_t)row * K * 2);
-    if (row >= tokens) {
-        for (int c = tid; c < K / 8; c += 256) out[c] = make_uint4(0u, 0u, 0u, 0u);
-        if (tid == 0) up[row] = 1.f;
-        return;
-    }
-    __shared__ float red[8];
-    const uint4* in = reinterpret_cast<const uint4*>(x + (size_t)row * K);
-    const uint4* in_up = x_up ? reinterpret_cast<const uint4*>(x_up + (size_t)row * K) : nullptr;
-    uint32_t biggest = 0u;
-    for (int c = tid; c < K / 8; c += 256) {
-        const uint4 v = in_up ? swiglu8(in[c], in_up[c]) : in[c];
-        biggest = max(max(biggest, max(v.x & 0x7fffu, (v.x >> 16) & 0x7fffu)), max(v.y & 0x7fffu, (v.y >> 16) & 0x7fffu));
-        biggest = max(max(biggest, max(v.z & 0x7fffu, (v.z >> 16) & 0x7fffu)), max(v.w & 0x7fffu, (v.w >> 16) & 0x7fffu));
-    }
-    float top = warp_max(__uint_as_float(biggest << 16));
-    if (lane == 0) red[warp] = top;
-    __syncthreads();
-    top = fmaxf(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
-    const int exponent = (int)((__float_as_uint(top) >> 23) & 0xffu) - 127;
-    const int shift = (exponent > 14 && exponent < 128) ? exponent - 14 : 0;
-    const float down = __uint_as_float((uint32_t)(127 - shift) << 23);
-    for (int c = tid; c < K / 8; c += 256) {
-        const uint4 v = in_up ? swiglu8(in[c], in_up[c]) : in[c];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        uint32_t o[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-            o[q] = pack_f16x2(__uint_as_float(w[q] << 16) * down, __uint_as_float(w[q] & 0xffff0000u) * down);
-        out[c] = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-    if (tid == 0) up[row] = __uint_as_float((uint32_t)(127 + shift) << 23);
-}
 
 template <int GROUPS>
 __global__ void __launch_bounds__(kDenseThreads, 1) dense_rows_kernel(const DenseParams p) {

@@ -7,11 +7,14 @@
 // expert e).  The tcgen05 grouped product expands an expert's weights to bf16 for a 128-token
 // tile that holds a handful of rows; here the weights are decoded once per eight routes on the
 // warp-level tensor-core instruction, with the routes as the columns of the B operand:
+//   a first small kernel writes the input rows as f16 (a row scaled down by a power of two only if it
+//   would leave f16; optionally the SwiGLU of two inputs) into a scratch area;
 //   block = (expert, 64 to 256 weight rows: about 90 KB); its NVFP4 tile (codes and block scales, checkpoint
 //   layout) is copied to shared memory with cp.async in two halves of the inputs, rows padded
 //   against bank conflicts; two blocks share an SM, so one computes while the other loads;
-//   the expert's input rows go to shared memory eight at a time as f16 (scaled down by a power
-//   of two only if they would overflow);
+//   the expert's input rows follow eight at a time through two buffers of half a row each (cp.async
+//   from the scratch area: one half is multiplied while the next one, of this or of the next eight
+//   routes, is on its way);
 //   a warp owns sixteen weight rows at a time (at 2048 inputs two warps share them, each with
 //   one input quarter of either half): per 128 inputs a lane converts 32 codes of two rows (cvt.rn.f16x2.e2m1x2, exact f16 multiply with
 //   the E4M3 scale) and feeds 8 MMAs (m16n8k16); fp32 accumulators, the two warps of a row
@@ -29,9 +32,9 @@ constexpr int kRowsThreads = 256;
 // Shape of a block per input width K and routes per pass (8 NT): PARTS warps share a group of
 // sixteen rows (each takes a part of the inputs), the 8 / PARTS groups take ITERS turns:
 // 16 * (8 / PARTS) * ITERS weight rows.  NT = 1 (a decode batch: one or two routes per expert):
-// about 100 KB of shared memory, two blocks per SM.  NT = 4 (a short prompt chunk: some sixteen
-// routes per expert, all multiplied with ONE decoding of the tile): the 32 input rows take up to
-// 130 KB, one block per SM.
+// about 110 KB of shared memory, two blocks per SM.  NT = 4 (a short prompt chunk: some sixteen
+// routes per expert, all multiplied with ONE decoding of the tile): the two buffers of 32 half rows
+// take up to 130 KB, one block per SM.
 template <int K, int NT> struct RowsShape {
     static constexpr int kParts = K >= 2048 ? 2 : 1;
     static constexpr int kIters = (K <= 512 && NT == 1) ? 2 : 1;
@@ -40,8 +43,13 @@ template <int K, int NT> struct RowsShape {
     static constexpr int kBlocksPerSM = NT == 1 ? 2 : 1;
 };
 
+// The f16 input rows of a pass go through two buffers: a pass's rows in halves of the inputs (one half is
+// multiplied while the next is copied), or whole when the row groups take turns (kIters = 2: every turn
+// reads both halves).
+template <int K, int NT> constexpr int rows_units_per_pass() { return RowsShape<K, NT>::kIters == 1 ? 2 : 1; }
+template <int K, int NT> constexpr int rows_x_unit_row() { return 2 * K / rows_units_per_pass<K, NT>() + 16; }   // padded, bytes
 template <int K, int NT> constexpr size_t rows_smem_bytes() {
-    return (size_t)RowsShape<K, NT>::kTile * (rows_code_row<K>() + rows_scale_row<K>()) + (size_t)8 * NT * rows_x_row<K>();
+    return (size_t)RowsShape<K, NT>::kTile * (rows_code_row<K>() + rows_scale_row<K>()) + (size_t)2 * 8 * NT * rows_x_unit_row<K, NT>();
 }
 
 template <int K, int NT>
@@ -50,25 +58,35 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
     using Shape = RowsShape<K, NT>;
     constexpr int kParts = Shape::kParts, kIters = Shape::kIters, kGroups = Shape::kGroups, kRowsTile = Shape::kTile;
     constexpr int kTokens = 8 * NT;                         // routes per pass over the tile
+    constexpr int kUnits = rows_units_per_pass<K, NT>();    // copies of input rows per pass
     static_assert(kParts == 1 || kIters == 1, "one meeting buffer");
     const int e = blockIdx.y, r0 = blockIdx.x * kRowsTile;
     const int b0 = p.boundaries[e], b1 = p.boundaries[e + 1];
     if (b1 <= b0) return;
-    constexpr int code_row = rows_code_row<K>(), scale_row = rows_scale_row<K>(), x_row = rows_x_row<K>();
-    constexpr int kPieces = K / 8;                          // 16-byte pieces of a bf16 input row
-    constexpr int kBatch = (kTokens * kPieces / kRowsThreads) < 16 ? (kTokens * kPieces / kRowsThreads) : 16;   // loads in flight per thread
-    static_assert(kTokens * kPieces % (kBatch * kRowsThreads) == 0 && K % 512 == 0, "input width");
+    constexpr int code_row = rows_code_row<K>(), scale_row = rows_scale_row<K>(), x_row = rows_x_unit_row<K, NT>();
+    constexpr int kUnitPieces = K / 8 / kUnits;             // 16-byte pieces of an f16 input row per copy
+    constexpr int kUnitBytes = kTokens * x_row;
     const int R = p.out_features;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     uint8_t* w_codes = rows_smem;
     uint8_t* w_scales = w_codes + (size_t)kRowsTile * code_row;
-    uint8_t* xt = w_scales + (size_t)kRowsTile * scale_row;                             // [8 NT][x_row] f16
-    __shared__ float red[8];
-    __shared__ int source[kTokens], route_of[kTokens];
-    __shared__ float factor[kTokens];
+    uint8_t* xt = w_scales + (size_t)kRowsTile * scale_row;                             // [2][8 NT][x_row] f16
+    __shared__ int route_of[kTokens];
+    __shared__ float factor[kTokens], undo[kTokens];
     __shared__ float4 meet[NT][kGroups][32];
-    // ---- the expert's weight tile, in two cp.async groups by half of the inputs (rows past the
-    // matrix are not copied; the block scales travel with the first half)
+    const int units = ((b1 - b0 + kTokens - 1) / kTokens) * kUnits;
+    // input rows of copy `unit` = (pass, part of the inputs) into buffer unit & 1
+    auto issue_x = [&](int unit) {
+        const int first = b0 + (unit / kUnits) * kTokens, n = min(kTokens, b1 - first), h = unit % kUnits;
+        uint8_t* buffer = xt + (size_t)(unit & 1) * kUnitBytes;
+        for (int idx = tid; idx < n * kUnitPieces; idx += kRowsThreads) {
+            const int j = idx / kUnitPieces, c = idx % kUnitPieces;
+            const int row = p.by_token ? p.order[first + j] / p.topk : first + j;
+            rows_cp16(buffer + (size_t)j * x_row + x_piece(c) * 16, p.xf + ((size_t)row * K + (size_t)h * (K / kUnits)) * 2 + c * 16);
+        }
+    };
+    // ---- three cp.async groups: the block scales and the first half of the codes, the first input rows,
+    // the second half of the codes (rows past the matrix are not copied)
     const int rows = min(kRowsTile, R - r0);
     const uint8_t* codes = p.codes + (long long)e * p.codes_stride + (long long)r0 * (K / 2);
     const uint8_t* scales = p.scales + (long long)e * p.scales_stride + (long long)r0 * (K / 16);
@@ -84,77 +102,17 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
             rows_cp16(w_codes + (size_t)r * code_row + c * 16, codes + (size_t)r * (K / 2) + c * 16);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        if (h == 0) {
+            issue_x(0);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
     }
     const float global = p.global[p.global_per_expert ? e : 0];
     const int group = warp % kGroups, part = warp / kGroups;   // sixteen rows; which part of either half of the inputs
+    int unit = 0;
 #pragma unroll 1
     for (int first = b0; first < b1; first += kTokens) {
         const int n = min(kTokens, b1 - first), nts = (n + 7) >> 3;     // routes of this pass, groups of eight in use
-        __syncthreads();                  // the pass before is done with xt, red, source and meet
-        if (tid < kTokens) {              // where a route's input row lies, where its result goes, what multiplies it
-            const int r = first + tid, route = tid < n ? p.order[r] : 0;
-            source[tid] = tid < n ? (p.by_token ? route / p.topk : r) : -1;
-            route_of[tid] = p.scatter ? route : r;
-            factor[tid] = (p.routing && tid < n) ? round_bf16(global * p.routing[route]) : global;
-        }
-        __syncthreads();
-        // ---- the input rows of this pass as f16 (up to kBatch 16-byte loads in flight per thread) and
-        // their largest magnitude; `down`: power of two applied on the way
-        auto stage = [&](float down) -> float {
-            uint32_t biggest = 0u;
-#pragma unroll 1
-            for (int base = 0; base < nts * 8 * kPieces; base += kBatch * kRowsThreads) {
-                uint4 v[kBatch];
-#pragma unroll
-                for (int i = 0; i < kBatch; ++i) {
-                    const int idx = base + tid + i * kRowsThreads, j = idx / kPieces, c = idx % kPieces, row = source[j];
-                    v[i] = row >= 0 ? reinterpret_cast<const uint4*>(p.x + (size_t)row * K)[c] : make_uint4(0u, 0u, 0u, 0u);
-                }
-                if (p.x_up) {             // the input is bf16(bf16(silu(x)) * x_up): SwiGLU of the gate / up rows on the way in
-#pragma unroll
-                    for (int i = 0; i < kBatch; ++i) {
-                        const int idx = base + tid + i * kRowsThreads, j = idx / kPieces, c = idx % kPieces, row = source[j];
-                        if (row < 0) continue;
-                        const uint4 u = reinterpret_cast<const uint4*>(p.x_up + (size_t)row * K)[c];
-                        const uint32_t gw[4] = {v[i].x, v[i].y, v[i].z, v[i].w}, uw[4] = {u.x, u.y, u.z, u.w};
-                        uint32_t o[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float lo = round_bf16(silu_precise(__uint_as_float(gw[q] << 16))) * __uint_as_float(uw[q] << 16);
-                            const float hi = round_bf16(silu_precise(__uint_as_float(gw[q] & 0xffff0000u))) * __uint_as_float(uw[q] & 0xffff0000u);
-                            const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
-                            o[q] = *reinterpret_cast<const uint32_t*>(&pair);
-                        }
-                        v[i] = make_uint4(o[0], o[1], o[2], o[3]);
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < kBatch; ++i) {
-                    const int idx = base + tid + i * kRowsThreads, j = idx / kPieces, c = idx % kPieces;
-                    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-                    uint32_t o[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        biggest = max(biggest, max(w[q] & 0x7fffu, (w[q] >> 16) & 0x7fffu));
-                        o[q] = pack_f16x2(__uint_as_float(w[q] << 16) * down, __uint_as_float(w[q] & 0xffff0000u) * down);
-                    }
-                    *reinterpret_cast<uint4*>(xt + (size_t)j * x_row + x_piece(c) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-            }
-            return __uint_as_float(biggest << 16);
-        };
-        float top = warp_max(stage(1.f));
-        if (lane == 0) red[warp] = top;
-        __syncthreads();
-        top = fmaxf(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
-        float up = 1.f;
-        if (top >= 32768.f) {             // rare: the rows would leave f16; a power-of-two down-scale keeps them inside
-            const int exponent = (int)((__float_as_uint(top) >> 23) & 0xffu) - 127;
-            const int shift = exponent < 128 ? exponent - 14 : 0;
-            up = __uint_as_float((uint32_t)(127 + shift) << 23);
-            stage(__uint_as_float((uint32_t)(127 - shift) << 23));
-            __syncthreads();
-        }
         // ---- sixteen weight rows of this warp against the pass's routes, its part of either half
         constexpr int part_spans = K / 128 / (2 * kParts);
 #pragma unroll 1
@@ -167,11 +125,27 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
             for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = 0.f; acc[nt][1] = 0.f; acc[nt][2] = 0.f; acc[nt][3] = 0.f; }
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
-                if (first == b0 && it == 0) {              // block-uniform: this half of the tile has landed
-                    if (h == 0) asm volatile("cp.async.wait_group 1;" ::: "memory");
+                if (kUnits == 2 || (it == 0 && h == 0)) {  // block-uniform: the next copy of input rows is due
+                    // this copy has landed (behind it only the second half of the codes may be in flight) ...
+                    if (unit == 0) asm volatile("cp.async.wait_group 1;" ::: "memory");
                     else asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    __syncthreads();      // ... for everybody, and everybody is done with the copy before (and its pass)
+                    if (unit % kUnits == 0 && tid < kTokens) {     // where a route's result goes, what multiplies it
+                        const int r = first + tid, route = tid < n ? p.order[r] : 0;
+                        route_of[tid] = p.scatter ? route : r;
+                        factor[tid] = (p.routing && tid < n) ? round_bf16(global * p.routing[route]) : global;
+                        undo[tid] = tid < n ? p.up[p.by_token ? route / p.topk : r] : 1.f;
+                    }
+                    if (unit + 1 < units) issue_x(unit + 1);
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    if (kUnits == 1) __syncthreads();      // the epilogue of the first turn reads the route tables
+                    ++unit;
+                }
+                if (kUnits == 1 && first == b0 && it == 0 && h == 1) {       // the second half of the codes (the next rows may be in flight)
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
                     __syncthreads();
                 }
+                const uint8_t* xs0 = xt + (size_t)((unit - 1) & 1) * kUnitBytes + (size_t)g * x_row;
 #pragma unroll 2
                 for (int s = 0; s < part_spans; ++s) {
                     const int span = (h * kParts + part) * part_spans + s;
@@ -184,8 +158,7 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
                     const uint32_t sa1 = __byte_perm(p1, 0u, 0x1010), sb1 = __byte_perm(p1, 0u, 0x3232);
                     const uint32_t ra[4] = {w0.x, w0.y, w0.z, w0.w}, rb[4] = {w1.x, w1.y, w1.z, w1.w};
                     // the lane's activations of this span: route 8 nt + g is its column of group nt
-                    const uint8_t* xs0 = xt + (size_t)g * x_row;
-                    const int piece0 = span * 16 + t * 4;
+                    const int piece0 = (kUnits == 2 ? span - h * kParts * part_spans : span) * 16 + t * 4;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint32_t h0[4], h1[4];
@@ -228,7 +201,7 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
                     for (int c = 0; c < 4; ++c) {
                         const int j = 8 * nt + 2 * t + (c & 1), row = r0 + slot0 + g + 8 * (c >> 1);
                         if (j >= n || row >= R) continue;
-                        const float sum = acc[nt][c] * up;
+                        const float sum = acc[nt][c] * undo[j];
                         const float result = p.routing ? round_bf16(sum) * factor[j] : sum * factor[j];
                         p.y[(size_t)route_of[j] * R + row] = __float2bfloat16_rn(result);
                     }
@@ -259,9 +232,17 @@ template <int K> int launch_rows_for(const RowsParams& p, bool many, cudaStream_
 }  // namespace
 }  // namespace qd
 
+// Bytes of the scratch area for the f16 copy of `rows` input rows and their scale factors.
+extern "C" long long qd_nvfp4_expert_rows_scratch_bytes(int rows, int in_features) {
+    return rows > 0 && in_features > 0 ? (long long)rows * in_features * 2 + (long long)rows * (long long)sizeof(float) : 0;
+}
+
 // The grouped product for few rows per expert (the contract of qd_nvfp4_grouped_matmul).  x_up (or NULL):
 // the input rows are bf16(bf16(silu(x)) * x_up), the SwiGLU of the gate and up products
-// (quickdraw/models/qwen.py:184, 191), computed while the rows are staged.
+// (quickdraw/models/qwen.py:184, 191).  The input rows (routes / topk token rows with by_token, else one
+// row per route) are first written as f16 into `scratch` (qd_nvfp4_expert_rows_scratch_bytes(rows,
+// in_features) bytes, 16-byte aligned); convert = 0 reuses what the previous call with this scratch area
+// wrote (the gate and up products of the same tokens).
 // in_features 512, 1024 or 2048, out_features a multiple of 16, group size 16, 16-byte aligned
 // pointers; QD_ERR_UNSUPPORTED otherwise.  routes_per_pass: 8 or 32 routes multiplied per decoding of
 // a weight tile, 0 = the library's choice (8).
@@ -269,28 +250,39 @@ extern "C" int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void*
                                     const int32_t* order, const int32_t* boundaries, const float* routing, void* y,
                                     int routes, int experts, int topk, int out_features, int in_features,
                                     int group_size, int by_token, int scatter, int global_per_expert,
-                                    int routes_per_pass, void* stream) {
+                                    int routes_per_pass, void* scratch, int convert, void* stream) {
     using namespace qd;
-    QD_CHECK_ARG(x && codes && scales && global && order && boundaries && y);
+    QD_CHECK_ARG(x && codes && scales && global && order && boundaries && y && scratch);
     QD_CHECK_ARG(routes > 0 && experts > 0 && experts <= 65535 && topk > 0 && out_features > 0 && in_features > 0);
     QD_CHECK_ARG(routes_per_pass == 0 || routes_per_pass == 8 || routes_per_pass == 32);
     if (group_size != 16 || out_features % 16 != 0) return QD_ERR_UNSUPPORTED;
-    if (((uintptr_t)x | (uintptr_t)x_up | (uintptr_t)codes | (uintptr_t)scales) & 15u) return QD_ERR_UNSUPPORTED;
+    if (in_features != 512 && in_features != 1024 && in_features != 2048) return QD_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)x_up | (uintptr_t)codes | (uintptr_t)scales | (uintptr_t)scratch) & 15u) return QD_ERR_UNSUPPORTED;
+    const int in_rows = by_token ? routes / topk : routes;
+    QD_CHECK_ARG(in_rows > 0);
     RowsParams p = {};
-    p.x = (const bf16*)x; p.x_up = (const bf16*)x_up; p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
+    p.xf = (const uint8_t*)scratch; p.up = reinterpret_cast<const float*>(p.xf + (size_t)in_rows * in_features * 2);
+    p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
     p.order = order; p.boundaries = boundaries; p.routing = routing; p.y = (bf16*)y;
     p.routes = routes; p.experts = experts; p.topk = topk; p.out_features = out_features;
     p.by_token = by_token; p.scatter = scatter; p.global_per_expert = global_per_expert;
     p.codes_stride = (long long)out_features * (in_features / 2);
     p.scales_stride = (long long)out_features * (in_features / 16);
-    // Eight routes per pass unless the caller asks for 32: measured at 16 routes per expert (a 511-token
-    // chunk) the two forms are within 10 % of each other (gate 105 against 118 us, down 101 against 98 us:
-    // one decoding of the tile for all routes, but one block per SM and four times the MMAs per pass).
+    if (convert) {
+        const unsigned blocks = (unsigned)((in_rows + 7) / 8);
+        uint8_t* xf = (uint8_t*)scratch;
+        float* up = reinterpret_cast<float*>(xf + (size_t)in_rows * in_features * 2);
+        if (in_features == 512) rows_to_f16_warp_kernel<512><<<blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)x_up, in_rows, xf, up);
+        else if (in_features == 1024) rows_to_f16_warp_kernel<1024><<<blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)x_up, in_rows, xf, up);
+        else rows_to_f16_warp_kernel<2048><<<blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)x_up, in_rows, xf, up);
+        if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
+    }
+    // Eight routes per pass unless the caller asks for 32 (one decoding of the tile for up to 32 routes,
+    // but one block per SM and four times the MMAs per pass).
     const bool many = routes_per_pass == 32;
     switch (in_features) {
         case 512: return launch_rows_for<512>(p, many, (cudaStream_t)stream);
         case 1024: return launch_rows_for<1024>(p, many, (cudaStream_t)stream);
-        case 2048: return launch_rows_for<2048>(p, many, (cudaStream_t)stream);
-        default: return QD_ERR_UNSUPPORTED;
+        default: return launch_rows_for<2048>(p, many, (cudaStream_t)stream);
     }
 }

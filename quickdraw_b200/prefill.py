@@ -33,6 +33,8 @@ class ChunkPrefill:
     sliced, group, expert_range = False, None, None      # defaults of a whole model on one GPU
     total_experts = None                                  # experts of the whole model (None: the bank's own count)
     _rows_scratch = None
+    _expert_scratch = None
+    _retired = None
     _fp8_rows = None
     CHUNKED_FROM = 64                                     # tokens from which the DeltaNet recurrence takes the chunked form
     FEW_TOKENS = 32                                       # token rows up to which a dense product takes the mma.sync form
@@ -49,7 +51,7 @@ class ChunkPrefill:
         self.gammas = [((1 + layer.input_layernorm.float()).contiguous(),
                         (1 + layer.post_attention_layernorm.float()).contiguous()) for layer in ckpt.layers]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._rows_scratch = {}
+        self._rows_scratch, self._expert_scratch, self._retired = {}, {}, []
         for layer in ckpt.layers:
             assert layer.moe.experts_gate.weight.shape[0] == self.expert_range[1] - self.expert_range[0], \
                 "the expert banks must hold exactly the owned range"
@@ -57,6 +59,11 @@ class ChunkPrefill:
     # ------------------------------------------------------------------ building blocks
     def _empty(self, *shape, dtype=BF16):
         return torch.empty(shape, dtype=dtype, device=self.device)
+
+    def _retire(self, scratch):
+        """Keep a scratch area that is being replaced by a larger one: a captured graph may still write to it."""
+        if scratch is not None:
+            self._retired = (self._retired or []) + [scratch]
 
     def _rows_form(self, tokens, proj):
         return tokens <= self.FEW_TOKENS and proj.in_features % 512 == 0 and proj.out_features % 16 == 0
@@ -71,6 +78,7 @@ class ChunkPrefill:
                 x = self._swiglu(x, x_up)
             scratch, source, scale = self._fp8_rows or (None, None, None)
             if scratch is None or scratch.numel() < x.numel():
+                self._retire(scratch)
                 scratch = torch.empty(x.numel(), dtype=torch.uint8, device=self.device)
                 source = None
             fresh = source is not x or scale != proj.input_scale.data_ptr()      # (no host read of the scale: capturable)
@@ -143,11 +151,22 @@ class ChunkPrefill:
         out = (torch.zeros if self.sliced and scatter else torch.empty)((routes, bank.out_features), dtype=BF16, device=self.device)
         experts = bank.weight.shape[0]
         if routes <= self.FEW_ROWS * (self.total_experts or experts) and bank.in_features in (512, 1024, 2048) and bank.out_features % 16 == 0:
-            # few rows per expert: weights decoded once per 8 or 32 routes on mma.sync, no 128-token tiles
+            # few rows per expert: weights decoded once per 8 or 32 routes on mma.sync, no 128-token tiles;
+            # the f16 copy of the input rows is shared by the products of the same input (gate, up)
+            in_rows = routes // topk if by_token else routes
+            if self._expert_scratch is None:
+                self._expert_scratch = {}
+            scratch, source = self._expert_scratch.get(bank.in_features, (None, None))
+            need = lib().qd_nvfp4_expert_rows_scratch_bytes(in_rows, bank.in_features)
+            if scratch is None or scratch.numel() < need:
+                self._retire(scratch)
+                scratch, source = torch.empty(need, dtype=torch.uint8, device=self.device), None
+            fresh = x_up is not None or source is not x
             call("qd_nvfp4_expert_rows", ptr(x), ptr(x_up), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
                  ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, experts, topk, bank.out_features,
                  bank.in_features, bank.group_size, int(by_token), int(scatter),
-                 int(bank.weight_scale_2.numel() != 1), self.ROUTES_PER_PASS, stream_of(x))
+                 int(bank.weight_scale_2.numel() != 1), self.ROUTES_PER_PASS, ptr(scratch), int(fresh), stream_of(x))
+            self._expert_scratch[bank.in_features] = (scratch, None if x_up is not None else x)
             return out
         if x_up is not None:
             x = self._swiglu(x, x_up)
@@ -213,9 +232,9 @@ class ChunkPrefill:
             boundaries = boundaries[self.expert_range[0]:self.expert_range[1] + 1]
         gate = self._grouped(x, w.experts_gate, order, boundaries, routes, topk, by_token=True, scatter=False)
         up = self._grouped(x, w.experts_up, order, boundaries, routes, topk, by_token=True, scatter=False)
-        # SwiGLU as its own kernel here: fused into the down product, each of an expert's row tiles would redo
-        # it for the same rows (measured at 511 tokens: +30 us per layer against 13 us for the kernel)
-        contributions = self._grouped(self._swiglu(gate, up), w.experts_down, order, boundaries, routes, topk,
+        # the SwiGLU is formed while the rows of the down product are written as f16 (a separate kernel where
+        # the 128-token tiles take the product)
+        contributions = self._grouped(gate, w.experts_down, order, boundaries, routes, topk, x_up=up,
                                       routing=weights.flatten(), by_token=False, scatter=True)
         if self.sliced:
             import torch.distributed as dist

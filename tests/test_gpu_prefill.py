@@ -129,6 +129,14 @@ def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tok
         torch.testing.assert_close(plain[r].float(), want.float(), rtol=0.025, atol=0.003)
         want_routed = kernels.expert_gemv(x[token], bank, ids.flatten()[route:route + 1], weights.flatten()[route:route + 1])[0]
         torch.testing.assert_close(routed[route].float(), want_routed.float(), rtol=0.025, atol=0.003)
+    if few_rows:
+        # a token row beyond the f16 range: its f16 copy is scaled down by a power of two and the sums back up
+        big = x.clone()
+        big[0] *= 2.0 ** 17
+        scaled = helper._grouped(big, bank, order.to(torch.int32), boundaries, routes, topk, by_token=True, scatter=False)
+        of_token_0 = (order // topk == 0)
+        assert O.rel_l2(scaled[of_token_0].float().cpu(), (plain[of_token_0].float() * 2.0 ** 17).cpu()) < 1e-3
+        assert torch.equal(scaled[~of_token_0], plain[~of_token_0])
     # SwiGLU of two inputs formed on the way in (either form; the tcgen05 form runs the SwiGLU kernel first)
     up = src.normal("up", routes, width).to(cuda_device)
     hidden = (torch.nn.functional.silu(sorted_rows.float()).to(torch.bfloat16).float() * up.float()).to(torch.bfloat16)
