@@ -138,6 +138,16 @@ int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void* codes, con
                          int group_size, int by_token, int scatter, int global_per_expert,
                          int routes_per_pass, void* scratch, int convert, void* stream);
 
+/* Two banks of the same shape against the same routes in ONE launch: the gate and up products of the
+ * routed experts (quickdraw/models/qwen.py:176-186).  y and y2 are what two calls of
+ * qd_nvfp4_expert_rows with by_token = 1, no routing weights and results in sorted order give. */
+int qd_nvfp4_expert_rows2(const void* x, const void* codes, const void* scales, const float* global, void* y,
+                          const void* codes2, const void* scales2, const float* global2, void* y2,
+                          const int32_t* order, const int32_t* boundaries,
+                          int routes, int experts, int topk, int out_features, int in_features,
+                          int group_size, int global_per_expert, int routes_per_pass, void* scratch, int convert,
+                          void* stream);
+
 /* ---- Sequence forms for a chunk of prompt tokens (the 2-D branches of
  * quickdraw/kernel/triton/{norm,delta,attention,moe}.py, qwen.py:66-241): the single-token
  * arithmetic row by row.  All activations bf16 [tokens, width] contiguous. */

@@ -57,6 +57,7 @@ SIGNATURES = {
     "qd_nvfp4_matmul_w4a4": [P, P, P, P, P, P, P, I, I, I, I, P, P],
     "qd_nvfp4_grouped_matmul": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
     "qd_nvfp4_expert_rows_scratch_bytes": [I, I],
+    "qd_nvfp4_expert_rows2": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, P],
     "qd_nvfp4_expert_rows": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P],
     "qd_seq_add_rms_norm": [P, P, P, P, P, I, I, F, P],
     "qd_seq_bf16_matmul": [P, P, P, I, I, I, P],

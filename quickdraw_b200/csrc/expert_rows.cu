@@ -88,8 +88,10 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
     // ---- three cp.async groups: the block scales and the first half of the codes, the first input rows,
     // the second half of the codes (rows past the matrix are not copied)
     const int rows = min(kRowsTile, R - r0);
-    const uint8_t* codes = p.codes + (long long)e * p.codes_stride + (long long)r0 * (K / 2);
-    const uint8_t* scales = p.scales + (long long)e * p.scales_stride + (long long)r0 * (K / 16);
+    const bool second = blockIdx.z != 0;                    // the gate and up banks of the same routes share a launch
+    const uint8_t* codes = (second ? p.codes2 : p.codes) + (long long)e * p.codes_stride + (long long)r0 * (K / 2);
+    const uint8_t* scales = (second ? p.scales2 : p.scales) + (long long)e * p.scales_stride + (long long)r0 * (K / 16);
+    bf16* y = second ? p.y2 : p.y;
     for (int piece = tid; piece < rows * (K / 256); piece += kRowsThreads) {
         const int r = piece / (K / 256), c = piece % (K / 256);
         rows_cp16(w_scales + (size_t)r * scale_row + c * 16, scales + (size_t)r * (K / 16) + c * 16);
@@ -107,7 +109,7 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
     }
-    const float global = p.global[p.global_per_expert ? e : 0];
+    const float global = (second ? p.global2 : p.global)[p.global_per_expert ? e : 0];
     const int group = warp % kGroups, part = warp / kGroups;   // sixteen rows; which part of either half of the inputs
     int unit = 0;
 #pragma unroll 1
@@ -203,7 +205,7 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
                         if (j >= n || row >= R) continue;
                         const float sum = acc[nt][c] * undo[j];
                         const float result = p.routing ? round_bf16(sum) * factor[j] : sum * factor[j];
-                        p.y[(size_t)route_of[j] * R + row] = __float2bfloat16_rn(result);
+                        y[(size_t)route_of[j] * R + row] = __float2bfloat16_rn(result);
                     }
             }
         }
@@ -221,7 +223,7 @@ template <int K, int NT> int launch_rows(const RowsParams& p, cudaStream_t strea
         configured[dev] = true;
     }
     constexpr int tile = RowsShape<K, NT>::kTile;
-    const dim3 grid((unsigned)((p.out_features + tile - 1) / tile), (unsigned)p.experts);
+    const dim3 grid((unsigned)((p.out_features + tile - 1) / tile), (unsigned)p.experts, p.codes2 ? 2u : 1u);
     expert_rows_kernel<K, NT><<<grid, kRowsThreads, smem, stream>>>(p);
     return qd_launch_status();
 }
@@ -246,13 +248,16 @@ extern "C" long long qd_nvfp4_expert_rows_scratch_bytes(int rows, int in_feature
 // in_features 512, 1024 or 2048, out_features a multiple of 16, group size 16, 16-byte aligned
 // pointers; QD_ERR_UNSUPPORTED otherwise.  routes_per_pass: 8 or 32 routes multiplied per decoding of
 // a weight tile, 0 = the library's choice (8).
-extern "C" int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global,
-                                    const int32_t* order, const int32_t* boundaries, const float* routing, void* y,
-                                    int routes, int experts, int topk, int out_features, int in_features,
-                                    int group_size, int by_token, int scatter, int global_per_expert,
-                                    int routes_per_pass, void* scratch, int convert, void* stream) {
+static int expert_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global, void* y,
+                       const void* codes2, const void* scales2, const float* global2, void* y2,
+                       const int32_t* order, const int32_t* boundaries, const float* routing,
+                       int routes, int experts, int topk, int out_features, int in_features,
+                       int group_size, int by_token, int scatter, int global_per_expert,
+                       int routes_per_pass, void* scratch, int convert, void* stream) {
     using namespace qd;
     QD_CHECK_ARG(x && codes && scales && global && order && boundaries && y && scratch);
+    QD_CHECK_ARG(!codes2 || (scales2 && global2 && y2));
+    if (((uintptr_t)codes2 | (uintptr_t)scales2) & 15u) return QD_ERR_UNSUPPORTED;
     QD_CHECK_ARG(routes > 0 && experts > 0 && experts <= 65535 && topk > 0 && out_features > 0 && in_features > 0);
     QD_CHECK_ARG(routes_per_pass == 0 || routes_per_pass == 8 || routes_per_pass == 32);
     if (group_size != 16 || out_features % 16 != 0) return QD_ERR_UNSUPPORTED;
@@ -263,6 +268,7 @@ extern "C" int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void*
     RowsParams p = {};
     p.xf = (const uint8_t*)scratch; p.up = reinterpret_cast<const float*>(p.xf + (size_t)in_rows * in_features * 2);
     p.codes = (const uint8_t*)codes; p.scales = (const uint8_t*)scales; p.global = global;
+    p.codes2 = (const uint8_t*)codes2; p.scales2 = (const uint8_t*)scales2; p.global2 = global2; p.y2 = (bf16*)y2;
     p.order = order; p.boundaries = boundaries; p.routing = routing; p.y = (bf16*)y;
     p.routes = routes; p.experts = experts; p.topk = topk; p.out_features = out_features;
     p.by_token = by_token; p.scatter = scatter; p.global_per_expert = global_per_expert;
@@ -285,4 +291,28 @@ extern "C" int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void*
         case 1024: return launch_rows_for<1024>(p, many, (cudaStream_t)stream);
         default: return launch_rows_for<2048>(p, many, (cudaStream_t)stream);
     }
+}
+
+extern "C" int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global,
+                                    const int32_t* order, const int32_t* boundaries, const float* routing, void* y,
+                                    int routes, int experts, int topk, int out_features, int in_features,
+                                    int group_size, int by_token, int scatter, int global_per_expert,
+                                    int routes_per_pass, void* scratch, int convert, void* stream) {
+    return expert_rows(x, x_up, codes, scales, global, y, nullptr, nullptr, nullptr, nullptr, order, boundaries, routing, routes, experts,
+                       topk, out_features, in_features, group_size, by_token, scatter, global_per_expert, routes_per_pass, scratch,
+                       convert, stream);
+}
+
+// Two banks of the same shape against the same routes in one launch (the gate and up products of the
+// routed experts, quickdraw/models/qwen.py:176-186): y = bank(x), y2 = bank2(x), each as
+// qd_nvfp4_expert_rows would give it with by_token = 1, no routing weights, results in sorted order.
+extern "C" int qd_nvfp4_expert_rows2(const void* x, const void* codes, const void* scales, const float* global, void* y,
+                                     const void* codes2, const void* scales2, const float* global2, void* y2,
+                                     const int32_t* order, const int32_t* boundaries,
+                                     int routes, int experts, int topk, int out_features, int in_features,
+                                     int group_size, int global_per_expert, int routes_per_pass, void* scratch, int convert,
+                                     void* stream) {
+    QD_CHECK_ARG(codes2 && scales2 && global2 && y2);
+    return expert_rows(x, nullptr, codes, scales, global, y, codes2, scales2, global2, y2, order, boundaries, nullptr, routes, experts,
+                       topk, out_features, in_features, group_size, 1, 0, global_per_expert, routes_per_pass, scratch, convert, stream);
 }

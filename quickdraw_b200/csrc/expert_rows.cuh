@@ -9,6 +9,7 @@ namespace qd {
 struct RowsParams {
     const uint8_t* xf; const float* up; const uint8_t* codes; const uint8_t* scales; const float* global;
     const int32_t* order; const int32_t* boundaries; const float* routing; bf16* y;
+    const uint8_t* codes2; const uint8_t* scales2; const float* global2; bf16* y2;    // a second bank of the same shape (blockIdx.z = 1)
     int routes, experts, topk, out_features, by_token, scatter, global_per_expert;
     long long codes_stride, scales_stride;
 };

@@ -146,21 +146,43 @@ class ChunkPrefill:
         call("qd_swiglu", ptr(gate), ptr(up), ptr(out), gate.numel(), stream_of(gate))
         return out
 
+    def _few_rows(self, routes, bank):
+        return (routes <= self.FEW_ROWS * (self.total_experts or bank.weight.shape[0]) and bank.in_features in (512, 1024, 2048)
+                and bank.out_features % 16 == 0)
+
+    def _expert_rows_scratch(self, in_rows, in_features):
+        """The area for the f16 copy of the input rows of the few-rows form, and the input it holds."""
+        if self._expert_scratch is None:
+            self._expert_scratch = {}
+        scratch, source = self._expert_scratch.get(in_features, (None, None))
+        need = lib().qd_nvfp4_expert_rows_scratch_bytes(in_rows, in_features)
+        if scratch is None or scratch.numel() < need:
+            self._retire(scratch)
+            scratch, source = torch.empty(need, dtype=torch.uint8, device=self.device), None
+        return scratch, source
+
+    def _grouped_pair(self, x, bank, bank2, order, boundaries, routes, topk):
+        """The gate and up products of the routed experts (token rows in, sorted order out); one launch in the few-rows form."""
+        if not (self._few_rows(routes, bank) and bank.weight.shape == bank2.weight.shape):
+            return (self._grouped(x, bank, order, boundaries, routes, topk, by_token=True, scatter=False),
+                    self._grouped(x, bank2, order, boundaries, routes, topk, by_token=True, scatter=False))
+        out, out2 = self._empty(routes, bank.out_features), self._empty(routes, bank.out_features)
+        scratch, source = self._expert_rows_scratch(routes // topk, bank.in_features)
+        call("qd_nvfp4_expert_rows2", ptr(x), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2), ptr(out),
+             ptr(bank2.weight), ptr(bank2.weight_scale), ptr(bank2.weight_scale_2), ptr(out2), ptr(order), ptr(boundaries),
+             routes, bank.weight.shape[0], topk, bank.out_features, bank.in_features, bank.group_size,
+             int(bank.weight_scale_2.numel() != 1), self.ROUTES_PER_PASS, ptr(scratch), int(source is not x), stream_of(x))
+        self._expert_scratch[bank.in_features] = (scratch, x)
+        return out, out2
+
     def _grouped(self, x, bank: NVFP4Linear, order, boundaries, routes, topk, *, routing=None, by_token, scatter, x_up=None):
         # rows of experts another rank owns stay zero in the scattered (route-order) output
         out = (torch.zeros if self.sliced and scatter else torch.empty)((routes, bank.out_features), dtype=BF16, device=self.device)
         experts = bank.weight.shape[0]
-        if routes <= self.FEW_ROWS * (self.total_experts or experts) and bank.in_features in (512, 1024, 2048) and bank.out_features % 16 == 0:
+        if self._few_rows(routes, bank):
             # few rows per expert: weights decoded once per 8 or 32 routes on mma.sync, no 128-token tiles;
             # the f16 copy of the input rows is shared by the products of the same input (gate, up)
-            in_rows = routes // topk if by_token else routes
-            if self._expert_scratch is None:
-                self._expert_scratch = {}
-            scratch, source = self._expert_scratch.get(bank.in_features, (None, None))
-            need = lib().qd_nvfp4_expert_rows_scratch_bytes(in_rows, bank.in_features)
-            if scratch is None or scratch.numel() < need:
-                self._retire(scratch)
-                scratch, source = torch.empty(need, dtype=torch.uint8, device=self.device), None
+            scratch, source = self._expert_rows_scratch(routes // topk if by_token else routes, bank.in_features)
             fresh = x_up is not None or source is not x
             call("qd_nvfp4_expert_rows", ptr(x), ptr(x_up), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
                  ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, experts, topk, bank.out_features,
@@ -230,8 +252,7 @@ class ChunkPrefill:
         call("qd_seq_group_routes", ptr(ids), routes, c.num_experts, ptr(order), ptr(boundaries), stream_of(x))
         if self.sliced:      # this rank's experts: their slice of the boundaries, indices local to the bank
             boundaries = boundaries[self.expert_range[0]:self.expert_range[1] + 1]
-        gate = self._grouped(x, w.experts_gate, order, boundaries, routes, topk, by_token=True, scatter=False)
-        up = self._grouped(x, w.experts_up, order, boundaries, routes, topk, by_token=True, scatter=False)
+        gate, up = self._grouped_pair(x, w.experts_gate, w.experts_up, order, boundaries, routes, topk)
         # the SwiGLU is formed while the rows of the down product are written as f16 (a separate kernel where
         # the 128-token tiles take the product)
         contributions = self._grouped(gate, w.experts_down, order, boundaries, routes, topk, x_up=up,

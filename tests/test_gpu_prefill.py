@@ -137,6 +137,11 @@ def test_grouped_matmul_matches_per_route_matvec(cuda_device, experts, topk, tok
         of_token_0 = (order // topk == 0)
         assert O.rel_l2(scaled[of_token_0].float().cpu(), (plain[of_token_0].float() * 2.0 ** 17).cpu()) < 1e-3
         assert torch.equal(scaled[~of_token_0], plain[~of_token_0])
+    # two banks against the same routes (gate and up): one launch in the few-rows form, the same bits either way
+    bank2 = to_device(src.nvfp4("bank2", rows, width, experts, global_scale=0.25, per_expert_global=True), cuda_device)
+    first, second = helper._grouped_pair(x, bank, bank2, order.to(torch.int32), boundaries, routes, topk)
+    alone = helper._grouped(x, bank2, order.to(torch.int32), boundaries, routes, topk, by_token=True, scatter=False)
+    assert torch.equal(first, plain) and torch.equal(second, alone)
     # SwiGLU of two inputs formed on the way in (either form; the tcgen05 form runs the SwiGLU kernel first)
     up = src.normal("up", routes, width).to(cuda_device)
     hidden = (torch.nn.functional.silu(sorted_rows.float()).to(torch.bfloat16).float() * up.float()).to(torch.bfloat16)
