@@ -65,10 +65,9 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_rows_kernel(const Dens
     const uint8_t* codes = mx.codes + (size_t)r0 * (K / 2);
     const uint8_t* scales = mx.scales + (size_t)r0 * (K / 16);
 
-    auto issue = [&](int c) {             // chunk c of the inputs into its stage of the ring
+    auto issue_weights = [&](int c) {     // chunk c of the codes and block scales into its stage of the ring
         uint8_t* st = dense_smem + (size_t)(c % kDenseStages) * kStage;
         uint8_t* st_scales = st + TILE * kDenseCodeRow;
-        uint8_t* st_x = st_scales + TILE * kDenseScaleRow;
         for (int piece = tid; piece < rows * 16; piece += kDenseThreads) {
             const int r = piece >> 4, q = piece & 15;
             dense_cp16(st + r * kDenseCodeRow + q * 16, codes + (size_t)r * (K / 2) + c * (kDenseChunk / 2) + q * 16);
@@ -77,15 +76,25 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_rows_kernel(const Dens
             const int r = piece >> 1, q = piece & 1;
             dense_cp16(st_scales + r * kDenseScaleRow + q * 16, scales + (size_t)r * (K / 16) + c * (kDenseChunk / 16) + q * 16);
         }
+    };
+    auto issue_rows = [&](int c) {        // chunk c of the f16 token rows
+        uint8_t* st_x = dense_smem + (size_t)(c % kDenseStages) * kStage + TILE * (kDenseCodeRow + kDenseScaleRow);
 #pragma unroll
         for (int i = 0; i < kDenseTokens * 64 / kDenseThreads; ++i) {
             const int piece = tid + i * kDenseThreads, row = piece >> 6, q = piece & 63;
             dense_cp16(st_x + row * kDenseXRow + dense_piece(q) * 16, p.xf + ((size_t)row * K + (size_t)c * kDenseChunk) * 2 + q * 16);
         }
     };
+    // The weights of the first chunks do not depend on the kernel before this one (the writer of the f16
+    // token rows): when launched as its programmatic dependent, the block fetches them while that kernel
+    // still runs, and only then waits for it (no effect in an ordinary launch).
+#pragma unroll
+    for (int c = 0; c < kDenseStages; ++c)
+        if (c < chunks) issue_weights(c);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll
     for (int c = 0; c < kDenseStages; ++c) {
-        if (c < chunks) issue(c);
+        if (c < chunks) issue_rows(c);
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
     float acc[4][4];
@@ -130,7 +139,7 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_rows_kernel(const Dens
             }
         }
         __syncthreads();                  // every warp is done with this stage
-        if (c + kDenseStages < chunks) issue(c + kDenseStages);
+        if (c + kDenseStages < chunks) { issue_weights(c + kDenseStages); issue_rows(c + kDenseStages); }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -164,7 +173,7 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_rows_kernel(const Dens
         }
 }
 
-template <int GROUPS> int launch_dense(DenseParams p, int count, cudaStream_t stream) {
+template <int GROUPS> int launch_dense(DenseParams p, int count, bool dependent, cudaStream_t stream) {
     constexpr int smem = kDenseStages * dense_stage_bytes<GROUPS>();
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
@@ -180,7 +189,14 @@ template <int GROUPS> int launch_dense(DenseParams p, int count, cudaStream_t st
         p.m[i].first_tile = i < count ? tiles : 0x7fffffff;
         if (i < count) tiles += (p.m[i].out_features + tile - 1) / tile;
     }
-    dense_rows_kernel<GROUPS><<<tiles, kDenseThreads, smem, stream>>>(p);
+    // after the kernel that writes the token rows: a programmatic dependent of it (see the kernel's prologue)
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)tiles); config.blockDim = dim3(kDenseThreads); config.dynamicSmemBytes = smem; config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute; config.numAttrs = dependent ? 1 : 0;
+    if (cudaLaunchKernelEx(&config, dense_rows_kernel<GROUPS>, p) != cudaSuccess) return QD_ERR_LAUNCH;
     return qd_launch_status();
 }
 
@@ -233,8 +249,8 @@ extern "C" int qd_nvfp4_matmul_rows3(const void* x, const void* x_up, int tokens
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // 32-row tiles while they fit one wave of the GPU (twice the blocks, half the chain), else 64-row tiles
-    return (rows + 31) / 32 > (sms > 0 ? sms : 148) ? launch_dense<4>(p, count, (cudaStream_t)stream)
-                                                    : launch_dense<2>(p, count, (cudaStream_t)stream);
+    return (rows + 31) / 32 > (sms > 0 ? sms : 148) ? launch_dense<4>(p, count, convert != 0, (cudaStream_t)stream)
+                                                    : launch_dense<2>(p, count, convert != 0, (cudaStream_t)stream);
 }
 
 // One matrix: see qd_nvfp4_matmul_rows3.

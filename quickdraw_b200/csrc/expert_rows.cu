@@ -104,7 +104,11 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
             rows_cp16(w_codes + (size_t)r * code_row + c * 16, codes + (size_t)r * (K / 2) + c * 16);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        if (h == 0) {
+        if (h == (p.dependent ? 1 : 0)) {
+            // The weights do not depend on the kernel before this one (the writer of the f16 rows): as its
+            // programmatic dependent the block fetches its whole tile while that kernel still runs and
+            // waits for it here; in an ordinary launch the second half of the codes follows the rows.
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             issue_x(0);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
@@ -128,8 +132,8 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
                 if (kUnits == 2 || (it == 0 && h == 0)) {  // block-uniform: the next copy of input rows is due
-                    // this copy has landed (behind it only the second half of the codes may be in flight) ...
-                    if (unit == 0) asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    // this copy has landed (behind the first one the second half of the codes may be in flight) ...
+                    if (unit == 0 && !p.dependent) asm volatile("cp.async.wait_group 1;" ::: "memory");
                     else asm volatile("cp.async.wait_group 0;" ::: "memory");
                     __syncthreads();      // ... for everybody, and everybody is done with the copy before (and its pass)
                     if (unit % kUnits == 0 && tid < kTokens) {     // where a route's result goes, what multiplies it
@@ -223,8 +227,14 @@ template <int K, int NT> int launch_rows(const RowsParams& p, cudaStream_t strea
         configured[dev] = true;
     }
     constexpr int tile = RowsShape<K, NT>::kTile;
-    const dim3 grid((unsigned)((p.out_features + tile - 1) / tile), (unsigned)p.experts, p.codes2 ? 2u : 1u);
-    expert_rows_kernel<K, NT><<<grid, kRowsThreads, smem, stream>>>(p);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)((p.out_features + tile - 1) / tile), (unsigned)p.experts, p.codes2 ? 2u : 1u);
+    config.blockDim = dim3(kRowsThreads); config.dynamicSmemBytes = smem; config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute; config.numAttrs = p.dependent ? 1 : 0;
+    if (cudaLaunchKernelEx(&config, expert_rows_kernel<K, NT>, p) != cudaSuccess) return QD_ERR_LAUNCH;
     return qd_launch_status();
 }
 template <int K> int launch_rows_for(const RowsParams& p, bool many, cudaStream_t stream) {
@@ -274,6 +284,7 @@ static int expert_rows(const void* x, const void* x_up, const void* codes, const
     p.by_token = by_token; p.scatter = scatter; p.global_per_expert = global_per_expert;
     p.codes_stride = (long long)out_features * (in_features / 2);
     p.scales_stride = (long long)out_features * (in_features / 16);
+    p.dependent = convert != 0;
     if (convert) {
         const unsigned blocks = (unsigned)((in_rows + 7) / 8);
         uint8_t* xf = (uint8_t*)scratch;

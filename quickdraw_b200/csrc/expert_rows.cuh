@@ -11,6 +11,7 @@ struct RowsParams {
     const int32_t* order; const int32_t* boundaries; const float* routing; bf16* y;
     const uint8_t* codes2; const uint8_t* scales2; const float* global2; bf16* y2;    // a second bank of the same shape (blockIdx.z = 1)
     int routes, experts, topk, out_features, by_token, scatter, global_per_expert;
+    int dependent;        // launched as the programmatic dependent of the kernel that writes xf and up
     long long codes_stride, scales_stride;
 };
 
@@ -66,6 +67,8 @@ namespace {
 __global__ void __launch_bounds__(256) rows_to_f16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ x_up, int tokens, int K,
                                                           uint8_t* __restrict__ xf, float* __restrict__ up) {
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // the product that reads these rows may start (it fetches weights until this kernel has finished)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint4* out = reinterpret_cast<uint4*>(xf + (size_t)row * K * 2);
     if (row >= tokens) {
         for (int c = tid; c < K / 8; c += 256) out[c] = make_uint4(0u, 0u, 0u, 0u);
@@ -93,6 +96,7 @@ __global__ void __launch_bounds__(256) rows_to_f16_warp_kernel(const bf16* __res
                                                                uint8_t* __restrict__ xf, float* __restrict__ up) {
     constexpr int N = K / 256;
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // as above
     if (row >= rows) return;
     const uint4* in = reinterpret_cast<const uint4*>(x + (size_t)row * K);
     uint4 v[N];
