@@ -148,6 +148,12 @@ int qd_nvfp4_expert_rows2(const void* x, const void* codes, const void* scales, 
                           int group_size, int global_per_expert, int routes_per_pass, void* scratch, int convert,
                           void* stream);
 
+/* The kernels of the chunk and batch entry points below wait, as their first instruction, for the
+ * kernel before them in the stream and are launched as its programmatic dependents, so that their
+ * launch overlaps its last blocks (512-token chunk: 32.2 -> 30.9 ms).  on = 0 launches them
+ * ordinarily: measured faster while a step is captured into a CUDA graph.  Returns the old setting. */
+int qd_set_chained_launches(int on);
+
 /* ---- Sequence forms for a chunk of prompt tokens (the 2-D branches of
  * quickdraw/kernel/triton/{norm,delta,attention,moe}.py, qwen.py:66-241): the single-token
  * arithmetic row by row.  All activations bf16 [tokens, width] contiguous. */

@@ -48,6 +48,7 @@ SIGNATURES = {
     "qd_decode_step_persistent": [P, P, P, P, I, P, P, P, P, P, I, P, P],
     "qd_exchange_bytes": [P],
     "qd_set_wait_limit_us": [ctypes.c_uint],
+    "qd_set_chained_launches": [I],
     "qd_nvfp4_gemv_bank": [P, P, P, P, P, I, I, I, I, P],
     "qd_nvfp4_matmul": [P, P, P, P, P, I, I, I, I, P, P],
     "qd_nvfp4_matmul_rows_scratch_bytes": [I],

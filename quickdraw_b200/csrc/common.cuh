@@ -177,6 +177,11 @@ QD_DEVINL void named_barrier(int id, int threads) {
 // global write, comes after grid_dependency_wait().
 QD_DEVINL void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 QD_DEVINL void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// First statement of a kernel that is launched as a programmatic dependent (qd_launch with pdl = true):
+// the next kernel of the stream may be scheduled behind this one's blocks, then the kernel waits until
+// the one before it has finished and its writes are visible.  Before this call a kernel must not touch
+// anything another kernel of the stream writes; in an ordinary launch both instructions do nothing.
+QD_DEVINL void chain_enter() { grid_launch_dependents(); grid_dependency_wait(); }
 
 QD_DEVINL uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
@@ -184,16 +189,20 @@ QD_DEVINL uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p
 #define QD_CHECK_ARG(cond) do { if (!(cond)) return QD_ERR_ARG; } while (0)
 static inline int qd_launch_status() { return cudaGetLastError() == cudaSuccess ? QD_OK : QD_ERR_LAUNCH; }
 
-// Launch helper that optionally marks the kernel as a programmatic dependent of the
-// previous one in the stream.
+// Whether kernels that open with chain_enter() are launched as programmatic dependents (qd_set_chained_launches).
+inline int& qd_chain_switch() { static int on = 1; return on; }
+
+// Launch helper that optionally marks the kernel as a programmatic dependent of the previous one in
+// the stream.  pdl: 0 = ordinary launch, 1 = dependent unless chained launches are switched off,
+// 2 = always dependent (a kernel that fetches weights before its wait).
 template <typename... KArgs, typename... Args>
 static inline int qd_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                            cudaStream_t stream, bool pdl, Args... args) {
+                            cudaStream_t stream, int pdl, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = (pdl == 2 || (pdl == 1 && qd_chain_switch())) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) == cudaSuccess ? QD_OK : QD_ERR_LAUNCH;
 }

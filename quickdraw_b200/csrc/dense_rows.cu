@@ -86,12 +86,13 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_rows_kernel(const Dens
         }
     };
     // The weights of the first chunks do not depend on the kernel before this one (the writer of the f16
-    // token rows): when launched as its programmatic dependent, the block fetches them while that kernel
-    // still runs, and only then waits for it (no effect in an ordinary launch).
+    // token rows): as its programmatic dependent the block fetches them while that kernel still runs, and
+    // only then waits for it (chain_enter() split around the fetch).
+    grid_launch_dependents();
 #pragma unroll
     for (int c = 0; c < kDenseStages; ++c)
         if (c < chunks) issue_weights(c);
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    grid_dependency_wait();
 #pragma unroll
     for (int c = 0; c < kDenseStages; ++c) {
         if (c < chunks) issue_rows(c);
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_rows_kernel(const Dens
         }
 }
 
-template <int GROUPS> int launch_dense(DenseParams p, int count, bool dependent, cudaStream_t stream) {
+template <int GROUPS> int launch_dense(DenseParams p, int count, cudaStream_t stream) {
     constexpr int smem = kDenseStages * dense_stage_bytes<GROUPS>();
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return QD_ERR_LAUNCH;
@@ -189,14 +190,7 @@ template <int GROUPS> int launch_dense(DenseParams p, int count, bool dependent,
         p.m[i].first_tile = i < count ? tiles : 0x7fffffff;
         if (i < count) tiles += (p.m[i].out_features + tile - 1) / tile;
     }
-    // after the kernel that writes the token rows: a programmatic dependent of it (see the kernel's prologue)
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)tiles); config.blockDim = dim3(kDenseThreads); config.dynamicSmemBytes = smem; config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute; config.numAttrs = dependent ? 1 : 0;
-    if (cudaLaunchKernelEx(&config, dense_rows_kernel<GROUPS>, p) != cudaSuccess) return QD_ERR_LAUNCH;
+    if (qd_launch(dense_rows_kernel<GROUPS>, dim3((unsigned)tiles), dim3(kDenseThreads), smem, stream, 2, p) != QD_OK) return QD_ERR_LAUNCH;
     return qd_launch_status();
 }
 
@@ -242,15 +236,15 @@ extern "C" int qd_nvfp4_matmul_rows3(const void* x, const void* x_up, int tokens
         rows += outs[i];
     }
     if (convert) {
-        rows_to_f16_kernel<<<kDenseTokens, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)x_up, tokens, in_features, xf, up);
+        qd_launch(rows_to_f16_kernel, dim3(kDenseTokens), dim3(256), 0, (cudaStream_t)stream, true, (const bf16*)x, (const bf16*)x_up, tokens, in_features, xf, up);
         if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     }
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // 32-row tiles while they fit one wave of the GPU (twice the blocks, half the chain), else 64-row tiles
-    return (rows + 31) / 32 > (sms > 0 ? sms : 148) ? launch_dense<4>(p, count, convert != 0, (cudaStream_t)stream)
-                                                    : launch_dense<2>(p, count, convert != 0, (cudaStream_t)stream);
+    return (rows + 31) / 32 > (sms > 0 ? sms : 148) ? launch_dense<4>(p, count, (cudaStream_t)stream)
+                                                    : launch_dense<2>(p, count, (cudaStream_t)stream);
 }
 
 // One matrix: see qd_nvfp4_matmul_rows3.

@@ -60,8 +60,11 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
     constexpr int kTokens = 8 * NT;                         // routes per pass over the tile
     constexpr int kUnits = rows_units_per_pass<K, NT>();    // copies of input rows per pass
     static_assert(kParts == 1 || kIters == 1, "one meeting buffer");
+    // chain_enter() in two parts: the wait follows the fetch of the weight tile.  What is read before it
+    // (the boundaries) was written before the conversion kernel let this one start; read past L1.
+    grid_launch_dependents();
     const int e = blockIdx.y, r0 = blockIdx.x * kRowsTile;
-    const int b0 = p.boundaries[e], b1 = p.boundaries[e + 1];
+    const int b0 = __ldcg(p.boundaries + e), b1 = __ldcg(p.boundaries + e + 1);
     if (b1 <= b0) return;
     constexpr int code_row = rows_code_row<K>(), scale_row = rows_scale_row<K>(), x_row = rows_x_unit_row<K, NT>();
     constexpr int kUnitPieces = K / 8 / kUnits;             // 16-byte pieces of an f16 input row per copy
@@ -108,7 +111,7 @@ __global__ void __launch_bounds__(kRowsThreads, RowsShape<K, NT>::kBlocksPerSM) 
             // The weights do not depend on the kernel before this one (the writer of the f16 rows): as its
             // programmatic dependent the block fetches its whole tile while that kernel still runs and
             // waits for it here; in an ordinary launch the second half of the codes follows the rows.
-            asm volatile("griddepcontrol.wait;" ::: "memory");
+            grid_dependency_wait();
             issue_x(0);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
@@ -227,14 +230,9 @@ template <int K, int NT> int launch_rows(const RowsParams& p, cudaStream_t strea
         configured[dev] = true;
     }
     constexpr int tile = RowsShape<K, NT>::kTile;
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)((p.out_features + tile - 1) / tile), (unsigned)p.experts, p.codes2 ? 2u : 1u);
-    config.blockDim = dim3(kRowsThreads); config.dynamicSmemBytes = smem; config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute; config.numAttrs = p.dependent ? 1 : 0;
-    if (cudaLaunchKernelEx(&config, expert_rows_kernel<K, NT>, p) != cudaSuccess) return QD_ERR_LAUNCH;
+    const dim3 grid((unsigned)((p.out_features + tile - 1) / tile), (unsigned)p.experts, p.codes2 ? 2u : 1u);
+    // a programmatic dependent only behind its own conversion kernel (which holds it back until the routes are grouped)
+    if (qd_launch(expert_rows_kernel<K, NT>, grid, dim3(kRowsThreads), smem, stream, p.dependent ? 2 : 0, p) != QD_OK) return QD_ERR_LAUNCH;
     return qd_launch_status();
 }
 template <int K> int launch_rows_for(const RowsParams& p, bool many, cudaStream_t stream) {
@@ -289,9 +287,9 @@ static int expert_rows(const void* x, const void* x_up, const void* codes, const
         const unsigned blocks = (unsigned)((in_rows + 7) / 8);
         uint8_t* xf = (uint8_t*)scratch;
         float* up = reinterpret_cast<float*>(xf + (size_t)in_rows * in_features * 2);
-        if (in_features == 512) rows_to_f16_warp_kernel<512><<<blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)x_up, in_rows, xf, up);
-        else if (in_features == 1024) rows_to_f16_warp_kernel<1024><<<blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)x_up, in_rows, xf, up);
-        else rows_to_f16_warp_kernel<2048><<<blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)x_up, in_rows, xf, up);
+        if (in_features == 512) qd_launch(rows_to_f16_warp_kernel<512>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, true, (const bf16*)x, (const bf16*)x_up, in_rows, xf, up);
+        else if (in_features == 1024) qd_launch(rows_to_f16_warp_kernel<1024>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, true, (const bf16*)x, (const bf16*)x_up, in_rows, xf, up);
+        else qd_launch(rows_to_f16_warp_kernel<2048>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, true, (const bf16*)x, (const bf16*)x_up, in_rows, xf, up);
         if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     }
     // Eight routes per pass unless the caller asks for 32 (one decoding of the tile for up to 32 routes,

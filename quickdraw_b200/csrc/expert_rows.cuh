@@ -67,8 +67,7 @@ namespace {
 __global__ void __launch_bounds__(256) rows_to_f16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ x_up, int tokens, int K,
                                                           uint8_t* __restrict__ xf, float* __restrict__ up) {
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // the product that reads these rows may start (it fetches weights until this kernel has finished)
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    chain_enter();            // the product that reads these rows may start: it fetches weights until this kernel has finished
     uint4* out = reinterpret_cast<uint4*>(xf + (size_t)row * K * 2);
     if (row >= tokens) {
         for (int c = tid; c < K / 8; c += 256) out[c] = make_uint4(0u, 0u, 0u, 0u);
@@ -96,7 +95,11 @@ __global__ void __launch_bounds__(256) rows_to_f16_warp_kernel(const bf16* __res
                                                                uint8_t* __restrict__ xf, float* __restrict__ up) {
     constexpr int N = K / 256;
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // as above
+    // The routed product that follows reads the routes' boundaries before its own wait, so it may only be
+    // scheduled once the kernels before this one have finished: wait first, then let it start (it fetches
+    // its weight tile while this kernel runs).
+    grid_dependency_wait();
+    grid_launch_dependents();
     if (row >= rows) return;
     const uint4* in = reinterpret_cast<const uint4*>(x + (size_t)row * K);
     uint4 v[N];

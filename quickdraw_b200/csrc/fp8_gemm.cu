@@ -21,6 +21,7 @@ constexpr size_t kF8Smem = (size_t)kF8Stages * kF8StageBytes;
 
 __global__ void __launch_bounds__(256) fp8_quantize_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ in_scale,
                                                                 uint2* __restrict__ q, long long n8) {
+    chain_enter();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n8) return;
     const float s = *in_scale;
@@ -48,6 +49,7 @@ QD_DEVINL void f8_cp16(void* dst, const void* src) {
 __global__ void __launch_bounds__(kF8Threads, 1)
 fp8_gemm_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ w, const float* __restrict__ w_scale,
                 const float* __restrict__ in_scale, bf16* __restrict__ y, int tokens, int rows, int K) {
+    chain_enter();
     extern __shared__ __align__(128) uint8_t f8_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int t0 = blockIdx.y * kF8Tile, r0 = blockIdx.x * kF8Tile;
@@ -137,7 +139,7 @@ extern "C" int qd_fp8_matmul(const void* x, const void* w, const float* w_scale,
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)q_scratch) & 15u || ((uintptr_t)y & 3u)) return QD_ERR_UNSUPPORTED;
     if (convert) {
         const long long n8 = (long long)tokens * in_features / 8;
-        fp8_quantize_rows_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        qd_launch(fp8_quantize_rows_kernel, dim3((unsigned)((n8 + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, true, 
             (const uint4*)x, in_scale, (uint2*)q_scratch, n8);
         if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     }
@@ -150,7 +152,7 @@ extern "C" int qd_fp8_matmul(const void* x, const void* w, const float* w_scale,
         configured[dev] = true;
     }
     const dim3 grid((unsigned)((out_features + kF8Tile - 1) / kF8Tile), (unsigned)((tokens + kF8Tile - 1) / kF8Tile));
-    fp8_gemm_kernel<<<grid, kF8Threads, kF8Smem, (cudaStream_t)stream>>>(
+    qd_launch(fp8_gemm_kernel, dim3(grid), dim3(kF8Threads), kF8Smem, (cudaStream_t)stream, true, 
         (const uint8_t*)q_scratch, (const uint8_t*)w, w_scale, in_scale, (bf16*)y, tokens, out_features, in_features);
     return qd_launch_status();
 }

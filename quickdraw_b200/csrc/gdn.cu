@@ -144,6 +144,7 @@ extern "C" int qd_gdn_recurrence(const void* conv_qkv, const void* a, const void
 __global__ void gdn_gated_norm_kernel(const bf16* __restrict__ o, const bf16* __restrict__ z,
                                       const bf16* __restrict__ gamma, bf16* __restrict__ out, int heads,
                                       int dv, float eps) {
+    chain_enter();
     const int head = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (head >= heads) return;
     if (dv == 128 && !(((uintptr_t)o | (uintptr_t)z | (uintptr_t)gamma | (uintptr_t)out) & 7u)) {
@@ -179,7 +180,7 @@ __global__ void gdn_gated_norm_kernel(const bf16* __restrict__ o, const bf16* __
 extern "C" int qd_gdn_gated_norm(const void* o, const void* z, const void* gamma, void* out, int heads,
                                  int value_dim, float eps, void* stream) {
     QD_CHECK_ARG(o && z && gamma && out && heads > 0 && value_dim > 0);
-    gdn_gated_norm_kernel<<<(heads + 3) / 4, 128, 0, (cudaStream_t)stream>>>(
+    qd_launch(gdn_gated_norm_kernel, dim3((heads + 3) / 4), dim3(128), 0, (cudaStream_t)stream, true, 
         (const bf16*)o, (const bf16*)z, (const bf16*)gamma, (bf16*)out, heads, value_dim, eps);
     return qd_launch_status();
 }

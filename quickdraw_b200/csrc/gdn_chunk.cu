@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(256, 2)
 gdn_chunk_prepare_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ a, const bf16* __restrict__ b,
                          const bf16* __restrict__ a_log, const bf16* __restrict__ dt_bias, float* __restrict__ scratch,
                          int tokens, int hk, int hv, int dv) {
+    chain_enter();
     extern __shared__ __align__(16) float prep_smem[];
     float* Kn = prep_smem;                     // [64][kKP]
     float* Qn = Kn + kC * kKP;
@@ -192,6 +193,7 @@ __global__ void __launch_bounds__(256, 1)
 gdn_chunk_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ a, const bf16* __restrict__ a_log,
                             const bf16* __restrict__ dt_bias, float* __restrict__ state, bf16* __restrict__ out,
                             const float* __restrict__ scratch, int tokens, int hk, int hv, int dv) {
+    chain_enter();
     extern __shared__ __align__(16) float rec_smem[];
     float* Kn = rec_smem;                      // [64 tokens][kKP]
     float* Qn = Kn + kC * kKP;
@@ -397,11 +399,11 @@ extern "C" int qd_seq_gdn_recurrence_chunked(const void* conv_qkv, const void* a
         configured[dev] = true;
     }
     const int chunks = (tokens + kC - 1) / kC;
-    gdn_chunk_prepare_kernel<<<dim3(chunks, value_heads), 256, kPrepSmem, (cudaStream_t)stream>>>(
+    qd_launch(gdn_chunk_prepare_kernel, dim3(chunks, value_heads), dim3(256), kPrepSmem, (cudaStream_t)stream, true, 
         (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, (float*)scratch,
         tokens, key_heads, value_heads, value_dim);
     if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
-    gdn_chunk_recurrence_kernel<<<dim3(value_heads, value_dim / kCols), 256, kRecSmem, (cudaStream_t)stream>>>(
+    qd_launch(gdn_chunk_recurrence_kernel, dim3(value_heads, value_dim / kCols), dim3(256), kRecSmem, (cudaStream_t)stream, true, 
         (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)a_log, (const bf16*)dt_bias, rec_state, (bf16*)out,
         (const float*)scratch, tokens, key_heads, value_heads, value_dim);
     return qd_launch_status();

@@ -158,6 +158,7 @@ struct StageRegs {
 template <int TN, bool DENSE, int AHEAD, int TM>
 __global__ void __launch_bounds__(block_threads(DENSE, TM), blocks_per_sm(TM))
 nvfp4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+    chain_enter();
     constexpr int kProducerWarps = producer_warps(DENSE, TM), kProducerThreads = group_threads(DENSE, TM);
     constexpr int kThreads = block_threads(DENSE, TM), kLoaderWarp = 1 + kProducerWarps;
     constexpr int kGroups = groups_of(TM), kStages = stages_of(TM), kTileM = TM;
@@ -452,7 +453,7 @@ static int launch_variant(const GemmParams& p, int row_tiles, cudaStream_t strea
         if (rc != QD_OK) return rc;
     }
     dim3 grid(row_tiles, (p.out_features + TN - 1) / TN);
-    return qd_launch(nvfp4_gemm_kernel<TN, DENSE, AHEAD, TM>, grid, dim3(block_threads(DENSE, TM)), smem, stream, false, p, map);
+    return qd_launch(nvfp4_gemm_kernel<TN, DENSE, AHEAD, TM>, grid, dim3(block_threads(DENSE, TM)), smem, stream, true, p, map);
 }
 
 // The widest weight tile that still gives every SM a tile (narrower tiles expand fewer weights

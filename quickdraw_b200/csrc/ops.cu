@@ -382,11 +382,13 @@ extern "C" int qd_moe_combine(const void* contributions, const int32_t* ids, con
 
 // Elementwise helpers of the composed (non-fused) step.
 __global__ void swiglu_kernel(const bf16* gate, const bf16* up, bf16* out, int n) {
+    chain_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __float2bfloat16_rn(round_bf16(silu_precise(ld_bf16(gate + i))) * ld_bf16(up + i));
 }
 // eight elements per thread (16-byte accesses)
 __global__ void swiglu8_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out, int n8) {
+    chain_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n8) return;
     const uint4 g = gate[i], u = up[i];
@@ -405,9 +407,9 @@ extern "C" int qd_swiglu(const void* gate, const void* up, void* out, int n, voi
     QD_CHECK_ARG(gate && up && out && n >= 0);
     if (n == 0) return QD_OK;
     if (n % 8 == 0 && !(((uintptr_t)gate | (uintptr_t)up | (uintptr_t)out) & 15u))
-        swiglu8_kernel<<<(n / 8 + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const uint4*)gate, (const uint4*)up, (uint4*)out, n / 8);
+        qd_launch(swiglu8_kernel, dim3((n / 8 + 255) / 256), dim3(256), 0, (cudaStream_t)stream, true, (const uint4*)gate, (const uint4*)up, (uint4*)out, n / 8);
     else
-        swiglu_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const bf16*)gate, (const bf16*)up, (bf16*)out, n);
+        qd_launch(swiglu_kernel, dim3((n + 255) / 256), dim3(256), 0, (cudaStream_t)stream, true, (const bf16*)gate, (const bf16*)up, (bf16*)out, n);
     return qd_launch_status();
 }
 
@@ -424,3 +426,15 @@ extern "C" const char* qd_error_string(int code) {
         default: return "unknown";
     }
 }
+
+// Kernels of the chunk and batch paths open with a wait for the kernel before them and are launched as
+// its programmatic dependents, so that their launch overlaps its last blocks.  on = 0 launches them
+// ordinarily (measured faster inside a captured graph, whose edges are cheaper than the overlap gains;
+// the few-row products stay dependents of their conversion kernels either way).  Returns the old setting.
+extern "C" int qd_set_chained_launches(int on) {
+    int& current = qd_chain_switch();
+    const int before = current;
+    current = on != 0;
+    return before;
+}
+

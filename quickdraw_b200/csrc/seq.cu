@@ -21,6 +21,7 @@ using qd::mma_bf16;
 __global__ void seq_add_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual,
                                     const float* __restrict__ gamma, bf16* __restrict__ normed,
                                     bf16* __restrict__ residual_out, int width, float eps) {
+    chain_enter();
     __shared__ float partial[32];
     const size_t base = (size_t)blockIdx.x * width;
     float ss = 0.f;
@@ -47,6 +48,7 @@ constexpr int kNormVecs = 2;            // 16-byte pieces per thread: 256 thread
 __global__ void __launch_bounds__(256)
 seq_add_norm8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, const float* __restrict__ gamma,
                      bf16* __restrict__ normed, bf16* __restrict__ residual_out, int width, float eps) {
+    chain_enter();
     __shared__ float partial[8];
     const size_t base = (size_t)blockIdx.x * width;
     const int tid = threadIdx.x, pieces = width / 8;
@@ -96,6 +98,7 @@ seq_add_norm8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residu
 // the width allows them.
 __global__ void seq_bf16_matmul_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
                                        int rows, int width) {
+    chain_enter();
     const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const int t = blockIdx.y;
     if (n >= rows) return;
@@ -130,6 +133,7 @@ constexpr int kTallTokens = 32, kTallMaxWidth = 3072, kTallUnroll = 2, kTallWarp
 __global__ void __launch_bounds__(kTallWarps * 32, 1)
 seq_bf16_matmul_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
                             int tokens, int rows, int width, int groups_per_block, int input_parts) {
+    chain_enter();
     extern __shared__ __align__(16) unsigned char tall_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int t0 = blockIdx.y * kTallTokens, nt_rows = min(kTallTokens, tokens - t0);
@@ -255,6 +259,7 @@ QD_DEVINL float conv_input(const bf16* __restrict__ mixed, const bf16* __restric
 }
 __global__ void seq_conv_kernel(const bf16* __restrict__ mixed, const bf16* __restrict__ taps,
                                 const bf16* __restrict__ state, bf16* __restrict__ out, int channels, int width) {
+    chain_enter();
     const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (c >= channels) return;
     float acc = 0.f;
@@ -269,6 +274,7 @@ constexpr int kConvRun = 16;
 __global__ void __launch_bounds__(128)
 seq_conv4_kernel(const bf16* __restrict__ mixed, const bf16* __restrict__ taps, const bf16* __restrict__ state,
                  bf16* __restrict__ out, int tokens, int channels) {
+    chain_enter();
     const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x), t0 = blockIdx.y * kConvRun;
     if (c >= channels) return;
     const uint2 tp0 = *reinterpret_cast<const uint2*>(taps + (size_t)c * 4), tp1 = *reinterpret_cast<const uint2*>(taps + (size_t)c * 4 + 4);
@@ -306,6 +312,7 @@ seq_conv4_kernel(const bf16* __restrict__ mixed, const bf16* __restrict__ taps, 
     }
 }
 __global__ void seq_conv_state_kernel(const bf16* __restrict__ mixed, bf16* state, int tokens, int channels, int width) {
+    chain_enter();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= channels) return;
     bf16 keep[8];
@@ -320,6 +327,7 @@ __global__ void seq_conv_state_kernel(const bf16* __restrict__ mixed, bf16* stat
 // single-token arithmetic on the sequence's own history (state_stride elements apart).
 __global__ void batch_conv_kernel(const bf16* __restrict__ mixed, const bf16* __restrict__ taps, bf16* state,
                                   bf16* __restrict__ out, int channels, int width, long long state_stride) {
+    chain_enter();
     const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
     if (c >= channels) return;
     bf16* hist = state + (size_t)b * state_stride + (size_t)c * (width - 1);
@@ -357,6 +365,7 @@ __global__ void __launch_bounds__(128)
 seq_recurrence128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ a, const bf16* __restrict__ b,
                          const bf16* __restrict__ a_log, const bf16* __restrict__ dt_bias, float* __restrict__ state,
                          bf16* __restrict__ out, int tokens, int hk, int hv, int dv, long long state_stride) {
+    chain_enter();
     constexpr int dk = 128;
     // batched decode: grid z = sequence, one token each; rows and state move on by one sequence
     if (blockIdx.z) {
@@ -478,6 +487,7 @@ __global__ void __launch_bounds__(256)
 seq_recurrence_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ a, const bf16* __restrict__ b,
                       const bf16* __restrict__ a_log, const bf16* __restrict__ dt_bias, float* __restrict__ state,
                       bf16* __restrict__ out, int tokens, int hk, int hv, int dk, int dv) {
+    chain_enter();
     __shared__ float sq[128], sk[128];
     __shared__ float part[8][32];
     __shared__ float norms[2], gates[2];
@@ -570,6 +580,7 @@ __global__ void seq_attn_prepare_kernel(const bf16* __restrict__ qg, const bf16*
                                         bf16* __restrict__ v_cache, bf16* __restrict__ q_out, int position0, int hq,
                                         int hk, int d, int rotary, float theta, float eps,
                                         const int* __restrict__ positions, long long cache_stride, int capacity) {
+    chain_enter();
     const int t = blockIdx.y, head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (head >= hq + hk) return;
     // a chunk of one sequence: consecutive positions of one cache; batched decode: row t is
@@ -626,6 +637,7 @@ __global__ void seq_attn_prepare_kernel(const bf16* __restrict__ qg, const bf16*
 __global__ void __launch_bounds__(256)
 seq_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ qg, const bf16* __restrict__ k_cache,
                 const bf16* __restrict__ v_cache, bf16* __restrict__ out, int position0, int hq, int hk, int d) {
+    chain_enter();
     const int t = blockIdx.y, kvh = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = hq / hk;
     if (warp >= G) return;
@@ -754,6 +766,7 @@ __device__ void lane_attn_finish(const LaneAttnParams& p, const float* __restric
 
 __global__ void __launch_bounds__(kLaneAttnWarps * 32)
 batch_attn_lanes_kernel(const LaneAttnParams p) {
+    chain_enter();
     extern __shared__ __align__(16) unsigned char lane_attn_smem[];
     const int G = p.hq / p.hk, D = p.d, stride = D + 2;
     bf16* qs = reinterpret_cast<bf16*>(lane_attn_smem);                                  // [G][D]
@@ -902,6 +915,7 @@ QD_DEVINL void attn_load_keys(AttnKeys& k, const uint8_t* __restrict__ base, siz
 
 __global__ void __launch_bounds__(kLaneAttnWarps * 32, 1)
 batch_attn_mma_kernel(const LaneAttnParams p) {
+    chain_enter();
     extern __shared__ __align__(16) unsigned char mma_attn_smem[];
     constexpr int D = 256;
     const int G = p.hq / p.hk, stride = D + 2;
@@ -996,6 +1010,7 @@ constexpr size_t kFlashSmem = (size_t)kFlashTokens * 8 * kAttnQRow + 2 * (size_t
 __global__ void __launch_bounds__(kFlashThreads, 1)
 seq_flash_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ qg, const bf16* __restrict__ k_cache,
                            const bf16* __restrict__ v_cache, bf16* __restrict__ out, int tokens, int position0, int hq, int hk) {
+    chain_enter();
     extern __shared__ __align__(16) unsigned char flash_smem[];
     constexpr int D = 256;
     const int G = hq / hk, kvh = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -1071,6 +1086,7 @@ seq_flash_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
 // ----------------------------------------------------------------------------- routing
 __global__ void seq_route_kernel(const bf16* __restrict__ logits, int experts, int topk, int32_t* __restrict__ ids,
                                  float* __restrict__ weights) {
+    chain_enter();
     const int t = blockIdx.x;
     qd::route_small(logits + (size_t)t * experts, experts, topk, ids + (size_t)t * topk, weights + (size_t)t * topk,
                     threadIdx.x);
@@ -1088,6 +1104,7 @@ __global__ void seq_route_kernel(const bf16* __restrict__ logits, int experts, i
 __global__ void __launch_bounds__(1024)
 seq_group_routes_kernel(const int32_t* __restrict__ ids, int routes, int experts, int32_t* __restrict__ order,
                         int32_t* __restrict__ boundaries) {
+    chain_enter();
     extern __shared__ int32_t counters[];               // [warps][experts], then first[experts + 1]
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int32_t* first = counters + warps * experts;
@@ -1145,6 +1162,7 @@ __global__ void __launch_bounds__(256)
 seq_combine_kernel(const bf16* __restrict__ contributions, const int32_t* __restrict__ ids,
                    const bf16* __restrict__ shared, const bf16* __restrict__ strength,
                    bf16* __restrict__ out, int hidden, int topk) {
+    chain_enter();
     // block = one token; slot_of[n] = the slot with the n-th smallest expert id; a thread then
     // adds eight features of the token's rows in that order (16-byte loads)
     __shared__ int slot_of[32];
@@ -1197,10 +1215,10 @@ extern "C" int qd_seq_add_rms_norm(const void* x, const void* residual, const fl
     QD_CHECK_ARG(x && gamma && normed && residual_out && tokens > 0 && width > 0);
     const uintptr_t align = (uintptr_t)x | (uintptr_t)residual | (uintptr_t)gamma | (uintptr_t)normed | (uintptr_t)residual_out;
     if (width % 8 == 0 && width <= 8 * 256 * kNormVecs && !(align & 15u))
-        seq_add_norm8_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)residual, gamma,
+        qd_launch(seq_add_norm8_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, true, (const bf16*)x, (const bf16*)residual, gamma,
                                                                        (bf16*)normed, (bf16*)residual_out, width, eps);
     else
-        seq_add_norm_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)residual, gamma,
+        qd_launch(seq_add_norm_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, true, (const bf16*)x, (const bf16*)residual, gamma,
                                                                       (bf16*)normed, (bf16*)residual_out, width, eps);
     return qd_launch_status();
 }
@@ -1238,11 +1256,11 @@ extern "C" int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tok
             launch_smem += (size_t)(parts - 1) * per_block * 4 * 32 * 16;
             if (launch_smem > (size_t)kTallTokens * (kTallMaxWidth * 2 + 16)) { parts = 1; launch_smem = smem; }
         }
-        seq_bf16_matmul_tall_kernel<<<dim3(row_blocks < sms ? row_blocks : sms, token_tiles), kTallWarps * 32, launch_smem, (cudaStream_t)stream>>>(
+        qd_launch(seq_bf16_matmul_tall_kernel, dim3(row_blocks < sms ? row_blocks : sms, token_tiles), dim3(kTallWarps * 32), launch_smem, (cudaStream_t)stream, true, 
             (const bf16*)x, (const bf16*)w, (bf16*)y, tokens, rows, width, per_block, parts);
         return qd_launch_status();
     }
-    seq_bf16_matmul_kernel<<<dim3((rows + 7) / 8, tokens), 256, 0, (cudaStream_t)stream>>>(
+    qd_launch(seq_bf16_matmul_kernel, dim3((rows + 7) / 8, tokens), dim3(256), 0, (cudaStream_t)stream, true, 
         (const bf16*)x, (const bf16*)w, (bf16*)y, rows, width);
     return qd_launch_status();
 }
@@ -1252,14 +1270,14 @@ extern "C" int qd_seq_gdn_conv(const void* mixed, const void* taps, void* conv_s
     QD_CHECK_ARG(mixed && taps && out && tokens > 0 && channels > 0 && width >= 1 && width <= 8 && (width == 1 || conv_state));
     if (tokens > 65535) return QD_ERR_UNSUPPORTED;
     if (width == 4 && channels % 2 == 0 && tokens >= kConvRun && !(((uintptr_t)mixed | (uintptr_t)out) & 3u) && !((uintptr_t)taps & 7u))
-        seq_conv4_kernel<<<dim3((channels / 2 + 127) / 128, (tokens + kConvRun - 1) / kConvRun), 128, 0, (cudaStream_t)stream>>>(
+        qd_launch(seq_conv4_kernel, dim3((channels / 2 + 127) / 128, (tokens + kConvRun - 1) / kConvRun), dim3(128), 0, (cudaStream_t)stream, true, 
             (const bf16*)mixed, (const bf16*)taps, (const bf16*)conv_state, (bf16*)out, tokens, channels);
     else
-        seq_conv_kernel<<<dim3((channels + 127) / 128, tokens), 128, 0, (cudaStream_t)stream>>>(
+        qd_launch(seq_conv_kernel, dim3((channels + 127) / 128, tokens), dim3(128), 0, (cudaStream_t)stream, true, 
             (const bf16*)mixed, (const bf16*)taps, (const bf16*)conv_state, (bf16*)out, channels, width);
     if (qd_launch_status() != QD_OK) return QD_ERR_LAUNCH;
     if (width > 1)
-        seq_conv_state_kernel<<<(channels + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
+        qd_launch(seq_conv_state_kernel, dim3((channels + 127) / 128), dim3(128), 0, (cudaStream_t)stream, true, 
             (const bf16*)mixed, (bf16*)conv_state, tokens, channels, width);
     return qd_launch_status();
 }
@@ -1271,12 +1289,12 @@ extern "C" int qd_seq_gdn_recurrence(const void* conv_qkv, const void* a, const 
     QD_CHECK_ARG(key_heads > 0 && value_heads % key_heads == 0 && key_dim > 0 && value_dim > 0);
     if (key_dim > 128) return QD_ERR_UNSUPPORTED;
     if (key_dim == 128) {
-        seq_recurrence128_kernel<<<dim3(value_heads, (value_dim + kRecCols - 1) / kRecCols), 128, 0, (cudaStream_t)stream>>>(
+        qd_launch(seq_recurrence128_kernel, dim3(value_heads, (value_dim + kRecCols - 1) / kRecCols), dim3(128), 0, (cudaStream_t)stream, true, 
             (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
             (bf16*)out, tokens, key_heads, value_heads, value_dim, 0);
         return qd_launch_status();
     }
-    seq_recurrence_kernel<<<dim3(value_heads, (value_dim + 31) / 32), 256, 0, (cudaStream_t)stream>>>(
+    qd_launch(seq_recurrence_kernel, dim3(value_heads, (value_dim + 31) / 32), dim3(256), 0, (cudaStream_t)stream, true, 
         (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
         (bf16*)out, tokens, key_heads, value_heads, key_dim, value_dim);
     return qd_launch_status();
@@ -1287,7 +1305,7 @@ extern "C" int qd_batch_gdn_conv(const void* mixed, const void* taps, void* conv
                                  void* out, int batch, int channels, int width, void* stream) {
     QD_CHECK_ARG(mixed && taps && out && batch > 0 && batch <= 65535 && channels > 0 && width >= 1 && width <= 8);
     QD_CHECK_ARG(width == 1 || (conv_state && (batch == 1 || state_stride >= (long long)channels * (width - 1))));
-    batch_conv_kernel<<<dim3((channels + 127) / 128, batch), 128, 0, (cudaStream_t)stream>>>(
+    qd_launch(batch_conv_kernel, dim3((channels + 127) / 128, batch), dim3(128), 0, (cudaStream_t)stream, true, 
         (const bf16*)mixed, (const bf16*)taps, (bf16*)conv_state, (bf16*)out, channels, width, state_stride);
     return qd_launch_status();
 }
@@ -1300,7 +1318,7 @@ extern "C" int qd_batch_gdn_recurrence(const void* conv_qkv, const void* a, cons
     QD_CHECK_ARG(key_heads > 0 && value_heads % key_heads == 0 && key_dim > 0 && value_dim > 0);
     QD_CHECK_ARG(batch == 1 || state_stride >= (long long)value_heads * key_dim * value_dim);
     if (key_dim != 128) return QD_ERR_UNSUPPORTED;
-    seq_recurrence128_kernel<<<dim3(value_heads, (value_dim + kRecCols - 1) / kRecCols, batch), 128, 0, (cudaStream_t)stream>>>(
+    qd_launch(seq_recurrence128_kernel, dim3(value_heads, (value_dim + kRecCols - 1) / kRecCols, batch), dim3(128), 0, (cudaStream_t)stream, true, 
         (const bf16*)conv_qkv, (const bf16*)a, (const bf16*)b, (const bf16*)a_log, (const bf16*)dt_bias, rec_state,
         (bf16*)out, 1, key_heads, value_heads, value_dim, state_stride);
     return qd_launch_status();
@@ -1315,7 +1333,7 @@ extern "C" int qd_seq_attention(const void* qg, const void* k_new, const void* v
     if (head_dim > 256 || head_dim % 8 != 0 || q_heads / kv_heads > 8 || rotary_dim % 64 != 0 || rotary_dim > head_dim)
         return QD_ERR_UNSUPPORTED;
     const int heads = q_heads + kv_heads;
-    seq_attn_prepare_kernel<<<dim3((heads + 7) / 8, tokens), 256, 0, (cudaStream_t)stream>>>(
+    qd_launch(seq_attn_prepare_kernel, dim3((heads + 7) / 8, tokens), dim3(256), 0, (cudaStream_t)stream, true, 
         (const bf16*)qg, (const bf16*)k_new, (const bf16*)v_new, (const bf16*)q_norm, (const bf16*)k_norm,
         (bf16*)k_cache, (bf16*)v_cache, (bf16*)q_scratch, position0, q_heads, kv_heads, head_dim, rotary_dim, theta, eps,
         nullptr, 0, capacity);
@@ -1330,12 +1348,11 @@ extern "C" int qd_seq_attention(const void* qg, const void* k_new, const void* v
                 return QD_ERR_LAUNCH;
             flash_configured[dev] = true;
         }
-        seq_flash_attention_kernel<<<dim3((tokens + kFlashTokens - 1) / kFlashTokens, kv_heads), kFlashThreads, kFlashSmem,
-                                     (cudaStream_t)stream>>>((const bf16*)q_scratch, (const bf16*)qg, (const bf16*)k_cache,
+        qd_launch(seq_flash_attention_kernel, dim3((tokens + kFlashTokens - 1) / kFlashTokens, kv_heads), dim3(kFlashThreads), kFlashSmem, (cudaStream_t)stream, true, (const bf16*)q_scratch, (const bf16*)qg, (const bf16*)k_cache,
                                                              (const bf16*)v_cache, (bf16*)out, tokens, position0, q_heads, kv_heads);
         return qd_launch_status();
     }
-    seq_attn_kernel<<<dim3(kv_heads, tokens), 256, 0, (cudaStream_t)stream>>>(
+    qd_launch(seq_attn_kernel, dim3(kv_heads, tokens), dim3(256), 0, (cudaStream_t)stream, true, 
         (const bf16*)q_scratch, (const bf16*)qg, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, position0,
         q_heads, kv_heads, head_dim);
     return qd_launch_status();
@@ -1359,7 +1376,7 @@ extern "C" int qd_batch_attention(const void* qg, const void* k_new, const void*
     const uintptr_t align = (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q_scratch;
     if ((align & 15u) || (cache_stride & 7)) return QD_ERR_UNSUPPORTED;
     const int heads = q_heads + kv_heads;
-    seq_attn_prepare_kernel<<<dim3((heads + 7) / 8, batch), 256, 0, (cudaStream_t)stream>>>(
+    qd_launch(seq_attn_prepare_kernel, dim3((heads + 7) / 8, batch), dim3(256), 0, (cudaStream_t)stream, true, 
         (const bf16*)qg, (const bf16*)k_new, (const bf16*)v_new, (const bf16*)q_norm, (const bf16*)k_norm,
         (bf16*)k_cache, (bf16*)v_cache, (bf16*)q_scratch, 0, q_heads, kv_heads, head_dim, rotary_dim, theta, eps,
         positions, cache_stride, capacity);
@@ -1387,10 +1404,10 @@ extern "C" int qd_batch_attention(const void* qg, const void* k_new, const void*
                 return QD_ERR_LAUNCH;
             mma_configured[dev] = true;
         }
-        batch_attn_mma_kernel<<<dim3(kv_heads, splits, batch), kLaneAttnWarps * 32, mma_smem, (cudaStream_t)stream>>>(p);
+        qd_launch(batch_attn_mma_kernel, dim3(kv_heads, splits, batch), dim3(kLaneAttnWarps * 32), mma_smem, (cudaStream_t)stream, true, p);
         return qd_launch_status();
     }
-    batch_attn_lanes_kernel<<<dim3(kv_heads, splits, batch), kLaneAttnWarps * 32, smem, (cudaStream_t)stream>>>(p);
+    qd_launch(batch_attn_lanes_kernel, dim3(kv_heads, splits, batch), dim3(kLaneAttnWarps * 32), smem, (cudaStream_t)stream, true, p);
     return qd_launch_status();
 }
 
@@ -1398,7 +1415,7 @@ extern "C" int qd_seq_route_topk(const void* logits, int tokens, int experts, in
                                  void* stream) {
     QD_CHECK_ARG(logits && ids && weights && tokens > 0 && topk >= 1 && topk <= 32 && topk <= experts);
     if (experts > 256) return QD_ERR_UNSUPPORTED;
-    seq_route_kernel<<<tokens, 32, 0, (cudaStream_t)stream>>>((const bf16*)logits, experts, topk, ids, weights);
+    qd_launch(seq_route_kernel, dim3(tokens), dim3(32), 0, (cudaStream_t)stream, true, (const bf16*)logits, experts, topk, ids, weights);
     return qd_launch_status();
 }
 
@@ -1410,7 +1427,7 @@ extern "C" int qd_seq_group_routes(const int32_t* ids, int routes, int experts, 
     int warps = 32;
     while (warps > 1 && (size_t)warps * experts * 4 > 40960) warps >>= 1;
     const size_t smem = ((size_t)warps * experts + experts + 1) * sizeof(int32_t);
-    seq_group_routes_kernel<<<1, warps * 32, smem, (cudaStream_t)stream>>>(ids, routes, experts, order, boundaries);
+    qd_launch(seq_group_routes_kernel, dim3(1), dim3(warps * 32), smem, (cudaStream_t)stream, true, ids, routes, experts, order, boundaries);
     return qd_launch_status();
 }
 
@@ -1418,7 +1435,7 @@ extern "C" int qd_seq_moe_combine(const void* contributions, const int32_t* ids,
                                   const void* strength, void* out, int tokens, int hidden, int topk, void* stream) {
     QD_CHECK_ARG(contributions && ids && shared && strength && out && tokens > 0 && hidden > 0 && topk > 0);
     if (topk > 32) return QD_ERR_UNSUPPORTED;
-    seq_combine_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>(
+    qd_launch(seq_combine_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, true, 
         (const bf16*)contributions, ids, (const bf16*)shared, (const bf16*)strength, (bf16*)out, hidden, topk);
     return qd_launch_status();
 }
