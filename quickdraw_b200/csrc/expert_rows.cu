@@ -40,7 +40,7 @@ template <int K, int NT> struct RowsShape {
     static constexpr int kIters = (K <= 512 && NT == 1) ? 2 : 1;
     static constexpr int kGroups = 8 / kParts;
     static constexpr int kTile = 16 * kGroups * kIters;
-    static constexpr int kBlocksPerSM = NT == 1 ? 2 : 1;
+    static constexpr int kBlocksPerSM = (NT == 1 || K <= 512) ? 2 : 1;
 };
 
 // The f16 input rows of a pass go through two buffers: a pass's rows in halves of the inputs (one half is

@@ -184,10 +184,13 @@ class ChunkPrefill:
             # the f16 copy of the input rows is shared by the products of the same input (gate, up)
             scratch, source = self._expert_rows_scratch(routes // topk if by_token else routes, bank.in_features)
             fresh = x_up is not None or source is not x
+            # 512 inputs (the down product) and eight or more routes per expert: 32 routes per decoding of a tile
+            # (measured at 16 routes per expert: 91 against 105 us; the 2048-input products: 245 against 201 us)
+            per_pass = self.ROUTES_PER_PASS or (32 if bank.in_features == 512 and routes >= 8 * (self.total_experts or experts) else 0)
             call("qd_nvfp4_expert_rows", ptr(x), ptr(x_up), ptr(bank.weight), ptr(bank.weight_scale), ptr(bank.weight_scale_2),
                  ptr(order), ptr(boundaries), ptr(routing), ptr(out), routes, experts, topk, bank.out_features,
                  bank.in_features, bank.group_size, int(by_token), int(scatter),
-                 int(bank.weight_scale_2.numel() != 1), self.ROUTES_PER_PASS, ptr(scratch), int(fresh), stream_of(x))
+                 int(bank.weight_scale_2.numel() != 1), per_pass, ptr(scratch), int(fresh), stream_of(x))
             self._expert_scratch[bank.in_features] = (scratch, None if x_up is not None else x)
             return out
         if x_up is not None:
