@@ -161,6 +161,9 @@ int qd_seq_add_rms_norm(const void* x, const void* residual, const float* gamma,
                         void* residual_out, int tokens, int width, float eps, void* stream);
 /* y[t, n] = bf16(x[t] . w[n]) for a small bf16 matrix (router, shared gate, DeltaNet a / b). */
 int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tokens, int rows, int width, void* stream);
+/* Two such matrices of the same input in one launch (a and b; router and shared gate). */
+int qd_seq_bf16_matmul2(const void* x, const void* w0, void* y0, int rows0, const void* w1, void* y1, int rows1,
+                        int tokens, int width, void* stream);
 /* short convolution walked along the chunk; conv_state ends with the last width - 1 inputs */
 int qd_seq_gdn_conv(const void* mixed, const void* taps, void* conv_state, void* out, int tokens,
                     int channels, int width, void* stream);

@@ -62,6 +62,7 @@ SIGNATURES = {
     "qd_nvfp4_expert_rows": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P],
     "qd_seq_add_rms_norm": [P, P, P, P, P, I, I, F, P],
     "qd_seq_bf16_matmul": [P, P, P, I, I, I, P],
+    "qd_seq_bf16_matmul2": [P, P, P, I, P, P, I, I, I, P],
     "qd_seq_gdn_conv": [P, P, P, P, I, I, I, P],
     "qd_seq_gdn_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, P],
     "qd_seq_gdn_chunk_scratch_bytes": [I, I],

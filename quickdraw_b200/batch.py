@@ -86,7 +86,7 @@ class BatchDecode(ChunkPrefill):
         batch = x.shape[0]
         hv, dv = c.linear_num_value_heads, c.linear_value_head_dim
         qkv, z = self._matmul_many(x, [w.in_proj_qkv, w.in_proj_z])
-        a, b = self._small(x, w.in_proj_a), self._small(x, w.in_proj_b)
+        a, b = self._small_pair(x, w.in_proj_a, w.in_proj_b)
         conv = torch.empty_like(qkv)
         conv_state, rec_state = state.conv_state[:, index], state.rec_state[:, index]
         call("qd_batch_gdn_conv", ptr(qkv), ptr(w.conv1d), ptr(conv_state[0]), conv_state.stride(0), ptr(conv),

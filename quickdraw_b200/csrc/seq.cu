@@ -96,11 +96,17 @@ seq_add_norm8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residu
 // --------------------------------------------------- small bf16 projection of every token
 // y[t, n] = bf16( sum_k x[t, k] w[n, k] ): one warp per (token, output row), 16-byte loads where
 // the width allows them.
+// A second matrix of the same input (w1, y1, rows1; or NULL) takes the blocks from first_block1 on.
 __global__ void seq_bf16_matmul_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
-                                       int rows, int width) {
+                                       int rows, int width, const bf16* __restrict__ w1, bf16* __restrict__ y1, int rows1,
+                                       int first_block1) {
     chain_enter();
-    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    const int t = blockIdx.y;
+    const int lane = threadIdx.x & 31, t = blockIdx.y;
+    int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w1 && (int)blockIdx.x >= first_block1) {
+        n -= first_block1 * (blockDim.x >> 5);
+        w = w1; y = y1; rows = rows1;
+    }
     if (n >= rows) return;
     const bf16* row = w + (size_t)n * width;
     const bf16* xt = x + (size_t)t * width;
@@ -1260,8 +1266,24 @@ extern "C" int qd_seq_bf16_matmul(const void* x, const void* w, void* y, int tok
             (const bf16*)x, (const bf16*)w, (bf16*)y, tokens, rows, width, per_block, parts);
         return qd_launch_status();
     }
-    qd_launch(seq_bf16_matmul_kernel, dim3((rows + 7) / 8, tokens), dim3(256), 0, (cudaStream_t)stream, true, 
-        (const bf16*)x, (const bf16*)w, (bf16*)y, rows, width);
+    qd_launch(seq_bf16_matmul_kernel, dim3((rows + 7) / 8, tokens), dim3(256), 0, (cudaStream_t)stream, true,
+              (const bf16*)x, (const bf16*)w, (bf16*)y, rows, width, (const bf16*)nullptr, (bf16*)nullptr, 0, 0);
+    return qd_launch_status();
+}
+
+// Two small matrices of the same input in one launch (the a and b projections of a DeltaNet layer, the
+// router and the shared-expert gate: quickdraw/models/qwen.py:120-131, 165-170); shapes that
+// qd_seq_bf16_matmul gives to the tensor-core form go there one after the other.
+extern "C" int qd_seq_bf16_matmul2(const void* x, const void* w0, void* y0, int rows0, const void* w1, void* y1, int rows1,
+                                   int tokens, int width, void* stream) {
+    QD_CHECK_ARG(x && w0 && y0 && w1 && y1 && tokens > 0 && rows0 > 0 && rows1 > 0 && width > 0);
+    if (rows0 >= 4096 || rows1 >= 4096 || tokens >= 64 || tokens > 65535) {
+        const int first = qd_seq_bf16_matmul(x, w0, y0, tokens, rows0, width, stream);
+        return first != QD_OK ? first : qd_seq_bf16_matmul(x, w1, y1, tokens, rows1, width, stream);
+    }
+    const int blocks0 = (rows0 + 7) / 8, blocks1 = (rows1 + 7) / 8;
+    qd_launch(seq_bf16_matmul_kernel, dim3(blocks0 + blocks1, tokens), dim3(256), 0, (cudaStream_t)stream, true,
+              (const bf16*)x, (const bf16*)w0, (bf16*)y0, rows0, width, (const bf16*)w1, (bf16*)y1, rows1, blocks0);
     return qd_launch_status();
 }
 

@@ -135,6 +135,13 @@ class ChunkPrefill:
         call("qd_seq_bf16_matmul", ptr(x), ptr(weight), ptr(out), x.shape[0], rows, x.shape[1], stream_of(x))
         return out
 
+    def _small_pair(self, x, weight0, weight1):
+        """Two small bf16 projections of the same input in one launch."""
+        out0, out1 = self._empty(x.shape[0], weight0.shape[0]), self._empty(x.shape[0], weight1.shape[0])
+        call("qd_seq_bf16_matmul2", ptr(x), ptr(weight0), ptr(out0), weight0.shape[0], ptr(weight1), ptr(out1), weight1.shape[0],
+             x.shape[0], x.shape[1], stream_of(x))
+        return out0, out1
+
     def _add_norm(self, x, residual, gamma, eps):
         normed, new_residual = torch.empty_like(x), torch.empty_like(x)
         call("qd_seq_add_rms_norm", ptr(x), ptr(residual), ptr(gamma), ptr(normed), ptr(new_residual),
@@ -207,7 +214,7 @@ class ChunkPrefill:
         tokens = x.shape[0]
         hv, dv = c.linear_num_value_heads, c.linear_value_head_dim
         qkv, z = self._matmul_many(x, [w.in_proj_qkv, w.in_proj_z])
-        a, b = self._small(x, w.in_proj_a), self._small(x, w.in_proj_b)
+        a, b = self._small_pair(x, w.in_proj_a, w.in_proj_b)
         conv = torch.empty_like(qkv)
         call("qd_seq_gdn_conv", ptr(qkv), ptr(w.conv1d), ptr(state.conv_state[index]), ptr(conv), tokens,
              qkv.shape[1], c.linear_conv_kernel_dim, stream_of(x))
@@ -244,7 +251,7 @@ class ChunkPrefill:
     def _moe(self, w, x):
         c = self.ckpt.config
         tokens, topk = x.shape[0], c.num_experts_per_tok
-        logits, strength = self._small(x, w.router), self._small(x, w.shared_expert_gate)
+        logits, strength = self._small_pair(x, w.router, w.shared_expert_gate)
         ids = self._empty(tokens, topk, dtype=torch.int32)
         weights = self._empty(tokens, topk, dtype=torch.float32)
         call("qd_seq_route_topk", ptr(logits), tokens, c.num_experts, topk, ptr(ids), ptr(weights), stream_of(x))

@@ -88,12 +88,20 @@ def test_batched_state_kernels_equal_single_sequence_kernels(cuda_device):
 def test_tall_projection_equals_row_by_row(cuda_device):
     from quickdraw_b200._lib import call, ptr, stream_of
     src = synthetic.Source(29, cuda_device)
-    for tokens, rows, width in ((5, 4100, 2048), (33, 4096, 512), (32, 4112, 320), (200, 1, 2048), (130, 32, 2048), (64, 256, 2048), (70, 40, 192)):
+    for tokens, rows, width in ((3, 40, 2048), (32, 257, 1024), (5, 4100, 2048), (33, 4096, 512), (32, 4112, 320), (200, 1, 2048), (130, 32, 2048), (64, 256, 2048), (70, 40, 192)):
         x, w = src.normal(f"x{tokens}", tokens, width), src.normal(f"w{rows}", rows, width, std=0.05)
         y = torch.empty(tokens, rows, dtype=torch.bfloat16, device=cuda_device)
         call("qd_seq_bf16_matmul", ptr(x), ptr(w), ptr(y), tokens, rows, width, stream_of(x))
         want = (x.double() @ w.double().T)
         assert O.rel_l2(y.cpu().double(), want.cpu()) < 4e-3
+        # a second matrix of the same input in the same launch (or one after the other in the tall form): the same bits
+        rows1 = 19
+        w1 = src.normal(f"v{width}", rows1, width, std=0.05)
+        y0, y1, alone = torch.empty_like(y), torch.empty(tokens, rows1, dtype=torch.bfloat16, device=cuda_device), None
+        call("qd_seq_bf16_matmul2", ptr(x), ptr(w), ptr(y0), rows, ptr(w1), ptr(y1), rows1, tokens, width, stream_of(x))
+        alone = torch.empty_like(y1)
+        call("qd_seq_bf16_matmul", ptr(x), ptr(w1), ptr(alone), tokens, rows1, width, stream_of(x))
+        assert torch.equal(y0, y) and torch.equal(y1, alone)
 
 
 def test_batch_decode_follows_independent_sequences(cuda_device):
