@@ -1135,8 +1135,19 @@ seq_group_routes_kernel(const int32_t* __restrict__ ids, int routes, int experts
     }
     if (threadIdx.x == 0) first[0] = 0;
     __syncthreads();
-    if (threadIdx.x == 0)
-        for (int e = 0; e < experts; ++e) first[e + 1] += first[e];
+    if (warp == 0) {      // inclusive scan by one warp: a lane adds up its run of experts, the runs are scanned with shuffles
+        const int run = (experts + 31) / 32, lo = min(experts, lane * run), hi = min(experts, lo + run);
+        int sum = 0;
+        for (int e = lo; e < hi; ++e) sum += first[e + 1];
+        int inclusive = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int below = __shfl_up_sync(0xffffffffu, inclusive, d);
+            if (lane >= d) inclusive += below;
+        }
+        int running = inclusive - sum;
+        for (int e = lo; e < hi; ++e) { running += first[e + 1]; first[e + 1] = running; }
+    }
     __syncthreads();
     for (int e = threadIdx.x; e <= experts; e += blockDim.x) boundaries[e] = first[e];
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
