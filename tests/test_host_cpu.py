@@ -36,6 +36,31 @@ def test_binding_table_covers_the_header():
     assert set(declared_symbols()) == set(_lib.exported_symbols())
 
 
+def test_binding_argument_types_follow_the_header():
+    """Every ctypes signature has the header's parameters, in order: pointers, int, unsigned, float, long long."""
+    import ctypes
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    kinds = {ctypes.c_void_p: "pointer", ctypes.c_int: "int", ctypes.c_float: "float", ctypes.c_longlong: "long long",
+             ctypes.c_uint: "unsigned int"}
+    checked = 0
+    for result, name, params in re.findall(r"\b(int|long long|const char\*)\s+(qd_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", text):
+        if name == "qd_error_string":
+            continue
+        declared = []
+        for param in (piece.strip() for piece in params.split(",")):
+            if param in ("", "void"):
+                continue
+            if "*" in param:
+                declared.append("pointer")
+            else:
+                declared.append(re.sub(r"\s+\w+$", "", param).replace("const ", "").strip())
+        bound = [kinds[t] for t in _lib.SIGNATURES[name]]
+        assert bound == declared, (name, bound, declared)
+        assert (name in _lib.LONG_RESULTS) == (result == "long long"), name
+        checked += 1
+    assert checked == len(_lib.SIGNATURES)
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "_lib", None)
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libquickdraw_b200.so")
