@@ -235,6 +235,11 @@ int qd_seq_group_routes(const int32_t* ids, int routes, int experts, int32_t* or
  * [tokens, hidden], strength bf16 [tokens] */
 int qd_seq_moe_combine(const void* contributions, const int32_t* ids, const void* shared,
                        const void* strength, void* out, int tokens, int hidden, int topk, void* stream);
+/* qd_seq_moe_combine followed by qd_seq_add_rms_norm(x = its output, residual, gamma) in one launch;
+ * hidden a multiple of 8, at most 4096, else QD_ERR_UNSUPPORTED. */
+int qd_seq_moe_combine_norm(const void* contributions, const int32_t* ids, const void* shared, const void* strength,
+                            const void* residual, const float* gamma, void* normed, void* residual_out,
+                            int tokens, int hidden, int topk, float eps, void* stream);
 
 /* expert_gemv(x, proj, ids, weights=None) — quickdraw/kernel/cute/matvec.py:152-154,
  * quickdraw/kernel/triton/matvec.py:84-99.  Bank [E, rows, in/2]; y [slots, rows];

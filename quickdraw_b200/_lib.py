@@ -75,6 +75,7 @@ SIGNATURES = {
     "qd_batch_attention": [P, P, P, P, P, P, P, L, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
     "qd_seq_group_routes": [P, I, I, P, P, P],
     "qd_seq_moe_combine": [P, P, P, P, P, I, I, I, P],
+    "qd_seq_moe_combine_norm": [P, P, P, P, P, P, P, P, I, I, I, F, P],
 }
 
 LONG_RESULTS = {"qd_decode_workspace_bytes", "qd_program_bytes", "qd_exchange_bytes",

@@ -124,9 +124,10 @@ class BatchDecode(ChunkPrefill):
         if not positions_checked:
             assert int(state.positions.max().item()) < state.max_context, "a sequence has filled its cache"
         x = self.ckpt.embed_tokens[tokens].contiguous()
-        residual = None
-        for layer, (gamma_in, gamma_post) in zip(self.ckpt.layers, self.gammas):
-            normed, residual = self._add_norm(x, residual, gamma_in, c.rms_norm_eps)
+        normed, residual = self._add_norm(x, None, self.gammas[0][0], c.rms_norm_eps)
+        # the norm after a layer's MoE block (in front of the next layer, or the final one) rides on its combine
+        following = [gamma_in for gamma_in, _ in self.gammas[1:]] + [self.final_gamma]
+        for (layer, (_, gamma_post)), gamma_next in zip(zip(self.ckpt.layers, self.gammas), following):
             if layer.layer_type == "full_attention":
                 index = sum(1 for k in c.layer_types[:layer.idx] if k == "full_attention")
                 mixed = self._attention_batch(layer.attn, normed, state, index)
@@ -134,8 +135,8 @@ class BatchDecode(ChunkPrefill):
                 index = sum(1 for k in c.layer_types[:layer.idx] if k != "full_attention")
                 mixed = self._delta_net_batch(layer.attn, normed, state, index)
             normed, residual = self._add_norm(mixed, residual, gamma_post, c.rms_norm_eps)
-            x = self._moe(layer.moe, normed)
-        final, _ = self._add_norm(x, residual, self.final_gamma, c.rms_norm_eps)
+            normed, residual = self._moe(layer.moe, normed, follow=(residual, gamma_next))
+        final = normed
         head = self.ckpt.lm_head
         logits = self._small(final, head) if isinstance(head, torch.Tensor) else self._matmul(final, head)   # bf16 / NVFP4 head
         if self.vocab_range is not None and logits.shape[1] != c.vocab_size:

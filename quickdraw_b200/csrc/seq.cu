@@ -1225,6 +1225,81 @@ seq_combine_kernel(const bf16* __restrict__ contributions, const int32_t* __rest
     }
 }
 
+// The combine above followed by the residual add + RMSNorm in front of the next layer (seq_add_norm8_kernel),
+// a token per block: thread tid holds the same eight features (pieces tid and tid + 256) in both, so the
+// layer output never goes to memory.  normed / residual_out as seq_add_norm8_kernel writes them for
+// x = the combine's bf16 output.  hidden a multiple of 8, at most 4096.
+__global__ void __launch_bounds__(256)
+seq_combine_norm_kernel(const bf16* __restrict__ contributions, const int32_t* __restrict__ ids,
+                        const bf16* __restrict__ shared, const bf16* __restrict__ strength,
+                        const bf16* __restrict__ residual, const float* __restrict__ gamma,
+                        bf16* __restrict__ normed, bf16* __restrict__ residual_out, int hidden, int topk, float eps) {
+    chain_enter();
+    __shared__ int slot_of[32];
+    __shared__ float partial[8];
+    const int t = blockIdx.x, tid = threadIdx.x, pieces = hidden / 8;
+    const int32_t* my = ids + (size_t)t * topk;
+    if (tid < topk) {
+        const int e = my[tid];
+        int rank = 0;
+        for (int s = 0; s < topk; ++s) { const int o = my[s]; rank += (o < e) || (o == e && s < tid); }
+        slot_of[rank] = tid;
+    }
+    __syncthreads();
+    const bf16* rows = contributions + (size_t)t * topk * hidden;
+    const float gate = round_bf16(sigmoid_precise(ld_bf16(strength + t)));
+    const size_t base = (size_t)t * hidden;
+    float v[kNormVecs][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kNormVecs; ++k) {
+        const int c = tid + k * 256;
+        if (c >= pieces) break;
+        float routed[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+        for (int n = 0; n < topk; ++n) {
+            const uint4 row = *reinterpret_cast<const uint4*>(rows + (size_t)slot_of[n] * hidden + 8 * c);
+            const uint32_t w[4] = {row.x, row.y, row.z, row.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { routed[2 * q] += bf16_bits_to_float(w[q] & 0xffffu); routed[2 * q + 1] += bf16_bits_to_float(w[q] >> 16); }
+        }
+        const uint4 sh = *reinterpret_cast<const uint4*>(shared + base + 8 * c);
+        const uint4 r = *reinterpret_cast<const uint4*>(residual + base + 8 * c);
+        const uint32_t sw[4] = {sh.x, sh.y, sh.z, sh.w}, rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            // the layer output as the combine rounds it, then the sum with the residual as the norm kernel forms it
+            const float lo = round_bf16(round_bf16(routed[2 * q]) + round_bf16(bf16_bits_to_float(sw[q] & 0xffffu) * gate));
+            const float hi = round_bf16(round_bf16(routed[2 * q + 1]) + round_bf16(bf16_bits_to_float(sw[q] >> 16) * gate));
+            v[k][2 * q] = lo + __uint_as_float(rw[q] << 16);
+            v[k][2 * q + 1] = hi + __uint_as_float(rw[q] & 0xffff0000u);
+            ss += v[k][2 * q] * v[k][2 * q] + v[k][2 * q + 1] * v[k][2 * q + 1];
+        }
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) partial[tid >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += partial[w];
+    const float inv = rsqrtf(total / (float)hidden + eps);
+#pragma unroll
+    for (int k = 0; k < kNormVecs; ++k) {
+        const int c = tid + k * 256;
+        if (c >= pieces) break;
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + 8 * c), g1 = *reinterpret_cast<const float4*>(gamma + 8 * c + 4);
+        const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        uint32_t n[4], o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            n[q] = qd::pack_bf16x2((v[k][2 * q] * inv) * gm[2 * q], (v[k][2 * q + 1] * inv) * gm[2 * q + 1]);
+            o[q] = qd::pack_bf16x2(v[k][2 * q], v[k][2 * q + 1]);
+        }
+        *reinterpret_cast<uint4*>(normed + base + 8 * c) = make_uint4(n[0], n[1], n[2], n[3]);
+        *reinterpret_cast<uint4*>(residual_out + base + 8 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 }  // namespace
 
 extern "C" int qd_seq_add_rms_norm(const void* x, const void* residual, const float* gamma, void* normed,
@@ -1472,3 +1547,21 @@ extern "C" int qd_seq_moe_combine(const void* contributions, const int32_t* ids,
         (const bf16*)contributions, ids, (const bf16*)shared, (const bf16*)strength, (bf16*)out, hidden, topk);
     return qd_launch_status();
 }
+
+// qd_seq_moe_combine followed by qd_seq_add_rms_norm(x = its output, residual, gamma) in one launch: the
+// end of a layer and the norm in front of the next one (quickdraw/models/qwen.py:189-194, 203-207).
+// hidden a multiple of 8, at most 4096, 16-byte aligned rows; QD_ERR_UNSUPPORTED otherwise.
+extern "C" int qd_seq_moe_combine_norm(const void* contributions, const int32_t* ids, const void* shared, const void* strength,
+                                       const void* residual, const float* gamma, void* normed, void* residual_out,
+                                       int tokens, int hidden, int topk, float eps, void* stream) {
+    QD_CHECK_ARG(contributions && ids && shared && strength && residual && gamma && normed && residual_out);
+    QD_CHECK_ARG(tokens > 0 && hidden > 0 && topk > 0);
+    if (topk > 32 || hidden % 8 != 0 || hidden > 8 * 256 * kNormVecs) return QD_ERR_UNSUPPORTED;
+    if (((uintptr_t)contributions | (uintptr_t)shared | (uintptr_t)residual | (uintptr_t)gamma | (uintptr_t)normed | (uintptr_t)residual_out) & 15u)
+        return QD_ERR_UNSUPPORTED;
+    qd_launch(seq_combine_norm_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, true,
+              (const bf16*)contributions, ids, (const bf16*)shared, (const bf16*)strength, (const bf16*)residual, gamma,
+              (bf16*)normed, (bf16*)residual_out, hidden, topk, eps);
+    return qd_launch_status();
+}
+

@@ -248,7 +248,9 @@ class ChunkPrefill:
              c.rope_theta, c.rms_norm_eps, stream_of(x))
         return self._matmul(out, w.o_proj)
 
-    def _moe(self, w, x):
+    def _moe(self, w, x, follow=None):
+        """The MoE block; with ``follow`` = (residual, gamma of the next norm) the residual add and RMSNorm in front
+        of the next layer run in the combine's launch and (normed, new residual) is returned."""
         c = self.ckpt.config
         tokens, topk = x.shape[0], c.num_experts_per_tok
         logits, strength = self._small_pair(x, w.router, w.shared_expert_gate)
@@ -272,10 +274,16 @@ class ChunkPrefill:
             dist.all_reduce(contributions, group=self.group)
         shared_gate, shared_up = self._matmul_many(x, [w.shared_gate, w.shared_up])
         shared = self._matmul(shared_gate, w.shared_down, x_up=shared_up)
+        if follow is not None and x.shape[1] % 8 == 0 and x.shape[1] <= 4096:
+            residual, gamma = follow
+            normed, new_residual = torch.empty_like(x), torch.empty_like(x)
+            call("qd_seq_moe_combine_norm", ptr(contributions), ptr(ids), ptr(shared), ptr(strength), ptr(residual), ptr(gamma),
+                 ptr(normed), ptr(new_residual), tokens, x.shape[1], topk, c.rms_norm_eps, stream_of(x))
+            return normed, new_residual
         out = torch.empty_like(x)
         call("qd_seq_moe_combine", ptr(contributions), ptr(ids), ptr(shared), ptr(strength), ptr(out), tokens,
              x.shape[1], topk, stream_of(x))
-        return out
+        return out if follow is None else self._add_norm(out, follow[0], follow[1], c.rms_norm_eps)
 
     # ------------------------------------------------------------------------------ run
     @torch.inference_mode()
@@ -285,17 +293,19 @@ class ChunkPrefill:
         assert token_ids.ndim == 1 and token_ids.dtype == torch.long and token_ids.is_cuda
         assert 0 <= position0 and position0 + token_ids.numel() <= state.kv_k.shape[1]
         x = self.ckpt.embed_tokens[token_ids].contiguous()
-        residual = None
-        for layer, (gamma_in, gamma_post) in zip(self.ckpt.layers, self.gammas):
-            normed, residual = self._add_norm(x, residual, gamma_in, c.rms_norm_eps)
+        normed, residual = self._add_norm(x, None, self.gammas[0][0], c.rms_norm_eps)
+        for number, (layer, (_, gamma_post)) in enumerate(zip(self.ckpt.layers, self.gammas)):
             if layer.layer_type == "full_attention":
                 index = sum(1 for k in c.layer_types[:layer.idx] if k == "full_attention")
                 mixed = self._attention(layer.attn, normed, state, index, position0)
             else:
                 index = sum(1 for k in c.layer_types[:layer.idx] if k != "full_attention")
                 mixed = self._delta_net(layer.attn, normed, state, index)
+            if number + 1 == len(self.ckpt.layers):
+                break             # the chunk step returns nothing: behind the last mixer no state is written
             normed, residual = self._add_norm(mixed, residual, gamma_post, c.rms_norm_eps)
-            x = self._moe(layer.moe, normed)
+            # the norm in front of the next layer rides on the combine
+            normed, residual = self._moe(layer.moe, normed, follow=(residual, self.gammas[number + 1][0]))
 
     def check(self) -> int:
         """Status word of the tensor-core products (0 = clean)."""

@@ -229,3 +229,27 @@ def test_group_routes_is_the_stable_sort_by_expert(cuda_device, routes, experts)
     sorted_ids, want_order = ids.sort(stable=True)
     want_boundaries = torch.searchsorted(sorted_ids, torch.arange(experts + 1, device=cuda_device, dtype=torch.int32))
     assert torch.equal(order.long(), want_order) and torch.equal(boundaries.long(), want_boundaries)
+
+
+@pytest.mark.parametrize("tokens,hidden,topk", [(5, 2048, 8), (33, 4096, 2), (1, 520, 3)])
+def test_combine_with_the_next_norm_equals_the_two_calls(cuda_device, tokens, hidden, topk):
+    """The MoE combine with the residual add + RMSNorm of the next layer in its launch: the same bits as
+    qd_seq_moe_combine followed by qd_seq_add_rms_norm."""
+    from quickdraw_b200._lib import call, ptr, stream_of
+    src = synthetic.Source(43, cuda_device)
+    contributions = src.normal("c", tokens * topk, hidden)
+    shared, residual = src.normal("s", tokens, hidden), src.normal("r", tokens, hidden)
+    strength = src.normal("g", tokens, 1)
+    gamma = (1 + src.normal("w", hidden, std=0.1).float()).contiguous()
+    gen = torch.Generator().manual_seed(tokens)
+    ids = torch.stack([torch.randperm(64, generator=gen)[:topk] for _ in range(tokens)]).to(torch.int32).to(cuda_device)
+    out, normed, new_residual = (torch.empty(tokens, hidden, dtype=torch.bfloat16, device=cuda_device) for _ in range(3))
+    fused_normed, fused_residual = torch.empty_like(normed), torch.empty_like(normed)
+    call("qd_seq_moe_combine", ptr(contributions), ptr(ids), ptr(shared), ptr(strength), ptr(out), tokens, hidden, topk,
+         stream_of(out))
+    call("qd_seq_add_rms_norm", ptr(out), ptr(residual), ptr(gamma), ptr(normed), ptr(new_residual), tokens, hidden, 1e-6,
+         stream_of(out))
+    call("qd_seq_moe_combine_norm", ptr(contributions), ptr(ids), ptr(shared), ptr(strength), ptr(residual), ptr(gamma),
+         ptr(fused_normed), ptr(fused_residual), tokens, hidden, topk, 1e-6, stream_of(out))
+    assert torch.equal(fused_normed, normed) and torch.equal(fused_residual, new_residual)
+
