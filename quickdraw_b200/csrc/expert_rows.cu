@@ -302,6 +302,7 @@ static int expert_rows(const void* x, const void* x_up, const void* codes, const
     }
 }
 
+// One bank (the contract described above; a second bank: qd_nvfp4_expert_rows2 below).
 extern "C" int qd_nvfp4_expert_rows(const void* x, const void* x_up, const void* codes, const void* scales, const float* global,
                                     const int32_t* order, const int32_t* boundaries, const float* routing, void* y,
                                     int routes, int experts, int topk, int out_features, int in_features,
