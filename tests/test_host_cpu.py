@@ -226,3 +226,50 @@ def test_bench_byte_counts_of_a_step_and_of_a_batched_step():
     per_sequence = (large - small) / 32
     state = 36 * 2 * (32 * 128 * 128 * 4 + 8192 * 3 * 2) + 12 * 2 * 2 * 256 * 2 * 8193
     assert state < per_sequence < state + cfg.num_hidden_layers * 8 * expert
+
+
+@pytest.mark.parametrize("tokens,fp8", [(3, False), (70, False), (3, True), (40, True)])
+def test_chunk_and_batch_paths_pass_the_declared_number_of_arguments(monkeypatch, tokens, fp8):
+    """The Python drivers of the prompt-chunk and batched-decode paths, run on CPU tensors with the library
+    call replaced by a recorder: every call names a bound entry point and passes as many arguments as the
+    header declares for it (ctypes would not notice a missing trailing argument), and both paths reach
+    their few-row and many-row forms."""
+    from quickdraw_b200 import batch, prefill
+    from quickdraw_b200.state import DecodeState
+    seen = {}
+
+    def record(name, *args):
+        assert name in _lib.SIGNATURES, name
+        assert len(args) == len(_lib.SIGNATURES[name]), (name, len(args), len(_lib.SIGNATURES[name]))
+        seen[name] = seen.get(name, 0) + 1
+
+    class FakeLibrary:
+        def __getattr__(self, name):
+            assert name in _lib.SIGNATURES, name
+            return lambda *args: 4096 if name.endswith("_bytes") else 1
+
+    for module in (prefill, batch):
+        monkeypatch.setattr(module, "call", record)
+        monkeypatch.setattr(module, "lib", lambda: FakeLibrary())
+        monkeypatch.setattr(module, "stream_of", lambda t: None)
+    class AsIfOnGpu(torch.Tensor):         # the drivers refuse token ids that are not on a GPU
+        is_cuda = property(lambda self: True)
+
+    cfg = synthetic.model_config(num_layers=4, vocab_size=512, experts=16, topk=4)
+    ckpt = synthetic.make_checkpoint(cfg, seed=2, device="cpu", fp8_mixers=fp8, nvfp4_head=fp8)
+    state = DecodeState.allocate(cfg, 128, "cpu")
+    prefill.ChunkPrefill(ckpt).run((torch.arange(tokens) % cfg.vocab_size).as_subclass(AsIfOnGpu), 0, state)
+    assert seen.get("qd_seq_moe_combine_norm", 0) == 3 and "qd_seq_moe_combine" not in seen      # the last MoE block is not run
+    assert ("qd_fp8_matmul" in seen) == fp8
+    assert ("qd_nvfp4_expert_rows2" in seen) or ("qd_nvfp4_grouped_matmul" in seen)
+    chunk_calls = dict(seen)
+    seen.clear()
+    many = batch.BatchState(cfg, 3, 64, "cpu")
+    decoder = batch.BatchDecode(ckpt)
+    monkeypatch.setattr(decoder, "_attn_splits", lambda *a: 1, raising=False)
+    picked, logits = decoder.step(torch.tensor([1, 2, 3]).as_subclass(AsIfOnGpu), many)
+    assert picked.shape == (3,) and logits.shape == (3, cfg.vocab_size) and many.positions.tolist() == [1, 1, 1]
+    assert seen["qd_seq_moe_combine_norm"] == 4 and seen["qd_nvfp4_expert_rows2"] == 4 and seen["qd_seq_bf16_matmul2"] >= 4
+    assert "qd_nvfp4_matmul_rows3" in seen or fp8
+    assert chunk_calls
+
