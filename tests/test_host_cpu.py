@@ -273,3 +273,51 @@ def test_chunk_and_batch_paths_pass_the_declared_number_of_arguments(monkeypatch
     assert "qd_nvfp4_matmul_rows3" in seen or fp8
     assert chunk_calls
 
+
+def test_every_kernel_launched_as_a_programmatic_dependent_waits_for_its_predecessor():
+    """Source check: a kernel that qd_launch may start before the kernel in front of it has finished
+    (pdl argument other than false / 0) contains the wait, as chain_enter() or grid_dependency_wait()."""
+    sources = {path.name: path.read_text() for path in (ROOT / "quickdraw_b200" / "csrc").glob("*.cu*")}
+
+    def arguments(text, start):          # top-level arguments of the call whose "(" ends at `start`
+        depth, current, found, i = 0, "", [], start
+        while True:
+            ch = text[i]
+            if ch in "([":
+                depth += 1
+            elif ch in ")]":
+                if depth == 0:
+                    return found + [current.strip()]
+                depth -= 1
+            if ch == "," and depth == 0 and (found or current.count("<") == current.count(">")):      # template arguments of the kernel
+                found.append(current.strip())
+                current = ""
+            else:
+                current += ch
+            i += 1
+
+    def bodies(kernel):
+        for text in sources.values():
+            for match in re.finditer(r"__global__[^{;]*?\b" + kernel + r"\s*\(", text, flags=re.S):
+                start = text.index("{", match.end())
+                depth, end = 0, start
+                while True:
+                    depth += {"{": 1, "}": -1}.get(text[end], 0)
+                    if depth == 0:
+                        break
+                    end += 1
+                yield text[start:end]
+
+    dependents = 0
+    for name, text in sources.items():
+        for match in re.finditer(r"(?<!int )qd_launch\(", text):
+            args = arguments(text, match.end())
+            kernel, pdl = re.match(r"\w+", args[0]).group(0), args[5]
+            if pdl in ("false", "0"):
+                continue
+            found = list(bodies(kernel))
+            assert found, (name, kernel)
+            assert all("chain_enter();" in body or "grid_dependency_wait();" in body for body in found), (name, kernel)
+            dependents += 1
+    assert dependents >= 30
+
